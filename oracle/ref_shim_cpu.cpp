@@ -1,0 +1,104 @@
+// TEST INFRASTRUCTURE, NOT PRODUCT.  C entry points over the reference engine's own CPU code (its vendored ggml
+// quantisers/dequantisers and its CPU expert-offload pool), so the Python tests and the bench's cpu_baseline leg can call
+// them through ctypes.  This file is compiled together with the reference's sources, where they lie in the reference
+// checkout, into oracle/_ref/libref_cpu.so by oracle/Makefile; nothing from the reference is copied into this repository.
+//
+// Wrapped reference interfaces:
+//   ggml_get_type_traits / ggml_quantize_chunk          include/basalt/ggml/ggml.h:60-77
+//   cpu::native_fmt / native_quant_act / native_quant_h  include/basalt/kernels/cpu/native_expert.hpp:44-58
+//   cpu::ExpertPool::run_split_multi_native              include/basalt/kernels/cpu/pool.hpp:96-97
+#include "basalt/ggml/ggml.h"
+#include "basalt/kernels/cpu/native_expert.hpp"
+#include "basalt/kernels/cpu/pool.hpp"
+
+#include <cstdint>
+#include <cstring>
+#include <string>
+#include <vector>
+
+using namespace basalt::kernels;
+
+extern "C" {
+
+// Bytes of one row of n values of `type` (0 when the reference build does not carry the type).
+int64_t ref_row_bytes(int type, int64_t n) {
+    const ggml_type_traits* t = ggml_get_type_traits((ggml_type) type);
+    if (!t || n % t->blck_size) return 0;
+    return (int64_t) (n / t->blck_size * t->type_size);
+}
+
+// dst <- rows x cols floats quantised by the reference quantiser; returns bytes written (0: no quantiser).
+int64_t ref_quantize(int type, const float* src, void* dst, int64_t rows, int64_t cols) {
+    const ggml_type_traits* t = ggml_get_type_traits((ggml_type) type);
+    if (!t || !t->from_float_ref) return 0;
+    return (int64_t) ggml_quantize_chunk((ggml_type) type, src, dst, 0, rows, cols);
+}
+
+// y <- n values decoded by the reference's to_float; returns 0 on success.
+int ref_dequantize(int type, const void* src, float* y, int64_t n) {
+    const ggml_type_traits* t = ggml_get_type_traits((ggml_type) type);
+    if (!t || !t->to_float) return -1;
+    t->to_float(src, y, n);
+    return 0;
+}
+
+// The reference's blob geometry: out[0..6] = gu_row, d_row, up_off, down_off, bytes, tail, act_bytes; returns 0 or -1.
+int ref_native_fmt(int gu_type, int d_type, int64_t n_embd, int64_t n_ff, float swiglu_limit, int64_t* out, char* err,
+                   int err_len) {
+    cpu::NativeFmt f;
+    std::string e;
+    if (!cpu::native_fmt(gu_type, d_type, n_embd, n_ff, f, e, swiglu_limit)) {
+        if (err && err_len > 0) { std::strncpy(err, e.c_str(), (size_t) err_len - 1); err[err_len - 1] = 0; }
+        return -1;
+    }
+    out[0] = (int64_t) f.gu_row; out[1] = (int64_t) f.d_row; out[2] = (int64_t) f.up_off; out[3] = (int64_t) f.down_off;
+    out[4] = (int64_t) f.bytes; out[5] = (int64_t) f.tail; out[6] = (int64_t) f.act_bytes;
+    return 0;
+}
+
+struct RefPool {
+    cpu::ExpertPool* pool;
+};
+
+void* ref_pool_create(int n_workers) { return new RefPool{new cpu::ExpertPool(n_workers < 1 ? 1 : n_workers)}; }
+void ref_pool_destroy(void* p) {
+    if (!p) return;
+    RefPool* rp = (RefPool*) p;
+    delete rp->pool;
+    delete rp;
+}
+int ref_pool_workers(void* p) { return ((RefPool*) p)->pool->workers(); }
+
+// The reference's CPU expert-offload path for one layer step: `n_pairs` (token, expert) pairs grouped by the caller into
+// expert-sorted rows.  blobs[e] = expert e's blob; off[E+1] = row offsets per expert; src[row] = token of that row;
+// x = [T][n_embd] fp32.  Each row's unweighted expert output lands in rows_out[row][n_embd].  Experts with more than
+// MAXT rows are cut into several jobs, as the engine's callers do (include/basalt/kernels/cpu/expert.hpp:74).
+// Returns 0, or -1 when the reference refuses the geometry.
+int ref_pool_layer(void* p, int gu_type, int d_type, int64_t n_embd, int64_t n_ff, float swiglu_limit,
+                   const uint8_t* const* blobs, int n_expert, const int32_t* off, const int32_t* src, const float* x,
+                   int T, float* rows_out) {
+    cpu::NativeFmt f;
+    std::string e;
+    if (!cpu::native_fmt(gu_type, d_type, n_embd, n_ff, f, e, swiglu_limit)) return -1;
+    // quantise every token's activation once (the caller's native_quant_act)
+    std::vector<uint8_t> act((size_t) T * f.act_bytes);
+    for (int t = 0; t < T; ++t) cpu::native_quant_act(f, x + (size_t) t * n_embd, act.data() + (size_t) t * f.act_bytes);
+    std::vector<cpu::ExpertJobMulti> jobs;
+    for (int ex = 0; ex < n_expert; ++ex) {
+        for (int r0 = off[ex]; r0 < off[ex + 1]; r0 += cpu::MAXT) {
+            cpu::ExpertJobMulti j;
+            j.blob = blobs[ex];
+            j.nt = off[ex + 1] - r0 < cpu::MAXT ? off[ex + 1] - r0 : cpu::MAXT;
+            for (int i = 0; i < j.nt; ++i) {
+                j.nact[i] = act.data() + (size_t) src[r0 + i] * f.act_bytes;
+                j.out[i] = rows_out + (size_t) (r0 + i) * n_embd;
+            }
+            jobs.push_back(j);
+        }
+    }
+    cpu::ExpertPool* pool = ((RefPool*) p)->pool;
+    if (!jobs.empty()) pool->run_split_multi_native(f, jobs.data(), (int) jobs.size());   // batches internally
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,117 @@
+// TEST INFRASTRUCTURE, NOT PRODUCT.  C entry points over the reference engine's own portable CUDA kernels for the
+// MoE-layer path, compiled from the reference checkout for sm_100a into oracle/_ref/libref_gpu.so by oracle/Makefile.
+// The GPU parity tests use it as the on-device oracle for bit-exact routing (the reference's own expf/logf code paths)
+// and as a behavioural check of the grouped decode experts.  Nothing from the reference is copied into this repository.
+//
+// Wrapped reference interfaces:
+//   router / router_select            include/basalt/kernels/router.hpp:30-37
+//   route_tail_skip                   include/basalt/kernels/route_lossy.hpp:58-59
+//   router_top10                      include/basalt/models/qwen4exp/kernels/router_top10.hpp
+//   native_router_top10_multi         include/basalt/models/qwen4exp/kernels/native_router.hpp
+//   quantize_q8_1_rows, native_expert_layout, native_expert_scratch_bytes, native_expert_grouped
+//                                     include/basalt/kernels/iq_kernels.hpp:23,68,75,84
+//   native_moe_combine_multi          include/basalt/models/qwen4exp/kernels/native_moe.hpp
+#include "basalt/kernels/iq_kernels.hpp"
+#include "basalt/kernels/router.hpp"
+#include "basalt/models/qwen4exp/kernels/native_moe.hpp"
+#include "basalt/models/qwen4exp/kernels/native_router.hpp"
+#include "basalt/models/qwen4exp/kernels/router_top10.hpp"
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <exception>
+
+using namespace basalt::kernels;
+
+extern "C" {
+
+// All pointers are device pointers.  Returns 0, -1 on a reference exception, or the CUDA error after synchronising.
+static int finish() {
+    const cudaError_t e = cudaDeviceSynchronize();
+    return e == cudaSuccess ? 0 : (int) e;
+}
+
+int refg_router(const float* x, const float* gate, const float* bias, int T, int n_expert, int n_embd, int k, float scale,
+                int gate_kind, float* logits, int32_t* ids, float* weights) {
+    RouterArgs a;
+    a.n_expert = n_expert; a.n_embd = n_embd; a.k = k; a.weight_scale = scale;
+    a.gate = gate_kind == 1 ? RouterGate::Sigmoid : RouterGate::SqrtSoftplus;
+    try { router(x, gate, bias, T, a, logits, ids, weights, nullptr); } catch (const std::exception&) { return -1; }
+    return finish();
+}
+
+int refg_router_select(const float* logits, const float* bias, int T, int n_expert, int k, float scale, int gate_kind,
+                       float prior, const int32_t* held, int32_t* ids, float* weights) {
+    RouterArgs a;
+    a.n_expert = n_expert; a.k = k; a.weight_scale = scale; a.prior = prior;
+    a.gate = gate_kind == 1 ? RouterGate::Sigmoid : RouterGate::SqrtSoftplus;
+    if (held) a.held.add(held);
+    try { router_select(logits, bias, T, a, ids, weights, nullptr); } catch (const std::exception&) { return -1; }
+    return finish();
+}
+
+int refg_route_tail_skip(int32_t* ids, float* weights, const int32_t* held, int n_entries, int k, int rank, int n_expert,
+                         unsigned long long* counts) {
+    ResidentTabs tabs;
+    if (held) tabs.add(held);
+    route_tail_skip(ids, weights, tabs, n_entries, k, rank, n_expert, counts, nullptr);
+    return finish();
+}
+
+int refg_router_top10(const float* logits, int T, int n_expert, int k, int32_t* ids, float* weights) {
+    router_top10(logits, T, n_expert, k, ids, weights, nullptr);
+    return finish();
+}
+
+// the fp32 one-warp softmax router (512 experts, top-10 only; fast-math translation unit)
+int refg_native_router_top10(const float* logits, int T, int32_t* ids, float* weights) {
+    cudaStream_t s;
+    if (cudaStreamCreate(&s) != cudaSuccess) return -2;
+    int rc = 0;
+    try { native_router_top10_multi(logits, ids, weights, T, s); } catch (const std::exception&) { rc = -1; }
+    const int f = finish();
+    cudaStreamDestroy(s);
+    return rc ? rc : f;
+}
+
+int refg_quantize_q8_1(const float* x, int64_t rows, int64_t cols, void* y) {
+    quantize_q8_1_rows(x, rows, cols, y, nullptr);
+    return finish();
+}
+
+int64_t refg_expert_blob_bytes(int gu_type, int d_type, int64_t n_embd, int64_t n_ff) {
+    if (!native_expert_supported(gu_type, d_type, n_embd, n_ff)) return 0;
+    return (int64_t) native_expert_layout(gu_type, d_type, n_embd, n_ff).bytes;
+}
+int64_t refg_expert_scratch_bytes(int64_t cap_entries, int64_t n_ff) {
+    return (int64_t) native_expert_scratch_bytes(cap_entries, n_ff);
+}
+
+// the reference's grouped decode experts on q8_1 activations (unweighted rows out)
+int refg_expert_grouped(int gu_type, int d_type, int64_t n_embd, int64_t n_ff, float swiglu_limit,
+                        const unsigned long long* grp_ptr, const int32_t* grp_start, const int32_t* n_groups,
+                        const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups, int64_t cap_entries,
+                        const void* x_q8_1, void* scratch, float* out) {
+    if (!native_expert_supported(gu_type, d_type, n_embd, n_ff)) return -1;
+    const NativeExpertLayout L = native_expert_layout(gu_type, d_type, n_embd, n_ff, swiglu_limit);
+    cudaStream_t s;
+    if (cudaStreamCreate(&s) != cudaSuccess) return -2;
+    native_expert_grouped(L, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups, cap_entries, x_q8_1, scratch, out, s);
+    const int f = finish();
+    cudaStreamDestroy(s);
+    return f;
+}
+
+int refg_combine_multi(const float* parts, const float* weights, const float* shared, float* output, int64_t n_embd,
+                       int64_t k, int n_tok) {
+    cudaStream_t s;
+    if (cudaStreamCreate(&s) != cudaSuccess) return -2;
+    int rc = 0;
+    try { native_moe_combine_multi(parts, weights, shared, output, n_embd, k, n_tok, s); } catch (const std::exception&) { rc = -1; }
+    const int f = finish();
+    cudaStreamDestroy(s);
+    return rc ? rc : f;
+}
+
+}  // extern "C"
