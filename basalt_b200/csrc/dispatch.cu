@@ -1,0 +1,263 @@
+// dispatch.cu - token-to-expert dispatch on sm_100a: expert histogram, prefix-sum offsets, stable permutation, tile list,
+// and the decode-window plan.
+//
+// Replaces the Basalt engine's host counting sort (src/models/qwen4exp/prefill/routing.cpp:67-108, which costs a device-to-host
+// copy, a stream synchronise and a host-to-device copy per layer), its GPU grouping (src/models/qwen4exp/prefill/moe_fused.cu:
+// 99-168, whose atomicAdd cursors leave the row order inside an expert undefined) and the decode plan
+// (src/models/inkling2/kernels/ops.cu:275-340).  Here the permutation is the host path's stable counting sort, computed on
+// the device without position atomics: every warp owns a contiguous chunk of pairs, counts it, a scan turns the
+// [expert][chunk] counts into chunk bases, and each warp places its pairs in order with __match_any_sync ranks.
+#include "common.cuh"
+
+namespace bsx {
+namespace {
+
+constexpr int kChunk = 256;          // pairs per warp chunk
+constexpr int kWarpsPerBlock = 8;
+constexpr int kMaxExpert = 1024;
+
+__host__ __device__ inline int64_t n_chunks_of(int64_t n) { return (n + kChunk - 1) / kChunk; }
+
+// per-warp histogram of one chunk -> tbl[e * n_chunks + c]
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+dispatch_count_kernel(const int32_t* __restrict__ ids, int64_t n, int E, int n_chunks, int32_t* __restrict__ tbl) {
+    extern __shared__ int32_t hist[];   // [warps][E]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * kWarpsPerBlock + warp;
+    int32_t* h = hist + (size_t) warp * E;
+    for (int e = lane; e < E; e += 32) h[e] = 0;
+    __syncwarp();
+    if (c < n_chunks) {
+        const int64_t i0 = (int64_t) c * kChunk;
+        for (int j = 0; j < kChunk; j += 32) {
+            const int64_t i = i0 + j + lane;
+            const int e = i < n ? ids[i] : -1;
+            const bool ok = (unsigned) e < (unsigned) E;
+            const unsigned peers = __match_any_sync(kFull, ok ? e : -1 - lane);
+            if (ok && (__ffs(peers) - 1) == lane) h[e] += __popc(peers);
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32) tbl[(size_t) e * n_chunks + c] = h[e];
+    }
+}
+
+// block-wide exclusive sum (blockDim a multiple of 32, at most 1024); *total = the block's sum
+__device__ int block_excl_sum(int v, int* total, int* sh) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    int x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(kFull, x, o);
+        if (lane >= o) x += y;
+    }
+    if (lane == 31) sh[w] = x;
+    __syncthreads();
+    if (w == 0) {
+        int s = lane < nw ? sh[lane] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(kFull, s, o);
+            if (lane >= o) s += y;
+        }
+        sh[lane] = s;
+    }
+    __syncthreads();
+    const int r = x - v + (w > 0 ? sh[w - 1] : 0);
+    *total = sh[nw - 1];
+    __syncthreads();
+    return r;
+}
+
+// one block of 1024 threads: (1) a warp per expert scans its chunk counts into exclusive chunk bases and the expert's
+// total; (2) a block scan over the experts gives off[], and the tile list.
+__global__ void __launch_bounds__(1024)
+dispatch_scan_kernel(int E, int n_chunks, int32_t* __restrict__ tbl, int32_t* __restrict__ cnt, int32_t* __restrict__ off,
+                     int tile_rows, int32_t* __restrict__ tiles, int32_t* __restrict__ n_tiles) {
+    __shared__ int s_cnt[kMaxExpert];
+    __shared__ int sh[32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int e = warp; e < E; e += nw) {
+        int32_t* row = tbl + (size_t) e * n_chunks;
+        int carry = 0;
+        for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+            const int c = c0 + lane;
+            const int v = c < n_chunks ? row[c] : 0;
+            int x = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_up_sync(kFull, x, o);
+                if (lane >= o) x += y;
+            }
+            if (c < n_chunks) row[c] = carry + x - v;
+            carry += __shfl_sync(kFull, x, 31);
+        }
+        if (lane == 0) s_cnt[e] = carry;
+    }
+    __syncthreads();
+    const int e = threadIdx.x;
+    const int c = e < E ? s_cnt[e] : 0;
+    const int nt = tile_rows > 0 ? (c + tile_rows - 1) / tile_rows : 0;
+    int rows = 0, ntl = 0;
+    const int o = block_excl_sum(c, &rows, sh);
+    const int to = block_excl_sum(nt, &ntl, sh);
+    if (e < E) {
+        cnt[e] = c;
+        off[e] = o;
+        if (tiles)
+            for (int i = 0; i < nt; ++i) {
+                tiles[2 * (to + i)] = e;
+                tiles[2 * (to + i) + 1] = o + i * tile_rows;
+            }
+    }
+    if (e == 0) {
+        off[E] = rows;
+        if (n_tiles) *n_tiles = ntl;
+    }
+}
+
+// each warp replays its chunk in order: a pair's row = off[e] + (pairs of e in earlier chunks) + (earlier pairs of e in
+// this chunk), the last term from a per-warp running count plus the pair's rank among the lanes holding the same expert.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+dispatch_place_kernel(const int32_t* __restrict__ ids, int64_t n, int k, int E, int n_chunks, const int32_t* __restrict__ tbl,
+                      const int32_t* __restrict__ off, int32_t* __restrict__ slot, int32_t* __restrict__ src) {
+    extern __shared__ int32_t run[];   // [warps][E]: absolute next row of expert e for this chunk
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * kWarpsPerBlock + warp;
+    if (c >= n_chunks) return;
+    int32_t* r = run + (size_t) warp * E;
+    for (int e = lane; e < E; e += 32) r[e] = off[e] + tbl[(size_t) e * n_chunks + c];
+    __syncwarp();
+    const int64_t i0 = (int64_t) c * kChunk;
+    const unsigned lt = (1u << lane) - 1u;
+    for (int j = 0; j < kChunk; j += 32) {
+        const int64_t i = i0 + j + lane;
+        const int e = i < n ? ids[i] : -1;
+        const bool ok = (unsigned) e < (unsigned) E;
+        const unsigned peers = __match_any_sync(kFull, ok ? e : -1 - lane);
+        int p = -1;
+        if (ok) p = r[e] + __popc(peers & lt);
+        __syncwarp();
+        if (ok && (__ffs(peers) - 1) == lane) r[e] += __popc(peers);
+        __syncwarp();
+        if (i < n) {
+            slot[i] = p;
+            if (ok) src[p] = (int32_t) (i / k);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- decode-window plan
+// One block.  Counts per expert in shared memory, one warp scans the experts into compacted groups, then the pairs are
+// placed in pair order: the block walks the pairs 32 at a time per warp, warps taking turns, so an expert's entries keep
+// the order of the pairs (the reference counts the earlier equal ids instead, ops.cu:331-339; the result is the same).
+__global__ void __launch_bounds__(256)
+moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsigned long long* __restrict__ blobs,
+                unsigned long long* __restrict__ ptr, int32_t* __restrict__ start, int32_t* __restrict__ n_groups,
+                int32_t* __restrict__ dst, int32_t* __restrict__ tok) {
+    extern __shared__ unsigned long long smb[];
+    unsigned long long* blob = smb;                               // [E]
+    int32_t* count = reinterpret_cast<int32_t*>(smb + E);         // [E]
+    int32_t* next = count + E;                                    // [E]: the expert's next entry
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        blob[e] = blobs[e];
+        count[e] = 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = ids[i];
+        if ((unsigned) e < (unsigned) E && blob[e]) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int at = 0, g = 0;
+        for (int e0 = 0; e0 < E; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < E ? count[e] : 0;
+            int s = c, used = c > 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int a = __shfl_up_sync(kFull, s, o), u = __shfl_up_sync(kFull, used, o);
+                if (lane >= o) { s += a; used += u; }
+            }
+            if (e < E) next[e] = at + s - c;
+            if (c > 0) {
+                ptr[g + used - 1] = blob[e];
+                start[g + used - 1] = at + s - c;
+            }
+            at += __shfl_sync(kFull, s, 31);
+            g += __shfl_sync(kFull, used, 31);
+        }
+        if (lane == 0) {
+            start[g] = at;
+            start[g + 1] = at;
+            *n_groups = g;
+        }
+    }
+    __syncthreads();
+    const unsigned lt = (1u << lane) - 1u;
+    for (int i0 = 0; i0 < n; i0 += blockDim.x) {
+        for (int w = 0; w < nw; ++w) {
+            if (warp == w) {
+                const int i = i0 + w * 32 + lane;
+                const int e = i < n ? ids[i] : -1;
+                const bool ok = (unsigned) e < (unsigned) E && blob[e] != 0ull;
+                const unsigned peers = __match_any_sync(kFull, ok ? e : -1 - lane);
+                int at = -1;
+                if (ok) at = next[e] + __popc(peers & lt);
+                __syncwarp();
+                if (ok && (__ffs(peers) - 1) == lane) next[e] += __popc(peers);
+                if (ok) {
+                    dst[at] = i;
+                    tok[at] = i / k;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+}  // namespace
+}  // namespace bsx
+
+using namespace bsx;
+
+extern "C" size_t bsx_dispatch_scratch_bytes(int64_t n_pairs, int32_t E) {
+    if (n_pairs < 0 || E < 1) return 0;
+    const int64_t nc = n_chunks_of(n_pairs > 0 ? n_pairs : 1);
+    return (size_t) E * (size_t) nc * sizeof(int32_t) + 256;
+}
+
+extern "C" int32_t bsx_dispatch(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t E, int32_t* cnt, int32_t* off,
+                                int32_t* slot, int32_t* src, int32_t tile_rows, int32_t* tiles, int32_t* n_tiles, void* scratch,
+                                void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (E < 1 || E > kMaxExpert || k < 1 || n_pairs < 0 || n_pairs > (int64_t) 1 << 30 || tile_rows < 0) return BSX_E_GEOMETRY;
+    if (!cnt || !off || !scratch || (n_pairs > 0 && (!ids || !slot || !src))) return BSX_E_POINTER;
+    if (tile_rows > 0 && (!tiles || !n_tiles)) return BSX_E_POINTER;
+    const cudaStream_t st = (cudaStream_t) stream;
+    const int nc = (int) n_chunks_of(n_pairs > 0 ? n_pairs : 1);
+    int32_t* tbl = (int32_t*) scratch;
+    const unsigned blocks = (unsigned) ((nc + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    const size_t smem = (size_t) kWarpsPerBlock * E * sizeof(int32_t);
+    dispatch_count_kernel<<<blocks, kWarpsPerBlock * 32, smem, st>>>(ids, n_pairs, E, nc, tbl);
+    dispatch_scan_kernel<<<1, 1024, 0, st>>>(E, nc, tbl, cnt, off, tile_rows, tile_rows > 0 ? tiles : nullptr,
+                                              tile_rows > 0 ? n_tiles : nullptr);
+    if (n_pairs > 0)
+        dispatch_place_kernel<<<blocks, kWarpsPerBlock * 32, smem, st>>>(ids, n_pairs, k, E, nc, tbl, off, slot, src);
+    return launch_status();
+}
+
+extern "C" int32_t bsx_moe_plan(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table,
+                                unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok,
+                                void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    const int64_t n = (int64_t) T * k;
+    if (n <= 0) return BSX_OK;   // the reference returns without touching its outputs (ops.cu:491)
+    if (n > BSX_PLAN_MAX_PAIRS) return BSX_E_LIMIT;
+    if (E < 1 || E > 4096) return BSX_E_GEOMETRY;
+    if (!ids || !blob_table || !ptr || !start || !n_groups || !dst || !tok) return BSX_E_POINTER;
+    const size_t smem = (size_t) E * (sizeof(unsigned long long) + 2 * sizeof(int32_t));
+    moe_plan_kernel<<<1, 256, smem, (cudaStream_t) stream>>>(ids, (int) n, k, E, blob_table, ptr, start, n_groups, dst, tok);
+    return launch_status();
+}

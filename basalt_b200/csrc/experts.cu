@@ -1,0 +1,218 @@
+// experts.cu - entry points of the expert stage: blob geometry, q8_1 activation rows, the grouped decode experts and the
+// weighted combine.
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+#include "experts.cuh"
+#include "formats.cuh"
+
+namespace bsx {
+namespace {
+
+__device__ const uint16_t g_iq1_grid[2048] = {
+#include "iq1_grid_u16.inc"
+};
+const uint16_t h_iq1_grid[2048] = {
+#include "iq1_grid_u16.inc"
+};
+
+const uint16_t* device_grid() {
+    static const uint16_t* cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cached[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_iq1_grid) != cudaSuccess) return nullptr;
+        cached[dev] = static_cast<const uint16_t*>(p);
+    }
+    return cached[dev];
+}
+
+// src/kernels/cuda/iq_kernels.cu:2471-2503 with include/basalt/kernels/q8_1_finite.hpp:17-31: a warp per 32 values
+__global__ void __launch_bounds__(256) quantize_q8_1_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, int64_t n) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;   // n % 32 == 0: whole warps leave together
+    const float xi = x[i];
+    float amax = fabsf(xi), sum = xi;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, o));
+        sum += __shfl_xor_sync(kFull, sum, o);
+    }
+    float d = amax / 127.0f;
+    if (fabsf(d) > 65504.0f) d = copysignf(65504.0f, d);
+    float q = 0.0f;
+    if (amax != 0.0f) {
+        q = roundf(xi / d);
+        q = q > 127.0f ? 127.0f : q < -127.0f ? -127.0f : q;
+    }
+    uint8_t* blk = y + (i / 32) * 36;
+    blk[4 + (i & 31)] = (uint8_t) (int8_t) q;
+    if ((i & 31) == 0) {
+        if (fabsf(sum) > 65504.0f) sum = copysignf(65504.0f, sum);
+        reinterpret_cast<__half2*>(blk)[0] = __halves2half2(__float2half(d), __float2half(sum));
+    }
+}
+
+// y[t] = fma chain over the k rows in order, then the shared expert: src/models/qwen4exp/kernels/native_moe.cu:36-50 and
+// src/models/qwen4exp/prefill/kernels.cu:438-449 (bit-equal forms).  A thread owns 4 consecutive columns.
+__global__ void __launch_bounds__(256)
+combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ slot, const float* __restrict__ w,
+               const float* __restrict__ shared, const float* __restrict__ sg, int k, int H, float* __restrict__ y) {
+    const int t = blockIdx.y;
+    const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c4 * 4 >= H) return;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < k; ++j) {
+        const int64_t r = slot ? (int64_t) slot[(size_t) t * k + j] : (int64_t) t * k + j;
+        if (r < 0) continue;
+        const float wj = w[(size_t) t * k + j];
+        const float4 p = reinterpret_cast<const float4*>(rows + (size_t) r * H)[c4];
+        s.x = fmaf(wj, p.x, s.x);
+        s.y = fmaf(wj, p.y, s.y);
+        s.z = fmaf(wj, p.z, s.z);
+        s.w = fmaf(wj, p.w, s.w);
+    }
+    if (shared) {
+        const float4 p = reinterpret_cast<const float4*>(shared + (size_t) t * H)[c4];
+        if (sg) {
+            const float gate = 1.0f / (1.0f + expf(-sg[t]));
+            s.x = fmaf(p.x, gate, s.x);
+            s.y = fmaf(p.y, gate, s.y);
+            s.z = fmaf(p.z, gate, s.z);
+            s.w = fmaf(p.w, gate, s.w);
+        } else {
+            s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
+        }
+    }
+    reinterpret_cast<float4*>(y + (size_t) t * H)[c4] = s;
+}
+
+size_t row_bytes(int type, int64_t n) {
+    if (!type_supported(type) || n <= 0 || n % block_values(type)) return 0;
+    return (size_t) (n / block_values(type)) * (size_t) block_bytes(type);
+}
+
+}  // namespace
+}  // namespace bsx
+
+using namespace bsx;
+
+extern "C" size_t bsx_row_bytes(int32_t type, int64_t n) { return row_bytes(type, n); }
+extern "C" const char* bsx_version(void) { return "basalt_b200 0.1 (sm_100a)"; }
+
+extern "C" int32_t bsx_host_decode_row(int32_t type, const void* row, float* y, int64_t n) {
+    if (!row_bytes(type, n) || !row || !y) return BSX_E_TYPE;
+    const uint8_t* b = static_cast<const uint8_t*>(row);
+    if (type == kTypeNVFP4) {
+        for (int64_t i = 0; i < n / 64; ++i) decode_block_nvfp4(b + i * 36, y + i * 64);
+    } else if (type == kTypeQ6K) {
+        for (int64_t u = 0; u < n / 32; ++u) decode_q6k_32(b + (u >> 3) * 210, (int) (u & 7), y + u * 32);
+    } else {
+        for (int64_t u = 0; u < n / 32; ++u) decode_iq1m_32(b + (u >> 3) * 56, (int) (u & 7), h_iq1_grid, y + u * 32);
+    }
+    return BSX_OK;
+}
+
+extern "C" int32_t bsx_expert_supported(int32_t gu_type, int32_t d_type, int32_t up_type, int64_t n_embd, int64_t n_ff) {
+    if (up_type < 0) up_type = gu_type;
+    if (!type_supported(gu_type) || !type_supported(d_type) || !type_supported(up_type)) return 0;
+    // NVFP4 tail scales belong to an all-NVFP4 gate/up pair (src/kernels/cuda/iq_kernels.cu:3236)
+    if ((gu_type == kTypeNVFP4) != (up_type == kTypeNVFP4)) return 0;
+    if (n_embd <= 0 || n_ff <= 0 || n_embd % 256 || n_embd > 16384 || n_ff > 16384) return 0;
+    if (!row_bytes(gu_type, n_embd) || !row_bytes(up_type, n_embd) || !row_bytes(d_type, n_ff)) return 0;
+    return 1;
+}
+
+extern "C" int32_t bsx_expert_layout_init(int32_t gu_type, int32_t d_type, int32_t up_type, int64_t n_embd, int64_t n_ff,
+                                          float swiglu_limit, float gate_softcap, float up_softcap, bsx_expert_layout* L) {
+    if (!L) return BSX_E_POINTER;
+    if (up_type < 0) up_type = gu_type;
+    if (!bsx_expert_supported(gu_type, d_type, up_type, n_embd, n_ff)) return BSX_E_TYPE;
+    memset(L, 0, sizeof *L);
+    L->gu_type = gu_type;
+    L->d_type = d_type;
+    L->up_type = up_type;
+    L->n_embd = n_embd;
+    L->n_ff = n_ff;
+    L->gu_row = row_bytes(gu_type, n_embd);
+    L->up_row = row_bytes(up_type, n_embd);
+    L->d_row = row_bytes(d_type, n_ff);
+    L->up_off = (uint64_t) n_ff * L->gu_row;
+    L->down_off = L->up_off + (uint64_t) n_ff * L->up_row;
+    L->bytes = L->down_off + (uint64_t) n_embd * L->d_row + (gu_type == kTypeNVFP4 ? 16 : 0);
+    L->swiglu_limit = swiglu_limit;
+    L->gate_softcap = gate_softcap;
+    L->up_softcap = up_softcap;
+    return BSX_OK;
+}
+
+extern "C" size_t bsx_expert_scratch_bytes(int64_t cap_entries, int64_t n_ff) {
+    if (cap_entries < 0 || n_ff < 0) return 0;
+    const size_t f = (((size_t) cap_entries * (size_t) n_ff * sizeof(float)) + 255) & ~(size_t) 255;
+    return f + 4096;
+}
+
+extern "C" int32_t bsx_quantize_q8_1_rows(const float* x, int64_t n_rows, int64_t n_cols, void* y, void* stream) {
+    if (n_rows < 0 || n_cols < 0 || n_cols % 32) return BSX_E_GEOMETRY;
+    const int64_t n = n_rows * n_cols;
+    if (n == 0) return BSX_OK;
+    if (!x || !aligned(y, 4)) return BSX_E_POINTER;
+    quantize_q8_1_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, (cudaStream_t) stream>>>(x, (uint8_t*) y, n);
+    const int32_t rc = launch_status();
+    if (rc == BSX_OK && !stream) {
+        const cudaError_t e = cudaStreamSynchronize(nullptr);
+        if (e != cudaSuccess) return (int32_t) e;
+    }
+    return rc;
+}
+
+extern "C" int32_t bsx_experts_grouped(const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
+                                       const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
+                                       int64_t cap_entries, const void* x, int32_t x_kind, void* scratch, void* out,
+                                       int32_t out_kind, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (!layout) return BSX_E_POINTER;
+    if (!bsx_expert_supported(layout->gu_type, layout->d_type, layout->up_type, layout->n_embd, layout->n_ff)) return BSX_E_TYPE;
+    if (x_kind < BSX_X_F32 || x_kind > BSX_X_Q8_1 || (out_kind != BSX_OUT_F32 && out_kind != BSX_OUT_BF16)) return BSX_E_GEOMETRY;
+    if (cap_groups < 0 || cap_entries < 0 || cap_entries > (int64_t) 1 << 30) return BSX_E_GEOMETRY;
+    if (cap_groups == 0 || cap_entries == 0) return BSX_OK;
+    if (!grp_ptr || !grp_start || !n_groups || !ent_dst || !ent_tok || !aligned(x, 16) || !aligned(scratch, 16) || !aligned(out, 16))
+        return BSX_E_POINTER;
+    ExpertArgs a;
+    a.L = *layout;
+    a.grp_ptr = grp_ptr;
+    a.grp_start = grp_start;
+    a.n_groups = n_groups;
+    a.ent_dst = ent_dst;
+    a.ent_tok = ent_tok;
+    a.cap_groups = cap_groups;
+    a.cap_entries = cap_entries;
+    a.x = x;
+    a.x_kind = x_kind;
+    a.h = static_cast<float*>(scratch);
+    a.out = out;
+    a.out_kind = out_kind;
+    a.grid = device_grid();
+    if (!a.grid) return (int32_t) cudaErrorInvalidSymbol;
+    const cudaStream_t st = (cudaStream_t) stream;
+    // BSX_EXPERT_IMPL=simple forces the plain kernels (tests compare the two paths)
+    static const bool force_simple = [] { const char* e = getenv("BSX_EXPERT_IMPL"); return e && !strcmp(e, "simple"); }();
+    if (!force_simple) {
+        const int32_t rc = experts_grouped_mma(a, st);
+        if (rc != BSX_E_TYPE) return rc;
+    }
+    return experts_grouped_simple(a, st);
+}
+
+extern "C" int32_t bsx_combine(const float* rows, const int32_t* slot, const float* weights, const float* shared,
+                               const float* shared_gate, int32_t T, int32_t k, int32_t H, float* y, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (T < 0 || k < 1 || k > 64 || H < 4 || H % 4) return BSX_E_GEOMETRY;
+    if (T == 0) return BSX_OK;
+    if (!aligned(rows, 16) || !weights || !aligned(y, 16) || (shared && !aligned(shared, 16))) return BSX_E_POINTER;
+    const dim3 grid((unsigned) ((H / 4 + 255) / 256), (unsigned) T);
+    combine_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(rows, slot, weights, shared, shared_gate, k, H, y);
+    return launch_status();
+}

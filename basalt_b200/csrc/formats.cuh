@@ -1,0 +1,115 @@
+// formats.cuh - exact decoders of the ggml block formats the expert kernels read (NVFP4, Q6_K, IQ1_M).
+//
+// The meaning of every weight byte is the reference's (paths inside the Basalt project): block layouts
+// include/basalt/ggml/ggml_common.h:146-156 (NVFP4), :279-285 (Q6_K), :350-362 (IQ1_M); decoding rules
+// src/kernels/cpu/ggml/ggml_quants.c:1397-1422 (NVFP4, UE4M3 scale), :1048-1075 (Q6_K), :1266-1314 (IQ1_M).
+// All functions are __host__ __device__ so the same code is checked on the CPU against the reference's to_float.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bsx {
+
+enum : int { kTypeQ6K = 14, kTypeIQ1M = 29, kTypeNVFP4 = 40 };
+
+// values per block and bytes per block
+__host__ __device__ constexpr int block_values(int type) { return type == kTypeNVFP4 ? 64 : 256; }
+__host__ __device__ constexpr int block_bytes(int type) { return type == kTypeNVFP4 ? 36 : type == kTypeQ6K ? 210 : type == kTypeIQ1M ? 56 : 0; }
+
+__host__ __device__ inline bool type_supported(int type) { return type == kTypeNVFP4 || type == kTypeQ6K || type == kTypeIQ1M; }
+
+// UE4M3 scale byte as ggml reads it, already halved (the E2M1 table below is doubled): bit 7 ignored, 0 and 0x7F -> 0.
+// (b & 0x7F) << 20 places the 4 exponent bits and 3 mantissa bits where fp32 keeps them; 2^(127-7-1) re-biases, and the
+// same product is exact for UE4M3 subnormals because an fp32 subnormal times a power of two is exact.
+__host__ __device__ __forceinline__ float ue4m3_half(uint32_t b) {
+    b &= 0x7Fu;
+    if (b == 0x7Fu) return 0.0f;
+    const uint32_t u = b << 20;
+#ifdef __CUDA_ARCH__
+    return __uint_as_float(u) * 6.646139978924579e35f;   // 2^119
+#else
+    float f;
+    memcpy(&f, &u, 4);
+    return f * 6.646139978924579e35f;
+#endif
+}
+
+// E2M1 code -> doubled value {0,1,2,3,4,6,8,12} with sign (ggml's kvalues_fp4)
+__host__ __device__ __forceinline__ float e2m1_x2(uint32_t c) {
+    const uint32_t m = c & 7u;
+    const float v = m < 4u ? (float) m : m == 4u ? 4.0f : m == 5u ? 6.0f : m == 6u ? 8.0f : 12.0f;
+    return ((c & 8u) && m) ? -v : v;   // code 8 is +0, as in ggml's integer table
+}
+
+__host__ __device__ __forceinline__ float half_bits_to_float(uint16_t h) {
+#ifdef __CUDA_ARCH__
+    return __half2float(__ushort_as_half(h));
+#else
+    const uint32_t s = (uint32_t) (h & 0x8000) << 16;
+    uint32_t e = (h >> 10) & 0x1F, m = h & 0x3FF, u;
+    if (e == 0) {
+        if (m == 0) u = s;
+        else {
+            int sh = 0;
+            while (!(m & 0x400)) { m <<= 1; ++sh; }
+            u = s | ((uint32_t) (113 - sh) << 23) | ((m & 0x3FF) << 13);
+        }
+    } else if (e == 31) u = s | 0x7F800000u | (m << 13);
+    else u = s | ((e + 112) << 23) | (m << 13);
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+#endif
+}
+
+// ---- whole-block decoders (the simple kernels and the host check use these; the fast kernels decode in fragment order)
+
+// one NVFP4 block (36 bytes, 4-byte aligned) -> 64 floats
+__host__ __device__ inline void decode_block_nvfp4(const uint8_t* b, float* y) {
+    for (int s = 0; s < 4; ++s) {
+        const float d = ue4m3_half(b[s]);
+        const uint8_t* q = b + 4 + 8 * s;
+        for (int j = 0; j < 8; ++j) {
+            y[16 * s + j] = e2m1_x2(q[j] & 15u) * d;
+            y[16 * s + j + 8] = e2m1_x2(q[j] >> 4) * d;
+        }
+    }
+}
+
+// 32 consecutive values [32u, 32u+32) of a Q6_K block (210 bytes, 2-byte aligned)
+__host__ __device__ inline void decode_q6k_32(const uint8_t* b, int u, float* y) {
+    const int half = u >> 2, sub = u & 3;              // 128-value half, 32-value quarter inside it
+    const uint8_t* ql = b + 64 * half + 32 * (sub & 1);
+    const uint8_t* qh = b + 128 + 32 * half;
+    const int8_t* sc = (const int8_t*) (b + 192) + 8 * half + 2 * sub;
+    const float d = half_bits_to_float((uint16_t) (b[208] | (b[209] << 8)));
+    for (int l = 0; l < 32; ++l) {
+        const int lo = sub < 2 ? (ql[l] & 15) : (ql[l] >> 4);
+        const int hi = (qh[l] >> (2 * sub)) & 3;
+        const int q = (lo | (hi << 4)) - 32;
+        y[l] = d * (float) sc[l >> 4] * (float) q;
+    }
+}
+
+// 32 consecutive values [32u, 32u+32) of an IQ1_M block (56 bytes, 2-byte aligned... only byte loads are used)
+__host__ __device__ inline void decode_iq1m_32(const uint8_t* b, int u, const uint16_t* grid, float* y) {
+    const uint8_t* qs = b + 4 * u;
+    const uint8_t* qh = b + 32 + 2 * u;
+    const uint16_t sc0 = (uint16_t) (b[48] | (b[49] << 8)), sc1 = (uint16_t) (b[50] | (b[51] << 8)),
+                   sc2 = (uint16_t) (b[52] | (b[53] << 8)), sc3 = (uint16_t) (b[54] | (b[55] << 8));
+    const uint16_t dh = (uint16_t) ((sc0 >> 12) | ((sc1 >> 8) & 0x00F0) | ((sc2 >> 4) & 0x0F00) | (sc3 & 0xF000));
+    const float d = half_bits_to_float(dh);
+    const uint16_t scw = (u >> 1) == 0 ? sc0 : (u >> 1) == 1 ? sc1 : (u >> 1) == 2 ? sc2 : sc3;
+    const float dl[2] = {d * (float) (2 * ((scw >> (6 * (u & 1))) & 7) + 1), d * (float) (2 * ((scw >> (6 * (u & 1) + 3)) & 7) + 1)};
+    for (int l = 0; l < 4; ++l) {
+        const uint32_t h = qh[l >> 1];
+        const uint32_t idx = qs[l] | (((l & 1) ? (h << 4) : (h << 8)) & 0x700u);
+        const float delta = (h & ((l & 1) ? 0x80u : 0x08u)) ? -0.125f : 0.125f;
+        const uint32_t g = grid[idx];
+        for (int j = 0; j < 8; ++j) y[8 * l + j] = dl[l >> 1] * ((float) ((int) ((g >> (2 * j)) & 3u) - 1) + delta);
+    }
+}
+
+}  // namespace bsx

@@ -1,0 +1,442 @@
+// router.cu - the MoE router on sm_100a: gate-matrix logits, warp-level top-k selection for the sigmoid / sqrt-softplus
+// gates (with the group-limited step), the fp32 and fp64 softmax routers, and the opt-in tail skip.
+//
+// Parity contract: logits, ids and weights carry the bits of the Basalt engine's kernels (src/kernels/cuda/router.cu,
+// src/models/qwen4exp/prefill/kernels.cu:351-390, src/models/qwen4exp/kernels/router_top10.cu) on the same inputs.  The
+// launch shapes are this library's own: several gate rows per block so a token vector is read once for all of them, and
+// one warp per token for the selection instead of one block.
+#define BSX_SOFTMAX_KERNEL softmax_topk_kernel
+#define BSX_SOFTMAX_LAUNCH softmax_topk_launch
+#define BSX_SOFTMAX_RECIPROCAL 0
+#include "router_softmax.cuh"
+
+#include <climits>
+
+namespace bsx {
+
+int32_t softmax_fast(const float* logits, int64_t T, int E, int k, int32_t* ids, float* w, cudaStream_t st);
+
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+namespace {
+
+constexpr int kLogitThreads = 256;   // the summation order is defined over 256 column-strided chains
+constexpr int kTokTile = 8;
+
+// G gate rows a block, NV float4 a thread and row.  Each (row, token) sum runs exactly as
+// src/kernels/cuda/router.cu:49-88 defines it: thread i owns float4 columns i, i + 256, ... as one fmaf chain, the warp's 32
+// chains are summed by xor butterfly, and the 8 warp sums are added in warp order.
+template <int NV, int G>
+__global__ void __launch_bounds__(kLogitThreads)
+router_logits_kernel(const float* __restrict__ x, const float* __restrict__ gate, int n_embd, int n_expert, int n_tokens,
+                     int tok_per_block, float* __restrict__ logits) {
+    __shared__ float red[G][kTokTile][kLogitThreads / 32];
+    const int n4 = n_embd >> 2;
+    const int r0 = blockIdx.x * G;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float4 w[G][NV];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int c = 0; c < NV; ++c) {
+            const int i = threadIdx.x + c * kLogitThreads;
+            w[g][c] = i < n4 ? reinterpret_cast<const float4*>(gate + (size_t) (r0 + g) * n_embd)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    const int t_begin = blockIdx.y * tok_per_block;
+    const int t_end = min(n_tokens, t_begin + tok_per_block);
+    for (int t0 = t_begin; t0 < t_end; t0 += kTokTile) {
+        const int nt = min(kTokTile, t_end - t0);
+        for (int t = 0; t < nt; ++t) {
+            const float4* xv = reinterpret_cast<const float4*>(x + (size_t) (t0 + t) * n_embd);
+            float acc[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc[g] = 0.f;
+#pragma unroll
+            for (int c = 0; c < NV; ++c) {
+                const int i = threadIdx.x + c * kLogitThreads;
+                if (i < n4) {
+                    const float4 v = xv[i];
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        acc[g] = fmaf(w[g][c].x, v.x, acc[g]);
+                        acc[g] = fmaf(w[g][c].y, v.y, acc[g]);
+                        acc[g] = fmaf(w[g][c].z, v.z, acc[g]);
+                        acc[g] = fmaf(w[g][c].w, v.w, acc[g]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float s = warp_sum_xor(acc[g]);
+                if (lane == 0) red[g][t][warp] = s;
+            }
+        }
+        __syncthreads();
+        {
+            const int g = threadIdx.x / kTokTile, t = threadIdx.x % kTokTile;
+            if (g < G && t < nt) {
+                float s = 0.f;
+#pragma unroll
+                for (int i = 0; i < kLogitThreads / 32; ++i) s += red[g][t][i];
+                logits[(size_t) (t0 + t) * n_expert + r0 + g] = s;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int NV, int G>
+void launch_logits(const float* x, const float* gate, int T, int E, int H, float* logits, cudaStream_t st) {
+    const int tpb = T <= 256 ? kTokTile : 8 * kTokTile;
+    const dim3 grid((unsigned) (E / G), (unsigned) ((T + tpb - 1) / tpb));
+    router_logits_kernel<NV, G><<<grid, kLogitThreads, 0, st>>>(x, gate, H, E, T, tpb, logits);
+}
+
+template <int G>
+bool dispatch_nv(int nv, const float* x, const float* gate, int T, int E, int H, float* logits, cudaStream_t st) {
+    switch (nv) {
+        case 1: launch_logits<1, G>(x, gate, T, E, H, logits, st); return true;
+        case 2: launch_logits<2, G>(x, gate, T, E, H, logits, st); return true;
+        case 3: if constexpr (G <= 4) { launch_logits<3, G>(x, gate, T, E, H, logits, st); return true; } return false;
+        case 4: if constexpr (G <= 4) { launch_logits<4, G>(x, gate, T, E, H, logits, st); return true; } return false;
+        case 5: if constexpr (G <= 2) { launch_logits<5, G>(x, gate, T, E, H, logits, st); return true; } return false;
+        case 6: if constexpr (G <= 2) { launch_logits<6, G>(x, gate, T, E, H, logits, st); return true; } return false;
+        case 7: if constexpr (G <= 2) { launch_logits<7, G>(x, gate, T, E, H, logits, st); return true; } return false;
+        case 8: if constexpr (G <= 2) { launch_logits<8, G>(x, gate, T, E, H, logits, st); return true; } return false;
+        default: return false;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- sigmoid / sqrt-softplus select
+struct HeldTabs {
+    const int32_t* t[BSX_MAX_HELD_TABS];
+    int n;
+    __device__ bool held(int e) const {
+        bool in = false;
+        for (int q = 0; q < n; ++q) in |= t[q][e] >= 0;
+        return in;
+    }
+};
+
+// src/kernels/cuda/router.cu:148-153
+__device__ __forceinline__ float gate_score(float x, int gate) {
+    if (gate == BSX_GATE_SQRT_SOFTPLUS) {
+        const float sp = x > 20.f ? x : logf(1.f + expf(x));
+        return sqrtf(sp);
+    }
+    return 1.f / (1.f + expf(-x));
+}
+
+// One warp per token; lane l holds experts l, l+32, ...  The selection is the reference's rank rule (higher s + bias first,
+// the lower index on a tie; src/kernels/cuda/router.cu:170-217) made as k warp-wide argmax passes, which yield the ids in rank
+// order directly; lane 0 adds the chosen unbiased scores in that order, as the reference's thread 0 does.
+template <int REGT>
+__global__ void __launch_bounds__(256)
+router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, int E, int k, float scale,
+                     int gate, int n_group, int topk_group, float prior, HeldTabs held, int32_t* __restrict__ ids,
+                     float* __restrict__ weights) {
+    constexpr int MAXR = REGT > 0 ? REGT : 32;
+    const int64_t t = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const int lane = threadIdx.x & 31;
+    const int reg = REGT > 0 ? REGT : (E >> 5);
+    const float* lg = logits + t * E;
+    float s[MAXR], b[MAXR];
+    uint32_t dead = 0;   // bit i: expert lane + 32 i cannot be chosen (outside E, masked group, or already taken)
+#pragma unroll
+    for (int i = 0; i < MAXR; ++i) {
+        if (i < reg) {
+            const int e = lane + i * 32;
+            s[i] = gate_score(lg[e], gate);
+            b[i] = s[i] + (bias ? bias[e] : 0.f);
+            if (prior > 0.f && held.n > 0 && held.held(e)) b[i] += prior;
+        } else {
+            s[i] = 0.f;
+            b[i] = -INFINITY;
+            dead |= 1u << i;
+        }
+    }
+    if (n_group > 1 && topk_group < n_group) {
+        const int gs = E / n_group;
+        float my_score = -INFINITY;
+        for (int g = 0; g < n_group; ++g) {
+            float m1 = -INFINITY, m2 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < MAXR; ++i)
+                if (i < reg && (lane + i * 32) / gs == g) {
+                    const float v = b[i];
+                    if (v > m1) { m2 = m1; m1 = v; }
+                    else if (v > m2) m2 = v;
+                }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) {
+                const float o1 = __shfl_xor_sync(kFull, m1, o), o2 = __shfl_xor_sync(kFull, m2, o);
+                const float hi = fmaxf(m1, o1), lo = fminf(m1, o1);
+                m2 = fmaxf(lo, fmaxf(m2, o2));
+                m1 = hi;
+            }
+            const float sc = gs > 1 ? m1 + m2 : m1;
+            if (lane == g) my_score = sc;
+        }
+        int rank = 0;
+        for (int j = 0; j < n_group; ++j) {
+            const float oj = __shfl_sync(kFull, my_score, j);
+            rank += (oj > my_score) | ((oj == my_score) & (j < lane));
+        }
+        const unsigned live = __ballot_sync(kFull, lane < n_group && rank < topk_group);
+#pragma unroll
+        for (int i = 0; i < MAXR; ++i)
+            if (i < reg && !((live >> ((lane + i * 32) / gs)) & 1u)) dead |= 1u << i;
+    }
+    float my_sel = 0.f, sum = 0.f;
+    for (int r = 0; r < k; ++r) {
+        float best = -INFINITY;
+        int ex = INT_MAX;
+#pragma unroll
+        for (int i = 0; i < MAXR; ++i)
+            if (!((dead >> i) & 1u) && (ex == INT_MAX || b[i] > best)) { best = b[i]; ex = lane + i * 32; }
+#pragma unroll
+        for (int m = 16; m; m >>= 1) {
+            const float ob = __shfl_xor_sync(kFull, best, m);
+            const int oi = __shfl_xor_sync(kFull, ex, m);
+            if (oi != INT_MAX && (ex == INT_MAX || ob > best || (ob == best && oi < ex))) { best = ob; ex = oi; }
+        }
+        float sv = 0.f;
+        if (ex != INT_MAX && (ex & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < MAXR; ++i)
+                if (i == (ex >> 5)) { sv = s[i]; dead |= 1u << i; }
+        }
+        sv = __shfl_sync(kFull, sv, ex == INT_MAX ? 0 : (ex & 31));
+        sum += sv;
+        if (lane == r) my_sel = sv;
+        if (lane == 0) ids[t * k + r] = ex == INT_MAX ? -1 : ex;
+    }
+    const float denom = sum + 1e-20f;
+    if (lane < k) weights[t * k + lane] = my_sel / denom * scale;
+}
+
+// ---------------------------------------------------------------------------------------------- fp64 softmax router
+// src/models/qwen4exp/kernels/router_top10.cu:57-174: p[e] = (float)(exp((double) l - (double) max) * (float)(1 / sum)) with the
+// sum taken serially in ascending expert order in double; k argmax passes (value desc, index asc); weights renormalised
+// in double over max(sum of the chosen, 2^-14).  One warp per token; the exponentials sit in shared memory for the serial sum.
+__global__ void __launch_bounds__(128)
+router_softmax_f64_kernel(const float* __restrict__ logits, int64_t T, int E, int k, int32_t* __restrict__ ids,
+                          float* __restrict__ weights) {
+    extern __shared__ double s_ex[];   // [warps][E]
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t t = (int64_t) blockIdx.x * (blockDim.x >> 5) + wib;
+    if (t >= T) return;
+    double* ex = s_ex + (size_t) wib * E;
+    const float* l = logits + t * E;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, l[e]);
+    mx = warp_max_xor(mx);
+    for (int e = lane; e < E; e += 32) ex[e] = exp((double) l[e] - (double) mx);
+    __syncwarp();
+    double sum = 0.0;
+    if (lane == 0)
+        for (int e = 0; e < E; ++e) sum += ex[e];
+    sum = __shfl_sync(kFull, sum, 0);
+    const float inv = (float) (1.0 / sum);
+    float p[32];
+    const int reg = E >> 5;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) p[i] = i < reg ? (float) (ex[lane + i * 32] * inv) : -INFINITY;
+    uint32_t taken = 0;
+    float my_w = 0.f;
+    for (int r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        int bi = E;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < reg && !((taken >> i) & 1u) && p[i] > bv) { bv = p[i]; bi = lane + i * 32; }
+#pragma unroll
+        for (int m = 16; m; m >>= 1) {
+            const float ov = __shfl_xor_sync(kFull, bv, m);
+            const int oi = __shfl_xor_sync(kFull, bi, m);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bi < E) {
+            if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+            if (lane == 0) ids[t * k + r] = bi;
+            if (lane == r) my_w = bv;
+        }
+    }
+    double ws = 0.0;
+    for (int r = 0; r < k; ++r) ws += (double) __shfl_sync(kFull, my_w, r);
+    const double sc = fmax(ws, 6.103515625e-05);
+    if (lane < k) weights[t * k + lane] = (float) ((double) my_w / sc);
+}
+
+// ---------------------------------------------------------------------------------------------- tail skip
+// include/basalt/kernels/route_lossy.hpp:34-60, src/kernels/cuda/route_tail_skip.cu:14-39: one block, a thread per window entry.
+__global__ void __launch_bounds__(BSX_TAIL_SKIP_MAX)
+route_tail_skip_kernel(int32_t* __restrict__ ids, float* __restrict__ w, HeldTabs held, int n, int k, int R, int n_expert,
+                       unsigned long long* counts) {
+    __shared__ int32_t s_ids[BSX_TAIL_SKIP_MAX];
+    __shared__ uint8_t s_tail[BSX_TAIL_SKIP_MAX];
+    const int tid = threadIdx.x;
+    bool miss = false;
+    if (tid < n) {
+        const int32_t e = ids[tid];
+        s_ids[tid] = e;
+        const float wi = w[tid];
+        const int base = tid - tid % k;
+        int rank = 0;
+        for (int j = 0; j < k; ++j) {
+            const float wj = w[base + j];
+            rank += wj > wi || (wj == wi && base + j < tid);
+        }
+        s_tail[tid] = rank >= R;
+        miss = e >= 0 && e < n_expert && !held.held(e);
+    }
+    __syncthreads();
+    bool drop = tid < n && miss;
+    if (drop)
+        for (int j = 0; j < n; ++j)
+            if (s_ids[j] == s_ids[tid] && !s_tail[j]) { drop = false; break; }
+    const int n_miss = __syncthreads_count(miss), n_drop = __syncthreads_count(drop);
+    if (drop) {
+        ids[tid] = -1;
+        w[tid] = 0.0f;
+    }
+    if (counts != nullptr && tid == 0) {
+        atomicAdd(&counts[0], (unsigned long long) n);
+        atomicAdd(&counts[1], (unsigned long long) n_miss);
+        atomicAdd(&counts[2], (unsigned long long) n_drop);
+    }
+}
+
+bool make_held(const int32_t* const* tabs, int n, HeldTabs& h) {
+    h.n = 0;
+    for (int i = 0; i < BSX_MAX_HELD_TABS; ++i) h.t[i] = nullptr;
+    if (n < 0 || n > BSX_MAX_HELD_TABS || (n > 0 && !tabs)) return false;
+    for (int i = 0; i < n; ++i)
+        if (tabs[i]) h.t[h.n++] = tabs[i];
+    return true;
+}
+
+}  // namespace
+}  // namespace bsx
+
+using namespace bsx;
+
+extern "C" int32_t bsx_router_logits(const float* x, const float* gate, int32_t T, int32_t E, int32_t H, float* logits, void* stream) {
+    if (E < 32 || E % 32 || H < 128 || H % 128 || H > 8192 || T < 0) return BSX_E_GEOMETRY;
+    if (T == 0) return BSX_OK;
+    if (!aligned(x, 16) || !aligned(gate, 16) || !aligned(logits, 4)) return BSX_E_POINTER;
+    const cudaStream_t st = (cudaStream_t) stream;
+    const int nv = (H / 4 + kLogitThreads - 1) / kLogitThreads;
+    // the most gate rows a block whose registers fit and whose grid still covers the SMs twice
+    int G = nv <= 2 ? 8 : nv <= 4 ? 4 : 2;
+    const int tiles = (T + kTokTile - 1) / kTokTile;
+    while (G > 2 && (int64_t) (E / G) * tiles < 2 * (int64_t) sm_count()) G >>= 1;
+    bool ok = false;
+    if (G == 8) ok = dispatch_nv<8>(nv, x, gate, T, E, H, logits, st);
+    else if (G == 4) ok = dispatch_nv<4>(nv, x, gate, T, E, H, logits, st);
+    else ok = dispatch_nv<2>(nv, x, gate, T, E, H, logits, st);
+    if (!ok) return BSX_E_GEOMETRY;
+    const int32_t rc = launch_status();
+    if (rc == BSX_OK && !stream) {
+        const cudaError_t e = cudaStreamSynchronize(nullptr);
+        if (e != cudaSuccess) return (int32_t) e;
+    }
+    return rc;
+}
+
+extern "C" int32_t bsx_router_select(const float* logits, const float* bias, int32_t T, int32_t E, int32_t k, int32_t gate_kind,
+                                     float weight_scale, int32_t n_group, int32_t topk_group, float prior,
+                                     const int32_t* const* held_tabs, int32_t n_held, int32_t* ids, float* weights, void* stream) {
+    if (E < 32 || E % 32 || E > 1024 || k < 1 || k > 32 || k > E || T < 0) return BSX_E_GEOMETRY;
+    if (T == 0) return BSX_OK;
+    if (!logits || !ids || !weights) return BSX_E_POINTER;
+    const cudaStream_t st = (cudaStream_t) stream;
+    int32_t rc;
+    if (gate_kind == BSX_GATE_SOFTMAX) {
+        rc = softmax_topk_launch(logits, T, E, k, ids, weights, st);
+    } else if (gate_kind == BSX_GATE_SOFTMAX_FAST) {
+        rc = softmax_fast(logits, T, E, k, ids, weights, st);
+    } else if (gate_kind == BSX_GATE_SOFTMAX_F64) {
+        const size_t smem = (size_t) 4 * E * sizeof(double);
+        router_softmax_f64_kernel<<<(unsigned) ((T + 3) / 4), 128, smem, st>>>(logits, T, E, k, ids, weights);
+        rc = launch_status();
+    } else if (gate_kind == BSX_GATE_SIGMOID || gate_kind == BSX_GATE_SQRT_SOFTPLUS) {
+        if (k > 16) return BSX_E_GEOMETRY;
+        if (n_group < 1) n_group = 1;
+        if (n_group > 32 || E % n_group) return BSX_E_GEOMETRY;
+        if (topk_group < 1 || topk_group > n_group) topk_group = n_group;
+        if ((int64_t) topk_group * (E / n_group) < k) return BSX_E_GEOMETRY;
+        HeldTabs held;
+        if (!make_held(held_tabs, n_held, held)) return BSX_E_POINTER;
+        const unsigned blocks = (unsigned) ((T + 7) / 8);
+#define BSX_SEL(R) router_select_kernel<R><<<blocks, 256, 0, st>>>(logits, bias, T, E, k, weight_scale, gate_kind, n_group, topk_group, prior, held, ids, weights)
+        switch (E >> 5) {
+            case 2: BSX_SEL(2); break;
+            case 4: BSX_SEL(4); break;
+            case 8: BSX_SEL(8); break;
+            case 12: BSX_SEL(12); break;
+            case 16: BSX_SEL(16); break;
+            default: BSX_SEL(0); break;
+        }
+#undef BSX_SEL
+        rc = launch_status();
+    } else {
+        return BSX_E_GEOMETRY;
+    }
+    if (rc == BSX_OK && !stream) {
+        const cudaError_t e = cudaStreamSynchronize(nullptr);
+        if (e != cudaSuccess) return (int32_t) e;
+    }
+    return rc;
+}
+
+extern "C" int32_t bsx_router(const float* x, const float* gate, const float* bias, int32_t T, int32_t E, int32_t H, int32_t k,
+                              int32_t gate_kind, float weight_scale, int32_t n_group, int32_t topk_group, float prior,
+                              const int32_t* const* held_tabs, int32_t n_held, float* logits, int32_t* ids, float* weights,
+                              void* stream) {
+    // the reference's router() limits (src/kernels/cuda/router.cu:235) apply to the gates it has
+    if ((gate_kind == BSX_GATE_SIGMOID || gate_kind == BSX_GATE_SQRT_SOFTPLUS) && (k > 16)) return BSX_E_GEOMETRY;
+    if (E < 32 || E % 32 || E > 1024 || k < 1 || k > E) return BSX_E_GEOMETRY;
+    // both launches go to the same stream; with a null stream the select call synchronises at the end
+    const cudaStream_t st = (cudaStream_t) stream;
+    if (E < 32 || E % 32 || H < 128 || H % 128 || H > 8192 || T < 0) return BSX_E_GEOMETRY;
+    if (T == 0) return BSX_OK;
+    int32_t rc;
+    if (stream) rc = bsx_router_logits(x, gate, T, E, H, logits, stream);
+    else {
+        // no synchronisation between the two stages: launch on the default stream without the trailing sync
+        const int nv = (H / 4 + kLogitThreads - 1) / kLogitThreads;
+        int G = nv <= 2 ? 8 : nv <= 4 ? 4 : 2;
+        const int tiles = (T + kTokTile - 1) / kTokTile;
+        while (G > 2 && (int64_t) (E / G) * tiles < 2 * (int64_t) sm_count()) G >>= 1;
+        bool ok = G == 8 ? dispatch_nv<8>(nv, x, gate, T, E, H, logits, st)
+                  : G == 4 ? dispatch_nv<4>(nv, x, gate, T, E, H, logits, st) : dispatch_nv<2>(nv, x, gate, T, E, H, logits, st);
+        rc = ok ? launch_status() : BSX_E_GEOMETRY;
+    }
+    if (rc != BSX_OK) return rc;
+    return bsx_router_select(logits, bias, T, E, k, gate_kind, weight_scale, n_group, topk_group, prior, held_tabs, n_held, ids,
+                             weights, stream);
+}
+
+extern "C" int32_t bsx_route_tail_skip(int32_t* ids, float* weights, const int32_t* const* held_tabs, int32_t n_held,
+                                       int32_t n_entries, int32_t k, int32_t rank, int32_t E, unsigned long long* counts,
+                                       void* stream) {
+    // the reference returns silently outside these bounds (src/kernels/cuda/route_tail_skip.cu:45)
+    if (rank < 1 || rank >= k || n_entries < 1 || n_entries > BSX_TAIL_SKIP_MAX || k < 1) return BSX_OK;
+    if (!ids || !weights) return BSX_E_POINTER;
+    HeldTabs held;
+    if (!make_held(held_tabs, n_held, held)) return BSX_E_POINTER;
+    route_tail_skip_kernel<<<1, BSX_TAIL_SKIP_MAX, 0, (cudaStream_t) stream>>>(ids, weights, held, n_entries, k, rank, E, counts);
+    return launch_status();
+}

@@ -1,0 +1,87 @@
+// router_softmax.cuh - the one-warp-per-token fp32 softmax top-k router, included by two translation units: router.cu
+// (IEEE expf and division; the Basalt prompt path's route_kernel, src/models/qwen4exp/prefill/kernels.cu:351-390) and
+// router_fast.cu (built with --use_fast_math, weight = p * (1 / sum); the decode path's route,
+// src/models/qwen4exp/kernels/native_router.cu:44-99).  The including file defines BSX_SOFTMAX_KERNEL (the kernel's name)
+// and BSX_SOFTMAX_RECIPROCAL (0: divide, 1: multiply by the reciprocal).
+//
+// Arithmetic order, which fixes every bit of the result: lane l holds experts l, l+32, ...; max over all experts; per lane
+// v = expf(v - max) summed in index order, lanes summed by xor butterfly; v *= 1/sum; NaN -> -FLT_MAX; k argmax passes
+// (value descending, index ascending); the chosen probabilities are added per WINNING lane in selection order, lanes summed
+// by butterfly, clamped below at 2^-14.  The reference instantiates 512 and 256 experts with k = 10 only; this is the same
+// sequence for any E % 32 == 0 (E <= 1024) and k <= 32.
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace bsx {
+
+template <int REGT>
+__global__ void __launch_bounds__(256) BSX_SOFTMAX_KERNEL(const float* __restrict__ logits, int32_t* __restrict__ ids,
+                                                         float* __restrict__ wout, int64_t T, int E, int k) {
+    constexpr int MAXR = REGT > 0 ? REGT : 32;
+    const int64_t t = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const int lane = threadIdx.x & 31;
+    const int reg = REGT > 0 ? REGT : (E >> 5);
+    const float* lg = logits + t * E;
+    float v[MAXR];
+#pragma unroll
+    for (int i = 0; i < MAXR; ++i) v[i] = i < reg ? lg[lane + i * 32] : -INFINITY;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MAXR; ++i)
+        if (i < reg) mx = fmaxf(mx, v[i]);
+    mx = warp_max_xor(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MAXR; ++i)
+        if (i < reg) { v[i] = expf(v[i] - mx); sum += v[i]; }
+    const float rcp = 1.0f / warp_sum_xor(sum);
+#pragma unroll
+    for (int i = 0; i < MAXR; ++i)
+        if (i < reg) { v[i] *= rcp; if (isnan(v[i])) v[i] = -FLT_MAX; }
+    float selected = 0.0f, selected_sum = 0.0f;
+    for (int rank = 0; rank < k; ++rank) {
+        float best = v[0];
+        int ex = lane;
+#pragma unroll
+        for (int i = 1; i < MAXR; ++i)
+            if (i < reg && v[i] > best) { best = v[i]; ex = lane + i * 32; }
+#pragma unroll
+        for (int m = 16; m; m >>= 1) {
+            const float ob = __shfl_xor_sync(kFull, best, m);
+            const int oi = __shfl_xor_sync(kFull, ex, m);
+            if (ob > best || (ob == best && oi < ex)) { best = ob; ex = oi; }
+        }
+        if ((ex & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < MAXR; ++i)
+                if (i == (ex >> 5)) v[i] = -INFINITY;
+            selected_sum += best;
+        }
+        if (lane == 0) ids[t * k + rank] = ex;
+        if (rank == lane) selected = best;
+    }
+    selected_sum = fmaxf(warp_sum_xor(selected_sum), 6.103515625e-5f);
+#if BSX_SOFTMAX_RECIPROCAL
+    const float inv = 1.0f / selected_sum;
+    if (lane < k) wout[t * k + lane] = selected * inv;
+#else
+    if (lane < k) wout[t * k + lane] = selected / selected_sum;
+#endif
+}
+
+static inline int32_t BSX_SOFTMAX_LAUNCH(const float* logits, int64_t T, int E, int k, int32_t* ids, float* w, cudaStream_t st) {
+    const unsigned blocks = (unsigned) ((T + 7) / 8);
+    switch (E >> 5) {
+        case 2: BSX_SOFTMAX_KERNEL<2><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
+        case 4: BSX_SOFTMAX_KERNEL<4><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
+        case 8: BSX_SOFTMAX_KERNEL<8><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
+        case 12: BSX_SOFTMAX_KERNEL<12><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
+        case 16: BSX_SOFTMAX_KERNEL<16><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
+        default: BSX_SOFTMAX_KERNEL<0><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
+    }
+    return launch_status();
+}
+
+}  // namespace bsx

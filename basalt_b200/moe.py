@@ -1,0 +1,278 @@
+"""Host-side mirror of the Basalt engine's MoE operator interface over the B200 C ABI (include/basalt_b200.h).
+
+Function names and argument meanings follow the reference's `basalt::kernels` operators (router, router_select,
+route_tail_skip, native_expert_layout, native_expert_grouped, native_moe_combine, ...; see each docstring), so a parity
+test reads like the reference's own.  torch supplies device memory and streams only: every computation is a hand-written
+CUDA kernel behind the C ABI, and a missing library or GPU raises instead of falling back.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from . import capi
+from .capi import (GATE_SIGMOID, GATE_SOFTMAX, GATE_SOFTMAX_F64, GATE_SOFTMAX_FAST, GATE_SQRT_SOFTPLUS, OUT_BF16, OUT_F32,
+                   TYPE_IQ1_M, TYPE_NVFP4, TYPE_Q6_K, X_BF16, X_F32, X_Q8_1, ExpertLayout, check)
+
+
+def _stream(stream=None) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return int(stream.cuda_stream) if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "device, contiguous tensors only"
+    return t.data_ptr()
+
+
+@dataclass
+class RouterArgs:
+    """basalt::kernels::RouterArgs (include/basalt/kernels/router.hpp:16-27) plus the group-limited step and the softmax
+    gate kinds this library adds."""
+    n_expert: int = 384
+    n_embd: int = 5120
+    k: int = 6
+    weight_scale: float = 1.5
+    gate: int = GATE_SQRT_SOFTPLUS
+    prior: float = 0.0
+    held: Sequence[torch.Tensor] = field(default_factory=tuple)   # ResidentTabs: up to 4 int32 [n_expert] device tables
+    n_group: int = 1
+    topk_group: int = 1
+
+
+def _held(args: RouterArgs):
+    tabs = [t for t in args.held if t is not None]
+    if not tabs:
+        return None, 0, None
+    arr = (C.c_void_p * len(tabs))(*[t.data_ptr() for t in tabs])
+    return C.cast(arr, C.c_void_p), len(tabs), arr
+
+
+def router(x, gate, bias, a: RouterArgs, logits=None, ids=None, weights=None, stream=None):
+    """basalt::kernels::router (router.hpp:30-32): logits = gate . x, selection, weights.  Returns (logits, ids, weights)."""
+    T = x.shape[0]
+    dev = x.device
+    logits = torch.empty((T, a.n_expert), dtype=torch.float32, device=dev) if logits is None else logits
+    ids = torch.empty((T, a.k), dtype=torch.int32, device=dev) if ids is None else ids
+    weights = torch.empty((T, a.k), dtype=torch.float32, device=dev) if weights is None else weights
+    hp, hn, keep = _held(a)
+    check("bsx_router", capi.lib().bsx_router(_p(x), _p(gate), _p(bias), T, a.n_expert, a.n_embd, a.k, a.gate, a.weight_scale,
+                                               a.n_group, a.topk_group, a.prior, hp, hn, _p(logits), _p(ids), _p(weights),
+                                               _stream(stream)))
+    return logits, ids, weights
+
+
+def router_logits(x, gate, logits=None, stream=None):
+    T, H = x.shape
+    E = gate.shape[0]
+    logits = torch.empty((T, E), dtype=torch.float32, device=x.device) if logits is None else logits
+    check("bsx_router_logits", capi.lib().bsx_router_logits(_p(x), _p(gate), T, E, H, _p(logits), _stream(stream)))
+    return logits
+
+
+def router_select(logits, bias, a: RouterArgs, ids=None, weights=None, stream=None):
+    """basalt::kernels::router_select (router.hpp:36-37); with a softmax gate kind, qwen4exp's route / native_router_top10 /
+    router_top10."""
+    T, E = logits.shape
+    ids = torch.empty((T, a.k), dtype=torch.int32, device=logits.device) if ids is None else ids
+    weights = torch.empty((T, a.k), dtype=torch.float32, device=logits.device) if weights is None else weights
+    hp, hn, keep = _held(a)
+    check("bsx_router_select", capi.lib().bsx_router_select(_p(logits), _p(bias), T, E, a.k, a.gate, a.weight_scale, a.n_group,
+                                                             a.topk_group, a.prior, hp, hn, _p(ids), _p(weights), _stream(stream)))
+    return ids, weights
+
+
+def route_tail_skip(ids, weights, held: Sequence[torch.Tensor], k: int, rank: int, n_expert: int, counts=None, stream=None):
+    """basalt::kernels::route_tail_skip (include/basalt/kernels/route_lossy.hpp:58-59); edits ids / weights in place."""
+    a = RouterArgs(held=tuple(held))
+    hp, hn, keep = _held(a)
+    check("bsx_route_tail_skip", capi.lib().bsx_route_tail_skip(_p(ids), _p(weights), hp, hn, ids.numel(), k, rank, n_expert,
+                                                                 _p(counts), _stream(stream)))
+
+
+def dispatch(ids, k: int, n_expert: int, tile_rows: int = 0, stream=None):
+    """The prompt path's grouping (qwen4exp Group::group, routing.cpp:67-108; fused::group, moe_fused.hpp:46-50): returns
+    (cnt, off, slot, src, tiles, n_tiles); tiles / n_tiles are None without tile_rows."""
+    n = ids.numel()
+    dev = ids.device
+    cnt = torch.empty(n_expert, dtype=torch.int32, device=dev)
+    off = torch.empty(n_expert + 1, dtype=torch.int32, device=dev)
+    slot = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    src = torch.full((max(n, 1),), -1, dtype=torch.int32, device=dev)
+    tiles = n_tiles = None
+    if tile_rows > 0:
+        tiles = torch.zeros((n // tile_rows + n_expert, 2), dtype=torch.int32, device=dev)
+        n_tiles = torch.zeros(1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(capi.lib().bsx_dispatch_scratch_bytes(n, n_expert), dtype=torch.uint8, device=dev)
+    check("bsx_dispatch", capi.lib().bsx_dispatch(_p(ids), n, k, n_expert, _p(cnt), _p(off), _p(slot), _p(src), tile_rows,
+                                                   _p(tiles), _p(n_tiles), _p(scratch), _stream(stream)))
+    return cnt, off, slot[:n], src[:n], tiles, n_tiles
+
+
+def moe_plan(ids, k: int, n_expert: int, blob_table, stream=None):
+    """inkling2 moe_plan (src/models/inkling2/kernels/ops.cu:488-498): (ptr, start, n_groups, dst, tok) device tensors."""
+    n = ids.numel()
+    T = n // k
+    dev = ids.device
+    ptr = torch.zeros(max(n, 1), dtype=torch.int64, device=dev)
+    start = torch.zeros(n + 2, dtype=torch.int32, device=dev)
+    n_groups = torch.zeros(1, dtype=torch.int32, device=dev)
+    dst = torch.zeros(max(n, 1), dtype=torch.int32, device=dev)
+    tok = torch.zeros(max(n, 1), dtype=torch.int32, device=dev)
+    check("bsx_moe_plan", capi.lib().bsx_moe_plan(_p(ids), T, k, n_expert, _p(blob_table), _p(ptr), _p(start), _p(n_groups),
+                                                   _p(dst), _p(tok), _stream(stream)))
+    return ptr, start, n_groups, dst, tok
+
+
+def native_expert_layout(gu_type: int, d_type: int, n_embd: int, n_ff: int, swiglu_limit: float = 0.0, up_type: int = -1,
+                         gate_softcap: float = 0.0, up_softcap: float = 0.0) -> ExpertLayout:
+    """basalt::kernels::native_expert_layout (include/basalt/kernels/iq_kernels.hpp:68-69)."""
+    L = ExpertLayout()
+    check("bsx_expert_layout_init", capi.lib().bsx_expert_layout_init(gu_type, d_type, up_type, n_embd, n_ff, swiglu_limit,
+                                                                       gate_softcap, up_softcap, C.byref(L)))
+    return L
+
+
+def native_expert_supported(gu_type, d_type, n_embd, n_ff, up_type=-1) -> bool:
+    return bool(capi.lib().bsx_expert_supported(gu_type, d_type, up_type, n_embd, n_ff))
+
+
+def native_expert_scratch_bytes(cap_entries: int, n_ff: int) -> int:
+    return int(capi.lib().bsx_expert_scratch_bytes(cap_entries, n_ff))
+
+
+def quantize_q8_1_rows(x, stream=None):
+    """basalt::kernels::quantize_q8_1_rows (iq_kernels.hpp:23): [rows][cols] fp32 -> uint8 [rows * cols / 32 * 36]."""
+    rows, cols = x.shape
+    y = torch.empty(rows * cols // 32 * 36, dtype=torch.uint8, device=x.device)
+    check("bsx_quantize_q8_1_rows", capi.lib().bsx_quantize_q8_1_rows(_p(x), rows, cols, _p(y), _stream(stream)))
+    return y
+
+
+def _x_kind(x) -> int:
+    if x.dtype == torch.float32:
+        return X_F32
+    if x.dtype == torch.bfloat16:
+        return X_BF16
+    if x.dtype == torch.uint8:
+        return X_Q8_1
+    raise TypeError("activations must be fp32, bf16 or q8_1 bytes")
+
+
+def native_expert_grouped(L: ExpertLayout, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups: int, cap_entries: int,
+                          x, scratch, out, stream=None):
+    """basalt::kernels::native_expert_grouped (iq_kernels.hpp:84-87).  `x` may be fp32, bf16 or q8_1 bytes; `out` fp32 or bf16."""
+    out_kind = OUT_BF16 if out.dtype == torch.bfloat16 else OUT_F32
+    check("bsx_experts_grouped", capi.lib().bsx_experts_grouped(C.byref(L), _p(grp_ptr), _p(grp_start), _p(n_groups), _p(ent_dst),
+                                                                 _p(ent_tok), cap_groups, cap_entries, _p(x), _x_kind(x),
+                                                                 _p(scratch), _p(out), out_kind, _stream(stream)))
+    return out
+
+
+def moe_combine(rows, slot, weights, shared=None, shared_gate=None, y=None, stream=None):
+    """native_moe_combine_multi (native_moe.hpp:10-15) / prompt-path moe_combine (prefill/kernels.cu:705-709)."""
+    T, k = weights.shape
+    H = rows.shape[-1]
+    y = torch.empty((T, H), dtype=torch.float32, device=rows.device) if y is None else y
+    check("bsx_combine", capi.lib().bsx_combine(_p(rows), _p(slot), _p(weights), _p(shared), _p(shared_gate), T, k, H, _p(y),
+                                                 _stream(stream)))
+    return y
+
+
+class MoELayer:
+    """One resident MoE layer: router gate, routed expert blobs, optional shared expert, run as the reference's decode
+    window does (inkling2/session.cpp:680-716): router -> moe_plan -> native_expert_grouped -> combine."""
+
+    def __init__(self, gate_w: torch.Tensor, bias: Optional[torch.Tensor], blobs: torch.Tensor, layout: ExpertLayout,
+                 args: RouterArgs, shared_blob: Optional[torch.Tensor] = None, shared_layout: Optional[ExpertLayout] = None,
+                 max_tokens: int = 64):
+        assert blobs.dtype == torch.uint8 and blobs.dim() == 2 and blobs.is_cuda
+        self.gate_w, self.bias, self.blobs, self.L, self.args = gate_w, bias, blobs, layout, args
+        self.shared_blob, self.shared_L = shared_blob, shared_layout or layout
+        dev = blobs.device
+        E, stride = blobs.shape
+        assert stride % 16 == 0 and stride >= layout.bytes
+        self.blob_table = (blobs.data_ptr() + torch.arange(E, dtype=torch.int64) * stride).to(dev)
+        self.max_tokens = max_tokens
+        n = max_tokens * args.k
+        assert n <= 1024, "the decode-window plan takes at most 1024 (token, expert) pairs"
+        f32, i32 = torch.float32, torch.int32
+        self.logits = torch.empty((max_tokens, E), dtype=f32, device=dev)
+        self.ids = torch.empty((max_tokens, args.k), dtype=i32, device=dev)
+        self.w = torch.empty((max_tokens, args.k), dtype=f32, device=dev)
+        self.ptr = torch.zeros(n, dtype=torch.int64, device=dev)
+        self.start = torch.zeros(n + 2, dtype=i32, device=dev)
+        self.n_groups = torch.zeros(1, dtype=i32, device=dev)
+        self.dst = torch.zeros(n, dtype=i32, device=dev)
+        self.tok = torch.zeros(n, dtype=i32, device=dev)
+        self.rows = torch.empty((n, layout.n_embd), dtype=f32, device=dev)
+        self.scratch = torch.empty(native_expert_scratch_bytes(n, layout.n_ff), dtype=torch.uint8, device=dev)
+        self.y = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
+        if shared_blob is not None:
+            self.s_ptr = torch.tensor([shared_blob.data_ptr()], dtype=torch.int64, device=dev)
+            self.s_iota = torch.arange(max_tokens, dtype=i32, device=dev)
+            self.s_one = torch.ones(1, dtype=i32, device=dev)
+            self.s_start = torch.zeros(3, dtype=i32, device=dev)
+            self.s_out = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
+            self.s_scratch = torch.empty(native_expert_scratch_bytes(max_tokens, self.shared_L.n_ff), dtype=torch.uint8, device=dev)
+            self._s_T = -1
+
+    def forward(self, x: torch.Tensor, x_router: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """x: [T][n_embd] fp32 or bf16 activations for the experts; x_router: the fp32 rows the router reads (defaults to
+        x, converted when x is bf16).  Returns y [T][n_embd] fp32 (a view of an internal buffer)."""
+        T = x.shape[0]
+        a, lib, st = self.args, capi.lib(), _stream(stream)
+        assert T <= self.max_tokens
+        xr = x_router if x_router is not None else (x if x.dtype == torch.float32 else x.float())
+        hp, hn, keep = _held(a)
+        check("bsx_router", lib.bsx_router(_p(xr), _p(self.gate_w), _p(self.bias), T, a.n_expert, a.n_embd, a.k, a.gate,
+                                            a.weight_scale, a.n_group, a.topk_group, a.prior, hp, hn, _p(self.logits), _p(self.ids),
+                                            _p(self.w), st))
+        check("bsx_moe_plan", lib.bsx_moe_plan(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), _p(self.ptr), _p(self.start),
+                                                _p(self.n_groups), _p(self.dst), _p(self.tok), st))
+        n = T * a.k
+        kind = _x_kind(x)
+        check("bsx_experts_grouped", lib.bsx_experts_grouped(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
+                                                             _p(self.dst), _p(self.tok), min(n, a.n_expert), n, _p(x), kind,
+                                                             _p(self.scratch), _p(self.rows), OUT_F32, st))
+        shared = None
+        if self.shared_blob is not None:
+            if self._s_T != T:
+                self.s_start.copy_(torch.tensor([0, T, T], dtype=torch.int32))
+                self._s_T = T
+            check("bsx_experts_grouped", lib.bsx_experts_grouped(C.byref(self.shared_L), _p(self.s_ptr), _p(self.s_start),
+                                                                 _p(self.s_one), _p(self.s_iota), _p(self.s_iota), 1, T, _p(x), kind,
+                                                                 _p(self.s_scratch), _p(self.s_out), OUT_F32, st))
+            shared = self.s_out
+        check("bsx_combine", lib.bsx_combine(_p(self.rows), None, _p(self.w), _p(shared), None, T, a.k, self.L.n_embd, _p(self.y), st))
+        return self.y[:T]
+EOF
+cat > basalt_b200/__init__.py <<'EOF'
+"""basalt_b200 - the Basalt engine's mixture-of-experts layer hot path as hand-written CUDA for NVIDIA B200 (sm_100a),
+behind a C ABI (include/basalt_b200.h) and a thin host-side mirror of the reference's operator interface (moe.py)."""
+from . import capi  # noqa: F401
+
+__all__ = ["capi", "moe", "build"]
+EOF
+python -c "
+from basalt_b200 import capi
+print(capi.lib().bsx_version())
+import numpy as np, ctypes as C
+from oracle import oracle as O
+rng=np.random.default_rng(1)
+for t,bs,nv in ((40,36,64),(14,210,256),(29,56,256)):
+    raw = rng.integers(0,256,size=512*bs,dtype=np.uint8)
+    if t==14: raw.reshape(-1,210)[:,209]&=0x7b
+    if t==29: raw = O.random_iq1m_rows(rng, 1, 512*256)
+    n = raw.size//bs*nv
+    a = O.dequantize(t, raw, 1, n)
+    b = np.empty(n, np.float32)
+    rc = capi.lib().bsx_host_decode_row(t, raw.ctypes.data, b.ctypes.data, n)
+    print(t, rc, np.array_equal(a.view(np.uint32).reshape(-1), b.view(np.uint32)))
+"

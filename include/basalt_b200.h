@@ -1,0 +1,171 @@
+/* basalt_b200.h - C ABI of the B200 (sm_100a) mixture-of-experts layer: router, token-to-expert dispatch, grouped expert
+ * gate-up / SwiGLU / down products over ggml block formats (NVFP4, Q6_K, IQ1_M), weighted combine with the shared expert.
+ *
+ * Every entry point is a drop-in for one operator of the Basalt engine's src/kernels / src/prefill layer; the comment above
+ * each declaration cites the reference interface it replaces (paths inside the Basalt project).  basalt_shim.hpp wraps
+ * these in inline C++ functions that carry the reference's exact signatures and exception behaviour.
+ *
+ * Conventions (the reference's, include/basalt/kernels/router.hpp:4-5, iq_kernels.hpp:77-95):
+ *   - every data pointer is a DEVICE pointer; the caller owns all buffers including scratch, sized by the *_bytes helpers;
+ *   - `stream` is a cudaStream_t passed as void*; nothing is allocated, no host read happens inside a call and, with a
+ *     non-null stream, no synchronisation, so calls can be captured into a CUDA graph.  For the router family a null
+ *     stream means "default stream, then synchronise" (router.cu:266); the expert, dispatch and combine family refuses
+ *     a null stream (BSX_E_STREAM), as the reference's native family does (native_moe.cu:61);
+ *   - a token's result does not depend on the number of tokens in the call or on its position;
+ *   - return value: 0 = ok, negative = BSX_E_* argument error, positive = a cudaError_t from a launch.  Nothing exits
+ *     or throws.  There is no CPU fallback: without a usable CUDA device every compute call fails with a CUDA error.
+ */
+#ifndef BASALT_B200_H
+#define BASALT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define BSX_API __attribute__((visibility("default")))
+#else
+#define BSX_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    BSX_OK = 0,
+    BSX_E_GEOMETRY = -1,   /* unsupported shape (the reference throws std::invalid_argument / exits) */
+    BSX_E_STREAM = -2,     /* null stream where the reference forbids it */
+    BSX_E_TYPE = -3,       /* block format not supported */
+    BSX_E_POINTER = -4,    /* null or misaligned pointer */
+    BSX_E_LIMIT = -5       /* a size beyond a documented fixed maximum */
+};
+
+/* gate functions of bsx_router_select */
+enum {
+    BSX_GATE_SQRT_SOFTPLUS = 0, /* RouterGate::SqrtSoftplus, router.hpp:14 */
+    BSX_GATE_SIGMOID = 1,       /* RouterGate::Sigmoid */
+    BSX_GATE_SOFTMAX = 2,       /* fp32 one-warp softmax top-k, src/models/qwen4exp/prefill/kernels.cu:351-390 */
+    BSX_GATE_SOFTMAX_FAST = 3,  /* the same built with fast-math, src/models/qwen4exp/kernels/native_router.cu:44-99 */
+    BSX_GATE_SOFTMAX_F64 = 4    /* fp64 exponentials and renormalisation, src/models/qwen4exp/kernels/router_top10.cu:57-174 */
+};
+
+/* ggml type ids of the block formats (include/basalt/ggml/ggml.h) */
+enum { BSX_TYPE_Q6_K = 14, BSX_TYPE_IQ1_M = 29, BSX_TYPE_NVFP4 = 40 };
+
+/* activation / output element kinds */
+enum { BSX_X_F32 = 0, BSX_X_BF16 = 1, BSX_X_Q8_1 = 2 };
+enum { BSX_OUT_F32 = 0, BSX_OUT_BF16 = 1 };
+
+#define BSX_MAX_HELD_TABS 4      /* ResidentTabs::kMax, include/basalt/kernels/route_lossy.hpp:20 */
+#define BSX_TAIL_SKIP_MAX 128    /* kRouteTailSkipMax, route_lossy.hpp:33 */
+#define BSX_PLAN_MAX_PAIRS 1024  /* moe_plan's limit, src/models/inkling2/kernels/ops.cu:493 */
+
+/* ---- a1: router logits.  Replaces the logits stage of basalt::kernels::router (include/basalt/kernels/router.hpp:30-32,
+ * src/kernels/cuda/router.cu:49-146,233-253).  logits[t][e] = gate[e] . x[t]; x [T][H] fp32, gate [E][H] fp32 row-major,
+ * logits [T][E] fp32.  Bit-identical to the reference: each sum runs as 256 column-strided fmaf chains, a 32-wide xor
+ * butterfly per chain group, then the 8 partial sums in order.  E % 32 == 0, H % 128 == 0, H <= 8192. */
+BSX_API int32_t bsx_router_logits(const float* x, const float* gate, int32_t T, int32_t E, int32_t H, float* logits, void* stream);
+
+/* ---- a2-a4: selection and weights from logits.  Replaces basalt::kernels::router_select (router.hpp:36-37,
+ * router.cu:170-229,255-267), qwen4exp::route / route_kernel (src/models/qwen4exp/prefill/kernels.cu:351-390,639-647),
+ * native_router_top10[_multi] (include/basalt/models/qwen4exp/kernels/native_router.hpp:8-16) and router_top10
+ * (src/models/qwen4exp/kernels/router_top10.cu:181-214).
+ * Sigmoid / sqrt-softplus: s = gate(logit); the k largest s + bias (+ prior for experts a held table names, when
+ * prior > 0) are chosen, the lower index winning a tie; ids come in rank order; weight = s / (sum of the chosen s + 1e-20)
+ * * weight_scale.  Softmax kinds ignore bias, weight_scale, groups and prior: p = softmax over all experts, k argmax passes
+ * (value desc, index asc), weight = p / max(sum of chosen p, 2^-14).
+ * Group-limited selection (no counterpart in the reference; n_group <= 1 or topk_group >= n_group reduces to the plain
+ * selection bit for bit): experts form n_group contiguous groups, a group scores the sum of its two largest s + bias, only
+ * the topk_group best groups (lower index on a tie) can be chosen from.
+ * E % 32 == 0, E <= 1024, 1 <= k <= 32 (k <= 16 for the non-softmax kinds, as the reference), n_group <= 32.
+ * held_tabs: n_held (<= 4) device tables [E] of int32 (slot or -1), may be null. */
+BSX_API int32_t bsx_router_select(const float* logits, const float* bias, int32_t T, int32_t E, int32_t k, int32_t gate_kind,
+                          float weight_scale, int32_t n_group, int32_t topk_group, float prior,
+                          const int32_t* const* held_tabs, int32_t n_held, int32_t* ids, float* weights, void* stream);
+
+/* ---- a1+a2: basalt::kernels::router (router.hpp:30-32): bsx_router_logits then bsx_router_select on one stream. */
+BSX_API int32_t bsx_router(const float* x, const float* gate, const float* bias, int32_t T, int32_t E, int32_t H, int32_t k,
+                   int32_t gate_kind, float weight_scale, int32_t n_group, int32_t topk_group, float prior,
+                   const int32_t* const* held_tabs, int32_t n_held, float* logits, int32_t* ids, float* weights, void* stream);
+
+/* ---- a5: opt-in lossy tail skip.  Replaces basalt::kernels::route_tail_skip (include/basalt/kernels/route_lossy.hpp:58-59,
+ * src/kernels/cuda/route_tail_skip.cu:14-53).  n_entries <= 128; rank outside 1..k-1 leaves the window untouched.
+ * counts (optional, 3 x uint64 on the device): entries, entries no table holds, entries dropped (added to). */
+BSX_API int32_t bsx_route_tail_skip(int32_t* ids, float* weights, const int32_t* const* held_tabs, int32_t n_held, int32_t n_entries,
+                            int32_t k, int32_t rank, int32_t E, unsigned long long* counts, void* stream);
+
+/* ---- a6: dispatch.  Replaces qwen4exp Group::group() (src/models/qwen4exp/prefill/routing.cpp:67-108), fused::group
+ * (include/basalt/models/qwen4exp/prefill/moe_fused.hpp:46-50, moe_fused.cu:99-168,412-428), route_count
+ * (prefill/kernels.cu:648-657) and the tile plans of fp4::plan / plan_blocks (include/basalt/prefill/moe_fp4.hpp:23-41).
+ * ids [n_pairs] (pair i = token i / k, choice i % k) -> cnt [E], off [E+1] (exclusive prefix sum in expert-id order),
+ * slot [n_pairs] (row of pair i; -1 for an id outside [0, E)), src [n_pairs] (token of each row).  The permutation is the
+ * stable counting sort: pairs keep their order inside an expert (the host path's order; deterministic, no atomics on
+ * row positions).  tiles (optional, with tile_rows > 0): int32 pairs {expert, first row} per tile of tile_rows rows,
+ * experts ascending, n_tiles[0] = their number; capacity n_pairs / tile_rows + E entries.
+ * scratch: bsx_dispatch_scratch_bytes(n_pairs, E).  E <= 1024. */
+BSX_API size_t bsx_dispatch_scratch_bytes(int64_t n_pairs, int32_t E);
+BSX_API int32_t bsx_dispatch(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t E, int32_t* cnt, int32_t* off, int32_t* slot,
+                     int32_t* src, int32_t tile_rows, int32_t* tiles, int32_t* n_tiles, void* scratch, void* stream);
+
+/* ---- a6, decode-window form.  Replaces inkling2 moe_plan (src/models/inkling2/kernels/ops.cu:275-340,488-498): the experts
+ * with pairs and a non-zero blob address become groups in ascending expert order (ptr[g], start[g]; start[n_groups] =
+ * start[n_groups+1] = entries), entries inside a group in pair order, dst[entry] = pair index (the output row),
+ * tok[entry] = pair / k.  T * k <= 1024; ids outside [0, E) are skipped. */
+BSX_API int32_t bsx_moe_plan(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table,
+                     unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok, void* stream);
+
+/* ---- a8: expert blob geometry.  Mirrors NativeExpertLayout / native_expert_layout / native_expert_supported /
+ * native_expert_scratch_bytes (include/basalt/kernels/iq_kernels.hpp:51-75, src/kernels/cuda/iq_kernels.cu:3208-3242):
+ * blob = [gate rows | up rows | down rows | NVFP4 only: fp32 {s_gate, s_up, s_down, 0}], raw ggml blocks. */
+typedef struct bsx_expert_layout {
+    int32_t gu_type, d_type, up_type;
+    int32_t reserved;
+    int64_t n_embd, n_ff;
+    uint64_t gu_row, d_row, up_row;    /* bytes per gate, down and up row */
+    uint64_t up_off, down_off, bytes;  /* offsets inside the blob; its size */
+    float swiglu_limit;                /* > 0: gate capped above at it, up clamped to +-it */
+    float gate_softcap, up_softcap;    /* > 0 (both): h = cg tanh(g/cg) sigmoid(g) cu tanh(u/cu) */
+    float reserved_f;
+} bsx_expert_layout;
+
+BSX_API int32_t bsx_expert_layout_init(int32_t gu_type, int32_t d_type, int32_t up_type, int64_t n_embd, int64_t n_ff,
+                               float swiglu_limit, float gate_softcap, float up_softcap, bsx_expert_layout* layout);
+BSX_API int32_t bsx_expert_supported(int32_t gu_type, int32_t d_type, int32_t up_type, int64_t n_embd, int64_t n_ff);
+BSX_API size_t bsx_expert_scratch_bytes(int64_t cap_entries, int64_t n_ff);
+
+/* ---- a7: q8_1 activation rows.  Replaces basalt::kernels::quantize_q8_1_rows (iq_kernels.hpp:23, iq_kernels.cu:2471-2503):
+ * per 32 values fp16 d = amax / 127, fp16 sum, 32 int8 codes.  n_cols % 32 == 0.  Bit-identical to the reference. */
+BSX_API int32_t bsx_quantize_q8_1_rows(const float* x, int64_t n_rows, int64_t n_cols, void* y, void* stream);
+
+/* ---- a9/a10: grouped decode experts.  Replaces native_expert_grouped / native_expert_grouped_clamped / gated_mlp_clamped
+ * (iq_kernels.hpp:77-98, iq_kernels.cu:3304-3447).  Group g's blob is at device address grp_ptr[g]; its entries
+ * [grp_start[g], grp_start[g+1]) read activation row ent_tok[e] of x and write row ent_dst[e] of out (n_embd values,
+ * unweighted): out = s_down W_down ( silu(s_gate W_gate x) * (s_up W_up x) ).  n_groups is read on the device;
+ * cap_groups / cap_entries bound the launch.  x_kind: BSX_X_F32 ([rows][n_embd] floats), BSX_X_BF16, or BSX_X_Q8_1 (the
+ * reference's activation blocks, decoded as d * q).  Unlike the reference, activations and the SwiGLU output are NOT
+ * re-quantised to int8: products accumulate in fp32 on exactly decoded weights, so results sit within ~1e-5 relative
+ * of the dequantised fp32 reference instead of the reference kernels' ~1e-2.
+ * scratch: bsx_expert_scratch_bytes(cap_entries, n_ff).  A shared expert is one group holding every token. */
+BSX_API int32_t bsx_experts_grouped(const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
+                            const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
+                            int64_t cap_entries, const void* x, int32_t x_kind, void* scratch, void* out, int32_t out_kind,
+                            void* stream);
+
+/* ---- a13: weighted combine.  Replaces native_moe_combine[_multi] (include/basalt/models/qwen4exp/kernels/native_moe.hpp:5-15,
+ * native_moe.cu:36-85), moe_combine (src/models/qwen4exp/prefill/kernels.cu:438-449,705-709) and weighted_sum_tokens
+ * (src/models/deepseek41/prefill_ffn.cu:33-50).  y[t] = fma chain over j < k of weights[t][j] * rows[slot[t*k+j]] in j
+ * order starting from 0, then + shared[t] (as one more fma with sigmoid(shared_gate[t]) when shared_gate is given).
+ * slot may be null (row = t*k+j, the decode form); a slot < 0 contributes nothing.  A gather, never a scatter-add:
+ * bit-stable from run to run.  rows [n_rows][H] fp32, y [T][H] fp32, H % 4 == 0. */
+BSX_API int32_t bsx_combine(const float* rows, const int32_t* slot, const float* weights, const float* shared, const float* shared_gate,
+                    int32_t T, int32_t k, int32_t H, float* y, void* stream);
+
+/* ---- device self-check helpers (host-side; no GPU needed): the block decoders compiled for the host, for tests. */
+BSX_API int32_t bsx_host_decode_row(int32_t type, const void* row, float* y, int64_t n);
+BSX_API size_t bsx_row_bytes(int32_t type, int64_t n);
+BSX_API const char* bsx_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BASALT_B200_H */

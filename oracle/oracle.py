@@ -26,7 +26,7 @@ def build(force: bool = False) -> None:
     """Compiles liboracle.so (always possible: gcc only) and, if a reference checkout is present, oracle/_ref/*."""
     so = HERE / "liboracle.so"
     src = HERE / "moe_oracle.c"
-    if force or not so.exists() or so.stat().st_mtime < src.stat().st_mtime:
+    if force or not so.exists() or so.stat().st_mtime < src.stat().st_mtime or not (HERE / "libstdrandn.so").exists():
         subprocess.check_call(["make", "-C", str(HERE), "oracle"], stdout=subprocess.DEVNULL)
     ref = Path(os.environ.get("BASALT_REFERENCE", "/root/reference"))
     if ref.is_dir() and (force or not (HERE / "_ref" / "libref_cpu.so").exists() or not (HERE / "_ref" / "libref_gpu.so").exists()):
@@ -64,6 +64,17 @@ def lib() -> C.CDLL:
         L.orc_ue4m3_half.argtypes = [C.c_uint8]
         _lib = L
     return _lib
+
+
+def std_randn(n: int, seed: int, sigma: float = 1.0, mean: float = 0.0) -> np.ndarray:
+    """n floats from std::mt19937(seed) + std::normal_distribution<float>(mean, sigma) (libstdc++), the generator of the
+    reference's own tests."""
+    build()
+    L = C.CDLL(str(HERE / "libstdrandn.so"))
+    L.std_randn.argtypes = [_f32p, C.c_size_t, C.c_uint32, C.c_float, C.c_float]
+    out = np.empty(n, np.float32)
+    L.std_randn(out, n, seed, sigma, mean)
+    return out
 
 
 def _ptr(a):

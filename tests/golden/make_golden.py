@@ -1,0 +1,73 @@
+"""Generates tests/golden/ref_vectors.npz from the reference engine's own code (oracle/_ref/libref_cpu.so, built from a
+reference checkout by oracle/Makefile).  Run in a container that has the reference; the .npz travels with the repository
+so the CPU tests can pin the oracle where the reference is absent.
+
+Contents: raw blocks of each format with the reference's to_float output; seeded fp32 rows with the reference quantiser's
+bytes (NVFP4, Q6_K); the reference's blob geometry for the benchmark shapes; and the reference CPU expert pool's output
+rows for a small Q6_K and a small NVFP4 layer (inputs are regenerated from the seeds stored alongside).
+"""
+import ctypes as C
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+from oracle import oracle as O   # noqa: E402
+from tests.helpers import make_expert_blobs   # noqa: E402
+
+
+def main():
+    R = O.ref_cpu()
+    assert R is not None, "build oracle/_ref first (make -C oracle ref_cpu)"
+    out = {}
+    rng = np.random.default_rng(2024)
+    # decoders: random blocks (finite super-scales) and the reference's floats
+    for name, t, bs, nv, nblk in (("nvfp4", 40, 36, 64, 8), ("q6k", 14, 210, 256, 3), ("iq1m", 29, 56, 256, 3)):
+        raw = rng.integers(0, 256, size=nblk * bs, dtype=np.uint8)
+        if t == 14:
+            raw.reshape(-1, 210)[:, 209] &= 0x7B
+        if t == 29:
+            raw = O.random_iq1m_rows(rng, 1, nblk * 256)
+        y = np.empty(nblk * nv, np.float32)
+        assert R.ref_dequantize(t, raw.ctypes.data, y, y.size) == 0
+        out[f"dec_{name}_raw"], out[f"dec_{name}_f32"] = raw, y
+    # quantisers
+    for name, t in (("nvfp4", 40), ("q6k", 14)):
+        w = (rng.standard_normal((2, 512)) * 0.02).astype(np.float32)
+        if t == 40:
+            w = (w / (np.abs(w).max() / (6 * 448))).astype(np.float32)
+        w[0, :16] = 0
+        q = np.zeros(2 * O.row_bytes(t, 512), np.uint8)
+        assert R.ref_quantize(t, w, q, 2, 512) == q.size
+        out[f"quant_{name}_in"], out[f"quant_{name}_out"] = w, q
+    # geometry
+    geo = []
+    for cfg in ((14, 14, 2048, 512), (40, 40, 2048, 512), (29, 29, 5120, 2304), (40, 40, 2560, 640), (29, 14, 2048, 512)):
+        o = (C.c_int64 * 7)()
+        err = C.create_string_buffer(256)
+        rc = R.ref_native_fmt(*cfg, 0.0, o, err, 256)
+        geo.append(list(cfg) + ([int(v) for v in o][:6] if rc == 0 else [-1] * 6))
+    out["geometry"] = np.array(geo, np.int64)
+    # the reference's CPU expert pool on a small layer (rows in expert-sorted order)
+    pool = R.ref_pool_create(3)
+    for name, gt, dt in (("q6k", 14, 14), ("nvfp4", 40, 40)):
+        H, I, E, T, k = 512, 256, 4, 6, 2
+        r2 = np.random.default_rng(7)
+        L, blobs = make_expert_blobs(r2, E, gt, dt, H, I)
+        x = r2.standard_normal((T, H)).astype(np.float32)
+        ids = np.stack([r2.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+        cnt, off, slot, src, _ = O.dispatch(ids, k, E)
+        ptrs = (C.c_void_p * E)(*[b.ctypes.data for b in blobs])
+        rows = np.zeros((T * k, H), np.float32)
+        assert R.ref_pool_layer(pool, gt, dt, H, I, 0.0, ptrs, E, off, src, x, T, rows) == 0
+        out[f"pool_{name}_x"], out[f"pool_{name}_ids"], out[f"pool_{name}_rows"] = x, ids, rows
+        out[f"pool_{name}_blobhash"] = np.array([O.fnv1a(*blobs)], np.uint64)
+    R.ref_pool_destroy(pool)
+    np.savez_compressed(Path(__file__).with_name("ref_vectors.npz"), **out)
+    print("wrote ref_vectors.npz:", {k: v.shape for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main()
