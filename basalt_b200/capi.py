@@ -33,6 +33,10 @@ _SIGNATURES = {
                                       C.c_float, P, C.c_int32, P, P, P]),
     "bsx_router": (C.c_int32, [P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_int32,
                                C.c_int32, C.c_float, P, C.c_int32, P, P, P, P]),
+    "bsx_router_logits_x": (C.c_int32, [P, C.c_int32, P, C.c_int32, C.c_int32, C.c_int32, P, P]),
+    "bsx_router_x": (C.c_int32, [P, C.c_int32, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_int32,
+                                 C.c_int32, C.c_float, P, C.c_int32, P, P, P, P]),
+    "bsx_experts_set_phase": (None, [C.c_int32]),
     "bsx_route_tail_skip": (C.c_int32, [P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, P]),
     "bsx_dispatch_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "bsx_dispatch": (C.c_int32, [P, C.c_int64, C.c_int32, C.c_int32, P, P, P, P, C.c_int32, P, P, P, P]),

@@ -97,7 +97,14 @@ size_t row_bytes(int type, int64_t n) {
 }  // namespace
 }  // namespace bsx
 
+namespace bsx {
+static int g_phase = 0;
+int experts_phase() { return g_phase; }
+}  // namespace bsx
+
 using namespace bsx;
+
+extern "C" void bsx_experts_set_phase(int32_t phase) { g_phase = phase == 1 || phase == 2 ? phase : 0; }
 
 extern "C" size_t bsx_row_bytes(int32_t type, int64_t n) { return row_bytes(type, n); }
 extern "C" const char* bsx_version(void) { return "basalt_b200 0.1 (sm_100a)"; }

@@ -42,6 +42,9 @@ __device__ __forceinline__ void store_out(void* out, int kind, int64_t i, float 
     else static_cast<float*>(out)[i] = v;
 }
 
+// 0 all launches, 1 gate/up only, 2 down only (bsx_experts_set_phase)
+int experts_phase();
+
 int32_t experts_grouped_simple(const ExpertArgs& a, cudaStream_t st);
 // returns BSX_E_TYPE when the fast path does not cover the layout (the caller then runs the plain kernels)
 int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st);

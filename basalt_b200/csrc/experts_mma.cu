@@ -1,4 +1,312 @@
+// experts_mma.cu - decode-sized grouped experts for NVFP4 blobs: a bandwidth-bound weight stream through shared memory with
+// the dot products on the tensor cores.
+//
+// Shape of the work (HBM-bound): every touched expert's gate, up and down rows are read exactly once per pass of up to 8
+// activation columns.  Each warp owns 16 weight rows (8 gate rows paired with the 8 matching up rows, or 16 down rows) and
+// streams them in 256-column chunks (144 bytes a row) through its own 4-stage cp.async ring, so no block-wide barrier sits
+// in the stream and ~110 KB a SM is in flight.  A row's E2M1 codes go to fp16 pairs with cvt.rn.f16x2.e2m1x2, are
+// multiplied by the block's UE4M3 scale as fp16 (the product has at most 5 significant bits: exact), and feed
+// mma.sync.m16n8k16 with fp32 accumulation.  The activation columns (up to 8 bf16 tokens, or 4 fp32 tokens split into
+// hi + lo fp16 terms, each column pre-scaled by a power of two so it fits fp16) sit in shared memory permuted into
+// B-fragment order.  Gate and up rows of one neuron land in the same thread's accumulators, so SwiGLU is fused.
+//
+// Semantics: Basalt's native_expert_grouped (include/basalt/kernels/iq_kernels.hpp:77-92; kernels src/kernels/cuda/iq_kernels.cu:
+// 1605-1658 gate/up, :2512-2524 SwiGLU, :2140-2164 down), NVFP4 decoding per src/kernels/cpu/ggml/ggml_quants.c:1397-1422,
+// tail scales per iq_kernels.cu:683-701 - but without the int8 rounding of x and h the reference applies.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
 #include "experts.cuh"
+#include "formats.cuh"
+
 namespace bsx {
-int32_t experts_grouped_mma(const ExpertArgs&, cudaStream_t) { return BSX_E_TYPE; }
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStages = 4;
+constexpr int kRowBytes = 144;                 // 4 NVFP4 blocks = 256 columns of one row
+constexpr int kRows = 16;                      // weight rows per warp
+constexpr int kStageBytes = kRows * kRowBytes; // 2304
+constexpr int kPieces = kStageBytes / 16;      // 144 16-byte pieces a stage
+constexpr int kCols = 8;                       // MMA n: activation columns per pass
+
+enum { MODE_GU = 0, MODE_DOWN = 1 };
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// four E2M1 pairs (one byte each) of a 32-bit word -> four fp16 pairs; low nibble in the low half
+__device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t (&h)[4]) {
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "mov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+        "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+        "}\n"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(w));
+}
+
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The four UE4M3 scale bytes of a block -> fp16 pairs {d, d} for sub-blocks sa and sa + 2, each d = scale / 2^8:
+// (byte & 0x7F) << 7 puts E4M3's exponent and mantissa where fp16 keeps them (value 2^(e-15) (1 + m/8), subnormals
+// included); the scale itself is 2^(e-7) (1 + m/8) (ggml halves it only because its E2M1 table is doubled, and the cvt
+// above yields undoubled values), so the epilogue multiplies the sums by 2^8.  0x7F decodes to 0.
+__device__ __forceinline__ void scale_pairs(uint32_t dw, uint32_t sel_a, uint32_t sel_b, uint32_t& s0, uint32_t& s1) {
+    uint32_t m = dw & 0x7F7F7F7Fu;
+    m &= ~__vcmpeq4(m, 0x7F7F7F7Fu);
+    s0 = __byte_perm(m, 0u, sel_a) << 7;
+    s1 = __byte_perm(m, 0u, sel_b) << 7;
+}
+
+__device__ __forceinline__ float load_x(const void* x, int kind, int64_t row, int64_t K, int c) {
+    if (kind == BSX_X_F32) return static_cast<const float*>(x)[row * K + c];
+    if (kind == BSX_X_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(x)[row * K + c]);
+    const uint8_t* b = static_cast<const uint8_t*>(x) + (row * (K / 32) + (c >> 5)) * 36;
+    return __half2float(*reinterpret_cast<const __half*>(b)) * (float) (int8_t) b[4 + (c & 31)];
+}
+
+// MODE_GU:  rows = 8 gate rows r0.. paired with up rows r0..; x = the call's activations through ent_tok; writes h.
+// MODE_DOWN: rows = 16 down rows; x = h rows of the entries; writes out rows through ent_dst.
+// TERMS = 1: 8 bf16 columns a pass; TERMS = 2: 4 columns a pass, each as hi + lo fp16 terms.
+template <int MODE, int TERMS>
+__global__ void __launch_bounds__(kThreads, 2) nvfp4_mma_kernel(ExpertArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int64_t K = MODE == MODE_GU ? a.L.n_embd : a.L.n_ff;
+    const int n_gran = (int) (K >> 6);                       // 64-column granules
+    __half* xs = reinterpret_cast<__half*>(smem);            // [n_gran][2][8 cols][4][8]
+    float* col_inv = reinterpret_cast<float*>(smem + (size_t) K * kCols * 2);   // [8] inverse column scales, then [8] scales
+    uint8_t* wbase = smem + (size_t) K * kCols * 2 + 64;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    uint8_t* wring = wbase + (size_t) warp * kStages * kStageBytes;
+    const uint32_t wring_s = (uint32_t) __cvta_generic_to_shared(wring);
+    constexpr int NTOK = kCols / TERMS;
+
+    const int64_t n_rows = MODE == MODE_GU ? a.L.n_ff : a.L.n_embd;      // neurons (pairs) or down rows
+    const int64_t r0 = (int64_t) blockIdx.x * (MODE == MODE_GU ? kWarps * 8 : kWarps * 16) + warp * (MODE == MODE_GU ? 8 : 16);
+    const bool live = r0 < n_rows;
+    const int n_chunks = n_gran >> 2;
+
+    // this lane's copy duty inside a stage: pieces lane, lane + 32, ... (< 144); row = piece / 9
+    int cp_row[5], cp_off[5];
+#pragma unroll
+    for (int j = 0; j < 5; ++j) {
+        const int p = lane + 32 * j;
+        cp_row[j] = p / 9;
+        cp_off[j] = (p % 9) * 16;
+    }
+    const uint32_t sel_a = (uint32_t) (t >> 1) | (4u << 4) | ((uint32_t) (t >> 1) << 8) | (4u << 12);
+    const uint32_t sel_b = sel_a + 0x0202u;   // sub-block + 2
+
+    const int ng = min(*a.n_groups, (int) a.cap_groups);
+    for (int grp = blockIdx.y; grp < ng; grp += gridDim.y) {
+        const uint8_t* blob = reinterpret_cast<const uint8_t*>(a.grp_ptr[grp]);
+        const float* tail = reinterpret_cast<const float*>(blob + a.L.bytes - 16);
+        const int e0 = a.grp_start[grp], e1 = min(a.grp_start[grp + 1], (int) a.cap_entries);
+        // global address of this lane's pieces at chunk 0
+        const uint8_t* src[5];
+#pragma unroll
+        for (int j = 0; j < 5; ++j) {
+            const int row = cp_row[j];
+            const uint8_t* rp;
+            if (MODE == MODE_GU)
+                rp = row < 8 ? blob + (size_t) (r0 + row) * a.L.gu_row : blob + a.L.up_off + (size_t) (r0 + row - 8) * a.L.up_row;
+            else
+                rp = blob + a.L.down_off + (size_t) (r0 + row) * a.L.d_row;
+            src[j] = rp + cp_off[j];
+        }
+        auto issue = [&](int chunk) {
+            if (live && chunk < n_chunks) {
+                const uint32_t dst = wring_s + (uint32_t) (chunk % kStages) * kStageBytes;
+#pragma unroll
+                for (int j = 0; j < 5; ++j)
+                    if (lane + 32 * j < kPieces)
+                        cp_async16(dst + (uint32_t) (cp_row[j] * kRowBytes + cp_off[j]), src[j] + (size_t) chunk * kRowBytes);
+            }
+            cp_async_commit();
+        };
+
+        for (int eb = e0; eb < e1; eb += NTOK) {
+            const int ntok = min(NTOK, e1 - eb);
+            // the weight stream does not depend on x: start it before the activations are staged
+#pragma unroll
+            for (int c = 0; c < kStages - 1; ++c) issue(c);
+
+            __syncthreads();   // the previous pass has finished reading xs / col_inv
+            if (warp < ntok) {
+                const int64_t row = MODE == MODE_GU ? (int64_t) a.ent_tok[eb + warp] : (int64_t) (eb + warp);
+                const void* xp = MODE == MODE_GU ? a.x : (const void*) a.h;
+                const int kind = MODE == MODE_GU ? a.x_kind : BSX_X_F32;
+                float amax = 0.f;
+                for (int c = lane; c < K; c += 32) amax = fmaxf(amax, fabsf(load_x(xp, kind, row, K, c)));
+                amax = warp_max_xor(amax);
+                if (lane == 0) {
+                    int e = 0;
+                    float s = 1.f, inv = 1.f;
+                    if (amax > 0.f && amax <= 3.0e38f) {
+                        frexpf(amax, &e);                     // amax = m 2^e, m in [0.5, 1)
+                        e = max(-100, min(100, 14 - e));      // amax 2^(14-e) lies in [2^13, 2^14): inside fp16
+                        s = ldexpf(1.f, e);
+                        inv = ldexpf(1.f, -e);
+                    }
+                    col_inv[warp] = inv;
+                    col_inv[8 + warp] = s;
+                }
+            }
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < ntok * (int) K; idx += kThreads) {
+                const int j = idx / (int) K, c = idx - j * (int) K;
+                const int64_t row = MODE == MODE_GU ? (int64_t) a.ent_tok[eb + j] : (int64_t) (eb + j);
+                const float v = load_x(MODE == MODE_GU ? a.x : (const void*) a.h, MODE == MODE_GU ? a.x_kind : BSX_X_F32, row, K, c) * col_inv[8 + j];
+                const int gran = c >> 6, jj = c & 15, sb = (c >> 4) & 3;
+                const int hh = sb >> 1, tt = 2 * (sb & 1) + ((jj & 7) >> 2), p = 2 * (jj & 3) + (jj >> 3);
+                const __half hi = __float2half_rn(v);
+                const size_t base = ((size_t) (gran * 2 + hh) * kCols) * 32 + (size_t) tt * 8 + p;
+                xs[base + (size_t) (j * TERMS) * 32] = hi;
+                if (TERMS == 2) xs[base + (size_t) (j * TERMS + 1) * 32] = __float2half_rn(v - __half2float(hi));
+            }
+            __syncthreads();
+
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            if (live) {
+                const bool col_live = g < ntok * TERMS;
+                for (int chunk = 0; chunk < n_chunks; ++chunk) {
+                    issue(chunk + kStages - 1);
+                    cp_async_wait<kStages - 1>();
+                    __syncwarp();
+                    const uint8_t* st = wring + (size_t) (chunk % kStages) * kStageBytes;
+                    const uint32_t* ra = reinterpret_cast<const uint32_t*>(st + g * kRowBytes);          // row g
+                    const uint32_t* rb = reinterpret_cast<const uint32_t*>(st + (g + 8) * kRowBytes);    // row g + 8
+#pragma unroll
+                    for (int blk = 0; blk < 4; ++blk) {
+                        const int gran = chunk * 4 + blk;
+                        uint4 b0 = make_uint4(0u, 0u, 0u, 0u), b1 = b0;
+                        if (col_live) {
+                            const uint4* bp = reinterpret_cast<const uint4*>(xs + ((size_t) (gran * 2) * kCols + g) * 32 + t * 8);
+                            b0 = bp[0];
+                            b1 = bp[kCols * 4];   // the second half-granule: + 8 columns * 32 halves
+                        }
+                        uint32_t sa0, sa1, sb0, sb1, qa0[4], qa1[4], qb0[4], qb1[4];
+                        scale_pairs(ra[9 * blk], sel_a, sel_b, sa0, sa1);
+                        scale_pairs(rb[9 * blk], sel_a, sel_b, sb0, sb1);
+                        cvt_e2m1x8(ra[9 * blk + 1 + t], qa0);
+                        cvt_e2m1x8(ra[9 * blk + 5 + t], qa1);
+                        cvt_e2m1x8(rb[9 * blk + 1 + t], qb0);
+                        cvt_e2m1x8(rb[9 * blk + 5 + t], qb1);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            qa0[i] = hmul2_bits(qa0[i], sa0);
+                            qa1[i] = hmul2_bits(qa1[i], sa1);
+                            qb0[i] = hmul2_bits(qb0[i], sb0);
+                            qb1[i] = hmul2_bits(qb1[i], sb1);
+                        }
+                        mma_f16(acc, qa0[0], qb0[0], qa0[1], qb0[1], b0.x, b0.y);
+                        mma_f16(acc, qa0[2], qb0[2], qa0[3], qb0[3], b0.z, b0.w);
+                        mma_f16(acc, qa1[0], qb1[0], qa1[1], qb1[1], b1.x, b1.y);
+                        mma_f16(acc, qa1[2], qb1[2], qa1[3], qb1[3], b1.z, b1.w);
+                    }
+                    __syncwarp();   // every lane is done with this stage before a later issue overwrites it
+                }
+            } else {
+                // keep the commit-group count in step (nothing was copied)
+                cp_async_wait<0>();
+            }
+            // epilogue: undo the column scale and the 2^-8 of the fp16 block scales, apply the tail scales
+            if (live) {
+                if (MODE == MODE_GU) {
+                    const float sg = tail[0] * 256.f, su = tail[1] * 256.f;
+                    if (TERMS == 1) {
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            const int j = 2 * t + q;
+                            if (j < ntok) {
+                                const float f = col_inv[j];
+                                a.h[(size_t) (eb + j) * a.L.n_ff + r0 + g] = swiglu(acc[q] * f * sg, acc[2 + q] * f * su, a.L);
+                            }
+                        }
+                    } else if (t < ntok) {
+                        const float f = col_inv[t];
+                        a.h[(size_t) (eb + t) * a.L.n_ff + r0 + g] = swiglu((acc[0] + acc[1]) * f * sg, (acc[2] + acc[3]) * f * su, a.L);
+                    }
+                } else {
+                    const float sd = tail[2] * 256.f;
+                    if (TERMS == 1) {
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            const int j = 2 * t + q;
+                            if (j < ntok) {
+                                const float f = col_inv[j] * sd;
+                                const int64_t o = (int64_t) a.ent_dst[eb + j] * a.L.n_embd + r0 + g;
+                                store_out(a.out, a.out_kind, o, acc[q] * f);
+                                store_out(a.out, a.out_kind, o + 8, acc[2 + q] * f);
+                            }
+                        }
+                    } else if (t < ntok) {
+                        const float f = col_inv[t] * sd;
+                        const int64_t o = (int64_t) a.ent_dst[eb + t] * a.L.n_embd + r0 + g;
+                        store_out(a.out, a.out_kind, o, (acc[0] + acc[1]) * f);
+                        store_out(a.out, a.out_kind, o + 8, (acc[2] + acc[3]) * f);
+                    }
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+size_t smem_bytes(int64_t K) { return (size_t) K * kCols * 2 + 64 + (size_t) kWarps * kStages * kStageBytes; }
+
+template <int MODE, int TERMS>
+int32_t launch(const ExpertArgs& a, cudaStream_t st) {
+    const int64_t K = MODE == MODE_GU ? a.L.n_embd : a.L.n_ff;
+    const size_t smem = smem_bytes(K);
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(nvfp4_mma_kernel<MODE, TERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int32_t) e;
+        configured[dev] = true;
+    }
+    const int64_t rows = MODE == MODE_GU ? a.L.n_ff : a.L.n_embd;
+    const int per_block = MODE == MODE_GU ? kWarps * 8 : kWarps * 16;
+    const unsigned gy = (unsigned) (a.cap_groups < 1 ? 1 : a.cap_groups > 1024 ? 1024 : a.cap_groups);
+    nvfp4_mma_kernel<MODE, TERMS><<<dim3((unsigned) ((rows + per_block - 1) / per_block), gy), kThreads, smem, st>>>(a);
+    return launch_status();
+}
+
+}  // namespace
+
+int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st) {
+    const bsx_expert_layout& L = a.L;
+    if (L.gu_type != kTypeNVFP4 || L.up_type != kTypeNVFP4 || L.d_type != kTypeNVFP4) return BSX_E_TYPE;
+    // 16-byte row chunks: both K dimensions must be whole 256-column chunks; the activation image must fit shared memory
+    if (L.n_embd % 256 || L.n_ff % 256 || L.n_ff % 8 || L.n_embd % 16) return BSX_E_TYPE;
+    if (smem_bytes(L.n_embd) > 200 * 1024 || smem_bytes(L.n_ff) > 200 * 1024) return BSX_E_TYPE;
+    const int phase = experts_phase();
+    int32_t rc = BSX_OK;
+    if (phase != 2) rc = a.x_kind == BSX_X_BF16 ? launch<MODE_GU, 1>(a, st) : launch<MODE_GU, 2>(a, st);
+    if (rc != BSX_OK || phase == 1) return rc;
+    return launch<MODE_DOWN, 2>(a, st);
+}
+
+}  // namespace bsx

@@ -36,9 +36,16 @@ constexpr int kTokTile = 8;
 // G gate rows a block, NV float4 a thread and row.  Each (row, token) sum runs exactly as
 // src/kernels/cuda/router.cu:49-88 defines it: thread i owns float4 columns i, i + 256, ... as one fmaf chain, the warp's 32
 // chains are summed by xor butterfly, and the 8 warp sums are added in warp order.
-template <int NV, int G>
+__device__ __forceinline__ float4 load_x4(const void* x, size_t row, int n_embd, int i, bool bf16) {
+    if (!bf16) return reinterpret_cast<const float4*>(static_cast<const float*>(x) + row * n_embd)[i];
+    const uint2 u = reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(x) + row * n_embd)[i];
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16),
+                       __uint_as_float(u.y & 0xFFFF0000u));
+}
+
+template <int NV, int G, bool BF16>
 __global__ void __launch_bounds__(kLogitThreads)
-router_logits_kernel(const float* __restrict__ x, const float* __restrict__ gate, int n_embd, int n_expert, int n_tokens,
+router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate, int n_embd, int n_expert, int n_tokens,
                      int tok_per_block, float* __restrict__ logits) {
     __shared__ float red[G][kTokTile][kLogitThreads / 32];
     const int n4 = n_embd >> 2;
@@ -57,7 +64,6 @@ router_logits_kernel(const float* __restrict__ x, const float* __restrict__ gate
     for (int t0 = t_begin; t0 < t_end; t0 += kTokTile) {
         const int nt = min(kTokTile, t_end - t0);
         for (int t = 0; t < nt; ++t) {
-            const float4* xv = reinterpret_cast<const float4*>(x + (size_t) (t0 + t) * n_embd);
             float acc[G];
 #pragma unroll
             for (int g = 0; g < G; ++g) acc[g] = 0.f;
@@ -65,7 +71,7 @@ router_logits_kernel(const float* __restrict__ x, const float* __restrict__ gate
             for (int c = 0; c < NV; ++c) {
                 const int i = threadIdx.x + c * kLogitThreads;
                 if (i < n4) {
-                    const float4 v = xv[i];
+                    const float4 v = load_x4(x, (size_t) (t0 + t), n_embd, i, BF16);
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
                         acc[g] = fmaf(w[g][c].x, v.x, acc[g]);
@@ -96,23 +102,24 @@ router_logits_kernel(const float* __restrict__ x, const float* __restrict__ gate
 }
 
 template <int NV, int G>
-void launch_logits(const float* x, const float* gate, int T, int E, int H, float* logits, cudaStream_t st) {
+void launch_logits(const void* x, bool bf16, const float* gate, int T, int E, int H, float* logits, cudaStream_t st) {
     const int tpb = T <= 256 ? kTokTile : 8 * kTokTile;
     const dim3 grid((unsigned) (E / G), (unsigned) ((T + tpb - 1) / tpb));
-    router_logits_kernel<NV, G><<<grid, kLogitThreads, 0, st>>>(x, gate, H, E, T, tpb, logits);
+    if (bf16) router_logits_kernel<NV, G, true><<<grid, kLogitThreads, 0, st>>>(x, gate, H, E, T, tpb, logits);
+    else router_logits_kernel<NV, G, false><<<grid, kLogitThreads, 0, st>>>(x, gate, H, E, T, tpb, logits);
 }
 
 template <int G>
-bool dispatch_nv(int nv, const float* x, const float* gate, int T, int E, int H, float* logits, cudaStream_t st) {
+bool dispatch_nv(int nv, const void* x, bool bf16, const float* gate, int T, int E, int H, float* logits, cudaStream_t st) {
     switch (nv) {
-        case 1: launch_logits<1, G>(x, gate, T, E, H, logits, st); return true;
-        case 2: launch_logits<2, G>(x, gate, T, E, H, logits, st); return true;
-        case 3: if constexpr (G <= 4) { launch_logits<3, G>(x, gate, T, E, H, logits, st); return true; } return false;
-        case 4: if constexpr (G <= 4) { launch_logits<4, G>(x, gate, T, E, H, logits, st); return true; } return false;
-        case 5: if constexpr (G <= 2) { launch_logits<5, G>(x, gate, T, E, H, logits, st); return true; } return false;
-        case 6: if constexpr (G <= 2) { launch_logits<6, G>(x, gate, T, E, H, logits, st); return true; } return false;
-        case 7: if constexpr (G <= 2) { launch_logits<7, G>(x, gate, T, E, H, logits, st); return true; } return false;
-        case 8: if constexpr (G <= 2) { launch_logits<8, G>(x, gate, T, E, H, logits, st); return true; } return false;
+        case 1: launch_logits<1, G>(x, bf16, gate, T, E, H, logits, st); return true;
+        case 2: launch_logits<2, G>(x, bf16, gate, T, E, H, logits, st); return true;
+        case 3: if constexpr (G <= 4) { launch_logits<3, G>(x, bf16, gate, T, E, H, logits, st); return true; } return false;
+        case 4: if constexpr (G <= 4) { launch_logits<4, G>(x, bf16, gate, T, E, H, logits, st); return true; } return false;
+        case 5: if constexpr (G <= 2) { launch_logits<5, G>(x, bf16, gate, T, E, H, logits, st); return true; } return false;
+        case 6: if constexpr (G <= 2) { launch_logits<6, G>(x, bf16, gate, T, E, H, logits, st); return true; } return false;
+        case 7: if constexpr (G <= 2) { launch_logits<7, G>(x, bf16, gate, T, E, H, logits, st); return true; } return false;
+        case 8: if constexpr (G <= 2) { launch_logits<8, G>(x, bf16, gate, T, E, H, logits, st); return true; } return false;
         default: return false;
     }
 }
@@ -332,27 +339,40 @@ bool make_held(const int32_t* const* tabs, int n, HeldTabs& h) {
 
 using namespace bsx;
 
-extern "C" int32_t bsx_router_logits(const float* x, const float* gate, int32_t T, int32_t E, int32_t H, float* logits, void* stream) {
+// launches the logits kernel (no synchronisation); x is fp32 or bf16 rows
+static int32_t logits_launch(const void* x, int32_t x_kind, const float* gate, int32_t T, int32_t E, int32_t H, float* logits, cudaStream_t st) {
     if (E < 32 || E % 32 || H < 128 || H % 128 || H > 8192 || T < 0) return BSX_E_GEOMETRY;
+    if (x_kind != BSX_X_F32 && x_kind != BSX_X_BF16) return BSX_E_GEOMETRY;
     if (T == 0) return BSX_OK;
     if (!aligned(x, 16) || !aligned(gate, 16) || !aligned(logits, 4)) return BSX_E_POINTER;
-    const cudaStream_t st = (cudaStream_t) stream;
+    const bool bf16 = x_kind == BSX_X_BF16;
     const int nv = (H / 4 + kLogitThreads - 1) / kLogitThreads;
     // the most gate rows a block whose registers fit and whose grid still covers the SMs twice
     int G = nv <= 2 ? 8 : nv <= 4 ? 4 : 2;
     const int tiles = (T + kTokTile - 1) / kTokTile;
     while (G > 2 && (int64_t) (E / G) * tiles < 2 * (int64_t) sm_count()) G >>= 1;
     bool ok = false;
-    if (G == 8) ok = dispatch_nv<8>(nv, x, gate, T, E, H, logits, st);
-    else if (G == 4) ok = dispatch_nv<4>(nv, x, gate, T, E, H, logits, st);
-    else ok = dispatch_nv<2>(nv, x, gate, T, E, H, logits, st);
-    if (!ok) return BSX_E_GEOMETRY;
-    const int32_t rc = launch_status();
+    if (G == 8) ok = dispatch_nv<8>(nv, x, bf16, gate, T, E, H, logits, st);
+    else if (G == 4) ok = dispatch_nv<4>(nv, x, bf16, gate, T, E, H, logits, st);
+    else ok = dispatch_nv<2>(nv, x, bf16, gate, T, E, H, logits, st);
+    return ok ? launch_status() : BSX_E_GEOMETRY;
+}
+
+static int32_t sync_if_null(int32_t rc, void* stream) {
     if (rc == BSX_OK && !stream) {
         const cudaError_t e = cudaStreamSynchronize(nullptr);
         if (e != cudaSuccess) return (int32_t) e;
     }
     return rc;
+}
+
+extern "C" int32_t bsx_router_logits(const float* x, const float* gate, int32_t T, int32_t E, int32_t H, float* logits, void* stream) {
+    return sync_if_null(logits_launch(x, BSX_X_F32, gate, T, E, H, logits, (cudaStream_t) stream), stream);
+}
+
+extern "C" int32_t bsx_router_logits_x(const void* x, int32_t x_kind, const float* gate, int32_t T, int32_t E, int32_t H, float* logits,
+                                       void* stream) {
+    return sync_if_null(logits_launch(x, x_kind, gate, T, E, H, logits, (cudaStream_t) stream), stream);
 }
 
 extern "C" int32_t bsx_router_select(const float* logits, const float* bias, int32_t T, int32_t E, int32_t k, int32_t gate_kind,
@@ -401,32 +421,25 @@ extern "C" int32_t bsx_router_select(const float* logits, const float* bias, int
     return rc;
 }
 
+extern "C" int32_t bsx_router_x(const void* x, int32_t x_kind, const float* gate, const float* bias, int32_t T, int32_t E, int32_t H,
+                                int32_t k, int32_t gate_kind, float weight_scale, int32_t n_group, int32_t topk_group, float prior,
+                                const int32_t* const* held_tabs, int32_t n_held, float* logits, int32_t* ids, float* weights,
+                                void* stream) {
+    // the limits of the reference's router() (src/kernels/cuda/router.cu:235), E widened to 1024
+    if (E < 32 || E % 32 || E > 1024 || k < 1 || k > E || k > 32) return BSX_E_GEOMETRY;
+    if ((gate_kind == BSX_GATE_SIGMOID || gate_kind == BSX_GATE_SQRT_SOFTPLUS) && k > 16) return BSX_E_GEOMETRY;
+    const int32_t rc = logits_launch(x, x_kind, gate, T, E, H, logits, (cudaStream_t) stream);   // same stream, no sync in between
+    if (rc != BSX_OK || T == 0) return rc;
+    return bsx_router_select(logits, bias, T, E, k, gate_kind, weight_scale, n_group, topk_group, prior, held_tabs, n_held, ids,
+                             weights, stream);
+}
+
 extern "C" int32_t bsx_router(const float* x, const float* gate, const float* bias, int32_t T, int32_t E, int32_t H, int32_t k,
                               int32_t gate_kind, float weight_scale, int32_t n_group, int32_t topk_group, float prior,
                               const int32_t* const* held_tabs, int32_t n_held, float* logits, int32_t* ids, float* weights,
                               void* stream) {
-    // the reference's router() limits (src/kernels/cuda/router.cu:235) apply to the gates it has
-    if ((gate_kind == BSX_GATE_SIGMOID || gate_kind == BSX_GATE_SQRT_SOFTPLUS) && (k > 16)) return BSX_E_GEOMETRY;
-    if (E < 32 || E % 32 || E > 1024 || k < 1 || k > E) return BSX_E_GEOMETRY;
-    // both launches go to the same stream; with a null stream the select call synchronises at the end
-    const cudaStream_t st = (cudaStream_t) stream;
-    if (E < 32 || E % 32 || H < 128 || H % 128 || H > 8192 || T < 0) return BSX_E_GEOMETRY;
-    if (T == 0) return BSX_OK;
-    int32_t rc;
-    if (stream) rc = bsx_router_logits(x, gate, T, E, H, logits, stream);
-    else {
-        // no synchronisation between the two stages: launch on the default stream without the trailing sync
-        const int nv = (H / 4 + kLogitThreads - 1) / kLogitThreads;
-        int G = nv <= 2 ? 8 : nv <= 4 ? 4 : 2;
-        const int tiles = (T + kTokTile - 1) / kTokTile;
-        while (G > 2 && (int64_t) (E / G) * tiles < 2 * (int64_t) sm_count()) G >>= 1;
-        bool ok = G == 8 ? dispatch_nv<8>(nv, x, gate, T, E, H, logits, st)
-                  : G == 4 ? dispatch_nv<4>(nv, x, gate, T, E, H, logits, st) : dispatch_nv<2>(nv, x, gate, T, E, H, logits, st);
-        rc = ok ? launch_status() : BSX_E_GEOMETRY;
-    }
-    if (rc != BSX_OK) return rc;
-    return bsx_router_select(logits, bias, T, E, k, gate_kind, weight_scale, n_group, topk_group, prior, held_tabs, n_held, ids,
-                             weights, stream);
+    return bsx_router_x(x, BSX_X_F32, gate, bias, T, E, H, k, gate_kind, weight_scale, n_group, topk_group, prior, held_tabs, n_held,
+                        logits, ids, weights, stream);
 }
 
 extern "C" int32_t bsx_route_tail_skip(int32_t* ids, float* weights, const int32_t* const* held_tabs, int32_t n_held,

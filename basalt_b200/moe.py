@@ -21,7 +21,10 @@ from .capi import (GATE_SIGMOID, GATE_SOFTMAX, GATE_SOFTMAX_F64, GATE_SOFTMAX_FA
 def _stream(stream=None) -> int:
     if stream is None:
         stream = torch.cuda.current_stream()
-    return int(stream.cuda_stream) if hasattr(stream, "cuda_stream") else int(stream)
+    h = int(stream.cuda_stream) if hasattr(stream, "cuda_stream") else int(stream)
+    # torch's default stream is the null handle, which the expert / dispatch / combine family refuses (as the reference
+    # does); cudaStreamLegacy (1) names the same stream explicitly
+    return h if h != 0 else 1
 
 
 def _p(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -224,14 +227,14 @@ class MoELayer:
             self._s_T = -1
 
     def forward(self, x: torch.Tensor, x_router: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
-        """x: [T][n_embd] fp32 or bf16 activations for the experts; x_router: the fp32 rows the router reads (defaults to
-        x, converted when x is bf16).  Returns y [T][n_embd] fp32 (a view of an internal buffer)."""
+        """x: [T][n_embd] fp32 or bf16 activations; x_router: other rows for the router to read (defaults to x).
+        Returns y [T][n_embd] fp32 (a view of an internal buffer)."""
         T = x.shape[0]
         a, lib, st = self.args, capi.lib(), _stream(stream)
         assert T <= self.max_tokens
-        xr = x_router if x_router is not None else (x if x.dtype == torch.float32 else x.float())
+        xr = x_router if x_router is not None else x     # fp32 or bf16 rows; bf16 is widened exactly inside the kernel
         hp, hn, keep = _held(a)
-        check("bsx_router", lib.bsx_router(_p(xr), _p(self.gate_w), _p(self.bias), T, a.n_expert, a.n_embd, a.k, a.gate,
+        check("bsx_router", lib.bsx_router_x(_p(xr), X_BF16 if xr.dtype == torch.bfloat16 else X_F32, _p(self.gate_w), _p(self.bias), T, a.n_expert, a.n_embd, a.k, a.gate,
                                             a.weight_scale, a.n_group, a.topk_group, a.prior, hp, hn, _p(self.logits), _p(self.ids),
                                             _p(self.w), st))
         check("bsx_moe_plan", lib.bsx_moe_plan(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), _p(self.ptr), _p(self.start),
@@ -252,27 +255,3 @@ class MoELayer:
             shared = self.s_out
         check("bsx_combine", lib.bsx_combine(_p(self.rows), None, _p(self.w), _p(shared), None, T, a.k, self.L.n_embd, _p(self.y), st))
         return self.y[:T]
-EOF
-cat > basalt_b200/__init__.py <<'EOF'
-"""basalt_b200 - the Basalt engine's mixture-of-experts layer hot path as hand-written CUDA for NVIDIA B200 (sm_100a),
-behind a C ABI (include/basalt_b200.h) and a thin host-side mirror of the reference's operator interface (moe.py)."""
-from . import capi  # noqa: F401
-
-__all__ = ["capi", "moe", "build"]
-EOF
-python -c "
-from basalt_b200 import capi
-print(capi.lib().bsx_version())
-import numpy as np, ctypes as C
-from oracle import oracle as O
-rng=np.random.default_rng(1)
-for t,bs,nv in ((40,36,64),(14,210,256),(29,56,256)):
-    raw = rng.integers(0,256,size=512*bs,dtype=np.uint8)
-    if t==14: raw.reshape(-1,210)[:,209]&=0x7b
-    if t==29: raw = O.random_iq1m_rows(rng, 1, 512*256)
-    n = raw.size//bs*nv
-    a = O.dequantize(t, raw, 1, n)
-    b = np.empty(n, np.float32)
-    rc = capi.lib().bsx_host_decode_row(t, raw.ctypes.data, b.ctypes.data, n)
-    print(t, rc, np.array_equal(a.view(np.uint32).reshape(-1), b.view(np.uint32)))
-"

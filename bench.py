@@ -1,0 +1,338 @@
+#!/usr/bin/env python
+"""MoE-layer throughput benchmark: `python bench.py --gpus N --steps K --warmup W [--impl reference]`.
+
+Workload at N = 1 (BASELINE.json configs[1], the configuration the metric is quoted on): a Flash-Next-style MoE layer at
+decode - hidden 2048, 512 routed experts + 1 shared expert, intermediate 512, softmax top-10 renormalised, NVFP4 experts
+(E2M1 codes, UE4M3 scale per 16, fp32 scale per matrix) quantised from N(0, 0.02^2), bf16 activations N(0, 1), 64 tokens per
+step.  A step is one pass of the layer over one batch: router -> plan -> grouped experts (+ shared) -> combine.  Inputs are
+seeded synthetic data of those shapes and distributions (no dataset or checkpoint is involved).
+
+The JSON line carries: `value` = tokens/s with inputs resident in HBM (CUDA events, max over ranks); `e2e` = the same through
+the public call with host buffers (pinned host -> device copy of the step's activations and device -> host read of its
+output inside the timed region); `roofline` = the dominant kernel (the routed experts' gate/up stream) against the measured
+HBM copy bandwidth; `cpu_baseline` = the reference engine's own CPU expert-offload path (its thread pool and AVX kernels,
+compiled from a reference checkout into oracle/_ref) on the same layer and tokens, timed on this box's host cores.
+
+`--impl reference` times that CPU path alone (all host threads), printing the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CFG = dict(workload="flash-next-style MoE layer decode, 64 tokens/step", hidden=2048, n_expert=512, n_shared=1, intermediate=512,
+           top_k=10, router="softmax fp32 top-10 renormalised", expert_format="NVFP4 (ggml block_nvfp4 + fp32 tail scales)",
+           activations="bf16", tokens_per_step=64)
+H, E, I, K_TOP, T = 2048, 512, 512, 10, 64
+LAYER_COPIES = 4   # the step cycles through copies of the layer (3.6 GB) so the 126 MB L2 cannot hold the weights
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+def make_layer_weights(device, seed=0):
+    """gate [E][H] fp32 and E + 1 NVFP4 blobs (the last is the shared expert), quantised from N(0, 0.02^2)."""
+    from basalt_b200 import pack
+    g = torch.Generator(device=device).manual_seed(seed)
+    gate = (torch.randn((E, H), generator=g, device=device) * 0.02).float()
+    blob_bytes = 3 * I * (H // 64 * 36) + 16
+    stride = (blob_bytes + 15) // 16 * 16
+    blobs = torch.zeros((E + 1, stride), dtype=torch.uint8, device=device)
+    for e in range(E + 1):
+        G = torch.randn((I, H), generator=g, device=device) * 0.02
+        U = torch.randn((I, H), generator=g, device=device) * 0.02
+        D = torch.randn((H, I), generator=g, device=device) * 0.02
+        blobs[e, :blob_bytes] = pack.pack_nvfp4_expert(G, U, D)
+    return gate, blobs, blob_bytes
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 7:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------------- CPU reference arm
+def cpu_reference_layer(gate, blobs_host, blob_bytes, xs_host, steps, warmup, workers=None):
+    """The reference engine's CPU expert-offload path (ExpertPool::run_split_multi_native over its AVX kernels, from
+    oracle/_ref/libref_cpu.so) for the same layer: the oracle's CPU router / dispatch / combine around it.  Returns
+    (seconds per step list, cores used, kind)."""
+    from oracle import oracle as O
+    R = O.ref_cpu()
+    n_thr = workers or max(1, (os.cpu_count() or 2))
+    gate = np.ascontiguousarray(gate, np.float32)
+    times = []
+    if R is not None:
+        pool = R.ref_pool_create(max(1, n_thr - 1))     # the host thread drains too (pool.hpp:57-76)
+        ptrs = (C.c_void_p * E)(*[blobs_host[e].ctypes.data for e in range(E)])
+        sptr = (C.c_void_p * 1)(blobs_host[E].ctypes.data)
+        s_off = np.array([0, T], np.int32)
+        s_src = np.arange(T, dtype=np.int32)
+    L = O.Layout(O.T_NVFP4, O.T_NVFP4, H, I)
+    for it in range(warmup + steps):
+        x = xs_host[it % len(xs_host)]
+        t0 = time.perf_counter()
+        logits = O.router_logits(x, gate)
+        ids, w = O.router_select(logits, None, K_TOP, O.GATE_SOFTMAX)
+        cnt, off, slot, src, _ = O.dispatch(ids, K_TOP, E)
+        rows = np.zeros((T * K_TOP, H), np.float32)
+        shared = np.zeros((T, H), np.float32)
+        if R is not None:
+            assert R.ref_pool_layer(pool, 40, 40, H, I, 0.0, ptrs, E, off, src, x, T, rows) == 0
+            assert R.ref_pool_layer(pool, 40, 40, H, I, 0.0, sptr, 1, s_off, s_src, x, T, shared) == 0
+        else:   # the plain-C port: dequantise and multiply, one expert at a time
+            for e in range(E):
+                if cnt[e]:
+                    rows[off[e]:off[e + 1]] = O.expert_forward(L, blobs_host[e][:blob_bytes], x[src[off[e]:off[e + 1]]])
+            shared = O.expert_forward(L, blobs_host[E][:blob_bytes], x)
+        y = O.combine(rows, slot, w, shared)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    if R is not None:
+        R.ref_pool_destroy(pool)
+    return times, n_thr, ("reference" if R is not None else "port"), y
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    dev = torch.device("cuda:0" if torch.cuda.is_available() else "cpu")
+    gate, blobs, blob_bytes = make_layer_weights(dev)
+    gate_h, blobs_h = gate.cpu().numpy(), blobs.cpu().numpy()
+    del gate, blobs
+    rng = np.random.default_rng(1)
+    xs = [torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).bfloat16().float().numpy() for _ in range(4)]
+    times, cores, kind, _ = cpu_reference_layer(gate_h, blobs_h, blob_bytes, xs, args.steps, args.warmup)
+    ms = 1e3 * sum(times) / len(times)
+    val = T / (ms / 1e3)
+    line = {"impl": "reference", "metric": "MoE-layer tokens/s (decode)", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x NVFP4 dot products, fp32 accumulation (the reference's CPU arithmetic)", "data": "synthetic",
+            "config": CFG,
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": kind,
+                             "sample": f"{args.steps} full layer steps of 64 tokens (all 640 routed rows + shared expert)"},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------------------------- the B200 arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the MoE layer has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    from basalt_b200 import build, capi, moe
+    if rank == 0:
+        build.build()
+    if world > 1:
+        dist.barrier()
+    lib = capi.lib()
+
+    gate, blobs, blob_bytes = make_layer_weights(dev)
+    L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
+    assert L.bytes == blob_bytes
+    rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
+    layers = []
+    for c in range(LAYER_COPIES):
+        b = blobs if c == 0 else blobs.clone()
+        layers.append(moe.MoELayer(gate if c == 0 else gate.clone(), None, b[:E], L, rargs, shared_blob=b[E], max_tokens=T))
+    n_batches = 8
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    xs = [torch.randn((T, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
+    xr = [x.float() for x in xs]   # the router reads fp32 rows (the reference's router ABI); produced by the step before the layer
+    stream = torch.cuda.Stream(device=dev)
+
+    def step(i, x=None):
+        return layers[i % LAYER_COPIES].forward(xs[i % n_batches] if x is None else x, xr[i % n_batches] if x is None else None, stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup):
+            step(i)
+        barrier()
+        # ---- resident-input throughput
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            ev0.record(stream)
+            for i in range(args.steps):
+                step(i)
+            ev1.record(stream)
+            barrier()
+        ms_total = ev0.elapsed_time(ev1)
+        # ---- end to end: pinned host activations in, host output out, every step
+        x_host = [x.cpu().pin_memory() for x in xs]
+        xin = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        y_host = torch.empty((T, H), dtype=torch.float32).pin_memory()
+        for i in range(3):
+            xin.copy_(x_host[i % n_batches], non_blocking=True)
+            y_host.copy_(step(i, xin), non_blocking=True)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(args.steps):
+            xin.copy_(x_host[i % n_batches], non_blocking=True)
+            y_host.copy_(step(i, xin), non_blocking=True)
+            stream.synchronize()          # the caller reads the step's result before it issues the next step
+        e1.record(stream)
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
+        # ---- per-stage device times for the roofline (same steps, events between the C ABI calls)
+        stage_ms, gu_bytes = instrumented_pass(layers, xs, xr, stream, min(args.steps, 100), L)
+        barrier()
+
+    times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = times.tolist()
+    if rank != 0:
+        return
+    ms_step = ms_total / args.steps
+    peak, peak_src = measured_peaks()
+    gu_ms = stage_ms["experts_gate_up"]
+    achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
+    line = {
+        "metric": "MoE-layer tokens/s (decode)", "value": T * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16 x NVFP4 tensor-core products, fp32 accumulation", "data": "synthetic",
+        "config": dict(CFG, l2_policy=f"weights cycle through {LAYER_COPIES} layer copies (3.6 GB) and each step touches ~650 MB: larger than L2",
+                       parallelism="single GPU" if world == 1 else f"ep{world}"),
+        "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
+        "gpu_launches": 8 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "nvfp4_mma_kernel<gate/up> (routed experts)", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
+                     "algorithmic_bytes_per_launch": gu_bytes, "kernel_ms": gu_ms, "frac_of_nominal_8TBs": achieved / 8000.0},
+        "stage_ms": stage_ms,
+        "clocks": clocks.summary(),
+    }
+    if not args.no_cpu_baseline:
+        try:
+            gate_h, blobs_h = gate.cpu().numpy(), blobs.cpu().numpy()
+            xh = [x.float().cpu().numpy() for x in xs[:4]]
+            tms, cores, kind, _ = cpu_reference_layer(gate_h, blobs_h, blob_bytes, xh, 20, 3)
+            sec = sum(tms) / len(tms)
+            line["cpu_baseline"] = {"value": T / sec, "unit": "tokens/s", "cores": cores, "kind": kind,
+                                    "sample": "20 full layer steps of 64 tokens on the same weights (reference CPU expert pool; oracle router/dispatch/combine)"}
+        except Exception as exc:   # the baseline is reported, never required
+            line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
+    print(json.dumps(line))
+
+
+def instrumented_pass(layers, xs, xr, stream, steps, L):
+    """Re-runs the steps with CUDA events between the C ABI calls; returns mean ms per stage and the gate/up launch's
+    algorithmic bytes (distinct routed experts touched x gate+up bytes + activations in + h out), averaged over steps."""
+    from basalt_b200 import capi
+    from basalt_b200.moe import _p, _stream, _x_kind
+    lib = capi.lib()
+    st = _stream(stream)
+    names = ["router", "plan", "experts_gate_up", "experts_down", "shared_expert", "combine"]
+    acc = {n: 0.0 for n in names}
+    gu_bytes = 0.0
+    for i in range(steps):
+        ly, x, xrr = layers[i % len(layers)], xs[i % len(xs)], xr[i % len(xs)]
+        a = ly.args
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
+        n = T * a.k
+        ev[0].record(stream)
+        capi.check("router", lib.bsx_router(_p(xrr), _p(ly.gate_w), None, T, a.n_expert, a.n_embd, a.k, a.gate, a.weight_scale, 1, 1, 0.0, None, 0,
+                                            _p(ly.logits), _p(ly.ids), _p(ly.w), st))
+        ev[1].record(stream)
+        capi.check("plan", lib.bsx_moe_plan(_p(ly.ids), T, a.k, a.n_expert, _p(ly.blob_table), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok), st))
+        ev[2].record(stream)
+        for phase in (1, 2):
+            lib.bsx_experts_set_phase(phase)
+            capi.check("experts", lib.bsx_experts_grouped(C.byref(ly.L), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok), min(n, a.n_expert), n,
+                                                           _p(x), _x_kind(x), _p(ly.scratch), _p(ly.rows), capi.OUT_F32, st))
+            ev[2 + phase].record(stream)
+        lib.bsx_experts_set_phase(0)
+        capi.check("shared", lib.bsx_experts_grouped(C.byref(ly.shared_L), _p(ly.s_ptr), _p(ly.s_start), _p(ly.s_one), _p(ly.s_iota), _p(ly.s_iota), 1, T, _p(x),
+                                                      _x_kind(x), _p(ly.s_scratch), _p(ly.s_out), capi.OUT_F32, st))
+        ev[5].record(stream)
+        capi.check("combine", lib.bsx_combine(_p(ly.rows), None, _p(ly.w), _p(ly.s_out), None, T, a.k, L.n_embd, _p(ly.y), st))
+        ev[6].record(stream)
+        stream.synchronize()
+        for j, nme in enumerate(names):
+            acc[nme] += ev[j].elapsed_time(ev[j + 1])
+        distinct = int(ly.n_groups.item())
+        gu_bytes += distinct * 2 * L.n_ff * L.gu_row + T * L.n_embd * 2 + n * L.n_ff * 4
+    return {k: v / steps for k, v in acc.items()}, gu_bytes / steps
+
+
+if __name__ == "__main__":
+    main()

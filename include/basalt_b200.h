@@ -88,6 +88,15 @@ BSX_API int32_t bsx_router(const float* x, const float* gate, const float* bias,
                    int32_t gate_kind, float weight_scale, int32_t n_group, int32_t topk_group, float prior,
                    const int32_t* const* held_tabs, int32_t n_held, float* logits, int32_t* ids, float* weights, void* stream);
 
+/* ---- a1/a2 with bf16 activation rows (x_kind BSX_X_F32 or BSX_X_BF16; no counterpart in the reference, whose router reads
+ * fp32 only: a bf16 row is widened exactly, then the same sums run, so the result equals bsx_router on the widened rows). */
+BSX_API int32_t bsx_router_logits_x(const void* x, int32_t x_kind, const float* gate, int32_t T, int32_t E, int32_t H, float* logits,
+                                    void* stream);
+BSX_API int32_t bsx_router_x(const void* x, int32_t x_kind, const float* gate, const float* bias, int32_t T, int32_t E, int32_t H,
+                             int32_t k, int32_t gate_kind, float weight_scale, int32_t n_group, int32_t topk_group, float prior,
+                             const int32_t* const* held_tabs, int32_t n_held, float* logits, int32_t* ids, float* weights,
+                             void* stream);
+
 /* ---- a5: opt-in lossy tail skip.  Replaces basalt::kernels::route_tail_skip (include/basalt/kernels/route_lossy.hpp:58-59,
  * src/kernels/cuda/route_tail_skip.cu:14-53).  n_entries <= 128; rank outside 1..k-1 leaves the window untouched.
  * counts (optional, 3 x uint64 on the device): entries, entries no table holds, entries dropped (added to). */
@@ -150,6 +159,10 @@ BSX_API int32_t bsx_experts_grouped(const bsx_expert_layout* layout, const unsig
                             const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
                             int64_t cap_entries, const void* x, int32_t x_kind, void* scratch, void* out, int32_t out_kind,
                             void* stream);
+
+/* The bench only: which launches bsx_experts_grouped makes (0 all, 1 gate/up + SwiGLU, 2 down), so each stage can be timed
+ * alone.  Mirrors native_expert_set_mode's phase (iq_kernels.hpp:113-115).  Process-wide; set it back to 0. */
+BSX_API void bsx_experts_set_phase(int32_t phase);
 
 /* ---- a13: weighted combine.  Replaces native_moe_combine[_multi] (include/basalt/models/qwen4exp/kernels/native_moe.hpp:5-15,
  * native_moe.cu:36-85), moe_combine (src/models/qwen4exp/prefill/kernels.cu:438-449,705-709) and weighted_sum_tokens
