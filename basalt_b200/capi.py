@@ -44,7 +44,7 @@ _SIGNATURES = {
     "bsx_expert_layout_init": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_float, C.c_float,
                                            C.c_float, C.POINTER(ExpertLayout)]),
     "bsx_expert_supported": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64]),
-    "bsx_expert_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),
+    "bsx_expert_scratch_bytes": (C.c_size_t, [C.POINTER(ExpertLayout), C.c_int64]),
     "bsx_quantize_q8_1_rows": (C.c_int32, [P, C.c_int64, C.c_int64, P, P]),
     "bsx_experts_grouped": (C.c_int32, [C.POINTER(ExpertLayout), P, P, P, P, P, C.c_int64, C.c_int64, P, C.c_int32, P, P,
                                         C.c_int32, P]),

@@ -147,9 +147,9 @@ dispatch_place_kernel(const int32_t* __restrict__ ids, int64_t n, int k, int E, 
 }
 
 // ---------------------------------------------------------------------------------------------- decode-window plan
-// One block.  Counts per expert in shared memory, one warp scans the experts into compacted groups, then the pairs are
-// placed in pair order: the block walks the pairs 32 at a time per warp, warps taking turns, so an expert's entries keep
-// the order of the pairs (the reference counts the earlier equal ids instead, ops.cu:331-339; the result is the same).
+// One block.  Counts per expert in shared memory, one warp scans the experts into compacted groups, then one warp
+// places the pairs in pair order, 32 at a time with __match_any_sync ranks, so an expert's entries keep the order of the
+// pairs (the reference counts the earlier equal ids instead, ops.cu:331-339; the result is the same).
 __global__ void __launch_bounds__(256)
 moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsigned long long* __restrict__ blobs,
                 unsigned long long* __restrict__ ptr, int32_t* __restrict__ start, int32_t* __restrict__ n_groups,
@@ -158,7 +158,7 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsi
     unsigned long long* blob = smb;                               // [E]
     int32_t* count = reinterpret_cast<int32_t*>(smb + E);         // [E]
     int32_t* next = count + E;                                    // [E]: the expert's next entry
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         blob[e] = blobs[e];
         count[e] = 0;
@@ -195,24 +195,23 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsi
         }
     }
     __syncthreads();
-    const unsigned lt = (1u << lane) - 1u;
-    for (int i0 = 0; i0 < n; i0 += blockDim.x) {
-        for (int w = 0; w < nw; ++w) {
-            if (warp == w) {
-                const int i = i0 + w * 32 + lane;
-                const int e = i < n ? ids[i] : -1;
-                const bool ok = (unsigned) e < (unsigned) E && blob[e] != 0ull;
-                const unsigned peers = __match_any_sync(kFull, ok ? e : -1 - lane);
-                int at = -1;
-                if (ok) at = next[e] + __popc(peers & lt);
-                __syncwarp();
-                if (ok && (__ffs(peers) - 1) == lane) next[e] += __popc(peers);
-                if (ok) {
-                    dst[at] = i;
-                    tok[at] = i / k;
-                }
+    // one warp walks the pairs in order, 32 at a time: no block barrier inside the walk
+    if (warp == 0) {
+        const unsigned lt = (1u << lane) - 1u;
+        for (int i0 = 0; i0 < n; i0 += 32) {
+            const int i = i0 + lane;
+            const int e = i < n ? ids[i] : -1;
+            const bool ok = (unsigned) e < (unsigned) E && blob[e] != 0ull;
+            const unsigned peers = __match_any_sync(kFull, ok ? e : -1 - lane);
+            int at = -1;
+            if (ok) at = next[e] + __popc(peers & lt);
+            __syncwarp();
+            if (ok && (__ffs(peers) - 1) == lane) next[e] += __popc(peers);
+            __syncwarp();
+            if (ok) {
+                dst[at] = i;
+                tok[at] = i / k;
             }
-            __syncthreads();
         }
     }
 }

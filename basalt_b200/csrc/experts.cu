@@ -155,10 +155,10 @@ extern "C" int32_t bsx_expert_layout_init(int32_t gu_type, int32_t d_type, int32
     return BSX_OK;
 }
 
-extern "C" size_t bsx_expert_scratch_bytes(int64_t cap_entries, int64_t n_ff) {
-    if (cap_entries < 0 || n_ff < 0) return 0;
-    const size_t f = (((size_t) cap_entries * (size_t) n_ff * sizeof(float)) + 255) & ~(size_t) 255;
-    return f + 4096;
+extern "C" size_t bsx_expert_scratch_bytes(const bsx_expert_layout* L, int64_t cap_entries) {
+    if (!L || cap_entries < 0 || L->n_ff <= 0 || L->n_embd <= 0) return 0;
+    const size_t f = (((size_t) cap_entries * (size_t) L->n_ff * sizeof(float)) + 255) & ~(size_t) 255;
+    return f + experts_mma_scratch_bytes(cap_entries, L->n_embd, L->n_ff) + 4096;
 }
 
 extern "C" int32_t bsx_quantize_q8_1_rows(const float* x, int64_t n_rows, int64_t n_cols, void* y, void* stream) {

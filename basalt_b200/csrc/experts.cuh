@@ -48,5 +48,6 @@ int experts_phase();
 int32_t experts_grouped_simple(const ExpertArgs& a, cudaStream_t st);
 // returns BSX_E_TYPE when the fast path does not cover the layout (the caller then runs the plain kernels)
 int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st);
+size_t experts_mma_scratch_bytes(int64_t cap_entries, int64_t n_embd, int64_t n_ff);
 
 }  // namespace bsx

@@ -4,11 +4,14 @@
 // Shape of the work (HBM-bound): every touched expert's gate, up and down rows are read exactly once per pass of up to 8
 // activation columns.  Each warp owns 16 weight rows (8 gate rows paired with the 8 matching up rows, or 16 down rows) and
 // streams them in 256-column chunks (144 bytes a row) through its own 4-stage cp.async ring, so no block-wide barrier sits
-// in the stream and ~110 KB a SM is in flight.  A row's E2M1 codes go to fp16 pairs with cvt.rn.f16x2.e2m1x2, are
-// multiplied by the block's UE4M3 scale as fp16 (the product has at most 5 significant bits: exact), and feed
-// mma.sync.m16n8k16 with fp32 accumulation.  The activation columns (up to 8 bf16 tokens, or 4 fp32 tokens split into
-// hi + lo fp16 terms, each column pre-scaled by a power of two so it fits fp16) sit in shared memory permuted into
-// B-fragment order.  Gate and up rows of one neuron land in the same thread's accumulators, so SwiGLU is fused.
+// in the stream and ~110 KB a SM is in flight.  A row's E2M1 codes go to fp16 pairs with cvt.rn.f16x2.e2m1x2 (one ALU-pipe
+// instruction per byte, the scarce resource here: the ALU pipe issues at half rate), are multiplied by the block's UE4M3
+// scale as fp16 (the product has at most 5 significant bits: exact; the scale comes from a 256-entry shared-memory table)
+// and feed mma.sync.m16n8k16 with fp32 accumulation.  Each of a row group's four threads owns one 16-value sub-block, so it
+// decodes one scale per row and block.  The activation columns (8 bf16 tokens, or 4 fp32 tokens split into hi + lo fp16
+// terms, each row pre-scaled by a power of two so it fits fp16) are prepared once per call by a small kernel into
+// B-fragment order and copied into shared memory by cp.async.  Gate and up rows of one neuron land in the same thread's
+// accumulators, so SwiGLU is fused; a second small kernel turns the SwiGLU output into the down product's fp16 image.
 //
 // Semantics: Basalt's native_expert_grouped (include/basalt/kernels/iq_kernels.hpp:77-92; kernels src/kernels/cuda/iq_kernels.cu:
 // 1605-1658 gate/up, :2512-2524 SwiGLU, :2140-2164 down), NVFP4 decoding per src/kernels/cpu/ggml/ggml_quants.c:1397-1422,
@@ -66,15 +69,24 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// The four UE4M3 scale bytes of a block -> fp16 pairs {d, d} for sub-blocks sa and sa + 2, each d = scale / 2^8:
-// (byte & 0x7F) << 7 puts E4M3's exponent and mantissa where fp16 keeps them (value 2^(e-15) (1 + m/8), subnormals
-// included); the scale itself is 2^(e-7) (1 + m/8) (ggml halves it only because its E2M1 table is doubled, and the cvt
-// above yields undoubled values), so the epilogue multiplies the sums by 2^8.  0x7F decodes to 0.
-__device__ __forceinline__ void scale_pairs(uint32_t dw, uint32_t sel_a, uint32_t sel_b, uint32_t& s0, uint32_t& s1) {
-    uint32_t m = dw & 0x7F7F7F7Fu;
-    m &= ~__vcmpeq4(m, 0x7F7F7F7Fu);
-    s0 = __byte_perm(m, 0u, sel_a) << 7;
-    s1 = __byte_perm(m, 0u, sel_b) << 7;
+// UE4M3 scale byte -> fp16 pair {d, d} with d = scale / 2^8: (byte & 0x7F) << 7 puts E4M3's exponent and mantissa where
+// fp16 keeps them (value 2^(e-15) (1 + m/8), subnormals included) while the scale itself is 2^(e-7) (1 + m/8) (ggml halves
+// it only because its E2M1 table is doubled; the cvt above yields undoubled values), so the epilogue multiplies the sums
+// by 2^8.  0x7F decodes to 0 and bit 7 is ignored (src/kernels/cpu/ggml/ggml_quants.c:1397-1406).
+__device__ __forceinline__ uint32_t scale_pair_bits(uint32_t byte) {
+    const uint32_t b = byte & 0x7Fu;
+    const uint32_t v = b == 0x7Fu ? 0u : b << 7;
+    return v | (v << 16);
+}
+
+// Where column c of an activation row sits in its fp16 image, which is laid out so that a thread's B fragments are two
+// 16-byte pieces per 64 columns: piece (gran, h, t) holds, for sub-block t of granule gran, the values the thread with
+// id-in-group t needs for MMA steps 2h and 2h + 1.  Step s takes code bytes 2s and 2s + 1 of the sub-block's 8 bytes; byte b
+// holds values b (low nibble -> k slot 2t) and b + 8 (high nibble -> k slot 2t + 1), bytes 2s + 1 go to slots 2t + 8, 2t + 9.
+__device__ __forceinline__ int image_index(int c) {
+    const int gran = c >> 6, t = (c >> 4) & 3, jj = c & 15, b = jj & 7, half = jj >> 3;
+    const int step = b >> 1, reg = b & 1;
+    return (((gran * 2 + (step >> 1)) * 4 + t) << 3) + 4 * (step & 1) + 2 * reg + half;
 }
 
 __device__ __forceinline__ float load_x(const void* x, int kind, int64_t row, int64_t K, int c) {
@@ -84,27 +96,78 @@ __device__ __forceinline__ float load_x(const void* x, int kind, int64_t row, in
     return __half2float(*reinterpret_cast<const __half*>(b)) * (float) (int8_t) b[4 + (c & 31)];
 }
 
-// MODE_GU:  rows = 8 gate rows r0.. paired with up rows r0..; x = the call's activations through ent_tok; writes h.
-// MODE_DOWN: rows = 16 down rows; x = h rows of the entries; writes out rows through ent_dst.
-// TERMS = 1: 8 bf16 columns a pass; TERMS = 2: 4 columns a pass, each as hi + lo fp16 terms.
+// One block per entry: the entry's activation row -> fp16 image(s) in fragment order plus the inverse of the power of two it
+// was scaled by (so that its largest magnitude lands in [2^13, 2^14), inside fp16 whatever the row's range).
+// FROM_H = false: row ent_tok[e] of x (kind x_kind, width n_embd); true: row e of the SwiGLU output h (fp32, width n_ff).
+template <bool FROM_H, int TERMS>
+__global__ void __launch_bounds__(256) prep_image_kernel(ExpertArgs a, __half* __restrict__ img, float* __restrict__ inv) {
+    __shared__ float s_red[8];
+    __shared__ float s_scale;
+    const int e = blockIdx.x;
+    const int ng = min(*a.n_groups, (int) a.cap_groups);
+    const int total = min(a.grp_start[ng], (int) a.cap_entries);
+    if (e >= total) return;
+    const int64_t K = FROM_H ? a.L.n_ff : a.L.n_embd;
+    const int64_t row = FROM_H ? (int64_t) e : (int64_t) a.ent_tok[e];
+    const void* src = FROM_H ? (const void*) a.h : a.x;
+    const int kind = FROM_H ? BSX_X_F32 : a.x_kind;
+    float amax = 0.f;
+    for (int c = threadIdx.x; c < K; c += 256) amax = fmaxf(amax, fabsf(load_x(src, kind, row, K, c)));
+    amax = warp_max_xor(amax);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m = 0.f;
+        for (int i = 0; i < 8; ++i) m = fmaxf(m, s_red[i]);
+        int ex = 0;
+        float s = 1.f, iv = 1.f;
+        if (m > 0.f && m <= 3.0e38f) {
+            frexpf(m, &ex);                          // m = f 2^ex, f in [0.5, 1)
+            ex = max(-100, min(100, 14 - ex));
+            s = ldexpf(1.f, ex);
+            iv = ldexpf(1.f, -ex);
+        }
+        s_scale = s;
+        inv[e] = iv;
+    }
+    __syncthreads();
+    const float s = s_scale;
+    __half* out = img + (size_t) e * K * TERMS;
+    for (int c = threadIdx.x; c < K; c += 256) {
+        const float v = load_x(src, kind, row, K, c) * s;
+        const __half hi = __float2half_rn(v);
+        const int at = image_index(c);
+        out[at] = hi;
+        if (TERMS == 2) out[K + at] = __float2half_rn(v - __half2float(hi));
+    }
+}
+
+// MODE_GU:  rows = 8 gate rows r0.. paired with up rows r0..; columns = the entries' x images; writes h (fp32).
+// MODE_DOWN: rows = 16 down rows; columns = the entries' h images; writes out rows through ent_dst.
+// TERMS = 1: 8 entries a pass; TERMS = 2: 4 entries a pass, each as hi + lo fp16 columns.
 template <int MODE, int TERMS>
-__global__ void __launch_bounds__(kThreads, 2) nvfp4_mma_kernel(ExpertArgs a) {
+__global__ void __launch_bounds__(kThreads, 2)
+nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __restrict__ inv) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int64_t K = MODE == MODE_GU ? a.L.n_embd : a.L.n_ff;
     const int n_gran = (int) (K >> 6);                       // 64-column granules
     __half* xs = reinterpret_cast<__half*>(smem);            // [n_gran][2][8 cols][4][8]
-    float* col_inv = reinterpret_cast<float*>(smem + (size_t) K * kCols * 2);   // [8] inverse column scales, then [8] scales
-    uint8_t* wbase = smem + (size_t) K * kCols * 2 + 64;
+    uint32_t* lut = reinterpret_cast<uint32_t*>(smem + (size_t) K * kCols * 2);   // [256] scale pairs
+    uint8_t* wbase = smem + (size_t) K * kCols * 2 + 1024;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     uint8_t* wring = wbase + (size_t) warp * kStages * kStageBytes;
     const uint32_t wring_s = (uint32_t) __cvta_generic_to_shared(wring);
+    const uint32_t xs_s = (uint32_t) __cvta_generic_to_shared(xs);
     constexpr int NTOK = kCols / TERMS;
+
+    lut[threadIdx.x] = scale_pair_bits(threadIdx.x);   // 256 threads, 256 entries; the first barrier below publishes it
 
     const int64_t n_rows = MODE == MODE_GU ? a.L.n_ff : a.L.n_embd;      // neurons (pairs) or down rows
     const int64_t r0 = (int64_t) blockIdx.x * (MODE == MODE_GU ? kWarps * 8 : kWarps * 16) + warp * (MODE == MODE_GU ? 8 : 16);
     const bool live = r0 < n_rows;
     const int n_chunks = n_gran >> 2;
+    const int pieces_per_col = (int) (K >> 3);               // 16-byte pieces of one image
 
     // this lane's copy duty inside a stage: pieces lane, lane + 32, ... (< 144); row = piece / 9
     int cp_row[5], cp_off[5];
@@ -114,8 +177,7 @@ __global__ void __launch_bounds__(kThreads, 2) nvfp4_mma_kernel(ExpertArgs a) {
         cp_row[j] = p / 9;
         cp_off[j] = (p % 9) * 16;
     }
-    const uint32_t sel_a = (uint32_t) (t >> 1) | (4u << 4) | ((uint32_t) (t >> 1) << 8) | (4u << 12);
-    const uint32_t sel_b = sel_a + 0x0202u;   // sub-block + 2
+    const uint32_t sel = (uint32_t) t | 0x4440u;   // byte t of the scale word, zero-extended
 
     const int ng = min(*a.n_groups, (int) a.cap_groups);
     for (int grp = blockIdx.y; grp < ng; grp += gridDim.y) {
@@ -145,50 +207,28 @@ __global__ void __launch_bounds__(kThreads, 2) nvfp4_mma_kernel(ExpertArgs a) {
             cp_async_commit();
         };
 
-        for (int eb = e0; eb < e1; eb += NTOK) {
+        // passes (batches of NTOK entries) of one group are dealt round-robin to the blocks along grid z
+        for (int eb = e0 + (int) blockIdx.z * NTOK; eb < e1; eb += NTOK * (int) gridDim.z) {
             const int ntok = min(NTOK, e1 - eb);
-            // the weight stream does not depend on x: start it before the activations are staged
+            const int ncol = ntok * TERMS;
+            __syncthreads();   // the previous pass has finished reading xs
+            // the activation columns: image piece q of column c goes to piece ((q >> 2) * 8 + c) * 4 + (q & 3) of xs
+            for (int i = threadIdx.x; i < ncol * pieces_per_col; i += kThreads) {
+                const int c = i / pieces_per_col, q = i - c * pieces_per_col;
+                const int ent = eb + c / TERMS, term = c % TERMS;
+                const __half* sp = img + ((size_t) ent * TERMS + term) * K + (size_t) q * 8;
+                cp_async16(xs_s + (uint32_t) ((((q >> 2) * kCols + c) * 4 + (q & 3)) * 16), sp);
+            }
+            cp_async_commit();
+            // the weight stream
 #pragma unroll
             for (int c = 0; c < kStages - 1; ++c) issue(c);
-
-            __syncthreads();   // the previous pass has finished reading xs / col_inv
-            if (warp < ntok) {
-                const int64_t row = MODE == MODE_GU ? (int64_t) a.ent_tok[eb + warp] : (int64_t) (eb + warp);
-                const void* xp = MODE == MODE_GU ? a.x : (const void*) a.h;
-                const int kind = MODE == MODE_GU ? a.x_kind : BSX_X_F32;
-                float amax = 0.f;
-                for (int c = lane; c < K; c += 32) amax = fmaxf(amax, fabsf(load_x(xp, kind, row, K, c)));
-                amax = warp_max_xor(amax);
-                if (lane == 0) {
-                    int e = 0;
-                    float s = 1.f, inv = 1.f;
-                    if (amax > 0.f && amax <= 3.0e38f) {
-                        frexpf(amax, &e);                     // amax = m 2^e, m in [0.5, 1)
-                        e = max(-100, min(100, 14 - e));      // amax 2^(14-e) lies in [2^13, 2^14): inside fp16
-                        s = ldexpf(1.f, e);
-                        inv = ldexpf(1.f, -e);
-                    }
-                    col_inv[warp] = inv;
-                    col_inv[8 + warp] = s;
-                }
-            }
-            __syncthreads();
-            for (int idx = threadIdx.x; idx < ntok * (int) K; idx += kThreads) {
-                const int j = idx / (int) K, c = idx - j * (int) K;
-                const int64_t row = MODE == MODE_GU ? (int64_t) a.ent_tok[eb + j] : (int64_t) (eb + j);
-                const float v = load_x(MODE == MODE_GU ? a.x : (const void*) a.h, MODE == MODE_GU ? a.x_kind : BSX_X_F32, row, K, c) * col_inv[8 + j];
-                const int gran = c >> 6, jj = c & 15, sb = (c >> 4) & 3;
-                const int hh = sb >> 1, tt = 2 * (sb & 1) + ((jj & 7) >> 2), p = 2 * (jj & 3) + (jj >> 3);
-                const __half hi = __float2half_rn(v);
-                const size_t base = ((size_t) (gran * 2 + hh) * kCols) * 32 + (size_t) tt * 8 + p;
-                xs[base + (size_t) (j * TERMS) * 32] = hi;
-                if (TERMS == 2) xs[base + (size_t) (j * TERMS + 1) * 32] = __float2half_rn(v - __half2float(hi));
-            }
+            cp_async_wait<kStages - 1>();   // the activation group (the oldest) has landed
             __syncthreads();
 
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             if (live) {
-                const bool col_live = g < ntok * TERMS;
+                const bool col_live = g < ncol;
                 for (int chunk = 0; chunk < n_chunks; ++chunk) {
                     issue(chunk + kStages - 1);
                     cp_async_wait<kStages - 1>();
@@ -205,19 +245,19 @@ __global__ void __launch_bounds__(kThreads, 2) nvfp4_mma_kernel(ExpertArgs a) {
                             b0 = bp[0];
                             b1 = bp[kCols * 4];   // the second half-granule: + 8 columns * 32 halves
                         }
-                        uint32_t sa0, sa1, sb0, sb1, qa0[4], qa1[4], qb0[4], qb1[4];
-                        scale_pairs(ra[9 * blk], sel_a, sel_b, sa0, sa1);
-                        scale_pairs(rb[9 * blk], sel_a, sel_b, sb0, sb1);
-                        cvt_e2m1x8(ra[9 * blk + 1 + t], qa0);
-                        cvt_e2m1x8(ra[9 * blk + 5 + t], qa1);
-                        cvt_e2m1x8(rb[9 * blk + 1 + t], qb0);
-                        cvt_e2m1x8(rb[9 * blk + 5 + t], qb1);
+                        const uint32_t sa = lut[__byte_perm(ra[9 * blk], 0u, sel)];
+                        const uint32_t sb = lut[__byte_perm(rb[9 * blk], 0u, sel)];
+                        uint32_t qa0[4], qa1[4], qb0[4], qb1[4];
+                        cvt_e2m1x8(ra[9 * blk + 1 + 2 * t], qa0);
+                        cvt_e2m1x8(ra[9 * blk + 2 + 2 * t], qa1);
+                        cvt_e2m1x8(rb[9 * blk + 1 + 2 * t], qb0);
+                        cvt_e2m1x8(rb[9 * blk + 2 + 2 * t], qb1);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            qa0[i] = hmul2_bits(qa0[i], sa0);
-                            qa1[i] = hmul2_bits(qa1[i], sa1);
-                            qb0[i] = hmul2_bits(qb0[i], sb0);
-                            qb1[i] = hmul2_bits(qb1[i], sb1);
+                            qa0[i] = hmul2_bits(qa0[i], sa);
+                            qa1[i] = hmul2_bits(qa1[i], sa);
+                            qb0[i] = hmul2_bits(qb0[i], sb);
+                            qb1[i] = hmul2_bits(qb1[i], sb);
                         }
                         mma_f16(acc, qa0[0], qb0[0], qa0[1], qb0[1], b0.x, b0.y);
                         mma_f16(acc, qa0[2], qb0[2], qa0[3], qb0[3], b0.z, b0.w);
@@ -226,11 +266,9 @@ __global__ void __launch_bounds__(kThreads, 2) nvfp4_mma_kernel(ExpertArgs a) {
                     }
                     __syncwarp();   // every lane is done with this stage before a later issue overwrites it
                 }
-            } else {
-                // keep the commit-group count in step (nothing was copied)
-                cp_async_wait<0>();
             }
-            // epilogue: undo the column scale and the 2^-8 of the fp16 block scales, apply the tail scales
+            cp_async_wait<0>();
+            // epilogue: undo the row scale and the 2^-8 of the fp16 block scales, apply the tail scales
             if (live) {
                 if (MODE == MODE_GU) {
                     const float sg = tail[0] * 256.f, su = tail[1] * 256.f;
@@ -239,12 +277,12 @@ __global__ void __launch_bounds__(kThreads, 2) nvfp4_mma_kernel(ExpertArgs a) {
                         for (int q = 0; q < 2; ++q) {
                             const int j = 2 * t + q;
                             if (j < ntok) {
-                                const float f = col_inv[j];
+                                const float f = inv[eb + j];
                                 a.h[(size_t) (eb + j) * a.L.n_ff + r0 + g] = swiglu(acc[q] * f * sg, acc[2 + q] * f * su, a.L);
                             }
                         }
                     } else if (t < ntok) {
-                        const float f = col_inv[t];
+                        const float f = inv[eb + t];
                         a.h[(size_t) (eb + t) * a.L.n_ff + r0 + g] = swiglu((acc[0] + acc[1]) * f * sg, (acc[2] + acc[3]) * f * su, a.L);
                     }
                 } else {
@@ -254,14 +292,14 @@ __global__ void __launch_bounds__(kThreads, 2) nvfp4_mma_kernel(ExpertArgs a) {
                         for (int q = 0; q < 2; ++q) {
                             const int j = 2 * t + q;
                             if (j < ntok) {
-                                const float f = col_inv[j] * sd;
+                                const float f = inv[eb + j] * sd;
                                 const int64_t o = (int64_t) a.ent_dst[eb + j] * a.L.n_embd + r0 + g;
                                 store_out(a.out, a.out_kind, o, acc[q] * f);
                                 store_out(a.out, a.out_kind, o + 8, acc[2 + q] * f);
                             }
                         }
                     } else if (t < ntok) {
-                        const float f = col_inv[t] * sd;
+                        const float f = inv[eb + t] * sd;
                         const int64_t o = (int64_t) a.ent_dst[eb + t] * a.L.n_embd + r0 + g;
                         store_out(a.out, a.out_kind, o, (acc[0] + acc[1]) * f);
                         store_out(a.out, a.out_kind, o + 8, (acc[2] + acc[3]) * f);
@@ -273,10 +311,11 @@ __global__ void __launch_bounds__(kThreads, 2) nvfp4_mma_kernel(ExpertArgs a) {
     cp_async_wait<0>();
 }
 
-size_t smem_bytes(int64_t K) { return (size_t) K * kCols * 2 + 64 + (size_t) kWarps * kStages * kStageBytes; }
+size_t smem_bytes(int64_t K) { return (size_t) K * kCols * 2 + 1024 + (size_t) kWarps * kStages * kStageBytes; }
+size_t align256(size_t v) { return (v + 255) & ~(size_t) 255; }
 
 template <int MODE, int TERMS>
-int32_t launch(const ExpertArgs& a, cudaStream_t st) {
+int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, cudaStream_t st) {
     const int64_t K = MODE == MODE_GU ? a.L.n_embd : a.L.n_ff;
     const size_t smem = smem_bytes(K);
     static bool configured[64] = {};
@@ -290,11 +329,23 @@ int32_t launch(const ExpertArgs& a, cudaStream_t st) {
     const int64_t rows = MODE == MODE_GU ? a.L.n_ff : a.L.n_embd;
     const int per_block = MODE == MODE_GU ? kWarps * 8 : kWarps * 16;
     const unsigned gy = (unsigned) (a.cap_groups < 1 ? 1 : a.cap_groups > 1024 ? 1024 : a.cap_groups);
-    nvfp4_mma_kernel<MODE, TERMS><<<dim3((unsigned) ((rows + per_block - 1) / per_block), gy), kThreads, smem, st>>>(a);
+    // blocks along z share a group's passes: about four passes' worth of blocks per possible group, never more than the
+    // passes the call can have
+    constexpr int NTOK = kCols / TERMS;
+    const int64_t max_passes = (a.cap_entries + NTOK - 1) / NTOK;
+    int64_t gz = (4 * a.cap_entries + (int64_t) NTOK * gy - 1) / ((int64_t) NTOK * gy);
+    gz = gz < 1 ? 1 : gz > 16 ? 16 : gz;
+    gz = gz > max_passes ? max_passes : gz;
+    nvfp4_mma_kernel<MODE, TERMS><<<dim3((unsigned) ((rows + per_block - 1) / per_block), gy, (unsigned) gz), kThreads, smem, st>>>(a, img, inv);
     return launch_status();
 }
 
 }  // namespace
+
+// scratch beyond the SwiGLU buffer: the x images (up to two fp16 terms), the h images (two terms), the inverse row scales
+size_t experts_mma_scratch_bytes(int64_t cap_entries, int64_t n_embd, int64_t n_ff) {
+    return align256((size_t) cap_entries * n_embd * 4) + align256((size_t) cap_entries * n_ff * 4) + 2 * align256((size_t) cap_entries * 4);
+}
 
 int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st) {
     const bsx_expert_layout& L = a.L;
@@ -302,11 +353,29 @@ int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st) {
     // 16-byte row chunks: both K dimensions must be whole 256-column chunks; the activation image must fit shared memory
     if (L.n_embd % 256 || L.n_ff % 256 || L.n_ff % 8 || L.n_embd % 16) return BSX_E_TYPE;
     if (smem_bytes(L.n_embd) > 200 * 1024 || smem_bytes(L.n_ff) > 200 * 1024) return BSX_E_TYPE;
+    // scratch: [h fp32][x images][h images][x inverse scales][h inverse scales]
+    uint8_t* p = reinterpret_cast<uint8_t*>(a.h) + align256((size_t) a.cap_entries * L.n_ff * 4);
+    __half* ximg = reinterpret_cast<__half*>(p);
+    p += align256((size_t) a.cap_entries * L.n_embd * 4);
+    __half* himg = reinterpret_cast<__half*>(p);
+    p += align256((size_t) a.cap_entries * L.n_ff * 4);
+    float* xinv = reinterpret_cast<float*>(p);
+    float* hinv = xinv + align256((size_t) a.cap_entries * 4) / 4;
     const int phase = experts_phase();
+    const unsigned nb = (unsigned) a.cap_entries;
     int32_t rc = BSX_OK;
-    if (phase != 2) rc = a.x_kind == BSX_X_BF16 ? launch<MODE_GU, 1>(a, st) : launch<MODE_GU, 2>(a, st);
+    if (phase != 2) {
+        if (a.x_kind == BSX_X_BF16) {
+            prep_image_kernel<false, 1><<<nb, 256, 0, st>>>(a, ximg, xinv);
+            rc = launch<MODE_GU, 1>(a, ximg, xinv, st);
+        } else {
+            prep_image_kernel<false, 2><<<nb, 256, 0, st>>>(a, ximg, xinv);
+            rc = launch<MODE_GU, 2>(a, ximg, xinv, st);
+        }
+    }
     if (rc != BSX_OK || phase == 1) return rc;
-    return launch<MODE_DOWN, 2>(a, st);
+    prep_image_kernel<true, 2><<<nb, 256, 0, st>>>(a, himg, hinv);
+    return launch<MODE_DOWN, 2>(a, himg, hinv, st);
 }
 
 }  // namespace bsx

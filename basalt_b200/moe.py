@@ -146,8 +146,10 @@ def native_expert_supported(gu_type, d_type, n_embd, n_ff, up_type=-1) -> bool:
     return bool(capi.lib().bsx_expert_supported(gu_type, d_type, up_type, n_embd, n_ff))
 
 
-def native_expert_scratch_bytes(cap_entries: int, n_ff: int) -> int:
-    return int(capi.lib().bsx_expert_scratch_bytes(cap_entries, n_ff))
+def native_expert_scratch_bytes(L: ExpertLayout, cap_entries: int) -> int:
+    """basalt::kernels::native_expert_scratch_bytes (iq_kernels.hpp:75), from the layout (the tensor-core path keeps fp16
+    images of the activations in scratch, so the width n_embd matters too)."""
+    return int(capi.lib().bsx_expert_scratch_bytes(C.byref(L), cap_entries))
 
 
 def quantize_q8_1_rows(x, stream=None):
@@ -215,7 +217,7 @@ class MoELayer:
         self.dst = torch.zeros(n, dtype=i32, device=dev)
         self.tok = torch.zeros(n, dtype=i32, device=dev)
         self.rows = torch.empty((n, layout.n_embd), dtype=f32, device=dev)
-        self.scratch = torch.empty(native_expert_scratch_bytes(n, layout.n_ff), dtype=torch.uint8, device=dev)
+        self.scratch = torch.empty(native_expert_scratch_bytes(layout, n), dtype=torch.uint8, device=dev)
         self.y = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
         if shared_blob is not None:
             self.s_ptr = torch.tensor([shared_blob.data_ptr()], dtype=torch.int64, device=dev)
@@ -223,7 +225,7 @@ class MoELayer:
             self.s_one = torch.ones(1, dtype=i32, device=dev)
             self.s_start = torch.zeros(3, dtype=i32, device=dev)
             self.s_out = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
-            self.s_scratch = torch.empty(native_expert_scratch_bytes(max_tokens, self.shared_L.n_ff), dtype=torch.uint8, device=dev)
+            self.s_scratch = torch.empty(native_expert_scratch_bytes(self.shared_L, max_tokens), dtype=torch.uint8, device=dev)
             self._s_T = -1
 
     def forward(self, x: torch.Tensor, x_router: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:

@@ -179,6 +179,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--copies", type=int, default=LAYER_COPIES, help="layer copies the steps cycle through (1 for a small profiler capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -206,7 +207,7 @@ def main():
     assert L.bytes == blob_bytes
     rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
     layers = []
-    for c in range(LAYER_COPIES):
+    for c in range(args.copies):
         b = blobs if c == 0 else blobs.clone()
         layers.append(moe.MoELayer(gate if c == 0 else gate.clone(), None, b[:E], L, rargs, shared_blob=b[E], max_tokens=T))
     n_batches = 8
@@ -216,7 +217,7 @@ def main():
     stream = torch.cuda.Stream(device=dev)
 
     def step(i, x=None):
-        return layers[i % LAYER_COPIES].forward(xs[i % n_batches] if x is None else x, xr[i % n_batches] if x is None else None, stream)
+        return layers[i % args.copies].forward(xs[i % n_batches] if x is None else x, xr[i % n_batches] if x is None else None, stream)
 
     def barrier():
         if world > 1:
@@ -271,7 +272,7 @@ def main():
         "metric": "MoE-layer tokens/s (decode)", "value": T * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp16 x NVFP4 tensor-core products, fp32 accumulation", "data": "synthetic",
-        "config": dict(CFG, l2_policy=f"weights cycle through {LAYER_COPIES} layer copies (3.6 GB) and each step touches ~650 MB: larger than L2",
+        "config": dict(CFG, l2_policy=f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB) and each step touches ~650 MB: larger than L2",
                        parallelism="single GPU" if world == 1 else f"ep{world}"),
         "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
         "gpu_launches": 8 * args.steps,

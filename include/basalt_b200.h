@@ -140,7 +140,9 @@ typedef struct bsx_expert_layout {
 BSX_API int32_t bsx_expert_layout_init(int32_t gu_type, int32_t d_type, int32_t up_type, int64_t n_embd, int64_t n_ff,
                                float swiglu_limit, float gate_softcap, float up_softcap, bsx_expert_layout* layout);
 BSX_API int32_t bsx_expert_supported(int32_t gu_type, int32_t d_type, int32_t up_type, int64_t n_embd, int64_t n_ff);
-BSX_API size_t bsx_expert_scratch_bytes(int64_t cap_entries, int64_t n_ff);
+/* scratch for bsx_experts_grouped with up to cap_entries entries: the SwiGLU buffer plus the fp16 activation images of the
+ * tensor-core path (the reference's helper takes (cap_entries, n_ff) only; this one needs n_embd as well, hence the layout) */
+BSX_API size_t bsx_expert_scratch_bytes(const bsx_expert_layout* layout, int64_t cap_entries);
 
 /* ---- a7: q8_1 activation rows.  Replaces basalt::kernels::quantize_q8_1_rows (iq_kernels.hpp:23, iq_kernels.cu:2471-2503):
  * per 32 values fp16 d = amax / 127, fp16 sum, 32 int8 codes.  n_cols % 32 == 0.  Bit-identical to the reference. */
@@ -154,7 +156,7 @@ BSX_API int32_t bsx_quantize_q8_1_rows(const float* x, int64_t n_rows, int64_t n
  * reference's activation blocks, decoded as d * q).  Unlike the reference, activations and the SwiGLU output are NOT
  * re-quantised to int8: products accumulate in fp32 on exactly decoded weights, so results sit within ~1e-5 relative
  * of the dequantised fp32 reference instead of the reference kernels' ~1e-2.
- * scratch: bsx_expert_scratch_bytes(cap_entries, n_ff).  A shared expert is one group holding every token. */
+ * scratch: bsx_expert_scratch_bytes(layout, cap_entries).  A shared expert is one group holding every token. */
 BSX_API int32_t bsx_experts_grouped(const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
                             const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
                             int64_t cap_entries, const void* x, int32_t x_kind, void* scratch, void* out, int32_t out_kind,

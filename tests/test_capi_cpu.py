@@ -62,6 +62,8 @@ def test_argument_errors(lib):
     assert lib.bsx_route_tail_skip(None, None, None, 0, 200, 4, 1, 8, None, None) == capi.OK   # out of range: a no-op
     assert lib.bsx_row_bytes(40, 2048) == 1152 and lib.bsx_row_bytes(14, 512) == 420 and lib.bsx_row_bytes(29, 100) == 0
     assert lib.bsx_dispatch_scratch_bytes(163840, 512) >= 163840 // 256 * 512 * 4
+    assert lib.bsx_expert_layout_init(40, 40, -1, 2048, 512, 0.0, 0.0, 0.0, C.byref(L)) == 0
+    assert lib.bsx_expert_scratch_bytes(C.byref(L), 640) >= 640 * 512 * 4 * 2 + 640 * 2048 * 4
 
 
 def test_nvfp4_packer_matches_oracle():

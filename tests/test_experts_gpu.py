@@ -36,7 +36,7 @@ def run_grouped(L, blobs_dev, group_experts, group_tokens, x_dev, n_out_rows, ou
     dst = dev(np.arange(max(n, 1), dtype=np.int32))
     ng = dev(np.array([len(group_experts)], np.int32))
     out = torch.full((max(n_out_rows, 1), L.n_embd), float("nan"), dtype=out_dtype, device="cuda")
-    scratch = torch.empty(moe.native_expert_scratch_bytes(max(n, 1), L.n_ff), dtype=torch.uint8, device="cuda")
+    scratch = torch.empty(moe.native_expert_scratch_bytes(L, max(n, 1)), dtype=torch.uint8, device="cuda")
     moe.native_expert_grouped(L, ptr, start, ng, dst, tok, cap_groups or len(group_experts), n, x_dev, scratch, out)
     torch.cuda.synchronize()
     return out
@@ -158,7 +158,7 @@ def test_reference_grouped_kernel_agrees(lib, cuda, gt, dt):
     """the reference's own CUDA kernel on the same blobs: int8 activations cost it ~1e-2, its own bar is rel L1 < 3e-2
     (tests/kernels/native_expert_parity.cpp:372-373); both implementations must describe the same expert."""
     rng = np.random.default_rng(gt)
-    H, I, E, T = 2560, 640, 3, 6
+    H, I, E, T = 2560, 512, 3, 6
     Lo, blobs = make_expert_blobs(rng, E, gt, dt, H, I)
     L = moe.native_expert_layout(gt, dt, H, I)
     x = rng.standard_normal((T, H)).astype(np.float32)
@@ -202,7 +202,8 @@ def test_combine_bit_exact(lib, cuda, T, k, H):
     if REFG is not None and k <= 15:
         out = torch.zeros((T, H), dtype=torch.float32, device="cuda")
         P = lambda t: C.c_void_p(t.data_ptr())
-        assert REFG.refg_combine_multi(P(dev(rows)), P(dev(w)), P(dev(shared)), P(out), C.c_int64(H), C.c_int64(k), T) == 0
+        drows, dw, dshared = dev(rows), dev(w), dev(shared)
+        assert REFG.refg_combine_multi(P(drows), P(dw), P(dshared), P(out), C.c_int64(H), C.c_int64(k), T) == 0
         mine = moe.moe_combine(dev(rows), None, dev(w), dev(shared))
         assert torch.equal(mine.view(torch.int32), out.view(torch.int32))
 

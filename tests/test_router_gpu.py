@@ -73,7 +73,8 @@ def test_select_vs_oracle_and_reference_kernel(lib, cuda, kind, E, k):
     if REFG is not None:
         rid = torch.zeros((T, k), dtype=torch.int32, device="cuda")
         rw = torch.zeros((T, k), dtype=torch.float32, device="cuda")
-        rc = REFG.refg_router_select(C.c_void_p(dev(lg).data_ptr()), C.c_void_p(dev(bias).data_ptr()), T, E, k, C.c_float(2.5), kind,
+        dlg, dbias = dev(lg), dev(bias)    # keep the device copies alive until the reference kernel has run
+        rc = REFG.refg_router_select(C.c_void_p(dlg.data_ptr()), C.c_void_p(dbias.data_ptr()), T, E, k, C.c_float(2.5), kind,
                                      C.c_float(0.0), None, C.c_void_p(rid.data_ptr()), C.c_void_p(rw.data_ptr()))
         assert rc == 0
         assert np.array_equal(ids, rid.cpu().numpy())
@@ -179,12 +180,13 @@ def test_softmax_routers(lib, cuda, E, k):
         assert sorted(ids[4][:10].tolist()) == list(range(10, 20)) if k >= 10 else True
     if REFG is not None:
         rid = torch.zeros((T, k), dtype=torch.int32, device="cuda"); rw = torch.zeros((T, k), dtype=torch.float32, device="cuda")
-        assert REFG.refg_router_top10(C.c_void_p(dev(lg).data_ptr()), T, E, k, C.c_void_p(rid.data_ptr()), C.c_void_p(rw.data_ptr())) == 0
+        dlg = dev(lg)
+        assert REFG.refg_router_top10(C.c_void_p(dlg.data_ptr()), T, E, k, C.c_void_p(rid.data_ptr()), C.c_void_p(rw.data_ptr())) == 0
         ids, w = outs[capi.GATE_SOFTMAX_F64]
         assert np.array_equal(ids, rid.cpu().numpy())
         assert np.array_equal(bits(w), bits(rw.cpu().numpy()))
         if E == 512 and k == 10:
-            assert REFG.refg_native_router_top10(C.c_void_p(dev(lg).data_ptr()), T, C.c_void_p(rid.data_ptr()), C.c_void_p(rw.data_ptr())) == 0
+            assert REFG.refg_native_router_top10(C.c_void_p(dlg.data_ptr()), T, C.c_void_p(rid.data_ptr()), C.c_void_p(rw.data_ptr())) == 0
             ids, w = outs[capi.GATE_SOFTMAX_FAST]
             assert np.array_equal(ids, rid.cpu().numpy())
             assert np.array_equal(bits(w), bits(rw.cpu().numpy()))
