@@ -152,20 +152,22 @@ dispatch_place_kernel(const int32_t* __restrict__ ids, int64_t n, int k, int E, 
 // pairs (the reference counts the earlier equal ids instead, ops.cu:331-339; the result is the same).
 __global__ void __launch_bounds__(256)
 moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsigned long long* __restrict__ blobs,
-                unsigned long long* __restrict__ ptr, int32_t* __restrict__ start, int32_t* __restrict__ n_groups,
-                int32_t* __restrict__ dst, int32_t* __restrict__ tok) {
+                unsigned long long shared_blob, int n_tok, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
+                int32_t* __restrict__ n_groups, int32_t* __restrict__ dst, int32_t* __restrict__ tok) {
     extern __shared__ unsigned long long smb[];
     unsigned long long* blob = smb;                               // [E]
     int32_t* count = reinterpret_cast<int32_t*>(smb + E);         // [E]
     int32_t* next = count + E;                                    // [E]: the expert's next entry
+    int32_t* sid = next + E;                                      // [n]: the ids, read once from global memory
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         blob[e] = blobs[e];
         count[e] = 0;
     }
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = ids[i];
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const int e = ids[i];
+        const int e = sid[i];
         if ((unsigned) e < (unsigned) E && blob[e]) atomicAdd(&count[e], 1);
     }
     __syncthreads();
@@ -188,6 +190,19 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsi
             at += __shfl_sync(kFull, s, 31);
             g += __shfl_sync(kFull, used, 31);
         }
+        // the shared expert: one more group holding every token, its rows after the routed pairs' rows
+        if (shared_blob != 0ull && n_tok > 0) {
+            if (lane == 0) {
+                ptr[g] = shared_blob;
+                start[g] = at;
+            }
+            for (int t = lane; t < n_tok; t += 32) {
+                dst[at + t] = n + t;
+                tok[at + t] = t;
+            }
+            at += n_tok;
+            ++g;
+        }
         if (lane == 0) {
             start[g] = at;
             start[g + 1] = at;
@@ -200,7 +215,7 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsi
         const unsigned lt = (1u << lane) - 1u;
         for (int i0 = 0; i0 < n; i0 += 32) {
             const int i = i0 + lane;
-            const int e = i < n ? ids[i] : -1;
+            const int e = i < n ? sid[i] : -1;
             const bool ok = (unsigned) e < (unsigned) E && blob[e] != 0ull;
             const unsigned peers = __match_any_sync(kFull, ok ? e : -1 - lane);
             int at = -1;
@@ -247,16 +262,28 @@ extern "C" int32_t bsx_dispatch(const int32_t* ids, int64_t n_pairs, int32_t k, 
     return launch_status();
 }
 
-extern "C" int32_t bsx_moe_plan(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table,
-                                unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok,
-                                void* stream) {
+static int32_t plan_launch(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table,
+                           unsigned long long shared_blob, unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst,
+                           int32_t* tok, void* stream) {
     if (!stream) return BSX_E_STREAM;
     const int64_t n = (int64_t) T * k;
     if (n <= 0) return BSX_OK;   // the reference returns without touching its outputs (ops.cu:491)
     if (n > BSX_PLAN_MAX_PAIRS) return BSX_E_LIMIT;
     if (E < 1 || E > 4096) return BSX_E_GEOMETRY;
     if (!ids || !blob_table || !ptr || !start || !n_groups || !dst || !tok) return BSX_E_POINTER;
-    const size_t smem = (size_t) E * (sizeof(unsigned long long) + 2 * sizeof(int32_t));
-    moe_plan_kernel<<<1, 256, smem, (cudaStream_t) stream>>>(ids, (int) n, k, E, blob_table, ptr, start, n_groups, dst, tok);
+    const size_t smem = (size_t) E * (sizeof(unsigned long long) + 2 * sizeof(int32_t)) + (size_t) n * sizeof(int32_t);
+    moe_plan_kernel<<<1, 256, smem, (cudaStream_t) stream>>>(ids, (int) n, k, E, blob_table, shared_blob, T, ptr, start, n_groups, dst, tok);
     return launch_status();
+}
+
+extern "C" int32_t bsx_moe_plan(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table,
+                                unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok,
+                                void* stream) {
+    return plan_launch(ids, T, k, E, blob_table, 0ull, ptr, start, n_groups, dst, tok, stream);
+}
+
+extern "C" int32_t bsx_moe_plan_shared(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table,
+                                       unsigned long long shared_blob, unsigned long long* ptr, int32_t* start, int32_t* n_groups,
+                                       int32_t* dst, int32_t* tok, void* stream) {
+    return plan_launch(ids, T, k, E, blob_table, shared_blob, ptr, start, n_groups, dst, tok, stream);
 }

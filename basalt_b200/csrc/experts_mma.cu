@@ -147,13 +147,14 @@ __global__ void __launch_bounds__(256) prep_image_kernel(ExpertArgs a, __half* _
 // TERMS = 1: 8 entries a pass; TERMS = 2: 4 entries a pass, each as hi + lo fp16 columns.
 template <int MODE, int TERMS>
 __global__ void __launch_bounds__(kThreads, 2)
-nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __restrict__ inv) {
+nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __restrict__ inv, int tiles_per_warp) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int64_t K = MODE == MODE_GU ? a.L.n_embd : a.L.n_ff;
     const int n_gran = (int) (K >> 6);                       // 64-column granules
     __half* xs = reinterpret_cast<__half*>(smem);            // [n_gran][2][8 cols][4][8]
     uint32_t* lut = reinterpret_cast<uint32_t*>(smem + (size_t) K * kCols * 2);   // [256] scale pairs
-    uint8_t* wbase = smem + (size_t) K * kCols * 2 + 1024;
+    uint4* zero = reinterpret_cast<uint4*>(smem + (size_t) K * kCols * 2 + 1024);   // 64 zero bytes: the B fragments of unused columns
+    uint8_t* wbase = smem + (size_t) K * kCols * 2 + 1152;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     uint8_t* wring = wbase + (size_t) warp * kStages * kStageBytes;
@@ -162,22 +163,29 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
     constexpr int NTOK = kCols / TERMS;
 
     lut[threadIdx.x] = scale_pair_bits(threadIdx.x);   // 256 threads, 256 entries; the first barrier below publishes it
+    if (threadIdx.x < 4) zero[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
 
     const int64_t n_rows = MODE == MODE_GU ? a.L.n_ff : a.L.n_embd;      // neurons (pairs) or down rows
-    const int64_t r0 = (int64_t) blockIdx.x * (MODE == MODE_GU ? kWarps * 8 : kWarps * 16) + warp * (MODE == MODE_GU ? 8 : 16);
-    const bool live = r0 < n_rows;
+    // a block covers tiles_per_warp row tiles per warp; tile j of warp w starts at row (or neuron) r0 + j * tile_stride
+    constexpr int kTileRows = MODE == MODE_GU ? 8 : 16;
+    constexpr int tile_stride = kWarps * kTileRows;
+    const int64_t r0 = (int64_t) blockIdx.x * tiles_per_warp * tile_stride + warp * kTileRows;
+    int live_tiles = 0;
+    while (live_tiles < tiles_per_warp && r0 + (int64_t) live_tiles * tile_stride < n_rows) ++live_tiles;
     const int n_chunks = n_gran >> 2;
+    const int n_units = live_tiles * n_chunks;               // (tile, chunk) stages this warp streams per pass
     const int pieces_per_col = (int) (K >> 3);               // 16-byte pieces of one image
 
     // this lane's copy duty inside a stage: pieces lane, lane + 32, ... (< 144); row = piece / 9
     int cp_row[5], cp_off[5];
+    uint32_t cp_dst[5];
 #pragma unroll
     for (int j = 0; j < 5; ++j) {
         const int p = lane + 32 * j;
         cp_row[j] = p / 9;
         cp_off[j] = (p % 9) * 16;
+        cp_dst[j] = (uint32_t) (cp_row[j] * kRowBytes + cp_off[j]);
     }
-    const uint32_t sel = (uint32_t) t | 0x4440u;   // byte t of the scale word, zero-extended
 
     const int ng = min(*a.n_groups, (int) a.cap_groups);
     for (int grp = blockIdx.y; grp < ng; grp += gridDim.y) {
@@ -196,17 +204,26 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
                 rp = blob + a.L.down_off + (size_t) (r0 + row) * a.L.d_row;
             src[j] = rp + cp_off[j];
         }
-        auto issue = [&](int chunk) {
-            if (live && chunk < n_chunks) {
-                const uint32_t dst = wring_s + (uint32_t) (chunk % kStages) * kStageBytes;
+        const size_t tile_bytes = (size_t) tile_stride * (MODE == MODE_GU ? a.L.gu_row : a.L.d_row);
+        // the next (tile, chunk) unit to request and its global byte offset from the tile-0, chunk-0 addresses
+        int iss_unit = 0, iss_chunk = 0;
+        size_t iss_off = 0;
+        auto issue = [&]() {
+            if (iss_unit < n_units) {
+                const uint32_t dst = wring_s + (uint32_t) (iss_unit & (kStages - 1)) * kStageBytes;
 #pragma unroll
                 for (int j = 0; j < 5; ++j)
-                    if (lane + 32 * j < kPieces)
-                        cp_async16(dst + (uint32_t) (cp_row[j] * kRowBytes + cp_off[j]), src[j] + (size_t) chunk * kRowBytes);
+                    if (lane + 32 * j < kPieces) cp_async16(dst + cp_dst[j], src[j] + iss_off);
+                ++iss_unit;
+                if (++iss_chunk == n_chunks) {
+                    iss_chunk = 0;
+                    iss_off += tile_bytes - (size_t) (n_chunks - 1) * kRowBytes;
+                } else {
+                    iss_off += kRowBytes;
+                }
             }
             cp_async_commit();
         };
-
         // passes (batches of NTOK entries) of one group are dealt round-robin to the blocks along grid z
         for (int eb = e0 + (int) blockIdx.z * NTOK; eb < e1; eb += NTOK * (int) gridDim.z) {
             const int ntok = min(NTOK, e1 - eb);
@@ -221,55 +238,61 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
             }
             cp_async_commit();
             // the weight stream
+            iss_unit = 0;
+            iss_chunk = 0;
+            iss_off = 0;
 #pragma unroll
-            for (int c = 0; c < kStages - 1; ++c) issue(c);
+            for (int c = 0; c < kStages - 1; ++c) issue();
             cp_async_wait<kStages - 1>();   // the activation group (the oldest) has landed
             __syncthreads();
 
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            if (live) {
-                const bool col_live = g < ncol;
-                for (int chunk = 0; chunk < n_chunks; ++chunk) {
-                    issue(chunk + kStages - 1);
-                    cp_async_wait<kStages - 1>();
-                    __syncwarp();
-                    const uint8_t* st = wring + (size_t) (chunk % kStages) * kStageBytes;
-                    const uint32_t* ra = reinterpret_cast<const uint32_t*>(st + g * kRowBytes);          // row g
-                    const uint32_t* rb = reinterpret_cast<const uint32_t*>(st + (g + 8) * kRowBytes);    // row g + 8
+            // two accumulator sets, so that consecutive MMAs do not wait on each other
+            float acc[4] = {0.f, 0.f, 0.f, 0.f}, acd[4] = {0.f, 0.f, 0.f, 0.f};
+            // this lane's B fragments: its column's pieces, or (column unused in this pass) the zero area with stride 0
+            const bool col_live = g < ncol;
+            const uint4* bcol = col_live ? reinterpret_cast<const uint4*>(xs) + g * 4 + t : zero;
+            const int bstep = col_live ? 2 * kCols * 4 : 0;      // uint4 per 64-column granule
+            const int bhalf = col_live ? kCols * 4 : 0;          // the second half-granule
+            int tile = 0, chunk = 0;
+            for (int unit = 0; unit < n_units; ++unit) {
+                issue();
+                cp_async_wait<kStages - 1>();
+                __syncwarp();
+                const uint8_t* st = wring + (size_t) (unit & (kStages - 1)) * kStageBytes;
+                const uint32_t* ra = reinterpret_cast<const uint32_t*>(st + g * kRowBytes);          // row g
+                const uint32_t* rb = reinterpret_cast<const uint32_t*>(st + (g + 8) * kRowBytes);    // row g + 8
+                const uint4* bp = bcol + (size_t) chunk * 4 * bstep;
 #pragma unroll
-                    for (int blk = 0; blk < 4; ++blk) {
-                        const int gran = chunk * 4 + blk;
-                        uint4 b0 = make_uint4(0u, 0u, 0u, 0u), b1 = b0;
-                        if (col_live) {
-                            const uint4* bp = reinterpret_cast<const uint4*>(xs + ((size_t) (gran * 2) * kCols + g) * 32 + t * 8);
-                            b0 = bp[0];
-                            b1 = bp[kCols * 4];   // the second half-granule: + 8 columns * 32 halves
-                        }
-                        const uint32_t sa = lut[__byte_perm(ra[9 * blk], 0u, sel)];
-                        const uint32_t sb = lut[__byte_perm(rb[9 * blk], 0u, sel)];
-                        uint32_t qa0[4], qa1[4], qb0[4], qb1[4];
-                        cvt_e2m1x8(ra[9 * blk + 1 + 2 * t], qa0);
-                        cvt_e2m1x8(ra[9 * blk + 2 + 2 * t], qa1);
-                        cvt_e2m1x8(rb[9 * blk + 1 + 2 * t], qb0);
-                        cvt_e2m1x8(rb[9 * blk + 2 + 2 * t], qb1);
+                for (int blk = 0; blk < 4; ++blk) {
+                    const uint4 b0 = bp[blk * bstep], b1 = bp[blk * bstep + bhalf];
+                    const uint32_t sa = lut[reinterpret_cast<const uint8_t*>(ra)[36 * blk + t]];
+                    const uint32_t sb = lut[reinterpret_cast<const uint8_t*>(rb)[36 * blk + t]];
+                    uint32_t qa0[4], qa1[4], qb0[4], qb1[4];
+                    cvt_e2m1x8(ra[9 * blk + 1 + 2 * t], qa0);
+                    cvt_e2m1x8(ra[9 * blk + 2 + 2 * t], qa1);
+                    cvt_e2m1x8(rb[9 * blk + 1 + 2 * t], qb0);
+                    cvt_e2m1x8(rb[9 * blk + 2 + 2 * t], qb1);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            qa0[i] = hmul2_bits(qa0[i], sa);
-                            qa1[i] = hmul2_bits(qa1[i], sa);
-                            qb0[i] = hmul2_bits(qb0[i], sb);
-                            qb1[i] = hmul2_bits(qb1[i], sb);
-                        }
-                        mma_f16(acc, qa0[0], qb0[0], qa0[1], qb0[1], b0.x, b0.y);
-                        mma_f16(acc, qa0[2], qb0[2], qa0[3], qb0[3], b0.z, b0.w);
-                        mma_f16(acc, qa1[0], qb1[0], qa1[1], qb1[1], b1.x, b1.y);
-                        mma_f16(acc, qa1[2], qb1[2], qa1[3], qb1[3], b1.z, b1.w);
+                    for (int i = 0; i < 4; ++i) {
+                        qa0[i] = hmul2_bits(qa0[i], sa);
+                        qa1[i] = hmul2_bits(qa1[i], sa);
+                        qb0[i] = hmul2_bits(qb0[i], sb);
+                        qb1[i] = hmul2_bits(qb1[i], sb);
                     }
-                    __syncwarp();   // every lane is done with this stage before a later issue overwrites it
+                    mma_f16(acc, qa0[0], qb0[0], qa0[1], qb0[1], b0.x, b0.y);
+                    mma_f16(acd, qa0[2], qb0[2], qa0[3], qb0[3], b0.z, b0.w);
+                    mma_f16(acc, qa1[0], qb1[0], qa1[1], qb1[1], b1.x, b1.y);
+                    mma_f16(acd, qa1[2], qb1[2], qa1[3], qb1[3], b1.z, b1.w);
                 }
-            }
-            cp_async_wait<0>();
-            // epilogue: undo the row scale and the 2^-8 of the fp16 block scales, apply the tail scales
-            if (live) {
+                __syncwarp();   // every lane is done with this stage before a later issue overwrites it
+                if (++chunk != n_chunks) continue;
+                // the tile is complete: undo the row scale and the 2^-8 of the fp16 block scales, apply the tail scales
+                const int64_t rt = r0 + (int64_t) tile * tile_stride;
+                chunk = 0;
+                ++tile;
+                const float c0 = acc[0] + acd[0], c1 = acc[1] + acd[1], c2 = acc[2] + acd[2], c3 = acc[3] + acd[3];
+                acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                acd[0] = acd[1] = acd[2] = acd[3] = 0.f;
                 if (MODE == MODE_GU) {
                     const float sg = tail[0] * 256.f, su = tail[1] * 256.f;
                     if (TERMS == 1) {
@@ -278,12 +301,12 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
                             const int j = 2 * t + q;
                             if (j < ntok) {
                                 const float f = inv[eb + j];
-                                a.h[(size_t) (eb + j) * a.L.n_ff + r0 + g] = swiglu(acc[q] * f * sg, acc[2 + q] * f * su, a.L);
+                                a.h[(size_t) (eb + j) * a.L.n_ff + rt + g] = swiglu((q ? c1 : c0) * f * sg, (q ? c3 : c2) * f * su, a.L);
                             }
                         }
                     } else if (t < ntok) {
                         const float f = inv[eb + t];
-                        a.h[(size_t) (eb + t) * a.L.n_ff + r0 + g] = swiglu((acc[0] + acc[1]) * f * sg, (acc[2] + acc[3]) * f * su, a.L);
+                        a.h[(size_t) (eb + t) * a.L.n_ff + rt + g] = swiglu((c0 + c1) * f * sg, (c2 + c3) * f * su, a.L);
                     }
                 } else {
                     const float sd = tail[2] * 256.f;
@@ -293,25 +316,26 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
                             const int j = 2 * t + q;
                             if (j < ntok) {
                                 const float f = inv[eb + j] * sd;
-                                const int64_t o = (int64_t) a.ent_dst[eb + j] * a.L.n_embd + r0 + g;
-                                store_out(a.out, a.out_kind, o, acc[q] * f);
-                                store_out(a.out, a.out_kind, o + 8, acc[2 + q] * f);
+                                const int64_t o = (int64_t) a.ent_dst[eb + j] * a.L.n_embd + rt + g;
+                                store_out(a.out, a.out_kind, o, (q ? c1 : c0) * f);
+                                store_out(a.out, a.out_kind, o + 8, (q ? c3 : c2) * f);
                             }
                         }
                     } else if (t < ntok) {
                         const float f = inv[eb + t] * sd;
-                        const int64_t o = (int64_t) a.ent_dst[eb + t] * a.L.n_embd + r0 + g;
-                        store_out(a.out, a.out_kind, o, (acc[0] + acc[1]) * f);
-                        store_out(a.out, a.out_kind, o + 8, (acc[2] + acc[3]) * f);
+                        const int64_t o = (int64_t) a.ent_dst[eb + t] * a.L.n_embd + rt + g;
+                        store_out(a.out, a.out_kind, o, (c0 + c1) * f);
+                        store_out(a.out, a.out_kind, o + 8, (c2 + c3) * f);
                     }
                 }
             }
+            cp_async_wait<0>();
         }
     }
     cp_async_wait<0>();
 }
 
-size_t smem_bytes(int64_t K) { return (size_t) K * kCols * 2 + 1024 + (size_t) kWarps * kStages * kStageBytes; }
+size_t smem_bytes(int64_t K) { return (size_t) K * kCols * 2 + 1152 + (size_t) kWarps * kStages * kStageBytes; }
 size_t align256(size_t v) { return (v + 255) & ~(size_t) 255; }
 
 template <int MODE, int TERMS>
@@ -327,7 +351,16 @@ int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, cudaStr
         configured[dev] = true;
     }
     const int64_t rows = MODE == MODE_GU ? a.L.n_ff : a.L.n_embd;
-    const int per_block = MODE == MODE_GU ? kWarps * 8 : kWarps * 16;
+    // a block streams ~256 KB of weights per pass, enough to hide its start-up (activation copy, first loads); the row
+    // tiles are dealt evenly over the blocks
+    const int64_t tile_bytes = (int64_t) kWarps * 16 * (K / 64 * 36);
+    const int64_t tile_rows = MODE == MODE_GU ? kWarps * 8 : kWarps * 16;
+    const int64_t n_tiles = (rows + tile_rows - 1) / tile_rows;
+    int64_t tpw0 = (256 * 1024 + tile_bytes - 1) / tile_bytes;
+    tpw0 = tpw0 < 1 ? 1 : tpw0 > 8 ? 8 : tpw0;
+    const int64_t n_blocks = (n_tiles + tpw0 - 1) / tpw0;
+    const int tpw = (int) ((n_tiles + n_blocks - 1) / n_blocks);
+    const int per_block = (int) tile_rows * tpw;
     const unsigned gy = (unsigned) (a.cap_groups < 1 ? 1 : a.cap_groups > 1024 ? 1024 : a.cap_groups);
     // blocks along z share a group's passes: about four passes' worth of blocks per possible group, never more than the
     // passes the call can have
@@ -336,7 +369,7 @@ int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, cudaStr
     int64_t gz = (4 * a.cap_entries + (int64_t) NTOK * gy - 1) / ((int64_t) NTOK * gy);
     gz = gz < 1 ? 1 : gz > 16 ? 16 : gz;
     gz = gz > max_passes ? max_passes : gz;
-    nvfp4_mma_kernel<MODE, TERMS><<<dim3((unsigned) ((rows + per_block - 1) / per_block), gy, (unsigned) gz), kThreads, smem, st>>>(a, img, inv);
+    nvfp4_mma_kernel<MODE, TERMS><<<dim3((unsigned) ((rows + per_block - 1) / per_block), gy, (unsigned) gz), kThreads, smem, st>>>(a, img, inv, tpw);
     return launch_status();
 }
 

@@ -63,7 +63,21 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
     const int t_end = min(n_tokens, t_begin + tok_per_block);
     for (int t0 = t_begin; t0 < t_end; t0 += kTokTile) {
         const int nt = min(kTokTile, t_end - t0);
+        // the next token's columns are requested while the current token's sums run
+        float4 xv[NV], xn[NV];
+#pragma unroll
+        for (int c = 0; c < NV; ++c) {
+            const int i = threadIdx.x + c * kLogitThreads;
+            xv[c] = i < n4 ? load_x4(x, (size_t) t0, n_embd, i, BF16) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
         for (int t = 0; t < nt; ++t) {
+            if (t + 1 < nt) {
+#pragma unroll
+                for (int c = 0; c < NV; ++c) {
+                    const int i = threadIdx.x + c * kLogitThreads;
+                    if (i < n4) xn[c] = load_x4(x, (size_t) (t0 + t + 1), n_embd, i, BF16);
+                }
+            }
             float acc[G];
 #pragma unroll
             for (int g = 0; g < G; ++g) acc[g] = 0.f;
@@ -71,7 +85,7 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
             for (int c = 0; c < NV; ++c) {
                 const int i = threadIdx.x + c * kLogitThreads;
                 if (i < n4) {
-                    const float4 v = load_x4(x, (size_t) (t0 + t), n_embd, i, BF16);
+                    const float4 v = xv[c];
 #pragma unroll
                     for (int g = 0; g < G; ++g) {
                         acc[g] = fmaf(w[g][c].x, v.x, acc[g]);
@@ -81,11 +95,32 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
                     }
                 }
             }
+            // The G butterflies at once: at the xor-16, -8 and -4 stages a lane keeps half of its values and hands the other
+            // half to its partner, so each stage adds exactly the pairs the plain butterfly adds (a + b == b + a bit for
+            // bit); after the halving stages the lane holds one row's partial sum and the remaining stages run in full.
+            int row = 0;
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float s = warp_sum_xor(acc[g]);
-                if (lane == 0) red[g][t][warp] = s;
+            for (int m = 16, n = G; m; m >>= 1) {
+                if (n > 1) {
+                    const int half = n >> 1;
+                    const bool up = (lane & m) != 0;
+#pragma unroll
+                    for (int i = 0; i < G / 2; ++i)
+                        if (i < half) {
+                            const float keep = up ? acc[i + half] : acc[i];
+                            const float send = up ? acc[i] : acc[i + half];
+                            acc[i] = keep + __shfl_xor_sync(kFull, send, m);
+                        }
+                    if (up) row += half;
+                    n = half;
+                } else {
+                    acc[0] += __shfl_xor_sync(kFull, acc[0], m);
+                }
             }
+            constexpr int kOwners = 32 / G;   // lanes holding the same row's sum
+            if ((lane & (kOwners - 1)) == 0) red[row][t][warp] = acc[0];
+#pragma unroll
+            for (int c = 0; c < NV; ++c) xv[c] = xn[c];
         }
         __syncthreads();
         {

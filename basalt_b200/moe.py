@@ -192,7 +192,9 @@ def moe_combine(rows, slot, weights, shared=None, shared_gate=None, y=None, stre
 
 class MoELayer:
     """One resident MoE layer: router gate, routed expert blobs, optional shared expert, run as the reference's decode
-    window does (inkling2/session.cpp:680-716): router -> moe_plan -> native_expert_grouped -> combine."""
+    window does (inkling2/session.cpp:680-716): router -> moe_plan -> native_expert_grouped -> combine.  A shared expert
+    with the routed experts' layout rides in the same grouped call as one more group (bsx_moe_plan_shared); one with
+    another layout (a Q6_K shared expert beside IQ1_M routed ones) gets its own call."""
 
     def __init__(self, gate_w: torch.Tensor, bias: Optional[torch.Tensor], blobs: torch.Tensor, layout: ExpertLayout,
                  args: RouterArgs, shared_blob: Optional[torch.Tensor] = None, shared_layout: Optional[ExpertLayout] = None,
@@ -207,19 +209,21 @@ class MoELayer:
         self.max_tokens = max_tokens
         n = max_tokens * args.k
         assert n <= 1024, "the decode-window plan takes at most 1024 (token, expert) pairs"
+        self.fused_shared = shared_blob is not None and bytes(self.shared_L) == bytes(layout)
+        rows = n + (max_tokens if self.fused_shared else 0)
         f32, i32 = torch.float32, torch.int32
         self.logits = torch.empty((max_tokens, E), dtype=f32, device=dev)
         self.ids = torch.empty((max_tokens, args.k), dtype=i32, device=dev)
         self.w = torch.empty((max_tokens, args.k), dtype=f32, device=dev)
-        self.ptr = torch.zeros(n, dtype=torch.int64, device=dev)
-        self.start = torch.zeros(n + 2, dtype=i32, device=dev)
+        self.ptr = torch.zeros(n + 3, dtype=torch.int64, device=dev)
+        self.start = torch.zeros(n + 3, dtype=i32, device=dev)
         self.n_groups = torch.zeros(1, dtype=i32, device=dev)
-        self.dst = torch.zeros(n, dtype=i32, device=dev)
-        self.tok = torch.zeros(n, dtype=i32, device=dev)
-        self.rows = torch.empty((n, layout.n_embd), dtype=f32, device=dev)
-        self.scratch = torch.empty(native_expert_scratch_bytes(layout, n), dtype=torch.uint8, device=dev)
+        self.dst = torch.zeros(rows, dtype=i32, device=dev)
+        self.tok = torch.zeros(rows, dtype=i32, device=dev)
+        self.rows = torch.empty((rows, layout.n_embd), dtype=f32, device=dev)
+        self.scratch = torch.empty(native_expert_scratch_bytes(layout, rows), dtype=torch.uint8, device=dev)
         self.y = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
-        if shared_blob is not None:
+        if shared_blob is not None and not self.fused_shared:
             self.s_ptr = torch.tensor([shared_blob.data_ptr()], dtype=torch.int64, device=dev)
             self.s_iota = torch.arange(max_tokens, dtype=i32, device=dev)
             self.s_one = torch.ones(1, dtype=i32, device=dev)
@@ -236,24 +240,32 @@ class MoELayer:
         assert T <= self.max_tokens
         xr = x_router if x_router is not None else x     # fp32 or bf16 rows; bf16 is widened exactly inside the kernel
         hp, hn, keep = _held(a)
-        check("bsx_router", lib.bsx_router_x(_p(xr), X_BF16 if xr.dtype == torch.bfloat16 else X_F32, _p(self.gate_w), _p(self.bias), T, a.n_expert, a.n_embd, a.k, a.gate,
-                                            a.weight_scale, a.n_group, a.topk_group, a.prior, hp, hn, _p(self.logits), _p(self.ids),
-                                            _p(self.w), st))
-        check("bsx_moe_plan", lib.bsx_moe_plan(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), _p(self.ptr), _p(self.start),
-                                                _p(self.n_groups), _p(self.dst), _p(self.tok), st))
+        check("bsx_router", lib.bsx_router_x(_p(xr), X_BF16 if xr.dtype == torch.bfloat16 else X_F32, _p(self.gate_w), _p(self.bias), T,
+                                              a.n_expert, a.n_embd, a.k, a.gate, a.weight_scale, a.n_group, a.topk_group, a.prior, hp, hn,
+                                              _p(self.logits), _p(self.ids), _p(self.w), st))
         n = T * a.k
         kind = _x_kind(x)
-        check("bsx_experts_grouped", lib.bsx_experts_grouped(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
-                                                             _p(self.dst), _p(self.tok), min(n, a.n_expert), n, _p(x), kind,
-                                                             _p(self.scratch), _p(self.rows), OUT_F32, st))
         shared = None
-        if self.shared_blob is not None:
-            if self._s_T != T:
-                self.s_start.copy_(torch.tensor([0, T, T], dtype=torch.int32))
-                self._s_T = T
-            check("bsx_experts_grouped", lib.bsx_experts_grouped(C.byref(self.shared_L), _p(self.s_ptr), _p(self.s_start),
-                                                                 _p(self.s_one), _p(self.s_iota), _p(self.s_iota), 1, T, _p(x), kind,
-                                                                 _p(self.s_scratch), _p(self.s_out), OUT_F32, st))
-            shared = self.s_out
+        if self.fused_shared:
+            check("bsx_moe_plan_shared", lib.bsx_moe_plan_shared(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), self.shared_blob.data_ptr(),
+                                                                 _p(self.ptr), _p(self.start), _p(self.n_groups), _p(self.dst), _p(self.tok), st))
+            check("bsx_experts_grouped", lib.bsx_experts_grouped(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups), _p(self.dst),
+                                                                 _p(self.tok), min(n, a.n_expert) + 1, n + T, _p(x), kind, _p(self.scratch),
+                                                                 _p(self.rows), OUT_F32, st))
+            shared = self.rows[n:n + T]
+        else:
+            check("bsx_moe_plan", lib.bsx_moe_plan(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), _p(self.ptr), _p(self.start),
+                                                    _p(self.n_groups), _p(self.dst), _p(self.tok), st))
+            check("bsx_experts_grouped", lib.bsx_experts_grouped(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups), _p(self.dst),
+                                                                 _p(self.tok), min(n, a.n_expert), n, _p(x), kind, _p(self.scratch),
+                                                                 _p(self.rows), OUT_F32, st))
+            if self.shared_blob is not None:
+                if self._s_T != T:
+                    self.s_start.copy_(torch.tensor([0, T, T], dtype=torch.int32))
+                    self._s_T = T
+                check("bsx_experts_grouped", lib.bsx_experts_grouped(C.byref(self.shared_L), _p(self.s_ptr), _p(self.s_start), _p(self.s_one),
+                                                                     _p(self.s_iota), _p(self.s_iota), 1, T, _p(x), kind, _p(self.s_scratch),
+                                                                     _p(self.s_out), OUT_F32, st))
+                shared = self.s_out
         check("bsx_combine", lib.bsx_combine(_p(self.rows), None, _p(self.w), _p(shared), None, T, a.k, self.L.n_embd, _p(self.y), st))
         return self.y[:T]

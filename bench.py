@@ -213,11 +213,10 @@ def main():
     n_batches = 8
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     xs = [torch.randn((T, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
-    xr = [x.float() for x in xs]   # the router reads fp32 rows (the reference's router ABI); produced by the step before the layer
     stream = torch.cuda.Stream(device=dev)
 
     def step(i, x=None):
-        return layers[i % args.copies].forward(xs[i % n_batches] if x is None else x, xr[i % n_batches] if x is None else None, stream)
+        return layers[i % args.copies].forward(xs[i % n_batches] if x is None else x, None, stream)
 
     def barrier():
         if world > 1:
@@ -255,7 +254,7 @@ def main():
         barrier()
         ms_e2e = e0.elapsed_time(e1)
         # ---- per-stage device times for the roofline (same steps, events between the C ABI calls)
-        stage_ms, gu_bytes = instrumented_pass(layers, xs, xr, stream, min(args.steps, 100), L)
+        stage_ms, gu_bytes = instrumented_pass(layers, xs, None, stream, min(args.steps, 100), L)
         barrier()
 
     times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
@@ -275,8 +274,8 @@ def main():
         "config": dict(CFG, l2_policy=f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB) and each step touches ~650 MB: larger than L2",
                        parallelism="single GPU" if world == 1 else f"ep{world}"),
         "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
-        "gpu_launches": 8 * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "nvfp4_mma_kernel<gate/up> (routed experts)", "achieved": achieved, "peak": peak,
+        "gpu_launches": 9 * args.steps,   # logits, select, plan, 2 x image prep, gate/up, down, combine (+0: the shared expert rides in the grouped call)
+        "roofline": {"bound": "hbm", "kernel": "nvfp4_mma_kernel<gate/up> (routed + shared experts; stage time includes the activation-image kernel)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
                      "algorithmic_bytes_per_launch": gu_bytes, "kernel_ms": gu_ms, "frac_of_nominal_8TBs": achieved / 8000.0},
         "stage_ms": stage_ms,
@@ -297,41 +296,40 @@ def main():
 
 def instrumented_pass(layers, xs, xr, stream, steps, L):
     """Re-runs the steps with CUDA events between the C ABI calls; returns mean ms per stage and the gate/up launch's
-    algorithmic bytes (distinct routed experts touched x gate+up bytes + activations in + h out), averaged over steps."""
+    algorithmic bytes (distinct experts touched, the shared one included, x gate+up bytes + activation images in + h out),
+    averaged over steps."""
     from basalt_b200 import capi
     from basalt_b200.moe import _p, _stream, _x_kind
     lib = capi.lib()
     st = _stream(stream)
-    names = ["router", "plan", "experts_gate_up", "experts_down", "shared_expert", "combine"]
+    names = ["router", "plan", "experts_gate_up", "experts_down", "combine"]
     acc = {n: 0.0 for n in names}
     gu_bytes = 0.0
     for i in range(steps):
-        ly, x, xrr = layers[i % len(layers)], xs[i % len(xs)], xr[i % len(xs)]
+        ly, x = layers[i % len(layers)], xs[i % len(xs)]
         a = ly.args
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(7)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         n = T * a.k
         ev[0].record(stream)
-        capi.check("router", lib.bsx_router(_p(xrr), _p(ly.gate_w), None, T, a.n_expert, a.n_embd, a.k, a.gate, a.weight_scale, 1, 1, 0.0, None, 0,
-                                            _p(ly.logits), _p(ly.ids), _p(ly.w), st))
+        capi.check("router", lib.bsx_router_x(_p(x), _x_kind(x), _p(ly.gate_w), None, T, a.n_expert, a.n_embd, a.k, a.gate, a.weight_scale, 1, 1, 0.0,
+                                              None, 0, _p(ly.logits), _p(ly.ids), _p(ly.w), st))
         ev[1].record(stream)
-        capi.check("plan", lib.bsx_moe_plan(_p(ly.ids), T, a.k, a.n_expert, _p(ly.blob_table), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok), st))
+        capi.check("plan", lib.bsx_moe_plan_shared(_p(ly.ids), T, a.k, a.n_expert, _p(ly.blob_table), ly.shared_blob.data_ptr(), _p(ly.ptr), _p(ly.start),
+                                                   _p(ly.n_groups), _p(ly.dst), _p(ly.tok), st))
         ev[2].record(stream)
         for phase in (1, 2):
             lib.bsx_experts_set_phase(phase)
-            capi.check("experts", lib.bsx_experts_grouped(C.byref(ly.L), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok), min(n, a.n_expert), n,
-                                                           _p(x), _x_kind(x), _p(ly.scratch), _p(ly.rows), capi.OUT_F32, st))
+            capi.check("experts", lib.bsx_experts_grouped(C.byref(ly.L), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
+                                                           min(n, a.n_expert) + 1, n + T, _p(x), _x_kind(x), _p(ly.scratch), _p(ly.rows), capi.OUT_F32, st))
             ev[2 + phase].record(stream)
         lib.bsx_experts_set_phase(0)
-        capi.check("shared", lib.bsx_experts_grouped(C.byref(ly.shared_L), _p(ly.s_ptr), _p(ly.s_start), _p(ly.s_one), _p(ly.s_iota), _p(ly.s_iota), 1, T, _p(x),
-                                                      _x_kind(x), _p(ly.s_scratch), _p(ly.s_out), capi.OUT_F32, st))
+        capi.check("combine", lib.bsx_combine(_p(ly.rows), None, _p(ly.w), _p(ly.rows[n:n + T]), None, T, a.k, L.n_embd, _p(ly.y), st))
         ev[5].record(stream)
-        capi.check("combine", lib.bsx_combine(_p(ly.rows), None, _p(ly.w), _p(ly.s_out), None, T, a.k, L.n_embd, _p(ly.y), st))
-        ev[6].record(stream)
         stream.synchronize()
         for j, nme in enumerate(names):
             acc[nme] += ev[j].elapsed_time(ev[j + 1])
-        distinct = int(ly.n_groups.item())
-        gu_bytes += distinct * 2 * L.n_ff * L.gu_row + T * L.n_embd * 2 + n * L.n_ff * 4
+        groups = int(ly.n_groups.item())      # distinct routed experts touched + the shared expert
+        gu_bytes += groups * 2 * L.n_ff * L.gu_row + (n + T) * L.n_embd * 2 + (n + T) * L.n_ff * 4
     return {k: v / steps for k, v in acc.items()}, gu_bytes / steps
 
 

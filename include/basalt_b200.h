@@ -123,6 +123,15 @@ BSX_API int32_t bsx_dispatch(const int32_t* ids, int64_t n_pairs, int32_t k, int
 BSX_API int32_t bsx_moe_plan(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table,
                      unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok, void* stream);
 
+/* ---- a6 + a10: the decode-window plan with the shared expert as one more group.  Basalt runs a shared expert as a dense
+ * gated MLP whose plan is "one group holding every token" (gated_mlp_plan_kernel, src/kernels/cuda/iq_kernels.cu:3414-3426);
+ * here that group is appended to the routed groups so one bsx_experts_grouped call covers both: ptr[n_groups-1] =
+ * shared_blob, its entries read token t and write output row T*k + t (t < T).  ptr / start need T*k + 3 slots, dst / tok
+ * T*k + T.  shared_blob = 0 gives bsx_moe_plan.  The shared expert must have the routed experts' layout. */
+BSX_API int32_t bsx_moe_plan_shared(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table,
+                                    unsigned long long shared_blob, unsigned long long* ptr, int32_t* start, int32_t* n_groups,
+                                    int32_t* dst, int32_t* tok, void* stream);
+
 /* ---- a8: expert blob geometry.  Mirrors NativeExpertLayout / native_expert_layout / native_expert_supported /
  * native_expert_scratch_bytes (include/basalt/kernels/iq_kernels.hpp:51-75, src/kernels/cuda/iq_kernels.cu:3208-3242):
  * blob = [gate rows | up rows | down rows | NVFP4 only: fp32 {s_gate, s_up, s_down, 0}], raw ggml blocks. */
