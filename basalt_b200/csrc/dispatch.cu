@@ -147,87 +147,77 @@ dispatch_place_kernel(const int32_t* __restrict__ ids, int64_t n, int k, int E, 
 }
 
 // ---------------------------------------------------------------------------------------------- decode-window plan
-// One block.  Counts per expert in shared memory, one warp scans the experts into compacted groups, then one warp
-// places the pairs in pair order, 32 at a time with __match_any_sync ranks, so an expert's entries keep the order of the
-// pairs (the reference counts the earlier equal ids instead, ops.cu:331-339; the result is the same).
-__global__ void __launch_bounds__(256)
+// One block of 1024 threads, everything in shared memory and nothing serial: the pairs are counted per expert with
+// shared-memory atomics, a block scan over the experts gives each used expert its group and first entry, and every pair
+// finds its place by counting the earlier pairs that name the same expert (the reference's rule, ops.cu:331-339), so an
+// expert's entries keep the order of the pairs and no position comes from an atomic.
+__global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsigned long long* __restrict__ blobs,
                 unsigned long long shared_blob, int n_tok, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
                 int32_t* __restrict__ n_groups, int32_t* __restrict__ dst, int32_t* __restrict__ tok) {
     extern __shared__ unsigned long long smb[];
     unsigned long long* blob = smb;                               // [E]
     int32_t* count = reinterpret_cast<int32_t*>(smb + E);         // [E]
-    int32_t* next = count + E;                                    // [E]: the expert's next entry
-    int32_t* sid = next + E;                                      // [n]: the ids, read once from global memory
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int32_t* first = count + E;                                   // [E]: the expert's first entry
+    int32_t* sid = first + E;                                     // [n]: the ids (-1: no entry)
+    __shared__ int sh[32];
+    __shared__ int s_tot[2];
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         blob[e] = blobs[e];
         count[e] = 0;
     }
-    for (int i = threadIdx.x; i < n; i += blockDim.x) sid[i] = ids[i];
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const int e = sid[i];
-        if ((unsigned) e < (unsigned) E && blob[e]) atomicAdd(&count[e], 1);
+        int e = ids[i];
+        if ((unsigned) e >= (unsigned) E || !blob[e]) e = -1;
+        sid[i] = e;
+        if (e >= 0) atomicAdd(&count[e], 1);
     }
     __syncthreads();
-    if (warp == 0) {
-        int at = 0, g = 0;
-        for (int e0 = 0; e0 < E; e0 += 32) {
-            const int e = e0 + lane;
-            const int c = e < E ? count[e] : 0;
-            int s = c, used = c > 0;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int a = __shfl_up_sync(kFull, s, o), u = __shfl_up_sync(kFull, used, o);
-                if (lane >= o) { s += a; used += u; }
-            }
-            if (e < E) next[e] = at + s - c;
-            if (c > 0) {
-                ptr[g + used - 1] = blob[e];
-                start[g + used - 1] = at + s - c;
-            }
-            at += __shfl_sync(kFull, s, 31);
-            g += __shfl_sync(kFull, used, 31);
+    int at = 0, g = 0;   // running totals over the expert chunks of blockDim.x
+    for (int e0 = 0; e0 < E; e0 += blockDim.x) {
+        const int e = e0 + threadIdx.x;
+        const int c = e < E ? count[e] : 0;
+        int rows = 0, used = 0;
+        const int o = block_excl_sum(c, &rows, sh);
+        const int u = block_excl_sum(c > 0 ? 1 : 0, &used, sh);
+        if (e < E) first[e] = at + o;
+        if (c > 0) {
+            ptr[g + u] = blob[e];
+            start[g + u] = at + o;
         }
+        at += rows;
+        g += used;
+    }
+    if (shared_blob != 0ull && n_tok > 0) {
         // the shared expert: one more group holding every token, its rows after the routed pairs' rows
-        if (shared_blob != 0ull && n_tok > 0) {
-            if (lane == 0) {
-                ptr[g] = shared_blob;
-                start[g] = at;
-            }
-            for (int t = lane; t < n_tok; t += 32) {
-                dst[at + t] = n + t;
-                tok[at + t] = t;
-            }
-            at += n_tok;
-            ++g;
-        }
-        if (lane == 0) {
+        if (threadIdx.x == 0) {
+            ptr[g] = shared_blob;
             start[g] = at;
-            start[g + 1] = at;
-            *n_groups = g;
         }
+        for (int t = threadIdx.x; t < n_tok; t += blockDim.x) {
+            dst[at + t] = n + t;
+            tok[at + t] = t;
+        }
+        at += n_tok;
+        ++g;
     }
-    __syncthreads();
-    // one warp walks the pairs in order, 32 at a time: no block barrier inside the walk
-    if (warp == 0) {
-        const unsigned lt = (1u << lane) - 1u;
-        for (int i0 = 0; i0 < n; i0 += 32) {
-            const int i = i0 + lane;
-            const int e = i < n ? sid[i] : -1;
-            const bool ok = (unsigned) e < (unsigned) E && blob[e] != 0ull;
-            const unsigned peers = __match_any_sync(kFull, ok ? e : -1 - lane);
-            int at = -1;
-            if (ok) at = next[e] + __popc(peers & lt);
-            __syncwarp();
-            if (ok && (__ffs(peers) - 1) == lane) next[e] += __popc(peers);
-            __syncwarp();
-            if (ok) {
-                dst[at] = i;
-                tok[at] = i / k;
-            }
-        }
+    if (threadIdx.x == 0) {
+        start[g] = at;
+        start[g + 1] = at;
+        *n_groups = g;
+    }
+    __syncthreads();   // first[] is complete
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = sid[i];
+        if (e < 0) continue;
+        int before = 0;
+        int j = 0;
+        for (; j + 4 <= i; j += 4) before += (sid[j] == e) + (sid[j + 1] == e) + (sid[j + 2] == e) + (sid[j + 3] == e);
+        for (; j < i; ++j) before += sid[j] == e;
+        const int p = first[e] + before;
+        dst[p] = i;
+        tok[p] = i / k;
     }
 }
 
@@ -272,7 +262,7 @@ static int32_t plan_launch(const int32_t* ids, int32_t T, int32_t k, int32_t E, 
     if (E < 1 || E > 4096) return BSX_E_GEOMETRY;
     if (!ids || !blob_table || !ptr || !start || !n_groups || !dst || !tok) return BSX_E_POINTER;
     const size_t smem = (size_t) E * (sizeof(unsigned long long) + 2 * sizeof(int32_t)) + (size_t) n * sizeof(int32_t);
-    moe_plan_kernel<<<1, 256, smem, (cudaStream_t) stream>>>(ids, (int) n, k, E, blob_table, shared_blob, T, ptr, start, n_groups, dst, tok);
+    moe_plan_kernel<<<1, 1024, smem, (cudaStream_t) stream>>>(ids, (int) n, k, E, blob_table, shared_blob, T, ptr, start, n_groups, dst, tok);
     return launch_status();
 }
 

@@ -57,22 +57,39 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const float* __restr
 
 // y[t] = fma chain over the k rows in order, then the shared expert: src/models/qwen4exp/kernels/native_moe.cu:36-50 and
 // src/models/qwen4exp/prefill/kernels.cu:438-449 (bit-equal forms).  A thread owns 4 consecutive columns.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ slot, const float* __restrict__ w,
-               const float* __restrict__ shared, const float* __restrict__ sg, int k, int H, float* __restrict__ y) {
+               const float* __restrict__ shared, const float* __restrict__ sg, int k, int H, int pair0, float* __restrict__ y) {
+    __shared__ int s_row[64];
+    __shared__ float s_w[64];
     const int t = blockIdx.y;
+    if (threadIdx.x < k) {
+        s_row[threadIdx.x] = slot ? slot[(size_t) t * k + threadIdx.x] : pair0 + t * k + (int) threadIdx.x;
+        s_w[threadIdx.x] = w[(size_t) t * k + threadIdx.x];
+    }
+    __syncthreads();
     const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
     if (c4 * 4 >= H) return;
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j = 0; j < k; ++j) {
-        const int64_t r = slot ? (int64_t) slot[(size_t) t * k + j] : (int64_t) t * k + j;
-        if (r < 0) continue;
-        const float wj = w[(size_t) t * k + j];
-        const float4 p = reinterpret_cast<const float4*>(rows + (size_t) r * H)[c4];
-        s.x = fmaf(wj, p.x, s.x);
-        s.y = fmaf(wj, p.y, s.y);
-        s.z = fmaf(wj, p.z, s.z);
-        s.w = fmaf(wj, p.w, s.w);
+    for (int j0 = 0; j0 < k; j0 += 4) {
+        // four row reads in flight, then their fused multiply-adds in j order
+        float4 p[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u;
+            p[u] = (j < k && s_row[j] >= 0) ? reinterpret_cast<const float4*>(rows + (size_t) s_row[j] * H)[c4] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u;
+            if (j < k && s_row[j] >= 0) {
+                const float wj = s_w[j];
+                s.x = fmaf(wj, p[u].x, s.x);
+                s.y = fmaf(wj, p[u].y, s.y);
+                s.z = fmaf(wj, p[u].z, s.z);
+                s.w = fmaf(wj, p[u].w, s.w);
+            }
+        }
     }
     if (shared) {
         const float4 p = reinterpret_cast<const float4*>(shared + (size_t) t * H)[c4];
@@ -175,7 +192,7 @@ extern "C" int32_t bsx_quantize_q8_1_rows(const float* x, int64_t n_rows, int64_
     return rc;
 }
 
-extern "C" int32_t bsx_experts_grouped(const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
+static int32_t experts_grouped_impl(int32_t n_x_rows, const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
                                        const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
                                        int64_t cap_entries, const void* x, int32_t x_kind, void* scratch, void* out,
                                        int32_t out_kind, void* stream) {
@@ -201,6 +218,7 @@ extern "C" int32_t bsx_experts_grouped(const bsx_expert_layout* layout, const un
     a.h = static_cast<float*>(scratch);
     a.out = out;
     a.out_kind = out_kind;
+    a.n_x_rows = n_x_rows > 0 ? n_x_rows : 0;
     a.grid = device_grid();
     if (!a.grid) return (int32_t) cudaErrorInvalidSymbol;
     const cudaStream_t st = (cudaStream_t) stream;
@@ -213,13 +231,35 @@ extern "C" int32_t bsx_experts_grouped(const bsx_expert_layout* layout, const un
     return experts_grouped_simple(a, st);
 }
 
+extern "C" int32_t bsx_experts_grouped(const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
+                                       const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
+                                       int64_t cap_entries, const void* x, int32_t x_kind, void* scratch, void* out, int32_t out_kind,
+                                       void* stream) {
+    return experts_grouped_impl(0, layout, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups, cap_entries, x, x_kind, scratch, out,
+                                out_kind, stream);
+}
+
+extern "C" int32_t bsx_experts_grouped_rows(const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
+                                            const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
+                                            int64_t cap_entries, const void* x, int32_t x_kind, int32_t n_x_rows, void* scratch, void* out,
+                                            int32_t out_kind, void* stream) {
+    if (n_x_rows < 0 || n_x_rows > cap_entries) n_x_rows = 0;   // more rows than entries: per-entry images are the cheaper form
+    return experts_grouped_impl(n_x_rows, layout, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups, cap_entries, x, x_kind, scratch,
+                                out, out_kind, stream);
+}
+
 extern "C" int32_t bsx_combine(const float* rows, const int32_t* slot, const float* weights, const float* shared,
                                const float* shared_gate, int32_t T, int32_t k, int32_t H, float* y, void* stream) {
     if (!stream) return BSX_E_STREAM;
     if (T < 0 || k < 1 || k > 64 || H < 4 || H % 4) return BSX_E_GEOMETRY;
     if (T == 0) return BSX_OK;
     if (!aligned(rows, 16) || !weights || !aligned(y, 16) || (shared && !aligned(shared, 16))) return BSX_E_POINTER;
-    const dim3 grid((unsigned) ((H / 4 + 255) / 256), (unsigned) T);
-    combine_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(rows, slot, weights, shared, shared_gate, k, H, y);
+    for (int32_t t0 = 0; t0 < T; t0 += 65535) {   // grid.y limit
+        const int32_t nt = T - t0 < 65535 ? T - t0 : 65535;
+        const dim3 grid((unsigned) ((H / 4 + 127) / 128), (unsigned) nt);
+        combine_kernel<<<grid, 128, 0, (cudaStream_t) stream>>>(rows, slot ? slot + (size_t) t0 * k : nullptr, weights + (size_t) t0 * k,
+                                                               shared ? shared + (size_t) t0 * H : nullptr, shared_gate ? shared_gate + t0 : nullptr,
+                                                               k, H, t0 * k, y + (size_t) t0 * H);
+    }
     return launch_status();
 }

@@ -21,6 +21,7 @@ struct ExpertArgs {
     void* out;
     int32_t out_kind;
     const uint16_t* grid;   // the IQ1 codebook on this device (2048 x uint16)
+    int32_t n_x_rows;       // rows of x when the caller knows them (activation images are then made once per row), else 0
 };
 
 // SwiGLU forms of the Basalt engine (src/kernels/cuda/iq_kernels.cu:2520-2521 plain, :3263-3279 limited, :3283-3298

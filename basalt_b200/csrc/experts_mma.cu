@@ -96,49 +96,128 @@ __device__ __forceinline__ float load_x(const void* x, int kind, int64_t row, in
     return __half2float(*reinterpret_cast<const __half*>(b)) * (float) (int8_t) b[4 + (c & 31)];
 }
 
-// One block per entry: the entry's activation row -> fp16 image(s) in fragment order plus the inverse of the power of two it
-// was scaled by (so that its largest magnitude lands in [2^13, 2^14), inside fp16 whatever the row's range).
-// FROM_H = false: row ent_tok[e] of x (kind x_kind, width n_embd); true: row e of the SwiGLU output h (fp32, width n_ff).
+// 16 consecutive values [16 sb, 16 sb + 16) of an activation row
+__device__ __forceinline__ void load16(const void* x, int kind, int64_t row, int64_t K, int sb, float (&v)[16]) {
+    if (kind == BSX_X_F32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) + row * K + 16 * sb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 f = p[i];
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+    } else if (kind == BSX_X_BF16) {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x) + row * K + 16 * sb);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint4 u = p[i];
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+                v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+            }
+        }
+    } else {   // q8_1: 36-byte blocks {fp16 d, fp16 sum, 32 int8}; value = d * q
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(x) + (row * (K / 32) + (sb >> 1)) * 36);
+        const float d = __half2float(__ushort_as_half((unsigned short) (p[0] & 0xFFFFu)));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t w = p[1 + 4 * (sb & 1) + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[4 * i + j] = d * (float) (int8_t) ((w >> (8 * j)) & 0xFFu);
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    return (uint32_t) __half_as_ushort(__float2half_rn(lo)) | ((uint32_t) __half_as_ushort(__float2half_rn(hi)) << 16);
+}
+
+// One warp per activation row: the row -> fp16 image(s) in fragment order plus the inverse of the power of two it was
+// scaled by (so that its largest magnitude lands in [2^13, 2^14), inside fp16 whatever the row's range).  A lane takes one
+// 16-value sub-block at a time, which is exactly two 16-byte pieces of the image (see image_index).
+// FROM_H = false: rows of x (kind x_kind, width n_embd) - row i of x when the caller gave the number of x rows, else the
+// row of entry i; true: row e of the SwiGLU output h (fp32, width n_ff).
+// The last block lists the passes of the product that follows: a pass is up to 8 / TERMS consecutive entries of one group,
+// items[i] = {group, first entry}, so that kernel's blocks take one pass each however the entries are spread.
 template <bool FROM_H, int TERMS>
-__global__ void __launch_bounds__(256) prep_image_kernel(ExpertArgs a, __half* __restrict__ img, float* __restrict__ inv) {
-    __shared__ float s_red[8];
-    __shared__ float s_scale;
-    const int e = blockIdx.x;
+__global__ void __launch_bounds__(256)
+prep_image_kernel(ExpertArgs a, __half* __restrict__ img, float* __restrict__ inv, int2* __restrict__ items, int* __restrict__ n_items) {
     const int ng = min(*a.n_groups, (int) a.cap_groups);
     const int total = min(a.grp_start[ng], (int) a.cap_entries);
-    if (e >= total) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (blockIdx.x == gridDim.x - 1) {
+        constexpr int NTOK = kCols / TERMS;
+        __shared__ int sh[8];
+        __shared__ int s_base;
+        if (threadIdx.x == 0) s_base = 0;
+        __syncthreads();
+        for (int g0 = 0; g0 < ng; g0 += 256) {
+            const int g = g0 + threadIdx.x;
+            const int s0 = g < ng ? a.grp_start[g] : 0;
+            const int cnt = g < ng ? max(0, min(a.grp_start[g + 1], (int) a.cap_entries) - s0) : 0;
+            const int np = (cnt + NTOK - 1) / NTOK;
+            int x = np;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_up_sync(kFull, x, o);
+                if (lane >= o) x += y;
+            }
+            if (lane == 31) sh[warp] = x;
+            __syncthreads();
+            int before = s_base;
+            for (int w = 0; w < warp; ++w) before += sh[w];
+            for (int p = 0; p < np; ++p) items[before + x - np + p] = make_int2(g, s0 + p * NTOK);
+            __syncthreads();
+            if (threadIdx.x == 255) s_base = before + x;
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) *n_items = s_base;
+        return;
+    }
+    const int i = blockIdx.x * 8 + warp;   // image row
+    const int n_img = FROM_H ? total : (a.n_x_rows > 0 ? a.n_x_rows : total);
+    if (i >= n_img) return;
     const int64_t K = FROM_H ? a.L.n_ff : a.L.n_embd;
-    const int64_t row = FROM_H ? (int64_t) e : (int64_t) a.ent_tok[e];
+    const int64_t row = FROM_H ? (int64_t) i : (a.n_x_rows > 0 ? (int64_t) i : (int64_t) a.ent_tok[i]);
     const void* src = FROM_H ? (const void*) a.h : a.x;
     const int kind = FROM_H ? BSX_X_F32 : a.x_kind;
+    const int n_sb = (int) (K >> 4);
     float amax = 0.f;
-    for (int c = threadIdx.x; c < K; c += 256) amax = fmaxf(amax, fabsf(load_x(src, kind, row, K, c)));
-    amax = warp_max_xor(amax);
-    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float m = 0.f;
-        for (int i = 0; i < 8; ++i) m = fmaxf(m, s_red[i]);
-        int ex = 0;
-        float s = 1.f, iv = 1.f;
-        if (m > 0.f && m <= 3.0e38f) {
-            frexpf(m, &ex);                          // m = f 2^ex, f in [0.5, 1)
-            ex = max(-100, min(100, 14 - ex));
-            s = ldexpf(1.f, ex);
-            iv = ldexpf(1.f, -ex);
-        }
-        s_scale = s;
-        inv[e] = iv;
+    for (int sb = lane; sb < n_sb; sb += 32) {
+        float v[16];
+        load16(src, kind, row, K, sb, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
     }
-    __syncthreads();
-    const float s = s_scale;
-    __half* out = img + (size_t) e * K * TERMS;
-    for (int c = threadIdx.x; c < K; c += 256) {
-        const float v = load_x(src, kind, row, K, c) * s;
-        const __half hi = __float2half_rn(v);
-        const int at = image_index(c);
-        out[at] = hi;
-        if (TERMS == 2) out[K + at] = __float2half_rn(v - __half2float(hi));
+    amax = warp_max_xor(amax);
+    int ex = 0;
+    float s = 1.f, iv = 1.f;
+    if (amax > 0.f && amax <= 3.0e38f) {
+        frexpf(amax, &ex);                          // amax = f 2^ex, f in [0.5, 1)
+        ex = max(-100, min(100, 14 - ex));
+        s = ldexpf(1.f, ex);
+        iv = ldexpf(1.f, -ex);
+    }
+    if (lane == 0) inv[i] = iv;
+    uint4* out = reinterpret_cast<uint4*>(img + (size_t) i * K * TERMS);
+    for (int sb = lane; sb < n_sb; sb += 32) {
+        float v[16];
+        load16(src, kind, row, K, sb, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] *= s;
+        // pieces (gran, 0, t) and (gran, 1, t): values {0,8,1,9,2,10,3,11} and {4,12,5,13,6,14,7,15}
+        const int piece = ((sb >> 2) * 2) * 4 + (sb & 3);
+        out[piece] = make_uint4(pack_half2(v[0], v[8]), pack_half2(v[1], v[9]), pack_half2(v[2], v[10]), pack_half2(v[3], v[11]));
+        out[piece + 4] = make_uint4(pack_half2(v[4], v[12]), pack_half2(v[5], v[13]), pack_half2(v[6], v[14]), pack_half2(v[7], v[15]));
+        if (TERMS == 2) {
+            float r[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = v[j] - __half2float(__float2half_rn(v[j]));
+            uint4* lo = out + (K >> 3);
+            lo[piece] = make_uint4(pack_half2(r[0], r[8]), pack_half2(r[1], r[9]), pack_half2(r[2], r[10]), pack_half2(r[3], r[11]));
+            lo[piece + 4] = make_uint4(pack_half2(r[4], r[12]), pack_half2(r[5], r[13]), pack_half2(r[6], r[14]), pack_half2(r[7], r[15]));
+        }
     }
 }
 
@@ -147,7 +226,8 @@ __global__ void __launch_bounds__(256) prep_image_kernel(ExpertArgs a, __half* _
 // TERMS = 1: 8 entries a pass; TERMS = 2: 4 entries a pass, each as hi + lo fp16 columns.
 template <int MODE, int TERMS>
 __global__ void __launch_bounds__(kThreads, 2)
-nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __restrict__ inv, int tiles_per_warp) {
+nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __restrict__ inv, const int2* __restrict__ items,
+                 const int* __restrict__ n_items, int tiles_per_warp) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int64_t K = MODE == MODE_GU ? a.L.n_embd : a.L.n_ff;
     const int n_gran = (int) (K >> 6);                       // 64-column granules
@@ -162,6 +242,7 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
     const uint32_t xs_s = (uint32_t) __cvta_generic_to_shared(xs);
     constexpr int NTOK = kCols / TERMS;
 
+    __shared__ int s_ir[kCols];                        // image row of each entry of the pass
     lut[threadIdx.x] = scale_pair_bits(threadIdx.x);   // 256 threads, 256 entries; the first barrier below publishes it
     if (threadIdx.x < 4) zero[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
 
@@ -187,11 +268,13 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
         cp_dst[j] = (uint32_t) (cp_row[j] * kRowBytes + cp_off[j]);
     }
 
-    const int ng = min(*a.n_groups, (int) a.cap_groups);
-    for (int grp = blockIdx.y; grp < ng; grp += gridDim.y) {
+    const int n_it = *n_items;
+    for (int item = blockIdx.y; item < n_it; item += gridDim.y) {
+        const int2 it = items[item];
+        const int grp = it.x;
         const uint8_t* blob = reinterpret_cast<const uint8_t*>(a.grp_ptr[grp]);
         const float* tail = reinterpret_cast<const float*>(blob + a.L.bytes - 16);
-        const int e0 = a.grp_start[grp], e1 = min(a.grp_start[grp + 1], (int) a.cap_entries);
+        const int e1 = min(a.grp_start[grp + 1], (int) a.cap_entries);
         // global address of this lane's pieces at chunk 0
         const uint8_t* src[5];
 #pragma unroll
@@ -224,16 +307,19 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
             }
             cp_async_commit();
         };
-        // passes (batches of NTOK entries) of one group are dealt round-robin to the blocks along grid z
-        for (int eb = e0 + (int) blockIdx.z * NTOK; eb < e1; eb += NTOK * (int) gridDim.z) {
+        {
+            const int eb = it.y;
             const int ntok = min(NTOK, e1 - eb);
             const int ncol = ntok * TERMS;
             __syncthreads();   // the previous pass has finished reading xs
+            if (threadIdx.x < ntok)
+                s_ir[threadIdx.x] = (MODE == MODE_GU && a.n_x_rows > 0) ? a.ent_tok[eb + threadIdx.x] : eb + (int) threadIdx.x;
+            __syncthreads();
             // the activation columns: image piece q of column c goes to piece ((q >> 2) * 8 + c) * 4 + (q & 3) of xs
             for (int i = threadIdx.x; i < ncol * pieces_per_col; i += kThreads) {
                 const int c = i / pieces_per_col, q = i - c * pieces_per_col;
-                const int ent = eb + c / TERMS, term = c % TERMS;
-                const __half* sp = img + ((size_t) ent * TERMS + term) * K + (size_t) q * 8;
+                const int ir = s_ir[c / TERMS], term = c % TERMS;
+                const __half* sp = img + ((size_t) ir * TERMS + term) * K + (size_t) q * 8;
                 cp_async16(xs_s + (uint32_t) ((((q >> 2) * kCols + c) * 4 + (q & 3)) * 16), sp);
             }
             cp_async_commit();
@@ -300,12 +386,12 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
                         for (int q = 0; q < 2; ++q) {
                             const int j = 2 * t + q;
                             if (j < ntok) {
-                                const float f = inv[eb + j];
+                                const float f = inv[s_ir[j]];
                                 a.h[(size_t) (eb + j) * a.L.n_ff + rt + g] = swiglu((q ? c1 : c0) * f * sg, (q ? c3 : c2) * f * su, a.L);
                             }
                         }
                     } else if (t < ntok) {
-                        const float f = inv[eb + t];
+                        const float f = inv[s_ir[t]];
                         a.h[(size_t) (eb + t) * a.L.n_ff + rt + g] = swiglu((c0 + c1) * f * sg, (c2 + c3) * f * su, a.L);
                     }
                 } else {
@@ -315,14 +401,14 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
                         for (int q = 0; q < 2; ++q) {
                             const int j = 2 * t + q;
                             if (j < ntok) {
-                                const float f = inv[eb + j] * sd;
+                                const float f = inv[s_ir[j]] * sd;
                                 const int64_t o = (int64_t) a.ent_dst[eb + j] * a.L.n_embd + rt + g;
                                 store_out(a.out, a.out_kind, o, (q ? c1 : c0) * f);
                                 store_out(a.out, a.out_kind, o + 8, (q ? c3 : c2) * f);
                             }
                         }
                     } else if (t < ntok) {
-                        const float f = inv[eb + t] * sd;
+                        const float f = inv[s_ir[t]] * sd;
                         const int64_t o = (int64_t) a.ent_dst[eb + t] * a.L.n_embd + rt + g;
                         store_out(a.out, a.out_kind, o, (c0 + c1) * f);
                         store_out(a.out, a.out_kind, o + 8, (c2 + c3) * f);
@@ -339,7 +425,7 @@ size_t smem_bytes(int64_t K) { return (size_t) K * kCols * 2 + 1152 + (size_t) k
 size_t align256(size_t v) { return (v + 255) & ~(size_t) 255; }
 
 template <int MODE, int TERMS>
-int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, cudaStream_t st) {
+int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, const int2* items, const int* n_items, cudaStream_t st) {
     const int64_t K = MODE == MODE_GU ? a.L.n_embd : a.L.n_ff;
     const size_t smem = smem_bytes(K);
     static bool configured[64] = {};
@@ -361,15 +447,10 @@ int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, cudaStr
     const int64_t n_blocks = (n_tiles + tpw0 - 1) / tpw0;
     const int tpw = (int) ((n_tiles + n_blocks - 1) / n_blocks);
     const int per_block = (int) tile_rows * tpw;
-    const unsigned gy = (unsigned) (a.cap_groups < 1 ? 1 : a.cap_groups > 1024 ? 1024 : a.cap_groups);
-    // blocks along z share a group's passes: about four passes' worth of blocks per possible group, never more than the
-    // passes the call can have
     constexpr int NTOK = kCols / TERMS;
-    const int64_t max_passes = (a.cap_entries + NTOK - 1) / NTOK;
-    int64_t gz = (4 * a.cap_entries + (int64_t) NTOK * gy - 1) / ((int64_t) NTOK * gy);
-    gz = gz < 1 ? 1 : gz > 16 ? 16 : gz;
-    gz = gz > max_passes ? max_passes : gz;
-    nvfp4_mma_kernel<MODE, TERMS><<<dim3((unsigned) ((rows + per_block - 1) / per_block), gy, (unsigned) gz), kThreads, smem, st>>>(a, img, inv, tpw);
+    const int64_t cap_items = a.cap_groups + a.cap_entries / NTOK + 1;
+    const unsigned gy = (unsigned) (cap_items > 4096 ? 4096 : cap_items);
+    nvfp4_mma_kernel<MODE, TERMS><<<dim3((unsigned) ((rows + per_block - 1) / per_block), gy), kThreads, smem, st>>>(a, img, inv, items, n_items, tpw);
     return launch_status();
 }
 
@@ -377,7 +458,9 @@ int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, cudaStr
 
 // scratch beyond the SwiGLU buffer: the x images (up to two fp16 terms), the h images (two terms), the inverse row scales
 size_t experts_mma_scratch_bytes(int64_t cap_entries, int64_t n_embd, int64_t n_ff) {
-    return align256((size_t) cap_entries * n_embd * 4) + align256((size_t) cap_entries * n_ff * 4) + 2 * align256((size_t) cap_entries * 4);
+    // the pass list: at most one pass per entry, 8 bytes each, plus its count
+    return align256((size_t) cap_entries * n_embd * 4) + align256((size_t) cap_entries * n_ff * 4) + 2 * align256((size_t) cap_entries * 4) +
+           align256((size_t) (cap_entries + 1) * 8 + 16);
 }
 
 int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st) {
@@ -394,21 +477,25 @@ int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st) {
     p += align256((size_t) a.cap_entries * L.n_ff * 4);
     float* xinv = reinterpret_cast<float*>(p);
     float* hinv = xinv + align256((size_t) a.cap_entries * 4) / 4;
+    int* n_items = reinterpret_cast<int*>(hinv + align256((size_t) a.cap_entries * 4) / 4);
+    int2* items = reinterpret_cast<int2*>(n_items + 4);
     const int phase = experts_phase();
-    const unsigned nb = (unsigned) a.cap_entries;
+    // a warp per image row, 8 a block, plus the block that lists the passes
+    const int64_t x_rows = a.n_x_rows > 0 ? a.n_x_rows : a.cap_entries;
+    const unsigned nbx = (unsigned) ((x_rows + 7) / 8 + 1), nbh = (unsigned) ((a.cap_entries + 7) / 8 + 1);
     int32_t rc = BSX_OK;
     if (phase != 2) {
         if (a.x_kind == BSX_X_BF16) {
-            prep_image_kernel<false, 1><<<nb, 256, 0, st>>>(a, ximg, xinv);
-            rc = launch<MODE_GU, 1>(a, ximg, xinv, st);
+            prep_image_kernel<false, 1><<<nbx, 256, 0, st>>>(a, ximg, xinv, items, n_items);
+            rc = launch<MODE_GU, 1>(a, ximg, xinv, items, n_items, st);
         } else {
-            prep_image_kernel<false, 2><<<nb, 256, 0, st>>>(a, ximg, xinv);
-            rc = launch<MODE_GU, 2>(a, ximg, xinv, st);
+            prep_image_kernel<false, 2><<<nbx, 256, 0, st>>>(a, ximg, xinv, items, n_items);
+            rc = launch<MODE_GU, 2>(a, ximg, xinv, items, n_items, st);
         }
     }
     if (rc != BSX_OK || phase == 1) return rc;
-    prep_image_kernel<true, 2><<<nb, 256, 0, st>>>(a, himg, hinv);
-    return launch<MODE_DOWN, 2>(a, himg, hinv, st);
+    prep_image_kernel<true, 2><<<nbh, 256, 0, st>>>(a, himg, hinv, items, n_items);
+    return launch<MODE_DOWN, 2>(a, himg, hinv, items, n_items, st);
 }
 
 }  // namespace bsx

@@ -44,7 +44,7 @@ __device__ __forceinline__ float4 load_x4(const void* x, size_t row, int n_embd,
 }
 
 template <int NV, int G, bool BF16>
-__global__ void __launch_bounds__(kLogitThreads)
+__global__ void __launch_bounds__(kLogitThreads, (NV <= 4 ? 2 : 1))
 router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate, int n_embd, int n_expert, int n_tokens,
                      int tok_per_block, float* __restrict__ logits) {
     __shared__ float red[G][kTokTile][kLogitThreads / 32];

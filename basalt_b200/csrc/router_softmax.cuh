@@ -40,25 +40,34 @@ __global__ void __launch_bounds__(256) BSX_SOFTMAX_KERNEL(const float* __restric
 #pragma unroll
     for (int i = 0; i < MAXR; ++i)
         if (i < reg) { v[i] *= rcp; if (isnan(v[i])) v[i] = -FLT_MAX; }
+    // k argmax passes (value descending, index ascending).  Floats are compared through an order-preserving map to
+    // unsigned integers, so the warp-wide maximum and the lowest index holding it are one redux instruction each; a lane
+    // keeps the maximum of its own values and only the winning lane rescans.  (+0 and -0 would order differently from the
+    // float compare, but a probability here is +0 at the lowest, and the markers -FLT_MAX and -inf are distinct values.)
     float selected = 0.0f, selected_sum = 0.0f;
-    for (int rank = 0; rank < k; ++rank) {
-        float best = v[0];
-        int ex = lane;
+    auto key = [](float f) { const uint32_t b = __float_as_uint(f); return (b & 0x80000000u) ? ~b : (b | 0x80000000u); };
+    uint32_t lmax = 0u;
+    int lidx = 0;
+    auto rescan = [&]() {
+        lmax = key(v[0]);
+        lidx = 0;
 #pragma unroll
         for (int i = 1; i < MAXR; ++i)
-            if (i < reg && v[i] > best) { best = v[i]; ex = lane + i * 32; }
-#pragma unroll
-        for (int m = 16; m; m >>= 1) {
-            const float ob = __shfl_xor_sync(kFull, best, m);
-            const int oi = __shfl_xor_sync(kFull, ex, m);
-            if (ob > best || (ob == best && oi < ex)) { best = ob; ex = oi; }
-        }
+            if (i < reg && key(v[i]) > lmax) { lmax = key(v[i]); lidx = i; }
+    };
+    rescan();
+    for (int rank = 0; rank < k; ++rank) {
+        const uint32_t gmax = __reduce_max_sync(kFull, lmax);
+        const int ex = (int) __reduce_min_sync(kFull, lmax == gmax ? (unsigned) (lane + lidx * 32) : 0xFFFFFFFFu);
+        float best = 0.f;
         if ((ex & 31) == lane) {
 #pragma unroll
             for (int i = 0; i < MAXR; ++i)
-                if (i == (ex >> 5)) v[i] = -INFINITY;
+                if (i == (ex >> 5)) { best = v[i]; v[i] = -INFINITY; }
             selected_sum += best;
+            rescan();
         }
+        best = __shfl_sync(kFull, best, ex & 31);
         if (lane == 0) ids[t * k + rank] = ex;
         if (rank == lane) selected = best;
     }

@@ -249,16 +249,16 @@ class MoELayer:
         if self.fused_shared:
             check("bsx_moe_plan_shared", lib.bsx_moe_plan_shared(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), self.shared_blob.data_ptr(),
                                                                  _p(self.ptr), _p(self.start), _p(self.n_groups), _p(self.dst), _p(self.tok), st))
-            check("bsx_experts_grouped", lib.bsx_experts_grouped(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups), _p(self.dst),
-                                                                 _p(self.tok), min(n, a.n_expert) + 1, n + T, _p(x), kind, _p(self.scratch),
-                                                                 _p(self.rows), OUT_F32, st))
+            check("bsx_experts_grouped", lib.bsx_experts_grouped_rows(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
+                                                                      _p(self.dst), _p(self.tok), min(n, a.n_expert) + 1, n + T, _p(x), kind, T,
+                                                                      _p(self.scratch), _p(self.rows), OUT_F32, st))
             shared = self.rows[n:n + T]
         else:
             check("bsx_moe_plan", lib.bsx_moe_plan(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), _p(self.ptr), _p(self.start),
                                                     _p(self.n_groups), _p(self.dst), _p(self.tok), st))
-            check("bsx_experts_grouped", lib.bsx_experts_grouped(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups), _p(self.dst),
-                                                                 _p(self.tok), min(n, a.n_expert), n, _p(x), kind, _p(self.scratch),
-                                                                 _p(self.rows), OUT_F32, st))
+            check("bsx_experts_grouped", lib.bsx_experts_grouped_rows(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
+                                                                      _p(self.dst), _p(self.tok), min(n, a.n_expert), n, _p(x), kind, T,
+                                                                      _p(self.scratch), _p(self.rows), OUT_F32, st))
             if self.shared_blob is not None:
                 if self._s_T != T:
                     self.s_start.copy_(torch.tensor([0, T, T], dtype=torch.int32))

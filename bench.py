@@ -319,8 +319,9 @@ def instrumented_pass(layers, xs, xr, stream, steps, L):
         ev[2].record(stream)
         for phase in (1, 2):
             lib.bsx_experts_set_phase(phase)
-            capi.check("experts", lib.bsx_experts_grouped(C.byref(ly.L), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
-                                                           min(n, a.n_expert) + 1, n + T, _p(x), _x_kind(x), _p(ly.scratch), _p(ly.rows), capi.OUT_F32, st))
+            capi.check("experts", lib.bsx_experts_grouped_rows(C.byref(ly.L), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
+                                                                min(n, a.n_expert) + 1, n + T, _p(x), _x_kind(x), T, _p(ly.scratch), _p(ly.rows),
+                                                                capi.OUT_F32, st))
             ev[2 + phase].record(stream)
         lib.bsx_experts_set_phase(0)
         capi.check("combine", lib.bsx_combine(_p(ly.rows), None, _p(ly.w), _p(ly.rows[n:n + T]), None, T, a.k, L.n_embd, _p(ly.y), st))

@@ -171,6 +171,14 @@ BSX_API int32_t bsx_experts_grouped(const bsx_expert_layout* layout, const unsig
                             int64_t cap_entries, const void* x, int32_t x_kind, void* scratch, void* out, int32_t out_kind,
                             void* stream);
 
+/* bsx_experts_grouped for a caller that knows how many rows x has (every ent_tok value is below n_x_rows): the fp16 images
+ * the tensor-core path makes of the activations are then built once per row instead of once per entry.  Same results.
+ * No counterpart in the reference (its q8_1 rows are made by the caller, once per token, for the same reason). */
+BSX_API int32_t bsx_experts_grouped_rows(const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
+                                         const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
+                                         int64_t cap_entries, const void* x, int32_t x_kind, int32_t n_x_rows, void* scratch, void* out,
+                                         int32_t out_kind, void* stream);
+
 /* The bench only: which launches bsx_experts_grouped makes (0 all, 1 gate/up + SwiGLU, 2 down), so each stage can be timed
  * alone.  Mirrors native_expert_set_mode's phase (iq_kernels.hpp:113-115).  Process-wide; set it back to 0. */
 BSX_API void bsx_experts_set_phase(int32_t phase);
