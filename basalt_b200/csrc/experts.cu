@@ -106,6 +106,21 @@ combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ slot,
     reinterpret_cast<float4*>(y + (size_t) t * H)[c4] = s;
 }
 
+// the one-group plan of a dense gated MLP (a shared expert): Basalt's gated_mlp_plan_kernel, src/kernels/cuda/iq_kernels.cu:3414-3426
+__global__ void __launch_bounds__(128)
+gated_mlp_plan_kernel(unsigned long long blob, int n_tok, unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* idx) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        ptr[0] = blob;
+        start[0] = 0;
+        start[1] = n_tok;
+        start[2] = n_tok;
+        *n_groups = 1;
+    }
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_tok; i += gridDim.x * blockDim.x) idx[i] = i;
+}
+
+size_t gated_plan_bytes(int64_t cap_tok) { return ((size_t) (64 + cap_tok * 4) + 255) & ~(size_t) 255; }
+
 size_t row_bytes(int type, int64_t n) {
     if (!type_supported(type) || n <= 0 || n % block_values(type)) return 0;
     return (size_t) (n / block_values(type)) * (size_t) block_bytes(type);
@@ -246,6 +261,30 @@ extern "C" int32_t bsx_experts_grouped_rows(const bsx_expert_layout* layout, con
     if (n_x_rows < 0 || n_x_rows > cap_entries) n_x_rows = 0;   // more rows than entries: per-entry images are the cheaper form
     return experts_grouped_impl(n_x_rows, layout, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups, cap_entries, x, x_kind, scratch,
                                 out, out_kind, stream);
+}
+
+extern "C" size_t bsx_gated_mlp_scratch_bytes(const bsx_expert_layout* L, int64_t cap_tok) {
+    const size_t e = bsx_expert_scratch_bytes(L, cap_tok);
+    return e ? e + gated_plan_bytes(cap_tok) : 0;
+}
+
+extern "C" int32_t bsx_gated_mlp(const bsx_expert_layout* layout, const void* blob, int32_t n_tok, int64_t cap_tok, const void* x,
+                                 int32_t x_kind, void* scratch, void* out, int32_t out_kind, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (!layout || !blob || !aligned(scratch, 16)) return BSX_E_POINTER;
+    if (n_tok < 0 || n_tok > cap_tok) return BSX_E_GEOMETRY;
+    if (n_tok == 0) return BSX_OK;
+    uint8_t* p = static_cast<uint8_t*>(scratch);
+    unsigned long long* ptr = reinterpret_cast<unsigned long long*>(p);
+    int32_t* start = reinterpret_cast<int32_t*>(p + 16);
+    int32_t* n_groups = reinterpret_cast<int32_t*>(p + 32);
+    int32_t* idx = reinterpret_cast<int32_t*>(p + 64);
+    gated_mlp_plan_kernel<<<(unsigned) ((n_tok + 127) / 128), 128, 0, (cudaStream_t) stream>>>((unsigned long long) (uintptr_t) blob, n_tok, ptr, start,
+                                                                                             n_groups, idx);
+    const int32_t rc = launch_status();
+    if (rc != BSX_OK) return rc;
+    return experts_grouped_impl(n_tok, layout, ptr, start, n_groups, idx, idx, 1, n_tok, x, x_kind, p + gated_plan_bytes(cap_tok), out, out_kind,
+                                stream);
 }
 
 extern "C" int32_t bsx_combine(const float* rows, const int32_t* slot, const float* weights, const float* shared,

@@ -180,6 +180,19 @@ def native_expert_grouped(L: ExpertLayout, grp_ptr, grp_start, n_groups, ent_dst
     return out
 
 
+def gated_mlp(L: ExpertLayout, blob, x, cap_tok: Optional[int] = None, out=None, scratch=None, stream=None):
+    """basalt::kernels::gated_mlp_clamped (iq_kernels.hpp:93-98): a dense gated MLP (a shared expert) over the rows of x; the
+    SwiGLU limit is the layout's."""
+    n = x.shape[0]
+    cap = cap_tok or n
+    out = torch.empty((n, L.n_embd), dtype=torch.float32, device=x.device) if out is None else out
+    if scratch is None:
+        scratch = torch.empty(capi.lib().bsx_gated_mlp_scratch_bytes(C.byref(L), cap), dtype=torch.uint8, device=x.device)
+    check("bsx_gated_mlp", capi.lib().bsx_gated_mlp(C.byref(L), _p(blob), n, cap, _p(x), _x_kind(x), _p(scratch), _p(out),
+                                                     OUT_BF16 if out.dtype == torch.bfloat16 else OUT_F32, _stream(stream)))
+    return out
+
+
 def moe_combine(rows, slot, weights, shared=None, shared_gate=None, y=None, stream=None):
     """native_moe_combine_multi (native_moe.hpp:10-15) / prompt-path moe_combine (prefill/kernels.cu:705-709)."""
     T, k = weights.shape

@@ -179,6 +179,13 @@ BSX_API int32_t bsx_experts_grouped_rows(const bsx_expert_layout* layout, const 
                                          int64_t cap_entries, const void* x, int32_t x_kind, int32_t n_x_rows, void* scratch, void* out,
                                          int32_t out_kind, void* stream);
 
+/* ---- a10: a dense gated MLP (a shared expert) on n_tok rows: row t of out is token t's unweighted output.  Replaces
+ * gated_mlp_clamped / gated_mlp_scratch_bytes (iq_kernels.hpp:93-98, iq_kernels.cu:3413-3447): the one-group plan is built on
+ * the device, then the grouped experts run.  The SwiGLU limit rides in the layout.  scratch: bsx_gated_mlp_scratch_bytes. */
+BSX_API size_t bsx_gated_mlp_scratch_bytes(const bsx_expert_layout* layout, int64_t cap_tok);
+BSX_API int32_t bsx_gated_mlp(const bsx_expert_layout* layout, const void* blob, int32_t n_tok, int64_t cap_tok, const void* x,
+                              int32_t x_kind, void* scratch, void* out, int32_t out_kind, void* stream);
+
 /* The bench only: which launches bsx_experts_grouped makes (0 all, 1 gate/up + SwiGLU, 2 down), so each stage can be timed
  * alone.  Mirrors native_expert_set_mode's phase (iq_kernels.hpp:113-115).  Process-wide; set it back to 0. */
 BSX_API void bsx_experts_set_phase(int32_t phase);
