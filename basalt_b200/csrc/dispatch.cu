@@ -221,6 +221,12 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsi
     }
 }
 
+// Scratch of bsx_dispatch_static: the [expert][chunk] count table for up to kStaticMaxPairs pairs over up to kMaxExpert
+// experts (1 MiB), resident on every device that loads this library.  Host code may only take its address
+// (cudaGetSymbolAddress); the name itself is not a device pointer on the host side.
+constexpr int64_t kStaticMaxPairs = 65536;
+static __device__ __align__(256) int32_t g_static_dispatch_tbl[kMaxExpert * (kStaticMaxPairs / kChunk)];
+
 }  // namespace
 }  // namespace bsx
 
@@ -230,6 +236,34 @@ extern "C" size_t bsx_dispatch_scratch_bytes(int64_t n_pairs, int32_t E) {
     if (n_pairs < 0 || E < 1) return 0;
     const int64_t nc = n_chunks_of(n_pairs > 0 ? n_pairs : 1);
     return (size_t) E * (size_t) nc * sizeof(int32_t) + 256;
+}
+
+// Device address of the static table on the current device; looked up once per device, with that device current.
+static int32_t* static_dispatch_table(int32_t* status) {
+    static int32_t* cached[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { *status = (int32_t) e; return nullptr; }
+    if (dev < 0 || dev >= 64) { *status = (int32_t) cudaErrorInvalidDevice; return nullptr; }
+    if (!cached[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_dispatch_tbl);
+        if (e != cudaSuccess) { *status = (int32_t) e; return nullptr; }
+        cached[dev] = static_cast<int32_t*>(p);
+    }
+    *status = BSX_OK;
+    return cached[dev];
+}
+
+extern "C" int32_t bsx_dispatch_static(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t E, int32_t* cnt, int32_t* off,
+                                       int32_t* slot, int32_t* src, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (E < 1 || E > kMaxExpert || k < 1 || n_pairs < 0) return BSX_E_GEOMETRY;
+    if (n_pairs > kStaticMaxPairs) return BSX_E_LIMIT;   // beyond the resident table: use bsx_dispatch with caller scratch
+    int32_t status = BSX_OK;
+    int32_t* tbl = static_dispatch_table(&status);
+    if (!tbl) return status;
+    return bsx_dispatch(ids, n_pairs, k, E, cnt, off, slot, src, 0, nullptr, nullptr, tbl, stream);
 }
 
 extern "C" int32_t bsx_dispatch(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t E, int32_t* cnt, int32_t* off,

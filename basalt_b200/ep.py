@@ -1,0 +1,148 @@
+"""Expert parallelism for the MoE layer: one process per GPU, experts sharded in contiguous blocks, tokens data-parallel,
+rows exchanged by an all-to-all over NCCL (NVLink / NVSwitch) before and after the local grouped experts.
+
+The reference shards experts across cards too ("expert tiers"), but moves rows through mapped host memory and doorbells
+(Basalt: include/basalt/models/qwen4exp/kernels/dec_moe.hpp:1-11, src/core/peer_experts.cpp:420-548); this replaces that
+transport with collectives and keeps its correctness argument - an expert gives the same rows on whichever card holds it
+(include/basalt/core/peer_experts.hpp:11-12).
+
+Step on rank r of N (router weights replicated, experts [r E/N, (r+1) E/N) local):
+  1. route the rank's own tokens; stable dispatch by expert id (rows come out grouped by destination rank);
+  2. all-gather the per-expert counts, from which every rank derives both directions' split sizes and its receive-side
+     group plan (entries ordered by source rank, then pair order: deterministic);
+  3. gather the activation rows in send order and all-to-all them;
+  4. run the local grouped experts over the received rows (they sit in local HBM: no peer-memory loads in any kernel);
+  5. all-to-all the result rows back (the mirror of 3) and combine them, with the locally computed shared expert.
+
+The planning functions are pure numpy so that the same code is exercised by the CPU tests (gloo, world_size 2) and the
+GPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import numpy as np
+
+
+def ep_partition(n_expert: int, world: int) -> np.ndarray:
+    """first expert of each rank's block (world + 1 entries); blocks are contiguous and equal."""
+    assert n_expert % world == 0, "experts must divide evenly over the ranks"
+    return np.arange(world + 1, dtype=np.int64) * (n_expert // world)
+
+
+def ep_splits(cnt_all: np.ndarray, rank: int) -> Tuple[np.ndarray, np.ndarray]:
+    """cnt_all [N][E] = every rank's per-expert pair counts.  Returns (send_splits, recv_splits): rows this rank sends to /
+    receives from each rank."""
+    world, E = cnt_all.shape
+    first = ep_partition(E, world)
+    send = np.array([cnt_all[rank, first[d]:first[d + 1]].sum() for d in range(world)], np.int64)
+    recv = np.array([cnt_all[s, first[rank]:first[rank + 1]].sum() for s in range(world)], np.int64)
+    return send, recv
+
+
+def ep_recv_plan(cnt_all: np.ndarray, rank: int):
+    """The receive-side group plan.  Rows arrive ordered by (source rank, expert, pair order).  Returns
+    (experts, start, rows): the local experts that received rows (ascending), start[g] = first entry of group g
+    (len(experts) + 1 entries), rows[entry] = index of the entry's row in the receive buffer.  Inside a group the entries
+    run by source rank, then in the source's pair order."""
+    world, E = cnt_all.shape
+    first = ep_partition(E, world)
+    lo, hi = int(first[rank]), int(first[rank + 1])
+    c = cnt_all[:, lo:hi].astype(np.int64)                       # [src][local expert]
+    src_base = np.concatenate([[0], np.cumsum(c.sum(1))])[:-1]   # first receive row of each source
+    within = np.cumsum(c, axis=1) - c                            # offset of expert e inside source s's rows
+    tot = c.sum(0)
+    experts = np.nonzero(tot)[0]
+    start = np.concatenate([[0], np.cumsum(tot[experts])]).astype(np.int32)
+    rows = np.empty(int(start[-1]), np.int32)
+    at = 0
+    for e in experts:
+        for s in range(world):
+            n = int(c[s, e])
+            if n:
+                b = int(src_base[s] + within[s, e])
+                rows[at:at + n] = np.arange(b, b + n, dtype=np.int32)
+                at += n
+    return (experts + lo).astype(np.int32), start, rows
+
+
+class EPMoELayer:
+    """The expert-parallel layer on one rank.  `blobs` holds this rank's experts only ([E/N][stride] uint8); the router gate,
+    bias and the shared expert are replicated."""
+
+    def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, shared_blob=None, max_tokens: int = 64,
+                 max_recv_rows: Optional[int] = None, group=None):
+        import torch
+        import torch.distributed as dist
+        from . import moe
+        self.torch, self.dist, self.moe = torch, dist, moe
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.E, self.L, self.args = n_expert_total, layout, args
+        self.first = ep_partition(n_expert_total, self.world)
+        self.gate_w, self.bias, self.blobs, self.shared_blob = gate_w, bias, blobs, shared_blob
+        dev = blobs.device
+        self.dev = dev
+        El, stride = blobs.shape
+        assert El == n_expert_total // self.world
+        self.blob_addr = blobs.data_ptr() + np.arange(El, dtype=np.int64) * stride
+        n = max_tokens * args.k
+        self.max_tokens, self.n_pairs = max_tokens, n
+        self.max_recv = max_recv_rows or n * self.world
+        f32, i32 = torch.float32, torch.int32
+        self.logits = torch.empty((max_tokens, n_expert_total), dtype=f32, device=dev)
+        self.ids = torch.empty((max_tokens, args.k), dtype=i32, device=dev)
+        self.w = torch.empty((max_tokens, args.k), dtype=f32, device=dev)
+        self.cnt_all = torch.empty((self.world, n_expert_total), dtype=i32, device=dev)
+        self.rows_back = torch.empty((n, layout.n_embd), dtype=f32, device=dev)
+        self.y = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
+        self.scratch = torch.empty(moe.native_expert_scratch_bytes(layout, self.max_recv), dtype=torch.uint8, device=dev)
+        self.side = torch.cuda.Stream(device=dev)
+        if shared_blob is not None:
+            self.s_out = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
+            self.s_scratch = torch.empty(C.c_size_t(moe.capi.lib().bsx_gated_mlp_scratch_bytes(C.byref(layout), max_tokens)).value,
+                                         dtype=torch.uint8, device=dev)
+
+    def forward(self, x):
+        torch, dist, moe = self.torch, self.dist, self.moe
+        a, L = self.args, self.L
+        T = x.shape[0]
+        n = T * a.k
+        cur = torch.cuda.current_stream()
+        # 1. route and dispatch the rank's own tokens
+        moe.router(x, self.gate_w, self.bias, a, self.logits, self.ids, self.w) if x.dtype == torch.float32 else \\
+            moe.router_x(x, self.gate_w, self.bias, a, self.logits, self.ids, self.w)
+        cnt, off, slot, src, _, _ = moe.dispatch(self.ids[:T].reshape(-1), a.k, self.E)
+        # the shared expert runs beside the exchange on its own stream
+        if self.shared_blob is not None:
+            self.side.wait_stream(cur)
+            with torch.cuda.stream(self.side):
+                moe.gated_mlp(L, self.shared_blob, x, cap_tok=self.max_tokens, out=self.s_out[:T], scratch=self.s_scratch)
+        # 2. counts of every rank -> split sizes and the receive plan (one device-to-host read per step)
+        dist.all_gather_into_tensor(self.cnt_all, cnt, group=self.group)
+        cnt_all = self.cnt_all.cpu().numpy()
+        send, recv = ep_splits(cnt_all, self.rank)
+        experts, start, rows = ep_recv_plan(cnt_all, self.rank)
+        n_recv = int(recv.sum())
+        assert n_recv <= self.max_recv, "receive buffer too small for this routing"
+        # 3. rows in send order, then the all-to-all
+        xs = moe.gather_rows(x, src[:n])
+        xr = torch.empty((max(n_recv, 1), L.n_embd), dtype=x.dtype, device=self.dev)
+        dist.all_to_all_single(xr[:n_recv], xs, recv.tolist(), send.tolist(), group=self.group)
+        # 4. local grouped experts over the received rows; output row = receive row
+        out = torch.empty((max(n_recv, 1), L.n_embd), dtype=torch.float32, device=self.dev)
+        if n_recv:
+            g = len(experts)
+            ptr = torch.from_numpy(self.blob_addr[experts - int(self.first[self.rank])]).to(self.dev)
+            st = torch.from_numpy(np.concatenate([start, start[-1:]])).to(self.dev)
+            ent = torch.from_numpy(rows).to(self.dev)
+            ng = torch.tensor([g], dtype=torch.int32, device=self.dev)
+            moe.native_expert_grouped(L, ptr, st, ng, ent, ent, g, n_recv, xr, self.scratch, out, n_x_rows=n_recv)
+        # 5. results back to their tokens' ranks (the mirror exchange), then the combine
+        dist.all_to_all_single(self.rows_back[:n], out[:n_recv], send.tolist(), recv.tolist(), group=self.group)
+        shared = None
+        if self.shared_blob is not None:
+            cur.wait_stream(self.side)
+            shared = self.s_out[:T]
+        return moe.moe_combine(self.rows_back[:n], slot.reshape(T, a.k), self.w[:T], shared, None, self.y[:T])

@@ -116,6 +116,20 @@ BSX_API size_t bsx_dispatch_scratch_bytes(int64_t n_pairs, int32_t E);
 BSX_API int32_t bsx_dispatch(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t E, int32_t* cnt, int32_t* off, int32_t* slot,
                      int32_t* src, int32_t tile_rows, int32_t* tiles, int32_t* n_tiles, void* scratch, void* stream);
 
+/* ---- bsx_dispatch for callers that cannot hand over scratch memory.  (No counterpart in the reference.)
+ * Some hosts of this library have given every byte of device memory to their own arenas before the first token, or run the
+ * layer from a thread or a phase in which the CUDA allocator must not be entered; they have nowhere to get the count table
+ * bsx_dispatch wants.  This entry point keeps that table inside the library instead: a 1 MiB array in device global memory
+ * that every GPU holding the library carries until the process exits.  It allocates nothing, ever.
+ * Limits: n_pairs <= 65536 and E <= 1024; a larger call is refused with BSX_E_LIMIT (use bsx_dispatch with your own scratch).
+ * No tile list.  The first call on each device looks the array's address up (with that device current) and should be made
+ * before any stream capture begins; later calls only launch.  All calls on a device share the one table, which keeps
+ * whatever the previous call left (each call overwrites every entry it reads, so nothing has to start at zero): two calls
+ * that overlap on the GPU - different streams, or a graph replayed while another call runs - race and give wrong rows.
+ * Results are those of bsx_dispatch, bit for bit. */
+BSX_API int32_t bsx_dispatch_static(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t E, int32_t* cnt, int32_t* off,
+                                    int32_t* slot, int32_t* src, void* stream);
+
 /* ---- a6, decode-window form.  Replaces inkling2 moe_plan (src/models/inkling2/kernels/ops.cu:275-340,488-498): the experts
  * with pairs and a non-zero blob address become groups in ascending expert order (ptr[g], start[g]; start[n_groups] =
  * start[n_groups+1] = entries), entries inside a group in pair order, dst[entry] = pair index (the output row),
