@@ -41,6 +41,7 @@ _SIGNATURES = {
     "bsx_dispatch_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "bsx_dispatch": (C.c_int32, [P, C.c_int64, C.c_int32, C.c_int32, P, P, P, P, C.c_int32, P, P, P, P]),
     "bsx_dispatch_static": (C.c_int32, [P, C.c_int64, C.c_int32, C.c_int32, P, P, P, P, P]),
+    "bsx_gather_rows": (C.c_int32, [P, C.c_int64, P, C.c_int64, P, P]),
     "bsx_moe_plan": (C.c_int32, [P, C.c_int32, C.c_int32, C.c_int32, P, P, P, P, P, P, P]),
     "bsx_moe_plan_shared": (C.c_int32, [P, C.c_int32, C.c_int32, C.c_int32, P, C.c_uint64, P, P, P, P, P, P]),
     "bsx_expert_layout_init": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_float, C.c_float,

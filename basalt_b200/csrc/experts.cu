@@ -119,6 +119,17 @@ gated_mlp_plan_kernel(unsigned long long blob, int n_tok, unsigned long long* pt
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_tok; i += gridDim.x * blockDim.x) idx[i] = i;
 }
 
+// out[r] = x[src[r]]: the rows of a dispatch in expert order (the prompt path's gather_rows16, src/models/qwen4exp/prefill/kernels.cu:
+// 430-437), 16 bytes a thread
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ src, uint4* __restrict__ out, int64_t n_rows, int64_t per) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rows * per) return;
+    const int64_t r = i / per, j = i - r * per;
+    const int32_t s = src[r];
+    out[i] = s >= 0 ? x[(int64_t) s * per + j] : make_uint4(0u, 0u, 0u, 0u);
+}
+
 size_t gated_plan_bytes(int64_t cap_tok) { return ((size_t) (64 + cap_tok * 4) + 255) & ~(size_t) 255; }
 
 size_t row_bytes(int type, int64_t n) {
@@ -261,6 +272,17 @@ extern "C" int32_t bsx_experts_grouped_rows(const bsx_expert_layout* layout, con
     if (n_x_rows < 0 || n_x_rows > cap_entries) n_x_rows = 0;   // more rows than entries: per-entry images are the cheaper form
     return experts_grouped_impl(n_x_rows, layout, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups, cap_entries, x, x_kind, scratch,
                                 out, out_kind, stream);
+}
+
+extern "C" int32_t bsx_gather_rows(const void* x, int64_t row_bytes, const int32_t* src, int64_t n_rows, void* out, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (n_rows < 0 || row_bytes <= 0 || row_bytes % 16) return BSX_E_GEOMETRY;
+    if (n_rows == 0) return BSX_OK;
+    if (!aligned(x, 16) || !aligned(out, 16) || !src) return BSX_E_POINTER;
+    const int64_t per = row_bytes / 16, n = n_rows * per;
+    gather_rows_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, (cudaStream_t) stream>>>(static_cast<const uint4*>(x), src, static_cast<uint4*>(out),
+                                                                                        n_rows, per);
+    return launch_status();
 }
 
 extern "C" size_t bsx_gated_mlp_scratch_bytes(const bsx_expert_layout* L, int64_t cap_tok) {

@@ -332,6 +332,23 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
             cp_async_wait<kStages - 1>();   // the activation group (the oldest) has landed
             __syncthreads();
 
+            // per-pass epilogue constants, fetched before the stream starts so that no tile's epilogue waits on global memory:
+            // the columns' inverse row scales times the tail scale(s) and the 2^8 of the fp16 block scales, and the output rows
+            float f0 = 0.f, f1 = 0.f;
+            int64_t o0 = 0, o1 = 0;
+            {
+                const int j0 = TERMS == 1 ? 2 * t : t, j1 = 2 * t + 1;
+                if (j0 < ntok) f0 = inv[s_ir[j0]] * 256.f;
+                if (TERMS == 1 && j1 < ntok) f1 = inv[s_ir[j1]] * 256.f;
+                if (MODE == MODE_GU) {
+                    o0 = (int64_t) (eb + j0) * a.L.n_ff;
+                    o1 = (int64_t) (eb + j1) * a.L.n_ff;
+                } else {
+                    if (j0 < ntok) o0 = (int64_t) a.ent_dst[eb + j0] * a.L.n_embd;
+                    if (TERMS == 1 && j1 < ntok) o1 = (int64_t) a.ent_dst[eb + j1] * a.L.n_embd;
+                }
+            }
+            const float sg = tail[0], su = tail[1], sd = tail[2];
             // two accumulator sets, so that consecutive MMAs do not wait on each other
             float acc[4] = {0.f, 0.f, 0.f, 0.f}, acd[4] = {0.f, 0.f, 0.f, 0.f};
             // this lane's B fragments: its column's pieces, or (column unused in this pass) the zero area with stride 0
@@ -380,38 +397,25 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
                 acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
                 acd[0] = acd[1] = acd[2] = acd[3] = 0.f;
                 if (MODE == MODE_GU) {
-                    const float sg = tail[0] * 256.f, su = tail[1] * 256.f;
                     if (TERMS == 1) {
-#pragma unroll
-                        for (int q = 0; q < 2; ++q) {
-                            const int j = 2 * t + q;
-                            if (j < ntok) {
-                                const float f = inv[s_ir[j]];
-                                a.h[(size_t) (eb + j) * a.L.n_ff + rt + g] = swiglu((q ? c1 : c0) * f * sg, (q ? c3 : c2) * f * su, a.L);
-                            }
-                        }
+                        if (2 * t < ntok) a.h[o0 + rt + g] = swiglu(c0 * f0 * sg, c2 * f0 * su, a.L);
+                        if (2 * t + 1 < ntok) a.h[o1 + rt + g] = swiglu(c1 * f1 * sg, c3 * f1 * su, a.L);
                     } else if (t < ntok) {
-                        const float f = inv[s_ir[t]];
-                        a.h[(size_t) (eb + t) * a.L.n_ff + rt + g] = swiglu((c0 + c1) * f * sg, (c2 + c3) * f * su, a.L);
+                        a.h[o0 + rt + g] = swiglu((c0 + c1) * f0 * sg, (c2 + c3) * f0 * su, a.L);
                     }
                 } else {
-                    const float sd = tail[2] * 256.f;
                     if (TERMS == 1) {
-#pragma unroll
-                        for (int q = 0; q < 2; ++q) {
-                            const int j = 2 * t + q;
-                            if (j < ntok) {
-                                const float f = inv[s_ir[j]] * sd;
-                                const int64_t o = (int64_t) a.ent_dst[eb + j] * a.L.n_embd + rt + g;
-                                store_out(a.out, a.out_kind, o, (q ? c1 : c0) * f);
-                                store_out(a.out, a.out_kind, o + 8, (q ? c3 : c2) * f);
-                            }
+                        if (2 * t < ntok) {
+                            store_out(a.out, a.out_kind, o0 + rt + g, c0 * f0 * sd);
+                            store_out(a.out, a.out_kind, o0 + rt + g + 8, c2 * f0 * sd);
+                        }
+                        if (2 * t + 1 < ntok) {
+                            store_out(a.out, a.out_kind, o1 + rt + g, c1 * f1 * sd);
+                            store_out(a.out, a.out_kind, o1 + rt + g + 8, c3 * f1 * sd);
                         }
                     } else if (t < ntok) {
-                        const float f = inv[s_ir[t]] * sd;
-                        const int64_t o = (int64_t) a.ent_dst[eb + t] * a.L.n_embd + rt + g;
-                        store_out(a.out, a.out_kind, o, (c0 + c1) * f);
-                        store_out(a.out, a.out_kind, o + 8, (c2 + c3) * f);
+                        store_out(a.out, a.out_kind, o0 + rt + g, (c0 + c1) * f0 * sd);
+                        store_out(a.out, a.out_kind, o0 + rt + g + 8, (c2 + c3) * f0 * sd);
                     }
                 }
             }

@@ -99,6 +99,7 @@ class EPMoELayer:
         self.y = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
         self.scratch = torch.empty(moe.native_expert_scratch_bytes(layout, self.max_recv), dtype=torch.uint8, device=dev)
         self.side = torch.cuda.Stream(device=dev)
+        self.time_experts, self.last_expert_ms, self.last_groups = False, 0.0, 0
         if shared_blob is not None:
             self.s_out = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
             self.s_scratch = torch.empty(C.c_size_t(moe.capi.lib().bsx_gated_mlp_scratch_bytes(C.byref(layout), max_tokens)).value,
@@ -111,8 +112,7 @@ class EPMoELayer:
         n = T * a.k
         cur = torch.cuda.current_stream()
         # 1. route and dispatch the rank's own tokens
-        moe.router(x, self.gate_w, self.bias, a, self.logits, self.ids, self.w) if x.dtype == torch.float32 else \\
-            moe.router_x(x, self.gate_w, self.bias, a, self.logits, self.ids, self.w)
+        moe.router_x(x, self.gate_w, self.bias, a, self.logits, self.ids, self.w)
         cnt, off, slot, src, _, _ = moe.dispatch(self.ids[:T].reshape(-1), a.k, self.E)
         # the shared expert runs beside the exchange on its own stream
         if self.shared_blob is not None:
@@ -138,7 +138,14 @@ class EPMoELayer:
             st = torch.from_numpy(np.concatenate([start, start[-1:]])).to(self.dev)
             ent = torch.from_numpy(rows).to(self.dev)
             ng = torch.tensor([g], dtype=torch.int32, device=self.dev)
+            if self.time_experts:
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(cur)
             moe.native_expert_grouped(L, ptr, st, ng, ent, ent, g, n_recv, xr, self.scratch, out, n_x_rows=n_recv)
+            if self.time_experts:
+                t1.record(cur)
+                t1.synchronize()
+                self.last_expert_ms, self.last_groups = t0.elapsed_time(t1), g
         # 5. results back to their tokens' ranks (the mirror exchange), then the combine
         dist.all_to_all_single(self.rows_back[:n], out[:n_recv], send.tolist(), recv.tolist(), group=self.group)
         shared = None

@@ -71,6 +71,28 @@ def router(x, gate, bias, a: RouterArgs, logits=None, ids=None, weights=None, st
     return logits, ids, weights
 
 
+def router_x(x, gate, bias, a: RouterArgs, logits=None, ids=None, weights=None, stream=None):
+    """router() on fp32 or bf16 activation rows (bf16 is widened exactly inside the kernel)."""
+    T = x.shape[0]
+    dev = x.device
+    logits = torch.empty((T, a.n_expert), dtype=torch.float32, device=dev) if logits is None else logits
+    ids = torch.empty((T, a.k), dtype=torch.int32, device=dev) if ids is None else ids
+    weights = torch.empty((T, a.k), dtype=torch.float32, device=dev) if weights is None else weights
+    hp, hn, keep = _held(a)
+    check("bsx_router_x", capi.lib().bsx_router_x(_p(x), X_BF16 if x.dtype == torch.bfloat16 else X_F32, _p(gate), _p(bias), T, a.n_expert,
+                                                   a.n_embd, a.k, a.gate, a.weight_scale, a.n_group, a.topk_group, a.prior, hp, hn,
+                                                   _p(logits), _p(ids), _p(weights), _stream(stream)))
+    return logits, ids, weights
+
+
+def gather_rows(x, src, out=None, stream=None):
+    """out[r] = x[src[r]] (the prompt path's gather_rows16, src/models/qwen4exp/prefill/kernels.cu:694-699)."""
+    n = src.numel()
+    out = torch.empty((n, x.shape[1]), dtype=x.dtype, device=x.device) if out is None else out
+    check("bsx_gather_rows", capi.lib().bsx_gather_rows(_p(x), x.shape[1] * x.element_size(), _p(src), n, _p(out), _stream(stream)))
+    return out
+
+
 def router_logits(x, gate, logits=None, stream=None):
     T, H = x.shape
     E = gate.shape[0]
@@ -171,12 +193,13 @@ def _x_kind(x) -> int:
 
 
 def native_expert_grouped(L: ExpertLayout, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups: int, cap_entries: int,
-                          x, scratch, out, stream=None):
-    """basalt::kernels::native_expert_grouped (iq_kernels.hpp:84-87).  `x` may be fp32, bf16 or q8_1 bytes; `out` fp32 or bf16."""
+                          x, scratch, out, stream=None, n_x_rows: int = 0):
+    """basalt::kernels::native_expert_grouped (iq_kernels.hpp:84-87).  `x` may be fp32, bf16 or q8_1 bytes; `out` fp32 or bf16.
+    n_x_rows: the number of rows of x when known (activation images are then built once per row)."""
     out_kind = OUT_BF16 if out.dtype == torch.bfloat16 else OUT_F32
-    check("bsx_experts_grouped", capi.lib().bsx_experts_grouped(C.byref(L), _p(grp_ptr), _p(grp_start), _p(n_groups), _p(ent_dst),
-                                                                 _p(ent_tok), cap_groups, cap_entries, _p(x), _x_kind(x),
-                                                                 _p(scratch), _p(out), out_kind, _stream(stream)))
+    check("bsx_experts_grouped", capi.lib().bsx_experts_grouped_rows(C.byref(L), _p(grp_ptr), _p(grp_start), _p(n_groups), _p(ent_dst),
+                                                                      _p(ent_tok), cap_groups, cap_entries, _p(x), _x_kind(x), n_x_rows,
+                                                                      _p(scratch), _p(out), out_kind, _stream(stream)))
     return out
 
 

@@ -201,6 +201,8 @@ def main():
     if world > 1:
         dist.barrier()
     lib = capi.lib()
+    if world > 1:
+        return run_expert_parallel(args, rank, world, dev)
 
     gate, blobs, blob_bytes = make_layer_weights(dev)
     L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
@@ -291,6 +293,92 @@ def main():
                                     "sample": "20 full layer steps of 64 tokens on the same weights (reference CPU expert pool; oracle router/dispatch/combine)"}
         except Exception as exc:   # the baseline is reported, never required
             line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port", "sample": f"failed: {exc}"}
+    print(json.dumps(line))
+
+
+def run_expert_parallel(args, rank, world, dev):
+    """N > 1: the same layer with its 512 routed experts sharded over the ranks in contiguous blocks (expert parallel), 64
+    tokens per rank and step (weak scaling: per-GPU tokens fixed), rows exchanged by NCCL all-to-all before and after the
+    local grouped experts; router and shared expert replicated.  Device time, max over ranks."""
+    import torch.distributed as dist
+    from basalt_b200 import capi, ep, moe
+    gate, blobs, blob_bytes = make_layer_weights(dev)          # the same seed on every rank: identical replicated weights
+    El = E // world
+    L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
+    rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
+    layers = []
+    for c in range(args.copies):
+        own = blobs[rank * El:(rank + 1) * El].clone()
+        layers.append(ep.EPMoELayer(gate.clone(), None, own, L, rargs, E, shared_blob=blobs[E].clone(), max_tokens=T))
+    del blobs
+    n_batches = 8
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    xs = [torch.randn((T, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
+    stream = torch.cuda.Stream(device=dev)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup):
+            layers[i % args.copies].forward(xs[i % n_batches])
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(dev.index or 0) as clocks:
+            ev0.record(stream)
+            for i in range(args.steps):
+                layers[i % args.copies].forward(xs[i % n_batches])
+            ev1.record(stream)
+            barrier()
+        ms_total = ev0.elapsed_time(ev1)
+        x_host = [x.cpu().pin_memory() for x in xs]
+        xin = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        y_host = torch.empty((T, H), dtype=torch.float32).pin_memory()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(args.steps):
+            xin.copy_(x_host[i % n_batches], non_blocking=True)
+            y_host.copy_(layers[i % args.copies].forward(xin), non_blocking=True)
+            stream.synchronize()
+        e1.record(stream)
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
+        # the local expert stage alone, for the roofline: bytes of the experts this rank touched / device time of the call
+        ly = layers[0]
+        ly.time_experts = True
+        exp_ms, exp_bytes = [], []
+        for i in range(min(args.steps, 50)):
+            ly.forward(xs[i % n_batches])
+            stream.synchronize()
+            exp_ms.append(ly.last_expert_ms)
+            exp_bytes.append(ly.last_groups * (L.bytes - 16))
+        ly.time_experts = False
+        barrier()
+    times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = times.tolist()
+    if rank != 0:
+        return
+    ms_step = ms_total / args.steps
+    peak, peak_src = measured_peaks()
+    k_ms, k_bytes = sum(exp_ms) / len(exp_ms), sum(exp_bytes) / len(exp_bytes)
+    achieved = k_bytes / (k_ms * 1e-3) / 1e9
+    line = {
+        "metric": "MoE-layer tokens/s (decode)", "value": T * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16 x NVFP4 tensor-core products, fp32 accumulation", "data": "synthetic",
+        "config": dict(CFG, tokens_per_step=T * world, tokens_per_gpu=T, parallelism=f"ep{world}: {E // world} routed experts per GPU, router and shared expert replicated, NCCL all-to-all of bf16 rows out and fp32 rows back",
+                       l2_policy=f"each rank cycles through {args.copies} copies of its expert shard"),
+        "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2 * world,
+                "d2h_bytes_per_step": T * H * 4 * world},
+        "gpu_launches": 12 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "rank 0's local grouped experts (image prep, gate/up, down)", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None, "algorithmic_bytes_per_launch": k_bytes,
+                     "kernel_ms": k_ms},
+        "clocks": clocks.summary(),
+    }
     print(json.dumps(line))
 
 

@@ -130,6 +130,10 @@ BSX_API int32_t bsx_dispatch(const int32_t* ids, int64_t n_pairs, int32_t k, int
 BSX_API int32_t bsx_dispatch_static(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t E, int32_t* cnt, int32_t* off,
                                     int32_t* slot, int32_t* src, void* stream);
 
+/* ---- a6: apply the permutation.  out[r] = x[src[r]] for rows of row_bytes bytes (a multiple of 16); src < 0 gives a zero row.
+ * Replaces gather_rows16 (src/models/qwen4exp/prefill/kernels.cu:430-437, :694-699). */
+BSX_API int32_t bsx_gather_rows(const void* x, int64_t row_bytes, const int32_t* src, int64_t n_rows, void* out, void* stream);
+
 /* ---- a6, decode-window form.  Replaces inkling2 moe_plan (src/models/inkling2/kernels/ops.cu:275-340,488-498): the experts
  * with pairs and a non-zero blob address become groups in ascending expert order (ptr[g], start[g]; start[n_groups] =
  * start[n_groups+1] = entries), entries inside a group in pair order, dst[entry] = pair index (the output row),

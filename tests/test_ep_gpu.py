@@ -1,0 +1,69 @@
+"""GPU, two ranks over NCCL: the expert-parallel layer (basalt_b200/ep.py) against the single-GPU layer on the same tokens.
+Each rank's rows must be bit-identical to what one GPU computes for its tokens: routing is replicated and an expert gives
+the same rows whichever rank holds it.  Needs two devices (skipped otherwise); NVLS is switched off for the test processes."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+E, H, I, K, T = 64, 2048, 512, 10, 24
+
+
+def _weights():
+    from oracle import oracle as O
+    from tests.helpers import make_expert_blobs, stack_blobs
+    rng = np.random.default_rng(3)
+    L, blobs = make_expert_blobs(rng, E + 1, O.T_NVFP4, O.T_NVFP4, H, I)
+    gate = (rng.standard_normal((E, H)) * 0.02).astype(np.float32)
+    return stack_blobs(blobs), gate
+
+
+def _rank(rank, world, port, q):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    from basalt_b200 import capi, ep, moe
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    blobs, gate = _weights()
+    bd = torch.from_numpy(blobs).to(dev)
+    gw = torch.from_numpy(gate).to(dev)
+    L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
+    args = moe.RouterArgs(n_expert=E, n_embd=H, k=K, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
+    g = torch.Generator(device=dev).manual_seed(10 + rank)
+    x = torch.randn((T - 5 * rank, H), generator=g, device=dev).bfloat16()      # ragged token counts across ranks
+    El = E // world
+    layer = ep.EPMoELayer(gw, None, bd[rank * El:(rank + 1) * El].contiguous(), L, args, E, shared_blob=bd[E], max_tokens=T)
+    y = layer.forward(x).clone()
+    y2 = layer.forward(x).clone()
+    single = moe.MoELayer(gw, None, bd[:E], L, args, shared_blob=bd[E], max_tokens=T)
+    want = single.forward(x).clone()
+    torch.cuda.synchronize()
+    q.put((rank, bool(torch.equal(y.view(torch.int32), want.view(torch.int32))), bool(torch.equal(y.view(torch.int32), y2.view(torch.int32))),
+           float((y - want).abs().max())))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_ep_two_gpus_matches_single_gpu(lib):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + os.getpid() % 90
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=600) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, same, stable, err in res:
+        assert stable, f"rank {rank}: not bit-stable from run to run"
+        assert same, f"rank {rank}: differs from the single-GPU layer (max abs {err})"
