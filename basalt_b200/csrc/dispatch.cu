@@ -221,6 +221,54 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsi
     }
 }
 
+// Groups for the experts this device holds, from a dispatch: the experts with rows and a non-zero blob address become
+// groups in ascending order; their dispatch rows, in order, become the entries (ent_dst = the dispatch row, so outputs land
+// where the combine's slot[] points; ent_tok = the row's token).  Rows of experts held elsewhere get no entry.
+// One block: a scan over the experts, then every thread places rows by binary search in the offsets.
+__global__ void __launch_bounds__(1024)
+plan_groups_kernel(const int32_t* __restrict__ cnt, const int32_t* __restrict__ off, const int32_t* __restrict__ src, int E,
+                   const unsigned long long* __restrict__ blobs, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
+                   int32_t* __restrict__ n_groups, int32_t* __restrict__ ent_dst, int32_t* __restrict__ ent_tok) {
+    __shared__ int sh[32];
+    __shared__ int s_off[kMaxExpert + 1];
+    __shared__ int s_first[kMaxExpert];     // first compact entry of expert e, or -1 when it has no group here
+    const int e = threadIdx.x;
+    const int c = e < E ? cnt[e] : 0;
+    const bool used = c > 0 && blobs[e] != 0ull;
+    int groups = 0, entries = 0;
+    const int g = block_excl_sum(used ? 1 : 0, &groups, sh);
+    const int first = block_excl_sum(used ? c : 0, &entries, sh);
+    if (e < E) {
+        s_off[e] = off[e];
+        s_first[e] = used ? first : -1;
+    }
+    if (used) {
+        ptr[g] = blobs[e];
+        start[g] = first;
+    }
+    if (e == 0) {
+        s_off[E] = off[E];
+        start[groups] = entries;
+        start[groups + 1] = entries;
+        *n_groups = groups;
+    }
+    __syncthreads();
+    const int n_rows = s_off[E];
+    for (int r = threadIdx.x; r < n_rows; r += blockDim.x) {
+        int lo = 0, hi = E;                 // the expert with off[x] <= r < off[x + 1]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_off[mid] <= r) lo = mid; else hi = mid;
+        }
+        const int f = s_first[lo];
+        if (f >= 0) {
+            const int i = f + (r - s_off[lo]);
+            ent_dst[i] = r;
+            ent_tok[i] = src[r];
+        }
+    }
+}
+
 // Scratch of bsx_dispatch_static: the [expert][chunk] count table for up to kStaticMaxPairs pairs over up to kMaxExpert
 // experts (1 MiB), resident on every device that loads this library.  Host code may only take its address
 // (cudaGetSymbolAddress); the name itself is not a device pointer on the host side.
@@ -297,6 +345,16 @@ static int32_t plan_launch(const int32_t* ids, int32_t T, int32_t k, int32_t E, 
     if (!ids || !blob_table || !ptr || !start || !n_groups || !dst || !tok) return BSX_E_POINTER;
     const size_t smem = (size_t) E * (sizeof(unsigned long long) + 2 * sizeof(int32_t)) + (size_t) n * sizeof(int32_t);
     moe_plan_kernel<<<1, 1024, smem, (cudaStream_t) stream>>>(ids, (int) n, k, E, blob_table, shared_blob, T, ptr, start, n_groups, dst, tok);
+    return launch_status();
+}
+
+extern "C" int32_t bsx_plan_groups(const int32_t* cnt, const int32_t* off, const int32_t* src, int32_t E,
+                                   const unsigned long long* blob_table, unsigned long long* ptr, int32_t* start, int32_t* n_groups,
+                                   int32_t* ent_dst, int32_t* ent_tok, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (E < 1 || E > kMaxExpert) return BSX_E_GEOMETRY;
+    if (!cnt || !off || !src || !blob_table || !ptr || !start || !n_groups || !ent_dst || !ent_tok) return BSX_E_POINTER;
+    plan_groups_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(cnt, off, src, E, blob_table, ptr, start, n_groups, ent_dst, ent_tok);
     return launch_status();
 }
 

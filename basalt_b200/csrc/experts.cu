@@ -59,12 +59,18 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const float* __restr
 // src/models/qwen4exp/prefill/kernels.cu:438-449 (bit-equal forms).  A thread owns 4 consecutive columns.
 __global__ void __launch_bounds__(128)
 combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ slot, const float* __restrict__ w,
-               const float* __restrict__ shared, const float* __restrict__ sg, int k, int H, int pair0, float* __restrict__ y) {
+               const float* __restrict__ shared, const float* __restrict__ sg, int k, int H, int pair0, const int32_t* __restrict__ ids,
+               int e_lo, int e_hi, float* __restrict__ y) {
     __shared__ int s_row[64];
     __shared__ float s_w[64];
     const int t = blockIdx.y;
     if (threadIdx.x < k) {
-        s_row[threadIdx.x] = slot ? slot[(size_t) t * k + threadIdx.x] : pair0 + t * k + (int) threadIdx.x;
+        int r = slot ? slot[(size_t) t * k + threadIdx.x] : pair0 + t * k + (int) threadIdx.x;
+        if (ids) {   // expert-parallel partial sum: only the pairs whose expert lies in [e_lo, e_hi)
+            const int e = ids[(size_t) t * k + threadIdx.x];
+            if (e < e_lo || e >= e_hi) r = -1;
+        }
+        s_row[threadIdx.x] = r;
         s_w[threadIdx.x] = w[(size_t) t * k + threadIdx.x];
     }
     __syncthreads();
@@ -309,8 +315,8 @@ extern "C" int32_t bsx_gated_mlp(const bsx_expert_layout* layout, const void* bl
                                 stream);
 }
 
-extern "C" int32_t bsx_combine(const float* rows, const int32_t* slot, const float* weights, const float* shared,
-                               const float* shared_gate, int32_t T, int32_t k, int32_t H, float* y, void* stream) {
+static int32_t combine_impl(const float* rows, const int32_t* slot, const float* weights, const float* shared, const float* shared_gate,
+                            int32_t T, int32_t k, int32_t H, const int32_t* ids, int32_t e_lo, int32_t e_hi, float* y, void* stream) {
     if (!stream) return BSX_E_STREAM;
     if (T < 0 || k < 1 || k > 64 || H < 4 || H % 4) return BSX_E_GEOMETRY;
     if (T == 0) return BSX_OK;
@@ -320,7 +326,18 @@ extern "C" int32_t bsx_combine(const float* rows, const int32_t* slot, const flo
         const dim3 grid((unsigned) ((H / 4 + 127) / 128), (unsigned) nt);
         combine_kernel<<<grid, 128, 0, (cudaStream_t) stream>>>(rows, slot ? slot + (size_t) t0 * k : nullptr, weights + (size_t) t0 * k,
                                                                shared ? shared + (size_t) t0 * H : nullptr, shared_gate ? shared_gate + t0 : nullptr,
-                                                               k, H, t0 * k, y + (size_t) t0 * H);
+                                                               k, H, t0 * k, ids ? ids + (size_t) t0 * k : nullptr, e_lo, e_hi, y + (size_t) t0 * H);
     }
     return launch_status();
+}
+
+extern "C" int32_t bsx_combine(const float* rows, const int32_t* slot, const float* weights, const float* shared,
+                               const float* shared_gate, int32_t T, int32_t k, int32_t H, float* y, void* stream) {
+    return combine_impl(rows, slot, weights, shared, shared_gate, T, k, H, nullptr, 0, 0, y, stream);
+}
+
+extern "C" int32_t bsx_combine_partial(const float* rows, const int32_t* slot, const float* weights, const int32_t* ids, int32_t e_lo,
+                                       int32_t e_hi, int32_t T, int32_t k, int32_t H, float* y, void* stream) {
+    if (!ids) return BSX_E_POINTER;
+    return combine_impl(rows, slot, weights, nullptr, nullptr, T, k, H, ids, e_lo, e_hi, y, stream);
 }

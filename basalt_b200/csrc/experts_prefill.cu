@@ -1,0 +1,379 @@
+// experts_prefill.cu - prompt-sized grouped experts for NVFP4 blobs on the 5th-generation tensor cores (tcgen05).
+//
+// A ragged grouped GEMM over the dispatch's expert-sorted rows: for every 128-row tile of one expert,
+//   gate/up:  [128 rows x H] . [H x 2I]  -> SwiGLU ->  h [rows x I]           (fp16, in scratch)
+//   down:     [128 rows x I] . [I x H]   ->             dm [rows x H]          (fp32, unweighted, row = dispatch slot)
+// which is what Basalt's fp4::run_group computes (include/basalt/prefill/moe_fp4.hpp:43-113, src/prefill/moe_fp4.cu:368-518,
+// :654-676) - but that kernel is mma.sync kind::mxf4nvf4 for sm_120a, does not assemble for sm_100, and rounds activations
+// to FP4.  Here the NVFP4 weights are decoded EXACTLY to fp16 (E2M1 x UE4M3 has at most 5 significant bits) by the producer
+// warps straight into 128-byte-swizzled shared memory, activations are fp16 (bf16 inputs convert exactly after a per-row
+// power-of-two scale), and tcgen05.mma kind::f16 accumulates in fp32 in tensor memory.  So the result sits ~2e-4 from the
+// dequantised fp32 reference instead of the reference kernel's ~1e-2 .. 0.2, at bf16-class tensor throughput.
+//
+// One CTA per (row tile, 128-column weight tile): warp 0 allocates 128 TMEM columns and issues the MMAs (one elected
+// lane); warps 1-4 are the producers - each thread owns one activation row (cp.async gather through `src`, zero-filled past
+// the expert's last row) and one weight row (36-byte NVFP4 block -> 64 fp16 per 64-column k-block) - and, after the last
+// MMA, the epilogue (thread = TMEM lane = output row).  K-blocks of 64 columns move through a 3-stage ring guarded by
+// mbarriers; every wait is bounded and reports through a status word instead of hanging.
+//
+// Both operands use the SAME permutation of k inside each 16-column group, (0,8,1,9,...,7,15) - the order cvt.e2m1x2 emits
+// a sub-block's values in - so no shuffling is needed: the activation image (made by a small kernel here) and the SwiGLU
+// output are simply written in that order.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "experts.cuh"
+#include "formats.cuh"
+
+namespace bsx {
+namespace {
+
+constexpr int kTileM = 128;        // rows (tokens) per tile = TMEM lanes
+constexpr int kTileN = 128;        // weight rows per tile = TMEM columns
+constexpr int kBlockK = 64;        // fp16 per k-block: one 128-byte swizzle row
+constexpr int kStagesP = 3;
+constexpr int kProducers = 128;    // warps 1..4
+constexpr int kThreadsP = 160;
+constexpr uint32_t kSpinLimit = 1u << 22;   // bounded mbarrier waits (~ seconds), then an error status
+constexpr float kHScale = 0.25f;   // the SwiGLU output is stored as fp16(h / 4): fp16 then holds |h| up to 2.6e5
+
+enum { PMODE_GU = 0, PMODE_DOWN = 1 };
+enum { kStatusTimeout = 1 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// waits for the phase with the given parity; false after kSpinLimit polls
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t a = smem_u32(bar);
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok)
+                     : "r"(a), "r"(parity)
+                     : "memory");
+        if (ok) return true;
+        if (i > 64) __nanosleep(64);
+    }
+    return false;
+}
+
+// K-major, 128-byte swizzle: 8-row atoms of 1024 bytes stacked along M/N (stride byte offset 1024), descriptor version 1
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t) ((addr & 0x3FFFFu) >> 4) | ((uint64_t) 1 << 16) | ((uint64_t) (1024 >> 4) << 32) | ((uint64_t) 1 << 46) |
+           ((uint64_t) 2 << 61);
+}
+// kind::f16: D fp32, A and B fp16, both K-major, N = 128, M = 128
+constexpr uint32_t kInstrDesc = (1u << 4) | ((uint32_t) (kTileN >> 3) << 17) | ((uint32_t) (kTileM >> 4) << 24);
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d), "l"(adesc),
+                 "l"(bdesc), "r"(kInstrDesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+        "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+__device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t (&h)[4]) {
+    asm("{\n.reg .b8 b0, b1, b2, b3;\nmov.b32 {b0, b1, b2, b3}, %4;\ncvt.rn.f16x2.e2m1x2 %0, b0;\ncvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\ncvt.rn.f16x2.e2m1x2 %3, b3;\n}\n"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+        : "r"(w));
+}
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+// UE4M3 byte -> fp16 pair {d, d}, d = scale / 2^8 (see experts_mma.cu: the epilogue multiplies by 2^8); 0x7F -> 0
+__device__ __forceinline__ uint32_t scale_pair_bits(uint32_t byte) {
+    const uint32_t b = byte & 0x7Fu;
+    const uint32_t v = b == 0x7Fu ? 0u : b << 7;
+    return v | (v << 16);
+}
+// position of column c inside its 16-column group in the permuted k order (0,8,1,9,...,7,15)
+__host__ __device__ constexpr int perm16(int j) { return 2 * (j & 7) + (j >> 3); }
+
+struct PrefillArgs {
+    bsx_expert_layout L;
+    const unsigned long long* blob_table;   // [E] device addresses
+    const int32_t* off;                      // [E + 1] row offsets per expert
+    const int32_t* src;                      // [rows] token of each row
+    const int32_t* tiles;                    // {expert, first row} per 128-row tile
+    const int32_t* n_tiles;
+    const __half* xh;                        // [T][H] fp16, permuted, row-scaled
+    const float* xinv;                       // [T]
+    __half* h;                               // [rows][I] fp16 (permuted, times kHScale)
+    float* dm;                               // [rows][H] fp32
+    int32_t* status;                         // sticky error word (0 = ok)
+};
+
+// x [T][H] (fp32 or bf16) -> fp16 rows scaled by a power of two into fp16's range, k-permuted inside 16-column groups
+__global__ void __launch_bounds__(256) prefill_prep_x_kernel(const void* __restrict__ x, int kind, int64_t T, int64_t H, __half* __restrict__ xh,
+                                                             float* __restrict__ xinv) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t t = (int64_t) blockIdx.x * 8 + warp;
+    if (t >= T) return;
+    auto ld = [&](int64_t c) {
+        return kind == BSX_X_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(x)[t * H + c]) : static_cast<const float*>(x)[t * H + c];
+    };
+    float amax = 0.f;
+    for (int64_t c = lane; c < H; c += 32) amax = fmaxf(amax, fabsf(ld(c)));
+    amax = warp_max_xor(amax);
+    int ex = 0;
+    float s = 1.f, iv = 1.f;
+    if (amax > 0.f && amax <= 3.0e38f) {
+        frexpf(amax, &ex);
+        ex = max(-100, min(100, 14 - ex));
+        s = ldexpf(1.f, ex);
+        iv = ldexpf(1.f, -ex);
+    }
+    if (lane == 0) xinv[t] = iv;
+    for (int64_t c = lane; c < H; c += 32) xh[t * H + (c & ~(int64_t) 15) + perm16((int) (c & 15))] = __float2half_rn(ld(c) * s);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // 1024-byte aligned operand stages: A then B per stage
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    constexpr int kABytes = kTileM * kBlockK * 2, kBBytes = kTileN * kBlockK * 2;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStagesP * (kABytes + kBBytes));   // full[S], empty[S], accum
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kStagesP;
+    uint64_t* accum = bars + 2 * kStagesP;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStagesP + 1);
+    uint32_t* lut = tmem_slot + 2;   // [256] fp16 scale pairs
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.y;
+    if (tile >= *a.n_tiles) return;
+    const int expert = a.tiles[2 * tile], row0 = a.tiles[2 * tile + 1];
+    if (a.blob_table[expert] == 0ull) return;   // an expert another device holds (expert parallelism): its rows are not ours
+    const int rows = min(kTileM, a.off[expert + 1] - row0);
+    const int64_t K = MODE == PMODE_GU ? a.L.n_embd : a.L.n_ff;
+    const int nkb = (int) (K / kBlockK);
+    const int n0 = blockIdx.x * (MODE == PMODE_GU ? kTileN / 2 : kTileN);   // first neuron (GU) or first down row of the tile
+    const uint8_t* blob = reinterpret_cast<const uint8_t*>(a.blob_table[expert]);
+
+    for (int i = threadIdx.x; i < 256; i += kThreadsP) lut[i] = scale_pair_bits(i);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStagesP; ++s) {
+            mbar_init(&full[s], kProducers);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t) kTileN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---- MMA issuer: one lane feeds the tensor core, four k = 16 instructions per 64-column k-block
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % kStagesP;
+                ok = mbar_wait(&full[s], (uint32_t) (kb / kStagesP) & 1u);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t sa = smem_u32(smem + s * (kABytes + kBBytes)), sb = sa + kABytes;
+#pragma unroll
+                for (int k = 0; k < kBlockK / 16; ++k)
+                    umma_f16(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), (kb | k) ? 1u : 0u);
+                umma_commit(&empty[s]);      // the stage may be refilled once these MMAs have read it
+            }
+            umma_commit(accum);              // every MMA issued so far has finished when this fires
+            if (!ok) atomicOr(a.status, kStatusTimeout);
+        }
+    } else {
+        // ---- producers: thread p owns activation row p and weight row p of the tile.  A warp may only read the 32 TMEM lanes
+        // 32 (warp % 4) .. + 31, and lane = output row, so the row assignment follows that rule from the start.
+        const int p = (warp & 3) * 32 + lane;
+        const bool row_live = p < rows;
+        const __half* arow;
+        if (MODE == PMODE_GU) arow = a.xh + (size_t) (row_live ? a.src[row0 + p] : 0) * K;
+        else arow = a.h + (size_t) (row0 + (row_live ? p : 0)) * K;
+        const uint8_t* wrow;
+        if (MODE == PMODE_GU) {
+            const int r = n0 + (p & 63);     // B rows 0..63 = gate rows, 64..127 = the matching up rows
+            wrow = p < 64 ? blob + (size_t) r * a.L.gu_row : blob + a.L.up_off + (size_t) r * a.L.up_row;
+        } else {
+            wrow = blob + a.L.down_off + (size_t) (n0 + p) * a.L.d_row;
+        }
+        const uint32_t swz = (uint32_t) (p & 7);
+        const uint32_t row_off = (uint32_t) ((p >> 3) * 1024 + (p & 7) * 128);
+        uint32_t wq[9];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) wq[i] = reinterpret_cast<const uint32_t*>(wrow)[i];
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % kStagesP;
+            ok = mbar_wait(&empty[s], ((uint32_t) (kb / kStagesP) & 1u) ^ 1u);
+            if (!ok) break;
+            uint8_t* sa = smem + s * (kABytes + kBBytes);
+            uint8_t* sb = sa + kABytes;
+            // A: the row's 128 bytes as 8 swizzled 16-byte chunks (zero-filled past the expert's rows)
+            {
+                const uint32_t dst = smem_u32(sa) + row_off;
+                const uint8_t* g = reinterpret_cast<const uint8_t*>(arow + (size_t) kb * kBlockK);
+                const uint32_t nbytes = row_live ? 16u : 0u;
+#pragma unroll
+                for (uint32_t c = 0; c < 8; ++c)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst + ((c ^ swz) << 4)), "l"(g + c * 16), "r"(nbytes) : "memory");
+                asm volatile("cp.async.commit_group;\n" ::: "memory");
+            }
+            // B: this k-block's NVFP4 block of the weight row -> 64 fp16 (already in the permuted order), next block prefetched
+            uint32_t cur[9];
+#pragma unroll
+            for (int i = 0; i < 9; ++i) cur[i] = wq[i];
+            if (kb + 1 < nkb) {
+#pragma unroll
+                for (int i = 0; i < 9; ++i) wq[i] = reinterpret_cast<const uint32_t*>(wrow)[9 * (kb + 1) + i];
+            }
+            uint4* brow = reinterpret_cast<uint4*>(sb + row_off);
+#pragma unroll
+            for (int sub = 0; sub < 4; ++sub) {
+                const uint32_t sc = lut[(cur[0] >> (8 * sub)) & 0xFFu];
+                uint32_t q0[4], q1[4];
+                cvt_e2m1x8(cur[1 + 2 * sub], q0);
+                cvt_e2m1x8(cur[2 + 2 * sub], q1);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    q0[i] = hmul2_bits(q0[i], sc);
+                    q1[i] = hmul2_bits(q1[i], sc);
+                }
+                brow[(2 * sub) ^ swz] = make_uint4(q0[0], q0[1], q0[2], q0[3]);
+                brow[(2 * sub + 1) ^ swz] = make_uint4(q1[0], q1[1], q1[2], q1[3]);
+            }
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+            mbar_arrive(&full[s]);
+        }
+        // ---- epilogue: thread p reads TMEM lane p (= output row p), 32 columns at a time
+        if (ok) ok = mbar_wait(accum, 0u);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        if (!ok) atomicOr(a.status, kStatusTimeout);
+        if (ok && row_live) {
+            const uint32_t lane_base = (uint32_t) ((warp & 3) * 32) << 16;
+            const float* tail = reinterpret_cast<const float*>(blob + a.L.bytes - 16);
+            if (MODE == PMODE_GU) {
+                const float f = a.xinv[a.src[row0 + p]] * 256.f;
+                const float sg = tail[0] * f, su = tail[1] * f;
+                __half* hrow = a.h + (size_t) (row0 + p) * a.L.n_ff + n0;
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(tmem + lane_base + (uint32_t) c0, g);
+                    tmem_ld32(tmem + lane_base + (uint32_t) (64 + c0), u);
+                    __half out[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float hv = swiglu(__uint_as_float(g[j]) * sg, __uint_as_float(u[j]) * su, a.L) * kHScale;
+                        out[(j & ~15) + perm16(j & 15)] = __float2half_rn(fminf(fmaxf(hv, -65504.f), 65504.f));
+                    }
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(hrow + c0)[v] = reinterpret_cast<const uint4*>(out)[v];
+                }
+            } else {
+                const float f = tail[2] * (256.f / kHScale);
+                float* orow = a.dm + (size_t) (row0 + p) * a.L.n_embd + n0;
+#pragma unroll
+                for (int c0 = 0; c0 < kTileN; c0 += 32) {
+                    uint32_t d[32];
+                    tmem_ld32(tmem + lane_base + (uint32_t) c0, d);
+#pragma unroll
+                    for (int v = 0; v < 8; ++v)
+                        reinterpret_cast<float4*>(orow + c0)[v] = make_float4(__uint_as_float(d[4 * v]) * f, __uint_as_float(d[4 * v + 1]) * f,
+                                                                               __uint_as_float(d[4 * v + 2]) * f, __uint_as_float(d[4 * v + 3]) * f);
+                }
+            }
+        }
+    }
+    // everyone is done with tensor memory before warp 0 gives it back
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t) kTileN) : "memory");
+    }
+}
+
+size_t align256p(size_t v) { return (v + 255) & ~(size_t) 255; }
+constexpr size_t kSmemP = 1024 + kStagesP * (kTileM * kBlockK * 2 + kTileN * kBlockK * 2) + 256 + 1024 + 64;
+
+}  // namespace
+}  // namespace bsx
+
+using namespace bsx;
+
+extern "C" size_t bsx_experts_prefill_scratch_bytes(const bsx_expert_layout* L, int64_t n_tokens, int64_t cap_rows) {
+    if (!L || n_tokens < 0 || cap_rows < 0) return 0;
+    return align256p((size_t) n_tokens * L->n_embd * 2) + align256p((size_t) n_tokens * 4) + align256p((size_t) (cap_rows + kTileM) * L->n_ff * 2) + 256;
+}
+
+extern "C" int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const unsigned long long* blob_table, const int32_t* off,
+                                       const int32_t* src, const int32_t* tiles, const int32_t* n_tiles, int64_t cap_tiles, int64_t cap_rows,
+                                       const void* x, int32_t x_kind, int64_t n_tokens, void* scratch, float* dm, int32_t* status, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (!layout || !blob_table || !off || !src || !tiles || !n_tiles || !aligned(x, 16) || !aligned(scratch, 256) || !aligned(dm, 16) || !status)
+        return BSX_E_POINTER;
+    const bsx_expert_layout& L = *layout;
+    if (L.gu_type != kTypeNVFP4 || L.up_type != kTypeNVFP4 || L.d_type != kTypeNVFP4) return BSX_E_TYPE;
+    if (L.n_embd % 128 || L.n_ff % 64 || (x_kind != BSX_X_F32 && x_kind != BSX_X_BF16)) return BSX_E_GEOMETRY;
+    if (cap_tiles < 0 || cap_tiles > 65535 || cap_rows < 0 || n_tokens < 0) return BSX_E_GEOMETRY;
+    if (cap_tiles == 0 || n_tokens == 0) return BSX_OK;
+    const cudaStream_t st = (cudaStream_t) stream;
+    uint8_t* p = static_cast<uint8_t*>(scratch);
+    PrefillArgs a;
+    a.L = L;
+    a.blob_table = blob_table;
+    a.off = off;
+    a.src = src;
+    a.tiles = tiles;
+    a.n_tiles = n_tiles;
+    __half* xh = reinterpret_cast<__half*>(p);
+    p += align256p((size_t) n_tokens * L.n_embd * 2);
+    float* xinv = reinterpret_cast<float*>(p);
+    p += align256p((size_t) n_tokens * 4);
+    a.xh = xh;
+    a.xinv = xinv;
+    a.h = reinterpret_cast<__half*>(p);
+    a.dm = dm;
+    a.status = status;
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_GU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
+        if (e != cudaSuccess) return (int32_t) e;
+        configured[dev] = true;
+    }
+    prefill_prep_x_kernel<<<(unsigned) ((n_tokens + 7) / 8), 256, 0, st>>>(x, x_kind, n_tokens, L.n_embd, xh, xinv);
+    prefill_gemm_kernel<PMODE_GU><<<dim3((unsigned) (L.n_ff / 64), (unsigned) cap_tiles), kThreadsP, kSmemP, st>>>(a);
+    prefill_gemm_kernel<PMODE_DOWN><<<dim3((unsigned) (L.n_embd / kTileN), (unsigned) cap_tiles), kThreadsP, kSmemP, st>>>(a);
+    return launch_status();
+}

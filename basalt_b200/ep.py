@@ -13,6 +13,11 @@ Step on rank r of N (router weights replicated, experts [r E/N, (r+1) E/N) local
   3. gather the activation rows in send order and all-to-all them;
   4. run the local grouped experts over the received rows (they sit in local HBM: no peer-memory loads in any kernel);
   5. all-to-all the result rows back (the mirror of 3) and combine them, with the locally computed shared expert.
+That is EPMoELayerA2A.  EPMoELayer is the low-latency form for decode-sized steps, with fixed-size collectives and no host
+round trip: all-gather the activations and the routing (a few MB), dispatch ALL pairs on every rank, run only the local
+experts' groups (bsx_plan_groups skips experts held elsewhere), sum each token's local pairs (bsx_combine_partial) and
+reduce-scatter the partial sums to the tokens' owners.  The cross-rank sum is NCCL's, so results match the single-GPU
+layer to rounding, not bit for bit.
 
 The planning functions are pure numpy so that the same code is exercised by the CPU tests (gloo, world_size 2) and the
 GPU path.
@@ -67,8 +72,9 @@ def ep_recv_plan(cnt_all: np.ndarray, rank: int):
     return (experts + lo).astype(np.int32), start, rows
 
 
-class EPMoELayer:
-    """The expert-parallel layer on one rank.  `blobs` holds this rank's experts only ([E/N][stride] uint8); the router gate,
+class EPMoELayerA2A:
+    """The expert-parallel layer on one rank, row all-to-all form (host-planned: one device-to-host read of the counts per
+    step, so it suits prompt-sized steps; every row is bit-identical to the single-GPU layer's).  `blobs` holds this rank's experts only ([E/N][stride] uint8); the router gate,
     bias and the shared expert are replicated."""
 
     def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, shared_blob=None, max_tokens: int = 64,
@@ -153,3 +159,113 @@ class EPMoELayer:
             cur.wait_stream(self.side)
             shared = self.s_out[:T]
         return moe.moe_combine(self.rows_back[:n], slot.reshape(T, a.k), self.w[:T], shared, None, self.y[:T])
+
+
+class EPMoELayer:
+    """The expert-parallel layer on one rank, collective form: all-gather (activations, routing) -> local experts ->
+    partial combine -> reduce-scatter.  Every size is fixed by (world, max_tokens), nothing is read back to the host, and
+    every rank must pass the same number of tokens per step."""
+
+    def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, shared_blob=None, max_tokens: int = 64, group=None):
+        import torch
+        import torch.distributed as dist
+        from . import capi, moe
+        self.torch, self.dist, self.moe, self.capi = torch, dist, moe, capi
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.E, self.L, self.args = n_expert_total, layout, args
+        first = ep_partition(n_expert_total, self.world)
+        self.lo, self.hi = int(first[self.rank]), int(first[self.rank + 1])
+        self.gate_w, self.bias, self.blobs, self.shared_blob = gate_w, bias, blobs, shared_blob
+        dev = blobs.device
+        self.dev = dev
+        El, stride = blobs.shape
+        assert El == self.hi - self.lo
+        table = np.zeros(n_expert_total, np.int64)                 # 0 = an expert another rank holds
+        table[self.lo:self.hi] = blobs.data_ptr() + np.arange(El, dtype=np.int64) * stride
+        self.blob_table = torch.from_numpy(table).to(dev)
+        W, T, k, H = self.world, max_tokens, args.k, layout.n_embd
+        self.max_tokens = T
+        n = W * T * k
+        f32, i32 = torch.float32, torch.int32
+        self.logits = torch.empty((T, n_expert_total), dtype=f32, device=dev)
+        self.route = torch.empty((T, 2 * k), dtype=i32, device=dev)          # [ids | weight bits] of the rank's own tokens
+        self.route_all = torch.empty((W * T, 2 * k), dtype=i32, device=dev)
+        self.ids_all = torch.empty((W * T, k), dtype=i32, device=dev)
+        self.w_all = torch.empty((W * T, k), dtype=f32, device=dev)
+        self.cnt = torch.empty(n_expert_total, dtype=i32, device=dev)
+        self.off = torch.empty(n_expert_total + 1, dtype=i32, device=dev)
+        self.slot = torch.empty(n, dtype=i32, device=dev)
+        self.src = torch.empty(n, dtype=i32, device=dev)
+        self.dscratch = torch.empty(capi.lib().bsx_dispatch_scratch_bytes(n, n_expert_total), dtype=torch.uint8, device=dev)
+        self.ptr = torch.zeros(n_expert_total + 2, dtype=torch.int64, device=dev)
+        self.start = torch.zeros(n_expert_total + 2, dtype=i32, device=dev)
+        self.n_groups = torch.zeros(1, dtype=i32, device=dev)
+        self.ent_dst = torch.zeros(n, dtype=i32, device=dev)
+        self.ent_tok = torch.zeros(n, dtype=i32, device=dev)
+        self.rows = torch.empty((n, H), dtype=f32, device=dev)
+        self.scratch = torch.empty(moe.native_expert_scratch_bytes(layout, n), dtype=torch.uint8, device=dev)
+        self.y_part = torch.empty((W * T, H), dtype=f32, device=dev)
+        self.y = torch.empty((T, H), dtype=f32, device=dev)
+        self.y_sum = torch.empty((T, H), dtype=f32, device=dev)
+        self.ones = torch.ones((T, 1), dtype=f32, device=dev)
+        self.x_all = None
+        self.side = torch.cuda.Stream(device=dev)
+        self.time_experts, self.last_expert_ms, self.last_groups = False, 0.0, 0
+        if shared_blob is not None:
+            self.s_out = torch.empty((T, H), dtype=f32, device=dev)
+            self.s_scratch = torch.empty(capi.lib().bsx_gated_mlp_scratch_bytes(C.byref(layout), T), dtype=torch.uint8, device=dev)
+
+    def forward(self, x):
+        torch, dist, moe, capi = self.torch, self.dist, self.moe, self.capi
+        lib, a, L = capi.lib(), self.args, self.L
+        T, k, W, H = x.shape[0], a.k, self.world, L.n_embd
+        assert T == self.max_tokens, "the collective form exchanges fixed-size buffers: pass max_tokens rows"
+        cur = torch.cuda.current_stream()
+        st = moe._stream(cur)
+        p = moe._p
+        # 1. route the rank's own tokens; ids and weights travel as one int32 row per token
+        ids_own, w_own = self.route[:, :k], self.route[:, k:].view(torch.float32)
+        ids_c = torch.empty((T, k), dtype=torch.int32, device=self.dev)
+        w_c = torch.empty((T, k), dtype=torch.float32, device=self.dev)
+        moe.router_x(x, self.gate_w, self.bias, a, self.logits, ids_c, w_c)
+        ids_own.copy_(ids_c)
+        w_own.copy_(w_c)
+        if self.shared_blob is not None:     # the shared expert of the rank's own tokens, beside the exchange
+            self.side.wait_stream(cur)
+            with torch.cuda.stream(self.side):
+                moe.gated_mlp(L, self.shared_blob, x, cap_tok=T, out=self.s_out, scratch=self.s_scratch)
+        # 2. everyone gets every token's activations and routing
+        if self.x_all is None or self.x_all.dtype != x.dtype:
+            self.x_all = torch.empty((W * T, H), dtype=x.dtype, device=self.dev)
+        dist.all_gather_into_tensor(self.x_all, x, group=self.group)
+        dist.all_gather_into_tensor(self.route_all, self.route, group=self.group)
+        self.ids_all.copy_(self.route_all[:, :k])
+        self.w_all.copy_(self.route_all[:, k:].view(torch.float32))
+        # 3. dispatch all pairs; groups only for the experts held here
+        n = W * T * k
+        capi.check("bsx_dispatch", lib.bsx_dispatch(p(self.ids_all), n, k, self.E, p(self.cnt), p(self.off), p(self.slot), p(self.src), 0, None, None,
+                                                     p(self.dscratch), st))
+        capi.check("bsx_plan_groups", lib.bsx_plan_groups(p(self.cnt), p(self.off), p(self.src), self.E, p(self.blob_table), p(self.ptr), p(self.start),
+                                                           p(self.n_groups), p(self.ent_dst), p(self.ent_tok), st))
+        # 4. the local experts over the rows routed to them (outputs land on their dispatch rows)
+        if self.time_experts:
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(cur)
+        moe.native_expert_grouped(L, self.ptr, self.start, self.n_groups, self.ent_dst, self.ent_tok, self.hi - self.lo, n, self.x_all, self.scratch,
+                                  self.rows, n_x_rows=W * T)
+        if self.time_experts:
+            t1.record(cur)
+            t1.synchronize()
+            self.last_expert_ms, self.last_groups = t0.elapsed_time(t1), int(self.n_groups.item())
+        # 5. each token's local pairs summed here, the ranks' partial sums reduced onto the token's owner
+        capi.check("bsx_combine_partial", lib.bsx_combine_partial(p(self.rows), p(self.slot), p(self.w_all), p(self.ids_all), self.lo, self.hi, W * T, k, H,
+                                                                   p(self.y_part), st))
+        if self.shared_blob is None:
+            dist.reduce_scatter_tensor(self.y, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
+            return self.y
+        dist.reduce_scatter_tensor(self.y_sum, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
+        cur.wait_stream(self.side)
+        # y = 1 * sum + shared, through the combine kernel (one "row" per token)
+        capi.check("bsx_combine", lib.bsx_combine(p(self.y_sum), None, p(self.ones), p(self.s_out), None, T, 1, H, p(self.y), st))
+        return self.y

@@ -203,6 +203,20 @@ def native_expert_grouped(L: ExpertLayout, grp_ptr, grp_start, n_groups, ent_dst
     return out
 
 
+def experts_prefill(L: ExpertLayout, blob_table, off, src, tiles, n_tiles, x, n_rows: int, dm=None, scratch=None, status=None, stream=None):
+    """The prompt path's grouped experts (Basalt: fp4::run_group, include/basalt/prefill/moe_fp4.hpp:104-113) over a dispatch's
+    expert-sorted rows; returns (dm [n_rows][n_embd] fp32, status int32[1])."""
+    T = x.shape[0]
+    dev = x.device
+    dm = torch.empty((max(n_rows, 1), L.n_embd), dtype=torch.float32, device=dev) if dm is None else dm
+    if scratch is None:
+        scratch = torch.empty(capi.lib().bsx_experts_prefill_scratch_bytes(C.byref(L), T, n_rows), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev) if status is None else status
+    check("bsx_experts_prefill", capi.lib().bsx_experts_prefill(C.byref(L), _p(blob_table), _p(off), _p(src), _p(tiles), _p(n_tiles), tiles.shape[0],
+                                                                 n_rows, _p(x), _x_kind(x), T, _p(scratch), _p(dm), _p(status), _stream(stream)))
+    return dm, status
+
+
 def gated_mlp(L: ExpertLayout, blob, x, cap_tok: Optional[int] = None, out=None, scratch=None, stream=None):
     """basalt::kernels::gated_mlp_clamped (iq_kernels.hpp:93-98): a dense gated MLP (a shared expert) over the rows of x; the
     SwiGLU limit is the layout's."""

@@ -208,6 +208,19 @@ BSX_API int32_t bsx_gated_mlp(const bsx_expert_layout* layout, const void* blob,
  * alone.  Mirrors native_expert_set_mode's phase (iq_kernels.hpp:113-115).  Process-wide; set it back to 0. */
 BSX_API void bsx_experts_set_phase(int32_t phase);
 
+/* ---- a11: prompt-sized grouped experts on the tcgen05 tensor cores (NVFP4 blobs).  Replaces fp4::run_group / run_experts
+ * (include/basalt/prefill/moe_fp4.hpp:43-113, src/prefill/moe_fp4.cu:604-687): for the expert-sorted rows of a bsx_dispatch
+ * (off, src, and its tile list with tile_rows = 128), gate/up through the rows' tokens, SwiGLU, down; dm[row] (fp32,
+ * unweighted, row = dispatch slot) is what bsx_combine reads.  blob_table[e] = device address of expert e's blob.
+ * x: fp32 or bf16 [n_tokens][n_embd].  Weights are decoded exactly to fp16 and multiplied by fp16 activations with fp32
+ * accumulation (kind::f16), so results sit ~2e-4 from the dequantised fp32 reference.  n_embd % 128 == 0, n_ff % 64 == 0.
+ * status: a device int32 the caller zeroes; a kernel that gives up on a bounded wait sets bit 0 there instead of hanging.
+ * scratch: bsx_experts_prefill_scratch_bytes(layout, n_tokens, cap_rows); cap_tiles >= the tile count, <= 65535. */
+BSX_API size_t bsx_experts_prefill_scratch_bytes(const bsx_expert_layout* layout, int64_t n_tokens, int64_t cap_rows);
+BSX_API int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const unsigned long long* blob_table, const int32_t* off,
+                                    const int32_t* src, const int32_t* tiles, const int32_t* n_tiles, int64_t cap_tiles, int64_t cap_rows,
+                                    const void* x, int32_t x_kind, int64_t n_tokens, void* scratch, float* dm, int32_t* status, void* stream);
+
 /* ---- a13: weighted combine.  Replaces native_moe_combine[_multi] (include/basalt/models/qwen4exp/kernels/native_moe.hpp:5-15,
  * native_moe.cu:36-85), moe_combine (src/models/qwen4exp/prefill/kernels.cu:438-449,705-709) and weighted_sum_tokens
  * (src/models/deepseek41/prefill_ffn.cu:33-50).  y[t] = fma chain over j < k of weights[t][j] * rows[slot[t*k+j]] in j
@@ -216,6 +229,17 @@ BSX_API void bsx_experts_set_phase(int32_t phase);
  * bit-stable from run to run.  rows [n_rows][H] fp32, y [T][H] fp32, H % 4 == 0. */
 BSX_API int32_t bsx_combine(const float* rows, const int32_t* slot, const float* weights, const float* shared, const float* shared_gate,
                     int32_t T, int32_t k, int32_t H, float* y, void* stream);
+
+/* ---- expert parallelism (no counterpart in the reference, which moves rows between cards through host memory:
+ * include/basalt/models/qwen4exp/kernels/dec_moe.hpp:1-11).  bsx_plan_groups turns a dispatch (cnt, off, src over ALL experts)
+ * into the groups of the experts this device holds (blob_table[e] != 0): ptr/start/n_groups as bsx_moe_plan makes them,
+ * ent_dst[entry] = the entry's dispatch row, ent_tok[entry] = its token; arrays sized for every row.  E <= 1024.
+ * bsx_combine_partial is bsx_combine restricted to the pairs whose expert id lies in [e_lo, e_hi) - one rank's share of
+ * y, to be summed across ranks (reduce-scatter). */
+BSX_API int32_t bsx_plan_groups(const int32_t* cnt, const int32_t* off, const int32_t* src, int32_t E, const unsigned long long* blob_table,
+                                unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* ent_dst, int32_t* ent_tok, void* stream);
+BSX_API int32_t bsx_combine_partial(const float* rows, const int32_t* slot, const float* weights, const int32_t* ids, int32_t e_lo,
+                                    int32_t e_hi, int32_t T, int32_t k, int32_t H, float* y, void* stream);
 
 /* ---- device self-check helpers (host-side; no GPU needed): the block decoders compiled for the host, for tests. */
 BSX_API int32_t bsx_host_decode_row(int32_t type, const void* row, float* y, int64_t n);

@@ -39,14 +39,22 @@ def _rank(rank, world, port, q):
     g = torch.Generator(device=dev).manual_seed(10 + rank)
     x = torch.randn((T - 5 * rank, H), generator=g, device=dev).bfloat16()      # ragged token counts across ranks
     El = E // world
-    layer = ep.EPMoELayer(gw, None, bd[rank * El:(rank + 1) * El].contiguous(), L, args, E, shared_blob=bd[E], max_tokens=T)
+    own = bd[rank * El:(rank + 1) * El].contiguous()
+    layer = ep.EPMoELayerA2A(gw, None, own, L, args, E, shared_blob=bd[E], max_tokens=T)
     y = layer.forward(x).clone()
     y2 = layer.forward(x).clone()
     single = moe.MoELayer(gw, None, bd[:E], L, args, shared_blob=bd[E], max_tokens=T)
     want = single.forward(x).clone()
+    # the collective form (fixed sizes: every rank passes T rows): equal to rounding, and stable from run to run
+    xf = torch.randn((T, H), generator=g, device=dev).bfloat16()
+    coll = ep.EPMoELayer(gw, None, own, L, args, E, shared_blob=bd[E], max_tokens=T)
+    yc = coll.forward(xf).clone()
+    yc2 = coll.forward(xf).clone()
+    wantc = single.forward(xf).clone()
     torch.cuda.synchronize()
+    relc = float((yc - wantc).norm() / wantc.norm())
     q.put((rank, bool(torch.equal(y.view(torch.int32), want.view(torch.int32))), bool(torch.equal(y.view(torch.int32), y2.view(torch.int32))),
-           float((y - want).abs().max())))
+           float((y - want).abs().max()), relc, bool(torch.equal(yc.view(torch.int32), yc2.view(torch.int32)))))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -64,6 +72,8 @@ def test_ep_two_gpus_matches_single_gpu(lib):
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    for rank, same, stable, err in res:
-        assert stable, f"rank {rank}: not bit-stable from run to run"
-        assert same, f"rank {rank}: differs from the single-GPU layer (max abs {err})"
+    for rank, same, stable, err, relc, stablec in res:
+        assert stable, f"rank {rank}: all-to-all form not bit-stable from run to run"
+        assert same, f"rank {rank}: all-to-all form differs from the single-GPU layer (max abs {err})"
+        assert relc < 1e-5, f"rank {rank}: collective form differs from the single-GPU layer (relative L2 {relc})"
+        assert stablec, f"rank {rank}: collective form not bit-stable from run to run"
