@@ -172,7 +172,10 @@ prep_image_kernel(ExpertArgs a, __half* __restrict__ img, float* __restrict__ in
             if (threadIdx.x == 255) s_base = before + x;
             __syncthreads();
         }
-        if (threadIdx.x == 0) *n_items = s_base;
+        if (threadIdx.x == 0) {
+            n_items[0] = s_base;
+            n_items[1] = 0;      // the work counter of the product kernel that follows
+        }
         return;
     }
     const int i = blockIdx.x * 8 + warp;   // image row
@@ -227,7 +230,7 @@ prep_image_kernel(ExpertArgs a, __half* __restrict__ img, float* __restrict__ in
 template <int MODE, int TERMS>
 __global__ void __launch_bounds__(kThreads, 2)
 nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __restrict__ inv, const int2* __restrict__ items,
-                 const int* __restrict__ n_items, int tiles_per_warp) {
+                 int* __restrict__ n_items, int tiles_per_warp, int n_row_blocks) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int64_t K = MODE == MODE_GU ? a.L.n_embd : a.L.n_ff;
     const int n_gran = (int) (K >> 6);                       // 64-column granules
@@ -247,14 +250,13 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
     if (threadIdx.x < 4) zero[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
 
     const int64_t n_rows = MODE == MODE_GU ? a.L.n_ff : a.L.n_embd;      // neurons (pairs) or down rows
-    // a block covers tiles_per_warp row tiles per warp; tile j of warp w starts at row (or neuron) r0 + j * tile_stride
+    // A work unit is (pass, row block): a row block covers tiles_per_warp row tiles per warp; tile j of warp w starts at row (or
+    // neuron) r0 + j * tile_stride.  The blocks are persistent and draw work units from a counter in global memory (zeroed by
+    // the image kernel that runs before this one), so no block idles while another still has several units queued.
     constexpr int kTileRows = MODE == MODE_GU ? 8 : 16;
     constexpr int tile_stride = kWarps * kTileRows;
-    const int64_t r0 = (int64_t) blockIdx.x * tiles_per_warp * tile_stride + warp * kTileRows;
-    int live_tiles = 0;
-    while (live_tiles < tiles_per_warp && r0 + (int64_t) live_tiles * tile_stride < n_rows) ++live_tiles;
+    __shared__ int s_work;
     const int n_chunks = n_gran >> 2;
-    const int n_units = live_tiles * n_chunks;               // (tile, chunk) stages this warp streams per pass
     const int pieces_per_col = (int) (K >> 3);               // 16-byte pieces of one image
 
     // this lane's copy duty inside a stage: pieces lane, lane + 32, ... (< 144); row = piece / 9
@@ -268,8 +270,18 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
         cp_dst[j] = (uint32_t) (cp_row[j] * kRowBytes + cp_off[j]);
     }
 
-    const int n_it = *n_items;
-    for (int item = blockIdx.y; item < n_it; item += gridDim.y) {
+    const int n_work = n_items[0] * n_row_blocks;
+    for (;;) {
+        __syncthreads();   // the previous unit is done with xs and s_work
+        if (threadIdx.x == 0) s_work = atomicAdd(&n_items[1], 1);
+        __syncthreads();
+        const int work = s_work;
+        if (work >= n_work) break;
+        const int item = work / n_row_blocks, rb = work - item * n_row_blocks;
+        const int64_t r0 = (int64_t) rb * tiles_per_warp * tile_stride + warp * kTileRows;
+        int live_tiles = 0;
+        while (live_tiles < tiles_per_warp && r0 + (int64_t) live_tiles * tile_stride < n_rows) ++live_tiles;
+        const int n_units = live_tiles * n_chunks;               // (tile, chunk) stages this warp streams for this unit
         const int2 it = items[item];
         const int grp = it.x;
         const uint8_t* blob = reinterpret_cast<const uint8_t*>(a.grp_ptr[grp]);
@@ -311,7 +323,6 @@ nvfp4_mma_kernel(ExpertArgs a, const __half* __restrict__ img, const float* __re
             const int eb = it.y;
             const int ntok = min(NTOK, e1 - eb);
             const int ncol = ntok * TERMS;
-            __syncthreads();   // the previous pass has finished reading xs
             if (threadIdx.x < ntok)
                 s_ir[threadIdx.x] = (MODE == MODE_GU && a.n_x_rows > 0) ? a.ent_tok[eb + threadIdx.x] : eb + (int) threadIdx.x;
             __syncthreads();
@@ -429,7 +440,7 @@ size_t smem_bytes(int64_t K) { return (size_t) K * kCols * 2 + 1152 + (size_t) k
 size_t align256(size_t v) { return (v + 255) & ~(size_t) 255; }
 
 template <int MODE, int TERMS>
-int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, const int2* items, const int* n_items, cudaStream_t st) {
+int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, const int2* items, int* n_items, cudaStream_t st) {
     const int64_t K = MODE == MODE_GU ? a.L.n_embd : a.L.n_ff;
     const size_t smem = smem_bytes(K);
     static bool configured[64] = {};
@@ -441,20 +452,17 @@ int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, const i
         configured[dev] = true;
     }
     const int64_t rows = MODE == MODE_GU ? a.L.n_ff : a.L.n_embd;
-    // a block streams ~256 KB of weights per pass, enough to hide its start-up (activation copy, first loads); the row
-    // tiles are dealt evenly over the blocks
+    // a work unit streams ~150 KB of weights (enough to hide its start-up: activation copy, first loads); the row tiles of an
+    // expert are dealt evenly over the units
     const int64_t tile_bytes = (int64_t) kWarps * 16 * (K / 64 * 36);
     const int64_t tile_rows = MODE == MODE_GU ? kWarps * 8 : kWarps * 16;
     const int64_t n_tiles = (rows + tile_rows - 1) / tile_rows;
-    int64_t tpw0 = (256 * 1024 + tile_bytes - 1) / tile_bytes;
+    int64_t tpw0 = (150 * 1024 + tile_bytes - 1) / tile_bytes;
     tpw0 = tpw0 < 1 ? 1 : tpw0 > 8 ? 8 : tpw0;
     const int64_t n_blocks = (n_tiles + tpw0 - 1) / tpw0;
     const int tpw = (int) ((n_tiles + n_blocks - 1) / n_blocks);
-    const int per_block = (int) tile_rows * tpw;
-    constexpr int NTOK = kCols / TERMS;
-    const int64_t cap_items = a.cap_groups + a.cap_entries / NTOK + 1;
-    const unsigned gy = (unsigned) (cap_items > 4096 ? 4096 : cap_items);
-    nvfp4_mma_kernel<MODE, TERMS><<<dim3((unsigned) ((rows + per_block - 1) / per_block), gy), kThreads, smem, st>>>(a, img, inv, items, n_items, tpw);
+    const int n_row_blocks = (int) ((n_tiles + tpw - 1) / tpw);
+    nvfp4_mma_kernel<MODE, TERMS><<<(unsigned) (2 * sm_count()), kThreads, smem, st>>>(a, img, inv, items, n_items, tpw, n_row_blocks);
     return launch_status();
 }
 

@@ -34,7 +34,7 @@ constexpr int kBlockK = 64;        // fp16 per k-block: one 128-byte swizzle row
 constexpr int kStagesP = 3;
 constexpr int kProducers = 128;    // warps 1..4
 constexpr int kThreadsP = 160;
-constexpr uint32_t kSpinLimit = 1u << 22;   // bounded mbarrier waits (~ seconds), then an error status
+constexpr unsigned long long kWaitNs = 200ull * 1000 * 1000;   // every mbarrier wait gives up after 200 ms and reports an error status
 constexpr float kHScale = 0.25f;   // the SwiGLU output is stored as fp16(h / 4): fp16 then holds |h| up to 2.6e5
 
 enum { PMODE_GU = 0, PMODE_DOWN = 1 };
@@ -48,19 +48,25 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
 }
-// waits for the phase with the given parity; false after kSpinLimit polls
+// Waits for the phase with the given parity, at most kWaitNs of wall time (non-blocking test_wait polls, so the bound is
+// the clock's, not a multiple of try_wait's own suspend time); false when it gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t a = smem_u32(bar);
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0;; ++i) {
         uint32_t ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
                      : "=r"(ok)
                      : "r"(a), "r"(parity)
                      : "memory");
         if (ok) return true;
-        if (i > 64) __nanosleep(64);
+        if (i < 32) continue;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(now));
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kWaitNs) return false;
+        __nanosleep(32);
     }
-    return false;
 }
 
 // K-major, 128-byte swizzle: 8-row atoms of 1024 bytes stacked along M/N (stride byte offset 1024), descriptor version 1
@@ -80,6 +86,7 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    __syncwarp();   // the load is warp-wide: all 32 lanes must arrive together
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
         "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
@@ -183,6 +190,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 0) {
+        __syncwarp();   // lane 0 initialised the barriers above: reconverge before the warp-wide allocation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t) kTileN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
@@ -276,11 +284,14 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
         if (ok) ok = mbar_wait(accum, 0u);
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (!ok) atomicOr(a.status, kStatusTimeout);
-        if (ok && row_live) {
+        // tcgen05.ld is warp-wide (.sync.aligned): every lane of the warp runs the loads together or none does; only the
+        // global stores depend on whether the lane's row exists
+        const bool warp_ok = __all_sync(kFull, ok);
+        if (warp_ok) {
             const uint32_t lane_base = (uint32_t) ((warp & 3) * 32) << 16;
             const float* tail = reinterpret_cast<const float*>(blob + a.L.bytes - 16);
             if (MODE == PMODE_GU) {
-                const float f = a.xinv[a.src[row0 + p]] * 256.f;
+                const float f = row_live ? a.xinv[a.src[row0 + p]] * 256.f : 0.f;
                 const float sg = tail[0] * f, su = tail[1] * f;
                 __half* hrow = a.h + (size_t) (row0 + p) * a.L.n_ff + n0;
 #pragma unroll
@@ -295,7 +306,8 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
                         out[(j & ~15) + perm16(j & 15)] = __float2half_rn(fminf(fmaxf(hv, -65504.f), 65504.f));
                     }
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(hrow + c0)[v] = reinterpret_cast<const uint4*>(out)[v];
+                    for (int v = 0; v < 4; ++v)
+                        if (row_live) reinterpret_cast<uint4*>(hrow + c0)[v] = reinterpret_cast<const uint4*>(out)[v];
                 }
             } else {
                 const float f = tail[2] * (256.f / kHScale);
@@ -306,7 +318,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
                     tmem_ld32(tmem + lane_base + (uint32_t) c0, d);
 #pragma unroll
                     for (int v = 0; v < 8; ++v)
-                        reinterpret_cast<float4*>(orow + c0)[v] = make_float4(__uint_as_float(d[4 * v]) * f, __uint_as_float(d[4 * v + 1]) * f,
+                        if (row_live) reinterpret_cast<float4*>(orow + c0)[v] = make_float4(__uint_as_float(d[4 * v]) * f, __uint_as_float(d[4 * v + 1]) * f,
                                                                                __uint_as_float(d[4 * v + 2]) * f, __uint_as_float(d[4 * v + 3]) * f);
                 }
             }
@@ -316,6 +328,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     if (warp == 0) {
+        __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t) kTileN) : "memory");
     }

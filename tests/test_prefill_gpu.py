@@ -77,7 +77,8 @@ def test_prefill_skips_experts_held_elsewhere_and_matches_decode_kernels(lib, cu
     ptr = torch.zeros(E + 2, dtype=torch.int64, device="cuda"); start = torch.zeros(E + 2, dtype=torch.int32, device="cuda")
     ng = torch.zeros(1, dtype=torch.int32, device="cuda"); ed = torch.zeros(n, dtype=torch.int32, device="cuda"); et = torch.zeros(n, dtype=torch.int32, device="cuda")
     st = torch.cuda.current_stream().cuda_stream or 1
-    capi.check("plan", lib.bsx_plan_groups(dev(cnt).data_ptr(), dev(off).data_ptr(), dev(src).data_ptr(), E, dev(table).data_ptr(), ptr.data_ptr(),
+    dcnt, doff, dsrc, dtab = dev(cnt), dev(off), dev(src), dev(table)     # kept alive until the kernels have run
+    capi.check("plan", lib.bsx_plan_groups(dcnt.data_ptr(), doff.data_ptr(), dsrc.data_ptr(), E, dtab.data_ptr(), ptr.data_ptr(),
                                            start.data_ptr(), ng.data_ptr(), ed.data_ptr(), et.data_ptr(), st))
     rows = torch.zeros((n, H), dtype=torch.float32, device="cuda")
     scr = torch.empty(moe.native_expert_scratch_bytes(L, n), dtype=torch.uint8, device="cuda")
