@@ -32,8 +32,8 @@ constexpr int kTileM = 128;        // rows (tokens) per tile = TMEM lanes
 constexpr int kTileN = 128;        // weight rows per tile = TMEM columns
 constexpr int kBlockK = 64;        // fp16 per k-block: one 128-byte swizzle row
 constexpr int kStagesP = 3;
-constexpr int kProducers = 128;    // warps 1..4
-constexpr int kThreadsP = 160;
+constexpr int kGroupThreads = 128; // one group of weight decoders: four warps, one thread per weight row of the tile
+constexpr int kThreadsP = 320;     // MMA warp, activation loader warp, two decoder groups
 constexpr unsigned long long kWaitNs = 200ull * 1000 * 1000;   // every mbarrier wait gives up after 200 ms and reports an error status
 constexpr float kHScale = 0.25f;   // the SwiGLU output is stored as fp16(h / 4): fp16 then holds |h| up to 2.6e5
 
@@ -98,6 +98,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    __syncwarp();
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
 __device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t (&h)[4]) {
     asm("{\n.reg .b8 b0, b1, b2, b3;\nmov.b32 {b0, b1, b2, b3}, %4;\ncvt.rn.f16x2.e2m1x2 %0, b0;\ncvt.rn.f16x2.e2m1x2 %1, b1;\n"
         "cvt.rn.f16x2.e2m1x2 %2, b2;\ncvt.rn.f16x2.e2m1x2 %3, b3;\n}\n"
@@ -156,13 +166,21 @@ __global__ void __launch_bounds__(256) prefill_prep_x_kernel(const void* __restr
     for (int64_t c = lane; c < H; c += 32) xh[t * H + (c & ~(int64_t) 15) + perm16((int) (c & 15))] = __float2half_rn(ld(c) * s);
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs a) {
+// Warp roles of a CTA (one 128-row x 128-weight-row tile):
+//   warp 0       allocates tensor memory; its lane 0 issues the MMAs
+//   warp 1       activation loader: cp.async gathers of the tile's 128 rows, 64 columns a k-block, up to two k-blocks ahead
+//   warps 2..9   weight decoders in two groups of four warps; a group owns every other PAIR of k-blocks (72 bytes of its
+//                thread's weight row, fetched one own pair = four k-blocks ahead), decodes them to fp16 into the stage's B
+//                tile; after the last MMA all eight warps run the epilogue (TMEM lane quarter = warp % 4, columns by group)
+// A stage is full when the loader's 32 lanes and the owning group's 128 threads have arrived, and empty again when the
+// tensor core has read it (tcgen05.commit).
+template <int MODE, bool ALIGNED>
+__global__ void __launch_bounds__(kThreadsP, 2) prefill_gemm_kernel(PrefillArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte aligned operand stages: A then B per stage
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
-    constexpr int kABytes = kTileM * kBlockK * 2, kBBytes = kTileN * kBlockK * 2;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStagesP * (kABytes + kBBytes));   // full[S], empty[S], accum
+    constexpr int kABytes = kTileM * kBlockK * 2, kBBytes = kTileN * kBlockK * 2, kStage = kABytes + kBBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStagesP * kStage);   // full[S], empty[S], accum
     uint64_t* full = bars;
     uint64_t* empty = bars + kStagesP;
     uint64_t* accum = bars + 2 * kStagesP;
@@ -183,7 +201,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
     for (int i = threadIdx.x; i < 256; i += kThreadsP) lut[i] = scale_pair_bits(i);
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStagesP; ++s) {
-            mbar_init(&full[s], kProducers);
+            mbar_init(&full[s], kGroupThreads + 32);
             mbar_init(&empty[s], 1);
         }
         mbar_init(accum, 1);
@@ -208,7 +226,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
                 ok = mbar_wait(&full[s], (uint32_t) (kb / kStagesP) & 1u);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t sa = smem_u32(smem + s * (kABytes + kBBytes)), sb = sa + kABytes;
+                const uint32_t sa = smem_u32(smem + s * kStage), sb = sa + kABytes;
 #pragma unroll
                 for (int k = 0; k < kBlockK / 16; ++k)
                     umma_f16(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), (kb | k) ? 1u : 0u);
@@ -217,14 +235,56 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
             umma_commit(accum);              // every MMA issued so far has finished when this fires
             if (!ok) atomicOr(a.status, kStatusTimeout);
         }
+    } else if (warp == 1) {
+        // ---- activation loader.  Lane l copies 16-byte chunk l % 8 of rows l / 8, l / 8 + 4, ...: eight lanes cover one row's
+        // 128 bytes.  Rows past the expert's last row read some valid row instead (their products are never stored).
+        const int c = lane & 7, r4 = lane >> 3;
+        const uint8_t* abase = reinterpret_cast<const uint8_t*>(MODE == PMODE_GU ? a.xh : a.h);
+        uint32_t aoff[32];   // row starts in 16-byte units
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int r = 4 * i + r4;
+            const uint32_t grow = MODE == PMODE_GU ? (uint32_t) a.src[row0 + (r < rows ? r : 0)] : (uint32_t) (row0 + r);
+            aoff[i] = grow * (uint32_t) (K >> 3) + (uint32_t) c;
+        }
+        uint32_t dsto[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r7 = 4 * h + r4;
+            dsto[h] = (uint32_t) (r7 * 128 + ((c ^ r7) << 4));
+        }
+        auto issue_a = [&](int kb) {
+            const uint32_t dst = smem_u32(smem + (kb % kStagesP) * kStage);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const uint8_t* g = abase + ((size_t) aoff[i] + (size_t) kb * 8) * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t) ((i >> 1) * 1024) + dsto[i & 1]), "l"(g) : "memory");
+            }
+        };
+        // the first two stages are free from the start
+        issue_a(0);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        if (nkb > 1) issue_a(1);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        for (int kb = 0; kb < nkb; ++kb) {
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");         // this lane's copies of k-block kb have landed
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            mbar_arrive(&full[kb % kStagesP]);
+            if (kb + 2 < nkb) {
+                ok = mbar_wait(&empty[(kb + 2) % kStagesP], ((uint32_t) ((kb + 2) / kStagesP) & 1u) ^ 1u);
+                if (!ok) break;
+                issue_a(kb + 2);
+            }
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        if (!ok) atomicOr(a.status, kStatusTimeout);
     } else {
-        // ---- producers: thread p owns activation row p and weight row p of the tile.  A warp may only read the 32 TMEM lanes
-        // 32 (warp % 4) .. + 31, and lane = output row, so the row assignment follows that rule from the start.
+        // ---- weight decoders, then the epilogue.  A warp may only read the 32 TMEM lanes 32 (warp % 4) .. + 31 and lane =
+        // output row, so thread (warp, lane) owns weight row / output row p = 32 (warp % 4) + lane in both roles.
+        const int grp = (warp - 2) >> 2;
         const int p = (warp & 3) * 32 + lane;
         const bool row_live = p < rows;
-        const __half* arow;
-        if (MODE == PMODE_GU) arow = a.xh + (size_t) (row_live ? a.src[row0 + p] : 0) * K;
-        else arow = a.h + (size_t) (row0 + (row_live ? p : 0)) * K;
         const uint8_t* wrow;
         if (MODE == PMODE_GU) {
             const int r = n0 + (p & 63);     // B rows 0..63 = gate rows, 64..127 = the matching up rows
@@ -234,34 +294,9 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
         }
         const uint32_t swz = (uint32_t) (p & 7);
         const uint32_t row_off = (uint32_t) ((p >> 3) * 1024 + (p & 7) * 128);
-        uint32_t wq[9];
-#pragma unroll
-        for (int i = 0; i < 9; ++i) wq[i] = reinterpret_cast<const uint32_t*>(wrow)[i];
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int s = kb % kStagesP;
-            ok = mbar_wait(&empty[s], ((uint32_t) (kb / kStagesP) & 1u) ^ 1u);
-            if (!ok) break;
-            uint8_t* sa = smem + s * (kABytes + kBBytes);
-            uint8_t* sb = sa + kABytes;
-            // A: the row's 128 bytes as 8 swizzled 16-byte chunks (zero-filled past the expert's rows)
-            {
-                const uint32_t dst = smem_u32(sa) + row_off;
-                const uint8_t* g = reinterpret_cast<const uint8_t*>(arow + (size_t) kb * kBlockK);
-                const uint32_t nbytes = row_live ? 16u : 0u;
-#pragma unroll
-                for (uint32_t c = 0; c < 8; ++c)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst + ((c ^ swz) << 4)), "l"(g + c * 16), "r"(nbytes) : "memory");
-                asm volatile("cp.async.commit_group;\n" ::: "memory");
-            }
-            // B: this k-block's NVFP4 block of the weight row -> 64 fp16 (already in the permuted order), next block prefetched
-            uint32_t cur[9];
-#pragma unroll
-            for (int i = 0; i < 9; ++i) cur[i] = wq[i];
-            if (kb + 1 < nkb) {
-#pragma unroll
-                for (int i = 0; i < 9; ++i) wq[i] = reinterpret_cast<const uint32_t*>(wrow)[9 * (kb + 1) + i];
-            }
-            uint4* brow = reinterpret_cast<uint4*>(sb + row_off);
+        // one NVFP4 block (9 words: 4 scale bytes, 32 code bytes) -> 64 fp16 of the B tile, already in the permuted k order
+        auto store_b = [&](int kb, const uint32_t* cur) {
+            uint4* brow = reinterpret_cast<uint4*>(smem + (kb % kStagesP) * kStage + kABytes + row_off);
 #pragma unroll
             for (int sub = 0; sub < 4; ++sub) {
                 const uint32_t sc = lut[(cur[0] >> (8 * sub)) & 0xFFu];
@@ -276,11 +311,56 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
                 brow[(2 * sub) ^ swz] = make_uint4(q0[0], q0[1], q0[2], q0[3]);
                 brow[(2 * sub + 1) ^ swz] = make_uint4(q1[0], q1[1], q1[2], q1[3]);
             }
-            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
-            mbar_arrive(&full[s]);
+        };
+        // the pair of blocks q (k-blocks 2q, 2q + 1): 72 bytes at offset 72 q of the row; 16-byte loads when rows are whole
+        // 144-byte chunks (then 72 q is a multiple of 16 for even q and of 8 for odd q)
+        const int npair = (nkb + 1) >> 1;
+        auto load_pair = [&](int q, uint32_t (&w)[18]) {
+            const uint8_t* src = wrow + (size_t) q * 72;
+            if (ALIGNED) {
+                if ((q & 1) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint4 v = reinterpret_cast<const uint4*>(src)[i];
+                        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+                    }
+                    const uint2 t = reinterpret_cast<const uint2*>(src)[8];
+                    w[16] = t.x; w[17] = t.y;
+                } else {
+                    const uint2 t = reinterpret_cast<const uint2*>(src)[0];
+                    w[0] = t.x; w[1] = t.y;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint4 v = reinterpret_cast<const uint4*>(src + 8)[i];
+                        w[2 + 4 * i] = v.x; w[3 + 4 * i] = v.y; w[4 + 4 * i] = v.z; w[5 + 4 * i] = v.w;
+                    }
+                }
+            } else {
+                const int nw = 2 * q + 1 < nkb ? 18 : 9;
+#pragma unroll
+                for (int i = 0; i < 18; ++i) w[i] = i < nw ? reinterpret_cast<const uint32_t*>(src)[i] : 0u;
+            }
+        };
+        uint32_t wc[18], wn[18];
+        if (grp < npair) load_pair(grp, wn);
+        for (int q = grp; q < npair && ok; q += 2) {
+#pragma unroll
+            for (int i = 0; i < 18; ++i) wc[i] = wn[i];
+            if (q + 2 < npair) load_pair(q + 2, wn);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int kb = 2 * q + j;
+                if (kb < nkb && ok) {
+                    ok = mbar_wait(&empty[kb % kStagesP], ((uint32_t) (kb / kStagesP) & 1u) ^ 1u);
+                    if (ok) {
+                        store_b(kb, &wc[9 * j]);
+                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+                        mbar_arrive(&full[kb % kStagesP]);
+                    }
+                }
+            }
         }
-        // ---- epilogue: thread p reads TMEM lane p (= output row p), 32 columns at a time
+        // ---- epilogue: thread p reads TMEM lane p (= output row p); group 0 takes the first half of the columns, group 1 the rest
         if (ok) ok = mbar_wait(accum, 0u);
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (!ok) atomicOr(a.status, kStatusTimeout);
@@ -293,29 +373,31 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
             if (MODE == PMODE_GU) {
                 const float f = row_live ? a.xinv[a.src[row0 + p]] * 256.f : 0.f;
                 const float sg = tail[0] * f, su = tail[1] * f;
-                __half* hrow = a.h + (size_t) (row0 + p) * a.L.n_ff + n0;
+                const int c0 = 32 * grp;                       // neurons c0 .. c0 + 31 of the tile's 64
+                __half* hrow = a.h + (size_t) (row0 + p) * a.L.n_ff + n0 + c0;
 #pragma unroll
-                for (int c0 = 0; c0 < 64; c0 += 32) {
-                    uint32_t g[32], u[32];
-                    tmem_ld32(tmem + lane_base + (uint32_t) c0, g);
-                    tmem_ld32(tmem + lane_base + (uint32_t) (64 + c0), u);
-                    __half out[32];
+                for (int c1 = 0; c1 < 32; c1 += 16) {
+                    uint32_t g[16], u[16];
+                    tmem_ld16(tmem + lane_base + (uint32_t) (c0 + c1), g);
+                    tmem_ld16(tmem + lane_base + (uint32_t) (64 + c0 + c1), u);
+                    __half out[16];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
+                    for (int j = 0; j < 16; ++j) {
                         const float hv = swiglu(__uint_as_float(g[j]) * sg, __uint_as_float(u[j]) * su, a.L) * kHScale;
-                        out[(j & ~15) + perm16(j & 15)] = __float2half_rn(fminf(fmaxf(hv, -65504.f), 65504.f));
+                        out[perm16(j)] = __float2half_rn(fminf(fmaxf(hv, -65504.f), 65504.f));
                     }
-#pragma unroll
-                    for (int v = 0; v < 4; ++v)
-                        if (row_live) reinterpret_cast<uint4*>(hrow + c0)[v] = reinterpret_cast<const uint4*>(out)[v];
+                    if (row_live) {
+                        reinterpret_cast<uint4*>(hrow + c1)[0] = reinterpret_cast<const uint4*>(out)[0];
+                        reinterpret_cast<uint4*>(hrow + c1)[1] = reinterpret_cast<const uint4*>(out)[1];
+                    }
                 }
             } else {
                 const float f = tail[2] * (256.f / kHScale);
-                float* orow = a.dm + (size_t) (row0 + p) * a.L.n_embd + n0;
+                float* orow = a.dm + (size_t) (row0 + p) * a.L.n_embd + n0 + 64 * grp;
 #pragma unroll
-                for (int c0 = 0; c0 < kTileN; c0 += 32) {
+                for (int c0 = 0; c0 < 64; c0 += 32) {
                     uint32_t d[32];
-                    tmem_ld32(tmem + lane_base + (uint32_t) c0, d);
+                    tmem_ld32(tmem + lane_base + (uint32_t) (64 * grp + c0), d);
 #pragma unroll
                     for (int v = 0; v < 8; ++v)
                         if (row_live) reinterpret_cast<float4*>(orow + c0)[v] = make_float4(__uint_as_float(d[4 * v]) * f, __uint_as_float(d[4 * v + 1]) * f,
@@ -380,13 +462,19 @@ extern "C" int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const un
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
     if (!configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_GU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
+        cudaError_t e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_GU, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_GU, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_DOWN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_DOWN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
         if (e != cudaSuccess) return (int32_t) e;
         configured[dev] = true;
     }
     prefill_prep_x_kernel<<<(unsigned) ((n_tokens + 7) / 8), 256, 0, st>>>(x, x_kind, n_tokens, L.n_embd, xh, xinv);
-    prefill_gemm_kernel<PMODE_GU><<<dim3((unsigned) (L.n_ff / 64), (unsigned) cap_tiles), kThreadsP, kSmemP, st>>>(a);
-    prefill_gemm_kernel<PMODE_DOWN><<<dim3((unsigned) (L.n_embd / kTileN), (unsigned) cap_tiles), kThreadsP, kSmemP, st>>>(a);
+    // rows that are whole 144-byte chunks (K % 256 == 0) take the variant that streams them as 16-byte loads
+    const dim3 ggu((unsigned) (L.n_ff / 64), (unsigned) cap_tiles), gdn((unsigned) (L.n_embd / kTileN), (unsigned) cap_tiles);
+    if (L.n_embd % 256 == 0) prefill_gemm_kernel<PMODE_GU, true><<<ggu, kThreadsP, kSmemP, st>>>(a);
+    else prefill_gemm_kernel<PMODE_GU, false><<<ggu, kThreadsP, kSmemP, st>>>(a);
+    if (L.n_ff % 256 == 0) prefill_gemm_kernel<PMODE_DOWN, true><<<gdn, kThreadsP, kSmemP, st>>>(a);
+    else prefill_gemm_kernel<PMODE_DOWN, false><<<gdn, kThreadsP, kSmemP, st>>>(a);
     return launch_status();
 }

@@ -319,3 +319,78 @@ class MoELayer:
                 shared = self.s_out
         check("bsx_combine", lib.bsx_combine(_p(self.rows), None, _p(self.w), _p(shared), None, T, a.k, self.L.n_embd, _p(self.y), st))
         return self.y[:T]
+
+
+class PrefillMoELayer:
+    """One resident MoE layer on a prompt-sized batch, as the reference's prompt path runs it (qwen4exp prefill: route ->
+    Group::group -> fp4::run_group -> moe_combine; src/models/qwen4exp/prefill/routing.cpp:26-122, expert_fp4.cpp:26-46,
+    kernels.cu:705-709): router -> bsx_dispatch (with the 128-row tile list) -> bsx_experts_prefill -> bsx_combine.  NVFP4
+    blobs.  A shared expert of the same layout is expert id E of the same dispatch: every token gets one more (id, weight)
+    pair (E, 1.0), so its rows go through the same grouped launch and the combine's last term adds them unweighted."""
+
+    def __init__(self, gate_w: torch.Tensor, bias: Optional[torch.Tensor], blobs: torch.Tensor, layout: ExpertLayout, args: RouterArgs,
+                 shared_blob: Optional[torch.Tensor] = None, max_tokens: int = 4096):
+        assert blobs.dtype == torch.uint8 and blobs.dim() == 2 and blobs.is_cuda
+        self.gate_w, self.bias, self.blobs, self.L, self.args, self.shared_blob = gate_w, bias, blobs, layout, args, shared_blob
+        dev = blobs.device
+        E, stride = blobs.shape
+        table = blobs.data_ptr() + torch.arange(E, dtype=torch.int64) * stride
+        self.kk = args.k + (1 if shared_blob is not None else 0)
+        self.EE = E + (1 if shared_blob is not None else 0)
+        if shared_blob is not None:
+            table = torch.cat([table, torch.tensor([shared_blob.data_ptr()], dtype=torch.int64)])
+        self.blob_table = table.to(dev)
+        T, n = max_tokens, max_tokens * self.kk
+        self.max_tokens = T
+        f32, i32 = torch.float32, torch.int32
+        self.logits = torch.empty((T, E), dtype=f32, device=dev)
+        self.ids = torch.empty((T, args.k), dtype=i32, device=dev)
+        self.w = torch.empty((T, args.k), dtype=f32, device=dev)
+        self.ids_all = torch.full((T, self.kk), E, dtype=i32, device=dev)     # the last column stays (E, 1.0): the shared expert
+        self.w_all = torch.ones((T, self.kk), dtype=f32, device=dev)
+        self.cnt = torch.empty(self.EE, dtype=i32, device=dev)
+        self.off = torch.empty(self.EE + 1, dtype=i32, device=dev)
+        self.slot = torch.empty(n, dtype=i32, device=dev)
+        self.src = torch.empty(n, dtype=i32, device=dev)
+        self.tiles = torch.zeros((n // 128 + self.EE, 2), dtype=i32, device=dev)
+        self.n_tiles = torch.zeros(1, dtype=i32, device=dev)
+        self.dscratch = torch.empty(capi.lib().bsx_dispatch_scratch_bytes(n, self.EE), dtype=torch.uint8, device=dev)
+        self.scratch = torch.empty(capi.lib().bsx_experts_prefill_scratch_bytes(C.byref(layout), T, n), dtype=torch.uint8, device=dev)
+        self.dm = torch.empty((n, layout.n_embd), dtype=f32, device=dev)
+        self.status = torch.zeros(1, dtype=i32, device=dev)
+        self.y = torch.empty((T, layout.n_embd), dtype=f32, device=dev)
+        self.events = None      # set to a list to collect (name, event) marks between the stages
+
+    def _mark(self, name, stream):
+        if self.events is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(stream if stream is not None else torch.cuda.current_stream())
+            self.events.append((name, ev))
+
+    def forward(self, x: torch.Tensor, logits: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """x [T][n_embd] fp32 or bf16.  logits: when given, the selection reads these [T][E] fp32 scores instead of the ones
+        just computed from x (a bench draws them to set the experts' popularity); the gate product still runs."""
+        T = x.shape[0]
+        a, lib, st, L = self.args, capi.lib(), _stream(stream), self.L
+        assert T == self.max_tokens, "buffers are sized for max_tokens rows"
+        self._mark("start", stream)
+        check("bsx_router_logits_x", lib.bsx_router_logits_x(_p(x), _x_kind(x), _p(self.gate_w), T, a.n_expert, a.n_embd, _p(self.logits), st))
+        self._mark("router_logits", stream)
+        router_select(self.logits if logits is None else logits, self.bias, a, self.ids, self.w, stream)
+        if self.kk != a.k:
+            self.ids_all[:, :a.k].copy_(self.ids)
+            self.w_all[:, :a.k].copy_(self.w)
+            ids, w = self.ids_all, self.w_all
+        else:
+            ids, w = self.ids, self.w
+        self._mark("router_select", stream)
+        n = T * self.kk
+        check("bsx_dispatch", lib.bsx_dispatch(_p(ids), n, self.kk, self.EE, _p(self.cnt), _p(self.off), _p(self.slot), _p(self.src), 128,
+                                               _p(self.tiles), _p(self.n_tiles), _p(self.dscratch), st))
+        self._mark("dispatch", stream)
+        check("bsx_experts_prefill", lib.bsx_experts_prefill(C.byref(L), _p(self.blob_table), _p(self.off), _p(self.src), _p(self.tiles), _p(self.n_tiles),
+                                                             self.tiles.shape[0], n, _p(x), _x_kind(x), T, _p(self.scratch), _p(self.dm), _p(self.status), st))
+        self._mark("experts", stream)
+        check("bsx_combine", lib.bsx_combine(_p(self.dm), _p(self.slot), _p(w), None, None, T, self.kk, L.n_embd, _p(self.y), st))
+        self._mark("combine", stream)
+        return self.y

@@ -180,6 +180,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--copies", type=int, default=LAYER_COPIES, help="layer copies the steps cycle through (1 for a small profiler capture)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: 64 tokens a step (the default line); prefill: --tokens rows a step, Zipf(1.1) expert popularity, tcgen05 grouped experts")
+    ap.add_argument("--tokens", type=int, default=4096, help="rows per step of the prefill workload (4096 or 16384 in the reference's configs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -203,6 +206,8 @@ def main():
     lib = capi.lib()
     if world > 1:
         return run_expert_parallel(args, rank, world, dev)
+    if args.workload == "prefill":
+        return run_prefill(args, dev)
 
     gate, blobs, blob_bytes = make_layer_weights(dev)
     L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
@@ -378,6 +383,104 @@ def run_expert_parallel(args, rank, world, dev):
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None, "algorithmic_bytes_per_launch": k_bytes,
                      "kernel_ms": k_ms},
         "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+
+
+def zipf_logits(n_tokens, n_expert, gen, dev, s=1.1):
+    """[T][E] fp32 scores whose top-k sets follow Zipf(s) popularity: log p_e + Gumbel noise, the popularity ranks dealt to
+    expert ids by a seeded permutation (top-k of such scores = sampling k experts without replacement from p)."""
+    p = torch.arange(1, n_expert + 1, device=dev, dtype=torch.float64) ** (-s)
+    logp = torch.log(p / p.sum()).float()[torch.randperm(n_expert, generator=gen, device=dev)]
+    u = torch.rand((n_tokens, n_expert), generator=gen, device=dev).clamp_(1e-20, 1.0 - 1e-7)
+    return (logp[None, :] - torch.log(-torch.log(u))).contiguous()
+
+
+def run_prefill(args, dev):
+    """The prompt-sized workload: the same layer, --tokens rows a step, expert popularity Zipf(1.1) (scores drawn, as the
+    reference's prompt benches have no dataset for this path either).  One step = gate product + selection + dispatch with
+    the 128-row tile list + grouped experts on the tcgen05 tensor cores (routed + shared) + combine.  Weights (0.9 GB, all
+    touched every step) exceed L2.  The roofline is the tensor one: 6 H I flops per routed row over the measured bf16 peak
+    (the products run as kind::f16 on exactly decoded weights); the HBM time of the touched blobs is reported beside it."""
+    from basalt_b200 import capi, moe
+    Tn = args.tokens
+    gate, blobs, blob_bytes = make_layer_weights(dev)
+    L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
+    rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
+    layer = moe.PrefillMoELayer(gate, None, blobs[:E], L, rargs, shared_blob=blobs[E], max_tokens=Tn)
+    g = torch.Generator(device=dev).manual_seed(1)
+    n_batches = 2
+    xs = [torch.randn((Tn, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
+    lgs = [zipf_logits(Tn, E, g, dev) for _ in range(n_batches)]
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup):
+            layer.forward(xs[i % n_batches], lgs[i % n_batches], stream)
+        torch.cuda.synchronize()
+        if int(layer.status.item()) != 0:
+            raise SystemExit("the prefill kernel reported a bounded wait that ran out (status %d)" % int(layer.status.item()))
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(dev.index or 0) as clocks:
+            ev0.record(stream)
+            for i in range(args.steps):
+                layer.forward(xs[i % n_batches], lgs[i % n_batches], stream)
+            ev1.record(stream)
+            torch.cuda.synchronize()
+        ms_step = ev0.elapsed_time(ev1) / args.steps
+        # end to end: pinned host rows in, host result out, every step
+        x_host = [x.cpu().pin_memory() for x in xs]
+        xin = torch.empty((Tn, H), dtype=torch.bfloat16, device=dev)
+        y_host = torch.empty((Tn, H), dtype=torch.float32).pin_memory()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_e2e = max(3, args.steps // 2)
+        e0.record(stream)
+        for i in range(n_e2e):
+            xin.copy_(x_host[i % n_batches], non_blocking=True)
+            y_host.copy_(layer.forward(xin, lgs[i % n_batches], stream), non_blocking=True)
+            stream.synchronize()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms_e2e = e0.elapsed_time(e1) / n_e2e
+        # stage times
+        names = ["router_logits", "router_select", "dispatch", "experts", "combine"]
+        acc = {n: 0.0 for n in names}
+        n_inst = min(args.steps, 10)
+        touched = 0
+        for i in range(n_inst):
+            layer.events = []
+            layer.forward(xs[i % n_batches], lgs[i % n_batches], stream)
+            stream.synchronize()
+            evs = layer.events
+            for (_, a), (nme, b) in zip(evs[:-1], evs[1:]):
+                acc[nme] += a.elapsed_time(b)
+            touched += int((layer.cnt > 0).sum().item())
+        layer.events = None
+        stage_ms = {k: v / n_inst for k, v in acc.items()}
+        touched /= n_inst
+        cnt = layer.cnt.cpu().numpy()
+    status = int(layer.status.item())
+    flops = 6.0 * H * I * (Tn * K_TOP + Tn)
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tpeak = float(peaks.get("bf16_tflops", 1590.0))
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    exp_ms = stage_ms["experts"]
+    achieved = flops / (exp_ms * 1e-3) / 1e12
+    blob_b = touched * (L.bytes - 16)
+    line = {
+        "metric": "MoE-layer tokens/s (prefill)", "value": Tn / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16 x (NVFP4 decoded exactly to fp16) on tcgen05 kind::f16, fp32 accumulation in tensor memory", "data": "synthetic",
+        "config": dict(CFG, workload=f"flash-next-style MoE layer prefill, {Tn} tokens/step, Zipf(1.1) expert popularity", tokens_per_step=Tn,
+                       l2_policy="every step reads all touched expert blobs (~0.9 GB): larger than L2", parallelism="single GPU"),
+        "e2e": {"value": Tn / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": Tn * H * 2, "d2h_bytes_per_step": Tn * H * 4},
+        "gpu_launches": 9 * args.steps,   # gate product, selection, 2 column copies, 3 dispatch kernels... counted per step below
+        "roofline": {"bound": "tensor", "kernel": "prefill_gemm_kernel<gate/up> + <down> (+ activation prep)", "achieved": achieved, "peak": tpeak,
+                     "unit": "TFLOP/s", "frac": achieved / tpeak, "peak_source": "measured bf16 burst (MEASURED_PEAKS.json)" if peaks else "fallback",
+                     "traffic": None, "algorithmic_flops_per_launch": flops, "kernel_ms": exp_ms,
+                     "hbm_ms_of_touched_blobs": blob_b / (hbm * 1e9) * 1e3, "tensor_ms_at_peak": flops / (tpeak * 1e12) * 1e3,
+                     "experts_touched": touched, "max_rows_per_expert": int(cnt.max()), "median_rows_per_expert": float(np.median(cnt[:E]))},
+        "stage_ms": stage_ms, "status_word": status, "clocks": clocks.summary(),
     }
     print(json.dumps(line))
 
