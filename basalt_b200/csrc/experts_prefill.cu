@@ -10,11 +10,13 @@
 // power-of-two scale), and tcgen05.mma kind::f16 accumulates in fp32 in tensor memory.  So the result sits ~2e-4 from the
 // dequantised fp32 reference instead of the reference kernel's ~1e-2 .. 0.2, at bf16-class tensor throughput.
 //
-// One CTA per (row tile, 128-column weight tile): warp 0 allocates 128 TMEM columns and issues the MMAs (one elected
-// lane); warps 1-4 are the producers - each thread owns one activation row (cp.async gather through `src`, zero-filled past
-// the expert's last row) and one weight row (36-byte NVFP4 block -> 64 fp16 per 64-column k-block) - and, after the last
-// MMA, the epilogue (thread = TMEM lane = output row).  K-blocks of 64 columns move through a 3-stage ring guarded by
-// mbarriers; every wait is bounded and reports through a status word instead of hanging.
+// Persistent CTAs, one per SM, each looping over work items (128-row tile of one expert, 256 weight rows).  Warp roles:
+// warp 0 allocates all 512 TMEM columns (two 256-column accumulators) and its lane 0 issues the MMAs (M = 128, N = 256);
+// warps 1-2 load the tile's activation rows (cp.async gather through `src`); warps 3-18 decode NVFP4 weight rows to fp16
+// straight into 128-byte-swizzled shared memory (two groups of 256 threads, a thread per weight row, the groups taking
+// alternate pairs of 64-column k-blocks); warps 19-22 are the epilogue (thread = TMEM lane = output row), which drains one
+// accumulator while the tensor core fills the other.  K-blocks move through a 4-stage ring guarded by mbarriers; every wait
+// is bounded and reports through a status word instead of hanging.
 //
 // Both operands use the SAME permutation of k inside each 16-column group, (0,8,1,9,...,7,15) - the order cvt.e2m1x2 emits
 // a sub-block's values in - so no shuffling is needed: the activation image (made by a small kernel here) and the SwiGLU
@@ -29,11 +31,12 @@ namespace bsx {
 namespace {
 
 constexpr int kTileM = 128;        // rows (tokens) per tile = TMEM lanes
-constexpr int kTileN = 128;        // weight rows per tile = TMEM columns
+constexpr int kTileN = 256;        // weight rows per tile = TMEM columns of one accumulator
 constexpr int kBlockK = 64;        // fp16 per k-block: one 128-byte swizzle row
-constexpr int kStagesP = 3;
-constexpr int kGroupThreads = 128; // one group of weight decoders: four warps, one thread per weight row of the tile
-constexpr int kThreadsP = 320;     // MMA warp, activation loader warp, two decoder groups
+constexpr int kStagesP = 4;
+constexpr int kLoaderWarps = 2, kDecoderWarps = 16, kEpilogueWarps = 4;
+constexpr int kGroupThreads = 256; // one group of weight decoders: a thread per weight row of the tile
+constexpr int kThreadsP = 32 * (1 + kLoaderWarps + kDecoderWarps + kEpilogueWarps);
 constexpr unsigned long long kWaitNs = 200ull * 1000 * 1000;   // every mbarrier wait gives up after 200 ms and reports an error status
 constexpr float kHScale = 0.25f;   // the SwiGLU output is stored as fp16(h / 4): fp16 then holds |h| up to 2.6e5
 
@@ -166,50 +169,43 @@ __global__ void __launch_bounds__(256) prefill_prep_x_kernel(const void* __restr
     for (int64_t c = lane; c < H; c += 32) xh[t * H + (c & ~(int64_t) 15) + perm16((int) (c & 15))] = __float2half_rn(ld(c) * s);
 }
 
-// Warp roles of a CTA (one 128-row x 128-weight-row tile):
-//   warp 0       allocates tensor memory; its lane 0 issues the MMAs
-//   warp 1       activation loader: cp.async gathers of the tile's 128 rows, 64 columns a k-block, up to two k-blocks ahead
-//   warps 2..9   weight decoders in two groups of four warps; a group owns every other PAIR of k-blocks (72 bytes of its
-//                thread's weight row, fetched one own pair = four k-blocks ahead), decodes them to fp16 into the stage's B
-//                tile; after the last MMA all eight warps run the epilogue (TMEM lane quarter = warp % 4, columns by group)
-// A stage is full when the loader's 32 lanes and the owning group's 128 threads have arrived, and empty again when the
-// tensor core has read it (tcgen05.commit).
 template <int MODE, bool ALIGNED>
-__global__ void __launch_bounds__(kThreadsP, 2) prefill_gemm_kernel(PrefillArgs a) {
+__global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte aligned operand stages: A then B per stage
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
     constexpr int kABytes = kTileM * kBlockK * 2, kBBytes = kTileN * kBlockK * 2, kStage = kABytes + kBBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStagesP * kStage);   // full[S], empty[S], accum
-    uint64_t* full = bars;
-    uint64_t* empty = bars + kStagesP;
-    uint64_t* accum = bars + 2 * kStagesP;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStagesP + 1);
-    uint32_t* lut = tmem_slot + 2;   // [256] fp16 scale pairs
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStagesP * kStage);
+    uint64_t* full = bars;                        // [S] loader lanes + one decoder group arrive
+    uint64_t* empty = bars + kStagesP;            // [S] tcgen05.commit arrives
+    uint64_t* acc_full = bars + 2 * kStagesP;     // [2] tcgen05.commit after a tile's last MMA
+    uint64_t* acc_empty = acc_full + 2;           // [2] the 128 epilogue threads arrive
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint32_t* lut = tmem_slot + 2;                // [256] fp16 scale pairs
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.y;
-    if (tile >= *a.n_tiles) return;
-    const int expert = a.tiles[2 * tile], row0 = a.tiles[2 * tile + 1];
-    if (a.blob_table[expert] == 0ull) return;   // an expert another device holds (expert parallelism): its rows are not ours
-    const int rows = min(kTileM, a.off[expert + 1] - row0);
     const int64_t K = MODE == PMODE_GU ? a.L.n_embd : a.L.n_ff;
     const int nkb = (int) (K / kBlockK);
-    const int n0 = blockIdx.x * (MODE == PMODE_GU ? kTileN / 2 : kTileN);   // first neuron (GU) or first down row of the tile
-    const uint8_t* blob = reinterpret_cast<const uint8_t*>(a.blob_table[expert]);
+    const int n_out = MODE == PMODE_GU ? (int) a.L.n_ff : (int) a.L.n_embd;      // neurons, or down rows
+    constexpr int kOutPerTile = MODE == PMODE_GU ? kTileN / 2 : kTileN;
+    const int n_n = (n_out + kOutPerTile - 1) / kOutPerTile;
+    const int n_items = *a.n_tiles * n_n;
 
     for (int i = threadIdx.x; i < 256; i += kThreadsP) lut[i] = scale_pair_bits(i);
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStagesP; ++s) {
-            mbar_init(&full[s], kGroupThreads + 32);
+            mbar_init(&full[s], kGroupThreads + 32 * kLoaderWarps);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(accum, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 32 * kEpilogueWarps);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 0) {
         __syncwarp();   // lane 0 initialised the barriers above: reconverge before the warp-wide allocation
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t) kTileN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -218,85 +214,112 @@ __global__ void __launch_bounds__(kThreadsP, 2) prefill_gemm_kernel(PrefillArgs 
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
 
+    // A work item: tile = item / n_n (expert, first row), weight rows n0 = (item % n_n) * kOutPerTile ...; every role walks the
+    // same item sequence and skips the same items (experts another device holds), so their k-block counters stay in step.
+    struct Item { const uint8_t* blob; int row0, rows, n0; };
+    auto get_item = [&](int item, Item& it) -> bool {
+        const int tile = item / n_n;
+        const int expert = a.tiles[2 * tile];
+        const unsigned long long bp = a.blob_table[expert];
+        if (bp == 0ull) return false;
+        it.blob = reinterpret_cast<const uint8_t*>(bp);
+        it.row0 = a.tiles[2 * tile + 1];
+        it.rows = min(kTileM, a.off[expert + 1] - it.row0);
+        it.n0 = (item - tile * n_n) * kOutPerTile;
+        return true;
+    };
+
     if (warp == 0) {
         // ---- MMA issuer: one lane feeds the tensor core, four k = 16 instructions per 64-column k-block
         if (lane == 0) {
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % kStagesP;
-                ok = mbar_wait(&full[s], (uint32_t) (kb / kStagesP) & 1u);
+            uint32_t kc = 0, ti = 0;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                Item it;
+                if (!get_item(item, it)) continue;
+                const uint32_t acc = ti & 1u;
+                ok = mbar_wait(&acc_empty[acc], ((ti >> 1) & 1u) ^ 1u);     // the epilogue has drained this accumulator
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t sa = smem_u32(smem + s * kStage), sb = sa + kABytes;
+                for (int kb = 0; kb < nkb; ++kb, ++kc) {
+                    const uint32_t s = kc % kStagesP;
+                    ok = mbar_wait(&full[s], (kc / kStagesP) & 1u);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t sa = smem_u32(smem + s * kStage), sb = sa + kABytes;
 #pragma unroll
-                for (int k = 0; k < kBlockK / 16; ++k)
-                    umma_f16(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), (kb | k) ? 1u : 0u);
-                umma_commit(&empty[s]);      // the stage may be refilled once these MMAs have read it
+                    for (int k = 0; k < kBlockK / 16; ++k)
+                        umma_f16(tmem + acc * kTileN, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), (kb | k) ? 1u : 0u);
+                    umma_commit(&empty[s]);      // the stage may be refilled once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[acc]);     // fires when every MMA of the tile has finished
+                ++ti;
             }
-            umma_commit(accum);              // every MMA issued so far has finished when this fires
             if (!ok) atomicOr(a.status, kStatusTimeout);
         }
-    } else if (warp == 1) {
-        // ---- activation loader.  Lane l copies 16-byte chunk l % 8 of rows l / 8, l / 8 + 4, ...: eight lanes cover one row's
-        // 128 bytes.  Rows past the expert's last row read some valid row instead (their products are never stored).
-        const int c = lane & 7, r4 = lane >> 3;
+    } else if (warp <= kLoaderWarps) {
+        // ---- activation loaders.  Lane l of loader warp w copies 16-byte chunk l % 8 of rows 64 w + l / 8 + 4 i: eight lanes
+        // cover one row's 128 bytes.  Rows past the expert's last row read some valid row instead (never stored).  A lane
+        // runs up to two k-blocks ahead of its own completed copies and arrives on a stage once its copies there landed.
+        const int lw = warp - 1, c = lane & 7, r4 = lane >> 3;
         const uint8_t* abase = reinterpret_cast<const uint8_t*>(MODE == PMODE_GU ? a.xh : a.h);
-        uint32_t aoff[32];   // row starts in 16-byte units
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int r = 4 * i + r4;
-            const uint32_t grow = MODE == PMODE_GU ? (uint32_t) a.src[row0 + (r < rows ? r : 0)] : (uint32_t) (row0 + r);
-            aoff[i] = grow * (uint32_t) (K >> 3) + (uint32_t) c;
-        }
         uint32_t dsto[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r7 = 4 * h + r4;
-            dsto[h] = (uint32_t) (r7 * 128 + ((c ^ r7) << 4));
+            dsto[h] = (uint32_t) (lw * 8 * 1024 + r7 * 128 + ((c ^ r7) << 4));
         }
-        auto issue_a = [&](int kb) {
-            const uint32_t dst = smem_u32(smem + (kb % kStagesP) * kStage);
+        uint32_t issued = 0, arrived = 0;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            Item it;
+            if (!get_item(item, it)) continue;
+            uint32_t aoff[16];   // row starts in 16-byte units
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const uint8_t* g = abase + ((size_t) aoff[i] + (size_t) kb * 8) * 16;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t) ((i >> 1) * 1024) + dsto[i & 1]), "l"(g) : "memory");
+            for (int i = 0; i < 16; ++i) {
+                const int r = lw * 64 + 4 * i + r4;
+                const uint32_t grow = MODE == PMODE_GU ? (uint32_t) a.src[it.row0 + (r < it.rows ? r : 0)] : (uint32_t) (it.row0 + r);
+                aoff[i] = grow * (uint32_t) (K >> 3) + (uint32_t) c;
             }
-        };
-        // the first two stages are free from the start
-        issue_a(0);
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-        if (nkb > 1) issue_a(1);
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-        for (int kb = 0; kb < nkb; ++kb) {
-            asm volatile("cp.async.wait_group 1;\n" ::: "memory");         // this lane's copies of k-block kb have landed
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            mbar_arrive(&full[kb % kStagesP]);
-            if (kb + 2 < nkb) {
-                ok = mbar_wait(&empty[(kb + 2) % kStagesP], ((uint32_t) ((kb + 2) / kStagesP) & 1u) ^ 1u);
+            for (int kb = 0; kb < nkb; ++kb) {
+                const uint32_t s = issued % kStagesP;
+                ok = mbar_wait(&empty[s], ((issued / kStagesP) & 1u) ^ 1u);
                 if (!ok) break;
-                issue_a(kb + 2);
+                const uint32_t dst = smem_u32(smem + s * kStage);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint8_t* g = abase + ((size_t) aoff[i] + (size_t) kb * 8) * 16;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t) ((i >> 1) * 1024) + dsto[i & 1]), "l"(g) : "memory");
+                }
+                asm volatile("cp.async.commit_group;\n" ::: "memory");
+                ++issued;
+                if (issued - arrived > 2) {
+                    asm volatile("cp.async.wait_group 2;\n" ::: "memory");
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    mbar_arrive(&full[arrived % kStagesP]);
+                    ++arrived;
+                }
             }
-            asm volatile("cp.async.commit_group;\n" ::: "memory");
         }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        for (; arrived < issued; ++arrived) mbar_arrive(&full[arrived % kStagesP]);
         if (!ok) atomicOr(a.status, kStatusTimeout);
-    } else {
-        // ---- weight decoders, then the epilogue.  A warp may only read the 32 TMEM lanes 32 (warp % 4) .. + 31 and lane =
-        // output row, so thread (warp, lane) owns weight row / output row p = 32 (warp % 4) + lane in both roles.
-        const int grp = (warp - 2) >> 2;
-        const int p = (warp & 3) * 32 + lane;
-        const bool row_live = p < rows;
-        const uint8_t* wrow;
-        if (MODE == PMODE_GU) {
-            const int r = n0 + (p & 63);     // B rows 0..63 = gate rows, 64..127 = the matching up rows
-            wrow = p < 64 ? blob + (size_t) r * a.L.gu_row : blob + a.L.up_off + (size_t) r * a.L.up_row;
-        } else {
-            wrow = blob + a.L.down_off + (size_t) (n0 + p) * a.L.d_row;
-        }
-        const uint32_t swz = (uint32_t) (p & 7);
-        const uint32_t row_off = (uint32_t) ((p >> 3) * 1024 + (p & 7) * 128);
+    } else if (warp <= kLoaderWarps + kDecoderWarps) {
+        // ---- weight decoders: thread (group, row r) turns the NVFP4 blocks of weight row r of the tile into fp16 B-tile rows
+        const int td = threadIdx.x - 32 * (1 + kLoaderWarps);
+        const int grp = td >> 8, r = td & 255;
+        const uint32_t swz = (uint32_t) (r & 7);
+        const uint32_t row_off = (uint32_t) (kABytes + (r >> 3) * 1024 + (r & 7) * 128);
+        auto weight_row = [&](const Item& it) -> const uint8_t* {
+            if (MODE == PMODE_GU) {     // B rows 0..127 = gate rows, 128..255 = the matching up rows
+                const int n = min(it.n0 + (r & 127), n_out - 1);
+                return r < 128 ? it.blob + (size_t) n * a.L.gu_row : it.blob + a.L.up_off + (size_t) n * a.L.up_row;
+            }
+            return it.blob + a.L.down_off + (size_t) min(it.n0 + r, n_out - 1) * a.L.d_row;
+        };
         // one NVFP4 block (9 words: 4 scale bytes, 32 code bytes) -> 64 fp16 of the B tile, already in the permuted k order
-        auto store_b = [&](int kb, const uint32_t* cur) {
-            uint4* brow = reinterpret_cast<uint4*>(smem + (kb % kStagesP) * kStage + kABytes + row_off);
+        auto store_b = [&](uint32_t s, const uint32_t* cur) {
+            uint4* brow = reinterpret_cast<uint4*>(smem + s * kStage + row_off);
 #pragma unroll
             for (int sub = 0; sub < 4; ++sub) {
                 const uint32_t sc = lut[(cur[0] >> (8 * sub)) & 0xFFu];
@@ -315,7 +338,7 @@ __global__ void __launch_bounds__(kThreadsP, 2) prefill_gemm_kernel(PrefillArgs 
         // the pair of blocks q (k-blocks 2q, 2q + 1): 72 bytes at offset 72 q of the row; 16-byte loads when rows are whole
         // 144-byte chunks (then 72 q is a multiple of 16 for even q and of 8 for odd q)
         const int npair = (nkb + 1) >> 1;
-        auto load_pair = [&](int q, uint32_t (&w)[18]) {
+        auto load_pair = [&](const uint8_t* wrow, int q, uint32_t (&w)[18]) {
             const uint8_t* src = wrow + (size_t) q * 72;
             if (ALIGNED) {
                 if ((q & 1) == 0) {
@@ -341,70 +364,99 @@ __global__ void __launch_bounds__(kThreadsP, 2) prefill_gemm_kernel(PrefillArgs 
                 for (int i = 0; i < 18; ++i) w[i] = i < nw ? reinterpret_cast<const uint32_t*>(src)[i] : 0u;
             }
         };
+        // the stream of own pairs runs across items: the first pair of the next item is requested while the last pair of this
+        // one is decoded, so a tile switch does not expose a load
         uint32_t wc[18], wn[18];
-        if (grp < npair) load_pair(grp, wn);
-        for (int q = grp; q < npair && ok; q += 2) {
+        uint32_t kc = 0;
+        int item = blockIdx.x;
+        Item it;
+        while (item < n_items && !get_item(item, it)) item += gridDim.x;
+        if (item < n_items && grp < npair) load_pair(weight_row(it), grp, wn);
+        while (item < n_items && ok) {
+            const uint8_t* wrow = weight_row(it);
+            int nxt = item + gridDim.x;
+            Item itn;
+            while (nxt < n_items && !get_item(nxt, itn)) nxt += gridDim.x;
+            for (int q = grp; q < npair && ok; q += 2) {
 #pragma unroll
-            for (int i = 0; i < 18; ++i) wc[i] = wn[i];
-            if (q + 2 < npair) load_pair(q + 2, wn);
+                for (int i = 0; i < 18; ++i) wc[i] = wn[i];
+                if (q + 2 < npair) load_pair(wrow, q + 2, wn);
+                else if (nxt < n_items) load_pair(weight_row(itn), grp, wn);
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int kb = 2 * q + j;
-                if (kb < nkb && ok) {
-                    ok = mbar_wait(&empty[kb % kStagesP], ((uint32_t) (kb / kStagesP) & 1u) ^ 1u);
-                    if (ok) {
-                        store_b(kb, &wc[9 * j]);
-                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
-                        mbar_arrive(&full[kb % kStagesP]);
+                for (int j = 0; j < 2; ++j) {
+                    const int kb = 2 * q + j;
+                    if (kb < nkb && ok) {
+                        const uint32_t kk = kc + (uint32_t) kb, s = kk % kStagesP;
+                        ok = mbar_wait(&empty[s], ((kk / kStagesP) & 1u) ^ 1u);
+                        if (ok) {
+                            store_b(s, &wc[9 * j]);
+                            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+                            mbar_arrive(&full[s]);
+                        }
                     }
                 }
             }
+            kc += (uint32_t) nkb;
+            item = nxt;
+            it = itn;
         }
-        // ---- epilogue: thread p reads TMEM lane p (= output row p); group 0 takes the first half of the columns, group 1 the rest
-        if (ok) ok = mbar_wait(accum, 0u);
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         if (!ok) atomicOr(a.status, kStatusTimeout);
-        // tcgen05.ld is warp-wide (.sync.aligned): every lane of the warp runs the loads together or none does; only the
-        // global stores depend on whether the lane's row exists
-        const bool warp_ok = __all_sync(kFull, ok);
-        if (warp_ok) {
-            const uint32_t lane_base = (uint32_t) ((warp & 3) * 32) << 16;
-            const float* tail = reinterpret_cast<const float*>(blob + a.L.bytes - 16);
+    } else {
+        // ---- epilogue: thread p reads TMEM lane p (= output row p) of the finished accumulator.  A warp may only read the 32
+        // TMEM lanes 32 (warp % 4) .. + 31.  tcgen05.ld is warp-wide: every lane runs the loads; only the stores are predicated.
+        const int p = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = (uint32_t) ((warp & 3) * 32) << 16;
+        uint32_t ti = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            Item it;
+            if (!get_item(item, it)) continue;
+            const uint32_t acc = ti & 1u;
+            ok = __all_sync(kFull, mbar_wait(&acc_full[acc], (ti >> 1) & 1u));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const bool row_live = p < it.rows;
+            const float* tail = reinterpret_cast<const float*>(it.blob + a.L.bytes - 16);
+            const uint32_t tbase = tmem + lane_base + acc * kTileN;
             if (MODE == PMODE_GU) {
-                const float f = row_live ? a.xinv[a.src[row0 + p]] * 256.f : 0.f;
+                const float f = row_live ? a.xinv[a.src[it.row0 + p]] * 256.f : 0.f;
                 const float sg = tail[0] * f, su = tail[1] * f;
-                const int c0 = 32 * grp;                       // neurons c0 .. c0 + 31 of the tile's 64
-                __half* hrow = a.h + (size_t) (row0 + p) * a.L.n_ff + n0 + c0;
-#pragma unroll
-                for (int c1 = 0; c1 < 32; c1 += 16) {
+                __half* hrow = a.h + (size_t) (it.row0 + p) * a.L.n_ff + it.n0;
+#pragma unroll 1
+                for (int c0 = 0; c0 < kTileN / 2; c0 += 16) {
                     uint32_t g[16], u[16];
-                    tmem_ld16(tmem + lane_base + (uint32_t) (c0 + c1), g);
-                    tmem_ld16(tmem + lane_base + (uint32_t) (64 + c0 + c1), u);
+                    tmem_ld16(tbase + (uint32_t) c0, g);
+                    tmem_ld16(tbase + (uint32_t) (kTileN / 2 + c0), u);
                     __half out[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const float hv = swiglu(__uint_as_float(g[j]) * sg, __uint_as_float(u[j]) * su, a.L) * kHScale;
                         out[perm16(j)] = __float2half_rn(fminf(fmaxf(hv, -65504.f), 65504.f));
                     }
-                    if (row_live) {
-                        reinterpret_cast<uint4*>(hrow + c1)[0] = reinterpret_cast<const uint4*>(out)[0];
-                        reinterpret_cast<uint4*>(hrow + c1)[1] = reinterpret_cast<const uint4*>(out)[1];
+                    if (row_live && it.n0 + c0 < n_out) {
+                        reinterpret_cast<uint4*>(hrow + c0)[0] = reinterpret_cast<const uint4*>(out)[0];
+                        reinterpret_cast<uint4*>(hrow + c0)[1] = reinterpret_cast<const uint4*>(out)[1];
                     }
                 }
             } else {
                 const float f = tail[2] * (256.f / kHScale);
-                float* orow = a.dm + (size_t) (row0 + p) * a.L.n_embd + n0 + 64 * grp;
-#pragma unroll
-                for (int c0 = 0; c0 < 64; c0 += 32) {
+                float* orow = a.dm + (size_t) (it.row0 + p) * a.L.n_embd + it.n0;
+#pragma unroll 1
+                for (int c0 = 0; c0 < kTileN; c0 += 32) {
                     uint32_t d[32];
-                    tmem_ld32(tmem + lane_base + (uint32_t) (64 * grp + c0), d);
+                    tmem_ld32(tbase + (uint32_t) c0, d);
+                    if (row_live && it.n0 + c0 < n_out) {
 #pragma unroll
-                    for (int v = 0; v < 8; ++v)
-                        if (row_live) reinterpret_cast<float4*>(orow + c0)[v] = make_float4(__uint_as_float(d[4 * v]) * f, __uint_as_float(d[4 * v + 1]) * f,
-                                                                               __uint_as_float(d[4 * v + 2]) * f, __uint_as_float(d[4 * v + 3]) * f);
+                        for (int v = 0; v < 8; ++v)
+                            reinterpret_cast<float4*>(orow + c0)[v] = make_float4(__uint_as_float(d[4 * v]) * f, __uint_as_float(d[4 * v + 1]) * f,
+                                                                                 __uint_as_float(d[4 * v + 2]) * f, __uint_as_float(d[4 * v + 3]) * f);
+                    }
                 }
             }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            mbar_arrive(&acc_empty[acc]);
+            ++ti;
         }
+        if (!ok && lane == 0) atomicOr(a.status, kStatusTimeout);
     }
     // everyone is done with tensor memory before warp 0 gives it back
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -412,12 +464,12 @@ __global__ void __launch_bounds__(kThreadsP, 2) prefill_gemm_kernel(PrefillArgs 
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t) kTileN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u) : "memory");
     }
 }
 
 size_t align256p(size_t v) { return (v + 255) & ~(size_t) 255; }
-constexpr size_t kSmemP = 1024 + kStagesP * (kTileM * kBlockK * 2 + kTileN * kBlockK * 2) + 256 + 1024 + 64;
+constexpr size_t kSmemP = 1024 + kStagesP * (kTileM * kBlockK * 2 + kTileN * kBlockK * 2) + 256 + 1024 + 64;   // 199,040 bytes: one CTA per SM
 
 }  // namespace
 }  // namespace bsx
@@ -437,7 +489,7 @@ extern "C" int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const un
         return BSX_E_POINTER;
     const bsx_expert_layout& L = *layout;
     if (L.gu_type != kTypeNVFP4 || L.up_type != kTypeNVFP4 || L.d_type != kTypeNVFP4) return BSX_E_TYPE;
-    if (L.n_embd % 128 || L.n_ff % 64 || (x_kind != BSX_X_F32 && x_kind != BSX_X_BF16)) return BSX_E_GEOMETRY;
+    if (L.n_embd % 64 || L.n_ff % 64 || (x_kind != BSX_X_F32 && x_kind != BSX_X_BF16)) return BSX_E_GEOMETRY;
     if (cap_tiles < 0 || cap_tiles > 65535 || cap_rows < 0 || n_tokens < 0) return BSX_E_GEOMETRY;
     if (cap_tiles == 0 || n_tokens == 0) return BSX_OK;
     const cudaStream_t st = (cudaStream_t) stream;
@@ -470,11 +522,11 @@ extern "C" int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const un
         configured[dev] = true;
     }
     prefill_prep_x_kernel<<<(unsigned) ((n_tokens + 7) / 8), 256, 0, st>>>(x, x_kind, n_tokens, L.n_embd, xh, xinv);
-    // rows that are whole 144-byte chunks (K % 256 == 0) take the variant that streams them as 16-byte loads
-    const dim3 ggu((unsigned) (L.n_ff / 64), (unsigned) cap_tiles), gdn((unsigned) (L.n_embd / kTileN), (unsigned) cap_tiles);
-    if (L.n_embd % 256 == 0) prefill_gemm_kernel<PMODE_GU, true><<<ggu, kThreadsP, kSmemP, st>>>(a);
-    else prefill_gemm_kernel<PMODE_GU, false><<<ggu, kThreadsP, kSmemP, st>>>(a);
-    if (L.n_ff % 256 == 0) prefill_gemm_kernel<PMODE_DOWN, true><<<gdn, kThreadsP, kSmemP, st>>>(a);
-    else prefill_gemm_kernel<PMODE_DOWN, false><<<gdn, kThreadsP, kSmemP, st>>>(a);
+    // persistent CTAs, one per SM; rows that are whole 144-byte chunks (K % 256 == 0) take the variant with 16-byte weight loads
+    const unsigned grid = (unsigned) sm_count();
+    if (L.n_embd % 256 == 0) prefill_gemm_kernel<PMODE_GU, true><<<grid, kThreadsP, kSmemP, st>>>(a);
+    else prefill_gemm_kernel<PMODE_GU, false><<<grid, kThreadsP, kSmemP, st>>>(a);
+    if (L.n_ff % 256 == 0) prefill_gemm_kernel<PMODE_DOWN, true><<<grid, kThreadsP, kSmemP, st>>>(a);
+    else prefill_gemm_kernel<PMODE_DOWN, false><<<grid, kThreadsP, kSmemP, st>>>(a);
     return launch_status();
 }
