@@ -101,6 +101,20 @@ def router_logits(x, gate, logits=None, stream=None):
     return logits
 
 
+def router_logits_prefill(x, gate, logits=None, scratch=None, status=None, stream=None):
+    """The prompt path's router product (qwen4exp prefill routing.cpp:26) as a tensor-core GEMM; returns (logits, status)."""
+    T, H = x.shape
+    E = gate.shape[0]
+    dev = x.device
+    logits = torch.empty((T, E), dtype=torch.float32, device=dev) if logits is None else logits
+    if scratch is None:
+        scratch = torch.empty(capi.lib().bsx_router_logits_prefill_scratch_bytes(T, E, H), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev) if status is None else status
+    check("bsx_router_logits_prefill", capi.lib().bsx_router_logits_prefill(_p(x), _x_kind(x), _p(gate), T, E, H, _p(logits), _p(scratch), _p(status),
+                                                                             _stream(stream)))
+    return logits, status
+
+
 def router_select(logits, bias, a: RouterArgs, ids=None, weights=None, stream=None):
     """basalt::kernels::router_select (router.hpp:36-37); with a softmax gate kind, qwen4exp's route / native_router_top10 /
     router_top10."""
@@ -358,6 +372,7 @@ class PrefillMoELayer:
         self.scratch = torch.empty(capi.lib().bsx_experts_prefill_scratch_bytes(C.byref(layout), T, n), dtype=torch.uint8, device=dev)
         self.dm = torch.empty((n, layout.n_embd), dtype=f32, device=dev)
         self.status = torch.zeros(1, dtype=i32, device=dev)
+        self.rscratch = torch.empty(capi.lib().bsx_router_logits_prefill_scratch_bytes(T, E, layout.n_embd), dtype=torch.uint8, device=dev)
         self.y = torch.empty((T, layout.n_embd), dtype=f32, device=dev)
         self.events = None      # set to a list to collect (name, event) marks between the stages
 
@@ -374,7 +389,8 @@ class PrefillMoELayer:
         a, lib, st, L = self.args, capi.lib(), _stream(stream), self.L
         assert T == self.max_tokens, "buffers are sized for max_tokens rows"
         self._mark("start", stream)
-        check("bsx_router_logits_x", lib.bsx_router_logits_x(_p(x), _x_kind(x), _p(self.gate_w), T, a.n_expert, a.n_embd, _p(self.logits), st))
+        check("bsx_router_logits_prefill", lib.bsx_router_logits_prefill(_p(x), _x_kind(x), _p(self.gate_w), T, a.n_expert, a.n_embd, _p(self.logits),
+                                                                         _p(self.rscratch), _p(self.status), st))
         self._mark("router_logits", stream)
         router_select(self.logits if logits is None else logits, self.bias, a, self.ids, self.w, stream)
         if self.kk != a.k:

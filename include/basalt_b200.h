@@ -88,6 +88,16 @@ BSX_API int32_t bsx_router(const float* x, const float* gate, const float* bias,
                    int32_t gate_kind, float weight_scale, int32_t n_group, int32_t topk_group, float prior,
                    const int32_t* const* held_tabs, int32_t n_held, float* logits, int32_t* ids, float* weights, void* stream);
 
+/* ---- a1 for prompt-sized batches: the gate product as a GEMM on the tcgen05 tensor cores.  Replaces the prompt path's router
+ * GEMM (src/models/qwen4exp/prefill/routing.cpp:26, a cuBLAS bf16 product).  Same logits layout as bsx_router_logits; values
+ * agree with it to ~1e-6 of |x||gate| (fp16 hi + lo operand images, fp32 accumulation), not bit for bit: use
+ * bsx_router_logits where routing must not depend on the batch.  x fp32 or bf16 [T][H]; E % 32 == 0, H % 64 == 0.
+ * scratch: bsx_router_logits_prefill_scratch_bytes(T, E, H), 256-byte aligned.  status: a device int32 the caller zeroes; bit 0
+ * is set if a bounded wait inside the kernel ran out (the kernel then returns instead of hanging). */
+BSX_API size_t bsx_router_logits_prefill_scratch_bytes(int64_t T, int32_t E, int32_t H);
+BSX_API int32_t bsx_router_logits_prefill(const void* x, int32_t x_kind, const float* gate, int64_t T, int32_t E, int32_t H, float* logits,
+                                          void* scratch, int32_t* status, void* stream);
+
 /* ---- a1/a2 with bf16 activation rows (x_kind BSX_X_F32 or BSX_X_BF16; no counterpart in the reference, whose router reads
  * fp32 only: a bf16 row is widened exactly, then the same sums run, so the result equals bsx_router on the widened rows). */
 BSX_API int32_t bsx_router_logits_x(const void* x, int32_t x_kind, const float* gate, int32_t T, int32_t E, int32_t H, float* logits,

@@ -89,3 +89,31 @@ def test_prefill_skips_experts_held_elsewhere_and_matches_decode_kernels(lib, cu
     lo, hi = int(off[0]), int(off[4])
     assert rel_l2(dm[lo:hi], rows[lo:hi]) < 1e-3          # two implementations of the same rows (fp16 h vs fp32 h)
     assert np.all(rows[hi:] == 0)                          # rows of experts held elsewhere are not touched by the decode path
+
+
+@pytest.mark.parametrize("T,E,H,xdt", [(300, 64, 512, "bf16"), (1000, 512, 2048, "bf16"), (130, 256, 7168, "bf16"), (257, 96, 1024, "f32")])
+def test_router_logits_prefill_matches_the_fp32_chain(lib, cuda, T, E, H, xdt):
+    """The tensor-core gate product against the fixed-order fp32 chain (bsx_router_logits): every logit within 4e-6 of
+    |x_t| |gate_e| (both sums carry fp32 rounding of that order), and the top-k ids equal except where scores tie to it."""
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    x = torch.randn((T, H), generator=g, device="cuda")
+    x[1] *= 1e-3                       # rows of very different scale: each row has its own power-of-two scale
+    x[2] *= 300.0
+    x = x.bfloat16() if xdt == "bf16" else x
+    gate = torch.randn((E, H), generator=g, device="cuda") * 0.02
+    gate[3] *= 50.0
+    want = torch.empty((T, E), dtype=torch.float32, device="cuda")
+    capi.check("logits", lib.bsx_router_logits_x(x.data_ptr(), moe._x_kind(x), gate.data_ptr(), T, E, H, want.data_ptr(), moe._stream(None)))
+    got, status = moe.router_logits_prefill(x, gate)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    bound = x.float().norm(dim=1)[:, None] * gate.norm(dim=1)[None, :]
+    err = ((got - want).abs() / bound).max().item()
+    print("worst |logit difference| / (|x| |gate|):", err)
+    assert err < 4e-6
+    a = moe.RouterArgs(n_expert=E, n_embd=H, k=8, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
+    ids_w, _ = moe.router_select(want, None, a)
+    ids_g, _ = moe.router_select(got, None, a)
+    torch.cuda.synchronize()
+    same = (ids_w == ids_g).all(dim=1).float().mean().item()
+    assert same > 0.99
