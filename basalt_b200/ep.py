@@ -269,3 +269,104 @@ class EPMoELayer:
         # y = 1 * sum + shared, through the combine kernel (one "row" per token)
         capi.check("bsx_combine", lib.bsx_combine(p(self.y_sum), None, p(self.ones), p(self.s_out), None, T, 1, H, p(self.y), st))
         return self.y
+
+
+class EPPrefillMoELayer:
+    """The expert-parallel layer for prompt-sized batches, collective form: every rank routes its own T tokens (tensor-core
+    gate product + selection), all-gathers activations and routing, dispatches all pairs, runs bsx_experts_prefill over the
+    experts it holds (blob_table = 0 for the others, whose tiles the kernel skips), sums its experts' weighted rows per
+    token (bsx_combine_partial) and reduce-scatters the partial sums to the tokens' owners.  The shared expert (replicated)
+    runs on the rank's own tokens as a one-expert prefill call and is added last.  Fixed sizes, no host reads."""
+
+    def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, shared_blob=None, max_tokens: int = 4096, group=None):
+        import torch
+        import torch.distributed as dist
+        from . import capi, moe
+        self.torch, self.dist, self.moe, self.capi = torch, dist, moe, capi
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.E, self.L, self.args = n_expert_total, layout, args
+        first = ep_partition(n_expert_total, self.world)
+        self.lo, self.hi = int(first[self.rank]), int(first[self.rank + 1])
+        self.gate_w, self.bias, self.blobs, self.shared_blob = gate_w, bias, blobs, shared_blob
+        dev = blobs.device
+        self.dev = dev
+        El, stride = blobs.shape
+        assert El == self.hi - self.lo
+        table = np.zeros(n_expert_total, np.int64)
+        table[self.lo:self.hi] = blobs.data_ptr() + np.arange(El, dtype=np.int64) * stride
+        self.blob_table = torch.from_numpy(table).to(dev)
+        W, T, k, H = self.world, max_tokens, args.k, layout.n_embd
+        self.max_tokens = T
+        n = W * T * k
+        f32, i32, u8 = torch.float32, torch.int32, torch.uint8
+        lib = capi.lib()
+        self.logits = torch.empty((T, n_expert_total), dtype=f32, device=dev)
+        self.rscratch = torch.empty(lib.bsx_router_logits_prefill_scratch_bytes(T, n_expert_total, H), dtype=u8, device=dev)
+        self.ids = torch.empty((T, k), dtype=i32, device=dev)
+        self.w = torch.empty((T, k), dtype=f32, device=dev)
+        self.route = torch.empty((T, 2 * k), dtype=i32, device=dev)
+        self.route_all = torch.empty((W * T, 2 * k), dtype=i32, device=dev)
+        self.ids_all = torch.empty((W * T, k), dtype=i32, device=dev)
+        self.w_all = torch.empty((W * T, k), dtype=f32, device=dev)
+        self.x_all = None
+        self.cnt = torch.empty(n_expert_total, dtype=i32, device=dev)
+        self.off = torch.empty(n_expert_total + 1, dtype=i32, device=dev)
+        self.slot = torch.empty(n, dtype=i32, device=dev)
+        self.src = torch.empty(n, dtype=i32, device=dev)
+        self.tiles = torch.zeros((n // 128 + n_expert_total, 2), dtype=i32, device=dev)
+        self.n_tiles = torch.zeros(1, dtype=i32, device=dev)
+        self.dscratch = torch.empty(lib.bsx_dispatch_scratch_bytes(n, n_expert_total), dtype=u8, device=dev)
+        self.scratch = torch.empty(lib.bsx_experts_prefill_scratch_bytes(C.byref(layout), W * T, n), dtype=u8, device=dev)
+        self.dm = torch.empty((n, H), dtype=f32, device=dev)
+        self.status = torch.zeros(1, dtype=i32, device=dev)
+        self.y_part = torch.empty((W * T, H), dtype=f32, device=dev)
+        self.y_sum = torch.empty((T, H), dtype=f32, device=dev)
+        self.y = torch.empty((T, H), dtype=f32, device=dev)
+        self.ones = torch.ones((T, 1), dtype=f32, device=dev)
+        if shared_blob is not None:
+            # the shared expert as a one-expert dispatch of the rank's own tokens: rows in token order
+            self.s_table = torch.tensor([shared_blob.data_ptr()], dtype=torch.int64, device=dev)
+            self.s_off = torch.tensor([0, T], dtype=i32, device=dev)
+            self.s_src = torch.arange(T, dtype=i32, device=dev)
+            nt = (T + 127) // 128
+            self.s_tiles = torch.stack([torch.zeros(nt, dtype=i32), torch.arange(nt, dtype=i32) * 128], dim=1).contiguous().to(dev)
+            self.s_ntiles = torch.tensor([nt], dtype=i32, device=dev)
+            self.s_scratch = torch.empty(lib.bsx_experts_prefill_scratch_bytes(C.byref(layout), T, T), dtype=u8, device=dev)
+            self.s_dm = torch.empty((T, H), dtype=f32, device=dev)
+
+    def forward(self, x):
+        torch, dist, moe, capi = self.torch, self.dist, self.moe, self.capi
+        lib, a, L = capi.lib(), self.args, self.L
+        T, k, W, H = x.shape[0], a.k, self.world, L.n_embd
+        assert T == self.max_tokens, "the collective form exchanges fixed-size buffers: pass max_tokens rows"
+        st = moe._stream(torch.cuda.current_stream())
+        p = moe._p
+        kind = moe._x_kind(x)
+        capi.check("bsx_router_logits_prefill", lib.bsx_router_logits_prefill(p(x), kind, p(self.gate_w), T, a.n_expert, a.n_embd, p(self.logits),
+                                                                              p(self.rscratch), p(self.status), st))
+        moe.router_select(self.logits, self.bias, a, self.ids, self.w)
+        self.route[:, :k].copy_(self.ids)
+        self.route[:, k:].view(torch.float32).copy_(self.w)
+        if self.x_all is None or self.x_all.dtype != x.dtype:
+            self.x_all = torch.empty((W * T, H), dtype=x.dtype, device=self.dev)
+        dist.all_gather_into_tensor(self.x_all, x, group=self.group)
+        dist.all_gather_into_tensor(self.route_all, self.route, group=self.group)
+        self.ids_all.copy_(self.route_all[:, :k])
+        self.w_all.copy_(self.route_all[:, k:].view(torch.float32))
+        n = W * T * k
+        capi.check("bsx_dispatch", lib.bsx_dispatch(p(self.ids_all), n, k, self.E, p(self.cnt), p(self.off), p(self.slot), p(self.src), 128,
+                                                     p(self.tiles), p(self.n_tiles), p(self.dscratch), st))
+        capi.check("bsx_experts_prefill", lib.bsx_experts_prefill(C.byref(L), p(self.blob_table), p(self.off), p(self.src), p(self.tiles), p(self.n_tiles),
+                                                                  self.tiles.shape[0], n, p(self.x_all), kind, W * T, p(self.scratch), p(self.dm),
+                                                                  p(self.status), st))
+        capi.check("bsx_combine_partial", lib.bsx_combine_partial(p(self.dm), p(self.slot), p(self.w_all), p(self.ids_all), self.lo, self.hi, W * T, k, H,
+                                                                   p(self.y_part), st))
+        if self.shared_blob is None:
+            dist.reduce_scatter_tensor(self.y, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
+            return self.y
+        capi.check("bsx_experts_prefill", lib.bsx_experts_prefill(C.byref(L), p(self.s_table), p(self.s_off), p(self.s_src), p(self.s_tiles), p(self.s_ntiles),
+                                                                  self.s_tiles.shape[0], T, p(x), kind, T, p(self.s_scratch), p(self.s_dm), p(self.status), st))
+        dist.reduce_scatter_tensor(self.y_sum, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
+        capi.check("bsx_combine", lib.bsx_combine(p(self.y_sum), None, p(self.ones), p(self.s_dm), None, T, 1, H, p(self.y), st))
+        return self.y

@@ -49,9 +49,32 @@ def measured_peaks():
     return 6650.0, "fallback (earlier measurement on this pool)"
 
 
-def make_layer_weights(device, seed=0):
-    """gate [E][H] fp32 and E + 1 NVFP4 blobs (the last is the shared expert), quantised from N(0, 0.02^2)."""
+SHAPES = {
+    # flash-next-style layer (the decode line's layer): softmax top-10 of 512 + 1 shared
+    "c1": dict(H=2048, E=512, I=512, k=10, gate="softmax", n_group=1, topk_group=1, scale=1.0, bias=False, zipf=True,
+               name="flash-next-style MoE layer"),
+    # v4-flash-style layer: sigmoid + bias, 8 groups keep 4, top-8 of 256 + 1 shared, weights x 2.5
+    "c3": dict(H=7168, E=256, I=2048, k=8, gate="sigmoid", n_group=8, topk_group=4, scale=2.5, bias=True, zipf=False,
+               name="v4-flash-style MoE layer"),
+}
+
+
+def make_layer_weights(device, seed=0, E=E, H=H, I=I, first=0, count=None):
+    """gate [E][H] fp32 and NVFP4 blobs quantised from N(0, 0.02^2): experts first .. first + count - 1 of E + 1 (the last,
+    index E, is the shared expert).  Every expert's values depend only on (seed, its index)."""
     from basalt_b200 import pack
+    if count is not None:
+        gate = (torch.randn((E, H), generator=torch.Generator(device=device).manual_seed(seed), device=device) * 0.02).float()
+        blob_bytes = 3 * I * (H // 64 * 36) + 16
+        stride = (blob_bytes + 15) // 16 * 16
+        blobs = torch.zeros((count, stride), dtype=torch.uint8, device=device)
+        for i in range(count):
+            g = torch.Generator(device=device).manual_seed(seed * 100003 + 1 + first + i)
+            G = torch.randn((I, H), generator=g, device=device) * 0.02
+            U = torch.randn((I, H), generator=g, device=device) * 0.02
+            D = torch.randn((H, I), generator=g, device=device) * 0.02
+            blobs[i, :blob_bytes] = pack.pack_nvfp4_expert(G, U, D)
+        return gate, blobs, blob_bytes
     g = torch.Generator(device=device).manual_seed(seed)
     gate = (torch.randn((E, H), generator=g, device=device) * 0.02).float()
     blob_bytes = 3 * I * (H // 64 * 36) + 16
@@ -182,7 +205,8 @@ def main():
     ap.add_argument("--copies", type=int, default=LAYER_COPIES, help="layer copies the steps cycle through (1 for a small profiler capture)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: 64 tokens a step (the default line); prefill: --tokens rows a step, Zipf(1.1) expert popularity, tcgen05 grouped experts")
-    ap.add_argument("--tokens", type=int, default=4096, help="rows per step of the prefill workload (4096 or 16384 in the reference's configs)")
+    ap.add_argument("--tokens", type=int, default=4096, help="rows per step of the prefill workload, per GPU (4096 or 16384 in the reference's configs)")
+    ap.add_argument("--shape", default="c1", choices=sorted(SHAPES), help="layer of the prefill workload: c1 (H 2048, 512 experts) or c3 (H 7168, 256 experts)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -204,10 +228,10 @@ def main():
     if world > 1:
         dist.barrier()
     lib = capi.lib()
+    if args.workload == "prefill":
+        return run_prefill(args, dev, rank, world)
     if world > 1:
         return run_expert_parallel(args, rank, world, dev)
-    if args.workload == "prefill":
-        return run_prefill(args, dev)
 
     gate, blobs, blob_bytes = make_layer_weights(dev)
     L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
@@ -396,91 +420,128 @@ def zipf_logits(n_tokens, n_expert, gen, dev, s=1.1):
     return (logp[None, :] - torch.log(-torch.log(u))).contiguous()
 
 
-def run_prefill(args, dev):
-    """The prompt-sized workload: the same layer, --tokens rows a step, expert popularity Zipf(1.1) (scores drawn, as the
-    reference's prompt benches have no dataset for this path either).  One step = gate product + selection + dispatch with
-    the 128-row tile list + grouped experts on the tcgen05 tensor cores (routed + shared) + combine.  Weights (0.9 GB, all
-    touched every step) exceed L2.  The roofline is the tensor one: 6 H I flops per routed row over the measured bf16 peak
-    (the products run as kind::f16 on exactly decoded weights); the HBM time of the touched blobs is reported beside it."""
-    from basalt_b200 import capi, moe
+def run_prefill(args, dev, rank=0, world=1):
+    """The prompt-sized workload: --tokens rows a step per GPU on the layer --shape names.  c1: expert popularity Zipf(1.1)
+    (scores drawn; the reference's prompt benches have no dataset for this path either); c3: the router's own scores.
+    One step = gate product (tensor cores) + selection + dispatch with the 128-row tile list + grouped experts on the tcgen05
+    tensor cores (routed + shared) + combine.  With N > 1 ranks the routed experts are sharded (expert parallel, collective
+    form: all-gather, local experts, reduce-scatter) and every rank brings --tokens rows (weak scaling).  The roofline is the
+    tensor one: 6 H I flops per expert row over the measured bf16 peak (the products run as kind::f16 on exactly decoded
+    weights); the HBM time of the touched blobs is reported beside it."""
+    from basalt_b200 import capi, ep, moe
+    import torch.distributed as dist
+    sh = SHAPES[args.shape]
+    Hs, Es, Is, ks = sh["H"], sh["E"], sh["I"], sh["k"]
     Tn = args.tokens
-    gate, blobs, blob_bytes = make_layer_weights(dev)
-    L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
-    rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
-    layer = moe.PrefillMoELayer(gate, None, blobs[:E], L, rargs, shared_blob=blobs[E], max_tokens=Tn)
-    g = torch.Generator(device=dev).manual_seed(1)
+    El = Es // world
+    gate, own, blob_bytes = make_layer_weights(dev, E=Es, H=Hs, I=Is, first=rank * El, count=El)
+    _, shared, _ = make_layer_weights(dev, E=Es, H=Hs, I=Is, first=Es, count=1)
+    L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, Hs, Is)
+    assert L.bytes == blob_bytes
+    gk = capi.GATE_SOFTMAX if sh["gate"] == "softmax" else capi.GATE_SIGMOID
+    rargs = moe.RouterArgs(n_expert=Es, n_embd=Hs, k=ks, weight_scale=sh["scale"], gate=gk, n_group=sh["n_group"], topk_group=sh["topk_group"])
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    bias = (torch.randn(Es, generator=torch.Generator(device=dev).manual_seed(7), device=dev) * 0.01).float() if sh["bias"] else None
+    if world == 1:
+        layer = moe.PrefillMoELayer(gate, bias, own, L, rargs, shared_blob=shared[0], max_tokens=Tn)
+    else:
+        layer = ep.EPPrefillMoELayer(gate, bias, own, L, rargs, Es, shared_blob=shared[0], max_tokens=Tn)
     n_batches = 2
-    xs = [torch.randn((Tn, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
-    lgs = [zipf_logits(Tn, E, g, dev) for _ in range(n_batches)]
+    xs = [torch.randn((Tn, Hs), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
+    lgs = [zipf_logits(Tn, Es, g, dev) if (sh["zipf"] and world == 1) else None for _ in range(n_batches)]
     stream = torch.cuda.Stream(device=dev)
-    torch.cuda.synchronize()
+
+    def fwd(i, x=None):
+        xx = xs[i % n_batches] if x is None else x
+        return layer.forward(xx, lgs[i % n_batches], stream) if world == 1 else layer.forward(xx)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    barrier()
     with torch.cuda.stream(stream):
         for i in range(args.warmup):
-            layer.forward(xs[i % n_batches], lgs[i % n_batches], stream)
-        torch.cuda.synchronize()
+            fwd(i)
+        barrier()
         if int(layer.status.item()) != 0:
             raise SystemExit("the prefill kernel reported a bounded wait that ran out (status %d)" % int(layer.status.item()))
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(dev.index or 0) as clocks:
             ev0.record(stream)
             for i in range(args.steps):
-                layer.forward(xs[i % n_batches], lgs[i % n_batches], stream)
+                fwd(i)
             ev1.record(stream)
-            torch.cuda.synchronize()
+            barrier()
         ms_step = ev0.elapsed_time(ev1) / args.steps
         # end to end: pinned host rows in, host result out, every step
         x_host = [x.cpu().pin_memory() for x in xs]
-        xin = torch.empty((Tn, H), dtype=torch.bfloat16, device=dev)
-        y_host = torch.empty((Tn, H), dtype=torch.float32).pin_memory()
+        xin = torch.empty((Tn, Hs), dtype=torch.bfloat16, device=dev)
+        y_host = torch.empty((Tn, Hs), dtype=torch.float32).pin_memory()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         n_e2e = max(3, args.steps // 2)
+        barrier()
         e0.record(stream)
         for i in range(n_e2e):
             xin.copy_(x_host[i % n_batches], non_blocking=True)
-            y_host.copy_(layer.forward(xin, lgs[i % n_batches], stream), non_blocking=True)
+            y_host.copy_(fwd(i, xin), non_blocking=True)
             stream.synchronize()
         e1.record(stream)
-        torch.cuda.synchronize()
+        barrier()
         ms_e2e = e0.elapsed_time(e1) / n_e2e
-        # stage times
-        names = ["router_logits", "router_select", "dispatch", "experts", "combine"]
-        acc = {n: 0.0 for n in names}
-        n_inst = min(args.steps, 10)
-        touched = 0
-        for i in range(n_inst):
-            layer.events = []
-            layer.forward(xs[i % n_batches], lgs[i % n_batches], stream)
-            stream.synchronize()
-            evs = layer.events
-            for (_, a), (nme, b) in zip(evs[:-1], evs[1:]):
-                acc[nme] += a.elapsed_time(b)
-            touched += int((layer.cnt > 0).sum().item())
-        layer.events = None
-        stage_ms = {k: v / n_inst for k, v in acc.items()}
-        touched /= n_inst
-        cnt = layer.cnt.cpu().numpy()
+        stage_ms, touched, cnt = {}, float(El), None
+        if world == 1:
+            names = ["router_logits", "router_select", "dispatch", "experts", "combine"]
+            acc = {n: 0.0 for n in names}
+            n_inst = min(args.steps, 10)
+            touched = 0
+            for i in range(n_inst):
+                layer.events = []
+                fwd(i)
+                stream.synchronize()
+                evs = layer.events
+                for (_, a), (nme, b) in zip(evs[:-1], evs[1:]):
+                    acc[nme] += a.elapsed_time(b)
+                touched += int((layer.cnt > 0).sum().item())
+            layer.events = None
+            stage_ms = {k: v / n_inst for k, v in acc.items()}
+            touched /= n_inst
+            cnt = layer.cnt.cpu().numpy()
     status = int(layer.status.item())
-    flops = 6.0 * H * I * (Tn * K_TOP + Tn)
+    times = torch.tensor([ms_step, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_step, ms_e2e = times.tolist()
+    if rank != 0:
+        return
+    flops = 6.0 * Hs * Is * (Tn * ks + Tn) * world
     peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
     tpeak = float(peaks.get("bf16_tflops", 1590.0))
     hbm = float(peaks.get("hbm_gbs", 6650.0))
-    exp_ms = stage_ms["experts"]
-    achieved = flops / (exp_ms * 1e-3) / 1e12
+    # the tensor roofline of the expert stage (one GPU: its own stage time; N GPUs: the whole step, per GPU)
+    exp_ms = stage_ms["experts"] if world == 1 else ms_step
+    achieved = flops / world / (exp_ms * 1e-3) / 1e12
     blob_b = touched * (L.bytes - 16)
+    roof = {"bound": "tensor", "kernel": "prefill_gemm_kernel<gate/up> + <down> (+ activation prep)" if world == 1 else "whole step per GPU (experts + collectives)",
+            "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak,
+            "peak_source": "measured bf16 burst (MEASURED_PEAKS.json)" if peaks else "fallback", "traffic": None,
+            "algorithmic_flops_per_launch": flops / world, "kernel_ms": exp_ms, "hbm_ms_of_touched_blobs": blob_b / (hbm * 1e9) * 1e3,
+            "tensor_ms_at_peak": flops / world / (tpeak * 1e12) * 1e3, "experts_touched": touched}
+    if cnt is not None:
+        roof.update(max_rows_per_expert=int(cnt.max()), median_rows_per_expert=float(np.median(cnt[:Es])))
     line = {
-        "metric": "MoE-layer tokens/s (prefill)", "value": Tn / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "metric": "MoE-layer tokens/s (prefill)", "value": Tn * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp16 x (NVFP4 decoded exactly to fp16) on tcgen05 kind::f16, fp32 accumulation in tensor memory", "data": "synthetic",
-        "config": dict(CFG, workload=f"flash-next-style MoE layer prefill, {Tn} tokens/step, Zipf(1.1) expert popularity", tokens_per_step=Tn,
-                       l2_policy="every step reads all touched expert blobs (~0.9 GB): larger than L2", parallelism="single GPU"),
-        "e2e": {"value": Tn / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": Tn * H * 2, "d2h_bytes_per_step": Tn * H * 4},
-        "gpu_launches": 9 * args.steps,   # gate product, selection, 2 column copies, 3 dispatch kernels... counted per step below
-        "roofline": {"bound": "tensor", "kernel": "prefill_gemm_kernel<gate/up> + <down> (+ activation prep)", "achieved": achieved, "peak": tpeak,
-                     "unit": "TFLOP/s", "frac": achieved / tpeak, "peak_source": "measured bf16 burst (MEASURED_PEAKS.json)" if peaks else "fallback",
-                     "traffic": None, "algorithmic_flops_per_launch": flops, "kernel_ms": exp_ms,
-                     "hbm_ms_of_touched_blobs": blob_b / (hbm * 1e9) * 1e3, "tensor_ms_at_peak": flops / (tpeak * 1e12) * 1e3,
-                     "experts_touched": touched, "max_rows_per_expert": int(cnt.max()), "median_rows_per_expert": float(np.median(cnt[:E]))},
-        "stage_ms": stage_ms, "status_word": status, "clocks": clocks.summary(),
+        "config": dict(workload=f"{sh['name']} prefill, {Tn} tokens/step per GPU" + (", Zipf(1.1) expert popularity" if lgs[0] is not None else ""),
+                       hidden=Hs, n_expert=Es, n_shared=1, intermediate=Is, top_k=ks, router=sh["gate"], n_group=sh["n_group"], topk_group=sh["topk_group"],
+                       expert_format="NVFP4 (ggml block_nvfp4 + fp32 tail scales)", activations="bf16", tokens_per_step=Tn * world,
+                       l2_policy=f"every step reads all touched expert blobs ({blob_b / 1e9:.2f} GB per GPU): larger than L2",
+                       parallelism="single GPU" if world == 1 else f"ep{world}: {El} routed experts per GPU; all-gather of bf16 rows and routing, reduce-scatter of fp32 partial sums"),
+        "e2e": {"value": Tn * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": Tn * Hs * 2 * world, "d2h_bytes_per_step": Tn * Hs * 4 * world},
+        "gpu_launches": (12 if world == 1 else 16) * args.steps,   # image prep x2, gate GEMM, selection, 3 dispatch, activation prep, gate/up, down, combine (+ shared expert's three and the partial combine with N > 1)
+        "roofline": roof, "stage_ms": stage_ms, "status_word": status, "clocks": clocks.summary(),
     }
     print(json.dumps(line))
 

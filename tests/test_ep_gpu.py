@@ -51,10 +51,18 @@ def _rank(rank, world, port, q):
     yc = coll.forward(xf).clone()
     yc2 = coll.forward(xf).clone()
     wantc = single.forward(xf).clone()
+    # the prompt-sized form (tensor-core experts): against the single-GPU prompt layer, and that layer against the decode one
+    pre = ep.EPPrefillMoELayer(gw, None, own, L, args, E, shared_blob=bd[E], max_tokens=T)
+    yp = pre.forward(xf).clone()
+    single_p = moe.PrefillMoELayer(gw, None, bd[:E], L, args, shared_blob=bd[E], max_tokens=T)
+    wantp = single_p.forward(xf).clone()
     torch.cuda.synchronize()
     relc = float((yc - wantc).norm() / wantc.norm())
+    relp = float((yp - wantp).norm() / wantp.norm())
+    relpd = float((wantp - wantc).norm() / wantc.norm())
+    st = int(pre.status.item()) | int(single_p.status.item())
     q.put((rank, bool(torch.equal(y.view(torch.int32), want.view(torch.int32))), bool(torch.equal(y.view(torch.int32), y2.view(torch.int32))),
-           float((y - want).abs().max()), relc, bool(torch.equal(yc.view(torch.int32), yc2.view(torch.int32)))))
+           float((y - want).abs().max()), relc, bool(torch.equal(yc.view(torch.int32), yc2.view(torch.int32))), relp, relpd, st))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -72,7 +80,10 @@ def test_ep_two_gpus_matches_single_gpu(lib):
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    for rank, same, stable, err, relc, stablec in res:
+    for rank, same, stable, err, relc, stablec, relp, relpd, st in res:
+        assert st == 0, f"rank {rank}: a bounded wait inside a prefill kernel gave up"
+        assert relp < 1e-5, f"rank {rank}: expert-parallel prompt layer differs from the single-GPU prompt layer (relative L2 {relp})"
+        assert relpd < 2e-3, f"rank {rank}: prompt layer differs from the decode layer (relative L2 {relpd})"
         assert stable, f"rank {rank}: all-to-all form not bit-stable from run to run"
         assert same, f"rank {rank}: all-to-all form differs from the single-GPU layer (max abs {err})"
         assert relc < 1e-5, f"rank {rank}: collective form differs from the single-GPU layer (relative L2 {relc})"
