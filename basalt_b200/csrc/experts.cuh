@@ -43,12 +43,48 @@ __device__ __forceinline__ void store_out(void* out, int kind, int64_t i, float 
     else static_cast<float*>(out)[i] = v;
 }
 
+// 16 consecutive values [16 sb, 16 sb + 16) of an activation row
+__device__ __forceinline__ void load16(const void* x, int kind, int64_t row, int64_t K, int sb, float (&v)[16]) {
+    if (kind == BSX_X_F32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) + row * K + 16 * sb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 f = p[i];
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+    } else if (kind == BSX_X_BF16) {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x) + row * K + 16 * sb);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint4 u = p[i];
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+                v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+            }
+        }
+    } else {   // q8_1: 36-byte blocks {fp16 d, fp16 sum, 32 int8}; value = d * q
+        const uint32_t* p = reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(x) + (row * (K / 32) + (sb >> 1)) * 36);
+        const float d = __half2float(__ushort_as_half((unsigned short) (p[0] & 0xFFFFu)));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t w = p[1 + 4 * (sb & 1) + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[4 * i + j] = d * (float) (int8_t) ((w >> (8 * j)) & 0xFFu);
+        }
+    }
+}
+
 // 0 all launches, 1 gate/up only, 2 down only (bsx_experts_set_phase)
 int experts_phase();
 
 int32_t experts_grouped_simple(const ExpertArgs& a, cudaStream_t st);
 // returns BSX_E_TYPE when the fast path does not cover the layout (the caller then runs the plain kernels)
 int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st);
+// the same call over blobs repacked by bsx_expert_pack (experts_nvf4.cu): block-scaled FP4 MMAs straight on the NVFP4 codes
+int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st);
+size_t experts_packed_scratch_bytes(int64_t cap_entries, int64_t n_embd, int64_t n_ff);
 size_t experts_mma_scratch_bytes(int64_t cap_entries, int64_t n_embd, int64_t n_ff);
 
 }  // namespace bsx

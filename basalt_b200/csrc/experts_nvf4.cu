@@ -1,0 +1,610 @@
+// experts_nvf4.cu - decode-sized grouped experts on the block-scaled FP4 tensor cores: tcgen05.mma kind::mxf4nvf4 reads the
+// NVFP4 codes and their UE4M3 block scales exactly as they are stored, so the weight stream needs no arithmetic at all and
+// the kernel is what the workload is: a copy from HBM into shared memory at the pace of the memory system.
+//
+// What makes that possible:
+//  * An NVFP4 block IS the tensor core's operand: 16 E2M1 codes share one UE4M3 scale (scale_vec::4X), element 2i of a
+//    16-value sub-block in the low nibble of byte i and element 2i + 1 in the high nibble.  ggml stores value b and value
+//    b + 8 in byte b (include/basalt/ggml/ggml_common.h:146-156), i.e. the same thing up to a fixed permutation inside the
+//    sub-block, which the activation side simply shares.  ggml's decode (value = doubled-E2M1 x scale / 2,
+//    src/kernels/cpu/ggml/ggml_quants.c:1397-1422) equals E2M1 x UE4M3, the product the hardware forms.
+//  * The only thing in the way is the layout: ggml interleaves 4 scale bytes with 32 code bytes (36-byte blocks), which
+//    no 16-byte copy can split.  bsx_expert_pack rewrites a blob once, at load time, into planes (codes row-major; scales
+//    in the 32-lane x 4-word order tcgen05.cp wants), the same bytes in another order - Basalt does the like for its own
+//    FP4 kernels (include/basalt/kernels/nvfp4_planes.hpp:6-20).
+//  * Activations must be FP4 too.  One FP4 term is worth ~3.3 bits, far from the 2e-3 bar; so a row goes in as FOUR terms
+//    (each term quantises the residual the terms before it left, with its own block scales): relative error ~1e-4.  The
+//    terms are extra columns of the small operand - 8 entries x 4 terms = 32 columns - which costs nothing here because
+//    the tensor core idles anyway: the kernel is bound by the weight stream.
+//
+// Kernel: persistent CTAs, one per SM, static round-robin over work units (pass of <= 8 entries of one expert, block of
+// 2 x 128 weight rows: 128 gate rows with their 128 up rows, or 256 down rows).  Warp 0 issues tcgen05.cp (scales ->
+// tensor memory) and the MMAs (M = 128 weight rows, N = 32 columns, K = 64 per instruction); warps 1-2 stream the operands
+// with cp.async into 128-byte-swizzled stages of 256 columns (4-stage ring, continuous across units); warps 3-6 are the
+// epilogue (thread = TMEM lane = weight row: sums each entry's four term columns, applies row and tail scales, SwiGLU for
+// gate/up, stores coalesced).  Two accumulator sets in tensor memory let the epilogue of one unit overlap the stream of
+// the next.  Every mbarrier wait is time-bounded and reports through a status word.
+//
+// Semantics: Basalt's native_expert_grouped (include/basalt/kernels/iq_kernels.hpp:77-92) without its int8 rounding of x, h.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "experts.cuh"
+#include "formats.cuh"
+#include "tc5.cuh"
+
+namespace bsx {
+namespace {
+
+constexpr int kTermsF = 4;                 // FP4 terms per activation row
+constexpr int kEntF = 8;                   // entries per pass
+constexpr int kColsF = kTermsF * kEntF;    // 32 = MMA N
+constexpr int kStagesF = 4;
+constexpr int kATile = 128 * 128;          // one operand tile of a stage: 128 rows x 128 bytes (256 columns of codes)
+constexpr int kBTile = kColsF * 128;
+constexpr int kSFTile = 4 * 512;           // 4 K-steps x (32 lanes x 4 words)
+constexpr int kOffA1 = kATile, kOffB = 2 * kATile, kOffSFA0 = kOffB + kBTile, kOffSFA1 = kOffSFA0 + kSFTile, kOffSFB = kOffSFA1 + kSFTile;
+constexpr int kStageF = kOffSFB + kSFTile;             // 43,008 bytes
+constexpr int kThreadsF = 32 * 7;                      // MMA warp, two loader warps, four epilogue warps
+constexpr size_t kSmemF = 1024 + (size_t) kStagesF * kStageF + 256;
+// tensor-memory columns: two accumulator sets of (D0, D1) x 32 columns, then per stage 16 columns each for SFA0, SFA1, SFB
+constexpr uint32_t kTmemSF = 128, kTmemCols = 512;
+// kind::mxf4nvf4, scale_vec::4X: E2M1 x E2M1, UE4M3 scales (bit 23 = 0), both K-major, N = 32, M = 128
+constexpr uint32_t kIdescF = (1u << 7) | (1u << 10) | ((uint32_t) (kColsF >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
+
+enum { FMODE_GU = 0, FMODE_DOWN = 1 };
+
+size_t al256f(size_t v) { return (v + 255) & ~(size_t) 255; }
+
+// ---------------------------------------------------------------- packed blob geometry
+struct PackedGeom {
+    size_t gate_codes, up_codes, down_codes, gate_sf, up_sf, down_sf, tail, bytes;
+};
+__host__ __device__ inline PackedGeom packed_geom(int64_t H, int64_t I) {
+    PackedGeom g;
+    const size_t gu_codes = (size_t) I * H / 2, d_codes = (size_t) H * I / 2;
+    const size_t gu_sf = (size_t) I * (H / 64) * 4, d_sf = (size_t) H * (I / 64) * 4;
+    g.gate_codes = 0;
+    g.up_codes = gu_codes;
+    g.down_codes = 2 * gu_codes;
+    g.gate_sf = 2 * gu_codes + d_codes;
+    g.up_sf = g.gate_sf + gu_sf;
+    g.down_sf = g.up_sf + gu_sf;
+    g.tail = g.down_sf + d_sf;
+    g.bytes = g.tail + 16;
+    return g;
+}
+
+// One thread per (matrix row, 64-column block): 36 bytes in, 32 code bytes and one scale word out.  A scale byte keeps its
+// low 7 bits and 0x7F becomes 0, which is what the ggml decoder does with them (ggml_quants.c:1397-1406).
+__global__ void __launch_bounds__(256) pack_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, bsx_expert_layout L) {
+    const int64_t H = L.n_embd, I = L.n_ff;
+    const PackedGeom g = packed_geom(H, I);
+    const int64_t n_gu = I * (H / 64), n_d = H * (I / 64);
+    const int64_t i = (int64_t) blockIdx.x * 256 + threadIdx.x;
+    if (i == 0) {
+        for (int k = 0; k < 4; ++k) reinterpret_cast<float*>(out + g.tail)[k] = reinterpret_cast<const float*>(in + L.bytes - 16)[k];
+    }
+    if (i >= 2 * n_gu + n_d) return;
+    const int mat = i < n_gu ? 0 : (i < 2 * n_gu ? 1 : 2);
+    const int64_t j = i - (mat == 0 ? 0 : (mat == 1 ? n_gu : 2 * n_gu));
+    const int64_t K = mat == 2 ? I : H, R = mat == 2 ? H : I;
+    const int64_t nb = K / 64, row = j / nb, blk = j - row * nb;
+    const uint8_t* src = in + (mat == 0 ? 0 : (mat == 1 ? (size_t) L.up_off : (size_t) L.down_off)) +
+                         (size_t) row * (mat == 0 ? L.gu_row : (mat == 1 ? L.up_row : L.d_row)) + (size_t) blk * 36;
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(src);
+    uint32_t sc = w[0] & 0x7F7F7F7Fu;
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+        if (((sc >> (8 * b)) & 0xFFu) == 0x7Fu) sc &= ~(0xFFu << (8 * b));
+    uint8_t* codes = out + (mat == 0 ? g.gate_codes : (mat == 1 ? g.up_codes : g.down_codes)) + (size_t) row * (K / 2) + (size_t) blk * 32;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) reinterpret_cast<uint32_t*>(codes)[k] = w[1 + k];
+    // scale word of (row, K-step blk): [blk][row / 128][row % 32][(row % 128) / 32]
+    uint32_t* sf = reinterpret_cast<uint32_t*>(out + (mat == 0 ? g.gate_sf : (mat == 1 ? g.up_sf : g.down_sf)));
+    sf[((size_t) blk * (R / 128) + row / 128) * 128 + (row & 31) * 4 + ((row & 127) >> 5)] = sc;
+}
+
+// ---------------------------------------------------------------- FP4 activation images
+// UE4M3 (bias 7, no sign, 0x7F unused): the value of a byte, and the smallest byte whose value times 6 reaches amax.
+__device__ __forceinline__ float ue4m3_value(uint32_t b) {
+    const int e = (int) (b >> 3), m = (int) (b & 7u);
+    return e ? ldexpf(1.f + (float) m * 0.125f, e - 7) : ldexpf((float) m, -9);
+}
+__device__ __forceinline__ uint32_t ue4m3_cover(float amax) {
+    if (!(amax > 0.f)) return 0u;
+    const float t = amax / 6.f;
+    uint32_t b;
+    if (t < 0.015625f) {
+        b = (uint32_t) ceilf(t * 512.f);
+    } else {
+        uint32_t bits = __float_as_uint(t) + 0x000FFFFFu;
+        const int e = (int) (bits >> 23) - 127 + 7;
+        b = e > 15 ? 0x7Eu : (uint32_t) ((e << 3) | (int) ((bits >> 20) & 7u));
+    }
+    if (b > 0x7Eu) b = 0x7Eu;
+    if (b > 0u && ue4m3_value(b - 1) * 6.f >= amax) --b;       // t was rounded up by the division
+    if (b < 0x7Eu && ue4m3_value(b) * 6.f < amax) ++b;         // ... or down
+    return b;
+}
+// two floats -> two E2M1 codes (round to nearest even, saturating): `lo` in bits 0-3, `hi` in bits 4-7
+__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
+    uint16_t r;
+    asm("{\n.reg .b8 t;\ncvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\ncvt.u16.u8 %0, t;\n}\n" : "=h"(r) : "f"(hi), "f"(lo));
+    return (uint32_t) r & 0xFFu;
+}
+__device__ __forceinline__ float e2m1_value(uint32_t c) {
+    const float m = (c & 7u) < 2u ? 0.5f * (float) (c & 7u) : ldexpf(1.f + 0.5f * (float) (c & 1u), (int) ((c >> 1) & 3u) - 1);
+    return (c & 8u) ? -m : m;
+}
+
+// One warp per activation row: the row times a power of two (largest magnitude into [2^7, 2^8), so block scales sit well
+// inside UE4M3's range) as kTermsF FP4 terms.  Term t of a 16-value sub-block: scale = the smallest UE4M3 value s with
+// 6 s >= the largest residual, codes = rn(residual / s), residual -= code value x s.  Layout: codes [row][term][K / 2]
+// bytes with ggml's nibble order (byte b of a sub-block = values b and b + 8), scales [row][term][K / 16] bytes, inv[row].
+// FROM_H = false: rows of x (kind x_kind) - row i of x when the caller gave the number of x rows, else the row of entry
+// i; true: row e of the SwiGLU output h.  The last block lists the passes (up to kEntF consecutive entries of one group).
+template <bool FROM_H>
+__global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __restrict__ codes, uint8_t* __restrict__ sfs, float* __restrict__ inv,
+                                                        int2* __restrict__ items, int* __restrict__ n_items) {
+    const int ng = min(*a.n_groups, (int) a.cap_groups);
+    const int total = min(a.grp_start[ng], (int) a.cap_entries);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (blockIdx.x == gridDim.x - 1) {
+        __shared__ int sh[8];
+        __shared__ int s_base;
+        if (threadIdx.x == 0) s_base = 0;
+        __syncthreads();
+        for (int g0 = 0; g0 < ng; g0 += 256) {
+            const int g = g0 + threadIdx.x;
+            const int s0 = g < ng ? a.grp_start[g] : 0;
+            const int cnt = g < ng ? max(0, min(a.grp_start[g + 1], (int) a.cap_entries) - s0) : 0;
+            const int np = (cnt + kEntF - 1) / kEntF;
+            int x = np;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_up_sync(kFull, x, o);
+                if (lane >= o) x += y;
+            }
+            if (lane == 31) sh[warp] = x;
+            __syncthreads();
+            int before = s_base;
+            for (int w = 0; w < warp; ++w) before += sh[w];
+            for (int p = 0; p < np; ++p) items[before + x - np + p] = make_int2(g, s0 + p * kEntF);
+            __syncthreads();
+            if (threadIdx.x == 255) s_base = before + x;
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) n_items[0] = s_base;
+        return;
+    }
+    const int i = blockIdx.x * 8 + warp;   // image row
+    const int n_img = FROM_H ? total : (a.n_x_rows > 0 ? a.n_x_rows : total);
+    if (i >= n_img) return;
+    const int64_t K = FROM_H ? a.L.n_ff : a.L.n_embd;
+    const int64_t row = FROM_H ? (int64_t) i : (a.n_x_rows > 0 ? (int64_t) i : (int64_t) a.ent_tok[i]);
+    const void* src = FROM_H ? (const void*) a.h : a.x;
+    const int kind = FROM_H ? BSX_X_F32 : a.x_kind;
+    const int n_sb = (int) (K >> 4);
+    float amax = 0.f;
+    for (int sb = lane; sb < n_sb; sb += 32) {
+        float v[16];
+        load16(src, kind, row, K, sb, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    }
+    amax = warp_max_xor(amax);
+    int ex = 0;
+    float s = 1.f, iv = 1.f;
+    if (amax > 0.f && amax <= 3.0e38f) {
+        frexpf(amax, &ex);                          // amax = f 2^ex, f in [0.5, 1)
+        ex = max(-100, min(100, 8 - ex));
+        s = ldexpf(1.f, ex);
+        iv = ldexpf(1.f, -ex);
+    }
+    if (lane == 0) inv[i] = iv;
+    for (int sb = lane; sb < n_sb; sb += 32) {
+        float v[16];
+        load16(src, kind, row, K, sb, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] *= s;
+#pragma unroll
+        for (int t = 0; t < kTermsF; ++t) {
+            float m = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) m = fmaxf(m, fabsf(v[j]));
+            const uint32_t sb8 = ue4m3_cover(m);
+            const float sv = ue4m3_value(sb8);
+            uint32_t w0 = 0u, w1 = 0u;
+            if (sv > 0.f) {
+#pragma unroll
+                for (int b = 0; b < 8; ++b) {
+                    const uint32_t c = e2m1x2(v[b] / sv, v[b + 8] / sv);
+                    v[b] -= e2m1_value(c & 15u) * sv;
+                    v[b + 8] -= e2m1_value(c >> 4) * sv;
+                    if (b < 4) w0 |= c << (8 * b);
+                    else w1 |= c << (8 * (b - 4));
+                }
+            }
+            const size_t r4 = (size_t) i * kTermsF + t;
+            *reinterpret_cast<uint2*>(codes + r4 * (K / 2) + (size_t) sb * 8) = make_uint2(w0, w1);
+            sfs[r4 * (K / 16) + sb] = (uint8_t) sb8;
+        }
+    }
+}
+
+// ---------------------------------------------------------------- the stream kernel
+struct StreamArgs {
+    ExpertArgs e;
+    const uint8_t* codes;     // activation images
+    const uint8_t* sfs;
+    const float* inv;
+    const int2* items;
+    const int* n_items;
+    int32_t* status;
+};
+
+__device__ __forceinline__ uint64_t sf_desc(uint32_t addr) {   // 32 rows x 16 bytes, 8-row groups 128 bytes apart, no swizzle
+    return (uint64_t) ((addr & 0x3FFFFu) >> 4) | ((uint64_t) (128 >> 4) << 16) | ((uint64_t) (128 >> 4) << 32) | ((uint64_t) 1 << 46);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStagesF * kStageF);
+    uint64_t* empty = full + kStagesF;
+    uint64_t* acc_full = empty + kStagesF;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const ExpertArgs& a = sa.e;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t K = MODE == FMODE_GU ? a.L.n_embd : a.L.n_ff;
+    const int64_t R = MODE == FMODE_GU ? a.L.n_ff : a.L.n_embd;       // rows of each weight matrix
+    const int n_chunk = (int) (K >> 8);                                 // stages (256 columns) per unit
+    constexpr int kRowsPerUnit = MODE == FMODE_GU ? 128 : 256;
+    const int n_rb = (int) ((R + kRowsPerUnit - 1) / kRowsPerUnit);
+    const int n_units = sa.n_items[0] * n_rb;
+    const PackedGeom geo = packed_geom(a.L.n_embd, a.L.n_ff);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStagesF; ++s) {
+            mbar_init(&full[s], 64);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+
+    // a unit: pass = unit / n_rb (group, first entry), row block = unit % n_rb.  Tile 0 / tile 1 of the unit: the 128 gate
+    // rows r0.. and the 128 up rows r0.. (gate/up), or down rows r0.. and r0 + 128.. (down).
+    struct Unit { const uint8_t* blob; int eb, ntok, r0; };
+    auto get_unit = [&](int unit, Unit& u) {
+        const int pass = unit / n_rb;
+        const int2 it = sa.items[pass];
+        u.blob = reinterpret_cast<const uint8_t*>(a.grp_ptr[it.x]);
+        u.eb = it.y;
+        u.ntok = min(kEntF, min(a.grp_start[it.x + 1], (int) a.cap_entries) - it.y);
+        u.r0 = (unit - pass * n_rb) * kRowsPerUnit;
+    };
+
+    if (warp == 0) {
+        // ---- MMA issuer: per 64-column K-step the three scale copies (smem -> tensor memory), then one MMA per tile
+        if (lane == 0) {
+            uint32_t kc = 0, ti = 0;
+            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+                const uint32_t acc = ti & 1u;
+                ok = mbar_wait(&acc_empty[acc], ((ti >> 1) & 1u) ^ 1u);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t d0 = tmem + acc * 64, d1 = d0 + 32;
+                for (int c = 0; c < n_chunk; ++c, ++kc) {
+                    const uint32_t s = kc % kStagesF;
+                    ok = mbar_wait(&full[s], (kc / kStagesF) & 1u);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t st = smem_u32(smem + s * kStageF);
+                    const uint32_t tsf = tmem + kTmemSF + s * 48;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsf + 4 * k), "l"(sf_desc(st + kOffSFA0 + k * 512)) : "memory");
+                        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsf + 16 + 4 * k), "l"(sf_desc(st + kOffSFA1 + k * 512)) : "memory");
+                        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsf + 32 + 4 * k), "l"(sf_desc(st + kOffSFB + k * 512)) : "memory");
+                        const uint64_t bd = smem_desc_sw128(st + kOffB + k * 32);
+                        const uint32_t accum = (c | k) ? 1u : 0u;
+                        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+                                     "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::"r"(d0),
+                                     "l"(smem_desc_sw128(st + k * 32)), "l"(bd), "r"(kIdescF), "r"(tsf + 4 * k), "r"(tsf + 32 + 4 * k), "r"(accum)
+                                     : "memory");
+                        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+                                     "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::"r"(d1),
+                                     "l"(smem_desc_sw128(st + kOffA1 + k * 32)), "l"(bd), "r"(kIdescF), "r"(tsf + 16 + 4 * k), "r"(tsf + 32 + 4 * k), "r"(accum)
+                                     : "memory");
+                    }
+                    umma_commit(&empty[s]);
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[acc]);
+                ++ti;
+            }
+            if (!ok) atomicOr(sa.status, 1);
+        }
+    } else if (warp <= 2) {
+        // ---- loaders.  Warp 1: tile 0, its scales, the activation codes; warp 2: tile 1, its scales, the activation scales.
+        // A lane copies 16-byte chunk lane % 8 of rows lane / 8 + 4 i (eight lanes = one 128-byte row of a stage); it runs
+        // up to two stages ahead of its own landed copies and arrives on a stage once its copies there are visible.
+        const int lw = warp - 1, c8 = lane & 7, r4 = lane >> 3;
+        uint32_t dsto[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r7 = 4 * h + r4;
+            dsto[h] = (uint32_t) (r7 * 128 + ((c8 ^ r7) << 4));
+        }
+        uint32_t issued = 0, arrived = 0;
+        for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+            Unit u;
+            get_unit(unit, u);
+            // weight tile rows (clamped to the matrix) and this warp's planes
+            const uint8_t* wcodes;
+            const uint8_t* wsf;
+            int row_first;
+            if (MODE == FMODE_GU) {
+                wcodes = u.blob + (lw == 0 ? geo.gate_codes : geo.up_codes);
+                wsf = u.blob + (lw == 0 ? geo.gate_sf : geo.up_sf);
+                row_first = u.r0;
+            } else {
+                wcodes = u.blob + geo.down_codes;
+                wsf = u.blob + geo.down_sf;
+                row_first = min(u.r0 + 128 * lw, (int) R - 128);
+            }
+            const uint8_t* wrow0 = wcodes + (size_t) (row_first + r4) * (size_t) (K >> 1) + c8 * 16;
+            const size_t wpitch4 = (size_t) 4 * (size_t) (K >> 1);
+            const uint8_t* sfrow = wsf + (size_t) (row_first >> 7) * 512 + lane * 16;
+            const size_t sf_step = (size_t) (R >> 7) * 512;
+            // the pass's image rows: entry j -> image row (the entry itself, or its token when images are per x row)
+            int ir[kEntF];
+#pragma unroll
+            for (int j = 0; j < kEntF; ++j) {
+                const int e = u.eb + (j < u.ntok ? j : 0);
+                ir[j] = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
+            }
+            int ir_lane;    // the image row behind column n = lane (entry lane / 4)
+            {
+                const int e = u.eb + ((lane >> 2) < u.ntok ? (lane >> 2) : 0);
+                ir_lane = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
+            }
+            for (int c = 0; c < n_chunk; ++c) {
+                const uint32_t s = issued % kStagesF;
+                ok = mbar_wait(&empty[s], ((issued / kStagesF) & 1u) ^ 1u);
+                if (!ok) break;
+                const uint32_t st = smem_u32(smem + s * kStageF);
+                // weight codes: 128 rows x 128 bytes
+                {
+                    const uint8_t* g = wrow0 + (size_t) c * 128;
+                    const uint32_t dst = st + (lw == 0 ? 0u : (uint32_t) kOffA1);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t) ((i >> 1) * 1024) + dsto[i & 1]),
+                                     "l"(g + (size_t) i * wpitch4)
+                                     : "memory");
+                }
+                // weight scales: 4 K-steps x 512 bytes, one 16-byte piece per lane and step
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(st + (uint32_t) (lw == 0 ? kOffSFA0 : kOffSFA1) + k * 512 + lane * 16),
+                                 "l"(sfrow + (size_t) (4 * c + k) * sf_step)
+                                 : "memory");
+                if (lw == 0) {
+                    // activation codes: column n = 4 j + t is term t of entry j; rows 4 i + r4 -> entry i, term r4
+#pragma unroll
+                    for (int i = 0; i < kEntF; ++i) {
+                        const uint8_t* g = sa.codes + ((size_t) ir[i] * kTermsF + r4) * (size_t) (K >> 1) + (size_t) c * 128 + c8 * 16;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(st + (uint32_t) kOffB + (uint32_t) ((i >> 1) * 1024) + dsto[i & 1]), "l"(g)
+                                     : "memory");
+                    }
+                } else {
+                    // activation scales: column n = lane; its scale word of K-step k goes to word (n, 0) of that step's block
+                    const uint8_t* g = sa.sfs + ((size_t) ir_lane * kTermsF + (lane & 3)) * (size_t) (K >> 4) + (size_t) c * 16;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(st + (uint32_t) kOffSFB + k * 512 + lane * 16), "l"(g + 4 * k) : "memory");
+                }
+                asm volatile("cp.async.commit_group;\n" ::: "memory");
+                ++issued;
+                if (issued - arrived > 2) {
+                    asm volatile("cp.async.wait_group 2;\n" ::: "memory");
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    mbar_arrive(&full[arrived % kStagesF]);
+                    ++arrived;
+                }
+            }
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        for (; arrived < issued; ++arrived) mbar_arrive(&full[arrived % kStagesF]);
+        if (!ok) atomicOr(sa.status, 1);
+    } else {
+        // ---- epilogue: thread = TMEM lane = weight row of both tiles.  A warp may only read lanes 32 (warp % 4) .. + 31.
+        const int q = warp & 3;
+        const int rl = q * 32 + lane;
+        const uint32_t lane_base = (uint32_t) (q * 32) << 16;
+        uint32_t ti = 0;
+        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+            Unit u;
+            get_unit(unit, u);
+            const uint32_t acc = ti & 1u;
+            ok = __all_sync(kFull, mbar_wait(&acc_full[acc], (ti >> 1) & 1u));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            uint32_t d0[32], d1[32];
+            tmem_ld32(tmem + lane_base + acc * 64, d0);
+            tmem_ld32(tmem + lane_base + acc * 64 + 32, d1);
+            // the accumulators are in registers: the MMA warp may start the next unit on this set
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            mbar_arrive(&acc_empty[acc]);
+            ++ti;
+            const float* tail = reinterpret_cast<const float*>(u.blob + geo.tail);
+            const float sg = tail[0], su = tail[1], sd = tail[2];
+#pragma unroll
+            for (int j = 0; j < kEntF; ++j) {
+                if (j < u.ntok) {
+                    const int e = u.eb + j;
+                    const int irow = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
+                    const float f = sa.inv[irow];
+                    const float v0 = ((__uint_as_float(d0[4 * j]) + __uint_as_float(d0[4 * j + 1])) + __uint_as_float(d0[4 * j + 2])) + __uint_as_float(d0[4 * j + 3]);
+                    const float v1 = ((__uint_as_float(d1[4 * j]) + __uint_as_float(d1[4 * j + 1])) + __uint_as_float(d1[4 * j + 2])) + __uint_as_float(d1[4 * j + 3]);
+                    if (MODE == FMODE_GU) {
+                        if (u.r0 + rl < R) a.h[(int64_t) e * a.L.n_ff + u.r0 + rl] = swiglu(v0 * f * sg, v1 * f * su, a.L);
+                    } else {
+                        const int64_t o = (int64_t) a.ent_dst[e] * a.L.n_embd;
+                        const int rA = u.r0 + rl, rB = min(u.r0 + 128, (int) R - 128) + rl;
+                        if (rA < R) store_out(a.out, a.out_kind, o + rA, v0 * f * sd);
+                        if (u.r0 + 128 < R) store_out(a.out, a.out_kind, o + rB, v1 * f * sd);
+                    }
+                }
+            }
+        }
+        if (!ok && lane == 0) atomicOr(sa.status, 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+template <int MODE>
+int32_t launch_stream(const StreamArgs& sa, cudaStream_t st) {
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(nvf4_stream_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemF);
+        if (e != cudaSuccess) return (int32_t) e;
+        configured[dev] = true;
+    }
+    nvf4_stream_kernel<MODE><<<(unsigned) sm_count(), kThreadsF, kSmemF, st>>>(sa);
+    return launch_status();
+}
+
+}  // namespace
+
+// scratch beyond the SwiGLU buffer: x images (codes, scales), h images, inverse row scales, the pass list
+size_t experts_packed_scratch_bytes(int64_t cap, int64_t H, int64_t I) {
+    return al256f((size_t) cap * kTermsF * H / 2) + al256f((size_t) cap * kTermsF * H / 16) + al256f((size_t) cap * kTermsF * I / 2) +
+           al256f((size_t) cap * kTermsF * I / 16) + 2 * al256f((size_t) cap * 4) + al256f((size_t) (cap + 1) * 8 + 16);
+}
+
+int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st) {
+    const bsx_expert_layout& L = a.L;
+    if (L.gu_type != kTypeNVFP4 || L.up_type != kTypeNVFP4 || L.d_type != kTypeNVFP4) return BSX_E_TYPE;
+    if (L.n_embd % 256 || L.n_ff % 256) return BSX_E_TYPE;       // whole 256-column stages, whole 128-row tiles
+    const int64_t cap = a.cap_entries, H = L.n_embd, I = L.n_ff;
+    uint8_t* p = reinterpret_cast<uint8_t*>(a.h) + al256f((size_t) cap * I * 4);
+    uint8_t* xcodes = p;
+    p += al256f((size_t) cap * kTermsF * H / 2);
+    uint8_t* xsf = p;
+    p += al256f((size_t) cap * kTermsF * H / 16);
+    uint8_t* hcodes = p;
+    p += al256f((size_t) cap * kTermsF * I / 2);
+    uint8_t* hsf = p;
+    p += al256f((size_t) cap * kTermsF * I / 16);
+    float* xinv = reinterpret_cast<float*>(p);
+    p += al256f((size_t) cap * 4);
+    float* hinv = reinterpret_cast<float*>(p);
+    p += al256f((size_t) cap * 4);
+    int* n_items = reinterpret_cast<int*>(p);
+    int2* items = reinterpret_cast<int2*>(n_items + 4);
+    const int phase = experts_phase();
+    const int64_t x_rows = a.n_x_rows > 0 ? a.n_x_rows : cap;
+    const unsigned nbx = (unsigned) ((x_rows + 7) / 8 + 1), nbh = (unsigned) ((cap + 7) / 8 + 1);
+    StreamArgs sa;
+    sa.e = a;
+    sa.items = items;
+    sa.n_items = n_items;
+    sa.status = status;
+    int32_t rc = BSX_OK;
+    if (phase != 2) {
+        prep_fp4_kernel<false><<<nbx, 256, 0, st>>>(a, xcodes, xsf, xinv, items, n_items);
+        sa.codes = xcodes;
+        sa.sfs = xsf;
+        sa.inv = xinv;
+        rc = launch_stream<FMODE_GU>(sa, st);
+    }
+    if (rc != BSX_OK || phase == 1) return rc;
+    prep_fp4_kernel<true><<<nbh, 256, 0, st>>>(a, hcodes, hsf, hinv, items, n_items);
+    sa.codes = hcodes;
+    sa.sfs = hsf;
+    sa.inv = hinv;
+    return launch_stream<FMODE_DOWN>(sa, st);
+}
+
+}  // namespace bsx
+
+using namespace bsx;
+
+extern "C" size_t bsx_expert_packed_bytes(const bsx_expert_layout* L) {
+    if (!L || L->gu_type != kTypeNVFP4 || L->up_type != kTypeNVFP4 || L->d_type != kTypeNVFP4 || L->n_embd % 256 || L->n_ff % 256) return 0;
+    return (packed_geom(L->n_embd, L->n_ff).bytes + 255) & ~(size_t) 255;
+}
+
+extern "C" int32_t bsx_expert_pack(const bsx_expert_layout* L, const void* blob, void* packed, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (!L || !aligned(blob, 16) || !aligned(packed, 256)) return BSX_E_POINTER;
+    if (!bsx_expert_packed_bytes(L)) return BSX_E_TYPE;
+    const int64_t n = 2 * L->n_ff * (L->n_embd / 64) + L->n_embd * (L->n_ff / 64);
+    pack_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, (cudaStream_t) stream>>>(static_cast<const uint8_t*>(blob), static_cast<uint8_t*>(packed), *L);
+    return launch_status();
+}
+
+extern "C" size_t bsx_experts_packed_scratch_bytes(const bsx_expert_layout* L, int64_t cap_entries) {
+    if (!L || cap_entries < 0 || !bsx_expert_packed_bytes(L)) return 0;
+    return al256f((size_t) cap_entries * L->n_ff * 4) + experts_packed_scratch_bytes(cap_entries, L->n_embd, L->n_ff) + 4096;
+}
+
+extern "C" int32_t bsx_experts_grouped_packed(const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
+                                              const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
+                                              int64_t cap_entries, const void* x, int32_t x_kind, int32_t n_x_rows, void* scratch, void* out,
+                                              int32_t out_kind, int32_t* status, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (!layout || !status) return BSX_E_POINTER;
+    if (!bsx_expert_packed_bytes(layout)) return BSX_E_TYPE;
+    if (x_kind < BSX_X_F32 || x_kind > BSX_X_Q8_1 || (out_kind != BSX_OUT_F32 && out_kind != BSX_OUT_BF16)) return BSX_E_GEOMETRY;
+    if (cap_groups < 0 || cap_entries < 0 || cap_entries > (int64_t) 1 << 30) return BSX_E_GEOMETRY;
+    if (cap_groups == 0 || cap_entries == 0) return BSX_OK;
+    if (!grp_ptr || !grp_start || !n_groups || !ent_dst || !ent_tok || !aligned(x, 16) || !aligned(scratch, 256) || !aligned(out, 16)) return BSX_E_POINTER;
+    if (n_x_rows < 0 || n_x_rows > cap_entries) n_x_rows = 0;
+    ExpertArgs a;
+    a.L = *layout;
+    a.grp_ptr = grp_ptr;
+    a.grp_start = grp_start;
+    a.n_groups = n_groups;
+    a.ent_dst = ent_dst;
+    a.ent_tok = ent_tok;
+    a.cap_groups = cap_groups;
+    a.cap_entries = cap_entries;
+    a.x = x;
+    a.x_kind = x_kind;
+    a.h = static_cast<float*>(scratch);
+    a.out = out;
+    a.out_kind = out_kind;
+    a.n_x_rows = n_x_rows;
+    a.grid = nullptr;
+    return experts_grouped_packed(a, status, (cudaStream_t) stream);
+}

@@ -217,6 +217,28 @@ def native_expert_grouped(L: ExpertLayout, grp_ptr, grp_start, n_groups, ent_dst
     return out
 
 
+def pack_experts(L: ExpertLayout, blobs: torch.Tensor, stream=None) -> torch.Tensor:
+    """blobs [E][stride] (ggml NVFP4 expert blobs) -> [E][packed stride] in the plane layout bsx_experts_grouped_packed streams
+    (a load-time step, like Basalt's nvfp4_planes: include/basalt/kernels/nvfp4_planes.hpp:6-20)."""
+    nb = capi.lib().bsx_expert_packed_bytes(C.byref(L))
+    if not nb:
+        raise ValueError("layout not covered by the packed path (all-NVFP4, n_embd % 256 == 0, n_ff % 256 == 0)")
+    out = torch.empty((blobs.shape[0], nb), dtype=torch.uint8, device=blobs.device)
+    for e in range(blobs.shape[0]):
+        check("bsx_expert_pack", capi.lib().bsx_expert_pack(C.byref(L), blobs[e].data_ptr(), out[e].data_ptr(), _stream(stream)))
+    return out
+
+
+def native_expert_grouped_packed(L: ExpertLayout, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups: int, cap_entries: int,
+                                 x, scratch, out, status, stream=None, n_x_rows: int = 0):
+    """native_expert_grouped over packed blobs on the block-scaled FP4 tensor cores (bsx_experts_grouped_packed)."""
+    out_kind = OUT_BF16 if out.dtype == torch.bfloat16 else OUT_F32
+    check("bsx_experts_grouped_packed", capi.lib().bsx_experts_grouped_packed(C.byref(L), _p(grp_ptr), _p(grp_start), _p(n_groups), _p(ent_dst),
+                                                                               _p(ent_tok), cap_groups, cap_entries, _p(x), _x_kind(x), n_x_rows,
+                                                                               _p(scratch), _p(out), out_kind, _p(status), _stream(stream)))
+    return out
+
+
 def experts_prefill(L: ExpertLayout, blob_table, off, src, tiles, n_tiles, x, n_rows: int, dm=None, scratch=None, status=None, stream=None):
     """The prompt path's grouped experts (Basalt: fp4::run_group, include/basalt/prefill/moe_fp4.hpp:104-113) over a dispatch's
     expert-sorted rows; returns (dm [n_rows][n_embd] fp32, status int32[1])."""
@@ -262,13 +284,16 @@ class MoELayer:
 
     def __init__(self, gate_w: torch.Tensor, bias: Optional[torch.Tensor], blobs: torch.Tensor, layout: ExpertLayout,
                  args: RouterArgs, shared_blob: Optional[torch.Tensor] = None, shared_layout: Optional[ExpertLayout] = None,
-                 max_tokens: int = 64):
+                 max_tokens: int = 64, packed: bool = False):
+        """packed: blobs (and the shared blob) are already in the plane layout of pack_experts; the experts then run on the
+        block-scaled FP4 tensor cores (needs a shared expert of the routed experts' layout, or none)."""
         assert blobs.dtype == torch.uint8 and blobs.dim() == 2 and blobs.is_cuda
         self.gate_w, self.bias, self.blobs, self.L, self.args = gate_w, bias, blobs, layout, args
         self.shared_blob, self.shared_L = shared_blob, shared_layout or layout
         dev = blobs.device
         E, stride = blobs.shape
-        assert stride % 16 == 0 and stride >= layout.bytes
+        assert stride % 16 == 0 and (packed or stride >= layout.bytes)
+        self.packed = packed
         self.blob_table = (blobs.data_ptr() + torch.arange(E, dtype=torch.int64) * stride).to(dev)
         self.max_tokens = max_tokens
         n = max_tokens * args.k
@@ -285,7 +310,12 @@ class MoELayer:
         self.dst = torch.zeros(rows, dtype=i32, device=dev)
         self.tok = torch.zeros(rows, dtype=i32, device=dev)
         self.rows = torch.empty((rows, layout.n_embd), dtype=f32, device=dev)
-        self.scratch = torch.empty(native_expert_scratch_bytes(layout, rows), dtype=torch.uint8, device=dev)
+        if packed:
+            assert shared_blob is None or self.fused_shared, "the packed path takes the shared expert as one more group"
+            self.scratch = torch.empty(capi.lib().bsx_experts_packed_scratch_bytes(C.byref(layout), rows), dtype=torch.uint8, device=dev)
+            self.status = torch.zeros(1, dtype=i32, device=dev)
+        else:
+            self.scratch = torch.empty(native_expert_scratch_bytes(layout, rows), dtype=torch.uint8, device=dev)
         self.y = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
         if shared_blob is not None and not self.fused_shared:
             self.s_ptr = torch.tensor([shared_blob.data_ptr()], dtype=torch.int64, device=dev)
@@ -313,16 +343,26 @@ class MoELayer:
         if self.fused_shared:
             check("bsx_moe_plan_shared", lib.bsx_moe_plan_shared(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), self.shared_blob.data_ptr(),
                                                                  _p(self.ptr), _p(self.start), _p(self.n_groups), _p(self.dst), _p(self.tok), st))
-            check("bsx_experts_grouped", lib.bsx_experts_grouped_rows(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
-                                                                      _p(self.dst), _p(self.tok), min(n, a.n_expert) + 1, n + T, _p(x), kind, T,
-                                                                      _p(self.scratch), _p(self.rows), OUT_F32, st))
+            if self.packed:
+                check("bsx_experts_grouped_packed", lib.bsx_experts_grouped_packed(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
+                                                                                   _p(self.dst), _p(self.tok), min(n, a.n_expert) + 1, n + T, _p(x), kind, T,
+                                                                                   _p(self.scratch), _p(self.rows), OUT_F32, _p(self.status), st))
+            else:
+                check("bsx_experts_grouped", lib.bsx_experts_grouped_rows(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
+                                                                          _p(self.dst), _p(self.tok), min(n, a.n_expert) + 1, n + T, _p(x), kind, T,
+                                                                          _p(self.scratch), _p(self.rows), OUT_F32, st))
             shared = self.rows[n:n + T]
         else:
             check("bsx_moe_plan", lib.bsx_moe_plan(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), _p(self.ptr), _p(self.start),
                                                     _p(self.n_groups), _p(self.dst), _p(self.tok), st))
-            check("bsx_experts_grouped", lib.bsx_experts_grouped_rows(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
-                                                                      _p(self.dst), _p(self.tok), min(n, a.n_expert), n, _p(x), kind, T,
-                                                                      _p(self.scratch), _p(self.rows), OUT_F32, st))
+            if self.packed:
+                check("bsx_experts_grouped_packed", lib.bsx_experts_grouped_packed(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
+                                                                                   _p(self.dst), _p(self.tok), min(n, a.n_expert), n, _p(x), kind, T,
+                                                                                   _p(self.scratch), _p(self.rows), OUT_F32, _p(self.status), st))
+            else:
+                check("bsx_experts_grouped", lib.bsx_experts_grouped_rows(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
+                                                                          _p(self.dst), _p(self.tok), min(n, a.n_expert), n, _p(x), kind, T,
+                                                                          _p(self.scratch), _p(self.rows), OUT_F32, st))
             if self.shared_blob is not None:
                 if self._s_T != T:
                     self.s_start.copy_(torch.tensor([0, T, T], dtype=torch.int32))

@@ -214,6 +214,23 @@ BSX_API size_t bsx_gated_mlp_scratch_bytes(const bsx_expert_layout* layout, int6
 BSX_API int32_t bsx_gated_mlp(const bsx_expert_layout* layout, const void* blob, int32_t n_tok, int64_t cap_tok, const void* x,
                               int32_t x_kind, void* scratch, void* out, int32_t out_kind, void* stream);
 
+/* ---- a9 on the block-scaled FP4 tensor cores (tcgen05.mma kind::mxf4nvf4): the weight stream with no decode arithmetic.
+ * bsx_expert_pack rewrites one all-NVFP4 blob (n_embd % 256 == 0, n_ff % 256 == 0), once, into planes - codes row-major,
+ * UE4M3 scales in the order the tensor core's scale copy reads, the fp32 tail - the same bytes in another order
+ * (cf. Basalt's own load-time planes, include/basalt/kernels/nvfp4_planes.hpp:6-20); bsx_expert_packed_bytes gives the size
+ * (0: layout not covered), packed must be 256-byte aligned.  bsx_experts_grouped_packed is bsx_experts_grouped_rows over
+ * packed blobs (grp_ptr[g] = a packed blob): activations enter as four FP4 terms per row (relative error ~1e-4, against
+ * the 2e-3 bar and the ~1e-2 of the reference's int8 rounding), accumulation is fp32 in tensor memory.
+ * scratch: bsx_experts_packed_scratch_bytes(layout, cap_entries), 256-byte aligned.  status: a device int32 the caller
+ * zeroes; bit 0 is set if a bounded wait inside a kernel ran out (the kernel returns instead of hanging). */
+BSX_API size_t bsx_expert_packed_bytes(const bsx_expert_layout* layout);
+BSX_API int32_t bsx_expert_pack(const bsx_expert_layout* layout, const void* blob, void* packed, void* stream);
+BSX_API size_t bsx_experts_packed_scratch_bytes(const bsx_expert_layout* layout, int64_t cap_entries);
+BSX_API int32_t bsx_experts_grouped_packed(const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
+                                           const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
+                                           int64_t cap_entries, const void* x, int32_t x_kind, int32_t n_x_rows, void* scratch, void* out,
+                                           int32_t out_kind, int32_t* status, void* stream);
+
 /* The bench only: which launches bsx_experts_grouped makes (0 all, 1 gate/up + SwiGLU, 2 down), so each stage can be timed
  * alone.  Mirrors native_expert_set_mode's phase (iq_kernels.hpp:113-115).  Process-wide; set it back to 0. */
 BSX_API void bsx_experts_set_phase(int32_t phase);

@@ -1,0 +1,130 @@
+"""GPU parity of the block-scaled FP4 tensor-core expert path (bsx_expert_pack + bsx_experts_grouped_packed): the plane
+layout against a numpy re-ordering of the ggml blob (bit-exact), the grouped experts against the dequantised fp32-accumulated
+oracle expert (bar: relative L2 <= 2e-3; four FP4 activation terms give ~1e-4), ragged passes, every activation kind, and the
+whole layer against the fp16-image kernels."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from basalt_b200 import capi, moe
+from oracle import oracle as O
+from tests.helpers import make_expert_blobs, rel_l2, stack_blobs
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def planes_from_ggml(blob, H, I):
+    """The plane layout restated on the host: codes row-major, scale words [K-step][row / 128][row % 32][(row % 128) / 32]
+    with bit 7 of every scale byte cleared and 0x7F -> 0, then the fp32 tail."""
+    def matrix(off, R, K):
+        rows = blob[off:off + R * (K // 64) * 36].reshape(R, K // 64, 36)
+        codes = np.ascontiguousarray(rows[:, :, 4:]).reshape(R, K // 2)
+        sc = rows[:, :, :4] & 0x7F
+        sc = np.where(sc == 0x7F, 0, sc).astype(np.uint8)
+        words = np.ascontiguousarray(sc).view(np.uint32).reshape(R, K // 64)          # [row][step]
+        sf = np.zeros((K // 64, R // 128, 32, 4), np.uint32)
+        r = np.arange(R)
+        sf[:, r // 128, r % 32, (r % 128) // 32] = words.T
+        return codes.reshape(-1), sf.reshape(-1).view(np.uint8)
+    gu = I * (H // 64) * 36
+    gc, gs = matrix(0, I, H)
+    uc, us = matrix(gu, I, H)
+    dc, ds = matrix(2 * gu, H, I)
+    tail = blob[2 * gu + H * (I // 64) * 36:][:16]
+    return np.concatenate([gc, uc, dc, gs, us, ds, tail])
+
+
+@pytest.mark.parametrize("H,I", [(512, 256), (2048, 512)])
+def test_pack_is_the_ggml_bytes_in_plane_order(lib, cuda, H, I):
+    rng = np.random.default_rng(H)
+    Lo, blobs = make_expert_blobs(rng, 2, O.T_NVFP4, O.T_NVFP4, H, I)
+    blobs[1] = blobs[1].copy()
+    blobs[1][0] = 0x7F                 # a scale byte the decoder reads as zero
+    blobs[1][36 + 1] |= 0x80           # and one with the ignored top bit set
+    L = moe.native_expert_layout(40, 40, H, I)
+    packed = moe.pack_experts(L, dev(stack_blobs(blobs)))
+    torch.cuda.synchronize()
+    for e in range(2):
+        want = planes_from_ggml(np.asarray(blobs[e]), H, I)
+        got = packed[e].cpu().numpy()[:want.size]
+        assert np.array_equal(got, want)
+
+
+def run_packed(L, packed, group_experts, group_tokens, x_dev, n_x_rows=0):
+    stride = packed.shape[1]
+    ptr = torch.tensor([packed.data_ptr() + e * stride for e in group_experts] + [0], dtype=torch.int64).cuda()
+    starts = np.concatenate([[0], np.cumsum([len(t) for t in group_tokens])]).astype(np.int32)
+    n = int(starts[-1])
+    start = dev(np.concatenate([starts, [starts[-1]]]).astype(np.int32))
+    tok = dev(np.concatenate([np.asarray(t, np.int32) for t in group_tokens] + [np.zeros(1, np.int32)])[:max(n, 1)].astype(np.int32))
+    dst = dev(np.arange(max(n, 1), dtype=np.int32))
+    ng = dev(np.array([len(group_experts)], np.int32))
+    out = torch.full((max(n, 1), L.n_embd), float("nan"), dtype=torch.float32, device="cuda")
+    scratch = torch.empty(capi.lib().bsx_experts_packed_scratch_bytes(C.byref(L), max(n, 1)), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    moe.native_expert_grouped_packed(L, ptr, start, ng, dst, tok, len(group_experts), n, x_dev, scratch, out, status, n_x_rows=n_x_rows)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded wait inside the kernel gave up"
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("H,I,xdt,rows_known", [(512, 256, "f32", False), (2048, 512, "bf16", True), (2048, 512, "f32", False), (7168, 2048, "bf16", True)])
+def test_packed_experts_vs_dequantised_reference(lib, cuda, H, I, xdt, rows_known):
+    rng = np.random.default_rng(H + I)
+    E = 3 if H > 4096 else 6
+    Lo, blobs = make_expert_blobs(rng, E, O.T_NVFP4, O.T_NVFP4, H, I)
+    L = moe.native_expert_layout(40, 40, H, I)
+    packed = moe.pack_experts(L, dev(stack_blobs(blobs)))
+    T = 24
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    x[3] *= 1e-3
+    x[5] *= 200.0
+    xd = dev(x)
+    if xdt == "bf16":
+        xd = xd.bfloat16()
+        x = xd.float().cpu().numpy()
+    sizes = ([1, 0, 3, 11, 8, 20] if E == 6 else [2, 9, 1])
+    group_tokens = [rng.integers(0, T, s).tolist() for s in sizes]
+    out = run_packed(L, packed, list(range(E)), group_tokens, xd, n_x_rows=T if rows_known else 0)
+    at, worst = 0, 0.0
+    for e, toks in enumerate(group_tokens):
+        if toks:
+            want = O.expert_forward(Lo, blobs[e], x[toks])
+            got = out[at:at + len(toks)]
+            assert np.isfinite(got).all()
+            worst = max(worst, rel_l2(got, want))
+            for r in range(len(toks)):
+                assert rel_l2(got[r], want[r]) < TOL, (e, r, rel_l2(got[r], want[r]))
+        at += len(toks)
+    print("worst relative L2 over experts:", worst)
+    assert worst < TOL
+
+
+def test_packed_layer_matches_the_fp16_image_layer(lib, cuda):
+    rng = np.random.default_rng(11)
+    E, H, I, K, T = 64, 2048, 512, 10, 64
+    Lo, blobs = make_expert_blobs(rng, E + 1, O.T_NVFP4, O.T_NVFP4, H, I)
+    L = moe.native_expert_layout(40, 40, H, I)
+    bd = dev(stack_blobs(blobs))
+    packed = moe.pack_experts(L, bd)
+    gate = dev((rng.standard_normal((E, H)) * 0.02).astype(np.float32))
+    args = moe.RouterArgs(n_expert=E, n_embd=H, k=K, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
+    x = torch.randn((T, H), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)).bfloat16()
+    plain = moe.MoELayer(gate, None, bd[:E], L, args, shared_blob=bd[E], max_tokens=T)
+    fast = moe.MoELayer(gate, None, packed[:E], L, args, shared_blob=packed[E], max_tokens=T, packed=True)
+    want = plain.forward(x).clone()
+    got = fast.forward(x).clone()
+    got2 = fast.forward(x).clone()
+    torch.cuda.synchronize()
+    assert int(fast.status.item()) == 0
+    rel = float((got - want).norm() / want.norm())
+    print("packed layer vs fp16-image layer, relative L2:", rel)
+    assert rel < 1e-3
+    assert torch.equal(got.view(torch.int32), got2.view(torch.int32)), "not bit-stable from run to run"
