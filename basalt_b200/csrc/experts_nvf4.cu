@@ -19,8 +19,9 @@
 //
 // Kernel: persistent CTAs, one per SM, static round-robin over work units (pass of <= 8 entries of one expert, block of
 // 2 x 128 weight rows: 128 gate rows with their 128 up rows, or 256 down rows).  Warp 0 issues tcgen05.cp (scales ->
-// tensor memory) and the MMAs (M = 128 weight rows, N = 32 columns, K = 64 per instruction); warps 1-2 stream the operands
-// with cp.async into 128-byte-swizzled stages of 256 columns (4-stage ring, continuous across units); warps 3-6 are the
+// tensor memory) and the MMAs (M = 128 weight rows, N = 32 columns, K = 64 per instruction); warp 1 streams the weights (one
+// lane, two 18 KB bulk copies a stage, completion in bytes on the stage's mbarrier), warp 2 the activation images (cp.async)
+// into stages of 256 columns (4-stage ring, continuous across units); warps 3-6 are the
 // epilogue (thread = TMEM lane = weight row: sums each entry's four term columns, applies row and tail scales, SwiGLU for
 // gate/up, stores coalesced).  Two accumulator sets in tensor memory let the epilogue of one unit overlap the stream of
 // the next.  Every mbarrier wait is time-bounded and reports through a status word.
@@ -43,7 +44,8 @@ constexpr int kStagesF = 4;
 constexpr int kATile = 128 * 128;          // one operand tile of a stage: 128 rows x 128 bytes (256 columns of codes)
 constexpr int kBTile = kColsF * 128;
 constexpr int kSFTile = 4 * 512;           // 4 K-steps x (32 lanes x 4 words)
-constexpr int kOffA1 = kATile, kOffB = 2 * kATile, kOffSFA0 = kOffB + kBTile, kOffSFA1 = kOffSFA0 + kSFTile, kOffSFB = kOffSFA1 + kSFTile;
+// a stage: [tile 0 codes | tile 0 scales | tile 1 codes | tile 1 scales | activation codes | activation scales]
+constexpr int kOffSFA0 = kATile, kOffA1 = kATile + kSFTile, kOffSFA1 = kOffA1 + kATile, kOffB = kOffSFA1 + kSFTile, kOffSFB = kOffB + kBTile;
 constexpr int kStageF = kOffSFB + kSFTile;             // 43,008 bytes
 constexpr int kThreadsF = 32 * 7;                      // MMA warp, two loader warps, four epilogue warps
 constexpr size_t kSmemF = 1024 + (size_t) kStagesF * kStageF + 256;
@@ -54,23 +56,32 @@ constexpr uint32_t kIdescF = (1u << 7) | (1u << 10) | ((uint32_t) (kColsF >> 3) 
 
 enum { FMODE_GU = 0, FMODE_DOWN = 1 };
 
+// a pass: up to kEntF consecutive entries [eb, eb + ntok) of one group, with the group's blob - everything a stream kernel
+// needs about it in one 16-byte load
+struct __align__(16) PassRec {
+    unsigned long long blob;
+    int eb, ntok;
+};
+
 size_t al256f(size_t v) { return (v + 255) & ~(size_t) 255; }
 
 // ---------------------------------------------------------------- packed blob geometry
+// A matrix of R rows x K columns becomes (R / 128) x (K / 256) blocks of kBlockF bytes, row tile major: the block of
+// (tile, chunk) holds that tile's 128 rows x 256 columns of codes as the 16 KB image a stage wants in shared memory
+// (128-byte rows, 16-byte pieces XOR-swizzled by row % 8), followed by the rows' scale words of the chunk's four K-steps,
+// each step as 32 lanes x 4 words (word (l, j) = row 32 j + l): what tcgen05.cp reads.  One block = one contiguous 18 KB
+// run of HBM = one bulk copy.  Blob: gate blocks, up blocks, down blocks, the fp32 tail.
+constexpr int kBlockF = 128 * 128 + 4 * 512;     // 18,432
 struct PackedGeom {
-    size_t gate_codes, up_codes, down_codes, gate_sf, up_sf, down_sf, tail, bytes;
+    size_t gate, up, down, tail, bytes;
 };
 __host__ __device__ inline PackedGeom packed_geom(int64_t H, int64_t I) {
     PackedGeom g;
-    const size_t gu_codes = (size_t) I * H / 2, d_codes = (size_t) H * I / 2;
-    const size_t gu_sf = (size_t) I * (H / 64) * 4, d_sf = (size_t) H * (I / 64) * 4;
-    g.gate_codes = 0;
-    g.up_codes = gu_codes;
-    g.down_codes = 2 * gu_codes;
-    g.gate_sf = 2 * gu_codes + d_codes;
-    g.up_sf = g.gate_sf + gu_sf;
-    g.down_sf = g.up_sf + gu_sf;
-    g.tail = g.down_sf + d_sf;
+    const size_t gu = (size_t) (I / 128) * (size_t) (H / 256) * kBlockF, d = (size_t) (H / 128) * (size_t) (I / 256) * kBlockF;
+    g.gate = 0;
+    g.up = gu;
+    g.down = 2 * gu;
+    g.tail = 2 * gu + d;
     g.bytes = g.tail + 16;
     return g;
 }
@@ -88,7 +99,7 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint8_t* __restrict__ i
     if (i >= 2 * n_gu + n_d) return;
     const int mat = i < n_gu ? 0 : (i < 2 * n_gu ? 1 : 2);
     const int64_t j = i - (mat == 0 ? 0 : (mat == 1 ? n_gu : 2 * n_gu));
-    const int64_t K = mat == 2 ? I : H, R = mat == 2 ? H : I;
+    const int64_t K = mat == 2 ? I : H;
     const int64_t nb = K / 64, row = j / nb, blk = j - row * nb;
     const uint8_t* src = in + (mat == 0 ? 0 : (mat == 1 ? (size_t) L.up_off : (size_t) L.down_off)) +
                          (size_t) row * (mat == 0 ? L.gu_row : (mat == 1 ? L.up_row : L.d_row)) + (size_t) blk * 36;
@@ -97,12 +108,18 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint8_t* __restrict__ i
 #pragma unroll
     for (int b = 0; b < 4; ++b)
         if (((sc >> (8 * b)) & 0xFFu) == 0x7Fu) sc &= ~(0xFFu << (8 * b));
-    uint8_t* codes = out + (mat == 0 ? g.gate_codes : (mat == 1 ? g.up_codes : g.down_codes)) + (size_t) row * (K / 2) + (size_t) blk * 32;
+    const int64_t tile = row >> 7, chunk = blk >> 2;
+    const int r = (int) (row & 127), step = (int) (blk & 3);
+    uint8_t* block = out + (mat == 0 ? g.gate : (mat == 1 ? g.up : g.down)) + (size_t) (tile * (K / 256) + chunk) * kBlockF;
+    // the K-step's 32 code bytes are 16-byte pieces 2 step and 2 step + 1 of the row's 128 bytes
 #pragma unroll
-    for (int k = 0; k < 8; ++k) reinterpret_cast<uint32_t*>(codes)[k] = w[1 + k];
-    // scale word of (row, K-step blk): [blk][row / 128][row % 32][(row % 128) / 32]
-    uint32_t* sf = reinterpret_cast<uint32_t*>(out + (mat == 0 ? g.gate_sf : (mat == 1 ? g.up_sf : g.down_sf)));
-    sf[((size_t) blk * (R / 128) + row / 128) * 128 + (row & 31) * 4 + ((row & 127) >> 5)] = sc;
+    for (int h = 0; h < 2; ++h) {
+        const int piece = 2 * step + h;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(block + (r >> 3) * 1024 + (r & 7) * 128 + ((piece ^ (r & 7)) << 4));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) dst[k] = w[1 + 4 * h + k];
+    }
+    reinterpret_cast<uint32_t*>(block + 128 * 128 + step * 512)[(r & 31) * 4 + (r >> 5)] = sc;
 }
 
 // ---------------------------------------------------------------- FP4 activation images
@@ -138,20 +155,22 @@ __device__ __forceinline__ float e2m1_value(uint32_t c) {
     return (c & 8u) ? -m : m;
 }
 
-// One warp per activation row: the row times a power of two (largest magnitude into [2^7, 2^8), so block scales sit well
-// inside UE4M3's range) as kTermsF FP4 terms.  Term t of a 16-value sub-block: scale = the smallest UE4M3 value s with
-// 6 s >= the largest residual, codes = rn(residual / s), residual -= code value x s.  Layout: codes [row][term][K / 2]
-// bytes with ggml's nibble order (byte b of a sub-block = values b and b + 8), scales [row][term][K / 16] bytes, inv[row].
-// FROM_H = false: rows of x (kind x_kind) - row i of x when the caller gave the number of x rows, else the row of entry
-// i; true: row e of the SwiGLU output h.  The last block lists the passes (up to kEntF consecutive entries of one group).
-template <bool FROM_H>
+// TPR threads per activation row (32, 128 or 256: a thread per 16-value sub-block where the row allows): the row times a
+// power of two (largest magnitude into [2^7, 2^8), so block scales sit well inside UE4M3's range) as kTermsF FP4 terms.
+// Term t of a sub-block: scale = the smallest UE4M3 value s with 6 s >= the largest residual, codes = rn(residual / s),
+// residual -= code value x s.  Layout: codes [row][term][K / 2] bytes with ggml's nibble order (byte b of a sub-block =
+// values b and b + 8), scales [row][term][K / 16] bytes, inv[row].  FROM_H = false: rows of x (kind x_kind) - row i of x
+// when the caller gave the number of x rows, else the row of entry i; true: row e of the SwiGLU output h.  The last block
+// lists the passes (up to kEntF consecutive entries of one group).
+template <bool FROM_H, int TPR>
 __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __restrict__ codes, uint8_t* __restrict__ sfs, float* __restrict__ inv,
-                                                        int2* __restrict__ items, int* __restrict__ n_items) {
+                                                        PassRec* __restrict__ items, int* __restrict__ n_items) {
     const int ng = min(*a.n_groups, (int) a.cap_groups);
     const int total = min(a.grp_start[ng], (int) a.cap_entries);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ int sh[8];
+    __shared__ float shf[8];
     if (blockIdx.x == gridDim.x - 1) {
-        __shared__ int sh[8];
         __shared__ int s_base;
         if (threadIdx.x == 0) s_base = 0;
         __syncthreads();
@@ -170,7 +189,13 @@ __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __
             __syncthreads();
             int before = s_base;
             for (int w = 0; w < warp; ++w) before += sh[w];
-            for (int p = 0; p < np; ++p) items[before + x - np + p] = make_int2(g, s0 + p * kEntF);
+            for (int p = 0; p < np; ++p) {
+                PassRec r;
+                r.blob = a.grp_ptr[g];
+                r.eb = s0 + p * kEntF;
+                r.ntok = min(kEntF, cnt - p * kEntF);
+                items[before + x - np + p] = r;
+            }
             __syncthreads();
             if (threadIdx.x == 255) s_base = before + x;
             __syncthreads();
@@ -178,22 +203,35 @@ __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __
         if (threadIdx.x == 0) n_items[0] = s_base;
         return;
     }
-    const int i = blockIdx.x * 8 + warp;   // image row
+    constexpr int kRowsPerBlock = 256 / TPR;
+    const int i = blockIdx.x * kRowsPerBlock + (int) threadIdx.x / TPR;   // image row
+    const int tr = (int) threadIdx.x % TPR;
     const int n_img = FROM_H ? total : (a.n_x_rows > 0 ? a.n_x_rows : total);
-    if (i >= n_img) return;
+    const bool live = i < n_img;
     const int64_t K = FROM_H ? a.L.n_ff : a.L.n_embd;
-    const int64_t row = FROM_H ? (int64_t) i : (a.n_x_rows > 0 ? (int64_t) i : (int64_t) a.ent_tok[i]);
+    const int64_t row = !live ? 0 : (FROM_H ? (int64_t) i : (a.n_x_rows > 0 ? (int64_t) i : (int64_t) a.ent_tok[i]));
     const void* src = FROM_H ? (const void*) a.h : a.x;
     const int kind = FROM_H ? BSX_X_F32 : a.x_kind;
     const int n_sb = (int) (K >> 4);
     float amax = 0.f;
-    for (int sb = lane; sb < n_sb; sb += 32) {
-        float v[16];
-        load16(src, kind, row, K, sb, v);
+    if (live) {
+        for (int sb = tr; sb < n_sb; sb += TPR) {
+            float v[16];
+            load16(src, kind, row, K, sb, v);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+            for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        }
     }
     amax = warp_max_xor(amax);
+    if (TPR > 32) {
+        if (lane == 0) shf[warp] = amax;
+        __syncthreads();
+        const int w0 = (warp / (TPR / 32)) * (TPR / 32);
+        amax = shf[w0];
+#pragma unroll
+        for (int w = 1; w < TPR / 32; ++w) amax = fmaxf(amax, shf[w0 + w]);
+    }
+    if (!live) return;
     int ex = 0;
     float s = 1.f, iv = 1.f;
     if (amax > 0.f && amax <= 3.0e38f) {
@@ -202,8 +240,8 @@ __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __
         s = ldexpf(1.f, ex);
         iv = ldexpf(1.f, -ex);
     }
-    if (lane == 0) inv[i] = iv;
-    for (int sb = lane; sb < n_sb; sb += 32) {
+    if (tr == 0) inv[i] = iv;
+    for (int sb = tr; sb < n_sb; sb += TPR) {
         float v[16];
         load16(src, kind, row, K, sb, v);
 #pragma unroll
@@ -217,9 +255,10 @@ __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __
             const float sv = ue4m3_value(sb8);
             uint32_t w0 = 0u, w1 = 0u;
             if (sv > 0.f) {
+                const float rs = 1.f / sv;          // 6 sv >= every |v|, so |v rs| <= 6 up to rounding, which the conversion saturates
 #pragma unroll
                 for (int b = 0; b < 8; ++b) {
-                    const uint32_t c = e2m1x2(v[b] / sv, v[b + 8] / sv);
+                    const uint32_t c = e2m1x2(v[b] * rs, v[b + 8] * rs);
                     v[b] -= e2m1_value(c & 15u) * sv;
                     v[b + 8] -= e2m1_value(c >> 4) * sv;
                     if (b < 4) w0 |= c << (8 * b);
@@ -233,13 +272,21 @@ __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __
     }
 }
 
+template <bool FROM_H>
+void launch_prep(const ExpertArgs& a, int64_t rows, int64_t K, uint8_t* codes, uint8_t* sfs, float* inv, PassRec* items, int* n_items, cudaStream_t st) {
+    const int64_t n_sb = K / 16;
+    if (n_sb <= 32) prep_fp4_kernel<FROM_H, 32><<<(unsigned) ((rows + 7) / 8 + 1), 256, 0, st>>>(a, codes, sfs, inv, items, n_items);
+    else if (n_sb <= 128) prep_fp4_kernel<FROM_H, 128><<<(unsigned) ((rows + 1) / 2 + 1), 256, 0, st>>>(a, codes, sfs, inv, items, n_items);
+    else prep_fp4_kernel<FROM_H, 256><<<(unsigned) (rows + 1), 256, 0, st>>>(a, codes, sfs, inv, items, n_items);
+}
+
 // ---------------------------------------------------------------- the stream kernel
 struct StreamArgs {
     ExpertArgs e;
     const uint8_t* codes;     // activation images
     const uint8_t* sfs;
     const float* inv;
-    const int2* items;
+    const PassRec* items;
     const int* n_items;
     int32_t* status;
 };
@@ -263,14 +310,18 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
     const int64_t K = MODE == FMODE_GU ? a.L.n_embd : a.L.n_ff;
     const int64_t R = MODE == FMODE_GU ? a.L.n_ff : a.L.n_embd;       // rows of each weight matrix
     const int n_chunk = (int) (K >> 8);                                 // stages (256 columns) per unit
-    constexpr int kRowsPerUnit = MODE == FMODE_GU ? 128 : 256;
-    const int n_rb = (int) ((R + kRowsPerUnit - 1) / kRowsPerUnit);
-    const int n_units = sa.n_items[0] * n_rb;
+    constexpr int kRowsPerBlock = MODE == FMODE_GU ? 128 : 256;         // weight rows of the two tiles of one accumulator set
+    const int n_rb = (int) ((R + kRowsPerBlock - 1) / kRowsPerBlock);
+    // a unit = one pass x n_sub consecutive row blocks, sized to at least 8 stages so that the per-unit bookkeeping (the
+    // pass record, the entries' rows and scales) is amortised and its loads hide behind the stream
+    const int n_sub = max(1, min(n_rb, (8 + n_chunk - 1) / n_chunk));
+    const int n_upp = (n_rb + n_sub - 1) / n_sub;                        // units per pass
+    const int n_units = sa.n_items[0] * n_upp;
     const PackedGeom geo = packed_geom(a.L.n_embd, a.L.n_ff);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStagesF; ++s) {
-            mbar_init(&full[s], 64);
+            mbar_init(&full[s], 33);     // the weight loader's expect_tx arrival + the 32 lanes of the activation loader
             mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -290,16 +341,13 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
 
-    // a unit: pass = unit / n_rb (group, first entry), row block = unit % n_rb.  Tile 0 / tile 1 of the unit: the 128 gate
-    // rows r0.. and the 128 up rows r0.. (gate/up), or down rows r0.. and r0 + 128.. (down).
-    struct Unit { const uint8_t* blob; int eb, ntok, r0; };
-    auto get_unit = [&](int unit, Unit& u) {
-        const int pass = unit / n_rb;
-        const int2 it = sa.items[pass];
-        u.blob = reinterpret_cast<const uint8_t*>(a.grp_ptr[it.x]);
-        u.eb = it.y;
-        u.ntok = min(kEntF, min(a.grp_start[it.x + 1], (int) a.cap_entries) - it.y);
-        u.r0 = (unit - pass * n_rb) * kRowsPerUnit;
+    // unit -> its pass record and its row blocks [rb0, rb1).  Tile 0 / tile 1 of a row block: the 128 gate rows r0.. and the
+    // 128 up rows r0.. (gate/up), or down rows r0.. and r0 + 128.. (down).
+    auto unit_blocks = [&](int unit, int& rb0, int& rb1) {
+        const int pass = unit / n_upp;
+        rb0 = (unit - pass * n_upp) * n_sub;
+        rb1 = min(n_rb, rb0 + n_sub);
+        return pass;
     };
 
     if (warp == 0) {
@@ -307,129 +355,137 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
         if (lane == 0) {
             uint32_t kc = 0, ti = 0;
             for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
-                const uint32_t acc = ti & 1u;
-                ok = mbar_wait(&acc_empty[acc], ((ti >> 1) & 1u) ^ 1u);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t d0 = tmem + acc * 64, d1 = d0 + 32;
-                for (int c = 0; c < n_chunk; ++c, ++kc) {
-                    const uint32_t s = kc % kStagesF;
-                    ok = mbar_wait(&full[s], (kc / kStagesF) & 1u);
+                int rb0, rb1;
+                unit_blocks(unit, rb0, rb1);
+                for (int rb = rb0; rb < rb1 && ok; ++rb) {
+                    const uint32_t acc = ti & 1u;
+                    ok = mbar_wait(&acc_empty[acc], ((ti >> 1) & 1u) ^ 1u);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const uint32_t st = smem_u32(smem + s * kStageF);
-                    const uint32_t tsf = tmem + kTmemSF + s * 48;
+                    const uint32_t d0 = tmem + acc * 64, d1 = d0 + 32;
+                    for (int c = 0; c < n_chunk; ++c, ++kc) {
+                        const uint32_t s = kc % kStagesF;
+                        ok = mbar_wait(&full[s], (kc / kStagesF) & 1u);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                        const uint32_t st = smem_u32(smem + s * kStageF);
+                        const uint32_t tsf = tmem + kTmemSF + s * 48;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsf + 4 * k), "l"(sf_desc(st + kOffSFA0 + k * 512)) : "memory");
-                        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsf + 16 + 4 * k), "l"(sf_desc(st + kOffSFA1 + k * 512)) : "memory");
-                        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsf + 32 + 4 * k), "l"(sf_desc(st + kOffSFB + k * 512)) : "memory");
-                        const uint64_t bd = smem_desc_sw128(st + kOffB + k * 32);
-                        const uint32_t accum = (c | k) ? 1u : 0u;
-                        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
-                                     "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::"r"(d0),
-                                     "l"(smem_desc_sw128(st + k * 32)), "l"(bd), "r"(kIdescF), "r"(tsf + 4 * k), "r"(tsf + 32 + 4 * k), "r"(accum)
-                                     : "memory");
-                        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
-                                     "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::"r"(d1),
-                                     "l"(smem_desc_sw128(st + kOffA1 + k * 32)), "l"(bd), "r"(kIdescF), "r"(tsf + 16 + 4 * k), "r"(tsf + 32 + 4 * k), "r"(accum)
-                                     : "memory");
+                        for (int k = 0; k < 4; ++k) {
+                            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsf + 4 * k), "l"(sf_desc(st + kOffSFA0 + k * 512)) : "memory");
+                            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsf + 16 + 4 * k), "l"(sf_desc(st + kOffSFA1 + k * 512)) : "memory");
+                            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsf + 32 + 4 * k), "l"(sf_desc(st + kOffSFB + k * 512)) : "memory");
+                            const uint64_t bd = smem_desc_sw128(st + kOffB + k * 32);
+                            const uint32_t accum = (c | k) ? 1u : 0u;
+                            asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+                                         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::"r"(d0),
+                                         "l"(smem_desc_sw128(st + k * 32)), "l"(bd), "r"(kIdescF), "r"(tsf + 4 * k), "r"(tsf + 32 + 4 * k), "r"(accum)
+                                         : "memory");
+                            asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+                                         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::"r"(d1),
+                                         "l"(smem_desc_sw128(st + kOffA1 + k * 32)), "l"(bd), "r"(kIdescF), "r"(tsf + 16 + 4 * k), "r"(tsf + 32 + 4 * k), "r"(accum)
+                                         : "memory");
+                        }
+                        umma_commit(&empty[s]);
                     }
-                    umma_commit(&empty[s]);
+                    if (!ok) break;
+                    umma_commit(&acc_full[acc]);
+                    ++ti;
                 }
-                if (!ok) break;
-                umma_commit(&acc_full[acc]);
-                ++ti;
             }
             if (!ok) atomicOr(sa.status, 1);
         }
-    } else if (warp <= 2) {
-        // ---- loaders.  Warp 1: tile 0, its scales, the activation codes; warp 2: tile 1, its scales, the activation scales.
-        // A lane copies 16-byte chunk lane % 8 of rows lane / 8 + 4 i (eight lanes = one 128-byte row of a stage); it runs
-        // up to two stages ahead of its own landed copies and arrives on a stage once its copies there are visible.
-        const int lw = warp - 1, c8 = lane & 7, r4 = lane >> 3;
+    } else if (warp == 1) {
+        // ---- weight loader: one lane, two bulk copies a stage (each a whole block of the packed blob: 16 KB of codes already
+        // in the stage's swizzled order + 2 KB of scales), completion counted in bytes on the stage's mbarrier.  The next
+        // unit's pass record is requested while this unit streams.
+        if (lane == 0) {
+            uint32_t issued = 0;
+            PassRec nxt;
+            nxt.blob = 0ull; nxt.eb = 0; nxt.ntok = 0;
+            if ((int) blockIdx.x < n_units) nxt = sa.items[blockIdx.x / n_upp];
+            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+                const PassRec u = nxt;
+                if (unit + (int) gridDim.x < n_units) nxt = sa.items[(unit + gridDim.x) / n_upp];
+                int rb0, rb1;
+                unit_blocks(unit, rb0, rb1);
+                const uint8_t* blob = reinterpret_cast<const uint8_t*>(u.blob);
+                for (int rb = rb0; rb < rb1 && ok; ++rb) {
+                    const uint8_t* b0 = MODE == FMODE_GU ? blob + geo.gate + (size_t) rb * n_chunk * kBlockF : blob + geo.down + (size_t) (2 * rb) * n_chunk * kBlockF;
+                    const uint8_t* b1 = MODE == FMODE_GU ? blob + geo.up + (size_t) rb * n_chunk * kBlockF : b0 + (size_t) n_chunk * kBlockF;
+                    for (int c = 0; c < n_chunk; ++c, ++issued) {
+                        const uint32_t s = issued % kStagesF;
+                        ok = mbar_wait(&empty[s], ((issued / kStagesF) & 1u) ^ 1u);
+                        if (!ok) break;
+                        const uint32_t st = smem_u32(smem + s * kStageF), bar = smem_u32(&full[s]);
+                        asm volatile("{\n.reg .b64 t;\nmbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1;\n}\n" ::"r"(bar), "r"(2u * kBlockF) : "memory");
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(st),
+                                     "l"(b0 + (size_t) c * kBlockF), "r"((uint32_t) kBlockF), "r"(bar)
+                                     : "memory");
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(st + (uint32_t) kOffA1),
+                                     "l"(b1 + (size_t) c * kBlockF), "r"((uint32_t) kBlockF), "r"(bar)
+                                     : "memory");
+                    }
+                }
+            }
+            if (!ok) atomicOr(sa.status, 1);
+        }
+    } else if (warp == 2) {
+        // ---- activation loader: the pass's FP4 images, 256 columns a stage.  Codes: column n = 4 j + t is term t of entry j;
+        // lane l copies 16-byte piece l % 8 of rows l / 8 + 4 i (row 4 i + r4 -> entry i, term r4).  Scales: lane = column n,
+        // its scale word of K-step k goes to word (n, 0) of that step's 512-byte block.  A lane runs up to two stages ahead of
+        // its own landed copies and arrives on a stage once its copies there are visible to the tensor core.
+        const int c8 = lane & 7, r4 = lane >> 3;
         uint32_t dsto[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r7 = 4 * h + r4;
-            dsto[h] = (uint32_t) (r7 * 128 + ((c8 ^ r7) << 4));
+            dsto[h] = (uint32_t) (kOffB + r7 * 128 + ((c8 ^ r7) << 4));
         }
         uint32_t issued = 0, arrived = 0;
+        PassRec nxt;
+        nxt.blob = 0ull; nxt.eb = 0; nxt.ntok = 0;
+        if ((int) blockIdx.x < n_units) nxt = sa.items[blockIdx.x / n_upp];
         for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
-            Unit u;
-            get_unit(unit, u);
-            // weight tile rows (clamped to the matrix) and this warp's planes
-            const uint8_t* wcodes;
-            const uint8_t* wsf;
-            int row_first;
-            if (MODE == FMODE_GU) {
-                wcodes = u.blob + (lw == 0 ? geo.gate_codes : geo.up_codes);
-                wsf = u.blob + (lw == 0 ? geo.gate_sf : geo.up_sf);
-                row_first = u.r0;
-            } else {
-                wcodes = u.blob + geo.down_codes;
-                wsf = u.blob + geo.down_sf;
-                row_first = min(u.r0 + 128 * lw, (int) R - 128);
-            }
-            const uint8_t* wrow0 = wcodes + (size_t) (row_first + r4) * (size_t) (K >> 1) + c8 * 16;
-            const size_t wpitch4 = (size_t) 4 * (size_t) (K >> 1);
-            const uint8_t* sfrow = wsf + (size_t) (row_first >> 7) * 512 + lane * 16;
-            const size_t sf_step = (size_t) (R >> 7) * 512;
-            // the pass's image rows: entry j -> image row (the entry itself, or its token when images are per x row)
-            int ir[kEntF];
+            const PassRec u = nxt;
+            if (unit + (int) gridDim.x < n_units) nxt = sa.items[(unit + gridDim.x) / n_upp];
+            int rb0, rb1;
+            unit_blocks(unit, rb0, rb1);
+            const uint8_t* crow[kEntF];
 #pragma unroll
             for (int j = 0; j < kEntF; ++j) {
                 const int e = u.eb + (j < u.ntok ? j : 0);
-                ir[j] = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
+                const int ir = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
+                crow[j] = sa.codes + ((size_t) ir * kTermsF + r4) * (size_t) (K >> 1) + c8 * 16;
             }
-            int ir_lane;    // the image row behind column n = lane (entry lane / 4)
+            const uint8_t* srow;
             {
                 const int e = u.eb + ((lane >> 2) < u.ntok ? (lane >> 2) : 0);
-                ir_lane = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
+                const int ir = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
+                srow = sa.sfs + ((size_t) ir * kTermsF + (lane & 3)) * (size_t) (K >> 4);
             }
-            for (int c = 0; c < n_chunk; ++c) {
-                const uint32_t s = issued % kStagesF;
-                ok = mbar_wait(&empty[s], ((issued / kStagesF) & 1u) ^ 1u);
-                if (!ok) break;
-                const uint32_t st = smem_u32(smem + s * kStageF);
-                // weight codes: 128 rows x 128 bytes
-                {
-                    const uint8_t* g = wrow0 + (size_t) c * 128;
-                    const uint32_t dst = st + (lw == 0 ? 0u : (uint32_t) kOffA1);
+            for (int rb = rb0; rb < rb1 && ok; ++rb) {
+                for (int c = 0; c < n_chunk; ++c) {
+                    const uint32_t s = issued % kStagesF;
+                    ok = mbar_wait(&empty[s], ((issued / kStagesF) & 1u) ^ 1u);
+                    if (!ok) break;
+                    const uint32_t st = smem_u32(smem + s * kStageF);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t) ((i >> 1) * 1024) + dsto[i & 1]),
-                                     "l"(g + (size_t) i * wpitch4)
+                    for (int i = 0; i < kEntF; ++i)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(st + (uint32_t) ((i >> 1) * 1024) + dsto[i & 1]), "l"(crow[i] + (size_t) c * 128)
                                      : "memory");
-                }
-                // weight scales: 4 K-steps x 512 bytes, one 16-byte piece per lane and step
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(st + (uint32_t) (lw == 0 ? kOffSFA0 : kOffSFA1) + k * 512 + lane * 16),
-                                 "l"(sfrow + (size_t) (4 * c + k) * sf_step)
-                                 : "memory");
-                if (lw == 0) {
-                    // activation codes: column n = 4 j + t is term t of entry j; rows 4 i + r4 -> entry i, term r4
-#pragma unroll
-                    for (int i = 0; i < kEntF; ++i) {
-                        const uint8_t* g = sa.codes + ((size_t) ir[i] * kTermsF + r4) * (size_t) (K >> 1) + (size_t) c * 128 + c8 * 16;
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(st + (uint32_t) kOffB + (uint32_t) ((i >> 1) * 1024) + dsto[i & 1]), "l"(g)
-                                     : "memory");
-                    }
-                } else {
-                    // activation scales: column n = lane; its scale word of K-step k goes to word (n, 0) of that step's block
-                    const uint8_t* g = sa.sfs + ((size_t) ir_lane * kTermsF + (lane & 3)) * (size_t) (K >> 4) + (size_t) c * 16;
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(st + (uint32_t) kOffSFB + k * 512 + lane * 16), "l"(g + 4 * k) : "memory");
-                }
-                asm volatile("cp.async.commit_group;\n" ::: "memory");
-                ++issued;
-                if (issued - arrived > 2) {
-                    asm volatile("cp.async.wait_group 2;\n" ::: "memory");
-                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                    mbar_arrive(&full[arrived % kStagesF]);
-                    ++arrived;
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(st + (uint32_t) kOffSFB + k * 512 + lane * 16), "l"(srow + (size_t) c * 16 + 4 * k)
+                                     : "memory");
+                    asm volatile("cp.async.commit_group;\n" ::: "memory");
+                    ++issued;
+                    if (issued - arrived > 2) {
+                        asm volatile("cp.async.wait_group 2;\n" ::: "memory");
+                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                        mbar_arrive(&full[arrived % kStagesF]);
+                        ++arrived;
+                    }
                 }
             }
         }
@@ -439,41 +495,55 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
         if (!ok) atomicOr(sa.status, 1);
     } else {
         // ---- epilogue: thread = TMEM lane = weight row of both tiles.  A warp may only read lanes 32 (warp % 4) .. + 31.
+        // The unit's entries (rows, scales, destinations) are fetched before the wait for its first accumulator, so those
+        // loads ride under the stream; the next unit's pass record is requested one unit ahead.
         const int q = warp & 3;
         const int rl = q * 32 + lane;
         const uint32_t lane_base = (uint32_t) (q * 32) << 16;
         uint32_t ti = 0;
-        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
-            Unit u;
-            get_unit(unit, u);
-            const uint32_t acc = ti & 1u;
-            ok = __all_sync(kFull, mbar_wait(&acc_full[acc], (ti >> 1) & 1u));
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            uint32_t d0[32], d1[32];
-            tmem_ld32(tmem + lane_base + acc * 64, d0);
-            tmem_ld32(tmem + lane_base + acc * 64 + 32, d1);
-            // the accumulators are in registers: the MMA warp may start the next unit on this set
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            mbar_arrive(&acc_empty[acc]);
-            ++ti;
-            const float* tail = reinterpret_cast<const float*>(u.blob + geo.tail);
+        PassRec nxt;
+        nxt.blob = 0ull; nxt.eb = 0; nxt.ntok = 0;
+        if ((int) blockIdx.x < n_units) nxt = sa.items[blockIdx.x / n_upp];
+        for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+            const PassRec u = nxt;
+            if (unit + (int) gridDim.x < n_units) nxt = sa.items[(unit + gridDim.x) / n_upp];
+            int rb0, rb1;
+            unit_blocks(unit, rb0, rb1);
+            const float* tail = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(u.blob) + geo.tail);
             const float sg = tail[0], su = tail[1], sd = tail[2];
+            float f[kEntF];
+            int64_t orow[kEntF];
 #pragma unroll
             for (int j = 0; j < kEntF; ++j) {
-                if (j < u.ntok) {
-                    const int e = u.eb + j;
-                    const int irow = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
-                    const float f = sa.inv[irow];
-                    const float v0 = ((__uint_as_float(d0[4 * j]) + __uint_as_float(d0[4 * j + 1])) + __uint_as_float(d0[4 * j + 2])) + __uint_as_float(d0[4 * j + 3]);
-                    const float v1 = ((__uint_as_float(d1[4 * j]) + __uint_as_float(d1[4 * j + 1])) + __uint_as_float(d1[4 * j + 2])) + __uint_as_float(d1[4 * j + 3]);
-                    if (MODE == FMODE_GU) {
-                        if (u.r0 + rl < R) a.h[(int64_t) e * a.L.n_ff + u.r0 + rl] = swiglu(v0 * f * sg, v1 * f * su, a.L);
-                    } else {
-                        const int64_t o = (int64_t) a.ent_dst[e] * a.L.n_embd;
-                        const int rA = u.r0 + rl, rB = min(u.r0 + 128, (int) R - 128) + rl;
-                        if (rA < R) store_out(a.out, a.out_kind, o + rA, v0 * f * sd);
-                        if (u.r0 + 128 < R) store_out(a.out, a.out_kind, o + rB, v1 * f * sd);
+                const int e = u.eb + (j < u.ntok ? j : 0);
+                const int ir = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
+                f[j] = sa.inv[ir];
+                orow[j] = MODE == FMODE_GU ? (int64_t) e * a.L.n_ff : (int64_t) a.ent_dst[e] * a.L.n_embd;
+            }
+            for (int rb = rb0; rb < rb1; ++rb) {
+                const int r0 = rb * kRowsPerBlock;
+                const uint32_t acc = ti & 1u;
+                ok = __all_sync(kFull, mbar_wait(&acc_full[acc], (ti >> 1) & 1u));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                uint32_t d0[32], d1[32];
+                tmem_ld32(tmem + lane_base + acc * 64, d0);
+                tmem_ld32(tmem + lane_base + acc * 64 + 32, d1);
+                // the accumulators are in registers: the MMA warp may start the next row block on this set
+                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+                mbar_arrive(&acc_empty[acc]);
+                ++ti;
+#pragma unroll
+                for (int j = 0; j < kEntF; ++j) {
+                    if (j < u.ntok) {
+                        const float v0 = ((__uint_as_float(d0[4 * j]) + __uint_as_float(d0[4 * j + 1])) + __uint_as_float(d0[4 * j + 2])) + __uint_as_float(d0[4 * j + 3]);
+                        const float v1 = ((__uint_as_float(d1[4 * j]) + __uint_as_float(d1[4 * j + 1])) + __uint_as_float(d1[4 * j + 2])) + __uint_as_float(d1[4 * j + 3]);
+                        if (MODE == FMODE_GU) {
+                            a.h[orow[j] + r0 + rl] = swiglu(v0 * f[j] * sg, v1 * f[j] * su, a.L);
+                        } else {
+                            store_out(a.out, a.out_kind, orow[j] + r0 + rl, v0 * f[j] * sd);
+                            store_out(a.out, a.out_kind, orow[j] + r0 + 128 + rl, v1 * f[j] * sd);
+                        }
                     }
                 }
             }
@@ -508,7 +578,7 @@ int32_t launch_stream(const StreamArgs& sa, cudaStream_t st) {
 // scratch beyond the SwiGLU buffer: x images (codes, scales), h images, inverse row scales, the pass list
 size_t experts_packed_scratch_bytes(int64_t cap, int64_t H, int64_t I) {
     return al256f((size_t) cap * kTermsF * H / 2) + al256f((size_t) cap * kTermsF * H / 16) + al256f((size_t) cap * kTermsF * I / 2) +
-           al256f((size_t) cap * kTermsF * I / 16) + 2 * al256f((size_t) cap * 4) + al256f((size_t) (cap + 1) * 8 + 16);
+           al256f((size_t) cap * kTermsF * I / 16) + 2 * al256f((size_t) cap * 4) + al256f((size_t) (cap + 1) * 16 + 16);
 }
 
 int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st) {
@@ -530,10 +600,9 @@ int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_
     float* hinv = reinterpret_cast<float*>(p);
     p += al256f((size_t) cap * 4);
     int* n_items = reinterpret_cast<int*>(p);
-    int2* items = reinterpret_cast<int2*>(n_items + 4);
+    PassRec* items = reinterpret_cast<PassRec*>(n_items + 4);
     const int phase = experts_phase();
     const int64_t x_rows = a.n_x_rows > 0 ? a.n_x_rows : cap;
-    const unsigned nbx = (unsigned) ((x_rows + 7) / 8 + 1), nbh = (unsigned) ((cap + 7) / 8 + 1);
     StreamArgs sa;
     sa.e = a;
     sa.items = items;
@@ -541,14 +610,14 @@ int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_
     sa.status = status;
     int32_t rc = BSX_OK;
     if (phase != 2) {
-        prep_fp4_kernel<false><<<nbx, 256, 0, st>>>(a, xcodes, xsf, xinv, items, n_items);
+        launch_prep<false>(a, x_rows, H, xcodes, xsf, xinv, items, n_items, st);
         sa.codes = xcodes;
         sa.sfs = xsf;
         sa.inv = xinv;
         rc = launch_stream<FMODE_GU>(sa, st);
     }
     if (rc != BSX_OK || phase == 1) return rc;
-    prep_fp4_kernel<true><<<nbh, 256, 0, st>>>(a, hcodes, hsf, hinv, items, n_items);
+    launch_prep<true>(a, cap, I, hcodes, hsf, hinv, items, n_items, st);
     sa.codes = hcodes;
     sa.sfs = hsf;
     sa.inv = hinv;

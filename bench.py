@@ -203,6 +203,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--copies", type=int, default=LAYER_COPIES, help="layer copies the steps cycle through (1 for a small profiler capture)")
+    ap.add_argument("--experts", default="packed", choices=["packed", "fp16"],
+                    help="decode expert kernels: packed = blobs repacked at load into planes, block-scaled FP4 tensor cores (tcgen05 kind::mxf4nvf4); "
+                         "fp16 = ggml blobs in place, fp16 activation images, mma.sync")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: 64 tokens a step (the default line); prefill: --tokens rows a step, Zipf(1.1) expert popularity, tcgen05 grouped experts")
     ap.add_argument("--tokens", type=int, default=4096, help="rows per step of the prefill workload, per GPU (4096 or 16384 in the reference's configs)")
@@ -238,9 +241,14 @@ def main():
     assert L.bytes == blob_bytes
     rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
     layers = []
+    use_packed = args.experts == "packed"
+    if use_packed:
+        blobs_ggml = blobs
+        blobs = moe.pack_experts(L, blobs_ggml)       # the load-time step: the same bytes in plane order
+        torch.cuda.synchronize()
     for c in range(args.copies):
         b = blobs if c == 0 else blobs.clone()
-        layers.append(moe.MoELayer(gate if c == 0 else gate.clone(), None, b[:E], L, rargs, shared_blob=b[E], max_tokens=T))
+        layers.append(moe.MoELayer(gate if c == 0 else gate.clone(), None, b[:E], L, rargs, shared_blob=b[E], max_tokens=T, packed=use_packed))
     n_batches = 8
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     xs = [torch.randn((T, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
@@ -301,12 +309,15 @@ def main():
     line = {
         "metric": "MoE-layer tokens/s (decode)", "value": T * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "fp16 x NVFP4 tensor-core products, fp32 accumulation", "data": "synthetic",
+        "vs_baseline": None,
+        "dtype": ("NVFP4 weights x 4-term FP4 activations on tcgen05 kind::mxf4nvf4 (block-scaled), fp32 accumulation" if use_packed
+                  else "fp16 x NVFP4 tensor-core products (mma.sync), fp32 accumulation"), "data": "synthetic",
         "config": dict(CFG, l2_policy=f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB) and each step touches ~650 MB: larger than L2",
-                       parallelism="single GPU" if world == 1 else f"ep{world}"),
+                       parallelism="single GPU" if world == 1 else f"ep{world}",
+                       expert_kernels="packed planes + tcgen05 block-scaled FP4" if use_packed else "ggml blobs in place + fp16 images + mma.sync"),
         "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
         "gpu_launches": 9 * args.steps,   # logits, select, plan, 2 x image prep, gate/up, down, combine (+0: the shared expert rides in the grouped call)
-        "roofline": {"bound": "hbm", "kernel": "nvfp4_mma_kernel<gate/up> (routed + shared experts; stage time includes the activation-image kernel)", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": ("nvf4_stream_kernel<gate/up>" if use_packed else "nvfp4_mma_kernel<gate/up>") + " (routed + shared experts; stage time includes the activation-image kernel)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
                      "algorithmic_bytes_per_launch": gu_bytes, "kernel_ms": gu_ms, "frac_of_nominal_8TBs": achieved / 8000.0},
         "stage_ms": stage_ms,
@@ -314,7 +325,7 @@ def main():
     }
     if not args.no_cpu_baseline:
         try:
-            gate_h, blobs_h = gate.cpu().numpy(), blobs.cpu().numpy()
+            gate_h, blobs_h = gate.cpu().numpy(), (blobs_ggml if use_packed else blobs).cpu().numpy()
             xh = [x.float().cpu().numpy() for x in xs[:4]]
             tms, cores, kind, _ = cpu_reference_layer(gate_h, blobs_h, blob_bytes, xh, 20, 3)
             sec = sum(tms) / len(tms)
@@ -571,9 +582,14 @@ def instrumented_pass(layers, xs, xr, stream, steps, L):
         ev[2].record(stream)
         for phase in (1, 2):
             lib.bsx_experts_set_phase(phase)
-            capi.check("experts", lib.bsx_experts_grouped_rows(C.byref(ly.L), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
-                                                                min(n, a.n_expert) + 1, n + T, _p(x), _x_kind(x), T, _p(ly.scratch), _p(ly.rows),
-                                                                capi.OUT_F32, st))
+            if ly.packed:
+                capi.check("experts", lib.bsx_experts_grouped_packed(C.byref(ly.L), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
+                                                                      min(n, a.n_expert) + 1, n + T, _p(x), _x_kind(x), T, _p(ly.scratch), _p(ly.rows),
+                                                                      capi.OUT_F32, _p(ly.status), st))
+            else:
+                capi.check("experts", lib.bsx_experts_grouped_rows(C.byref(ly.L), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
+                                                                    min(n, a.n_expert) + 1, n + T, _p(x), _x_kind(x), T, _p(ly.scratch), _p(ly.rows),
+                                                                    capi.OUT_F32, st))
             ev[2 + phase].record(stream)
         lib.bsx_experts_set_phase(0)
         capi.check("combine", lib.bsx_combine(_p(ly.rows), None, _p(ly.w), _p(ly.rows[n:n + T]), None, T, a.k, L.n_embd, _p(ly.y), st))
@@ -582,6 +598,8 @@ def instrumented_pass(layers, xs, xr, stream, steps, L):
         for j, nme in enumerate(names):
             acc[nme] += ev[j].elapsed_time(ev[j + 1])
         groups = int(ly.n_groups.item())      # distinct routed experts touched + the shared expert
+        # gate + up blob bytes of the touched experts, the activation images read (bf16 rows: 2 B a value as fp16, or 4 FP4 terms
+        # = 2.25 B with their scales), the SwiGLU rows written
         gu_bytes += groups * 2 * L.n_ff * L.gu_row + (n + T) * L.n_embd * 2 + (n + T) * L.n_ff * 4
     return {k: v / steps for k, v in acc.items()}, gu_bytes / steps
 

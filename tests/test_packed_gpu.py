@@ -21,24 +21,33 @@ def dev(a):
 
 
 def planes_from_ggml(blob, H, I):
-    """The plane layout restated on the host: codes row-major, scale words [K-step][row / 128][row % 32][(row % 128) / 32]
-    with bit 7 of every scale byte cleared and 0x7F -> 0, then the fp32 tail."""
+    """The packed layout restated on the host.  A matrix of R rows x K columns = (R / 128) x (K / 256) blocks of 18,432 bytes,
+    row tile major; a block = its 128 rows x 128 code bytes with the 16-byte pieces of row r at piece index p ^ (r % 8), then
+    four K-steps x (32 x 4) scale words, word (l, j) = row 32 j + l, scale bytes with bit 7 cleared and 0x7F -> 0."""
     def matrix(off, R, K):
         rows = blob[off:off + R * (K // 64) * 36].reshape(R, K // 64, 36)
-        codes = np.ascontiguousarray(rows[:, :, 4:]).reshape(R, K // 2)
+        codes = np.ascontiguousarray(rows[:, :, 4:]).reshape(R // 128, 128, K // 256, 8, 16)      # [tile][r][chunk][piece][16]
         sc = rows[:, :, :4] & 0x7F
         sc = np.where(sc == 0x7F, 0, sc).astype(np.uint8)
-        words = np.ascontiguousarray(sc).view(np.uint32).reshape(R, K // 64)          # [row][step]
-        sf = np.zeros((K // 64, R // 128, 32, 4), np.uint32)
-        r = np.arange(R)
-        sf[:, r // 128, r % 32, (r % 128) // 32] = words.T
-        return codes.reshape(-1), sf.reshape(-1).view(np.uint8)
+        words = np.ascontiguousarray(sc).view(np.uint32).reshape(R // 128, 128, K // 256, 4)          # [tile][r][chunk][step]
+        out = np.zeros((R // 128, K // 256, 18432), np.uint8)
+        r = np.arange(128)
+        for p in range(8):
+            dst = (r // 8) * 1024 + (r % 8) * 128 + ((p ^ (r % 8)) << 4)
+            for t in range(R // 128):
+                for c in range(K // 256):
+                    img = out[t, c]
+                    idx = dst[:, None] + np.arange(16)[None, :]
+                    img[idx] = codes[t, :, c, p, :]
+        for t in range(R // 128):
+            for c in range(K // 256):
+                sf = np.zeros((4, 32, 4), np.uint32)
+                sf[:, r % 32, r // 32] = words[t, :, c, :].T
+                out[t, c, 16384:] = sf.reshape(-1).view(np.uint8)
+        return out.reshape(-1)
     gu = I * (H // 64) * 36
-    gc, gs = matrix(0, I, H)
-    uc, us = matrix(gu, I, H)
-    dc, ds = matrix(2 * gu, H, I)
     tail = blob[2 * gu + H * (I // 64) * 36:][:16]
-    return np.concatenate([gc, uc, dc, gs, us, ds, tail])
+    return np.concatenate([matrix(0, I, H), matrix(gu, I, H), matrix(2 * gu, H, I), tail])
 
 
 @pytest.mark.parametrize("H,I", [(512, 256), (2048, 512)])
