@@ -21,7 +21,7 @@
 // 2 x 128 weight rows: 128 gate rows with their 128 up rows, or 256 down rows).  Warp 0 issues tcgen05.cp (scales ->
 // tensor memory) and the MMAs (M = 128 weight rows, N = 32 columns, K = 64 per instruction); warp 1 streams the weights (one
 // lane, two 18 KB bulk copies a stage, completion in bytes on the stage's mbarrier), warp 2 the activation images (cp.async)
-// into stages of 256 columns (4-stage ring, continuous across units); warps 3-6 are the
+// into stages of 256 columns (5-stage ring, continuous across units); warps 3-6 are the
 // epilogue (thread = TMEM lane = weight row: sums each entry's four term columns, applies row and tail scales, SwiGLU for
 // gate/up, stores coalesced).  Two accumulator sets in tensor memory let the epilogue of one unit overlap the stream of
 // the next.  Every mbarrier wait is time-bounded and reports through a status word.
@@ -40,7 +40,7 @@ namespace {
 constexpr int kTermsF = 4;                 // FP4 terms per activation row
 constexpr int kEntF = 8;                   // entries per pass
 constexpr int kColsF = kTermsF * kEntF;    // 32 = MMA N
-constexpr int kStagesF = 4;
+constexpr int kStagesF = 5;
 constexpr int kATile = 128 * 128;          // one operand tile of a stage: 128 rows x 128 bytes (256 columns of codes)
 constexpr int kBTile = kColsF * 128;
 constexpr int kSFTile = 4 * 512;           // 4 K-steps x (32 lanes x 4 words)
@@ -125,22 +125,21 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint8_t* __restrict__ i
 // ---------------------------------------------------------------- FP4 activation images
 // UE4M3 (bias 7, no sign, 0x7F unused): the value of a byte, and the smallest byte whose value times 6 reaches amax.
 __device__ __forceinline__ float ue4m3_value(uint32_t b) {
-    const int e = (int) (b >> 3), m = (int) (b & 7u);
-    return e ? ldexpf(1.f + (float) m * 0.125f, e - 7) : ldexpf((float) m, -9);
+    // normal: 2^(e - 7) (1 + m / 8) = fp32 with exponent field e + 120 and the three mantissa bits on top; e = 0: m 2^-9
+    return b >= 8u ? __uint_as_float((b + 960u) << 20) : (float) b * 0.001953125f;
 }
 __device__ __forceinline__ uint32_t ue4m3_cover(float amax) {
     if (!(amax > 0.f)) return 0u;
-    const float t = amax / 6.f;
+    const float t = amax * (1.f / 6.f);
     uint32_t b;
     if (t < 0.015625f) {
         b = (uint32_t) ceilf(t * 512.f);
     } else {
-        uint32_t bits = __float_as_uint(t) + 0x000FFFFFu;
-        const int e = (int) (bits >> 23) - 127 + 7;
-        b = e > 15 ? 0x7Eu : (uint32_t) ((e << 3) | (int) ((bits >> 20) & 7u));
+        const uint32_t bits = __float_as_uint(t) + 0x000FFFFFu;      // mantissa rounded up to three bits
+        b = (bits >> 20) - 960u;                                      // (exponent field - 120) << 3 | mantissa
     }
-    if (b > 0x7Eu) b = 0x7Eu;
-    if (b > 0u && ue4m3_value(b - 1) * 6.f >= amax) --b;       // t was rounded up by the division
+    b = min(b, 0x7Eu);
+    if (b > 0u && ue4m3_value(b - 1) * 6.f >= amax) --b;       // t was rounded up
     if (b < 0x7Eu && ue4m3_value(b) * 6.f < amax) ++b;         // ... or down
     return b;
 }
@@ -150,9 +149,11 @@ __device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
     asm("{\n.reg .b8 t;\ncvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\ncvt.u16.u8 %0, t;\n}\n" : "=h"(r) : "f"(hi), "f"(lo));
     return (uint32_t) r & 0xFFu;
 }
-__device__ __forceinline__ float e2m1_value(uint32_t c) {
-    const float m = (c & 7u) < 2u ? 0.5f * (float) (c & 7u) : ldexpf(1.f + 0.5f * (float) (c & 1u), (int) ((c >> 1) & 3u) - 1);
-    return (c & 8u) ? -m : m;
+// the two values of a code byte: low nibble -> .x, high nibble -> .y
+__device__ __forceinline__ float2 e2m1x2_values(uint32_t c) {
+    uint32_t h;
+    asm("{\n.reg .b8 t;\ncvt.u8.u32 t, %1;\ncvt.rn.f16x2.e2m1x2 %0, t;\n}\n" : "=r"(h) : "r"(c));
+    return __half22float2(*reinterpret_cast<const __half2*>(&h));
 }
 
 // TPR threads per activation row (32, 128 or 256: a thread per 16-value sub-block where the row allows): the row times a
@@ -259,8 +260,9 @@ __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __
 #pragma unroll
                 for (int b = 0; b < 8; ++b) {
                     const uint32_t c = e2m1x2(v[b] * rs, v[b + 8] * rs);
-                    v[b] -= e2m1_value(c & 15u) * sv;
-                    v[b + 8] -= e2m1_value(c >> 4) * sv;
+                    const float2 q = e2m1x2_values(c);
+                    v[b] -= q.x * sv;
+                    v[b + 8] -= q.y * sv;
                     if (b < 4) w0 |= c << (8 * b);
                     else w1 |= c << (8 * (b - 4));
                 }
