@@ -326,6 +326,18 @@ class MoELayer:
             self.s_scratch = torch.empty(native_expert_scratch_bytes(self.shared_L, max_tokens), dtype=torch.uint8, device=dev)
             self._s_T = -1
 
+    def capture(self, x_example: torch.Tensor):
+        """Records forward() for max_tokens rows of x_example's dtype into a CUDA graph (every call of the step is
+        stream-ordered and allocates nothing, as the reference requires of its own: iq_kernels.hpp:95); forward_graphed
+        then costs one launch."""
+        return _capture(self, x_example)
+
+    def forward_graphed(self, x: torch.Tensor) -> torch.Tensor:
+        """x [max_tokens][n_embd] of the captured dtype -> y (a view of an internal buffer), by replaying the graph."""
+        self.x_static.copy_(x, non_blocking=True)
+        self.graph.replay()
+        return self.y
+
     def forward(self, x: torch.Tensor, x_router: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
         """x: [T][n_embd] fp32 or bf16 activations; x_router: other rows for the router to read (defaults to x).
         Returns y [T][n_embd] fp32 (a view of an internal buffer)."""
@@ -373,6 +385,24 @@ class MoELayer:
                 shared = self.s_out
         check("bsx_combine", lib.bsx_combine(_p(self.rows), None, _p(self.w), _p(shared), None, T, a.k, self.L.n_embd, _p(self.y), st))
         return self.y[:T]
+
+
+def _capture(layer, x_example: torch.Tensor):
+    """Shared by the layer classes: run forward() twice outside a capture (one-time attribute calls, allocations), then
+    record it into a CUDA graph over a static input buffer."""
+    T, H = layer.max_tokens, layer.L.n_embd
+    layer.x_static = torch.zeros((T, H), dtype=x_example.dtype, device=x_example.device)
+    side = torch.cuda.Stream(device=x_example.device)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            layer.forward(layer.x_static)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    layer.graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(layer.graph):
+        layer.forward(layer.x_static)
+    return layer
 
 
 class PrefillMoELayer:

@@ -206,6 +206,7 @@ def main():
     ap.add_argument("--experts", default="packed", choices=["packed", "fp16"],
                     help="decode expert kernels: packed = blobs repacked at load into planes, block-scaled FP4 tensor cores (tcgen05 kind::mxf4nvf4); "
                          "fp16 = ggml blobs in place, fp16 activation images, mma.sync")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel of a step from the host instead of replaying the layer's CUDA graph")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: 64 tokens a step (the default line); prefill: --tokens rows a step, Zipf(1.1) expert popularity, tcgen05 grouped experts")
     ap.add_argument("--tokens", type=int, default=4096, help="rows per step of the prefill workload, per GPU (4096 or 16384 in the reference's configs)")
@@ -254,8 +255,18 @@ def main():
     xs = [torch.randn((T, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
     stream = torch.cuda.Stream(device=dev)
 
+    use_graph = not args.no_graph
+    if use_graph:
+        with torch.cuda.stream(stream):
+            for ly in layers:
+                ly.capture(xs[0])
+        torch.cuda.synchronize()
+
     def step(i, x=None):
-        return layers[i % args.copies].forward(xs[i % n_batches] if x is None else x, None, stream)
+        xx = xs[i % n_batches] if x is None else x
+        if use_graph:
+            return layers[i % args.copies].forward_graphed(xx)
+        return layers[i % args.copies].forward(xx, None, stream)
 
     def barrier():
         if world > 1:
@@ -314,7 +325,8 @@ def main():
                   else "fp16 x NVFP4 tensor-core products (mma.sync), fp32 accumulation"), "data": "synthetic",
         "config": dict(CFG, l2_policy=f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB) and each step touches ~650 MB: larger than L2",
                        parallelism="single GPU" if world == 1 else f"ep{world}",
-                       expert_kernels="packed planes + tcgen05 block-scaled FP4" if use_packed else "ggml blobs in place + fp16 images + mma.sync"),
+                       expert_kernels="packed planes + tcgen05 block-scaled FP4" if use_packed else "ggml blobs in place + fp16 images + mma.sync",
+                       launch="one CUDA graph per step (input copied into its static buffer, device to device)" if use_graph else "one host launch per kernel"),
         "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
         "gpu_launches": 9 * args.steps,   # logits, select, plan, 2 x image prep, gate/up, down, combine (+0: the shared expert rides in the grouped call)
         "roofline": {"bound": "hbm", "kernel": ("nvf4_stream_kernel<gate/up>" if use_packed else "nvfp4_mma_kernel<gate/up>") + " (routed + shared experts; stage time includes the activation-image kernel)", "achieved": achieved, "peak": peak,

@@ -137,3 +137,26 @@ def test_packed_layer_matches_the_fp16_image_layer(lib, cuda):
     print("packed layer vs fp16-image layer, relative L2:", rel)
     assert rel < 1e-3
     assert torch.equal(got.view(torch.int32), got2.view(torch.int32)), "not bit-stable from run to run"
+
+
+def test_layer_step_replays_as_a_cuda_graph(lib, cuda):
+    """The whole step (router, plan, images, experts, combine) is stream-ordered and allocation-free, so it records into a
+    CUDA graph; the replay gives the bits of the launch-by-launch step."""
+    rng = np.random.default_rng(12)
+    E, H, I, K, T = 32, 512, 256, 4, 16
+    Lo, blobs = make_expert_blobs(rng, E + 1, O.T_NVFP4, O.T_NVFP4, H, I)
+    L = moe.native_expert_layout(40, 40, H, I)
+    bd = dev(stack_blobs(blobs))
+    packed = moe.pack_experts(L, bd)
+    gate = dev((rng.standard_normal((E, H)) * 0.02).astype(np.float32))
+    args = moe.RouterArgs(n_expert=E, n_embd=H, k=K, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    xs = [torch.randn((T, H), device="cuda", generator=g).bfloat16() for _ in range(3)]
+    for pk, b in ((True, packed), (False, bd)):
+        layer = moe.MoELayer(gate, None, b[:E], L, args, shared_blob=b[E], max_tokens=T, packed=pk)
+        want = [layer.forward(x).clone() for x in xs]
+        layer.capture(xs[0])
+        got = [layer.forward_graphed(x).clone() for x in xs]
+        torch.cuda.synchronize()
+        for w, gt in zip(want, got):
+            assert torch.equal(w.view(torch.int32), gt.view(torch.int32))
