@@ -227,7 +227,8 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsi
 // One block: a scan over the experts, then every thread places rows by binary search in the offsets.
 __global__ void __launch_bounds__(1024)
 plan_groups_kernel(const int32_t* __restrict__ cnt, const int32_t* __restrict__ off, const int32_t* __restrict__ src, int E,
-                   const unsigned long long* __restrict__ blobs, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
+                   const unsigned long long* __restrict__ blobs, unsigned long long shared_blob, int tok_lo, int tok_n,
+                   unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
                    int32_t* __restrict__ n_groups, int32_t* __restrict__ ent_dst, int32_t* __restrict__ ent_tok) {
     __shared__ int sh[32];
     __shared__ int s_off[kMaxExpert + 1];
@@ -246,14 +247,27 @@ plan_groups_kernel(const int32_t* __restrict__ cnt, const int32_t* __restrict__ 
         ptr[g] = blobs[e];
         start[g] = first;
     }
+    // a shared expert: one more group, tokens tok_lo .. tok_lo + tok_n - 1, its rows after the dispatch's own
+    const int extra = shared_blob != 0ull ? tok_n : 0;
     if (e == 0) {
         s_off[E] = off[E];
         start[groups] = entries;
-        start[groups + 1] = entries;
-        *n_groups = groups;
+        if (extra > 0) {
+            ptr[groups] = shared_blob;
+            start[groups + 1] = entries + extra;
+            start[groups + 2] = entries + extra;
+            *n_groups = groups + 1;
+        } else {
+            start[groups + 1] = entries;
+            *n_groups = groups;
+        }
     }
     __syncthreads();
     const int n_rows = s_off[E];
+    for (int t = threadIdx.x; t < extra; t += blockDim.x) {
+        ent_dst[entries + t] = n_rows + t;
+        ent_tok[entries + t] = tok_lo + t;
+    }
     for (int r = threadIdx.x; r < n_rows; r += blockDim.x) {
         int lo = 0, hi = E;                 // the expert with off[x] <= r < off[x + 1]
         while (hi - lo > 1) {
@@ -354,7 +368,18 @@ extern "C" int32_t bsx_plan_groups(const int32_t* cnt, const int32_t* off, const
     if (!stream) return BSX_E_STREAM;
     if (E < 1 || E > kMaxExpert) return BSX_E_GEOMETRY;
     if (!cnt || !off || !src || !blob_table || !ptr || !start || !n_groups || !ent_dst || !ent_tok) return BSX_E_POINTER;
-    plan_groups_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(cnt, off, src, E, blob_table, ptr, start, n_groups, ent_dst, ent_tok);
+    plan_groups_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(cnt, off, src, E, blob_table, 0ull, 0, 0, ptr, start, n_groups, ent_dst, ent_tok);
+    return launch_status();
+}
+
+extern "C" int32_t bsx_plan_groups_shared(const int32_t* cnt, const int32_t* off, const int32_t* src, int32_t E, const unsigned long long* blob_table,
+                                          unsigned long long shared_blob, int32_t tok_lo, int32_t tok_n, unsigned long long* ptr, int32_t* start,
+                                          int32_t* n_groups, int32_t* ent_dst, int32_t* ent_tok, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (E < 1 || E > kMaxExpert || tok_lo < 0 || tok_n < 0) return BSX_E_GEOMETRY;
+    if (!cnt || !off || !src || !blob_table || !ptr || !start || !n_groups || !ent_dst || !ent_tok) return BSX_E_POINTER;
+    plan_groups_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(cnt, off, src, E, blob_table, shared_blob, tok_lo, tok_n, ptr, start, n_groups, ent_dst,
+                                                              ent_tok);
     return launch_status();
 }
 

@@ -164,16 +164,20 @@ class EPMoELayerA2A:
 class EPMoELayer:
     """The expert-parallel layer on one rank, collective form: all-gather (activations, routing) -> local experts ->
     partial combine -> reduce-scatter.  Every size is fixed by (world, max_tokens), nothing is read back to the host, and
-    every rank must pass the same number of tokens per step."""
+    every rank must pass the same number of tokens per step.  packed: blobs and the shared blob are in the plane layout
+    of moe.pack_experts and run on the block-scaled FP4 tensor cores.  The shared expert (replicated) runs on the rank's
+    own tokens as one more group of the same grouped call.  capture() records the step, collectives included, into a
+    CUDA graph."""
 
-    def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, shared_blob=None, max_tokens: int = 64, group=None):
+    def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, shared_blob=None, max_tokens: int = 64, group=None,
+                 packed: bool = False):
         import torch
         import torch.distributed as dist
         from . import capi, moe
         self.torch, self.dist, self.moe, self.capi = torch, dist, moe, capi
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        self.E, self.L, self.args = n_expert_total, layout, args
+        self.E, self.L, self.args, self.packed = n_expert_total, layout, args, packed
         first = ep_partition(n_expert_total, self.world)
         self.lo, self.hi = int(first[self.rank]), int(first[self.rank + 1])
         self.gate_w, self.bias, self.blobs, self.shared_blob = gate_w, bias, blobs, shared_blob
@@ -187,8 +191,11 @@ class EPMoELayer:
         W, T, k, H = self.world, max_tokens, args.k, layout.n_embd
         self.max_tokens = T
         n = W * T * k
+        rows = n + (T if shared_blob is not None else 0)
         f32, i32 = torch.float32, torch.int32
         self.logits = torch.empty((T, n_expert_total), dtype=f32, device=dev)
+        self.ids = torch.empty((T, k), dtype=i32, device=dev)
+        self.w = torch.empty((T, k), dtype=f32, device=dev)
         self.route = torch.empty((T, 2 * k), dtype=i32, device=dev)          # [ids | weight bits] of the rank's own tokens
         self.route_all = torch.empty((W * T, 2 * k), dtype=i32, device=dev)
         self.ids_all = torch.empty((W * T, k), dtype=i32, device=dev)
@@ -198,23 +205,46 @@ class EPMoELayer:
         self.slot = torch.empty(n, dtype=i32, device=dev)
         self.src = torch.empty(n, dtype=i32, device=dev)
         self.dscratch = torch.empty(capi.lib().bsx_dispatch_scratch_bytes(n, n_expert_total), dtype=torch.uint8, device=dev)
-        self.ptr = torch.zeros(n_expert_total + 2, dtype=torch.int64, device=dev)
-        self.start = torch.zeros(n_expert_total + 2, dtype=i32, device=dev)
+        self.ptr = torch.zeros(n_expert_total + 3, dtype=torch.int64, device=dev)
+        self.start = torch.zeros(n_expert_total + 3, dtype=i32, device=dev)
         self.n_groups = torch.zeros(1, dtype=i32, device=dev)
-        self.ent_dst = torch.zeros(n, dtype=i32, device=dev)
-        self.ent_tok = torch.zeros(n, dtype=i32, device=dev)
-        self.rows = torch.empty((n, H), dtype=f32, device=dev)
-        self.scratch = torch.empty(moe.native_expert_scratch_bytes(layout, n), dtype=torch.uint8, device=dev)
+        self.ent_dst = torch.zeros(rows, dtype=i32, device=dev)
+        self.ent_tok = torch.zeros(rows, dtype=i32, device=dev)
+        self.rows = torch.empty((rows, H), dtype=f32, device=dev)
+        if packed:
+            self.scratch = torch.empty(capi.lib().bsx_experts_packed_scratch_bytes(C.byref(layout), rows), dtype=torch.uint8, device=dev)
+        else:
+            self.scratch = torch.empty(moe.native_expert_scratch_bytes(layout, rows), dtype=torch.uint8, device=dev)
+        self.status = torch.zeros(1, dtype=i32, device=dev)
         self.y_part = torch.empty((W * T, H), dtype=f32, device=dev)
         self.y = torch.empty((T, H), dtype=f32, device=dev)
         self.y_sum = torch.empty((T, H), dtype=f32, device=dev)
         self.ones = torch.ones((T, 1), dtype=f32, device=dev)
         self.x_all = None
-        self.side = torch.cuda.Stream(device=dev)
         self.time_experts, self.last_expert_ms, self.last_groups = False, 0.0, 0
-        if shared_blob is not None:
-            self.s_out = torch.empty((T, H), dtype=f32, device=dev)
-            self.s_scratch = torch.empty(capi.lib().bsx_gated_mlp_scratch_bytes(C.byref(layout), T), dtype=torch.uint8, device=dev)
+        self.graph = None
+
+    def capture(self, x_example):
+        """Records forward() into a CUDA graph (NCCL collectives included).  Every rank must capture, and replay, in step."""
+        torch = self.torch
+        self.x_static = torch.zeros((self.max_tokens, self.L.n_embd), dtype=x_example.dtype, device=self.dev)
+        side = torch.cuda.Stream(device=self.dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self.forward(self.x_static)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        # thread-local capture mode: the process group's watchdog thread polls its events while this thread captures
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            self.forward(self.x_static)
+        return self
+
+    def forward_graphed(self, x):
+        self.x_static.copy_(x, non_blocking=True)
+        self.graph.replay()
+        return self.y
 
     def forward(self, x):
         torch, dist, moe, capi = self.torch, self.dist, self.moe, self.capi
@@ -225,16 +255,9 @@ class EPMoELayer:
         st = moe._stream(cur)
         p = moe._p
         # 1. route the rank's own tokens; ids and weights travel as one int32 row per token
-        ids_own, w_own = self.route[:, :k], self.route[:, k:].view(torch.float32)
-        ids_c = torch.empty((T, k), dtype=torch.int32, device=self.dev)
-        w_c = torch.empty((T, k), dtype=torch.float32, device=self.dev)
-        moe.router_x(x, self.gate_w, self.bias, a, self.logits, ids_c, w_c)
-        ids_own.copy_(ids_c)
-        w_own.copy_(w_c)
-        if self.shared_blob is not None:     # the shared expert of the rank's own tokens, beside the exchange
-            self.side.wait_stream(cur)
-            with torch.cuda.stream(self.side):
-                moe.gated_mlp(L, self.shared_blob, x, cap_tok=T, out=self.s_out, scratch=self.s_scratch)
+        moe.router_x(x, self.gate_w, self.bias, a, self.logits, self.ids, self.w)
+        self.route[:, :k].copy_(self.ids)
+        self.route[:, k:].view(torch.float32).copy_(self.w)
         # 2. everyone gets every token's activations and routing
         if self.x_all is None or self.x_all.dtype != x.dtype:
             self.x_all = torch.empty((W * T, H), dtype=x.dtype, device=self.dev)
@@ -242,18 +265,25 @@ class EPMoELayer:
         dist.all_gather_into_tensor(self.route_all, self.route, group=self.group)
         self.ids_all.copy_(self.route_all[:, :k])
         self.w_all.copy_(self.route_all[:, k:].view(torch.float32))
-        # 3. dispatch all pairs; groups only for the experts held here
+        # 3. dispatch all pairs; groups only for the experts held here (+ the shared expert over the rank's own tokens)
         n = W * T * k
         capi.check("bsx_dispatch", lib.bsx_dispatch(p(self.ids_all), n, k, self.E, p(self.cnt), p(self.off), p(self.slot), p(self.src), 0, None, None,
                                                      p(self.dscratch), st))
-        capi.check("bsx_plan_groups", lib.bsx_plan_groups(p(self.cnt), p(self.off), p(self.src), self.E, p(self.blob_table), p(self.ptr), p(self.start),
-                                                           p(self.n_groups), p(self.ent_dst), p(self.ent_tok), st))
-        # 4. the local experts over the rows routed to them (outputs land on their dispatch rows)
+        shared = self.shared_blob is not None
+        capi.check("bsx_plan_groups_shared", lib.bsx_plan_groups_shared(p(self.cnt), p(self.off), p(self.src), self.E, p(self.blob_table),
+                                                                         self.shared_blob.data_ptr() if shared else 0, self.rank * T, T if shared else 0,
+                                                                         p(self.ptr), p(self.start), p(self.n_groups), p(self.ent_dst), p(self.ent_tok), st))
+        # 4. the local experts over the rows routed to them (outputs land on their dispatch rows; shared rows after them)
         if self.time_experts:
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record(cur)
-        moe.native_expert_grouped(L, self.ptr, self.start, self.n_groups, self.ent_dst, self.ent_tok, self.hi - self.lo, n, self.x_all, self.scratch,
-                                  self.rows, n_x_rows=W * T)
+        cap_groups, cap_rows = self.hi - self.lo + (1 if shared else 0), n + (T if shared else 0)
+        if self.packed:
+            moe.native_expert_grouped_packed(L, self.ptr, self.start, self.n_groups, self.ent_dst, self.ent_tok, cap_groups, cap_rows, self.x_all,
+                                             self.scratch, self.rows, self.status, n_x_rows=W * T)
+        else:
+            moe.native_expert_grouped(L, self.ptr, self.start, self.n_groups, self.ent_dst, self.ent_tok, cap_groups, cap_rows, self.x_all, self.scratch,
+                                      self.rows, n_x_rows=W * T)
         if self.time_experts:
             t1.record(cur)
             t1.synchronize()
@@ -261,13 +291,12 @@ class EPMoELayer:
         # 5. each token's local pairs summed here, the ranks' partial sums reduced onto the token's owner
         capi.check("bsx_combine_partial", lib.bsx_combine_partial(p(self.rows), p(self.slot), p(self.w_all), p(self.ids_all), self.lo, self.hi, W * T, k, H,
                                                                    p(self.y_part), st))
-        if self.shared_blob is None:
+        if not shared:
             dist.reduce_scatter_tensor(self.y, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
             return self.y
         dist.reduce_scatter_tensor(self.y_sum, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
-        cur.wait_stream(self.side)
         # y = 1 * sum + shared, through the combine kernel (one "row" per token)
-        capi.check("bsx_combine", lib.bsx_combine(p(self.y_sum), None, p(self.ones), p(self.s_out), None, T, 1, H, p(self.y), st))
+        capi.check("bsx_combine", lib.bsx_combine(p(self.y_sum), None, p(self.ones), p(self.rows[n:n + T]), None, T, 1, H, p(self.y), st))
         return self.y
 
 

@@ -359,9 +359,13 @@ def run_expert_parallel(args, rank, world, dev):
     L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
     rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
     layers = []
+    use_packed = args.experts == "packed"
+    mine = torch.cat([blobs[rank * El:(rank + 1) * El], blobs[E:E + 1]])      # the rank's routed experts + the shared one
+    if use_packed:
+        mine = moe.pack_experts(L, mine)
     for c in range(args.copies):
-        own = blobs[rank * El:(rank + 1) * El].clone()
-        layers.append(ep.EPMoELayer(gate.clone(), None, own, L, rargs, E, shared_blob=blobs[E].clone(), max_tokens=T))
+        b = mine.clone()
+        layers.append(ep.EPMoELayer(gate.clone(), None, b[:El], L, rargs, E, shared_blob=b[El], max_tokens=T, packed=use_packed))
     del blobs
     n_batches = 8
     g = torch.Generator(device=dev).manual_seed(1 + rank)
@@ -372,15 +376,25 @@ def run_expert_parallel(args, rank, world, dev):
         dist.barrier()
         torch.cuda.synchronize()
 
+    use_graph = not args.no_graph
+
+    def fwd(i, x=None):
+        ly, xx = layers[i % args.copies], (xs[i % n_batches] if x is None else x)
+        return ly.forward_graphed(xx) if use_graph else ly.forward(xx)
+
     with torch.cuda.stream(stream):
+        if use_graph:
+            for ly in layers:
+                ly.capture(xs[0])
+            barrier()
         for i in range(args.warmup):
-            layers[i % args.copies].forward(xs[i % n_batches])
+            fwd(i)
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(dev.index or 0) as clocks:
             ev0.record(stream)
             for i in range(args.steps):
-                layers[i % args.copies].forward(xs[i % n_batches])
+                fwd(i)
             ev1.record(stream)
             barrier()
         ms_total = ev0.elapsed_time(ev1)
@@ -392,7 +406,7 @@ def run_expert_parallel(args, rank, world, dev):
         e0.record(stream)
         for i in range(args.steps):
             xin.copy_(x_host[i % n_batches], non_blocking=True)
-            y_host.copy_(layers[i % args.copies].forward(xin), non_blocking=True)
+            y_host.copy_(fwd(i, xin), non_blocking=True)
             stream.synchronize()
         e1.record(stream)
         barrier()
@@ -420,12 +434,17 @@ def run_expert_parallel(args, rank, world, dev):
     line = {
         "metric": "MoE-layer tokens/s (decode)", "value": T * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "fp16 x NVFP4 tensor-core products, fp32 accumulation", "data": "synthetic",
-        "config": dict(CFG, tokens_per_step=T * world, tokens_per_gpu=T, parallelism=f"ep{world}: {E // world} routed experts per GPU, router and shared expert replicated, NCCL all-to-all of bf16 rows out and fp32 rows back",
-                       l2_policy=f"each rank cycles through {args.copies} copies of its expert shard"),
+        "vs_baseline": None,
+        "dtype": ("NVFP4 weights x 4-term FP4 activations on tcgen05 kind::mxf4nvf4 (block-scaled), fp32 accumulation" if use_packed
+                  else "fp16 x NVFP4 tensor-core products (mma.sync), fp32 accumulation"), "data": "synthetic",
+        "config": dict(CFG, tokens_per_step=T * world, tokens_per_gpu=T,
+                       parallelism=f"ep{world}: {E // world} routed experts per GPU, router and shared expert replicated; NCCL all-gather of bf16 rows and routing, reduce-scatter of fp32 partial sums",
+                       l2_policy=f"each rank cycles through {args.copies} copies of its expert shard",
+                       expert_kernels="packed planes + tcgen05 block-scaled FP4" if use_packed else "ggml blobs in place + fp16 images + mma.sync",
+                       launch="one CUDA graph per step, collectives included" if use_graph else "one host launch per kernel"),
         "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2 * world,
                 "d2h_bytes_per_step": T * H * 4 * world},
-        "gpu_launches": 12 * args.steps,
+        "gpu_launches": 13 * args.steps,   # logits, select, 3 dispatch, plan, 2 x images, gate/up, down, partial combine, combine (+ torch's 4 small copies, 3 NCCL kernels)
         "roofline": {"bound": "hbm", "kernel": "rank 0's local grouped experts (image prep, gate/up, down)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None, "algorithmic_bytes_per_launch": k_bytes,
                      "kernel_ms": k_ms},

@@ -265,6 +265,11 @@ BSX_API int32_t bsx_combine(const float* rows, const int32_t* slot, const float*
  * y, to be summed across ranks (reduce-scatter). */
 BSX_API int32_t bsx_plan_groups(const int32_t* cnt, const int32_t* off, const int32_t* src, int32_t E, const unsigned long long* blob_table,
                                 unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* ent_dst, int32_t* ent_tok, void* stream);
+/* bsx_plan_groups plus one more group for a shared expert every device holds: its entries are tokens tok_lo .. tok_lo +
+ * tok_n - 1 (this device's own tokens), their rows follow the dispatch's rows (row off[E] + t); arrays sized for that. */
+BSX_API int32_t bsx_plan_groups_shared(const int32_t* cnt, const int32_t* off, const int32_t* src, int32_t E, const unsigned long long* blob_table,
+                                       unsigned long long shared_blob, int32_t tok_lo, int32_t tok_n, unsigned long long* ptr, int32_t* start,
+                                       int32_t* n_groups, int32_t* ent_dst, int32_t* ent_tok, void* stream);
 BSX_API int32_t bsx_combine_partial(const float* rows, const int32_t* slot, const float* weights, const int32_t* ids, int32_t e_lo,
                                     int32_t e_hi, int32_t T, int32_t k, int32_t H, float* y, void* stream);
 

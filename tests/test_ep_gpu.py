@@ -24,6 +24,15 @@ def _weights():
 
 
 def _rank(rank, world, port, q):
+    try:
+        _rank_body(rank, world, port, q)
+    except BaseException:       # the parent shows the child's traceback instead of waiting for a result that never comes
+        import traceback
+        q.put(("error", rank, traceback.format_exc()))
+        raise
+
+
+def _rank_body(rank, world, port, q):
     sys.path.insert(0, str(ROOT))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -51,6 +60,12 @@ def _rank(rank, world, port, q):
     yc = coll.forward(xf).clone()
     yc2 = coll.forward(xf).clone()
     wantc = single.forward(xf).clone()
+    # the collective form over packed blobs (block-scaled FP4 tensor cores), launched kernel by kernel and as a CUDA graph
+    mine = moe.pack_experts(L, torch.cat([own, bd[E:E + 1]]))
+    pk = ep.EPMoELayer(gw, None, mine[:El], L, args, E, shared_blob=mine[El], max_tokens=T, packed=True)
+    ypk = pk.forward(xf).clone()
+    pk.capture(xf)
+    ypg = pk.forward_graphed(xf).clone()
     # the prompt-sized form (tensor-core experts): against the single-GPU prompt layer, and that layer against the decode one
     pre = ep.EPPrefillMoELayer(gw, None, own, L, args, E, shared_blob=bd[E], max_tokens=T)
     yp = pre.forward(xf).clone()
@@ -60,10 +75,17 @@ def _rank(rank, world, port, q):
     relc = float((yc - wantc).norm() / wantc.norm())
     relp = float((yp - wantp).norm() / wantp.norm())
     relpd = float((wantp - wantc).norm() / wantc.norm())
-    st = int(pre.status.item()) | int(single_p.status.item())
+    st = int(pre.status.item()) | int(single_p.status.item()) | int(pk.status.item())
+    relk = float((ypk - wantc).norm() / wantc.norm())
+    assert torch.equal(ypk.view(torch.int32), ypg.view(torch.int32)), "graph replay differs from the launched step"
+    assert relk < 1e-3, f"packed collective form differs from the single-GPU layer (relative L2 {relk})"
     q.put((rank, bool(torch.equal(y.view(torch.int32), want.view(torch.int32))), bool(torch.equal(y.view(torch.int32), y2.view(torch.int32))),
            float((y - want).abs().max()), relc, bool(torch.equal(yc.view(torch.int32), yc2.view(torch.int32))), relp, relpd, st))
+    torch.cuda.synchronize()
+    pk.graph.reset()            # a recorded graph holds the communicator's resources: release it before the group goes away
+    del pk
     dist.barrier()
+    torch.cuda.synchronize()
     dist.destroy_process_group()
 
 
@@ -76,10 +98,19 @@ def test_ep_two_gpus_matches_single_gpu(lib):
     procs = [ctx.Process(target=_rank, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=600) for _ in procs]
+    res = [q.get(timeout=140) for _ in procs]
+    errs = [r for r in res if r[0] == "error"]
+    if errs:
+        for p in procs:
+            p.join(timeout=20)
+            if p.is_alive():
+                p.terminate()
+        raise AssertionError("rank %d failed:\n%s" % (errs[0][1], errs[0][2]))
     for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+        p.join(timeout=45)
+        if p.is_alive():        # results are in; a rank stuck in its own teardown is not what this test is about
+            p.terminate()
+            p.join(timeout=10)
     for rank, same, stable, err, relc, stablec, relp, relpd, st in res:
         assert st == 0, f"rank {rank}: a bounded wait inside a prefill kernel gave up"
         assert relp < 1e-5, f"rank {rank}: expert-parallel prompt layer differs from the single-GPU prompt layer (relative L2 {relp})"
