@@ -33,6 +33,8 @@ _SIGNATURES = {
                                       C.c_float, P, C.c_int32, P, P, P]),
     "bsx_router": (C.c_int32, [P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_int32,
                                C.c_int32, C.c_float, P, C.c_int32, P, P, P, P]),
+    "bsx_experts_prefill_packed_scratch_bytes": (C.c_size_t, [C.POINTER(ExpertLayout), C.c_int64, C.c_int64]),
+    "bsx_experts_prefill_packed": (C.c_int32, [C.POINTER(ExpertLayout), P, P, P, P, P, C.c_int64, C.c_int64, P, C.c_int32, C.c_int64, C.c_int32, P, P, P, P]),
     "bsx_expert_packed_bytes": (C.c_size_t, [C.POINTER(ExpertLayout)]),
     "bsx_expert_pack": (C.c_int32, [C.POINTER(ExpertLayout), P, P, P]),
     "bsx_experts_packed_scratch_bytes": (C.c_size_t, [C.POINTER(ExpertLayout), C.c_int64]),

@@ -413,9 +413,12 @@ class PrefillMoELayer:
     pair (E, 1.0), so its rows go through the same grouped launch and the combine's last term adds them unweighted."""
 
     def __init__(self, gate_w: torch.Tensor, bias: Optional[torch.Tensor], blobs: torch.Tensor, layout: ExpertLayout, args: RouterArgs,
-                 shared_blob: Optional[torch.Tensor] = None, max_tokens: int = 4096):
+                 shared_blob: Optional[torch.Tensor] = None, max_tokens: int = 4096, packed: bool = False):
+        """packed: blobs (and the shared blob) are in the plane layout of pack_experts; the experts then run on the
+        block-scaled FP4 tensor cores (bsx_experts_prefill_packed)."""
         assert blobs.dtype == torch.uint8 and blobs.dim() == 2 and blobs.is_cuda
         self.gate_w, self.bias, self.blobs, self.L, self.args, self.shared_blob = gate_w, bias, blobs, layout, args, shared_blob
+        self.packed = packed
         dev = blobs.device
         E, stride = blobs.shape
         table = blobs.data_ptr() + torch.arange(E, dtype=torch.int64) * stride
@@ -439,7 +442,8 @@ class PrefillMoELayer:
         self.tiles = torch.zeros((n // 128 + self.EE, 2), dtype=i32, device=dev)
         self.n_tiles = torch.zeros(1, dtype=i32, device=dev)
         self.dscratch = torch.empty(capi.lib().bsx_dispatch_scratch_bytes(n, self.EE), dtype=torch.uint8, device=dev)
-        self.scratch = torch.empty(capi.lib().bsx_experts_prefill_scratch_bytes(C.byref(layout), T, n), dtype=torch.uint8, device=dev)
+        nscr = (capi.lib().bsx_experts_prefill_packed_scratch_bytes if packed else capi.lib().bsx_experts_prefill_scratch_bytes)(C.byref(layout), T, n)
+        self.scratch = torch.empty(nscr, dtype=torch.uint8, device=dev)
         self.dm = torch.empty((n, layout.n_embd), dtype=f32, device=dev)
         self.status = torch.zeros(1, dtype=i32, device=dev)
         self.rscratch = torch.empty(capi.lib().bsx_router_logits_prefill_scratch_bytes(T, E, layout.n_embd), dtype=torch.uint8, device=dev)
@@ -474,8 +478,13 @@ class PrefillMoELayer:
         check("bsx_dispatch", lib.bsx_dispatch(_p(ids), n, self.kk, self.EE, _p(self.cnt), _p(self.off), _p(self.slot), _p(self.src), 128,
                                                _p(self.tiles), _p(self.n_tiles), _p(self.dscratch), st))
         self._mark("dispatch", stream)
-        check("bsx_experts_prefill", lib.bsx_experts_prefill(C.byref(L), _p(self.blob_table), _p(self.off), _p(self.src), _p(self.tiles), _p(self.n_tiles),
-                                                             self.tiles.shape[0], n, _p(x), _x_kind(x), T, _p(self.scratch), _p(self.dm), _p(self.status), st))
+        if self.packed:
+            check("bsx_experts_prefill_packed", lib.bsx_experts_prefill_packed(C.byref(L), _p(self.blob_table), _p(self.off), _p(self.src), _p(self.tiles),
+                                                                               _p(self.n_tiles), self.tiles.shape[0], n, _p(x), _x_kind(x), T, self.EE,
+                                                                               _p(self.scratch), _p(self.dm), _p(self.status), st))
+        else:
+            check("bsx_experts_prefill", lib.bsx_experts_prefill(C.byref(L), _p(self.blob_table), _p(self.off), _p(self.src), _p(self.tiles), _p(self.n_tiles),
+                                                                 self.tiles.shape[0], n, _p(x), _x_kind(x), T, _p(self.scratch), _p(self.dm), _p(self.status), st))
         self._mark("experts", stream)
         check("bsx_combine", lib.bsx_combine(_p(self.dm), _p(self.slot), _p(w), None, None, T, self.kk, L.n_embd, _p(self.y), st))
         self._mark("combine", stream)

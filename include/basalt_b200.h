@@ -248,6 +248,17 @@ BSX_API int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const unsig
                                     const int32_t* src, const int32_t* tiles, const int32_t* n_tiles, int64_t cap_tiles, int64_t cap_rows,
                                     const void* x, int32_t x_kind, int64_t n_tokens, void* scratch, float* dm, int32_t* status, void* stream);
 
+/* ---- a11 on the block-scaled FP4 tensor cores: bsx_experts_prefill over blobs packed by bsx_expert_pack (blob_table[e] = a
+ * packed blob, 0 = held elsewhere).  Activations enter as four FP4 terms per row (x rows and the SwiGLU rows alike), so the
+ * rows sit ~2e-4 from the dequantised fp32 reference; nothing is decoded on the way to the tensor core.  n_expert = the
+ * length of off minus one.  scratch: bsx_experts_prefill_packed_scratch_bytes(layout, n_tokens, cap_rows), 256-byte aligned.
+ * Tiles as for bsx_experts_prefill (bsx_dispatch with tile_rows = 128). */
+BSX_API size_t bsx_experts_prefill_packed_scratch_bytes(const bsx_expert_layout* layout, int64_t n_tokens, int64_t cap_rows);
+BSX_API int32_t bsx_experts_prefill_packed(const bsx_expert_layout* layout, const unsigned long long* blob_table, const int32_t* off,
+                                           const int32_t* src, const int32_t* tiles, const int32_t* n_tiles, int64_t cap_tiles, int64_t cap_rows,
+                                           const void* x, int32_t x_kind, int64_t n_tokens, int32_t n_expert, void* scratch, float* dm,
+                                           int32_t* status, void* stream);
+
 /* ---- a13: weighted combine.  Replaces native_moe_combine[_multi] (include/basalt/models/qwen4exp/kernels/native_moe.hpp:5-15,
  * native_moe.cu:36-85), moe_combine (src/models/qwen4exp/prefill/kernels.cu:438-449,705-709) and weighted_sum_tokens
  * (src/models/deepseek41/prefill_ffn.cu:33-50).  y[t] = fma chain over j < k of weights[t][j] * rows[slot[t*k+j]] in j
