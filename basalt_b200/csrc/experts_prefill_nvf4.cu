@@ -277,11 +277,18 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(st + (uint32_t) (t * kATileQ) + cdst[i]),
                                      "l"(crow[i] + (size_t) t * (size_t) (K >> 1) + (size_t) c * 128)
                                      : "memory");
+                }
+                // this row's scale words: 16 bytes a term (the chunk's four K-steps) through registers, then one word into slot
+                // (m % 32, m / 32) of each step's block (four rows share a 16-byte slot, so no 16-byte copy can place them)
+                uint4 sv[kTermsF];
+#pragma unroll
+                for (int t = 0; t < kTermsF; ++t) sv[t] = *reinterpret_cast<const uint4*>(srow + (size_t) t * (size_t) (K >> 4) + (size_t) c * 16);
+#pragma unroll
+                for (int t = 0; t < kTermsF; ++t) {
+                    const uint32_t w[4] = {sv[t].x, sv[t].y, sv[t].z, sv[t].w};
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(st + sdst + (uint32_t) (t * kSFQ + k * 512)),
-                                     "l"(srow + (size_t) t * (size_t) (K >> 4) + (size_t) c * 16 + 4 * k)
-                                     : "memory");
+                        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(st + sdst + (uint32_t) (t * kSFQ + k * 512)), "r"(w[k]) : "memory");
                 }
                 asm volatile("cp.async.commit_group;\n" ::: "memory");
                 ++issued;

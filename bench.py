@@ -484,8 +484,12 @@ def run_prefill(args, dev, rank=0, world=1):
     rargs = moe.RouterArgs(n_expert=Es, n_embd=Hs, k=ks, weight_scale=sh["scale"], gate=gk, n_group=sh["n_group"], topk_group=sh["topk_group"])
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     bias = (torch.randn(Es, generator=torch.Generator(device=dev).manual_seed(7), device=dev) * 0.01).float() if sh["bias"] else None
+    use_packed = args.experts == "packed" and world == 1
+    if use_packed:
+        own, shared = moe.pack_experts(L, own), moe.pack_experts(L, shared)
+        torch.cuda.synchronize()
     if world == 1:
-        layer = moe.PrefillMoELayer(gate, bias, own, L, rargs, shared_blob=shared[0], max_tokens=Tn)
+        layer = moe.PrefillMoELayer(gate, bias, own, L, rargs, shared_blob=shared[0], max_tokens=Tn, packed=use_packed)
     else:
         layer = ep.EPPrefillMoELayer(gate, bias, own, L, rargs, Es, shared_blob=shared[0], max_tokens=Tn)
     n_batches = 2
@@ -565,7 +569,7 @@ def run_prefill(args, dev, rank=0, world=1):
     exp_ms = stage_ms["experts"] if world == 1 else ms_step
     achieved = flops / world / (exp_ms * 1e-3) / 1e12
     blob_b = touched * (L.bytes - 16)
-    roof = {"bound": "tensor", "kernel": "prefill_gemm_kernel<gate/up> + <down> (+ activation prep)" if world == 1 else "whole step per GPU (experts + collectives)",
+    roof = {"bound": "tensor", "kernel": (("prefill_nvf4_kernel" if use_packed else "prefill_gemm_kernel") + "<gate/up> + <down> (+ activation images)") if world == 1 else "whole step per GPU (experts + collectives)",
             "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak,
             "peak_source": "measured bf16 burst (MEASURED_PEAKS.json)" if peaks else "fallback", "traffic": None,
             "algorithmic_flops_per_launch": flops / world, "kernel_ms": exp_ms, "hbm_ms_of_touched_blobs": blob_b / (hbm * 1e9) * 1e3,
@@ -575,7 +579,8 @@ def run_prefill(args, dev, rank=0, world=1):
     line = {
         "metric": "MoE-layer tokens/s (prefill)", "value": Tn * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "fp16 x (NVFP4 decoded exactly to fp16) on tcgen05 kind::f16, fp32 accumulation in tensor memory", "data": "synthetic",
+        "dtype": ("NVFP4 weights x 4-term FP4 activations on tcgen05 kind::mxf4nvf4 (block-scaled), fp32 accumulation in tensor memory" if use_packed
+                  else "fp16 x (NVFP4 decoded exactly to fp16) on tcgen05 kind::f16, fp32 accumulation in tensor memory"), "data": "synthetic",
         "config": dict(workload=f"{sh['name']} prefill, {Tn} tokens/step per GPU" + (", Zipf(1.1) expert popularity" if lgs[0] is not None else ""),
                        hidden=Hs, n_expert=Es, n_shared=1, intermediate=Is, top_k=ks, router=sh["gate"], n_group=sh["n_group"], topk_group=sh["topk_group"],
                        expert_format="NVFP4 (ggml block_nvfp4 + fp32 tail scales)", activations="bf16", tokens_per_step=Tn * world,
