@@ -50,12 +50,29 @@ struct Geo {
     static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t) (kN >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
 };
 
+// a 128-row tile of one expert with everything the kernels need about it in one 16-byte load (blob 0: held elsewhere)
+struct __align__(16) TileRec {
+    unsigned long long blob;
+    int row0, rows;
+};
+
+__global__ void __launch_bounds__(256) tile_records_kernel(const int32_t* __restrict__ tiles, const int32_t* __restrict__ n_tiles,
+                                                           const int32_t* __restrict__ off, const unsigned long long* __restrict__ blob_table,
+                                                           TileRec* __restrict__ recs, int64_t cap_tiles) {
+    const int64_t t = (int64_t) blockIdx.x * 256 + threadIdx.x;
+    if (t >= cap_tiles || t >= *n_tiles) return;
+    const int expert = tiles[2 * t], row0 = tiles[2 * t + 1];
+    TileRec r;
+    r.blob = blob_table[expert];
+    r.row0 = row0;
+    r.rows = min(128, off[expert + 1] - row0);
+    recs[t] = r;
+}
+
 struct PrefillFArgs {
     bsx_expert_layout L;
-    const unsigned long long* blob_table;   // [E] device addresses of packed blobs (0 = held elsewhere)
-    const int32_t* off;                      // [E + 1]
+    const TileRec* recs;                     // [n_tiles]
     const int32_t* src;                      // [rows] token of each row
-    const int32_t* tiles;                    // {expert, first row} per 128-row tile
     const int32_t* n_tiles;
     const uint8_t* codes;                    // activation images of this product's A operand
     const uint8_t* sfs;
@@ -135,12 +152,11 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
     struct Item { const uint8_t* blob; int row0, rows, n0; };
     auto get_item = [&](int item, Item& it) -> bool {
         const int tile = item / n_n;
-        const int expert = a.tiles[2 * tile];
-        const unsigned long long bp = a.blob_table[expert];
-        if (bp == 0ull) return false;
-        it.blob = reinterpret_cast<const uint8_t*>(bp);
-        it.row0 = a.tiles[2 * tile + 1];
-        it.rows = min(128, a.off[expert + 1] - it.row0);
+        const TileRec r = a.recs[tile];
+        if (r.blob == 0ull) return false;
+        it.blob = reinterpret_cast<const uint8_t*>(r.blob);
+        it.row0 = r.row0;
+        it.rows = r.rows;
         it.n0 = (item - tile * n_n) * 128;
         return true;
     };
@@ -236,9 +252,37 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
         const int tl = threadIdx.x - 64;
         const int c8 = tl & 7, r16 = tl >> 3;
         uint32_t issued = 0, arrived = 0;
-        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        // Software pipeline over items so that no item starts with a chain of dependent loads: the tile record of the item after
+        // next and the row indices of the next item are requested while this item streams.
+        auto next_valid = [&](int from, TileRec& r) {     // first item >= from (in this CTA's stride) whose expert is held here
+            int it = from;
+            for (; it < n_items; it += gridDim.x) {
+                r = a.recs[it / n_n];
+                if (r.blob != 0ull) break;
+            }
+            return it;
+        };
+        auto load_idx = [&](const TileRec& r, int (&idx)[9]) {   // image rows of this lane's 8 code rows and its scale row
+#pragma unroll
+            for (int i = 0; i < 9; ++i) {
+                const int rw = i < 8 ? r16 + 16 * i : tl;
+                const int rr = rw < r.rows ? rw : 0;
+                idx[i] = MODE == QMODE_GU ? a.src[r.row0 + rr] : r.row0 + rr;
+            }
+        };
+        TileRec rec0, rec1, rec2;
+        int idx0[9], idx1[9];
+        int item = next_valid(blockIdx.x, rec0);
+        int item1 = item < n_items ? next_valid(item + gridDim.x, rec1) : n_items;
+        if (item < n_items) load_idx(rec0, idx0);
+        if (item1 < n_items) load_idx(rec1, idx1);
+        while (item < n_items && ok) {
+            const int item2 = item1 < n_items ? next_valid(item1 + gridDim.x, rec2) : n_items;
             Item it;
-            if (!get_item(item, it)) continue;
+            it.blob = reinterpret_cast<const uint8_t*>(rec0.blob);
+            it.row0 = rec0.row0;
+            it.rows = rec0.rows;
+            it.n0 = (item - (item / n_n) * n_n) * 128;
             // image rows behind the tile's rows: the row's token (gate/up) or the dispatch row itself (down); rows past the
             // expert's last row read the tile's first row (their results are never stored)
             const uint8_t* crow[8];
@@ -246,17 +290,10 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int r = r16 + 16 * i;
-                const int rr = r < it.rows ? r : 0;
-                const int64_t ir = MODE == QMODE_GU ? (int64_t) a.src[it.row0 + rr] : (int64_t) (it.row0 + rr);
-                crow[i] = a.codes + (size_t) ir * kTermsF * (size_t) (K >> 1) + c8 * 16;
+                crow[i] = a.codes + (size_t) idx0[i] * kTermsF * (size_t) (K >> 1) + c8 * 16;
                 cdst[i] = (uint32_t) ((r >> 3) * 1024 + (r & 7) * 128 + ((c8 ^ (r & 7)) << 4));
             }
-            const uint8_t* srow;
-            {
-                const int rr = tl < it.rows ? tl : 0;
-                const int64_t ir = MODE == QMODE_GU ? (int64_t) a.src[it.row0 + rr] : (int64_t) (it.row0 + rr);
-                srow = a.sfs + (size_t) ir * kTermsF * (size_t) (K >> 4);
-            }
+            const uint8_t* srow = a.sfs + (size_t) idx0[8] * kTermsF * (size_t) (K >> 4);
             const uint32_t sdst = (uint32_t) (G::kOffSFA + (tl & 31) * 16 + (tl >> 5) * 4);
             for (int c = 0; c < n_chunk; ++c) {
                 // hand over what is already on its way before blocking on the next slot (it frees only when the tensor core has
@@ -293,6 +330,14 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
                 asm volatile("cp.async.commit_group;\n" ::: "memory");
                 ++issued;
             }
+            // advance the pipeline: the next item's indices were requested one item ago; request those of the item after it
+            item = item1;
+            item1 = item2;
+            rec0 = rec1;
+            rec1 = rec2;
+#pragma unroll
+            for (int i = 0; i < 9; ++i) idx0[i] = idx1[i];
+            if (item1 < n_items) load_idx(rec1, idx1);
         }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -387,7 +432,7 @@ extern "C" size_t bsx_experts_prefill_packed_scratch_bytes(const bsx_expert_layo
     if (!L || n_tokens < 0 || cap_rows < 0 || !bsx_expert_packed_bytes(L)) return 0;
     const size_t H = (size_t) L->n_embd, I = (size_t) L->n_ff, R = (size_t) cap_rows + 128;
     return al256q((size_t) n_tokens * kTermsF * H / 2) + al256q((size_t) n_tokens * kTermsF * H / 16) + al256q((size_t) n_tokens * 4) + al256q(R * I * 4) +
-           al256q(R * kTermsF * I / 2) + al256q(R * kTermsF * I / 16) + al256q(R * 4) + 256;
+           al256q(R * kTermsF * I / 2) + al256q(R * kTermsF * I / 16) + al256q(R * 4) + al256q(((size_t) cap_rows / 128 + 1025) * sizeof(TileRec)) + 256;
 }
 
 extern "C" int32_t bsx_experts_prefill_packed(const bsx_expert_layout* layout, const unsigned long long* blob_table, const int32_t* off,
@@ -418,12 +463,14 @@ extern "C" int32_t bsx_experts_prefill_packed(const bsx_expert_layout* layout, c
     uint8_t* hsf = p;
     p += al256q(R * kTermsF * I / 16);
     float* hinv = reinterpret_cast<float*>(p);
+    p += al256q(R * 4);
+    TileRec* recs = reinterpret_cast<TileRec*>(p);
+    if (cap_tiles > cap_rows / 128 + 1025) return BSX_E_LIMIT;      // more tiles than rows / 128 + experts can make
+    tile_records_kernel<<<(unsigned) ((cap_tiles + 255) / 256), 256, 0, st>>>(tiles, n_tiles, off, blob_table, recs, cap_tiles);
     PrefillFArgs a;
     a.L = L;
-    a.blob_table = blob_table;
-    a.off = off;
+    a.recs = recs;
     a.src = src;
-    a.tiles = tiles;
     a.n_tiles = n_tiles;
     a.h = h;
     a.dm = dm;
