@@ -307,14 +307,15 @@ class EPPrefillMoELayer:
     token (bsx_combine_partial) and reduce-scatters the partial sums to the tokens' owners.  The shared expert (replicated)
     runs on the rank's own tokens as a one-expert prefill call and is added last.  Fixed sizes, no host reads."""
 
-    def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, shared_blob=None, max_tokens: int = 4096, group=None):
+    def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, shared_blob=None, max_tokens: int = 4096, group=None,
+                 packed: bool = False):
         import torch
         import torch.distributed as dist
         from . import capi, moe
         self.torch, self.dist, self.moe, self.capi = torch, dist, moe, capi
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        self.E, self.L, self.args = n_expert_total, layout, args
+        self.E, self.L, self.args, self.packed = n_expert_total, layout, args, packed
         first = ep_partition(n_expert_total, self.world)
         self.lo, self.hi = int(first[self.rank]), int(first[self.rank + 1])
         self.gate_w, self.bias, self.blobs, self.shared_blob = gate_w, bias, blobs, shared_blob
@@ -346,7 +347,8 @@ class EPPrefillMoELayer:
         self.tiles = torch.zeros((n // 128 + n_expert_total, 2), dtype=i32, device=dev)
         self.n_tiles = torch.zeros(1, dtype=i32, device=dev)
         self.dscratch = torch.empty(lib.bsx_dispatch_scratch_bytes(n, n_expert_total), dtype=u8, device=dev)
-        self.scratch = torch.empty(lib.bsx_experts_prefill_scratch_bytes(C.byref(layout), W * T, n), dtype=u8, device=dev)
+        scr = lib.bsx_experts_prefill_packed_scratch_bytes if packed else lib.bsx_experts_prefill_scratch_bytes
+        self.scratch = torch.empty(scr(C.byref(layout), W * T, n), dtype=u8, device=dev)
         self.dm = torch.empty((n, H), dtype=f32, device=dev)
         self.status = torch.zeros(1, dtype=i32, device=dev)
         self.y_part = torch.empty((W * T, H), dtype=f32, device=dev)
@@ -361,7 +363,7 @@ class EPPrefillMoELayer:
             nt = (T + 127) // 128
             self.s_tiles = torch.stack([torch.zeros(nt, dtype=i32), torch.arange(nt, dtype=i32) * 128], dim=1).contiguous().to(dev)
             self.s_ntiles = torch.tensor([nt], dtype=i32, device=dev)
-            self.s_scratch = torch.empty(lib.bsx_experts_prefill_scratch_bytes(C.byref(layout), T, T), dtype=u8, device=dev)
+            self.s_scratch = torch.empty(scr(C.byref(layout), T, T), dtype=u8, device=dev)
             self.s_dm = torch.empty((T, H), dtype=f32, device=dev)
 
     def forward(self, x):
@@ -386,16 +388,26 @@ class EPPrefillMoELayer:
         n = W * T * k
         capi.check("bsx_dispatch", lib.bsx_dispatch(p(self.ids_all), n, k, self.E, p(self.cnt), p(self.off), p(self.slot), p(self.src), 128,
                                                      p(self.tiles), p(self.n_tiles), p(self.dscratch), st))
-        capi.check("bsx_experts_prefill", lib.bsx_experts_prefill(C.byref(L), p(self.blob_table), p(self.off), p(self.src), p(self.tiles), p(self.n_tiles),
-                                                                  self.tiles.shape[0], n, p(self.x_all), kind, W * T, p(self.scratch), p(self.dm),
-                                                                  p(self.status), st))
+        if self.packed:
+            capi.check("bsx_experts_prefill_packed", lib.bsx_experts_prefill_packed(C.byref(L), p(self.blob_table), p(self.off), p(self.src), p(self.tiles),
+                                                                                    p(self.n_tiles), self.tiles.shape[0], n, p(self.x_all), kind, W * T, self.E,
+                                                                                    p(self.scratch), p(self.dm), p(self.status), st))
+        else:
+            capi.check("bsx_experts_prefill", lib.bsx_experts_prefill(C.byref(L), p(self.blob_table), p(self.off), p(self.src), p(self.tiles), p(self.n_tiles),
+                                                                      self.tiles.shape[0], n, p(self.x_all), kind, W * T, p(self.scratch), p(self.dm),
+                                                                      p(self.status), st))
         capi.check("bsx_combine_partial", lib.bsx_combine_partial(p(self.dm), p(self.slot), p(self.w_all), p(self.ids_all), self.lo, self.hi, W * T, k, H,
                                                                    p(self.y_part), st))
         if self.shared_blob is None:
             dist.reduce_scatter_tensor(self.y, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
             return self.y
-        capi.check("bsx_experts_prefill", lib.bsx_experts_prefill(C.byref(L), p(self.s_table), p(self.s_off), p(self.s_src), p(self.s_tiles), p(self.s_ntiles),
-                                                                  self.s_tiles.shape[0], T, p(x), kind, T, p(self.s_scratch), p(self.s_dm), p(self.status), st))
+        if self.packed:
+            capi.check("bsx_experts_prefill_packed", lib.bsx_experts_prefill_packed(C.byref(L), p(self.s_table), p(self.s_off), p(self.s_src), p(self.s_tiles),
+                                                                                    p(self.s_ntiles), self.s_tiles.shape[0], T, p(x), kind, T, 1,
+                                                                                    p(self.s_scratch), p(self.s_dm), p(self.status), st))
+        else:
+            capi.check("bsx_experts_prefill", lib.bsx_experts_prefill(C.byref(L), p(self.s_table), p(self.s_off), p(self.s_src), p(self.s_tiles), p(self.s_ntiles),
+                                                                      self.s_tiles.shape[0], T, p(x), kind, T, p(self.s_scratch), p(self.s_dm), p(self.status), st))
         dist.reduce_scatter_tensor(self.y_sum, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
         capi.check("bsx_combine", lib.bsx_combine(p(self.y_sum), None, p(self.ones), p(self.s_dm), None, T, 1, H, p(self.y), st))
         return self.y

@@ -484,14 +484,14 @@ def run_prefill(args, dev, rank=0, world=1):
     rargs = moe.RouterArgs(n_expert=Es, n_embd=Hs, k=ks, weight_scale=sh["scale"], gate=gk, n_group=sh["n_group"], topk_group=sh["topk_group"])
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     bias = (torch.randn(Es, generator=torch.Generator(device=dev).manual_seed(7), device=dev) * 0.01).float() if sh["bias"] else None
-    use_packed = args.experts == "packed" and world == 1
+    use_packed = args.experts == "packed"
     if use_packed:
         own, shared = moe.pack_experts(L, own), moe.pack_experts(L, shared)
         torch.cuda.synchronize()
     if world == 1:
         layer = moe.PrefillMoELayer(gate, bias, own, L, rargs, shared_blob=shared[0], max_tokens=Tn, packed=use_packed)
     else:
-        layer = ep.EPPrefillMoELayer(gate, bias, own, L, rargs, Es, shared_blob=shared[0], max_tokens=Tn)
+        layer = ep.EPPrefillMoELayer(gate, bias, own, L, rargs, Es, shared_blob=shared[0], max_tokens=Tn, packed=use_packed)
     n_batches = 2
     xs = [torch.randn((Tn, Hs), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
     lgs = [zipf_logits(Tn, Es, g, dev) if (sh["zipf"] and world == 1) else None for _ in range(n_batches)]

@@ -69,6 +69,8 @@ def _rank_body(rank, world, port, q):
     # the prompt-sized form (tensor-core experts): against the single-GPU prompt layer, and that layer against the decode one
     pre = ep.EPPrefillMoELayer(gw, None, own, L, args, E, shared_blob=bd[E], max_tokens=T)
     yp = pre.forward(xf).clone()
+    prep = ep.EPPrefillMoELayer(gw, None, mine[:El], L, args, E, shared_blob=mine[El], max_tokens=T, packed=True)
+    ypp = prep.forward(xf).clone()
     single_p = moe.PrefillMoELayer(gw, None, bd[:E], L, args, shared_blob=bd[E], max_tokens=T)
     wantp = single_p.forward(xf).clone()
     torch.cuda.synchronize()
@@ -77,6 +79,9 @@ def _rank_body(rank, world, port, q):
     relpd = float((wantp - wantc).norm() / wantc.norm())
     st = int(pre.status.item()) | int(single_p.status.item()) | int(pk.status.item())
     relk = float((ypk - wantc).norm() / wantc.norm())
+    relpp = float((ypp - wantc).norm() / wantc.norm())
+    st |= int(prep.status.item())
+    assert relpp < 2e-3, f"packed expert-parallel prompt layer differs from the single-GPU layer (relative L2 {relpp})"
     assert torch.equal(ypk.view(torch.int32), ypg.view(torch.int32)), "graph replay differs from the launched step"
     assert relk < 1e-3, f"packed collective form differs from the single-GPU layer (relative L2 {relk})"
     q.put((rank, bool(torch.equal(y.view(torch.int32), want.view(torch.int32))), bool(torch.equal(y.view(torch.int32), y2.view(torch.int32))),
