@@ -407,6 +407,256 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
     }
 }
 
+// ---------------------------------------------------------------- down product with the tile's rows resident
+// When n_ff <= 512 a tile's SwiGLU rows - 128 rows x n_ff columns as four FP4 terms, 72 KB per 256 columns with their scale
+// words - fit in shared memory for the whole tile, so they are fetched once instead of once per block of down rows, and the
+// kernel streams only weights: one bulk copy a stage brings a block of 128 down rows over all of K (KC packed blocks, which
+// are consecutive in the blob).  Item = a 128-row tile; per tile 16 x (n_embd / 2048) stages, each one accumulator of 128
+// columns, two accumulators in flight.  Tensor memory: accumulators [0, 256), the tile's activation scales [256, 256 + 64 KC),
+// per stage the weight scales.
+template <int KC>
+struct GeoR {
+    static constexpr int kABytes = KC * kTermsF * kATileQ;          // [chunk][term] code tiles
+    static constexpr int kOffSFA = kABytes;                           // [chunk][term][step] scale blocks
+    static constexpr int kOffB = kOffSFA + KC * kTermsF * kSFQ;       // two stages of KC packed blocks
+    static constexpr int kStageB = KC * kBlockF;
+    static constexpr int kBars = kOffB + 2 * kStageB;
+    static constexpr size_t kSmem = 1024 + (size_t) kBars + 256;
+    static constexpr uint32_t kTmemSFA = 256, kTmemSFB = 256 + 64 * KC, kSFBStage = 16 * KC;
+    static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t) (128 >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
+};
+
+template <int KC>
+__global__ void __launch_bounds__(kThreadsQ, 1) prefill_down_resident_kernel(PrefillFArgs a) {
+    using G = GeoR<KC>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    uint64_t* b_full = reinterpret_cast<uint64_t*>(smem + G::kBars);
+    uint64_t* b_empty = b_full + 2;
+    uint64_t* acc_full = b_empty + 2;
+    uint64_t* acc_empty = acc_full + 2;
+    uint64_t* a_full = acc_empty + 2;
+    uint64_t* a_empty = a_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(a_empty + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t K = a.L.n_ff;
+    const int n_nb = (int) (a.L.n_embd / 128);            // blocks of 128 down rows = stages per tile
+    const int n_tiles = *a.n_tiles;
+    const PackedGeom geo = packed_geom(a.L.n_embd, a.L.n_ff);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&b_full[s], 1);
+            mbar_init(&b_empty[s], 1);
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 128);
+        }
+        mbar_init(a_full, 128);
+        mbar_init(a_empty, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t sbase = smem_u32(smem);
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t ti = 0, nbc = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                if (a.recs[tile].blob == 0ull) continue;
+                ok = mbar_wait(a_full, ti & 1u);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                // the tile's activation scales: shared -> tensor memory, once
+#pragma unroll
+                for (int c = 0; c < KC; ++c)
+#pragma unroll
+                    for (int t = 0; t < kTermsF; ++t)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tmem + G::kTmemSFA + (uint32_t) (64 * c + 16 * t + 4 * k)),
+                                         "l"(sf_desc_q(sbase + (uint32_t) G::kOffSFA + (uint32_t) (((c * kTermsF + t) * 4 + k) * 512)))
+                                         : "memory");
+                for (int nb = 0; nb < n_nb; ++nb, ++nbc) {
+                    const uint32_t s = nbc & 1u, par = (nbc >> 1) & 1u;
+                    ok = mbar_wait(&acc_empty[s], par ^ 1u);
+                    if (ok) ok = mbar_wait(&b_full[s], par);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t sb = sbase + (uint32_t) G::kOffB + s * G::kStageB;
+                    const uint32_t tsfb = tmem + G::kTmemSFB + s * G::kSFBStage;
+                    const uint32_t d = tmem + s * 128;
+#pragma unroll
+                    for (int c = 0; c < KC; ++c)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsfb + (uint32_t) (16 * c + 4 * k)),
+                                         "l"(sf_desc_q(sb + (uint32_t) (c * kBlockF + kATileQ + k * 512)))
+                                         : "memory");
+                            const uint64_t bd = smem_desc_sw128(sb + (uint32_t) (c * kBlockF) + k * 32);
+#pragma unroll
+                            for (int t = 0; t < kTermsF; ++t) {
+                                const uint32_t accum = (c | k | t) ? 1u : 0u;
+                                asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+                                             "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n}\n" ::"r"(d),
+                                             "l"(smem_desc_sw128(sbase + (uint32_t) ((c * kTermsF + t) * kATileQ) + k * 32)), "l"(bd), "r"(G::kIdesc),
+                                             "r"(tmem + G::kTmemSFA + (uint32_t) (64 * c + 16 * t + 4 * k)), "r"(tsfb + (uint32_t) (16 * c + 4 * k)), "r"(accum)
+                                             : "memory");
+                            }
+                        }
+                    umma_commit(&b_empty[s]);
+                    umma_commit(&acc_full[s]);
+                }
+                if (!ok) break;
+                umma_commit(a_empty);       // the resident rows may be replaced once every MMA of the tile has read them
+                ++ti;
+            }
+            if (!ok) atomicOr(a.status, 1);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t nbc = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const unsigned long long bp = a.recs[tile].blob;
+                if (bp == 0ull) continue;
+                const uint8_t* down = reinterpret_cast<const uint8_t*>(bp) + geo.down;
+                for (int nb = 0; nb < n_nb; ++nb, ++nbc) {
+                    const uint32_t s = nbc & 1u;
+                    ok = mbar_wait(&b_empty[s], ((nbc >> 1) & 1u) ^ 1u);
+                    if (!ok) break;
+                    const uint32_t bar = smem_u32(&b_full[s]);
+                    asm volatile("{\n.reg .b64 t;\nmbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1;\n}\n" ::"r"(bar), "r"((uint32_t) G::kStageB) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(sbase + (uint32_t) G::kOffB + s * G::kStageB),
+                                 "l"(down + (size_t) nb * G::kStageB), "r"((uint32_t) G::kStageB), "r"(bar)
+                                 : "memory");
+                }
+            }
+            if (!ok) atomicOr(a.status, 1);
+        }
+    } else if (warp <= 5) {
+        // ---- the tile's rows (images of dispatch rows row0 ..): codes by 16-byte cp.async, scale words through registers
+        const int tl = threadIdx.x - 64;
+        const int c8 = tl & 7, r16 = tl >> 3;
+        const uint32_t sdst = sbase + (uint32_t) (G::kOffSFA + (tl & 31) * 16 + (tl >> 5) * 4);
+        uint32_t ti = 0;
+        TileRec rec, nrec;
+        int tile = blockIdx.x;
+        for (; tile < n_tiles; tile += gridDim.x) {
+            rec = a.recs[tile];
+            if (rec.blob != 0ull) break;
+        }
+        while (tile < n_tiles && ok) {
+            int ntile = tile + gridDim.x;             // the next tile's record is requested while this one loads
+            for (; ntile < n_tiles; ntile += gridDim.x) {
+                nrec = a.recs[ntile];
+                if (nrec.blob != 0ull) break;
+            }
+            ok = mbar_wait(a_empty, (ti & 1u) ^ 1u);
+            if (!ok) break;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int r = r16 + 16 * i;
+                const int64_t ir = rec.row0 + (r < rec.rows ? r : 0);
+                const uint8_t* g = a.codes + (size_t) ir * kTermsF * (size_t) (K >> 1) + c8 * 16;
+                const uint32_t dst = sbase + (uint32_t) ((r >> 3) * 1024 + (r & 7) * 128 + ((c8 ^ (r & 7)) << 4));
+#pragma unroll
+                for (int c = 0; c < KC; ++c)
+#pragma unroll
+                    for (int t = 0; t < kTermsF; ++t)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t) ((c * kTermsF + t) * kATileQ)),
+                                     "l"(g + (size_t) t * (size_t) (K >> 1) + (size_t) c * 128)
+                                     : "memory");
+            }
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+            {
+                const int64_t ir = rec.row0 + (tl < rec.rows ? tl : 0);
+                const uint8_t* srow = a.sfs + (size_t) ir * kTermsF * (size_t) (K >> 4);
+#pragma unroll
+                for (int c = 0; c < KC; ++c)
+#pragma unroll
+                    for (int t = 0; t < kTermsF; ++t) {
+                        const uint4 sv = *reinterpret_cast<const uint4*>(srow + (size_t) t * (size_t) (K >> 4) + (size_t) c * 16);
+                        const uint32_t w[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(sdst + (uint32_t) (((c * kTermsF + t) * 4 + k) * 512)), "r"(w[k]) : "memory");
+                    }
+            }
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            mbar_arrive(a_full);
+            ++ti;
+            tile = ntile;
+            rec = nrec;
+        }
+        if (!ok) atomicOr(a.status, 1);
+    } else {
+        // ---- epilogue: thread p = tile row p reads TMEM lane p of each finished accumulator (128 down rows at a time)
+        const int p = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = (uint32_t) ((warp & 3) * 32) << 16;
+        uint32_t nbc = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            const TileRec rec = a.recs[tile];
+            if (rec.blob == 0ull) continue;
+            const bool row_live = p < rec.rows;
+            const float* tail = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(rec.blob) + geo.tail);
+            const float sd = row_live ? tail[2] * a.inv[rec.row0 + p] : 0.f;
+            float* orow = a.dm + (size_t) (rec.row0 + p) * a.L.n_embd;
+            for (int nb = 0; nb < n_nb; ++nb, ++nbc) {
+                const uint32_t s = nbc & 1u;
+                ok = __all_sync(kFull, mbar_wait(&acc_full[s], (nbc >> 1) & 1u));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    uint32_t d[32];
+                    tmem_ld32(tmem + lane_base + s * 128 + (uint32_t) c0, d);
+                    if (row_live) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            reinterpret_cast<float4*>(orow + nb * 128 + c0)[v] = make_float4(__uint_as_float(d[4 * v]) * sd, __uint_as_float(d[4 * v + 1]) * sd,
+                                                                                            __uint_as_float(d[4 * v + 2]) * sd, __uint_as_float(d[4 * v + 3]) * sd);
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+                mbar_arrive(&acc_empty[s]);
+            }
+            if (!ok) break;
+        }
+        if (!ok && lane == 0) atomicOr(a.status, 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+template <int KC>
+int32_t launch_down_resident(const PrefillFArgs& a, cudaStream_t st) {
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(prefill_down_resident_kernel<KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) GeoR<KC>::kSmem);
+        if (e != cudaSuccess) return (int32_t) e;
+        configured[dev] = true;
+    }
+    prefill_down_resident_kernel<KC><<<(unsigned) sm_count(), kThreadsQ, GeoR<KC>::kSmem, st>>>(a);
+    return launch_status();
+}
+
 size_t al256q(size_t v) { return (v + 255) & ~(size_t) 255; }
 
 template <int MODE>
@@ -485,5 +735,8 @@ extern "C" int32_t bsx_experts_prefill_packed(const bsx_expert_layout* layout, c
     a.codes = hcodes;
     a.sfs = hsf;
     a.inv = hinv;
+    // n_ff <= 512: the tile's rows stay in shared memory and only weights stream
+    if (I == 256) return launch_down_resident<1>(a, st);
+    if (I == 512) return launch_down_resident<2>(a, st);
     return launch_q<QMODE_DOWN>(a, st);
 }
