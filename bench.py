@@ -328,7 +328,7 @@ def main():
                        expert_kernels="packed planes + tcgen05 block-scaled FP4" if use_packed else "ggml blobs in place + fp16 images + mma.sync",
                        launch="one CUDA graph per step (input copied into its static buffer, device to device)" if use_graph else "one host launch per kernel"),
         "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
-        "gpu_launches": 9 * args.steps,   # logits, select, plan, 2 x image prep, gate/up, down, combine (+0: the shared expert rides in the grouped call)
+        "gpu_launches": 8 * args.steps,   # logits, select, plan, 2 x activation images, gate/up, down, combine (the shared expert rides in the grouped call)
         "roofline": {"bound": "hbm", "kernel": ("nvf4_stream_kernel<gate/up>" if use_packed else "nvfp4_mma_kernel<gate/up>") + " (routed + shared experts; stage time includes the activation-image kernel)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
                      "algorithmic_bytes_per_launch": gu_bytes, "kernel_ms": gu_ms, "frac_of_nominal_8TBs": achieved / 8000.0},
