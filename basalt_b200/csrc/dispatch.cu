@@ -68,15 +68,43 @@ __device__ int block_excl_sum(int v, int* total, int* sh) {
     return r;
 }
 
+// Prompt-sized dispatches (hundreds of chunks): step (1) of dispatch_scan_kernel as its own launch, one warp per expert over
+// as many blocks as that takes; the totals go to cnt[].
+__global__ void __launch_bounds__(256)
+dispatch_rowscan_kernel(int E, int n_chunks, int32_t* __restrict__ tbl, int32_t* __restrict__ cnt) {
+    const int lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (e >= E) return;
+    int32_t* row = tbl + (size_t) e * n_chunks;
+    int carry = 0;
+    for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+        const int c = c0 + lane;
+        const int v = c < n_chunks ? row[c] : 0;
+        int x = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(kFull, x, o);
+            if (lane >= o) x += y;
+        }
+        if (c < n_chunks) row[c] = carry + x - v;
+        carry += __shfl_sync(kFull, x, 31);
+    }
+    if (lane == 0) cnt[e] = carry;
+}
+
 // one block of 1024 threads: (1) a warp per expert scans its chunk counts into exclusive chunk bases and the expert's
-// total; (2) a block scan over the experts gives off[], and the tile list.
+// total (skipped when dispatch_rowscan_kernel has done it: rows_done); (2) a block scan over the experts gives off[], and
+// the tile list.
 __global__ void __launch_bounds__(1024)
 dispatch_scan_kernel(int E, int n_chunks, int32_t* __restrict__ tbl, int32_t* __restrict__ cnt, int32_t* __restrict__ off,
-                     int tile_rows, int32_t* __restrict__ tiles, int32_t* __restrict__ n_tiles) {
+                     int tile_rows, int32_t* __restrict__ tiles, int32_t* __restrict__ n_tiles, int rows_done) {
     __shared__ int s_cnt[kMaxExpert];
     __shared__ int sh[32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int e = warp; e < E; e += nw) {
+    if (rows_done) {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = cnt[e];
+    }
+    for (int e = warp; e < E && !rows_done; e += nw) {
         int32_t* row = tbl + (size_t) e * n_chunks;
         int carry = 0;
         for (int c0 = 0; c0 < n_chunks; c0 += 32) {
@@ -341,8 +369,10 @@ extern "C" int32_t bsx_dispatch(const int32_t* ids, int64_t n_pairs, int32_t k, 
     const unsigned blocks = (unsigned) ((nc + kWarpsPerBlock - 1) / kWarpsPerBlock);
     const size_t smem = (size_t) kWarpsPerBlock * E * sizeof(int32_t);
     dispatch_count_kernel<<<blocks, kWarpsPerBlock * 32, smem, st>>>(ids, n_pairs, E, nc, tbl);
+    const int split = nc > 64 ? 1 : 0;     // many chunks: the per-expert scans get their own, wider launch
+    if (split) dispatch_rowscan_kernel<<<(unsigned) ((E + 7) / 8), 256, 0, st>>>(E, nc, tbl, cnt);
     dispatch_scan_kernel<<<1, 1024, 0, st>>>(E, nc, tbl, cnt, off, tile_rows, tile_rows > 0 ? tiles : nullptr,
-                                              tile_rows > 0 ? n_tiles : nullptr);
+                                              tile_rows > 0 ? n_tiles : nullptr, split);
     if (n_pairs > 0)
         dispatch_place_kernel<<<blocks, kWarpsPerBlock * 32, smem, st>>>(ids, n_pairs, k, E, nc, tbl, off, slot, src);
     return launch_status();
