@@ -66,6 +66,7 @@ _SIGNATURES = {
     "bsx_experts_prefill_scratch_bytes": (C.c_size_t, [C.POINTER(ExpertLayout), C.c_int64, C.c_int64]),
     "bsx_experts_prefill": (C.c_int32, [C.POINTER(ExpertLayout), P, P, P, P, P, C.c_int64, C.c_int64, P, C.c_int32, C.c_int64, P, P, P, P]),
     "bsx_plan_groups": (C.c_int32, [P, P, P, C.c_int32, P, P, P, P, P, P, P]),
+    "bsx_tiles_from_bounds": (C.c_int32, [P, C.c_int32, C.c_int32, P, P, P]),
     "bsx_plan_groups_shared": (C.c_int32, [P, P, P, C.c_int32, P, C.c_uint64, C.c_int32, C.c_int32, P, P, P, P, P, P]),
     "bsx_combine_partial": (C.c_int32, [P, P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, P]),
     "bsx_combine": (C.c_int32, [P, P, P, P, P, C.c_int32, C.c_int32, C.c_int32, P, P]),

@@ -392,6 +392,31 @@ static int32_t plan_launch(const int32_t* ids, int32_t T, int32_t k, int32_t E, 
     return launch_status();
 }
 
+// the tile list of a dispatch from its row bounds alone: one block, a scan over the experts' tile counts
+__global__ void __launch_bounds__(1024)
+tiles_from_bounds_kernel(const int32_t* __restrict__ off, int E, int tile_rows, int32_t* __restrict__ tiles, int32_t* __restrict__ n_tiles) {
+    __shared__ int sh[32];
+    const int e = threadIdx.x;
+    const int o = e < E ? off[e] : 0;
+    const int c = e < E ? off[e + 1] - o : 0;
+    const int nt = c > 0 ? (c + tile_rows - 1) / tile_rows : 0;
+    int total = 0;
+    const int to = block_excl_sum(nt, &total, sh);
+    for (int i = 0; i < nt; ++i) {
+        tiles[2 * (to + i)] = e;
+        tiles[2 * (to + i) + 1] = o + i * tile_rows;
+    }
+    if (e == 0) *n_tiles = total;
+}
+
+extern "C" int32_t bsx_tiles_from_bounds(const int32_t* off, int32_t E, int32_t tile_rows, int32_t* tiles, int32_t* n_tiles, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (E < 1 || E > kMaxExpert || tile_rows < 1) return BSX_E_GEOMETRY;
+    if (!off || !tiles || !n_tiles) return BSX_E_POINTER;
+    tiles_from_bounds_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(off, E, tile_rows, tiles, n_tiles);
+    return launch_status();
+}
+
 extern "C" int32_t bsx_plan_groups(const int32_t* cnt, const int32_t* off, const int32_t* src, int32_t E,
                                    const unsigned long long* blob_table, unsigned long long* ptr, int32_t* start, int32_t* n_groups,
                                    int32_t* ent_dst, int32_t* ent_tok, void* stream) {

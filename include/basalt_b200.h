@@ -248,6 +248,12 @@ BSX_API int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const unsig
                                     const int32_t* src, const int32_t* tiles, const int32_t* n_tiles, int64_t cap_tiles, int64_t cap_rows,
                                     const void* x, int32_t x_kind, int64_t n_tokens, void* scratch, float* dm, int32_t* status, void* stream);
 
+/* The tile list bsx_dispatch makes, from row bounds alone - for a caller that grouped its rows itself (Group::group(),
+ * src/models/qwen4exp/prefill/routing.cpp:67-108, fp4::plan_blocks, include/basalt/prefill/moe_fp4.hpp:38-41): off[E + 1]
+ * expert row bounds on the device -> tiles {expert, first row} per tile_rows rows of an expert, in expert order, and their
+ * count.  tiles must hold off[E] / tile_rows + E entries.  E <= 1024. */
+BSX_API int32_t bsx_tiles_from_bounds(const int32_t* off, int32_t E, int32_t tile_rows, int32_t* tiles, int32_t* n_tiles, void* stream);
+
 /* ---- a11 on the block-scaled FP4 tensor cores: bsx_experts_prefill over blobs packed by bsx_expert_pack (blob_table[e] = a
  * packed blob, 0 = held elsewhere).  Activations enter as four FP4 terms per row (x rows and the SwiGLU rows alike), so the
  * rows sit ~2e-4 from the dequantised fp32 reference; nothing is decoded on the way to the tensor core.  n_expert = the

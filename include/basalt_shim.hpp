@@ -168,6 +168,32 @@ inline void native_expert_grouped_clamped(const NativeExpertLayout& L, float swi
                           grid_groups);
 }
 
+/// The load-time plane packing (cf. include/basalt/kernels/nvfp4_planes.hpp:6-20) and native_expert_grouped over packed blobs:
+/// grp_ptr[g] points at a blob packed by native_expert_pack; x are fp32 (or, with x_bf16, bf16) activation rows - the packed
+/// path makes its own FP4 images, so no quantize_q8_1_rows.  status: a device int32 the caller zeroes (bit 0 = a bounded
+/// wait inside a kernel ran out).
+inline size_t native_expert_packed_bytes(const NativeExpertLayout& L) {
+    const bsx_expert_layout c = shim_detail::to_c(L);
+    return bsx_expert_packed_bytes(&c);
+}
+inline void native_expert_pack(const NativeExpertLayout& L, const void* blob, void* packed, void* stream) {
+    const bsx_expert_layout c = shim_detail::to_c(L);
+    shim_detail::raise("native_expert_pack", bsx_expert_pack(&c, blob, packed, stream));
+}
+inline size_t native_expert_packed_scratch_bytes(const NativeExpertLayout& L, int64_t cap_entries) {
+    const bsx_expert_layout c = shim_detail::to_c(L);
+    return bsx_experts_packed_scratch_bytes(&c, cap_entries);
+}
+inline void native_expert_grouped_packed(const NativeExpertLayout& L, const unsigned long long* grp_ptr, const int32_t* grp_start,
+                                         const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
+                                         int64_t cap_entries, const void* x, bool x_bf16, int n_x_rows, void* scratch, float* out,
+                                         int32_t* status, void* stream) {
+    const bsx_expert_layout c = shim_detail::to_c(L);
+    shim_detail::raise("native_expert_grouped_packed",
+                       bsx_experts_grouped_packed(&c, grp_ptr, grp_start, n_groups, ent_dst, ent_tok, cap_groups, cap_entries, x,
+                                                  x_bf16 ? BSX_X_BF16 : BSX_X_F32, n_x_rows, scratch, out, BSX_OUT_F32, status, stream));
+}
+
 inline size_t gated_mlp_scratch_bytes(int64_t cap_tok, int64_t n_ff) {
     bsx_expert_layout c{};
     c.n_embd = 8192;

@@ -64,3 +64,22 @@ def test_moe_plan_bit_exact(lib, cuda, T, k, E):
     assert np.array_equal(start.cpu().numpy()[:g + 2], ostart[:g + 2])
     n = int(ostart[g])
     assert np.array_equal(dst.cpu().numpy()[:n], odst[:n]) and np.array_equal(tok.cpu().numpy()[:n], otok[:n])
+
+
+def test_tiles_from_bounds_equals_the_dispatch_tile_list(lib, cuda):
+    """bsx_tiles_from_bounds on a dispatch's row bounds gives the tile list bsx_dispatch itself made."""
+    from basalt_b200 import capi, moe
+    rng = np.random.default_rng(3)
+    E, k, T = 40, 4, 700
+    ids = rng.integers(0, E, (T, k)).astype(np.int32)
+    ids[:, 0] = 7                                  # one hot expert: several tiles
+    ids[ids == 11] = 12                            # and an empty one
+    d = torch.from_numpy(ids.reshape(-1)).cuda()
+    cnt, off, slot, src, tiles, n_tiles = moe.dispatch(d, k, E, tile_rows=128)
+    tiles2 = torch.full_like(tiles, -1)
+    n2 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    capi.check("tiles", lib.bsx_tiles_from_bounds(off.data_ptr(), E, 128, tiles2.data_ptr(), n2.data_ptr(), moe._stream(None)))
+    torch.cuda.synchronize()
+    n = int(n_tiles.item())
+    assert int(n2.item()) == n and n > E - 2
+    assert torch.equal(tiles[:n], tiles2[:n])
