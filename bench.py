@@ -207,12 +207,17 @@ def main():
                     help="decode expert kernels: packed = blobs repacked at load into planes, block-scaled FP4 tensor cores (tcgen05 kind::mxf4nvf4); "
                          "fp16 = ggml blobs in place, fp16 activation images, mma.sync")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel of a step from the host instead of replaying the layer's CUDA graph")
+    ap.add_argument("--decode-tokens", type=int, default=T, help="tokens per decode step and GPU (the reference's decode configs: 1, 8, 64; the metric is quoted on 64)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: 64 tokens a step (the default line); prefill: --tokens rows a step, Zipf(1.1) expert popularity, tcgen05 grouped experts")
     ap.add_argument("--tokens", type=int, default=4096, help="rows per step of the prefill workload, per GPU (4096 or 16384 in the reference's configs)")
     ap.add_argument("--shape", default="c1", choices=sorted(SHAPES), help="layer of the prefill workload: c1 (H 2048, 512 experts) or c3 (H 7168, 256 experts)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.decode_tokens != T:
+        assert 1 <= args.decode_tokens <= 64
+        globals()["T"] = args.decode_tokens
+        CFG.update(workload=f"flash-next-style MoE layer decode, {args.decode_tokens} tokens/step", tokens_per_step=args.decode_tokens)
     if args.impl == "reference":
         return run_reference_arm(args)
 
@@ -323,7 +328,8 @@ def main():
         "vs_baseline": None,
         "dtype": ("NVFP4 weights x 4-term FP4 activations on tcgen05 kind::mxf4nvf4 (block-scaled), fp32 accumulation" if use_packed
                   else "fp16 x NVFP4 tensor-core products (mma.sync), fp32 accumulation"), "data": "synthetic",
-        "config": dict(CFG, l2_policy=f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB) and each step touches ~650 MB: larger than L2",
+        "config": dict(CFG, l2_policy=(f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB) and each step touches ~650 MB: larger than L2" if T == 64 else
+                                  f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB); use --copies so that copies x touched experts exceed the 126 MB L2"),
                        parallelism="single GPU" if world == 1 else f"ep{world}",
                        expert_kernels="packed planes + tcgen05 block-scaled FP4" if use_packed else "ggml blobs in place + fp16 images + mma.sync",
                        launch="one CUDA graph per step (input copied into its static buffer, device to device)" if use_graph else "one host launch per kernel"),
