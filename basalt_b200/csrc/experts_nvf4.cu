@@ -200,9 +200,9 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
     const int n_chunk = (int) (K >> 8);                                 // stages (256 columns) per unit
     constexpr int kRowsPerBlock = MODE == FMODE_GU ? 128 : 256;         // weight rows of the two tiles of one accumulator set
     const int n_rb = (int) ((R + kRowsPerBlock - 1) / kRowsPerBlock);
-    // a unit = one pass x n_sub consecutive row blocks, sized to at least 8 stages so that the per-unit bookkeeping (the
+    // a unit = one pass x n_sub consecutive row blocks, sized to at least 4 stages so that the per-unit bookkeeping (the
     // pass record, the entries' rows and scales) is amortised and its loads hide behind the stream
-    const int n_sub = max(1, min(n_rb, (8 + n_chunk - 1) / n_chunk));
+    const int n_sub = max(1, min(n_rb, (4 + n_chunk - 1) / n_chunk));
     const int n_upp = (n_rb + n_sub - 1) / n_sub;                        // units per pass
     const int n_units = sa.n_items[0] * n_upp;
     const PackedGeom geo = packed_geom(a.L.n_embd, a.L.n_ff);

@@ -336,7 +336,11 @@ def main():
         "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
         "gpu_launches": 8 * args.steps,   # logits, select, plan, 2 x activation images, gate/up, down, combine (the shared expert rides in the grouped call)
         "roofline": {"bound": "hbm", "kernel": ("nvf4_stream_kernel<gate/up>" if use_packed else "nvfp4_mma_kernel<gate/up>") + " (routed + shared experts; stage time includes the activation-image kernel)", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch of this workload at 64 tokens (seeded, so the
+                     # same experts every run), from the ncu captures summarised in profiles/nvf4_stream_kernel_c1_t64.md and
+                     # profiles/nvfp4_mma_kernel_c1_t64.md; not measured by this run
+                     "traffic": ((450646784 if use_packed else 451744256) if T == 64 else None), "traffic_source": "ncu capture (profiles/)",
                      "algorithmic_bytes_per_launch": gu_bytes, "kernel_ms": gu_ms, "frac_of_nominal_8TBs": achieved / 8000.0},
         "stage_ms": stage_ms,
         "clocks": clocks.summary(),
