@@ -38,6 +38,7 @@ _SIGNATURES = {
     "bsx_expert_packed_bytes": (C.c_size_t, [C.POINTER(ExpertLayout)]),
     "bsx_expert_pack": (C.c_int32, [C.POINTER(ExpertLayout), P, P, P]),
     "bsx_experts_packed_scratch_bytes": (C.c_size_t, [C.POINTER(ExpertLayout), C.c_int64]),
+    "bsx_experts_packed_x_images": (C.c_int32, [C.POINTER(ExpertLayout), P, C.c_int32, C.c_int32, C.c_int64, P, P]),
     "bsx_experts_grouped_packed": (C.c_int32, [C.POINTER(ExpertLayout), P, P, P, P, P, C.c_int64, C.c_int64, P, C.c_int32, C.c_int32, P, P, C.c_int32, P, P]),
     "bsx_router_logits_prefill_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
     "bsx_router_logits_prefill": (C.c_int32, [P, C.c_int32, P, C.c_int64, C.c_int32, C.c_int32, P, P, P, P]),

@@ -83,7 +83,7 @@ int32_t experts_grouped_simple(const ExpertArgs& a, cudaStream_t st);
 // returns BSX_E_TYPE when the fast path does not cover the layout (the caller then runs the plain kernels)
 int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st);
 // the same call over blobs repacked by bsx_expert_pack (experts_nvf4.cu): block-scaled FP4 MMAs straight on the NVFP4 codes
-int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st);
+int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st, bool x_images_ready);
 size_t experts_packed_scratch_bytes(int64_t cap_entries, int64_t n_embd, int64_t n_ff);
 size_t experts_mma_scratch_bytes(int64_t cap_entries, int64_t n_embd, int64_t n_ff);
 

@@ -160,6 +160,15 @@ __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __
     fp4_image_row<TPR>(FROM_H ? (const void*) a.h : a.x, FROM_H ? BSX_X_F32 : a.x_kind, row, K, live, i, codes, sfs, inv, shf);
 }
 
+// rows 0 .. n_rows - 1 of x alone (no plan needed): for a caller that makes the images beside the routing
+template <int TPR>
+__global__ void __launch_bounds__(256) x_images_kernel(const void* __restrict__ x, int kind, int n_rows, int64_t K, uint8_t* __restrict__ codes,
+                                                        uint8_t* __restrict__ sfs, float* __restrict__ inv) {
+    __shared__ float shf[8];
+    const int i = blockIdx.x * (256 / TPR) + (int) threadIdx.x / TPR;
+    fp4_image_row<TPR>(x, kind, i < n_rows ? i : 0, K, i < n_rows, i, codes, sfs, inv, shf);
+}
+
 template <bool FROM_H>
 void launch_prep(const ExpertArgs& a, int64_t rows, int64_t K, uint8_t* codes, uint8_t* sfs, float* inv, PassRec* items, int* n_items, cudaStream_t st) {
     const int64_t n_sb = K / 16;
@@ -469,26 +478,52 @@ size_t experts_packed_scratch_bytes(int64_t cap, int64_t H, int64_t I) {
            al256f((size_t) cap * kTermsF * I / 16) + 2 * al256f((size_t) cap * 4) + al256f((size_t) (cap + 1) * 16 + 16);
 }
 
-int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st) {
+// the scratch regions behind the SwiGLU buffer
+struct PackedScratch {
+    uint8_t *xcodes, *xsf, *hcodes, *hsf;
+    float *xinv, *hinv;
+    int* n_items;
+    PassRec* items;
+};
+static PackedScratch carve_scratch(void* scratch, int64_t cap, int64_t H, int64_t I) {
+    PackedScratch r;
+    uint8_t* p = static_cast<uint8_t*>(scratch) + al256f((size_t) cap * I * 4);
+    r.xcodes = p;
+    p += al256f((size_t) cap * kTermsF * H / 2);
+    r.xsf = p;
+    p += al256f((size_t) cap * kTermsF * H / 16);
+    r.hcodes = p;
+    p += al256f((size_t) cap * kTermsF * I / 2);
+    r.hsf = p;
+    p += al256f((size_t) cap * kTermsF * I / 16);
+    r.xinv = reinterpret_cast<float*>(p);
+    p += al256f((size_t) cap * 4);
+    r.hinv = reinterpret_cast<float*>(p);
+    p += al256f((size_t) cap * 4);
+    r.n_items = reinterpret_cast<int*>(p);
+    r.items = reinterpret_cast<PassRec*>(r.n_items + 4);
+    return r;
+}
+
+int32_t experts_packed_x_images(const bsx_expert_layout& L, const void* x, int32_t x_kind, int32_t n_x_rows, int64_t cap, void* scratch, cudaStream_t st) {
+    const PackedScratch sc = carve_scratch(scratch, cap, L.n_embd, L.n_ff);
+    const int64_t n_sb = L.n_embd / 16;
+    if (n_sb <= 32) x_images_kernel<32><<<(unsigned) ((n_x_rows + 7) / 8), 256, 0, st>>>(x, x_kind, n_x_rows, L.n_embd, sc.xcodes, sc.xsf, sc.xinv);
+    else if (n_sb <= 128) x_images_kernel<128><<<(unsigned) ((n_x_rows + 1) / 2), 256, 0, st>>>(x, x_kind, n_x_rows, L.n_embd, sc.xcodes, sc.xsf, sc.xinv);
+    else x_images_kernel<256><<<(unsigned) n_x_rows, 256, 0, st>>>(x, x_kind, n_x_rows, L.n_embd, sc.xcodes, sc.xsf, sc.xinv);
+    return launch_status();
+}
+
+int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st, bool x_images_ready) {
     const bsx_expert_layout& L = a.L;
     if (L.gu_type != kTypeNVFP4 || L.up_type != kTypeNVFP4 || L.d_type != kTypeNVFP4) return BSX_E_TYPE;
     if (L.n_embd % 256 || L.n_ff % 256) return BSX_E_TYPE;       // whole 256-column stages, whole 128-row tiles
     const int64_t cap = a.cap_entries, H = L.n_embd, I = L.n_ff;
-    uint8_t* p = reinterpret_cast<uint8_t*>(a.h) + al256f((size_t) cap * I * 4);
-    uint8_t* xcodes = p;
-    p += al256f((size_t) cap * kTermsF * H / 2);
-    uint8_t* xsf = p;
-    p += al256f((size_t) cap * kTermsF * H / 16);
-    uint8_t* hcodes = p;
-    p += al256f((size_t) cap * kTermsF * I / 2);
-    uint8_t* hsf = p;
-    p += al256f((size_t) cap * kTermsF * I / 16);
-    float* xinv = reinterpret_cast<float*>(p);
-    p += al256f((size_t) cap * 4);
-    float* hinv = reinterpret_cast<float*>(p);
-    p += al256f((size_t) cap * 4);
-    int* n_items = reinterpret_cast<int*>(p);
-    PassRec* items = reinterpret_cast<PassRec*>(n_items + 4);
+    const PackedScratch sc = carve_scratch(a.h, cap, H, I);
+    uint8_t *xcodes = sc.xcodes, *xsf = sc.xsf, *hcodes = sc.hcodes, *hsf = sc.hsf;
+    float *xinv = sc.xinv, *hinv = sc.hinv;
+    int* n_items = sc.n_items;
+    PassRec* items = sc.items;
     const int phase = experts_phase();
     const int64_t x_rows = a.n_x_rows > 0 ? a.n_x_rows : cap;
     StreamArgs sa;
@@ -498,7 +533,8 @@ int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_
     sa.status = status;
     int32_t rc = BSX_OK;
     if (phase != 2) {
-        launch_prep<false>(a, x_rows, H, xcodes, xsf, xinv, items, n_items, st);
+        if (x_images_ready) prep_fp4_kernel<false, 32><<<1, 256, 0, st>>>(a, xcodes, xsf, xinv, items, n_items);   // the pass list alone
+        else launch_prep<false>(a, x_rows, H, xcodes, xsf, xinv, items, n_items, st);
         sa.codes = xcodes;
         sa.sfs = xsf;
         sa.inv = xinv;
@@ -546,7 +582,13 @@ extern "C" int32_t bsx_experts_grouped_packed(const bsx_expert_layout* layout, c
     if (cap_groups < 0 || cap_entries < 0 || cap_entries > (int64_t) 1 << 30) return BSX_E_GEOMETRY;
     if (cap_groups == 0 || cap_entries == 0) return BSX_OK;
     if (!grp_ptr || !grp_start || !n_groups || !ent_dst || !ent_tok || !aligned(x, 16) || !aligned(scratch, 256) || !aligned(out, 16)) return BSX_E_POINTER;
-    if (n_x_rows < 0 || n_x_rows > cap_entries) n_x_rows = 0;
+    // n_x_rows < 0: the images of -n_x_rows rows of x are already in this scratch (bsx_experts_packed_x_images)
+    const bool ready = n_x_rows < 0;
+    if (ready) n_x_rows = -n_x_rows;
+    if (n_x_rows > cap_entries) {
+        if (ready) return BSX_E_GEOMETRY;
+        n_x_rows = 0;
+    }
     ExpertArgs a;
     a.L = *layout;
     a.grp_ptr = grp_ptr;
@@ -563,5 +605,15 @@ extern "C" int32_t bsx_experts_grouped_packed(const bsx_expert_layout* layout, c
     a.out_kind = out_kind;
     a.n_x_rows = n_x_rows;
     a.grid = nullptr;
-    return experts_grouped_packed(a, status, (cudaStream_t) stream);
+    return experts_grouped_packed(a, status, (cudaStream_t) stream, ready);
+}
+
+extern "C" int32_t bsx_experts_packed_x_images(const bsx_expert_layout* layout, const void* x, int32_t x_kind, int32_t n_x_rows, int64_t cap_entries,
+                                               void* scratch, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (!layout || !aligned(x, 16) || !aligned(scratch, 256)) return BSX_E_POINTER;
+    if (!bsx_expert_packed_bytes(layout)) return BSX_E_TYPE;
+    if (x_kind < BSX_X_F32 || x_kind > BSX_X_Q8_1 || n_x_rows < 0 || n_x_rows > cap_entries) return BSX_E_GEOMETRY;
+    if (n_x_rows == 0) return BSX_OK;
+    return experts_packed_x_images(*layout, x, x_kind, n_x_rows, cap_entries, scratch, (cudaStream_t) stream);
 }

@@ -241,8 +241,10 @@ class EPMoELayer:
             self.forward(self.x_static)
         return self
 
-    def forward_graphed(self, x):
-        self.x_static.copy_(x, non_blocking=True)
+    def forward_graphed(self, x=None):
+        """x may be a pinned host tensor; None: the caller has already written self.x_static."""
+        if x is not None:
+            self.x_static.copy_(x, non_blocking=True)
         self.graph.replay()
         return self.y
 

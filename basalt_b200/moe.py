@@ -314,6 +314,8 @@ class MoELayer:
             assert shared_blob is None or self.fused_shared, "the packed path takes the shared expert as one more group"
             self.scratch = torch.empty(capi.lib().bsx_experts_packed_scratch_bytes(C.byref(layout), rows), dtype=torch.uint8, device=dev)
             self.status = torch.zeros(1, dtype=i32, device=dev)
+            self.cap_rows = rows
+            self.side = torch.cuda.Stream(device=dev)      # the FP4 images of x need no routing: they run beside router and plan
         else:
             self.scratch = torch.empty(native_expert_scratch_bytes(layout, rows), dtype=torch.uint8, device=dev)
         self.y = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
@@ -332,9 +334,12 @@ class MoELayer:
         then costs one launch."""
         return _capture(self, x_example)
 
-    def forward_graphed(self, x: torch.Tensor) -> torch.Tensor:
-        """x [max_tokens][n_embd] of the captured dtype -> y (a view of an internal buffer), by replaying the graph."""
-        self.x_static.copy_(x, non_blocking=True)
+    def forward_graphed(self, x: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x [max_tokens][n_embd] of the captured dtype -> y (a view of an internal buffer), by replaying the graph.  x may be
+        a pinned host tensor (it is copied straight into the graph's input buffer); None: the caller has already written
+        self.x_static."""
+        if x is not None:
+            self.x_static.copy_(x, non_blocking=True)
         self.graph.replay()
         return self.y
 
@@ -346,6 +351,13 @@ class MoELayer:
         assert T <= self.max_tokens
         xr = x_router if x_router is not None else x     # fp32 or bf16 rows; bf16 is widened exactly inside the kernel
         hp, hn, keep = _held(a)
+        images_ahead = self.packed and self.fused_shared
+        if images_ahead:
+            # fork: the activation images on the side stream while the router and the plan run on this one (joined before the experts)
+            cur = stream if stream is not None else torch.cuda.current_stream()
+            self.side.wait_stream(cur)
+            check("bsx_experts_packed_x_images", lib.bsx_experts_packed_x_images(C.byref(self.L), _p(x), _x_kind(x), T, T * a.k + T, _p(self.scratch),
+                                                                                 _stream(self.side)))
         check("bsx_router", lib.bsx_router_x(_p(xr), X_BF16 if xr.dtype == torch.bfloat16 else X_F32, _p(self.gate_w), _p(self.bias), T,
                                               a.n_expert, a.n_embd, a.k, a.gate, a.weight_scale, a.n_group, a.topk_group, a.prior, hp, hn,
                                               _p(self.logits), _p(self.ids), _p(self.w), st))
@@ -355,10 +367,13 @@ class MoELayer:
         if self.fused_shared:
             check("bsx_moe_plan_shared", lib.bsx_moe_plan_shared(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), self.shared_blob.data_ptr(),
                                                                  _p(self.ptr), _p(self.start), _p(self.n_groups), _p(self.dst), _p(self.tok), st))
+            if images_ahead:
+                cur.wait_stream(self.side)       # join
             if self.packed:
                 check("bsx_experts_grouped_packed", lib.bsx_experts_grouped_packed(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
-                                                                                   _p(self.dst), _p(self.tok), min(n, a.n_expert) + 1, n + T, _p(x), kind, T,
-                                                                                   _p(self.scratch), _p(self.rows), OUT_F32, _p(self.status), st))
+                                                                                   _p(self.dst), _p(self.tok), min(n, a.n_expert) + 1, n + T, _p(x), kind,
+                                                                                   -T if images_ahead else T, _p(self.scratch), _p(self.rows), OUT_F32,
+                                                                                   _p(self.status), st))
             else:
                 check("bsx_experts_grouped", lib.bsx_experts_grouped_rows(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),
                                                                           _p(self.dst), _p(self.tok), min(n, a.n_expert) + 1, n + T, _p(x), kind, T,

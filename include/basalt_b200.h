@@ -226,6 +226,11 @@ BSX_API int32_t bsx_gated_mlp(const bsx_expert_layout* layout, const void* blob,
 BSX_API size_t bsx_expert_packed_bytes(const bsx_expert_layout* layout);
 BSX_API int32_t bsx_expert_pack(const bsx_expert_layout* layout, const void* blob, void* packed, void* stream);
 BSX_API size_t bsx_experts_packed_scratch_bytes(const bsx_expert_layout* layout, int64_t cap_entries);
+/* The x images of bsx_experts_grouped_packed made ahead of the call - they need only x, not the routing, so a caller can run
+ * them on another stream beside router and plan: rows 0 .. n_x_rows - 1 of x into `scratch` (the same scratch and
+ * cap_entries the grouped call will get).  The grouped call is then told so by a NEGATIVE n_x_rows (-n_x_rows). */
+BSX_API int32_t bsx_experts_packed_x_images(const bsx_expert_layout* layout, const void* x, int32_t x_kind, int32_t n_x_rows, int64_t cap_entries,
+                                            void* scratch, void* stream);
 BSX_API int32_t bsx_experts_grouped_packed(const bsx_expert_layout* layout, const unsigned long long* grp_ptr, const int32_t* grp_start,
                                            const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
                                            int64_t cap_entries, const void* x, int32_t x_kind, int32_t n_x_rows, void* scratch, void* out,
