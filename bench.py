@@ -214,10 +214,16 @@ def main():
     ap.add_argument("--shape", default="c1", choices=sorted(SHAPES), help="layer of the prefill workload: c1 (H 2048, 512 experts) or c3 (H 7168, 256 experts)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload == "decode" and args.shape != "c1":
+        # the decode step on another layer shape (c3: the v4-flash / DeepSeek-style layer); the default line stays c1
+        sh = SHAPES[args.shape]
+        globals().update(H=sh["H"], E=sh["E"], I=sh["I"], K_TOP=sh["k"])
+        CFG.update(workload=f"{sh['name']} decode, {T} tokens/step", hidden=sh["H"], n_expert=sh["E"], intermediate=sh["I"], top_k=sh["k"],
+                   router=f"{sh['gate']} + bias, {sh['n_group']} groups keep {sh['topk_group']}, top-{sh['k']}, x {sh['scale']}" if sh["bias"] else sh["gate"])
     if args.decode_tokens != T:
         assert 1 <= args.decode_tokens <= 64
         globals()["T"] = args.decode_tokens
-        CFG.update(workload=f"flash-next-style MoE layer decode, {args.decode_tokens} tokens/step", tokens_per_step=args.decode_tokens)
+        CFG.update(workload=CFG["workload"].replace("64 tokens/step", f"{args.decode_tokens} tokens/step"), tokens_per_step=args.decode_tokens)
     if args.impl == "reference":
         return run_reference_arm(args)
 
@@ -242,19 +248,24 @@ def main():
     if world > 1:
         return run_expert_parallel(args, rank, world, dev)
 
-    gate, blobs, blob_bytes = make_layer_weights(dev)
+    sh = SHAPES[args.shape]
+    gate, blobs, blob_bytes = make_layer_weights(dev, E=E, H=H, I=I, first=0, count=E + 1) if args.shape != "c1" else make_layer_weights(dev)
     L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
     assert L.bytes == blob_bytes
-    rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
+    rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=sh["scale"], gate=capi.GATE_SOFTMAX if sh["gate"] == "softmax" else capi.GATE_SIGMOID,
+                           n_group=sh["n_group"], topk_group=sh["topk_group"])
+    bias = (torch.randn(E, generator=torch.Generator(device=dev).manual_seed(7), device=dev) * 0.01).float() if sh["bias"] else None
     layers = []
     use_packed = args.experts == "packed"
     if use_packed:
         blobs_ggml = blobs
         blobs = moe.pack_experts(L, blobs_ggml)       # the load-time step: the same bytes in plane order
         torch.cuda.synchronize()
+        if args.shape != "c1":
+            del blobs_ggml
     for c in range(args.copies):
         b = blobs if c == 0 else blobs.clone()
-        layers.append(moe.MoELayer(gate if c == 0 else gate.clone(), None, b[:E], L, rargs, shared_blob=b[E], max_tokens=T, packed=use_packed))
+        layers.append(moe.MoELayer(gate if c == 0 else gate.clone(), bias, b[:E], L, rargs, shared_blob=b[E], max_tokens=T, packed=use_packed))
     n_batches = 8
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     xs = [torch.randn((T, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
@@ -334,7 +345,7 @@ def main():
         "vs_baseline": None,
         "dtype": ("NVFP4 weights x 4-term FP4 activations on tcgen05 kind::mxf4nvf4 (block-scaled), fp32 accumulation" if use_packed
                   else "fp16 x NVFP4 tensor-core products (mma.sync), fp32 accumulation"), "data": "synthetic",
-        "config": dict(CFG, l2_policy=(f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB) and each step touches ~650 MB: larger than L2" if T == 64 else
+        "config": dict(CFG, l2_policy=(f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB) and each step touches ~650 MB: larger than L2" if (T == 64 and args.shape == "c1") else
                                   f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB); use --copies so that copies x touched experts exceed the 126 MB L2"),
                        parallelism="single GPU" if world == 1 else f"ep{world}",
                        expert_kernels="packed planes + tcgen05 block-scaled FP4" if use_packed else "ggml blobs in place + fp16 images + mma.sync",
@@ -346,12 +357,12 @@ def main():
                      # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch of this workload at 64 tokens (seeded, so the
                      # same experts every run), from the ncu captures summarised in profiles/nvf4_stream_kernel_c1_t64.md and
                      # profiles/nvfp4_mma_kernel_c1_t64.md; not measured by this run
-                     "traffic": ((450646784 if use_packed else 451744256) if T == 64 else None), "traffic_source": "ncu capture (profiles/)",
+                     "traffic": ((450646784 if use_packed else 451744256) if (T == 64 and args.shape == "c1") else None), "traffic_source": "ncu capture (profiles/)",
                      "algorithmic_bytes_per_launch": gu_bytes, "kernel_ms": gu_ms, "frac_of_nominal_8TBs": achieved / 8000.0},
         "stage_ms": stage_ms,
         "clocks": clocks.summary(),
     }
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and args.shape == "c1":
         try:
             gate_h, blobs_h = gate.cpu().numpy(), (blobs_ggml if use_packed else blobs).cpu().numpy()
             xh = [x.float().cpu().numpy() for x in xs[:4]]
@@ -629,7 +640,7 @@ def instrumented_pass(layers, xs, xr, stream, steps, L):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         n = T * a.k
         ev[0].record(stream)
-        capi.check("router", lib.bsx_router_x(_p(x), _x_kind(x), _p(ly.gate_w), None, T, a.n_expert, a.n_embd, a.k, a.gate, a.weight_scale, 1, 1, 0.0,
+        capi.check("router", lib.bsx_router_x(_p(x), _x_kind(x), _p(ly.gate_w), _p(ly.bias), T, a.n_expert, a.n_embd, a.k, a.gate, a.weight_scale, a.n_group, a.topk_group, 0.0,
                                               None, 0, _p(ly.logits), _p(ly.ids), _p(ly.w), st))
         ev[1].record(stream)
         capi.check("plan", lib.bsx_moe_plan_shared(_p(ly.ids), T, a.k, a.n_expert, _p(ly.blob_table), ly.shared_blob.data_ptr(), _p(ly.ptr), _p(ly.start),
