@@ -56,7 +56,35 @@ SHAPES = {
     # v4-flash-style layer: sigmoid + bias, 8 groups keep 4, top-8 of 256 + 1 shared, weights x 2.5
     "c3": dict(H=7168, E=256, I=2048, k=8, gate="sigmoid", n_group=8, topk_group=4, scale=2.5, bias=True, zipf=False,
                name="v4-flash-style MoE layer"),
+    # the c3 layer with IQ1_M routed experts and a Q6_K shared expert (decode only; random valid blocks)
+    "c4": dict(H=7168, E=256, I=2048, k=8, gate="sigmoid", n_group=8, topk_group=4, scale=2.5, bias=True, zipf=False,
+               name="v4-flash-style MoE layer, IQ1_M routed + Q6_K shared experts", routed_type=29, shared_type=14),
 }
+
+
+def random_codebook_blobs(device, type_id, n, H_, I_, seed):
+    """n expert blobs of random valid blocks of a ggml K/IQ format - uniform over the valid codes, as the reference's own
+    tests make IQ1_M weights (it has no quantiser for that format: tests/kernels/iq1s_parity.cpp:65-93).  IQ1_M (56 bytes per
+    256 values): random bytes with a finite fp16 super-scale in [2^-7, 2^-6) in the top nibbles of the four scale words.
+    Q6_K (210 bytes per 256 values): random ql / qh, int8 scales in [-32, 31], fp16 d = 2^-12."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    bb = 56 if type_id == 29 else 210
+    nb = 3 * I_ * H_ // 256
+    raw = torch.randint(0, 256, (n, nb, bb), generator=g, device=device, dtype=torch.int16)
+    if type_id == 29:
+        d = 0x2000 + torch.randint(0, 0x400, (n, nb), generator=g, device=device, dtype=torch.int32)
+        for j in range(4):                     # scale word j (bytes 48 + 2 j, 49 + 2 j): its top nibble = nibble j of d
+            raw[:, :, 49 + 2 * j] = (raw[:, :, 49 + 2 * j] & 0x0F) | ((((d >> (4 * j)) & 0xF) << 4).to(torch.int16))
+    else:
+        raw[:, :, 192:208] = (raw[:, :, 192:208] & 0x3F) - 32          # int8 scales
+        raw[:, :, 192:208] = raw[:, :, 192:208] & 0xFF
+        raw[:, :, 208] = 0x00
+        raw[:, :, 209] = 0x0C                                           # fp16 0x0C00 = 2^-12
+    blob_bytes = nb * bb
+    stride = (blob_bytes + 15) // 16 * 16
+    out = torch.zeros((n, stride), dtype=torch.uint8, device=device)
+    out[:, :blob_bytes] = raw.to(torch.uint8).reshape(n, -1)
+    return out, blob_bytes
 
 
 def make_layer_weights(device, seed=0, E=E, H=H, I=I, first=0, count=None):
@@ -249,6 +277,8 @@ def main():
         return run_expert_parallel(args, rank, world, dev)
 
     sh = SHAPES[args.shape]
+    if "routed_type" in sh:
+        return run_decode_codebook(args, dev, sh)
     gate, blobs, blob_bytes = make_layer_weights(dev, E=E, H=H, I=I, first=0, count=E + 1) if args.shape != "c1" else make_layer_weights(dev)
     L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
     assert L.bytes == blob_bytes
@@ -478,6 +508,70 @@ def run_expert_parallel(args, rank, world, dev):
         "roofline": {"bound": "hbm", "kernel": "rank 0's local grouped experts (image prep, gate/up, down)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None, "algorithmic_bytes_per_launch": k_bytes,
                      "kernel_ms": k_ms},
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+
+
+def run_decode_codebook(args, dev, sh):
+    """The decode step with K/IQ-format experts (configs[4]'s layer on one GPU): IQ1_M routed experts and a Q6_K shared
+    expert, both read in place by the plain kernels (one warp per weight row, fp32 FMA) - the formats have no tensor-core
+    path yet.  Reported: tokens/s and the bytes of the touched blobs over the expert stage's time."""
+    from basalt_b200 import capi, moe
+    rt, st_ = sh["routed_type"], sh["shared_type"]
+    gate = (torch.randn((E, H), generator=torch.Generator(device=dev).manual_seed(0), device=dev) * 0.02).float()
+    bias = (torch.randn(E, generator=torch.Generator(device=dev).manual_seed(7), device=dev) * 0.01).float()
+    blobs, rb = random_codebook_blobs(dev, rt, E, H, I, 11)
+    shared, sb = random_codebook_blobs(dev, st_, 1, H, I, 12)
+    L = moe.native_expert_layout(rt, rt, H, I)
+    Ls = moe.native_expert_layout(st_, st_, H, I)
+    assert L.bytes == rb and Ls.bytes == sb
+    rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=sh["scale"], gate=capi.GATE_SIGMOID, n_group=sh["n_group"],
+                           topk_group=sh["topk_group"])
+    layers = [moe.MoELayer(gate, bias, blobs if c == 0 else blobs.clone(), L, rargs, shared_blob=(shared if c == 0 else shared.clone())[0],
+                           shared_layout=Ls, max_tokens=T) for c in range(args.copies)]
+    g = torch.Generator(device=dev).manual_seed(1)
+    xs = [torch.randn((T, H), generator=g, device=dev).bfloat16() for _ in range(4)]
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup):
+            layers[i % args.copies].forward(xs[i % 4], None, stream)
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(dev.index or 0) as clocks:
+            ev0.record(stream)
+            for i in range(args.steps):
+                layers[i % args.copies].forward(xs[i % 4], None, stream)
+            ev1.record(stream)
+            torch.cuda.synchronize()
+        ms_step = ev0.elapsed_time(ev1) / args.steps
+        x_host = [x.cpu().pin_memory() for x in xs]
+        xin = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        y_host = torch.empty((T, H), dtype=torch.float32).pin_memory()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(args.steps):
+            xin.copy_(x_host[i % 4], non_blocking=True)
+            y_host.copy_(layers[i % args.copies].forward(xin, None, stream), non_blocking=True)
+            stream.synchronize()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms_e2e = e0.elapsed_time(e1) / args.steps
+        touched = sum(int(torch.unique(layers[0].ids[:T]).numel()) for _ in range(1))
+    peak, peak_src = measured_peaks()
+    bytes_step = touched * rb + sb
+    line = {
+        "metric": "MoE-layer tokens/s (decode)", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32 FMA on weights decoded in registers (IQ1_M codebook, Q6_K)", "data": "synthetic (random valid blocks)",
+        "config": dict(workload=f"{sh['name']} decode, {T} tokens/step", hidden=H, n_expert=E, n_shared=1, intermediate=I, top_k=K_TOP,
+                       expert_format="IQ1_M routed (56 B / 256 values), Q6_K shared (210 B / 256 values)", activations="bf16", tokens_per_step=T,
+                       l2_policy=f"weights cycle through {args.copies} layer copies; a step touches {bytes_step / 1e9:.2f} GB", parallelism="single GPU",
+                       expert_kernels="ggml blobs in place, plain kernels (experts_simple.cu)"),
+        "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
+        "gpu_launches": 12 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "whole step (the expert kernels dominate)", "achieved": bytes_step / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": bytes_step / (ms_step * 1e-3) / 1e9 / peak, "peak_source": peak_src, "traffic": None, "algorithmic_bytes_per_launch": bytes_step},
         "clocks": clocks.summary(),
     }
     print(json.dumps(line))
