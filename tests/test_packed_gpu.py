@@ -66,7 +66,7 @@ def test_pack_is_the_ggml_bytes_in_plane_order(lib, cuda, H, I):
         assert np.array_equal(got, want)
 
 
-def run_packed(L, packed, group_experts, group_tokens, x_dev, n_x_rows=0):
+def run_packed(L, packed, group_experts, group_tokens, x_dev, n_x_rows=0, out_dtype=torch.float32):
     stride = packed.shape[1]
     ptr = torch.tensor([packed.data_ptr() + e * stride for e in group_experts] + [0], dtype=torch.int64).cuda()
     starts = np.concatenate([[0], np.cumsum([len(t) for t in group_tokens])]).astype(np.int32)
@@ -75,13 +75,64 @@ def run_packed(L, packed, group_experts, group_tokens, x_dev, n_x_rows=0):
     tok = dev(np.concatenate([np.asarray(t, np.int32) for t in group_tokens] + [np.zeros(1, np.int32)])[:max(n, 1)].astype(np.int32))
     dst = dev(np.arange(max(n, 1), dtype=np.int32))
     ng = dev(np.array([len(group_experts)], np.int32))
-    out = torch.full((max(n, 1), L.n_embd), float("nan"), dtype=torch.float32, device="cuda")
+    out = torch.full((max(n, 1), L.n_embd), float("nan"), dtype=out_dtype, device="cuda")
     scratch = torch.empty(capi.lib().bsx_experts_packed_scratch_bytes(C.byref(L), max(n, 1)), dtype=torch.uint8, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     moe.native_expert_grouped_packed(L, ptr, start, ng, dst, tok, len(group_experts), n, x_dev, scratch, out, status, n_x_rows=n_x_rows)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "a bounded wait inside the kernel gave up"
-    return out.cpu().numpy()
+    return out.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("kind", ["q8_1", "bf16_out", "limit"])
+def test_packed_activation_output_and_swiglu_kinds(lib, cuda, kind):
+    """The packed path with the reference's q8_1 activation rows (decoded as d * q), bf16 output rows, and the limited SwiGLU."""
+    rng = np.random.default_rng(98)
+    H, I, E, T = 2048, 512, 4, 9
+    Lo, blobs = make_expert_blobs(rng, E, 40, 40, H, I, sigma=0.2 if kind == "limit" else 0.02)
+    L = moe.native_expert_layout(40, 40, H, I, swiglu_limit=3.0 if kind == "limit" else 0.0)
+    packed = moe.pack_experts(L, dev(stack_blobs(blobs)))
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    group_tokens = [[0, 3], [1], [2, 4, 5, 6, 7, 8, 0, 1, 2], []]
+    xt = torch.from_numpy(x).cuda()
+    if kind == "q8_1":
+        xd = moe.quantize_q8_1_rows(xt)
+        q = xd.cpu().numpy().reshape(-1, 36)
+        x_eff = (q[:, 4:].view(np.int8).astype(np.float32) * q[:, :2].copy().view(np.float16).astype(np.float32)).reshape(T, H)
+    else:
+        xd = xt.bfloat16()
+        x_eff = xd.float().cpu().numpy()
+    out = run_packed(L, packed, list(range(E)), group_tokens, xd, out_dtype=torch.bfloat16 if kind == "bf16_out" else torch.float32)
+    at = 0
+    for e, toks in enumerate(group_tokens):
+        if toks:
+            want = O.expert_forward(Lo, blobs[e], x_eff[toks], limit=3.0 if kind == "limit" else 0.0)
+            tol = 4e-3 if kind == "bf16_out" else TOL                      # bf16 output rounding alone is ~1.7e-3
+            assert rel_l2(out[at:at + len(toks)], want) < tol, (kind, e, rel_l2(out[at:at + len(toks)], want))
+            if kind == "limit":
+                assert rel_l2(out[at:at + len(toks)], O.expert_forward(Lo, blobs[e], x_eff[toks])) > 1e-2   # the limit bites
+        at += len(toks)
+
+
+def test_packed_call_with_no_groups_returns_cleanly(lib, cuda):
+    """A plan without groups (every expert held elsewhere): the kernels start, find no work and return; nothing is written."""
+    rng = np.random.default_rng(97)
+    H, I = 512, 256
+    Lo, blobs = make_expert_blobs(rng, 1, 40, 40, H, I)
+    L = moe.native_expert_layout(40, 40, H, I)
+    packed = moe.pack_experts(L, dev(stack_blobs(blobs)))
+    ptr = torch.zeros(4, dtype=torch.int64, device="cuda")
+    start = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ng = torch.zeros(1, dtype=torch.int32, device="cuda")
+    idx = torch.zeros(8, dtype=torch.int32, device="cuda")
+    x = torch.randn((4, H), device="cuda")
+    out = torch.full((8, H), 7.0, dtype=torch.float32, device="cuda")
+    scratch = torch.empty(capi.lib().bsx_experts_packed_scratch_bytes(C.byref(L), 8), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    moe.native_expert_grouped_packed(L, ptr, start, ng, idx, idx, 2, 8, x, scratch, out, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and bool((out == 7.0).all())
+    del packed
 
 
 @pytest.mark.parametrize("H,I,xdt,rows_known", [(512, 256, "f32", False), (2048, 512, "bf16", True), (2048, 512, "f32", False), (7168, 2048, "bf16", True)])
