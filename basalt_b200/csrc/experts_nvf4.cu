@@ -9,8 +9,9 @@
 //    sub-block, which the activation side simply shares.  ggml's decode (value = doubled-E2M1 x scale / 2,
 //    src/kernels/cpu/ggml/ggml_quants.c:1397-1422) equals E2M1 x UE4M3, the product the hardware forms.
 //  * The only thing in the way is the layout: ggml interleaves 4 scale bytes with 32 code bytes (36-byte blocks), which
-//    no 16-byte copy can split.  bsx_expert_pack rewrites a blob once, at load time, into planes (codes row-major; scales
-//    in the 32-lane x 4-word order tcgen05.cp wants), the same bytes in another order - Basalt does the like for its own
+//    no 16-byte copy can split.  bsx_expert_pack rewrites a blob once, at load time, into 18 KB blocks (the codes of 128 rows x
+//    256 columns as the swizzled image of a stage, then their scales in the 32-lane x 4-word order tcgen05.cp wants:
+//    nvf4.cuh), the same bytes in another order - Basalt does the like for its own
 //    FP4 kernels (include/basalt/kernels/nvfp4_planes.hpp:6-20).
 //  * Activations must be FP4 too.  One FP4 term is worth ~3.3 bits, far from the 2e-3 bar; so a row goes in as FOUR terms
 //    (each term quantises the residual the terms before it left, with its own block scales): relative error ~1e-4.  The
@@ -47,7 +48,7 @@ constexpr int kSFTile = 4 * 512;           // 4 K-steps x (32 lanes x 4 words)
 // a stage: [tile 0 codes | tile 0 scales | tile 1 codes | tile 1 scales | activation codes | activation scales]
 constexpr int kOffSFA0 = kATile, kOffA1 = kATile + kSFTile, kOffSFA1 = kOffA1 + kATile, kOffB = kOffSFA1 + kSFTile, kOffSFB = kOffB + kBTile;
 constexpr int kStageF = kOffSFB + kSFTile;             // 43,008 bytes
-constexpr int kThreadsF = 32 * 7;                      // MMA warp, two loader warps, four epilogue warps
+constexpr int kThreadsF = 32 * 7;                      // MMA warp, weight loader warp, activation loader warp, four epilogue warps
 constexpr size_t kSmemF = 1024 + (size_t) kStagesF * kStageF + 256;
 // tensor-memory columns: two accumulator sets of (D0, D1) x 32 columns, then per stage 16 columns each for SFA0, SFA1, SFB
 constexpr uint32_t kTmemSF = 128, kTmemCols = 512;

@@ -15,8 +15,9 @@
 //   down:    N = 128 (one packed block), two accumulators, so the epilogue of one item overlaps the next item's stream.
 // Warp 0: per K-step the scale copies (tcgen05.cp shared -> tensor memory) and the four MMAs (M = 128 rows); warp 1: the
 // weights (one lane, bulk copies, completion in bytes); warps 2-5: the tile's activation rows - codes by 16-byte cp.async
-// gathers into four swizzled A tiles, scale words by 4-byte copies into the lane-major order tcgen05.cp reads; warps 6-9:
+// gathers into four swizzled A tiles, scale words through registers into the lane-major order tcgen05.cp reads; warps 6-9:
 // epilogue (thread = TMEM lane = row).  Two stages of 256 columns; every wait is time-bounded with a status word.
+// With n_ff <= 512 the down product runs as prefill_down_resident_kernel instead (the tile's rows stay in shared memory).
 #include <cuda_fp16.h>
 
 #include "common.cuh"
