@@ -26,6 +26,16 @@ class ExpertLayout(C.Structure):
                 ("swiglu_limit", C.c_float), ("gate_softcap", C.c_float), ("up_softcap", C.c_float), ("reserved_f", C.c_float)]
 
 
+class LayoutRow(C.Structure):
+    _fields_ = [("gu_type", C.c_int32), ("d_type", C.c_int32), ("up_type", C.c_int32), ("kernels", C.c_int32),
+                ("offset", C.c_uint64), ("blob_bytes", C.c_uint64)]
+
+
+class LayoutInfo(C.Structure):
+    _fields_ = [("version", C.c_int32), ("reserved", C.c_int32), ("n_layers", C.c_int64), ("n_expert", C.c_int64),
+                ("max_blob", C.c_uint64), ("total", C.c_uint64)]
+
+
 P = C.c_void_p
 _SIGNATURES = {
     "bsx_router_logits": (C.c_int32, [P, P, C.c_int32, C.c_int32, C.c_int32, P, P]),
@@ -71,6 +81,7 @@ _SIGNATURES = {
     "bsx_plan_groups_shared": (C.c_int32, [P, P, P, C.c_int32, P, C.c_uint64, C.c_int32, C.c_int32, P, P, P, P, P, P]),
     "bsx_combine_partial": (C.c_int32, [P, P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, P]),
     "bsx_combine": (C.c_int32, [P, P, P, P, P, C.c_int32, C.c_int32, C.c_int32, P, P]),
+    "bsx_layout_parse": (C.c_int32, [C.c_char_p, C.c_size_t, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float, P, P, C.c_char_p, C.c_size_t]),
     "bsx_host_decode_row": (C.c_int32, [C.c_int32, P, P, C.c_int64]),
     "bsx_row_bytes": (C.c_size_t, [C.c_int32, C.c_int64]),
     "bsx_version": (C.c_char_p, []),

@@ -295,6 +295,29 @@ BSX_API int32_t bsx_plan_groups_shared(const int32_t* cnt, const int32_t* off, c
 BSX_API int32_t bsx_combine_partial(const float* rows, const int32_t* slot, const float* weights, const int32_t* ids, int32_t e_lo,
                                     int32_t e_hi, int32_t T, int32_t k, int32_t H, float* y, void* stream);
 
+/* ---- the model file's `experts.layout` text (host only): which ggml types each layer's expert blobs have, how large a blob is
+ * and where the layer's n_expert blobs start inside the `experts` section.  Replaces expert_layout_load_text / ExpertLayout
+ * (include/basalt/kernels/cpu/expert_layout.hpp:17-35,60-67; src/kernels/cpu/expert_layout.cpp:133-203) with the same rules:
+ * a "# experts vN: ... (n_expert E, total B)" header (a version above 7 is refused; E replaces the caller's n_expert), one
+ * "layer gu_type d_type offset blob_bytes [up_type from v7]" line per layer, further columns ignored, blob_bytes checked
+ * against the formats' geometry at (n_embd, n_ff), layers contiguous from offset 0.  rows: n_layers entries, filled by layer
+ * id.  Every ggml format the reference's loader takes parses (its block geometry is known here), also those this library
+ * has no kernels for yet: rows[l].kernels says which layers can run.  err (may be null): the reason in words.  Returns
+ * BSX_OK, or BSX_E_TYPE (newer version, a type without a dot product, a gate / up / down mix the loader refuses) /
+ * BSX_E_GEOMETRY (empty text, malformed line, rows that are not whole blocks, size mismatch, a missing layer). */
+typedef struct bsx_layout_row {
+    int32_t gu_type, d_type, up_type;
+    int32_t kernels;                 /* 1: this library has kernels for the layer's formats (bsx_expert_supported) */
+    uint64_t offset, blob_bytes;     /* of the layer's first blob inside the experts section; bytes per blob */
+} bsx_layout_row;
+typedef struct bsx_layout_info {
+    int32_t version, reserved;       /* the header's version (0: none given) */
+    int64_t n_layers, n_expert;
+    uint64_t max_blob, total;        /* the largest blob; the experts section's size */
+} bsx_layout_info;
+BSX_API int32_t bsx_layout_parse(const char* text, size_t len, int64_t n_layers, int64_t n_expert, int64_t n_embd, int64_t n_ff,
+                                 float swiglu_limit, bsx_layout_row* rows, bsx_layout_info* info, char* err, size_t err_cap);
+
 /* ---- device self-check helpers (host-side; no GPU needed): the block decoders compiled for the host, for tests. */
 BSX_API int32_t bsx_host_decode_row(int32_t type, const void* row, float* y, int64_t n);
 BSX_API size_t bsx_row_bytes(int32_t type, int64_t n);

@@ -17,6 +17,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "basalt_b200.h"
 
@@ -241,3 +242,62 @@ inline void moe_combine(const float* Dm, const int32_t* slot, const float* w, co
     basalt::kernels::shim_detail::raise("moe_combine", bsx_combine(Dm, slot, w, shared, sg, (int32_t) T, k, n_embd, bo, stream));
 }
 }  // namespace basalt::prefill
+
+// The model file's expert table (include/basalt/kernels/cpu/expert_layout.hpp:17-35,53-65): the same struct fields a caller
+// reads (fmt holds the kernel-side layout in place of the CPU pool's NativeFmt), the same process-wide table filled by
+// expert_layout_load_text, the same bool + err contract.
+namespace basalt::kernels::cpu {
+struct ExpertLayout {
+    bool native = false;
+    int64_t n_layers = 0, n_expert = 0;
+    std::vector<basalt::kernels::NativeExpertLayout> fmt;   ///< per layer
+    std::vector<uint64_t> offset, bytes;                   ///< per layer: where its blobs start, bytes per blob
+    int version = 0;
+    uint64_t max_blob = 0;
+    uint64_t total = 0;
+
+    uint64_t blob_bytes(int64_t layer) const { return bytes[(size_t) layer]; }
+    uint64_t layer_offset(int64_t layer) const { return offset[(size_t) layer]; }
+    uint64_t blob_offset(int64_t layer, int64_t expert) const { return layer_offset(layer) + (uint64_t) expert * blob_bytes(layer); }
+};
+
+inline constexpr int kExpertLayoutVersion = 7;
+
+namespace shim_detail {
+inline ExpertLayout& table() {
+    static ExpertLayout g;
+    return g;
+}
+}  // namespace shim_detail
+
+inline const ExpertLayout& expert_layout() { return shim_detail::table(); }
+
+inline bool expert_layout_load_text(const std::string& text, int64_t n_layers, int64_t n_expert, std::string& err, int64_t n_embd,
+                                    int64_t n_ff, float swiglu_limit = 0.f) {
+    if (n_layers <= 0) {
+        err = "expert layout: no layers";
+        return false;
+    }
+    std::vector<bsx_layout_row> rows((size_t) n_layers);
+    bsx_layout_info info{};
+    char why[512];
+    if (bsx_layout_parse(text.data(), text.size(), n_layers, n_expert, n_embd, n_ff, swiglu_limit, rows.data(), &info, why, sizeof why) != BSX_OK) {
+        err = why;
+        return false;
+    }
+    ExpertLayout L;
+    L.native = true;
+    L.n_layers = info.n_layers;
+    L.n_expert = info.n_expert;
+    L.version = info.version;
+    L.max_blob = info.max_blob;
+    L.total = info.total;
+    for (const bsx_layout_row& r : rows) {
+        L.fmt.push_back(basalt::kernels::native_expert_layout(r.gu_type, r.d_type, n_embd, n_ff, swiglu_limit, r.up_type));
+        L.offset.push_back(r.offset);
+        L.bytes.push_back(r.blob_bytes);
+    }
+    shim_detail::table() = L;
+    return true;
+}
+}  // namespace basalt::kernels::cpu

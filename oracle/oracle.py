@@ -332,8 +332,26 @@ def ref_cpu():
         L.ref_pool_workers.argtypes = [C.c_void_p]
         L.ref_pool_layer.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_float, C.c_void_p, C.c_int,
                                      _i32p, _i32p, _f32p, C.c_int, _f32p]
+        if hasattr(L, "ref_layout_load_text"):
+            L.ref_layout_load_text.argtypes = [C.c_char_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float,
+                                               C.c_void_p, C.c_void_p, C.c_char_p, C.c_int]
         _ref_cpu = L
     return _ref_cpu
+
+
+def ref_layout_load_text(text: bytes, n_layers: int, n_expert: int, n_embd: int, n_ff: int, swiglu_limit: float = 0.0):
+    """The reference's own parse of an `experts.layout` text (expert_layout_load_text, src/kernels/cpu/expert_layout.cpp:133-203)
+    through oracle/_ref: (True, head, rows) with head = [version, n_expert, max_blob, total, n_layers] and one
+    [gu_type, d_type, up_type, offset, blob_bytes, up_off] per layer, or (False, reason, None)."""
+    L = ref_cpu()
+    head = np.zeros(5, np.int64)
+    rows = np.zeros((max(n_layers, 1), 6), np.int64)
+    err = C.create_string_buffer(512)
+    ok = L.ref_layout_load_text(text, len(text), n_layers, n_expert, n_embd, n_ff, swiglu_limit, head.ctypes.data, rows.ctypes.data,
+                                err, len(err))
+    if not ok:
+        return False, err.value.decode("utf-8", "replace"), None
+    return True, head.tolist(), rows[:n_layers].tolist()
 
 
 def ref_gpu():

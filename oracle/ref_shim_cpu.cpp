@@ -7,7 +7,9 @@
 //   ggml_get_type_traits / ggml_quantize_chunk          include/basalt/ggml/ggml.h:60-77
 //   cpu::native_fmt / native_quant_act / native_quant_h  include/basalt/kernels/cpu/native_expert.hpp:44-58
 //   cpu::ExpertPool::run_split_multi_native              include/basalt/kernels/cpu/pool.hpp:96-97
+//   cpu::expert_layout_load_text / expert_layout         include/basalt/kernels/cpu/expert_layout.hpp:53-65
 #include "basalt/ggml/ggml.h"
+#include "basalt/kernels/cpu/expert_layout.hpp"
 #include "basalt/kernels/cpu/native_expert.hpp"
 #include "basalt/kernels/cpu/pool.hpp"
 
@@ -99,6 +101,26 @@ int ref_pool_layer(void* p, int gu_type, int d_type, int64_t n_embd, int64_t n_f
     cpu::ExpertPool* pool = ((RefPool*) p)->pool;
     if (!jobs.empty()) pool->run_split_multi_native(f, jobs.data(), (int) jobs.size());   // batches internally
     return 0;
+}
+
+// The reference's parse of an `experts.layout` text.  Returns 1 and fills head[0..4] = version, n_expert, max_blob, total,
+// n_layers and per layer rows[6 l ..] = gu_type, d_type, up_type, offset, blob_bytes, up_off; or 0 with the reason in err.
+int ref_layout_load_text(const char* text, int64_t len, int64_t n_layers, int64_t n_expert, int64_t n_embd, int64_t n_ff,
+                         float swiglu_limit, int64_t* head, int64_t* rows, char* err, int err_len) {
+    std::string e;
+    if (!cpu::expert_layout_load_text(std::string(text, (size_t) len), n_layers, n_expert, e, n_embd, n_ff, swiglu_limit)) {
+        if (err && err_len > 0) { std::strncpy(err, e.c_str(), (size_t) err_len - 1); err[err_len - 1] = 0; }
+        return 0;
+    }
+    const cpu::ExpertLayout& L = cpu::expert_layout();
+    head[0] = L.version; head[1] = L.n_expert; head[2] = (int64_t) L.max_blob; head[3] = (int64_t) L.total; head[4] = L.n_layers;
+    for (int64_t l = 0; l < L.n_layers; ++l) {
+        const cpu::NativeFmt& f = L.fmt[(size_t) l];
+        int64_t* r = rows + 6 * l;
+        r[0] = f.gu_type; r[1] = f.d_type; r[2] = f.up_type; r[3] = (int64_t) L.offset[(size_t) l]; r[4] = (int64_t) L.bytes[(size_t) l];
+        r[5] = (int64_t) f.up_off;
+    }
+    return 1;
 }
 
 }  // extern "C"

@@ -25,6 +25,18 @@ int main() {
     try { native_expert_layout(7, 7, 2048, 512); } catch (const std::invalid_argument&) { threw = true; }
     if (!threw) { std::puts("unknown type must throw"); ++failures; }
     route_tail_skip(nullptr, nullptr, ResidentTabs{}, 500, 4, 1, 8, nullptr, nullptr);   // out of range: a silent no-op, as in the reference
+    {
+        namespace c = basalt::kernels::cpu;
+        std::string err;
+        const std::string b = std::to_string(L.bytes);
+        const std::string text = "# experts v6: layer gu_type d_type offset blob_bytes (n_expert 4, total " + std::to_string(8 * L.bytes) +
+                                 ")\n0 40 40 0 " + b + "\n1 40 40 " + std::to_string(4 * L.bytes) + " " + b + "\n";
+        if (!c::expert_layout_load_text(text, 2, 512, err, 2048, 512) || c::expert_layout().n_expert != 4 ||
+            c::expert_layout().blob_offset(1, 2) != 6 * L.bytes || c::expert_layout().fmt[1].down_off != L.down_off ||
+            c::expert_layout().total != 8 * L.bytes || c::expert_layout().version != 6) { std::puts(("layout text: " + err).c_str()); ++failures; }
+        if (c::expert_layout_load_text("# experts v8: x\n", 2, 512, err, 2048, 512) || err.find("v8") == std::string::npos) { std::puts("v8 must be refused"); ++failures; }
+        if (c::expert_layout().version != 6) { std::puts("a refused text must leave the table alone"); ++failures; }
+    }
     std::printf("shim %s\n", failures ? "FAILED" : "ok");
     return failures;
 }
