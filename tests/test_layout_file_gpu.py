@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 def test_layers_load_from_a_file_as_direct_uploads(lib, cuda, tmp_path):
     rng = np.random.default_rng(3)
-    E, H, I, K, T = 24, 512, 256, 4, 16
+    E, H, I, K, T = 32, 512, 256, 4, 16
     _, nv = make_expert_blobs(rng, E, O.T_NVFP4, O.T_NVFP4, H, I)
     _, q6 = make_expert_blobs(rng, E, O.T_Q6_K, O.T_Q6_K, H, I)
     text = lf.layout_text([(40, 40, -1), (14, 14, -1)], E, H, I)
@@ -28,7 +28,7 @@ def test_layers_load_from_a_file_as_direct_uploads(lib, cuda, tmp_path):
     sec = lf.ExpertsSection(str(path), table, base_offset=4096)
 
     for layer, blobs in ((0, nv), (1, q6)):
-        got, L = sec.load_layer(layer, cuda, chunk_experts=5)   # 5 does not divide 24: a ragged last chunk, buffers reused
+        got, L = sec.load_layer(layer, cuda, chunk_experts=5)   # 5 does not divide 32: a ragged last chunk, buffers reused
         want = torch.from_numpy(stack_blobs(blobs)).to(cuda)
         assert got.shape == want.shape and torch.equal(got, want)
         assert L.bytes == blobs[0].size
@@ -39,7 +39,8 @@ def test_layers_load_from_a_file_as_direct_uploads(lib, cuda, tmp_path):
     want_packed = moe.pack_experts(L, torch.from_numpy(stack_blobs(nv)).to(cuda))
     got_packed, _ = sec.load_layer(0, cuda, pack=True, chunk_experts=7)
     torch.cuda.synchronize()
-    assert torch.equal(got_packed, want_packed)
+    used = (2 * (I // 128) * (H // 256) + (H // 128) * (I // 256)) * 18432 + 16      # blocks + the fp32 tail; the rest is padding
+    assert got_packed.shape == want_packed.shape and torch.equal(got_packed[:, :used], want_packed[:, :used])
     with pytest.raises(ValueError, match="packed path"):
         sec.load_layer(1, cuda, pack=True)
 
