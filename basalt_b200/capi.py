@@ -81,6 +81,8 @@ _SIGNATURES = {
     "bsx_plan_groups_shared": (C.c_int32, [P, P, P, C.c_int32, P, C.c_uint64, C.c_int32, C.c_int32, P, P, P, P, P, P]),
     "bsx_combine_partial": (C.c_int32, [P, P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, P]),
     "bsx_combine": (C.c_int32, [P, P, P, P, P, C.c_int32, C.c_int32, C.c_int32, P, P]),
+    "bsx_norm_pack": (C.c_int32, [P, C.c_int32, P, C.c_float, C.c_int64, C.c_int32, P, P, P]),
+    "bsx_norm_pack_images": (C.c_int32, [C.POINTER(ExpertLayout), P, C.c_int32, P, C.c_float, C.c_int32, C.c_int64, P, P, P, P]),
     "bsx_layout_parse": (C.c_int32, [C.c_char_p, C.c_size_t, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float, P, P, C.c_char_p, C.c_size_t]),
     "bsx_host_decode_row": (C.c_int32, [C.c_int32, P, P, C.c_int64]),
     "bsx_row_bytes": (C.c_size_t, [C.c_int32, C.c_int64]),

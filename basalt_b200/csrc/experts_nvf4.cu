@@ -33,6 +33,7 @@
 #include "common.cuh"
 #include "experts.cuh"
 #include "formats.cuh"
+#include "norm.cuh"
 #include "nvf4.cuh"
 #include "tc5.cuh"
 
@@ -168,6 +169,19 @@ __global__ void __launch_bounds__(256) x_images_kernel(const void* __restrict__ 
     __shared__ float shf[8];
     const int i = blockIdx.x * (256 / TPR) + (int) threadIdx.x / TPR;
     fp4_image_row<TPR>(x, kind, i < n_rows ? i : 0, K, i < n_rows, i, codes, sfs, inv, shf);
+}
+
+// The RMS norm of row blockIdx.x (norm.cuh: the reference's order, so xn carries its bits) and the FP4 images of the normed
+// row, one launch: the block reads back the fp32 row it has just written (still in L1 / L2) instead of a second kernel
+// fetching it from HBM.
+template <bool BF16>
+__global__ void __launch_bounds__(kNormThreads) norm_images_kernel(const void* __restrict__ x, const float* __restrict__ w, float eps, int64_t K,
+                                                                   uint16_t* act, float* xn, uint8_t* __restrict__ codes,
+                                                                   uint8_t* __restrict__ sfs, float* __restrict__ inv) {
+    __shared__ float red[kNormThreads / 32];
+    __shared__ float shf[kNormThreads / 32];
+    norm_row<BF16>(x, w, eps, K, blockIdx.x, act, xn, red);
+    fp4_image_row<kNormThreads>(xn, BSX_X_F32, blockIdx.x, K, true, (int) blockIdx.x, codes, sfs, inv, shf);
 }
 
 template <bool FROM_H>
@@ -607,6 +621,25 @@ extern "C" int32_t bsx_experts_grouped_packed(const bsx_expert_layout* layout, c
     a.n_x_rows = n_x_rows;
     a.grid = nullptr;
     return experts_grouped_packed(a, status, (cudaStream_t) stream, ready);
+}
+
+extern "C" int32_t bsx_norm_pack_images(const bsx_expert_layout* layout, const void* x, int32_t x_kind, const float* w, float eps,
+                                        int32_t n_x_rows, int64_t cap_entries, void* scratch, float* xn, void* act, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (!layout || !aligned(x, 16) || !aligned(scratch, 256) || !aligned(xn, 16) || !w) return BSX_E_POINTER;
+    if (!bsx_expert_packed_bytes(layout)) return BSX_E_TYPE;
+    if (x_kind != BSX_X_F32 && x_kind != BSX_X_BF16) return BSX_E_TYPE;
+    if (n_x_rows < 0 || n_x_rows > cap_entries) return BSX_E_GEOMETRY;
+    if (n_x_rows == 0) return BSX_OK;
+    const PackedScratch sc = carve_scratch(scratch, cap_entries, layout->n_embd, layout->n_ff);
+    cudaStream_t st = (cudaStream_t) stream;
+    if (x_kind == BSX_X_BF16)
+        norm_images_kernel<true><<<(unsigned) n_x_rows, kNormThreads, 0, st>>>(x, w, eps, layout->n_embd, static_cast<uint16_t*>(act), xn, sc.xcodes,
+                                                                              sc.xsf, sc.xinv);
+    else
+        norm_images_kernel<false><<<(unsigned) n_x_rows, kNormThreads, 0, st>>>(x, w, eps, layout->n_embd, static_cast<uint16_t*>(act), xn, sc.xcodes,
+                                                                               sc.xsf, sc.xinv);
+    return launch_status();
 }
 
 extern "C" int32_t bsx_experts_packed_x_images(const bsx_expert_layout* layout, const void* x, int32_t x_kind, int32_t n_x_rows, int64_t cap_entries,

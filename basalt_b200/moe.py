@@ -217,6 +217,16 @@ def native_expert_grouped(L: ExpertLayout, grp_ptr, grp_start, n_groups, ent_dst
     return out
 
 
+def norm_pack(x, w, eps: float, act: bool = True, xn: bool = True, stream=None):
+    """basalt::kernels::wgemm::norm_pack (include/basalt/kernels/window_gemm.hpp:36-40): the RMS norm of the rows of x (fp32 or
+    bf16) as (bf16 rows or None, fp32 rows or None)."""
+    T, K = x.shape
+    a = torch.empty((T, K), dtype=torch.bfloat16, device=x.device) if act else None
+    n = torch.empty((T, K), dtype=torch.float32, device=x.device) if xn else None
+    check("bsx_norm_pack", capi.lib().bsx_norm_pack(_p(x), _x_kind(x), _p(w), eps, K, T, _p(a), _p(n), _stream(stream)))
+    return a, n
+
+
 def pack_experts(L: ExpertLayout, blobs: torch.Tensor, stream=None) -> torch.Tensor:
     """blobs [E][stride] (ggml NVFP4 expert blobs) -> [E][packed stride] in the plane layout bsx_experts_grouped_packed streams
     (a load-time step, like Basalt's nvfp4_planes: include/basalt/kernels/nvfp4_planes.hpp:6-20)."""
@@ -284,9 +294,11 @@ class MoELayer:
 
     def __init__(self, gate_w: torch.Tensor, bias: Optional[torch.Tensor], blobs: torch.Tensor, layout: ExpertLayout,
                  args: RouterArgs, shared_blob: Optional[torch.Tensor] = None, shared_layout: Optional[ExpertLayout] = None,
-                 max_tokens: int = 64, packed: bool = False):
+                 max_tokens: int = 64, packed: bool = False, norm_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6):
         """packed: blobs (and the shared blob) are already in the plane layout of pack_experts; the experts then run on the
-        block-scaled FP4 tensor cores (needs a shared expert of the routed experts' layout, or none)."""
+        block-scaled FP4 tensor cores (needs a shared expert of the routed experts' layout, or none).
+        norm_w: the layer's input norm weights [n_embd] fp32; forward() then takes the un-normed rows and applies the RMS norm
+        itself (the reference's norm_pack step, fused with the FP4 activation images on the packed path)."""
         assert blobs.dtype == torch.uint8 and blobs.dim() == 2 and blobs.is_cuda
         self.gate_w, self.bias, self.blobs, self.L, self.args = gate_w, bias, blobs, layout, args
         self.shared_blob, self.shared_L = shared_blob, shared_layout or layout
@@ -319,6 +331,10 @@ class MoELayer:
         else:
             self.scratch = torch.empty(native_expert_scratch_bytes(layout, rows), dtype=torch.uint8, device=dev)
         self.y = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
+        self.norm_w, self.norm_eps = norm_w, float(norm_eps)
+        if norm_w is not None:
+            assert norm_w.dtype == f32 and norm_w.numel() == layout.n_embd and norm_w.is_cuda
+            self.xn = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
         if shared_blob is not None and not self.fused_shared:
             self.s_ptr = torch.tensor([shared_blob.data_ptr()], dtype=torch.int64, device=dev)
             self.s_iota = torch.arange(max_tokens, dtype=i32, device=dev)
@@ -352,7 +368,17 @@ class MoELayer:
         xr = x_router if x_router is not None else x     # fp32 or bf16 rows; bf16 is widened exactly inside the kernel
         hp, hn, keep = _held(a)
         images_ahead = self.packed and self.fused_shared
-        if images_ahead:
+        forked = images_ahead and self.norm_w is None
+        if self.norm_w is not None:
+            # the step before the layer: RMS norm of the input rows (fp32 rows for the router and the experts), on the packed path
+            # together with the FP4 images of the normed rows
+            if images_ahead:
+                check("bsx_norm_pack_images", lib.bsx_norm_pack_images(C.byref(self.L), _p(x), _x_kind(x), _p(self.norm_w), self.norm_eps, T,
+                                                                       T * a.k + T, _p(self.scratch), _p(self.xn), None, st))
+            else:
+                check("bsx_norm_pack", lib.bsx_norm_pack(_p(x), _x_kind(x), _p(self.norm_w), self.norm_eps, a.n_embd, T, None, _p(self.xn), st))
+            x = xr = self.xn[:T]
+        if forked:
             # fork: the activation images on the side stream while the router and the plan run on this one (joined before the experts)
             cur = stream if stream is not None else torch.cuda.current_stream()
             self.side.wait_stream(cur)
@@ -367,7 +393,7 @@ class MoELayer:
         if self.fused_shared:
             check("bsx_moe_plan_shared", lib.bsx_moe_plan_shared(_p(self.ids), T, a.k, a.n_expert, _p(self.blob_table), self.shared_blob.data_ptr(),
                                                                  _p(self.ptr), _p(self.start), _p(self.n_groups), _p(self.dst), _p(self.tok), st))
-            if images_ahead:
+            if forked:
                 cur.wait_stream(self.side)       # join
             if self.packed:
                 check("bsx_experts_grouped_packed", lib.bsx_experts_grouped_packed(C.byref(self.L), _p(self.ptr), _p(self.start), _p(self.n_groups),

@@ -295,6 +295,18 @@ BSX_API int32_t bsx_plan_groups_shared(const int32_t* cnt, const int32_t* off, c
 BSX_API int32_t bsx_combine_partial(const float* rows, const int32_t* slot, const float* weights, const int32_t* ids, int32_t e_lo,
                                     int32_t e_hi, int32_t T, int32_t k, int32_t H, float* y, void* stream);
 
+/* ---- the step before the layer: the RMS norm of the layer's input rows (weights w, any offset folded), as fp32 rows xn (what
+ * the router reads) and / or bf16 rows act; either may be null, not both.  Replaces wgemm::norm_pack
+ * (include/basalt/kernels/window_gemm.hpp:36-40, src/kernels/cuda/window_gemm.cu:75-112) with its summation order, so the rows
+ * carry the reference's bits.  x [T][K] fp32 or bf16 (x_kind BSX_X_F32 / BSX_X_BF16).
+ * bsx_norm_pack_images: the same norm plus the FP4 images bsx_experts_grouped_packed reads, in one launch - rows 0 ..
+ * n_x_rows - 1 into `scratch` exactly as bsx_experts_packed_x_images(xn) would leave them (the grouped call is then given
+ * -n_x_rows); xn is required, act optional. */
+BSX_API int32_t bsx_norm_pack(const void* x, int32_t x_kind, const float* w, float eps, int64_t K, int32_t T, void* act, float* xn,
+                              void* stream);
+BSX_API int32_t bsx_norm_pack_images(const bsx_expert_layout* layout, const void* x, int32_t x_kind, const float* w, float eps,
+                                     int32_t n_x_rows, int64_t cap_entries, void* scratch, float* xn, void* act, void* stream);
+
 /* ---- the model file's `experts.layout` text (host only): which ggml types each layer's expert blobs have, how large a blob is
  * and where the layer's n_expert blobs start inside the `experts` section.  Replaces expert_layout_load_text / ExpertLayout
  * (include/basalt/kernels/cpu/expert_layout.hpp:17-35,60-67; src/kernels/cpu/expert_layout.cpp:133-203) with the same rules:

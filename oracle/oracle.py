@@ -314,6 +314,34 @@ def moe_layer(x, gate_w, bias, blobs, L: Layout, k, kind, scale=1.0, n_group=1, 
 _ref_cpu = None
 
 
+def norm_pack(x: np.ndarray, w: np.ndarray, eps: float):
+    """The RMS norm of each row, restating wgemm::norm_pack (src/kernels/cuda/window_gemm.cu:40-112): thread i of 512 sums the
+    squares of columns i, i + 512, ... as one fma chain, a warp's 32 chains are added by xor butterfly, the 16 warp sums in
+    warp order; inv = 1 / sqrt(sum / K + eps); value = (x * inv) * w.  fp32 throughout (an fma as a product and a sum in
+    fp64 rounded once to fp32); the device's rsqrtf is an approximation, so the GPU rows sit within 4 ulp of these, not on
+    them.  Returns (xn fp32, act = xn rounded to bf16 bits as uint16)."""
+    x = np.ascontiguousarray(x, np.float32)
+    T, K = x.shape
+    n_chain = 512
+    pad = (-K) % n_chain
+    xp = np.pad(x, ((0, 0), (0, pad))).reshape(T, -1, n_chain)          # [T][j][thread]
+    ss = np.zeros((T, n_chain), np.float32)
+    for j in range(xp.shape[1]):
+        v = xp[:, j, :].astype(np.float64)
+        ss = (v * v + ss.astype(np.float64)).astype(np.float32)
+    s = ss.reshape(T, 16, 32)
+    for m in (16, 8, 4, 2, 1):
+        s = (s + s[:, :, np.arange(32) ^ m]).astype(np.float32)
+    t = np.zeros(T, np.float32)
+    for wp in range(16):
+        t = (t + s[:, wp, 0]).astype(np.float32)
+    inv = (np.float32(1.0) / np.sqrt((t / np.float32(K) + np.float32(eps)).astype(np.float32))).astype(np.float32)
+    xn = ((x * inv[:, None]).astype(np.float32) * w.astype(np.float32)[None, :]).astype(np.float32)
+    u = xn.view(np.uint32)
+    act = ((u + (0x7FFF + ((u >> 16) & 1))) >> 16).astype(np.uint16)      # round to nearest even (finite values)
+    return xn, act
+
+
 def ref_cpu():
     """oracle/_ref/libref_cpu.so (the reference's ggml quantisers and CPU expert pool), or None if it was never built."""
     global _ref_cpu
@@ -362,4 +390,6 @@ def ref_gpu():
     L = C.CDLL(str(p))
     L.refg_expert_blob_bytes.restype = C.c_int64
     L.refg_expert_scratch_bytes.restype = C.c_int64
+    if hasattr(L, "refg_norm_pack"):
+        L.refg_norm_pack.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_float, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]
     return L

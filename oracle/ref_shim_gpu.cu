@@ -11,8 +11,10 @@
 //   quantize_q8_1_rows, native_expert_layout, native_expert_scratch_bytes, native_expert_grouped
 //                                     include/basalt/kernels/iq_kernels.hpp:23,68,75,84
 //   native_moe_combine_multi          include/basalt/models/qwen4exp/kernels/native_moe.hpp
+//   wgemm::norm_pack                  include/basalt/kernels/window_gemm.hpp:36-40
 #include "basalt/kernels/iq_kernels.hpp"
 #include "basalt/kernels/router.hpp"
+#include "basalt/kernels/window_gemm.hpp"
 #include "basalt/models/qwen4exp/kernels/native_moe.hpp"
 #include "basalt/models/qwen4exp/kernels/native_router.hpp"
 #include "basalt/models/qwen4exp/kernels/router_top10.hpp"
@@ -112,6 +114,15 @@ int refg_combine_multi(const float* parts, const float* weights, const float* sh
     const int f = finish();
     cudaStreamDestroy(s);
     return rc ? rc : f;
+}
+
+// The RMS norm of T rows of K values (fp32, or bf16 when `bf16` is set) into bf16 rows `act` and fp32 rows `xn` (may be null).
+int refg_norm_pack(const void* x, int bf16, const float* w, float eps, int64_t K, int T, void* act, float* xn) {
+    try {
+        if (bf16) wgemm::norm_pack((const uint16_t*) x, w, eps, K, T, act, xn, nullptr);
+        else wgemm::norm_pack((const float*) x, w, eps, K, T, act, xn, nullptr);
+    } catch (const std::exception&) { return -1; }
+    return finish();
 }
 
 }  // extern "C"
