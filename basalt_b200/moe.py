@@ -294,11 +294,15 @@ class MoELayer:
 
     def __init__(self, gate_w: torch.Tensor, bias: Optional[torch.Tensor], blobs: torch.Tensor, layout: ExpertLayout,
                  args: RouterArgs, shared_blob: Optional[torch.Tensor] = None, shared_layout: Optional[ExpertLayout] = None,
-                 max_tokens: int = 64, packed: bool = False, norm_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6):
+                 max_tokens: int = 64, packed: bool = False, norm_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
+                 norm_fused: bool = True, fork_images: Optional[bool] = None):
         """packed: blobs (and the shared blob) are already in the plane layout of pack_experts; the experts then run on the
         block-scaled FP4 tensor cores (needs a shared expert of the routed experts' layout, or none).
         norm_w: the layer's input norm weights [n_embd] fp32; forward() then takes the un-normed rows and applies the RMS norm
-        itself (the reference's norm_pack step, fused with the FP4 activation images on the packed path)."""
+        itself (the reference's norm_pack step, fused with the FP4 activation images on the packed path; norm_fused=False keeps
+        the two as separate launches, for comparison).
+        fork_images: the packed path's activation images run on a side stream beside router and plan (True), ahead of them on
+        the step's stream (False), or whichever measured faster for the step's token count (None)."""
         assert blobs.dtype == torch.uint8 and blobs.dim() == 2 and blobs.is_cuda
         self.gate_w, self.bias, self.blobs, self.L, self.args = gate_w, bias, blobs, layout, args
         self.shared_blob, self.shared_L = shared_blob, shared_layout or layout
@@ -331,7 +335,7 @@ class MoELayer:
         else:
             self.scratch = torch.empty(native_expert_scratch_bytes(layout, rows), dtype=torch.uint8, device=dev)
         self.y = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
-        self.norm_w, self.norm_eps = norm_w, float(norm_eps)
+        self.norm_w, self.norm_eps, self.norm_fused, self.fork_images = norm_w, float(norm_eps), norm_fused, fork_images
         if norm_w is not None:
             assert norm_w.dtype == f32 and norm_w.numel() == layout.n_embd and norm_w.is_cuda
             self.xn = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
@@ -368,16 +372,23 @@ class MoELayer:
         xr = x_router if x_router is not None else x     # fp32 or bf16 rows; bf16 is widened exactly inside the kernel
         hp, hn, keep = _held(a)
         images_ahead = self.packed and self.fused_shared
-        forked = images_ahead and self.norm_w is None
+        fuse = images_ahead and self.norm_fused
+        forked = images_ahead and (self.norm_w is None or not fuse)
         if self.norm_w is not None:
             # the step before the layer: RMS norm of the input rows (fp32 rows for the router and the experts), on the packed path
             # together with the FP4 images of the normed rows
-            if images_ahead:
+            if fuse:
                 check("bsx_norm_pack_images", lib.bsx_norm_pack_images(C.byref(self.L), _p(x), _x_kind(x), _p(self.norm_w), self.norm_eps, T,
                                                                        T * a.k + T, _p(self.scratch), _p(self.xn), None, st))
             else:
                 check("bsx_norm_pack", lib.bsx_norm_pack(_p(x), _x_kind(x), _p(self.norm_w), self.norm_eps, a.n_embd, T, None, _p(self.xn), st))
             x = xr = self.xn[:T]
+        # measured on a B200 (512 experts, top-10): beside the router the images save ~0.4 us a step at 1 - 8 tokens and cost
+        # ~2.5 us at 64 (the join delays the gate/up launch more than the 5 us image kernel it hides)
+        if forked and not (self.fork_images if self.fork_images is not None else T <= 16):
+            # the images first on this stream, no fork
+            check("bsx_experts_packed_x_images", lib.bsx_experts_packed_x_images(C.byref(self.L), _p(x), _x_kind(x), T, T * a.k + T, _p(self.scratch), st))
+            forked = False
         if forked:
             # fork: the activation images on the side stream while the router and the plan run on this one (joined before the experts)
             cur = stream if stream is not None else torch.cuda.current_stream()

@@ -234,6 +234,11 @@ def main():
     ap.add_argument("--experts", default="packed", choices=["packed", "fp16"],
                     help="decode expert kernels: packed = blobs repacked at load into planes, block-scaled FP4 tensor cores (tcgen05 kind::mxf4nvf4); "
                          "fp16 = ggml blobs in place, fp16 activation images, mma.sync")
+    ap.add_argument("--input-norm", default="none", choices=["none", "fused", "separate"],
+                    help="decode workload: the layer also applies its input RMS norm (the reference's norm_pack step) - fused with the FP4 "
+                         "activation images, or as a launch of its own")
+    ap.add_argument("--no-fork", action="store_true", help="decode workload: the activation-image kernel runs on the step's own stream, ahead of the router, "
+                                                           "instead of where the layer would put it (a forked branch beside the router for up to 16 tokens)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel of a step from the host instead of replaying the layer's CUDA graph")
     ap.add_argument("--decode-tokens", type=int, default=T, help="tokens per decode step and GPU (the reference's decode configs: 1, 8, 64; the metric is quoted on 64)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
@@ -295,7 +300,9 @@ def main():
             del blobs_ggml
     for c in range(args.copies):
         b = blobs if c == 0 else blobs.clone()
-        layers.append(moe.MoELayer(gate if c == 0 else gate.clone(), bias, b[:E], L, rargs, shared_blob=b[E], max_tokens=T, packed=use_packed))
+        norm_w = None if args.input_norm == "none" else 1.0 + 0.1 * torch.randn(H, generator=torch.Generator(device=dev).manual_seed(3), device=dev)
+        layers.append(moe.MoELayer(gate if c == 0 else gate.clone(), bias, b[:E], L, rargs, shared_blob=b[E], max_tokens=T, packed=use_packed,
+                                   norm_w=norm_w, norm_fused=args.input_norm != "separate", fork_images=False if args.no_fork else None))
     n_batches = 8
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     xs = [torch.randn((T, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
@@ -379,9 +386,11 @@ def main():
                                   f"weights cycle through {args.copies} layer copies ({0.906 * args.copies:.1f} GB); use --copies so that copies x touched experts exceed the 126 MB L2"),
                        parallelism="single GPU" if world == 1 else f"ep{world}",
                        expert_kernels="packed planes + tcgen05 block-scaled FP4" if use_packed else "ggml blobs in place + fp16 images + mma.sync",
-                       launch="one CUDA graph per step (input copied into its static buffer, device to device)" if use_graph else "one host launch per kernel"),
+                       launch="one CUDA graph per step (input copied into its static buffer, device to device)" if use_graph else "one host launch per kernel",
+                       input_norm={"none": "not part of the step (rows arrive normed)", "fused": "RMS norm inside the step, fused with the FP4 activation images",
+                                   "separate": "RMS norm inside the step, a launch of its own"}[args.input_norm]),
         "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
-        "gpu_launches": 8 * args.steps,   # logits, select, plan, 2 x activation images, gate/up, down, combine (the shared expert rides in the grouped call)
+        "gpu_launches": (9 if args.input_norm == "separate" else 8) * args.steps,   # (norm,) logits, select, plan, 2 x activation images, gate/up, down, combine (the shared expert rides in the grouped call)
         "roofline": {"bound": "hbm", "kernel": ("nvf4_stream_kernel<gate/up>" if use_packed else "nvfp4_mma_kernel<gate/up>") + " (routed + shared experts; stage time includes the activation-image kernel)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch of this workload at 64 tokens (seeded, so the
