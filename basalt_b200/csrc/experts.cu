@@ -165,6 +165,12 @@ extern "C" int32_t bsx_host_decode_row(int32_t type, const void* row, float* y, 
         for (int64_t i = 0; i < n / 64; ++i) decode_block_nvfp4(b + i * 36, y + i * 64);
     } else if (type == kTypeQ6K) {
         for (int64_t u = 0; u < n / 32; ++u) decode_q6k_32(b + (u >> 3) * 210, (int) (u & 7), y + u * 32);
+    } else if (type == kTypeQ8_0) {
+        for (int64_t u = 0; u < n / 32; ++u) decode_q8_0_32(b + u * 34, y + u * 32);
+    } else if (type == kTypeQ4K) {
+        for (int64_t u = 0; u < n / 32; ++u) decode_q4k_32(b + (u >> 3) * 144, (int) (u & 7), y + u * 32);
+    } else if (type == kTypeQ5K) {
+        for (int64_t u = 0; u < n / 32; ++u) decode_q5k_32(b + (u >> 3) * 176, (int) (u & 7), y + u * 32);
     } else {
         for (int64_t u = 0; u < n / 32; ++u) decode_iq1m_32(b + (u >> 3) * 56, (int) (u & 7), h_iq1_grid, y + u * 32);
     }

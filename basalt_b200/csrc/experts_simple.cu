@@ -38,6 +38,12 @@ __device__ __forceinline__ void decode32(int type, const uint8_t* row, int unit,
         }
     } else if (type == kTypeQ6K) {
         decode_q6k_32(row + (size_t) (unit >> 3) * 210, unit & 7, y);
+    } else if (type == kTypeQ8_0) {
+        decode_q8_0_32(row + (size_t) unit * 34, y);
+    } else if (type == kTypeQ4K) {
+        decode_q4k_32(row + (size_t) (unit >> 3) * 144, unit & 7, y);
+    } else if (type == kTypeQ5K) {
+        decode_q5k_32(row + (size_t) (unit >> 3) * 176, unit & 7, y);
     } else {
         decode_iq1m_32(row + (size_t) (unit >> 3) * 56, unit & 7, grid, y);
     }

@@ -12,13 +12,18 @@
 
 namespace bsx {
 
-enum : int { kTypeQ6K = 14, kTypeIQ1M = 29, kTypeNVFP4 = 40 };
+enum : int { kTypeQ8_0 = 8, kTypeQ4K = 12, kTypeQ5K = 13, kTypeQ6K = 14, kTypeIQ1M = 29, kTypeNVFP4 = 40 };
 
-// values per block and bytes per block
-__host__ __device__ constexpr int block_values(int type) { return type == kTypeNVFP4 ? 64 : 256; }
-__host__ __device__ constexpr int block_bytes(int type) { return type == kTypeNVFP4 ? 36 : type == kTypeQ6K ? 210 : type == kTypeIQ1M ? 56 : 0; }
+// values per block and bytes per block (the GGUF formats' constants, include/basalt/ggml/ggml_common.h)
+__host__ __device__ constexpr int block_values(int type) { return type == kTypeNVFP4 ? 64 : type == kTypeQ8_0 ? 32 : 256; }
+__host__ __device__ constexpr int block_bytes(int type) {
+    return type == kTypeNVFP4 ? 36 : type == kTypeQ6K ? 210 : type == kTypeIQ1M ? 56 : type == kTypeQ8_0 ? 34 : type == kTypeQ4K ? 144
+           : type == kTypeQ5K ? 176 : 0;
+}
 
-__host__ __device__ inline bool type_supported(int type) { return type == kTypeNVFP4 || type == kTypeQ6K || type == kTypeIQ1M; }
+__host__ __device__ inline bool type_supported(int type) {
+    return type == kTypeNVFP4 || type == kTypeQ6K || type == kTypeIQ1M || type == kTypeQ8_0 || type == kTypeQ4K || type == kTypeQ5K;
+}
 
 // UE4M3 scale byte as ggml reads it, already halved (the E2M1 table below is doubled): bit 7 ignored, 0 and 0x7F -> 0.
 // (b & 0x7F) << 20 places the 4 exponent bits and 3 mantissa bits where fp32 keeps them; 2^(127-7-1) re-biases, and the
@@ -90,6 +95,59 @@ __host__ __device__ inline void decode_q6k_32(const uint8_t* b, int u, float* y)
         const int hi = (qh[l] >> (2 * sub)) & 3;
         const int q = (lo | (hi << 4)) - 32;
         y[l] = d * (float) sc[l >> 4] * (float) q;
+    }
+}
+
+// a product and a difference rounded separately, as the reference's dequantisers compute them (no fused multiply-add)
+__host__ __device__ inline float mul_then_sub(float a, float b, float c) {
+#ifdef __CUDA_ARCH__
+    return __fsub_rn(__fmul_rn(a, b), c);
+#else
+    volatile float p = a * b;
+    return p - c;
+#endif
+}
+
+// one Q8_0 block (34 bytes: fp16 d, 32 int8; src/kernels/cpu/ggml/ggml_quants.c dequantize_row_q8_0) -> 32 floats
+__host__ __device__ inline void decode_q8_0_32(const uint8_t* b, float* y) {
+    const float d = half_bits_to_float((uint16_t) (b[0] | (b[1] << 8)));
+    for (int l = 0; l < 32; ++l) y[l] = (float) (int8_t) b[2 + l] * d;
+}
+
+// the 6-bit scale and minimum j (0..7) of a Q4_K / Q5_K block's 12 packed bytes (ggml's get_scale_min_k4)
+__host__ __device__ inline void k4_scale_min(const uint8_t* q, int j, int& sc, int& m) {
+    if (j < 4) {
+        sc = q[j] & 63;
+        m = q[j + 4] & 63;
+    } else {
+        sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
+        m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+    }
+}
+
+// 32 consecutive values [32u, 32u+32) of a Q4_K block (144 bytes: fp16 d, fp16 dmin, scales[12], qs[128]; 64 values share
+// 32 bytes, the low nibbles first; dequantize_row_q4_K)
+__host__ __device__ inline void decode_q4k_32(const uint8_t* b, int u, float* y) {
+    const float d = half_bits_to_float((uint16_t) (b[0] | (b[1] << 8))), dmin = half_bits_to_float((uint16_t) (b[2] | (b[3] << 8)));
+    int sc, m;
+    k4_scale_min(b + 4, u, sc, m);
+    const float d1 = d * (float) sc, m1 = dmin * (float) m;
+    const uint8_t* q = b + 16 + 32 * (u >> 1);
+    for (int l = 0; l < 32; ++l) y[l] = mul_then_sub(d1, (float) ((u & 1) ? (q[l] >> 4) : (q[l] & 15)), m1);
+}
+
+// 32 consecutive values of a Q5_K block (176 bytes: d, dmin, scales[12], qh[32], qs[128]; bit u of qh[l] is value l's fifth
+// bit in the 32-value run u; dequantize_row_q5_K)
+__host__ __device__ inline void decode_q5k_32(const uint8_t* b, int u, float* y) {
+    const float d = half_bits_to_float((uint16_t) (b[0] | (b[1] << 8))), dmin = half_bits_to_float((uint16_t) (b[2] | (b[3] << 8)));
+    int sc, m;
+    k4_scale_min(b + 4, u, sc, m);
+    const float d1 = d * (float) sc, m1 = dmin * (float) m;
+    const uint8_t* qh = b + 16;
+    const uint8_t* q = b + 48 + 32 * (u >> 1);
+    for (int l = 0; l < 32; ++l) {
+        const int lo = (u & 1) ? (q[l] >> 4) : (q[l] & 15);
+        y[l] = mul_then_sub(d1, (float) (lo + (((qh[l] >> u) & 1) ? 16 : 0)), m1);
     }
 }
 

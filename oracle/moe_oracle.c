@@ -63,7 +63,7 @@ EXPORT float orc_h2f(uint16_t h) { return h2f(h); }
 EXPORT uint16_t orc_f2h(float f) { return f2h(f); }
 
 /* ------------------------------------------------------------------------------------------------ block formats */
-enum { T_Q6_K = 14, T_IQ1_M = 29, T_NVFP4 = 40 };
+enum { T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ1_M = 29, T_NVFP4 = 40 };
 
 /* include/basalt/ggml/ggml_common.h:1029-1031 - E2M1 values, doubled */
 static const int8_t kFp4x2[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
@@ -88,6 +88,9 @@ EXPORT int64_t orc_row_bytes(int type, int64_t n) {
         case T_NVFP4: return n % 64 ? 0 : n / 64 * 36;     /* ggml_common.h:146-156 */
         case T_Q6_K: return n % 256 ? 0 : n / 256 * 210;   /* ggml_common.h:279-285 */
         case T_IQ1_M: return n % 256 ? 0 : n / 256 * 56;   /* ggml_common.h:350-362 */
+        case T_Q8_0: return n % 32 ? 0 : n / 32 * 34;      /* block_q8_0: fp16 d, int8 qs[32] */
+        case T_Q4_K: return n % 256 ? 0 : n / 256 * 144;   /* block_q4_K: d, dmin, scales[12], qs[128] */
+        case T_Q5_K: return n % 256 ? 0 : n / 256 * 176;   /* block_q5_K: d, dmin, scales[12], qh[32], qs[128] */
         default: return 0;
     }
 }
@@ -154,10 +157,65 @@ static void dequant_iq1m(const uint8_t* b, float* y, int64_t n) {
     }
 }
 
+/* ggml's dequantize_row_q8_0 (src/kernels/cpu/ggml/ggml_quants.c): value = code x d. */
+static void dequant_q8_0(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / 32; ++i, b += 34) {
+        uint16_t dh;
+        memcpy(&dh, b, 2);
+        const float d = h2f(dh);
+        for (int j = 0; j < 32; ++j) *y++ = (float) (int8_t) b[2 + j] * d;
+    }
+}
+
+/* ggml's get_scale_min_k4: the 6-bit scale and minimum j of the 12 packed bytes of a Q4_K / Q5_K block. */
+static void k4_scale_min(int j, const uint8_t* q, uint8_t* sc, uint8_t* m) {
+    if (j < 4) {
+        *sc = q[j] & 63;
+        *m = q[j + 4] & 63;
+    } else {
+        *sc = (uint8_t) ((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4));
+        *m = (uint8_t) ((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+    }
+}
+
+/* ggml's dequantize_row_q4_K / dequantize_row_q5_K (src/kernels/cpu/ggml/ggml_quants.c): per 64 values two (scale, min) pairs;
+ * value = d sc q - dmin m, the product and the difference rounded separately; Q5_K adds 16 where the value's bit of qh is
+ * set (bit 2p for the low nibbles of pair p, bit 2p + 1 for the high ones). */
+static void dequant_q45k(const uint8_t* b, float* y, int64_t n, int five) {
+    const int bs = five ? 176 : 144;
+    for (int64_t i = 0; i < n / 256; ++i, b += bs) {
+        uint16_t dh, mh;
+        memcpy(&dh, b, 2);
+        memcpy(&mh, b + 2, 2);
+        const float d = h2f(dh), dmin = h2f(mh);
+        const uint8_t *scales = b + 4, *qh = b + 16, *q = b + (five ? 48 : 16);
+        for (int p = 0; p < 4; ++p, q += 32) {
+            uint8_t sc, m;
+            k4_scale_min(2 * p, scales, &sc, &m);
+            const float d1 = d * sc, m1 = dmin * m;
+            k4_scale_min(2 * p + 1, scales, &sc, &m);
+            const float d2 = d * sc, m2 = dmin * m;
+            for (int l = 0; l < 32; ++l) {
+                const int hi = five && ((qh[l] >> (2 * p)) & 1) ? 16 : 0;
+                volatile float t = d1 * (float) ((q[l] & 0xF) + hi);
+                *y++ = t - m1;
+            }
+            for (int l = 0; l < 32; ++l) {
+                const int hi = five && ((qh[l] >> (2 * p + 1)) & 1) ? 16 : 0;
+                volatile float t = d2 * (float) ((q[l] >> 4) + hi);
+                *y++ = t - m2;
+            }
+        }
+    }
+}
+
 EXPORT int orc_dequant_row(int type, const void* src, float* y, int64_t n) {
     if (orc_row_bytes(type, n) == 0) return -1;
     if (type == T_NVFP4) dequant_nvfp4(src, y, n);
     else if (type == T_Q6_K) dequant_q6k(src, y, n);
+    else if (type == T_Q8_0) dequant_q8_0(src, y, n);
+    else if (type == T_Q4_K) dequant_q45k(src, y, n, 0);
+    else if (type == T_Q5_K) dequant_q45k(src, y, n, 1);
     else dequant_iq1m(src, y, n);
     return 0;
 }

@@ -14,6 +14,7 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 T_Q6_K, T_IQ1_M, T_NVFP4 = 14, 29, 40
+T_Q8_0, T_Q4_K, T_Q5_K = 8, 12, 13
 GATE_SQRT_SOFTPLUS, GATE_SIGMOID, GATE_SOFTMAX = 0, 1, 2
 
 _f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
@@ -170,6 +171,21 @@ def random_iq1m_rows(rng: np.random.Generator, rows: int, cols: int) -> np.ndarr
     sc[:, 2] = (sc[:, 2] & 0x0FFF) | ((d & 0x0F00) << 4)
     sc[:, 3] = (sc[:, 3] & 0x0FFF) | (d & 0xF000)
     raw[:, 48:56] = sc.view(np.uint8)
+    return raw.reshape(-1)
+
+
+def random_rows(t: int, rng: np.random.Generator, rows: int, cols: int) -> np.ndarray:
+    """Random valid rows of a format the oracle has no quantiser for: uniform bytes with finite fp16 scales near 2^-9 (so
+    values are of order 0.02, like the quantised N(0, 0.02^2) weights of the other formats)."""
+    if t == T_IQ1_M:
+        return random_iq1m_rows(rng, rows, cols)
+    bs, nv, scale_at = {T_Q8_0: (34, 32, (0,)), T_Q4_K: (144, 256, (0, 2)), T_Q5_K: (176, 256, (0, 2))}[t]
+    nb = rows * cols // nv
+    raw = rng.integers(0, 256, size=(nb, bs), dtype=np.uint8)
+    for at in scale_at:
+        base = 0x0C00 if t == T_Q8_0 else 0x0800 if at == 0 else 0x1400    # fp16 2^-12 (x int8), 2^-13 (x 6-bit scale x code), 2^-10 (x 6-bit min)
+        h = (base + rng.integers(0, 0x400, size=nb)).astype(np.uint16)
+        raw[:, at:at + 2] = h.view(np.uint8).reshape(nb, 2)
     return raw.reshape(-1)
 
 

@@ -2,7 +2,7 @@
 reference checkout by oracle/Makefile).  Run in a container that has the reference; the .npz travels with the repository
 so the CPU tests can pin the oracle where the reference is absent.
 
-Contents: raw blocks of each format with the reference's to_float output; seeded fp32 rows with the reference quantiser's
+Contents: raw blocks of each format (NVFP4, Q6_K, IQ1_M, Q8_0, Q4_K, Q5_K) with the reference's to_float output; seeded fp32 rows with the reference quantiser's
 bytes (NVFP4, Q6_K); the reference's blob geometry for the benchmark shapes; and the reference CPU expert pool's output
 rows for a small Q6_K and a small NVFP4 layer (inputs are regenerated from the seeds stored alongside).
 """
@@ -65,6 +65,13 @@ def main():
         out[f"pool_{name}_x"], out[f"pool_{name}_ids"], out[f"pool_{name}_rows"] = x, ids, rows
         out[f"pool_{name}_blobhash"] = np.array([O.fnv1a(*blobs)], np.uint64)
     R.ref_pool_destroy(pool)
+    # decoders of the formats added later (their own generator, so the vectors above keep their bytes)
+    rng2 = np.random.default_rng(2025)
+    for name, t, nv, nblk in (("q8_0", 8, 32, 16), ("q4k", 12, 256, 3), ("q5k", 13, 256, 3)):
+        raw = O.random_rows(t, rng2, 1, nblk * nv)
+        y = np.empty(nblk * nv, np.float32)
+        assert R.ref_dequantize(t, raw.ctypes.data, y, y.size) == 0
+        out[f"dec_{name}_raw"], out[f"dec_{name}_f32"] = raw, y
     np.savez_compressed(Path(__file__).with_name("ref_vectors.npz"), **out)
     print("wrote ref_vectors.npz:", {k: v.shape for k, v in out.items()})
 
