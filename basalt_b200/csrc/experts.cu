@@ -171,6 +171,12 @@ extern "C" int32_t bsx_host_decode_row(int32_t type, const void* row, float* y, 
         for (int64_t u = 0; u < n / 32; ++u) decode_q4k_32(b + (u >> 3) * 144, (int) (u & 7), y + u * 32);
     } else if (type == kTypeQ5K) {
         for (int64_t u = 0; u < n / 32; ++u) decode_q5k_32(b + (u >> 3) * 176, (int) (u & 7), y + u * 32);
+    } else if (type == kTypeQ5_0 || type == kTypeQ5_1) {
+        for (int64_t u = 0; u < n / 32; ++u) decode_q5_01_32(b + u * (type == kTypeQ5_1 ? 24 : 22), type == kTypeQ5_1, y + u * 32);
+    } else if (type == kTypeIQ4NL) {
+        for (int64_t u = 0; u < n / 32; ++u) decode_iq4nl_32(b + u * 18, y + u * 32);
+    } else if (type == kTypeIQ4XS) {
+        for (int64_t u = 0; u < n / 32; ++u) decode_iq4xs_32(b + (u >> 3) * 136, (int) (u & 7), y + u * 32);
     } else {
         for (int64_t u = 0; u < n / 32; ++u) decode_iq1m_32(b + (u >> 3) * 56, (int) (u & 7), h_iq1_grid, y + u * 32);
     }

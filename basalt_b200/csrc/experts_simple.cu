@@ -44,6 +44,12 @@ __device__ __forceinline__ void decode32(int type, const uint8_t* row, int unit,
         decode_q4k_32(row + (size_t) (unit >> 3) * 144, unit & 7, y);
     } else if (type == kTypeQ5K) {
         decode_q5k_32(row + (size_t) (unit >> 3) * 176, unit & 7, y);
+    } else if (type == kTypeQ5_0 || type == kTypeQ5_1) {
+        decode_q5_01_32(row + (size_t) unit * (type == kTypeQ5_1 ? 24 : 22), type == kTypeQ5_1, y);
+    } else if (type == kTypeIQ4NL) {
+        decode_iq4nl_32(row + (size_t) unit * 18, y);
+    } else if (type == kTypeIQ4XS) {
+        decode_iq4xs_32(row + (size_t) (unit >> 3) * 136, unit & 7, y);
     } else {
         decode_iq1m_32(row + (size_t) (unit >> 3) * 56, unit & 7, grid, y);
     }

@@ -12,18 +12,19 @@
 
 namespace bsx {
 
-enum : int { kTypeQ8_0 = 8, kTypeQ4K = 12, kTypeQ5K = 13, kTypeQ6K = 14, kTypeIQ1M = 29, kTypeNVFP4 = 40 };
+enum : int { kTypeQ5_0 = 6, kTypeQ5_1 = 7, kTypeQ8_0 = 8, kTypeQ4K = 12, kTypeQ5K = 13, kTypeQ6K = 14, kTypeIQ4NL = 20, kTypeIQ4XS = 23, kTypeIQ1M = 29,
+              kTypeNVFP4 = 40 };
 
 // values per block and bytes per block (the GGUF formats' constants, include/basalt/ggml/ggml_common.h)
-__host__ __device__ constexpr int block_values(int type) { return type == kTypeNVFP4 ? 64 : type == kTypeQ8_0 ? 32 : 256; }
+__host__ __device__ constexpr int block_values(int type) {
+    return type == kTypeNVFP4 ? 64 : (type == kTypeQ8_0 || type == kTypeQ5_0 || type == kTypeQ5_1 || type == kTypeIQ4NL) ? 32 : 256;
+}
 __host__ __device__ constexpr int block_bytes(int type) {
     return type == kTypeNVFP4 ? 36 : type == kTypeQ6K ? 210 : type == kTypeIQ1M ? 56 : type == kTypeQ8_0 ? 34 : type == kTypeQ4K ? 144
-           : type == kTypeQ5K ? 176 : 0;
+           : type == kTypeQ5K ? 176 : type == kTypeQ5_0 ? 22 : type == kTypeQ5_1 ? 24 : type == kTypeIQ4NL ? 18 : type == kTypeIQ4XS ? 136 : 0;
 }
 
-__host__ __device__ inline bool type_supported(int type) {
-    return type == kTypeNVFP4 || type == kTypeQ6K || type == kTypeIQ1M || type == kTypeQ8_0 || type == kTypeQ4K || type == kTypeQ5K;
-}
+__host__ __device__ inline bool type_supported(int type) { return block_bytes(type) != 0; }
 
 // UE4M3 scale byte as ggml reads it, already halved (the E2M1 table below is doubled): bit 7 ignored, 0 and 0x7F -> 0.
 // (b & 0x7F) << 20 places the 4 exponent bits and 3 mantissa bits where fp32 keeps them; 2^(127-7-1) re-biases, and the
@@ -106,6 +107,64 @@ __host__ __device__ inline float mul_then_sub(float a, float b, float c) {
     volatile float p = a * b;
     return p - c;
 #endif
+}
+
+__host__ __device__ inline float mul_then_add(float a, float b, float c) {
+#ifdef __CUDA_ARCH__
+    return __fadd_rn(__fmul_rn(a, b), c);
+#else
+    volatile float p = a * b;
+    return p + c;
+#endif
+}
+
+// one Q5_0 block (22 bytes: fp16 d, qh[4], qs[16]; value j = nibble j | bit j of qh as the fifth bit, minus 16; values j and
+// j + 16 share byte j; dequantize_row_q5_0, src/kernels/cpu/ggml/ggml_quants.c:229-253) and one Q5_1 block (24 bytes: d, m, qh,
+// qs; value = code x d + m; :255-281) -> 32 floats
+__host__ __device__ inline void decode_q5_01_32(const uint8_t* b, bool one, float* y) {
+    const float d = half_bits_to_float((uint16_t) (b[0] | (b[1] << 8)));
+    const float m = one ? half_bits_to_float((uint16_t) (b[2] | (b[3] << 8))) : 0.f;
+    const uint8_t* h = b + (one ? 4 : 2);
+    const uint32_t qh = (uint32_t) h[0] | ((uint32_t) h[1] << 8) | ((uint32_t) h[2] << 16) | ((uint32_t) h[3] << 24);
+    const uint8_t* qs = h + 4;
+    for (int j = 0; j < 16; ++j) {
+        const int x0 = (qs[j] & 0x0F) | (int) (((qh >> j) << 4) & 0x10), x1 = (qs[j] >> 4) | (int) ((qh >> (j + 12)) & 0x10);
+        if (one) {
+            y[j] = mul_then_add((float) x0, d, m);
+            y[j + 16] = mul_then_add((float) x1, d, m);
+        } else {
+            y[j] = (float) (x0 - 16) * d;
+            y[j + 16] = (float) (x1 - 16) * d;
+        }
+    }
+}
+
+// the 16 levels of the non-linear 4-bit formats (kvalues_iq4nl, include/basalt/ggml/ggml_common.h:1023-1025)
+__host__ __device__ inline float iq4_level(int c) {
+    return (float) (int) (int8_t) ((c < 8 ? 0xF6EADDCFBFAD9881ull : 0x7159453526190D01ull) >> (8 * (c & 7)));
+}
+
+// one IQ4_NL block (18 bytes: fp16 d, qs[16]; dequantize_row_iq4_nl, ggml_quants.c:1316-1332) -> 32 floats
+__host__ __device__ inline void decode_iq4nl_32(const uint8_t* b, float* y) {
+    const float d = half_bits_to_float((uint16_t) (b[0] | (b[1] << 8)));
+    for (int j = 0; j < 16; ++j) {
+        y[j] = d * iq4_level(b[2 + j] & 15);
+        y[j + 16] = d * iq4_level(b[2 + j] >> 4);
+    }
+}
+
+// 32 consecutive values [32u, 32u+32) of an IQ4_XS block (136 bytes: fp16 d, u16 scales_h, scales_l[4], qs[128]; a 6-bit
+// scale per 32 values, minus 32; dequantize_row_iq4_xs, ggml_quants.c:1334-1356)
+__host__ __device__ inline void decode_iq4xs_32(const uint8_t* b, int u, float* y) {
+    const float d = half_bits_to_float((uint16_t) (b[0] | (b[1] << 8)));
+    const uint32_t sh = (uint32_t) b[2] | ((uint32_t) b[3] << 8);
+    const int ls = (int) ((b[4 + (u >> 1)] >> (4 * (u & 1))) & 0xF) | (int) (((sh >> (2 * u)) & 3) << 4);
+    const float dl = d * (float) (ls - 32);
+    const uint8_t* qs = b + 8 + 16 * u;
+    for (int j = 0; j < 16; ++j) {
+        y[j] = dl * iq4_level(qs[j] & 15);
+        y[j + 16] = dl * iq4_level(qs[j] >> 4);
+    }
 }
 
 // one Q8_0 block (34 bytes: fp16 d, 32 int8; src/kernels/cpu/ggml/ggml_quants.c dequantize_row_q8_0) -> 32 floats

@@ -63,7 +63,7 @@ EXPORT float orc_h2f(uint16_t h) { return h2f(h); }
 EXPORT uint16_t orc_f2h(float f) { return f2h(f); }
 
 /* ------------------------------------------------------------------------------------------------ block formats */
-enum { T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ1_M = 29, T_NVFP4 = 40 };
+enum { T_Q5_0 = 6, T_Q5_1 = 7, T_IQ4_NL = 20, T_IQ4_XS = 23, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ1_M = 29, T_NVFP4 = 40 };
 
 /* include/basalt/ggml/ggml_common.h:1029-1031 - E2M1 values, doubled */
 static const int8_t kFp4x2[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
@@ -88,6 +88,10 @@ EXPORT int64_t orc_row_bytes(int type, int64_t n) {
         case T_NVFP4: return n % 64 ? 0 : n / 64 * 36;     /* ggml_common.h:146-156 */
         case T_Q6_K: return n % 256 ? 0 : n / 256 * 210;   /* ggml_common.h:279-285 */
         case T_IQ1_M: return n % 256 ? 0 : n / 256 * 56;   /* ggml_common.h:350-362 */
+        case T_Q5_0: return n % 32 ? 0 : n / 32 * 22;      /* block_q5_0: d, qh[4], qs[16] */
+        case T_Q5_1: return n % 32 ? 0 : n / 32 * 24;      /* block_q5_1: d, m, qh[4], qs[16] */
+        case T_IQ4_NL: return n % 32 ? 0 : n / 32 * 18;    /* block_iq4_nl: d, qs[16] */
+        case T_IQ4_XS: return n % 256 ? 0 : n / 256 * 136; /* block_iq4_xs: d, scales_h, scales_l[4], qs[128] */
         case T_Q8_0: return n % 32 ? 0 : n / 32 * 34;      /* block_q8_0: fp16 d, int8 qs[32] */
         case T_Q4_K: return n % 256 ? 0 : n / 256 * 144;   /* block_q4_K: d, dmin, scales[12], qs[128] */
         case T_Q5_K: return n % 256 ? 0 : n / 256 * 176;   /* block_q5_K: d, dmin, scales[12], qh[32], qs[128] */
@@ -209,6 +213,65 @@ static void dequant_q45k(const uint8_t* b, float* y, int64_t n, int five) {
     }
 }
 
+/* src/kernels/cpu/ggml/ggml_quants.c:229-281: Q5_0 value = (nibble | fifth bit from qh) - 16, times d; Q5_1 = code x d + m. */
+static void dequant_q5_01(const uint8_t* b, float* y, int64_t n, int one) {
+    const int bs = one ? 24 : 22;
+    for (int64_t i = 0; i < n / 32; ++i, b += bs, y += 32) {
+        uint16_t dh, mh = 0;
+        uint32_t qh;
+        memcpy(&dh, b, 2);
+        if (one) memcpy(&mh, b + 2, 2);
+        memcpy(&qh, b + (one ? 4 : 2), 4);
+        const float d = h2f(dh), m = one ? h2f(mh) : 0.f;
+        const uint8_t* qs = b + (one ? 8 : 6);
+        for (int j = 0; j < 16; ++j) {
+            const int x0 = (qs[j] & 0x0F) | (int) (((qh >> j) << 4) & 0x10), x1 = (qs[j] >> 4) | (int) ((qh >> (j + 12)) & 0x10);
+            if (one) {
+                volatile float p0 = (float) x0 * d, p1 = (float) x1 * d;
+                y[j] = p0 + m;
+                y[j + 16] = p1 + m;
+            } else {
+                y[j] = (float) (x0 - 16) * d;
+                y[j + 16] = (float) (x1 - 16) * d;
+            }
+        }
+    }
+}
+
+/* include/basalt/ggml/ggml_common.h:1023-1025 */
+static const int8_t kIq4Levels[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+/* ggml_quants.c:1316-1356: IQ4_NL value = d x level[nibble]; IQ4_XS the same with a 6-bit scale (minus 32) per 32 values. */
+static void dequant_iq4(const uint8_t* b, float* y, int64_t n, int xs) {
+    if (!xs) {
+        for (int64_t i = 0; i < n / 32; ++i, b += 18, y += 32) {
+            uint16_t dh;
+            memcpy(&dh, b, 2);
+            const float d = h2f(dh);
+            for (int j = 0; j < 16; ++j) {
+                y[j] = d * kIq4Levels[b[2 + j] & 15];
+                y[j + 16] = d * kIq4Levels[b[2 + j] >> 4];
+            }
+        }
+        return;
+    }
+    for (int64_t i = 0; i < n / 256; ++i, b += 136) {
+        uint16_t dh, sh;
+        memcpy(&dh, b, 2);
+        memcpy(&sh, b + 2, 2);
+        const float d = h2f(dh);
+        const uint8_t* qs = b + 8;
+        for (int ib = 0; ib < 8; ++ib, qs += 16, y += 32) {
+            const int ls = ((b[4 + ib / 2] >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4);
+            const float dl = d * (float) (ls - 32);
+            for (int j = 0; j < 16; ++j) {
+                y[j] = dl * kIq4Levels[qs[j] & 15];
+                y[j + 16] = dl * kIq4Levels[qs[j] >> 4];
+            }
+        }
+    }
+}
+
 EXPORT int orc_dequant_row(int type, const void* src, float* y, int64_t n) {
     if (orc_row_bytes(type, n) == 0) return -1;
     if (type == T_NVFP4) dequant_nvfp4(src, y, n);
@@ -216,6 +279,10 @@ EXPORT int orc_dequant_row(int type, const void* src, float* y, int64_t n) {
     else if (type == T_Q8_0) dequant_q8_0(src, y, n);
     else if (type == T_Q4_K) dequant_q45k(src, y, n, 0);
     else if (type == T_Q5_K) dequant_q45k(src, y, n, 1);
+    else if (type == T_Q5_0) dequant_q5_01(src, y, n, 0);
+    else if (type == T_Q5_1) dequant_q5_01(src, y, n, 1);
+    else if (type == T_IQ4_NL) dequant_iq4(src, y, n, 0);
+    else if (type == T_IQ4_XS) dequant_iq4(src, y, n, 1);
     else dequant_iq1m(src, y, n);
     return 0;
 }

@@ -15,6 +15,8 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 T_Q6_K, T_IQ1_M, T_NVFP4 = 14, 29, 40
 T_Q8_0, T_Q4_K, T_Q5_K = 8, 12, 13
+T_Q5_0, T_Q5_1, T_IQ4_NL, T_IQ4_XS = 6, 7, 20, 23
+UNQUANTISED = (T_IQ1_M, T_Q8_0, T_Q4_K, T_Q5_K, T_Q5_0, T_Q5_1, T_IQ4_NL, T_IQ4_XS)   # formats the oracle has no quantiser for
 GATE_SQRT_SOFTPLUS, GATE_SIGMOID, GATE_SOFTMAX = 0, 1, 2
 
 _f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
@@ -179,11 +181,16 @@ def random_rows(t: int, rng: np.random.Generator, rows: int, cols: int) -> np.nd
     values are of order 0.02, like the quantised N(0, 0.02^2) weights of the other formats)."""
     if t == T_IQ1_M:
         return random_iq1m_rows(rng, rows, cols)
-    bs, nv, scale_at = {T_Q8_0: (34, 32, (0,)), T_Q4_K: (144, 256, (0, 2)), T_Q5_K: (176, 256, (0, 2))}[t]
+    bs, nv, scale_at = {T_Q8_0: (34, 32, (0,)), T_Q4_K: (144, 256, (0, 2)), T_Q5_K: (176, 256, (0, 2)), T_Q5_0: (22, 32, (0,)),
+                        T_Q5_1: (24, 32, (0, 2)), T_IQ4_NL: (18, 32, (0,)), T_IQ4_XS: (136, 256, (0,))}[t]
     nb = rows * cols // nv
     raw = rng.integers(0, 256, size=(nb, bs), dtype=np.uint8)
     for at in scale_at:
-        base = 0x0C00 if t == T_Q8_0 else 0x0800 if at == 0 else 0x1400    # fp16 2^-12 (x int8), 2^-13 (x 6-bit scale x code), 2^-10 (x 6-bit min)
+        # fp16 scales: Q8_0 / IQ4_NL 2^-12 (x 8-bit level), Q5_0 2^-9 (x 5-bit code), Q5_1 2^-9 and m 2^-6 (negated below: codes are
+        # unsigned), IQ4_XS 2^-15 (x 6-bit scale x level), Q4_K / Q5_K d 2^-13 (x 6-bit scale x code) and dmin 2^-10 (x 6-bit min)
+        base = {T_Q8_0: 0x0C00, T_IQ4_NL: 0x0C00, T_Q5_0: 0x1800, T_IQ4_XS: 0x0200}.get(t, 0x0800 if at == 0 else 0x1400)
+        if t == T_Q5_1:
+            base = 0x1800 if at == 0 else 0xA400
         h = (base + rng.integers(0, 0x400, size=nb)).astype(np.uint16)
         raw[:, at:at + 2] = h.view(np.uint8).reshape(nb, 2)
     return raw.reshape(-1)

@@ -22,7 +22,7 @@ int main() {
     try { native_moe_combine(nullptr, nullptr, nullptr, nullptr, 2048, 10, nullptr); } catch (const std::invalid_argument&) { threw = true; }
     if (!threw) { std::puts("combine without a stream must throw"); ++failures; }
     threw = false;
-    try { native_expert_layout(7, 7, 2048, 512); } catch (const std::invalid_argument&) { threw = true; }
+    try { native_expert_layout(9, 9, 2048, 512); } catch (const std::invalid_argument&) { threw = true; }
     if (!threw) { std::puts("unknown type must throw"); ++failures; }
     route_tail_skip(nullptr, nullptr, ResidentTabs{}, 500, 4, 1, 8, nullptr, nullptr);   // out of range: a silent no-op, as in the reference
     {

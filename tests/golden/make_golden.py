@@ -2,7 +2,7 @@
 reference checkout by oracle/Makefile).  Run in a container that has the reference; the .npz travels with the repository
 so the CPU tests can pin the oracle where the reference is absent.
 
-Contents: raw blocks of each format (NVFP4, Q6_K, IQ1_M, Q8_0, Q4_K, Q5_K) with the reference's to_float output; seeded fp32 rows with the reference quantiser's
+Contents: raw blocks of each format (NVFP4, Q6_K, IQ1_M, Q8_0, Q4_K, Q5_K, Q5_0, Q5_1, IQ4_NL, IQ4_XS) with the reference's to_float output; seeded fp32 rows with the reference quantiser's
 bytes (NVFP4, Q6_K); the reference's blob geometry for the benchmark shapes; and the reference CPU expert pool's output
 rows for a small Q6_K and a small NVFP4 layer (inputs are regenerated from the seeds stored alongside).
 """
@@ -67,7 +67,8 @@ def main():
     R.ref_pool_destroy(pool)
     # decoders of the formats added later (their own generator, so the vectors above keep their bytes)
     rng2 = np.random.default_rng(2025)
-    for name, t, nv, nblk in (("q8_0", 8, 32, 16), ("q4k", 12, 256, 3), ("q5k", 13, 256, 3)):
+    for name, t, nv, nblk in (("q8_0", 8, 32, 16), ("q4k", 12, 256, 3), ("q5k", 13, 256, 3), ("q5_0", 6, 32, 16), ("q5_1", 7, 32, 16),
+                              ("iq4nl", 20, 32, 16), ("iq4xs", 23, 256, 3)):
         raw = O.random_rows(t, rng2, 1, nblk * nv)
         y = np.empty(nblk * nv, np.float32)
         assert R.ref_dequantize(t, raw.ctypes.data, y, y.size) == 0

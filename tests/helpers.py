@@ -17,7 +17,7 @@ def make_expert_blobs(rng, n, gu_type, d_type, H, I, sigma=0.02):
     L = O.Layout(gu_type, d_type, H, I)
     blobs = []
     for _ in range(n):
-        unquantised = (O.T_IQ1_M, O.T_Q8_0, O.T_Q4_K, O.T_Q5_K)     # formats the oracle has no quantiser for: random valid blocks
+        unquantised = O.UNQUANTISED     # formats the oracle has no quantiser for: random valid blocks
         if gu_type in unquantised or d_type in unquantised:
             blob = np.zeros(L.bytes, np.uint8)
             for t, off, rows, cols in ((gu_type, 0, 2 * I, H), (d_type, L.down_off, H, I)):

@@ -23,7 +23,7 @@ def test_every_declared_symbol_is_exported(lib):
     assert declared == set(capi.exported_symbols()), declared ^ set(capi.exported_symbols())
 
 
-@pytest.mark.parametrize("name,t", [("nvfp4", 40), ("q6k", 14), ("iq1m", 29), ("q8_0", 8), ("q4k", 12), ("q5k", 13)])
+@pytest.mark.parametrize("name,t", [("nvfp4", 40), ("q6k", 14), ("iq1m", 29), ("q8_0", 8), ("q4k", 12), ("q5k", 13), ("q5_0", 6), ("q5_1", 7), ("iq4nl", 20), ("iq4xs", 23)])
 def test_host_decoders_match_reference_golden(lib, name, t):
     raw, want = np.ascontiguousarray(G[f"dec_{name}_raw"]), G[f"dec_{name}_f32"]
     got = np.empty(want.size, np.float32)
@@ -47,7 +47,7 @@ def test_layout_matches_reference_geometry(lib):
 
 def test_argument_errors(lib):
     L = capi.ExpertLayout()
-    assert lib.bsx_expert_layout_init(7, 40, -1, 2048, 512, 0.0, 0.0, 0.0, C.byref(L)) == capi.E_TYPE
+    assert lib.bsx_expert_layout_init(9, 40, -1, 2048, 512, 0.0, 0.0, 0.0, C.byref(L)) == capi.E_TYPE
     assert lib.bsx_expert_layout_init(40, 40, -1, 2000, 512, 0.0, 0.0, 0.0, C.byref(L)) == capi.E_TYPE
     assert lib.bsx_expert_supported(40, 40, -1, 2048, 512) == 1
     assert lib.bsx_expert_supported(40, 40, 14, 2048, 512) == 0

@@ -44,7 +44,8 @@ def run_grouped(L, blobs_dev, group_experts, group_tokens, x_dev, n_out_rows, ou
 
 CASES = [("nvfp4", 40, 40, 2048, 512), ("q6k", 14, 14, 2048, 512), ("iq1m", 29, 29, 2048, 512), ("nvfp4", 40, 40, 2560, 640),
          ("iq1m_q6k", 29, 14, 1024, 256), ("nvfp4_big", 40, 40, 7168, 2048), ("q8_0", 8, 8, 1024, 256), ("q4k", 12, 12, 1024, 512),
-         ("q5k", 13, 13, 1024, 256), ("q4k_q6k", 12, 14, 2048, 512)]
+         ("q5k", 13, 13, 1024, 256), ("q4k_q6k", 12, 14, 2048, 512), ("q5_0", 6, 6, 1024, 256), ("q5_1", 7, 7, 1024, 256),
+         ("iq4nl", 20, 20, 1024, 256), ("iq4xs", 23, 23, 1024, 512), ("iq4xs_q5_0", 23, 6, 1024, 256)]
 
 
 @pytest.mark.parametrize("impl", ["fast", "simple"])
@@ -154,7 +155,7 @@ def test_window_independence_bitwise(lib, cuda):
 
 
 @pytest.mark.skipif(REFG is None, reason="oracle/_ref/libref_gpu.so not built")
-@pytest.mark.parametrize("gt,dt", [(40, 40), (14, 14), (29, 29), (8, 8), (12, 12), (13, 13), (12, 14)])
+@pytest.mark.parametrize("gt,dt", [(40, 40), (14, 14), (29, 29), (8, 8), (12, 12), (13, 13), (12, 14), (6, 6), (7, 7), (20, 20), (23, 23)])
 def test_reference_grouped_kernel_agrees(lib, cuda, gt, dt):
     """the reference's own CUDA kernel on the same blobs: int8 activations cost it ~1e-2, its own bar is rel L1 < 3e-2
     (tests/kernels/native_expert_parity.cpp:372-373); both implementations must describe the same expert."""

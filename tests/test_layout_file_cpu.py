@@ -149,8 +149,8 @@ def test_refusals():
     with pytest.raises(ValueError, match="no dot product"):
         load(layout(5, b, types="9 14"))                                           # Q8_1 is an activation format, not a weight's
     # a format without kernels here still parses (the table is about bytes); the row says it cannot run yet
-    q4 = 2 * I * (H // 256 * 144) + H * (I // 32 * 24)
-    t = load(layout(5, q4, types="12 7"))
+    q23 = 2 * I * (H // 256 * 84) + H * (I // 256 * 110)                           # Q2_K gate/up, Q3_K down
+    t = load(layout(5, q23, types="10 11"))
     assert not t.rows[0].kernels and load(layout(5, b)).rows[0].kernels
     with pytest.raises(Exception, match="unsupported block format"):
         t.layout(0)
