@@ -269,6 +269,8 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         import torch.distributed as dist
+        # with NCCL_DEBUG=VERSION in the environment NCCL prints its version banner to stdout at the first collective; the JSON
+        # line below is always the last line of stdout
         dist.init_process_group("nccl", device_id=dev)
     from basalt_b200 import build, capi, moe
     if rank == 0:
