@@ -243,6 +243,17 @@ inline void moe_combine(const float* Dm, const int32_t* slot, const float* w, co
 }
 }  // namespace basalt::prefill
 
+// The step before the layer (include/basalt/kernels/window_gemm.hpp:36-40): both overloads, same argument order.  Unlike the
+// reference, which takes a null stream as the default stream, the stream must be given.
+namespace basalt::kernels::wgemm {
+inline void norm_pack(const float* x, const float* w, float eps, int64_t K, int T, void* act, float* xn, void* stream) {
+    basalt::kernels::shim_detail::raise("wgemm::norm_pack", bsx_norm_pack(x, BSX_X_F32, w, eps, K, T, act, xn, stream));
+}
+inline void norm_pack(const uint16_t* x, const float* w, float eps, int64_t K, int T, void* act, float* xn, void* stream) {
+    basalt::kernels::shim_detail::raise("wgemm::norm_pack", bsx_norm_pack(x, BSX_X_BF16, w, eps, K, T, act, xn, stream));
+}
+}  // namespace basalt::kernels::wgemm
+
 // The model file's expert table (include/basalt/kernels/cpu/expert_layout.hpp:17-35,53-65): the same struct fields a caller
 // reads (fmt holds the kernel-side layout in place of the CPU pool's NativeFmt), the same process-wide table filled by
 // expert_layout_load_text, the same bool + err contract.

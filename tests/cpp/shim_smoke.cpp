@@ -37,6 +37,9 @@ int main() {
         if (c::expert_layout_load_text("# experts v8: x\n", 2, 512, err, 2048, 512) || err.find("v8") == std::string::npos) { std::puts("v8 must be refused"); ++failures; }
         if (c::expert_layout().version != 6) { std::puts("a refused text must leave the table alone"); ++failures; }
     }
+    threw = false;
+    try { basalt::kernels::wgemm::norm_pack((const float*) nullptr, nullptr, 1e-6f, 2048, 4, nullptr, nullptr, nullptr); } catch (const std::invalid_argument&) { threw = true; }
+    if (!threw) { std::puts("norm_pack without a stream must throw"); ++failures; }
     std::printf("shim %s\n", failures ? "FAILED" : "ok");
     return failures;
 }
