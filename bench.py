@@ -237,6 +237,7 @@ def main():
     ap.add_argument("--input-norm", default="none", choices=["none", "fused", "separate"],
                     help="decode workload: the layer also applies its input RMS norm (the reference's norm_pack step) - fused with the FP4 "
                          "activation images, or as a launch of its own")
+    ap.add_argument("--act", default="bf16", choices=["bf16", "fp32"], help="decode workload: element type of the activation rows given to the layer")
     ap.add_argument("--no-fork", action="store_true", help="decode workload: the activation-image kernel runs on the step's own stream, ahead of the router, "
                                                            "instead of where the layer would put it (a forked branch beside the router for up to 16 tokens)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel of a step from the host instead of replaying the layer's CUDA graph")
@@ -308,6 +309,8 @@ def main():
     n_batches = 8
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     xs = [torch.randn((T, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
+    if args.act == "fp32":
+        xs = [x.float() for x in xs]
     stream = torch.cuda.Stream(device=dev)
 
     use_graph = not args.no_graph
@@ -343,7 +346,7 @@ def main():
         ms_total = ev0.elapsed_time(ev1)
         # ---- end to end: pinned host activations in, host output out, every step
         x_host = [x.cpu().pin_memory() for x in xs]
-        xin = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        xin = torch.empty((T, H), dtype=xs[0].dtype, device=dev)
         y_host = torch.empty((T, H), dtype=torch.float32).pin_memory()
         def e2e_step(i):
             # pinned host rows -> device (with a graph: straight into its input buffer), the step, the result -> pinned host
@@ -391,7 +394,7 @@ def main():
                        launch="one CUDA graph per step (input copied into its static buffer, device to device)" if use_graph else "one host launch per kernel",
                        input_norm={"none": "not part of the step (rows arrive normed)", "fused": "RMS norm inside the step, fused with the FP4 activation images",
                                    "separate": "RMS norm inside the step, a launch of its own"}[args.input_norm]),
-        "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
+        "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * xs[0].element_size(), "d2h_bytes_per_step": T * H * 4},
         "gpu_launches": (9 if args.input_norm == "separate" else 8) * args.steps,   # (norm,) logits, select, plan, 2 x activation images, gate/up, down, combine (the shared expert rides in the grouped call)
         "roofline": {"bound": "hbm", "kernel": ("nvf4_stream_kernel<gate/up>" if use_packed else "nvfp4_mma_kernel<gate/up>") + " (routed + shared experts; stage time includes the activation-image kernel)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
