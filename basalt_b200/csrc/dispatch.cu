@@ -7,6 +7,8 @@
 // (src/models/inkling2/kernels/ops.cu:275-340).  Here the permutation is the host path's stable counting sort, computed on
 // the device without position atomics: every warp owns a contiguous chunk of pairs, counts it, a scan turns the
 // [expert][chunk] counts into chunk bases, and each warp places its pairs in order with __match_any_sync ranks.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace bsx {
@@ -330,26 +332,28 @@ extern "C" size_t bsx_dispatch_scratch_bytes(int64_t n_pairs, int32_t E) {
 
 // Device address of the static table on the current device; looked up once per device, with that device current.
 static int32_t* static_dispatch_table(int32_t* status) {
-    static int32_t* cached[64] = {};
+    static std::atomic<int32_t*> cached[64];   // per device; two host threads racing on a first call store the same address
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) { *status = (int32_t) e; return nullptr; }
     if (dev < 0 || dev >= 64) { *status = (int32_t) cudaErrorInvalidDevice; return nullptr; }
-    if (!cached[dev]) {
+    int32_t* tbl = cached[dev].load(std::memory_order_acquire);
+    if (!tbl) {
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_dispatch_tbl);
         if (e != cudaSuccess) { *status = (int32_t) e; return nullptr; }
-        cached[dev] = static_cast<int32_t*>(p);
+        tbl = static_cast<int32_t*>(p);
+        cached[dev].store(tbl, std::memory_order_release);
     }
     *status = BSX_OK;
-    return cached[dev];
+    return tbl;
 }
 
 extern "C" int32_t bsx_dispatch_static(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t E, int32_t* cnt, int32_t* off,
                                        int32_t* slot, int32_t* src, void* stream) {
     if (!stream) return BSX_E_STREAM;
-    if (E < 1 || E > kMaxExpert || k < 1 || n_pairs < 0) return BSX_E_GEOMETRY;
-    if (n_pairs > kStaticMaxPairs) return BSX_E_LIMIT;   // beyond the resident table: use bsx_dispatch with caller scratch
+    if (E < 1 || k < 1 || n_pairs < 0) return BSX_E_GEOMETRY;
+    if (n_pairs > kStaticMaxPairs || E > kMaxExpert) return BSX_E_LIMIT;   // beyond the resident table: use bsx_dispatch with caller scratch
     int32_t status = BSX_OK;
     int32_t* tbl = static_dispatch_table(&status);
     if (!tbl) return status;
@@ -385,7 +389,7 @@ static int32_t plan_launch(const int32_t* ids, int32_t T, int32_t k, int32_t E, 
     const int64_t n = (int64_t) T * k;
     if (n <= 0) return BSX_OK;   // the reference returns without touching its outputs (ops.cu:491)
     if (n > BSX_PLAN_MAX_PAIRS) return BSX_E_LIMIT;
-    if (E < 1 || E > 4096) return BSX_E_GEOMETRY;
+    if (E < 1 || E > BSX_PLAN_MAX_EXPERTS) return BSX_E_GEOMETRY;   // E * 16 + n * 4 bytes of shared memory must stay below 48 KB
     if (!ids || !blob_table || !ptr || !start || !n_groups || !dst || !tok) return BSX_E_POINTER;
     const size_t smem = (size_t) E * (sizeof(unsigned long long) + 2 * sizeof(int32_t)) + (size_t) n * sizeof(int32_t);
     moe_plan_kernel<<<1, 1024, smem, (cudaStream_t) stream>>>(ids, (int) n, k, E, blob_table, shared_blob, T, ptr, start, n_groups, dst, tok);

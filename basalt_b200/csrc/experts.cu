@@ -1,5 +1,6 @@
 // experts.cu - entry points of the expert stage: blob geometry, q8_1 activation rows, the grouped decode experts and the
 // weighted combine.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -18,15 +19,17 @@ const uint16_t h_iq1_grid[2048] = {
 };
 
 const uint16_t* device_grid() {
-    static const uint16_t* cached[64] = {};
+    static std::atomic<const uint16_t*> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (!cached[dev]) {
+    const uint16_t* g = cached[dev].load(std::memory_order_acquire);
+    if (!g) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_iq1_grid) != cudaSuccess) return nullptr;
-        cached[dev] = static_cast<const uint16_t*>(p);
+        g = static_cast<const uint16_t*>(p);
+        cached[dev].store(g, std::memory_order_release);
     }
-    return cached[dev];
+    return g;
 }
 
 // src/kernels/cuda/iq_kernels.cu:2471-2503 with include/basalt/kernels/q8_1_finite.hpp:17-31: a warp per 32 values

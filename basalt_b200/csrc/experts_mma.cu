@@ -16,6 +16,7 @@
 // Semantics: Basalt's native_expert_grouped (include/basalt/kernels/iq_kernels.hpp:77-92; kernels src/kernels/cuda/iq_kernels.cu:
 // 1605-1658 gate/up, :2512-2524 SwiGLU, :2140-2164 down), NVFP4 decoding per src/kernels/cpu/ggml/ggml_quants.c:1397-1422,
 // tail scales per iq_kernels.cu:683-701 - but without the int8 rounding of x and h the reference applies.
+#include <atomic>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -410,13 +411,13 @@ template <int MODE, int TERMS>
 int32_t launch(const ExpertArgs& a, const __half* img, const float* inv, const int2* items, int* n_items, cudaStream_t st) {
     const int64_t K = MODE == MODE_GU ? a.L.n_embd : a.L.n_ff;
     const size_t smem = smem_bytes(K);
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];   // per device; threads of different devices call concurrently
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
-    if (!configured[dev]) {
+    if (!configured[dev].load(std::memory_order_acquire)) {
         const cudaError_t e = cudaFuncSetAttribute(nvfp4_mma_kernel<MODE, TERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int32_t) e;
-        configured[dev] = true;
+        configured[dev].store(true, std::memory_order_release);
     }
     const int64_t rows = MODE == MODE_GU ? a.L.n_ff : a.L.n_embd;
     // a work unit streams ~150 KB of weights (enough to hide its start-up: activation copy, first loads); the row tiles of an

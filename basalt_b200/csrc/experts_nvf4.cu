@@ -28,6 +28,7 @@
 // the next.  Every mbarrier wait is time-bounded and reports through a status word.
 //
 // Semantics: Basalt's native_expert_grouped (include/basalt/kernels/iq_kernels.hpp:77-92) without its int8 rounding of x, h.
+#include <atomic>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -473,13 +474,13 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
 
 template <int MODE>
 int32_t launch_stream(const StreamArgs& sa, cudaStream_t st) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];   // per device; threads of different devices call concurrently
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
-    if (!configured[dev]) {
+    if (!configured[dev].load(std::memory_order_acquire)) {
         const cudaError_t e = cudaFuncSetAttribute(nvf4_stream_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemF);
         if (e != cudaSuccess) return (int32_t) e;
-        configured[dev] = true;
+        configured[dev].store(true, std::memory_order_release);
     }
     nvf4_stream_kernel<MODE><<<(unsigned) sm_count(), kThreadsF, kSmemF, st>>>(sa);
     return launch_status();

@@ -21,6 +21,7 @@
 // Both operands use the SAME permutation of k inside each 16-column group, (0,8,1,9,...,7,15) - the order cvt.e2m1x2 emits
 // a sub-block's values in - so no shuffling is needed: the activation image (made by a small kernel here) and the SwiGLU
 // output are simply written in that order.
+#include <atomic>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -442,16 +443,16 @@ extern "C" int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const un
     a.h = reinterpret_cast<__half*>(p);
     a.dm = dm;
     a.status = status;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];   // per device; threads of different devices call concurrently
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
-    if (!configured[dev]) {
+    if (!configured[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_GU, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_GU, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_DOWN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_DOWN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
         if (e != cudaSuccess) return (int32_t) e;
-        configured[dev] = true;
+        configured[dev].store(true, std::memory_order_release);
     }
     prefill_prep_x_kernel<<<(unsigned) ((n_tokens + 7) / 8), 256, 0, st>>>(x, x_kind, n_tokens, L.n_embd, xh, xinv);
     // persistent CTAs, one per SM; rows that are whole 144-byte chunks (K % 256 == 0) take the variant with 16-byte weight loads

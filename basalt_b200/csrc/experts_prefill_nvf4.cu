@@ -18,6 +18,7 @@
 // gathers into four swizzled A tiles, scale words through registers into the lane-major order tcgen05.cp reads; warps 6-9:
 // epilogue (thread = TMEM lane = row).  Two stages of 256 columns; every wait is time-bounded with a status word.
 // With n_ff <= 512 the down product runs as prefill_down_resident_kernel instead (the tile's rows stay in shared memory).
+#include <atomic>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -646,13 +647,13 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_down_resident_kernel(Pre
 
 template <int KC>
 int32_t launch_down_resident(const PrefillFArgs& a, cudaStream_t st) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];   // per device; threads of different devices call concurrently
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
-    if (!configured[dev]) {
+    if (!configured[dev].load(std::memory_order_acquire)) {
         const cudaError_t e = cudaFuncSetAttribute(prefill_down_resident_kernel<KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) GeoR<KC>::kSmem);
         if (e != cudaSuccess) return (int32_t) e;
-        configured[dev] = true;
+        configured[dev].store(true, std::memory_order_release);
     }
     prefill_down_resident_kernel<KC><<<(unsigned) sm_count(), kThreadsQ, GeoR<KC>::kSmem, st>>>(a);
     return launch_status();
@@ -662,13 +663,13 @@ size_t al256q(size_t v) { return (v + 255) & ~(size_t) 255; }
 
 template <int MODE>
 int32_t launch_q(const PrefillFArgs& a, cudaStream_t st) {
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];   // per device; threads of different devices call concurrently
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
-    if (!configured[dev]) {
+    if (!configured[dev].load(std::memory_order_acquire)) {
         const cudaError_t e = cudaFuncSetAttribute(prefill_nvf4_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) Geo<MODE>::kSmem);
         if (e != cudaSuccess) return (int32_t) e;
-        configured[dev] = true;
+        configured[dev].store(true, std::memory_order_release);
     }
     prefill_nvf4_kernel<MODE><<<(unsigned) sm_count(), kThreadsQ, Geo<MODE>::kSmem, st>>>(a);
     return launch_status();

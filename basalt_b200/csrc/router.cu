@@ -10,6 +10,7 @@
 #define BSX_SOFTMAX_RECIPROCAL 0
 #include "router_softmax.cuh"
 
+#include <atomic>
 #include <climits>
 
 namespace bsx {
@@ -17,15 +18,15 @@ namespace bsx {
 int32_t softmax_fast(const float* logits, int64_t T, int E, int k, int32_t* ids, float* w, cudaStream_t st);
 
 int sm_count() {
-    static int cached[64] = {};
+    static std::atomic<int> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
 namespace {

@@ -13,6 +13,7 @@
 // One CTA per (128 tokens, 256 experts) tile: warp 0 allocates 256 TMEM columns and its lane 0 issues the MMAs; warp 1
 // loads activation rows, warps 2-3 gate rows (cp.async into 128-byte-swizzled stages, 4-stage mbarrier ring, every wait
 // time-bounded); warps 4-7 are the epilogue (thread = TMEM lane = token).
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -246,13 +247,13 @@ extern "C" int32_t bsx_router_logits_prefill(const void* x, int32_t x_kind, cons
     a.E = E;
     a.H = H;
     a.x_terms = x_kind == BSX_X_BF16 ? 1 : 2;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64];   // per device; threads of different devices call concurrently
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
-    if (!configured[dev]) {
+    if (!configured[dev].load(std::memory_order_acquire)) {
         const cudaError_t e = cudaFuncSetAttribute(router_logits_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemR);
         if (e != cudaSuccess) return (int32_t) e;
-        configured[dev] = true;
+        configured[dev].store(true, std::memory_order_release);
     }
     rows_to_fp16_planes_kernel<<<(unsigned) ((T + 7) / 8), 256, 0, st>>>(x, x_kind, T, H, a.x_terms, ximg, xinv);
     rows_to_fp16_planes_kernel<<<(unsigned) ((E + 7) / 8), 256, 0, st>>>(gate, BSX_X_F32, E, H, 2, gimg, ginv);

@@ -224,6 +224,10 @@ class EPMoELayer:
         self.time_experts, self.last_expert_ms, self.last_groups = False, 0.0, 0
         self.graph = None
 
+    def check_status(self):
+        """Raises moe.KernelWaitTimeout if a kernel of a step since the last check gave up on a bounded wait; clears the word."""
+        self.moe.read_status(self.status, "EPMoELayer")
+
     def capture(self, x_example):
         """Records forward() into a CUDA graph (NCCL collectives included).  Every rank must capture, and replay, in step."""
         torch = self.torch
@@ -367,6 +371,10 @@ class EPPrefillMoELayer:
             self.s_ntiles = torch.tensor([nt], dtype=i32, device=dev)
             self.s_scratch = torch.empty(scr(C.byref(layout), T, T), dtype=u8, device=dev)
             self.s_dm = torch.empty((T, H), dtype=f32, device=dev)
+
+    def check_status(self):
+        """Raises moe.KernelWaitTimeout if a kernel of a step since the last check gave up on a bounded wait; clears the word."""
+        self.moe.read_status(self.status, "EPPrefillMoELayer")
 
     def forward(self, x):
         torch, dist, moe, capi = self.torch, self.dist, self.moe, self.capi

@@ -286,6 +286,24 @@ def moe_combine(rows, slot, weights, shared=None, shared_gate=None, y=None, stre
     return y
 
 
+class KernelWaitTimeout(RuntimeError):
+    """A bounded wait inside a tcgen05 kernel ran out (the kernel returned early instead of hanging): the step's output is
+    not complete."""
+
+
+def read_status(status: Optional[torch.Tensor], what: str) -> None:
+    """Reads a layer's device status word and clears it; raises KernelWaitTimeout when a kernel reported a wait that ran out.
+    This is a device-to-host read (it synchronises the current stream), so call it where the caller synchronises anyway:
+    after reading a step's output, or every so many graph replays."""
+    if status is None:
+        return
+    v = int(status.item())
+    if v != 0:
+        status.zero_()
+        raise KernelWaitTimeout(f"{what}: kernel status word {v:#x}: a bounded wait inside a kernel gave up; the output of the steps since the "
+                                "last check is not valid")
+
+
 class MoELayer:
     """One resident MoE layer: router gate, routed expert blobs, optional shared expert, run as the reference's decode
     window does (inkling2/session.cpp:680-716): router -> moe_plan -> native_expert_grouped -> combine.  A shared expert
@@ -347,6 +365,12 @@ class MoELayer:
             self.s_out = torch.empty((max_tokens, layout.n_embd), dtype=f32, device=dev)
             self.s_scratch = torch.empty(native_expert_scratch_bytes(self.shared_L, max_tokens), dtype=torch.uint8, device=dev)
             self._s_T = -1
+
+    def check_status(self) -> None:
+        """Raises KernelWaitTimeout if any step since the last check hit a bounded wait that ran out (the tcgen05 kernels give up
+        after 200 ms instead of hanging and set a status word); clears the word.  Synchronises: call it where the output is
+        read on the host."""
+        read_status(getattr(self, "status", None), "MoELayer")
 
     def capture(self, x_example: torch.Tensor):
         """Records forward() for max_tokens rows of x_example's dtype into a CUDA graph (every call of the step is
@@ -501,6 +525,10 @@ class PrefillMoELayer:
         self.rscratch = torch.empty(capi.lib().bsx_router_logits_prefill_scratch_bytes(T, E, layout.n_embd), dtype=torch.uint8, device=dev)
         self.y = torch.empty((T, layout.n_embd), dtype=f32, device=dev)
         self.events = None      # set to a list to collect (name, event) marks between the stages
+
+    def check_status(self) -> None:
+        """See MoELayer.check_status."""
+        read_status(self.status, "PrefillMoELayer")
 
     def _mark(self, name, stream):
         if self.events is not None:

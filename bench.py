@@ -370,6 +370,18 @@ def main():
         # ---- per-stage device times for the roofline (same steps, events between the C ABI calls)
         stage_ms, gu_bytes = instrumented_pass(layers, xs, None, stream, min(args.steps, 100), L)
         barrier()
+        # ---- the run is only a number if no kernel gave up on a bounded wait and a step's output is right
+        for ly in layers:
+            ly.check_status()
+        if use_packed and args.input_norm == "none" and args.shape == "c1":
+            y_fast = step(0, xs[0]).clone()
+            twin = moe.MoELayer(gate, bias, blobs_ggml[:E], L, rargs, shared_blob=blobs_ggml[E], max_tokens=T)   # ggml blobs in place, fp16 images
+            y_ref = twin.forward(xs[0], None, stream)
+            stream.synchronize()
+            err = float((y_fast - y_ref).norm() / y_ref.norm())
+            if not err < 1e-3:
+                raise SystemExit(f"bench: the timed path's output differs from the in-place fp16 path (relative L2 {err:.3e})")
+            del twin
 
     times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:

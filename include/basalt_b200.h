@@ -60,6 +60,7 @@ enum { BSX_OUT_F32 = 0, BSX_OUT_BF16 = 1 };
 #define BSX_MAX_HELD_TABS 4      /* ResidentTabs::kMax, include/basalt/kernels/route_lossy.hpp:20 */
 #define BSX_TAIL_SKIP_MAX 128    /* kRouteTailSkipMax, route_lossy.hpp:33 */
 #define BSX_PLAN_MAX_PAIRS 1024  /* moe_plan's limit, src/models/inkling2/kernels/ops.cu:493 */
+#define BSX_PLAN_MAX_EXPERTS 2048 /* bsx_moe_plan[_shared]: the expert table lives in 48 KB of shared memory */
 
 /* ---- a1: router logits.  Replaces the logits stage of basalt::kernels::router (include/basalt/kernels/router.hpp:30-32,
  * src/kernels/cuda/router.cu:49-146,233-253).  logits[t][e] = gate[e] . x[t]; x [T][H] fp32, gate [E][H] fp32 row-major,
@@ -134,7 +135,7 @@ BSX_API int32_t bsx_dispatch(const int32_t* ids, int64_t n_pairs, int32_t k, int
  * that every GPU holding the library carries until the process exits.  It allocates nothing, ever.
  * Limits: n_pairs <= 65536 and E <= 1024; a larger call is refused with BSX_E_LIMIT (use bsx_dispatch with your own scratch).
  * No tile list.  The first call on each device looks the array's address up (with that device current) and should be made
- * before any stream capture begins; later calls only launch.  All calls on a device share the one table, which keeps
+ * before any stream capture begins; later calls only launch (two host threads may make that first call at once).  All calls on a device share the one table, which keeps
  * whatever the previous call left (each call overwrites every entry it reads, so nothing has to start at zero): two calls
  * that overlap on the GPU - different streams, or a graph replayed while another call runs - race and give wrong rows.
  * Results are those of bsx_dispatch, bit for bit. */
@@ -148,7 +149,7 @@ BSX_API int32_t bsx_gather_rows(const void* x, int64_t row_bytes, const int32_t*
 /* ---- a6, decode-window form.  Replaces inkling2 moe_plan (src/models/inkling2/kernels/ops.cu:275-340,488-498): the experts
  * with pairs and a non-zero blob address become groups in ascending expert order (ptr[g], start[g]; start[n_groups] =
  * start[n_groups+1] = entries), entries inside a group in pair order, dst[entry] = pair index (the output row),
- * tok[entry] = pair / k.  T * k <= 1024; ids outside [0, E) are skipped. */
+ * tok[entry] = pair / k.  T * k <= 1024 (BSX_E_LIMIT beyond), E <= 2048 (BSX_E_GEOMETRY beyond); ids outside [0, E) are skipped. */
 BSX_API int32_t bsx_moe_plan(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table,
                      unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok, void* stream);
 

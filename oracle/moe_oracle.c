@@ -485,15 +485,14 @@ static float gate_score(float x, int kind) {
  * the experts form n_group contiguous groups, a group scores the sum of its two largest biased scores, the topk_group
  * best groups (lower group index on a tie) stay and the others cannot be chosen.  n_group <= 1 is the reference's plain
  * selection.  `held` ([E] slot or -1, may be null) and `prior` follow router.cu:180 (--route-prior). */
-EXPORT void orc_router_select(const float* logits, const float* bias, int T, int E, int k, int kind, float scale,
-                              int n_group, int topk_group, float prior, const int32_t* held, int32_t* ids, float* weights) {
+static void router_select_impl(const float* logits, const float* scores, const float* bias, int T, int E, int k, int kind, float scale,
+                               int n_group, int topk_group, float prior, const int32_t* held, int32_t* ids, float* weights) {
     float* s = malloc(sizeof(float) * (size_t) E);
     float* b = malloc(sizeof(float) * (size_t) E);
     char* live = malloc((size_t) E);
     for (int t = 0; t < T; ++t) {
-        const float* lg = logits + (size_t) t * E;
         for (int e = 0; e < E; ++e) {
-            s[e] = gate_score(lg[e], kind);
+            s[e] = scores ? scores[(size_t) t * E + e] : gate_score(logits[(size_t) t * E + e], kind);
             b[e] = s[e] + (bias ? bias[e] : 0.f);
             if (held && prior > 0.f && held[e] >= 0) b[e] += prior;
             live[e] = 1;
@@ -532,6 +531,18 @@ EXPORT void orc_router_select(const float* logits, const float* bias, int T, int
     free(s);
     free(b);
     free(live);
+}
+
+EXPORT void orc_router_select(const float* logits, const float* bias, int T, int E, int k, int kind, float scale,
+                              int n_group, int topk_group, float prior, const int32_t* held, int32_t* ids, float* weights) {
+    router_select_impl(logits, NULL, bias, T, E, k, kind, scale, n_group, topk_group, prior, held, ids, weights);
+}
+
+/* The same selection from gate scores computed elsewhere (the device's own expf / logf results): everything after the score
+ * is fp32 IEEE arithmetic, so with the device's scores the ids and the weight bits must equal the device's. */
+EXPORT void orc_router_select_scores(const float* scores, const float* bias, int T, int E, int k, float scale,
+                                     int n_group, int topk_group, float prior, const int32_t* held, int32_t* ids, float* weights) {
+    router_select_impl(NULL, scores, bias, T, E, k, 1, scale, n_group, topk_group, prior, held, ids, weights);
 }
 
 /* src/models/qwen4exp/prefill/kernels.cu:351-390 generalised from (512 | 256 experts, top-10) to E % 32 == 0, k <= 32:

@@ -53,6 +53,8 @@ def lib() -> C.CDLL:
         L.orc_router_logits.argtypes = [_f32p, _f32p, C.c_int, C.c_int, C.c_int, _f32p]
         L.orc_router_select.argtypes = [_f32p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int,
                                         C.c_float, C.c_void_p, _i32p, _f32p]
+        L.orc_router_select_scores.argtypes = [_f32p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_float,
+                                               C.c_void_p, _i32p, _f32p]
         L.orc_router_softmax.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, _f32p]
         L.orc_router_top10.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, _i32p, _f32p]
         L.orc_route_tail_skip.argtypes = [_i32p, _f32p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
@@ -243,6 +245,19 @@ def router_select(logits, bias, k, kind, scale=1.0, n_group=1, topk_group=1, pri
         bias = None if bias is None else np.ascontiguousarray(bias, np.float32)
         held = None if held is None else np.ascontiguousarray(held, np.int32)
         lib().orc_router_select(logits, _ptr(bias), T, E, k, kind, scale, n_group, topk_group, prior, _ptr(held), ids, w)
+    return ids, w
+
+
+def router_select_scores(scores, bias, k, scale=1.0, n_group=1, topk_group=1, prior=0.0, held=None):
+    """router_select from gate scores already computed (e.g. by the device, so that no libm / device expf difference enters):
+    the group-limited step, the ranks and the weights in fp32, bit for bit what the device kernels must give."""
+    scores = np.ascontiguousarray(scores, np.float32)
+    T, E = scores.shape
+    ids = np.zeros((T, k), np.int32)
+    w = np.zeros((T, k), np.float32)
+    bias = None if bias is None else np.ascontiguousarray(bias, np.float32)
+    held = None if held is None else np.ascontiguousarray(held, np.int32)
+    lib().orc_router_select_scores(scores, _ptr(bias), T, E, k, scale, n_group, topk_group, prior, _ptr(held), ids, w)
     return ids, w
 
 
