@@ -36,8 +36,27 @@ class LayoutInfo(C.Structure):
                 ("max_blob", C.c_uint64), ("total", C.c_uint64)]
 
 
+class MoELayerDesc(C.Structure):
+    _fields_ = [("layout", ExpertLayout), ("shared_layout", ExpertLayout),
+                ("n_expert", C.c_int32), ("top_k", C.c_int32), ("gate_kind", C.c_int32), ("n_group", C.c_int32), ("topk_group", C.c_int32),
+                ("packed", C.c_int32), ("flags", C.c_int32), ("weight_scale", C.c_float), ("norm_eps", C.c_float),
+                ("gate", C.c_void_p), ("bias", C.c_void_p), ("blob_table", C.c_void_p), ("shared_blob", C.c_uint64), ("norm_w", C.c_void_p)]
+
+
+class MoELayerViews(C.Structure):
+    _fields_ = [("logits", C.c_void_p), ("ids", C.c_void_p), ("weights", C.c_void_p), ("n_groups", C.c_void_p), ("grp_start", C.c_void_p),
+                ("ent_dst", C.c_void_p), ("ent_tok", C.c_void_p), ("rows", C.c_void_p)]
+
+
+LAYER_NO_PDL = 1
+
 P = C.c_void_p
 _SIGNATURES = {
+    "bsx_combine_residual": (C.c_int32, [P, P, P, P, P, P, C.c_int32, C.c_int32, C.c_int32, P, P]),
+    "bsx_route_plan": (C.c_int32, [P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_int32, C.c_int32, P, C.c_uint64, P, P, P, P, P, P, P, P]),
+    "bsx_moe_layer_workspace_bytes": (C.c_size_t, [C.POINTER(MoELayerDesc), C.c_int32]),
+    "bsx_moe_layer_views": (C.c_int32, [C.POINTER(MoELayerDesc), C.c_int32, P, C.POINTER(MoELayerViews)]),
+    "bsx_moe_layer": (C.c_int32, [C.POINTER(MoELayerDesc), P, C.c_int32, C.c_int32, C.c_int32, P, P, P, P, P]),
     "bsx_router_logits": (C.c_int32, [P, P, C.c_int32, C.c_int32, C.c_int32, P, P]),
     "bsx_router_select": (C.c_int32, [P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_int32, C.c_int32,
                                       C.c_float, P, C.c_int32, P, P, P]),

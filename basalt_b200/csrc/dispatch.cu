@@ -10,6 +10,8 @@
 #include <atomic>
 
 #include "common.cuh"
+#include "pdl.cuh"
+#include "plan.cuh"
 
 namespace bsx {
 namespace {
@@ -41,33 +43,6 @@ dispatch_count_kernel(const int32_t* __restrict__ ids, int64_t n, int E, int n_c
         }
         for (int e = lane; e < E; e += 32) tbl[(size_t) e * n_chunks + c] = h[e];
     }
-}
-
-// block-wide exclusive sum (blockDim a multiple of 32, at most 1024); *total = the block's sum
-__device__ int block_excl_sum(int v, int* total, int* sh) {
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    int x = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int y = __shfl_up_sync(kFull, x, o);
-        if (lane >= o) x += y;
-    }
-    if (lane == 31) sh[w] = x;
-    __syncthreads();
-    if (w == 0) {
-        int s = lane < nw ? sh[lane] : 0;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int y = __shfl_up_sync(kFull, s, o);
-            if (lane >= o) s += y;
-        }
-        sh[lane] = s;
-    }
-    __syncthreads();
-    const int r = x - v + (w > 0 ? sh[w - 1] : 0);
-    *total = sh[nw - 1];
-    __syncthreads();
-    return r;
 }
 
 // Prompt-sized dispatches (hundreds of chunks): step (1) of dispatch_scan_kernel as its own launch, one warp per expert over
@@ -177,78 +152,20 @@ dispatch_place_kernel(const int32_t* __restrict__ ids, int64_t n, int k, int E, 
 }
 
 // ---------------------------------------------------------------------------------------------- decode-window plan
-// One block of 1024 threads, everything in shared memory and nothing serial: the pairs are counted per expert with
-// shared-memory atomics, a block scan over the experts gives each used expert its group and first entry, and every pair
-// finds its place by counting the earlier pairs that name the same expert (the reference's rule, ops.cu:331-339), so an
-// expert's entries keep the order of the pairs and no position comes from an atomic.
+// One block of 1024 threads, everything in shared memory (plan.cuh).
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsigned long long* __restrict__ blobs,
                 unsigned long long shared_blob, int n_tok, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
                 int32_t* __restrict__ n_groups, int32_t* __restrict__ dst, int32_t* __restrict__ tok) {
     extern __shared__ unsigned long long smb[];
-    unsigned long long* blob = smb;                               // [E]
-    int32_t* count = reinterpret_cast<int32_t*>(smb + E);         // [E]
-    int32_t* first = count + E;                                   // [E]: the expert's first entry
-    int32_t* sid = first + E;                                     // [n]: the ids (-1: no entry)
-    __shared__ int sh[32];
-    __shared__ int s_tot[2];
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        blob[e] = blobs[e];
-        count[e] = 0;
-    }
+    const PlanSmem ps = plan_smem(smb, E);
+    plan_load_blobs(ps, blobs, E);       // constant addresses: before the wait for the kernel that wrote the ids
+    pdl_wait();
+    pdl_launch_dependents();
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        int e = ids[i];
-        if ((unsigned) e >= (unsigned) E || !blob[e]) e = -1;
-        sid[i] = e;
-        if (e >= 0) atomicAdd(&count[e], 1);
-    }
+    for (int i = threadIdx.x; i < n; i += blockDim.x) plan_note_pair(ps, i, ids[i], E);
     __syncthreads();
-    int at = 0, g = 0;   // running totals over the expert chunks of blockDim.x
-    for (int e0 = 0; e0 < E; e0 += blockDim.x) {
-        const int e = e0 + threadIdx.x;
-        const int c = e < E ? count[e] : 0;
-        int rows = 0, used = 0;
-        const int o = block_excl_sum(c, &rows, sh);
-        const int u = block_excl_sum(c > 0 ? 1 : 0, &used, sh);
-        if (e < E) first[e] = at + o;
-        if (c > 0) {
-            ptr[g + u] = blob[e];
-            start[g + u] = at + o;
-        }
-        at += rows;
-        g += used;
-    }
-    if (shared_blob != 0ull && n_tok > 0) {
-        // the shared expert: one more group holding every token, its rows after the routed pairs' rows
-        if (threadIdx.x == 0) {
-            ptr[g] = shared_blob;
-            start[g] = at;
-        }
-        for (int t = threadIdx.x; t < n_tok; t += blockDim.x) {
-            dst[at + t] = n + t;
-            tok[at + t] = t;
-        }
-        at += n_tok;
-        ++g;
-    }
-    if (threadIdx.x == 0) {
-        start[g] = at;
-        start[g + 1] = at;
-        *n_groups = g;
-    }
-    __syncthreads();   // first[] is complete
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const int e = sid[i];
-        if (e < 0) continue;
-        int before = 0;
-        int j = 0;
-        for (; j + 4 <= i; j += 4) before += (sid[j] == e) + (sid[j + 1] == e) + (sid[j + 2] == e) + (sid[j + 3] == e);
-        for (; j < i; ++j) before += sid[j] == e;
-        const int p = first[e] + before;
-        dst[p] = i;
-        tok[p] = i / k;
-    }
+    plan_finish(ps, n, k, E, shared_blob, n_tok, ptr, start, n_groups, dst, tok, nullptr, nullptr);
 }
 
 // Groups for the experts this device holds, from a dispatch: the experts with rows and a non-zero blob address become
@@ -392,7 +309,7 @@ static int32_t plan_launch(const int32_t* ids, int32_t T, int32_t k, int32_t E, 
     if (E < 1 || E > BSX_PLAN_MAX_EXPERTS) return BSX_E_GEOMETRY;   // E * 16 + n * 4 bytes of shared memory must stay below 48 KB
     if (!ids || !blob_table || !ptr || !start || !n_groups || !dst || !tok) return BSX_E_POINTER;
     const size_t smem = (size_t) E * (sizeof(unsigned long long) + 2 * sizeof(int32_t)) + (size_t) n * sizeof(int32_t);
-    moe_plan_kernel<<<1, 1024, smem, (cudaStream_t) stream>>>(ids, (int) n, k, E, blob_table, shared_blob, T, ptr, start, n_groups, dst, tok);
+    launch_k(moe_plan_kernel, dim3(1), dim3(1024), smem, (cudaStream_t) stream, ids, (int) n, k, E, blob_table, shared_blob, (int) T, ptr, start, n_groups, dst, tok);
     return launch_status();
 }
 

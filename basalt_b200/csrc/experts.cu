@@ -7,6 +7,7 @@
 #include "common.cuh"
 #include "experts.cuh"
 #include "formats.cuh"
+#include "pdl.cuh"
 
 namespace bsx {
 namespace {
@@ -62,10 +63,12 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const float* __restr
 // src/models/qwen4exp/prefill/kernels.cu:438-449 (bit-equal forms).  A thread owns 4 consecutive columns.
 __global__ void __launch_bounds__(128)
 combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ slot, const float* __restrict__ w,
-               const float* __restrict__ shared, const float* __restrict__ sg, int k, int H, int pair0, const int32_t* __restrict__ ids,
-               int e_lo, int e_hi, float* __restrict__ y) {
+               const float* __restrict__ shared, const float* __restrict__ sg, const float* __restrict__ resid, int k, int H, int pair0,
+               const int32_t* __restrict__ ids, int e_lo, int e_hi, float* __restrict__ y) {
     __shared__ int s_row[64];
     __shared__ float s_w[64];
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.y;
     if (threadIdx.x < k) {
         int r = slot ? slot[(size_t) t * k + threadIdx.x] : pair0 + t * k + (int) threadIdx.x;
@@ -111,6 +114,10 @@ combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ slot,
         } else {
             s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
         }
+    }
+    if (resid) {   // the step after the layer: the residual stream's row, one more rounded add
+        const float4 r = reinterpret_cast<const float4*>(resid + (size_t) t * H)[c4];
+        s.x += r.x; s.y += r.y; s.z += r.z; s.w += r.w;
     }
     reinterpret_cast<float4*>(y + (size_t) t * H)[c4] = s;
 }
@@ -222,7 +229,8 @@ extern "C" int32_t bsx_expert_layout_init(int32_t gu_type, int32_t d_type, int32
 extern "C" size_t bsx_expert_scratch_bytes(const bsx_expert_layout* L, int64_t cap_entries) {
     if (!L || cap_entries < 0 || L->n_ff <= 0 || L->n_embd <= 0) return 0;
     const size_t f = (((size_t) cap_entries * (size_t) L->n_ff * sizeof(float)) + 255) & ~(size_t) 255;
-    return f + experts_mma_scratch_bytes(cap_entries, L->n_embd, L->n_ff) + 4096;
+    const size_t m = experts_mma_scratch_bytes(cap_entries, L->n_embd, L->n_ff), q = experts_kq_scratch_bytes(cap_entries, L->n_embd, L->n_ff);
+    return f + (m > q ? m : q) + 4096;
 }
 
 extern "C" int32_t bsx_quantize_q8_1_rows(const float* x, int64_t n_rows, int64_t n_cols, void* y, void* stream) {
@@ -272,7 +280,9 @@ static int32_t experts_grouped_impl(int32_t n_x_rows, const bsx_expert_layout* l
     // BSX_EXPERT_IMPL=simple forces the plain kernels (tests compare the two paths)
     static const bool force_simple = [] { const char* e = getenv("BSX_EXPERT_IMPL"); return e && !strcmp(e, "simple"); }();
     if (!force_simple) {
-        const int32_t rc = experts_grouped_mma(a, st);
+        int32_t rc = experts_grouped_mma(a, st);      // NVFP4 blobs: fp16 images, mma.sync
+        if (rc != BSX_E_TYPE) return rc;
+        rc = experts_grouped_kq(a, st);               // Q6_K / IQ1_M blobs: int8 images, integer mma.sync
         if (rc != BSX_E_TYPE) return rc;
     }
     return experts_grouped_simple(a, st);
@@ -331,28 +341,33 @@ extern "C" int32_t bsx_gated_mlp(const bsx_expert_layout* layout, const void* bl
 }
 
 static int32_t combine_impl(const float* rows, const int32_t* slot, const float* weights, const float* shared, const float* shared_gate,
-                            int32_t T, int32_t k, int32_t H, const int32_t* ids, int32_t e_lo, int32_t e_hi, float* y, void* stream) {
+                            const float* resid, int32_t T, int32_t k, int32_t H, const int32_t* ids, int32_t e_lo, int32_t e_hi, float* y, void* stream) {
     if (!stream) return BSX_E_STREAM;
     if (T < 0 || k < 1 || k > 64 || H < 4 || H % 4) return BSX_E_GEOMETRY;
     if (T == 0) return BSX_OK;
-    if (!aligned(rows, 16) || !weights || !aligned(y, 16) || (shared && !aligned(shared, 16))) return BSX_E_POINTER;
+    if (!aligned(rows, 16) || !weights || !aligned(y, 16) || (shared && !aligned(shared, 16)) || (resid && !aligned(resid, 16))) return BSX_E_POINTER;
     for (int32_t t0 = 0; t0 < T; t0 += 65535) {   // grid.y limit
         const int32_t nt = T - t0 < 65535 ? T - t0 : 65535;
         const dim3 grid((unsigned) ((H / 4 + 127) / 128), (unsigned) nt);
-        combine_kernel<<<grid, 128, 0, (cudaStream_t) stream>>>(rows, slot ? slot + (size_t) t0 * k : nullptr, weights + (size_t) t0 * k,
-                                                               shared ? shared + (size_t) t0 * H : nullptr, shared_gate ? shared_gate + t0 : nullptr,
-                                                               k, H, t0 * k, ids ? ids + (size_t) t0 * k : nullptr, e_lo, e_hi, y + (size_t) t0 * H);
+        launch_k(combine_kernel, grid, dim3(128), 0, (cudaStream_t) stream, rows, slot ? slot + (size_t) t0 * k : nullptr, weights + (size_t) t0 * k,
+                 shared ? shared + (size_t) t0 * H : nullptr, shared_gate ? shared_gate + t0 : nullptr, resid ? resid + (size_t) t0 * H : nullptr,
+                 (int) k, (int) H, (int) (t0 * k), ids ? ids + (size_t) t0 * k : nullptr, (int) e_lo, (int) e_hi, y + (size_t) t0 * H);
     }
     return launch_status();
 }
 
 extern "C" int32_t bsx_combine(const float* rows, const int32_t* slot, const float* weights, const float* shared,
                                const float* shared_gate, int32_t T, int32_t k, int32_t H, float* y, void* stream) {
-    return combine_impl(rows, slot, weights, shared, shared_gate, T, k, H, nullptr, 0, 0, y, stream);
+    return combine_impl(rows, slot, weights, shared, shared_gate, nullptr, T, k, H, nullptr, 0, 0, y, stream);
+}
+
+extern "C" int32_t bsx_combine_residual(const float* rows, const int32_t* slot, const float* weights, const float* shared,
+                                        const float* shared_gate, const float* residual, int32_t T, int32_t k, int32_t H, float* y, void* stream) {
+    return combine_impl(rows, slot, weights, shared, shared_gate, residual, T, k, H, nullptr, 0, 0, y, stream);
 }
 
 extern "C" int32_t bsx_combine_partial(const float* rows, const int32_t* slot, const float* weights, const int32_t* ids, int32_t e_lo,
                                        int32_t e_hi, int32_t T, int32_t k, int32_t H, float* y, void* stream) {
     if (!ids) return BSX_E_POINTER;
-    return combine_impl(rows, slot, weights, nullptr, nullptr, T, k, H, ids, e_lo, e_hi, y, stream);
+    return combine_impl(rows, slot, weights, nullptr, nullptr, nullptr, T, k, H, ids, e_lo, e_hi, y, stream);
 }

@@ -83,7 +83,14 @@ int32_t experts_grouped_simple(const ExpertArgs& a, cudaStream_t st);
 // returns BSX_E_TYPE when the fast path does not cover the layout (the caller then runs the plain kernels)
 int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st);
 // the same call over blobs repacked by bsx_expert_pack (experts_nvf4.cu): block-scaled FP4 MMAs straight on the NVFP4 codes
-int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st, bool x_images_ready);
+// pass_list_ready: the pass list (plan.cuh) already sits in the scratch (the fused selection + plan kernel wrote it)
+struct PassRec;
+int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st, bool x_images_ready, bool pass_list_ready);
+void experts_packed_pass_list(void* scratch, int64_t cap_entries, int64_t n_embd, int64_t n_ff, PassRec** items, int** n_items);
+int32_t experts_packed_x_images(const bsx_expert_layout& L, const void* x, int32_t x_kind, int32_t n_x_rows, int64_t cap, void* scratch, cudaStream_t st);
+// Q6_K / IQ1_M blobs in place on the integer tensor cores (experts_kq.cu); BSX_E_TYPE when the layout is not covered
+int32_t experts_grouped_kq(const ExpertArgs& a, cudaStream_t st);
+size_t experts_kq_scratch_bytes(int64_t cap_entries, int64_t n_embd, int64_t n_ff);
 size_t experts_packed_scratch_bytes(int64_t cap_entries, int64_t n_embd, int64_t n_ff);
 size_t experts_mma_scratch_bytes(int64_t cap_entries, int64_t n_embd, int64_t n_ff);
 

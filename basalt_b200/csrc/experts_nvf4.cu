@@ -36,12 +36,14 @@
 #include "formats.cuh"
 #include "norm.cuh"
 #include "nvf4.cuh"
+#include "pdl.cuh"
+#include "plan.cuh"
 #include "tc5.cuh"
 
 namespace bsx {
 namespace {
 
-constexpr int kEntF = 8;                   // entries per pass
+constexpr int kEntF = kPassEntries;        // entries per pass (8)
 constexpr int kColsF = kTermsF * kEntF;    // 32 = MMA N
 constexpr int kStagesF = 5;
 constexpr int kATile = 128 * 128;          // one operand tile of a stage: 128 rows x 128 bytes (256 columns of codes)
@@ -59,12 +61,8 @@ constexpr uint32_t kIdescF = (1u << 7) | (1u << 10) | ((uint32_t) (kColsF >> 3) 
 
 enum { FMODE_GU = 0, FMODE_DOWN = 1 };
 
-// a pass: up to kEntF consecutive entries [eb, eb + ntok) of one group, with the group's blob - everything a stream kernel
-// needs about it in one 16-byte load
-struct __align__(16) PassRec {
-    unsigned long long blob;
-    int eb, ntok;
-};
+// a pass (PassRec, plan.cuh): up to kEntF consecutive entries [eb, eb + ntok) of one group, with the group's blob - everything a
+// stream kernel needs about it in one 16-byte load
 
 size_t al256f(size_t v) { return (v + 255) & ~(size_t) 255; }
 
@@ -116,6 +114,8 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint8_t* __restrict__ i
 template <bool FROM_H, int TPR>
 __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __restrict__ codes, uint8_t* __restrict__ sfs, float* __restrict__ inv,
                                                         PassRec* __restrict__ items, int* __restrict__ n_items) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int ng = min(*a.n_groups, (int) a.cap_groups);
     const int total = min(a.grp_start[ng], (int) a.cap_entries);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -168,6 +168,8 @@ template <int TPR>
 __global__ void __launch_bounds__(256) x_images_kernel(const void* __restrict__ x, int kind, int n_rows, int64_t K, uint8_t* __restrict__ codes,
                                                         uint8_t* __restrict__ sfs, float* __restrict__ inv) {
     __shared__ float shf[8];
+    pdl_wait();
+    pdl_launch_dependents();
     const int i = blockIdx.x * (256 / TPR) + (int) threadIdx.x / TPR;
     fp4_image_row<TPR>(x, kind, i < n_rows ? i : 0, K, i < n_rows, i, codes, sfs, inv, shf);
 }
@@ -181,6 +183,8 @@ __global__ void __launch_bounds__(kNormThreads) norm_images_kernel(const void* _
                                                                    uint8_t* __restrict__ sfs, float* __restrict__ inv) {
     __shared__ float red[kNormThreads / 32];
     __shared__ float shf[kNormThreads / 32];
+    pdl_wait();
+    pdl_launch_dependents();
     norm_row<BF16>(x, w, eps, K, blockIdx.x, act, xn, red);
     fp4_image_row<kNormThreads>(xn, BSX_X_F32, blockIdx.x, K, true, (int) blockIdx.x, codes, sfs, inv, shf);
 }
@@ -188,9 +192,9 @@ __global__ void __launch_bounds__(kNormThreads) norm_images_kernel(const void* _
 template <bool FROM_H>
 void launch_prep(const ExpertArgs& a, int64_t rows, int64_t K, uint8_t* codes, uint8_t* sfs, float* inv, PassRec* items, int* n_items, cudaStream_t st) {
     const int64_t n_sb = K / 16;
-    if (n_sb <= 32) prep_fp4_kernel<FROM_H, 32><<<(unsigned) ((rows + 7) / 8 + 1), 256, 0, st>>>(a, codes, sfs, inv, items, n_items);
-    else if (n_sb <= 128) prep_fp4_kernel<FROM_H, 128><<<(unsigned) ((rows + 1) / 2 + 1), 256, 0, st>>>(a, codes, sfs, inv, items, n_items);
-    else prep_fp4_kernel<FROM_H, 256><<<(unsigned) (rows + 1), 256, 0, st>>>(a, codes, sfs, inv, items, n_items);
+    if (n_sb <= 32) launch_k(prep_fp4_kernel<FROM_H, 32>, dim3((unsigned) ((rows + 7) / 8 + 1)), dim3(256), 0, st, a, codes, sfs, inv, items, n_items);
+    else if (n_sb <= 128) launch_k(prep_fp4_kernel<FROM_H, 128>, dim3((unsigned) ((rows + 1) / 2 + 1)), dim3(256), 0, st, a, codes, sfs, inv, items, n_items);
+    else launch_k(prep_fp4_kernel<FROM_H, 256>, dim3((unsigned) (rows + 1)), dim3(256), 0, st, a, codes, sfs, inv, items, n_items);
 }
 
 // ---------------------------------------------------------------- the stream kernel
@@ -229,7 +233,6 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
     // pass record, the entries' rows and scales) is amortised and its loads hide behind the stream
     const int n_sub = max(1, min(n_rb, (4 + n_chunk - 1) / n_chunk));
     const int n_upp = (n_rb + n_sub - 1) / n_sub;                        // units per pass
-    const int n_units = sa.n_items[0] * n_upp;
     const PackedGeom geo = packed_geom(a.L.n_embd, a.L.n_ff);
 
     if (threadIdx.x == 0) {
@@ -253,6 +256,11 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
+    // barriers and tensor memory are set up; from here on the kernel reads what the kernels before it wrote (the pass list,
+    // the activation images), so a programmatic launch waits here for them to finish
+    pdl_wait();
+    pdl_launch_dependents();
+    const int n_units = sa.n_items[0] * n_upp;
 
     // unit -> its pass record and its row blocks [rb0, rb1).  Tile 0 / tile 1 of a row block: the 128 gate rows r0.. and the
     // 128 up rows r0.. (gate/up), or down rows r0.. and r0 + 128.. (down).
@@ -482,7 +490,7 @@ int32_t launch_stream(const StreamArgs& sa, cudaStream_t st) {
         if (e != cudaSuccess) return (int32_t) e;
         configured[dev].store(true, std::memory_order_release);
     }
-    nvf4_stream_kernel<MODE><<<(unsigned) sm_count(), kThreadsF, kSmemF, st>>>(sa);
+    launch_k(nvf4_stream_kernel<MODE>, dim3((unsigned) sm_count()), dim3(kThreadsF), kSmemF, st, sa);
     return launch_status();
 }
 
@@ -524,13 +532,19 @@ static PackedScratch carve_scratch(void* scratch, int64_t cap, int64_t H, int64_
 int32_t experts_packed_x_images(const bsx_expert_layout& L, const void* x, int32_t x_kind, int32_t n_x_rows, int64_t cap, void* scratch, cudaStream_t st) {
     const PackedScratch sc = carve_scratch(scratch, cap, L.n_embd, L.n_ff);
     const int64_t n_sb = L.n_embd / 16;
-    if (n_sb <= 32) x_images_kernel<32><<<(unsigned) ((n_x_rows + 7) / 8), 256, 0, st>>>(x, x_kind, n_x_rows, L.n_embd, sc.xcodes, sc.xsf, sc.xinv);
-    else if (n_sb <= 128) x_images_kernel<128><<<(unsigned) ((n_x_rows + 1) / 2), 256, 0, st>>>(x, x_kind, n_x_rows, L.n_embd, sc.xcodes, sc.xsf, sc.xinv);
-    else x_images_kernel<256><<<(unsigned) n_x_rows, 256, 0, st>>>(x, x_kind, n_x_rows, L.n_embd, sc.xcodes, sc.xsf, sc.xinv);
+    if (n_sb <= 32) launch_k(x_images_kernel<32>, dim3((unsigned) ((n_x_rows + 7) / 8)), dim3(256), 0, st, x, (int) x_kind, (int) n_x_rows, L.n_embd, sc.xcodes, sc.xsf, sc.xinv);
+    else if (n_sb <= 128) launch_k(x_images_kernel<128>, dim3((unsigned) ((n_x_rows + 1) / 2)), dim3(256), 0, st, x, (int) x_kind, (int) n_x_rows, L.n_embd, sc.xcodes, sc.xsf, sc.xinv);
+    else launch_k(x_images_kernel<256>, dim3((unsigned) n_x_rows), dim3(256), 0, st, x, (int) x_kind, (int) n_x_rows, L.n_embd, sc.xcodes, sc.xsf, sc.xinv);
     return launch_status();
 }
 
-int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st, bool x_images_ready) {
+void experts_packed_pass_list(void* scratch, int64_t cap, int64_t H, int64_t I, PassRec** items, int** n_items) {
+    const PackedScratch sc = carve_scratch(scratch, cap, H, I);
+    *items = sc.items;
+    *n_items = sc.n_items;
+}
+
+int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_t st, bool x_images_ready, bool pass_list_ready) {
     const bsx_expert_layout& L = a.L;
     if (L.gu_type != kTypeNVFP4 || L.up_type != kTypeNVFP4 || L.d_type != kTypeNVFP4) return BSX_E_TYPE;
     if (L.n_embd % 256 || L.n_ff % 256) return BSX_E_TYPE;       // whole 256-column stages, whole 128-row tiles
@@ -549,8 +563,8 @@ int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_
     sa.status = status;
     int32_t rc = BSX_OK;
     if (phase != 2) {
-        if (x_images_ready) prep_fp4_kernel<false, 32><<<1, 256, 0, st>>>(a, xcodes, xsf, xinv, items, n_items);   // the pass list alone
-        else launch_prep<false>(a, x_rows, H, xcodes, xsf, xinv, items, n_items, st);
+        if (x_images_ready && !pass_list_ready) launch_k(prep_fp4_kernel<false, 32>, dim3(1), dim3(256), 0, st, a, xcodes, xsf, xinv, items, n_items);   // the pass list alone
+        else if (!x_images_ready) launch_prep<false>(a, x_rows, H, xcodes, xsf, xinv, items, n_items, st);
         sa.codes = xcodes;
         sa.sfs = xsf;
         sa.inv = xinv;
@@ -621,7 +635,7 @@ extern "C" int32_t bsx_experts_grouped_packed(const bsx_expert_layout* layout, c
     a.out_kind = out_kind;
     a.n_x_rows = n_x_rows;
     a.grid = nullptr;
-    return experts_grouped_packed(a, status, (cudaStream_t) stream, ready);
+    return experts_grouped_packed(a, status, (cudaStream_t) stream, ready, false);
 }
 
 extern "C" int32_t bsx_norm_pack_images(const bsx_expert_layout* layout, const void* x, int32_t x_kind, const float* w, float eps,
@@ -635,11 +649,11 @@ extern "C" int32_t bsx_norm_pack_images(const bsx_expert_layout* layout, const v
     const PackedScratch sc = carve_scratch(scratch, cap_entries, layout->n_embd, layout->n_ff);
     cudaStream_t st = (cudaStream_t) stream;
     if (x_kind == BSX_X_BF16)
-        norm_images_kernel<true><<<(unsigned) n_x_rows, kNormThreads, 0, st>>>(x, w, eps, layout->n_embd, static_cast<uint16_t*>(act), xn, sc.xcodes,
-                                                                              sc.xsf, sc.xinv);
+        launch_k(norm_images_kernel<true>, dim3((unsigned) n_x_rows), dim3(kNormThreads), 0, st, x, w, eps, layout->n_embd, static_cast<uint16_t*>(act), xn, sc.xcodes,
+                 sc.xsf, sc.xinv);
     else
-        norm_images_kernel<false><<<(unsigned) n_x_rows, kNormThreads, 0, st>>>(x, w, eps, layout->n_embd, static_cast<uint16_t*>(act), xn, sc.xcodes,
-                                                                               sc.xsf, sc.xinv);
+        launch_k(norm_images_kernel<false>, dim3((unsigned) n_x_rows), dim3(kNormThreads), 0, st, x, w, eps, layout->n_embd, static_cast<uint16_t*>(act), xn, sc.xcodes,
+                 sc.xsf, sc.xinv);
     return launch_status();
 }
 

@@ -6,12 +6,15 @@
 // launch shapes are this library's own: several gate rows per block so a token vector is read once for all of them, and
 // one warp per token for the selection instead of one block.
 #define BSX_SOFTMAX_KERNEL softmax_topk_kernel
+#define BSX_SOFTMAX_TOKEN softmax_topk_token
 #define BSX_SOFTMAX_LAUNCH softmax_topk_launch
 #define BSX_SOFTMAX_RECIPROCAL 0
 #include "router_softmax.cuh"
 
 #include <atomic>
 #include <climits>
+
+#include "plan.cuh"
 
 namespace bsx {
 
@@ -53,6 +56,31 @@ __device__ __forceinline__ float4 widen(uint2 u) {
                        __uint_as_float(u.y & 0xFFFF0000u));
 }
 
+// The G butterflies of one token at once (see router_logits_kernel): returns the row whose sum this lane ends up holding in acc[0].
+template <int G>
+__device__ __forceinline__ int merged_butterfly(float (&acc)[G], int lane) {
+    int row = 0;
+#pragma unroll
+    for (int m = 16, n = G; m; m >>= 1) {
+        if (n > 1) {
+            const int half = n >> 1;
+            const bool up = (lane & m) != 0;
+#pragma unroll
+            for (int i = 0; i < G / 2; ++i)
+                if (i < half) {
+                    const float keep = up ? acc[i + half] : acc[i];
+                    const float send = up ? acc[i] : acc[i + half];
+                    acc[i] = keep + __shfl_xor_sync(kFull, send, m);
+                }
+            if (up) row += half;
+            n = half;
+        } else {
+            acc[0] += __shfl_xor_sync(kFull, acc[0], m);
+        }
+    }
+    return row;
+}
+
 template <int NV, int G, bool BF16>
 __global__ void __launch_bounds__(kLogitThreads, (NV <= 4 ? 2 : 1))
 router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate, int n_embd, int n_expert, int n_tokens,
@@ -62,6 +90,7 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
     const int r0 = blockIdx.x * G;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float4 w[G][NV];
+    // the gate rows are constant weights: they are requested before the wait for the kernel that wrote x
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
@@ -69,6 +98,8 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
             const int i = threadIdx.x + c * kLogitThreads;
             w[g][c] = i < n4 ? reinterpret_cast<const float4*>(gate + (size_t) (r0 + g) * n_embd)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
+    pdl_wait();
+    pdl_launch_dependents();
     const int t_begin = blockIdx.y * tok_per_block;
     const int t_end = min(n_tokens, t_begin + tok_per_block);
     for (int t0 = t_begin; t0 < t_end; t0 += kTokTile) {
@@ -109,25 +140,7 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
             // The G butterflies at once: at the xor-16, -8 and -4 stages a lane keeps half of its values and hands the other
             // half to its partner, so each stage adds exactly the pairs the plain butterfly adds (a + b == b + a bit for
             // bit); after the halving stages the lane holds one row's partial sum and the remaining stages run in full.
-            int row = 0;
-#pragma unroll
-            for (int m = 16, n = G; m; m >>= 1) {
-                if (n > 1) {
-                    const int half = n >> 1;
-                    const bool up = (lane & m) != 0;
-#pragma unroll
-                    for (int i = 0; i < G / 2; ++i)
-                        if (i < half) {
-                            const float keep = up ? acc[i + half] : acc[i];
-                            const float send = up ? acc[i] : acc[i + half];
-                            acc[i] = keep + __shfl_xor_sync(kFull, send, m);
-                        }
-                    if (up) row += half;
-                    n = half;
-                } else {
-                    acc[0] += __shfl_xor_sync(kFull, acc[0], m);
-                }
-            }
+            const int row = merged_butterfly<G>(acc, lane);
             constexpr int kOwners = 32 / G;   // lanes holding the same row's sum
             if ((lane & (kOwners - 1)) == 0) red[row][t][warp] = acc[0];
 #pragma unroll
@@ -147,12 +160,125 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
     }
 }
 
+
+// The same sums for decode windows of 16 tokens and more: a block keeps G gate rows in registers, copies its share of the
+// token rows into shared memory once (one contiguous range, 16-byte cp.async) and then runs every (row, token) chain from
+// there, so a token's columns cost a shared-memory read instead of an L2 round trip per token and the grid is one wave of
+// blocks that each read the gate rows once.  The order of every sum is unchanged: thread i owns float4 columns i, i + 256, ...
+// as one fmaf chain, xor butterfly over the warp, the 8 warp sums in order.  The per-tile reduction buffer is doubled so a
+// tile needs one block barrier.
+template <int NV, int G, bool BF16>
+__global__ void __launch_bounds__(kLogitThreads, 1)
+router_logits_staged_kernel(const void* __restrict__ x, const float* __restrict__ gate, int n_embd, int n_expert, int n_tokens,
+                            int tok_per_block, float* __restrict__ logits) {
+    extern __shared__ __align__(16) uint8_t xsm[];
+    __shared__ float red[2][G][kTokTile][kLogitThreads / 32];
+    const int n4 = n_embd >> 2;
+    const int r0 = blockIdx.x * G;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float4 w[G][NV];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int c = 0; c < NV; ++c) {
+            const int i = threadIdx.x + c * kLogitThreads;
+            w[g][c] = i < n4 ? reinterpret_cast<const float4*>(gate + (size_t) (r0 + g) * n_embd)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t_begin = blockIdx.y * tok_per_block;
+    const int nt_all = min(n_tokens, t_begin + tok_per_block) - t_begin;
+    const size_t row_bytes = (size_t) n_embd * (BF16 ? 2 : 4);
+    {
+        const uint8_t* src = static_cast<const uint8_t*>(x) + (size_t) t_begin * row_bytes;
+        const uint32_t dst = (uint32_t) __cvta_generic_to_shared(xsm);
+        const int pieces = (int) ((size_t) nt_all * row_bytes >> 4);
+        for (int i = threadIdx.x; i < pieces; i += kLogitThreads)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst + (uint32_t) i * 16u), "l"(src + (size_t) i * 16) : "memory");
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncthreads();
+    int tile = 0;
+    for (int t0 = 0; t0 < nt_all; t0 += kTokTile, ++tile) {
+        const int nt = min(kTokTile, nt_all - t0);
+        float (*rd)[kTokTile][kLogitThreads / 32] = red[tile & 1];
+#pragma unroll 2
+        for (int t = 0; t < nt; ++t) {
+            const uint8_t* xrow = xsm + (size_t) (t0 + t) * row_bytes;
+            float acc[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc[g] = 0.f;
+#pragma unroll
+            for (int c = 0; c < NV; ++c) {
+                const int i = threadIdx.x + c * kLogitThreads;
+                if (i < n4) {
+                    float4 v;
+                    if constexpr (BF16) v = widen(reinterpret_cast<const uint2*>(xrow)[i]);
+                    else v = reinterpret_cast<const float4*>(xrow)[i];
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        acc[g] = fmaf(w[g][c].x, v.x, acc[g]);
+                        acc[g] = fmaf(w[g][c].y, v.y, acc[g]);
+                        acc[g] = fmaf(w[g][c].z, v.z, acc[g]);
+                        acc[g] = fmaf(w[g][c].w, v.w, acc[g]);
+                    }
+                }
+            }
+            const int row = merged_butterfly<G>(acc, lane);
+            constexpr int kOwners = 32 / G;
+            if ((lane & (kOwners - 1)) == 0) rd[row][t][warp] = acc[0];
+        }
+        __syncthreads();
+        {
+            const int g = threadIdx.x / kTokTile, t = threadIdx.x % kTokTile;
+            if (g < G && t < nt) {
+                float s = 0.f;
+#pragma unroll
+                for (int i = 0; i < kLogitThreads / 32; ++i) s += rd[g][t][i];
+                logits[(size_t) (t_begin + t0 + t) * n_expert + r0 + g] = s;
+            }
+        }
+    }
+}
+
+constexpr size_t kStagedSmemMax = 160 * 1024;
+
+template <int NV, int G, bool BF16>
+int32_t launch_logits_staged(const void* x, const float* gate, int T, int E, int H, int tpb, float* logits, cudaStream_t st) {
+    static std::atomic<bool> configured[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
+    if (!configured[dev].load(std::memory_order_acquire)) {
+        const cudaError_t e = cudaFuncSetAttribute(router_logits_staged_kernel<NV, G, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kStagedSmemMax);
+        if (e != cudaSuccess) return (int32_t) e;
+        configured[dev].store(true, std::memory_order_release);
+    }
+    const size_t smem = (size_t) tpb * H * (BF16 ? 2 : 4);
+    const dim3 grid((unsigned) (E / G), (unsigned) ((T + tpb - 1) / tpb));
+    launch_k(router_logits_staged_kernel<NV, G, BF16>, grid, dim3(kLogitThreads), smem, st, x, gate, H, E, T, tpb, logits);
+    return launch_status();
+}
+
+// the staged kernel for the row widths decode layers have (NV float4 a thread and row: hidden up to 2048 with 8 rows a block, up to
+// 4096 with 4); -1: not covered, the caller runs the plain kernel
+template <bool BF16>
+int32_t staged_dispatch(int nv, int G, const void* x, const float* gate, int T, int E, int H, int tpb, float* logits, cudaStream_t st) {
+    if (nv == 1 && G == 8) return launch_logits_staged<1, 8, BF16>(x, gate, T, E, H, tpb, logits, st);
+    if (nv == 2 && G == 8) return launch_logits_staged<2, 8, BF16>(x, gate, T, E, H, tpb, logits, st);
+    if (nv == 1 && G == 4) return launch_logits_staged<1, 4, BF16>(x, gate, T, E, H, tpb, logits, st);
+    if (nv == 2 && G == 4) return launch_logits_staged<2, 4, BF16>(x, gate, T, E, H, tpb, logits, st);
+    if (nv == 3 && G == 4) return launch_logits_staged<3, 4, BF16>(x, gate, T, E, H, tpb, logits, st);
+    if (nv == 4 && G == 4) return launch_logits_staged<4, 4, BF16>(x, gate, T, E, H, tpb, logits, st);
+    return -1;
+}
+
 template <int NV, int G>
 void launch_logits(const void* x, bool bf16, const float* gate, int T, int E, int H, float* logits, cudaStream_t st) {
     const int tpb = T <= 256 ? kTokTile : 8 * kTokTile;
     const dim3 grid((unsigned) (E / G), (unsigned) ((T + tpb - 1) / tpb));
-    if (bf16) router_logits_kernel<NV, G, true><<<grid, kLogitThreads, 0, st>>>(x, gate, H, E, T, tpb, logits);
-    else router_logits_kernel<NV, G, false><<<grid, kLogitThreads, 0, st>>>(x, gate, H, E, T, tpb, logits);
+    if (bf16) launch_k(router_logits_kernel<NV, G, true>, grid, dim3(kLogitThreads), 0, st, x, gate, H, E, T, tpb, logits);
+    else launch_k(router_logits_kernel<NV, G, false>, grid, dim3(kLogitThreads), 0, st, x, gate, H, E, T, tpb, logits);
 }
 
 template <int G>
@@ -194,16 +320,12 @@ __device__ __forceinline__ float gate_score(float x, int gate) {
 // the lower index on a tie; src/kernels/cuda/router.cu:170-217) made as k warp-wide argmax passes, which yield the ids in rank
 // order directly; lane 0 adds the chosen unbiased scores in that order, as the reference's thread 0 does.
 template <int REGT>
-__global__ void __launch_bounds__(256)
-router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, int E, int k, float scale,
-                     int gate, int n_group, int topk_group, float prior, HeldTabs held, int32_t* __restrict__ ids,
-                     float* __restrict__ weights) {
+__device__ __forceinline__ void select_token(const float* __restrict__ lg, const float* __restrict__ bias, int E, int k, float scale, int gate,
+                                             int n_group, int topk_group, float prior, const HeldTabs& held, int32_t* __restrict__ ids,
+                                             float* __restrict__ weights) {
     constexpr int MAXR = REGT > 0 ? REGT : 32;
-    const int64_t t = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (t >= T) return;
     const int lane = threadIdx.x & 31;
     const int reg = REGT > 0 ? REGT : (E >> 5);
-    const float* lg = logits + t * E;
     float s[MAXR], b[MAXR];
     uint32_t dead = 0;   // bit i: expert lane + 32 i cannot be chosen (outside E, masked group, or already taken)
 #pragma unroll
@@ -273,10 +395,22 @@ router_select_kernel(const float* __restrict__ logits, const float* __restrict__
         sv = __shfl_sync(kFull, sv, ex == INT_MAX ? 0 : (ex & 31));
         sum += sv;
         if (lane == r) my_sel = sv;
-        if (lane == 0) ids[t * k + r] = ex == INT_MAX ? -1 : ex;
+        if (lane == 0) ids[r] = ex == INT_MAX ? -1 : ex;
     }
     const float denom = sum + 1e-20f;
-    if (lane < k) weights[t * k + lane] = my_sel / denom * scale;
+    if (lane < k) weights[lane] = my_sel / denom * scale;
+}
+
+template <int REGT>
+__global__ void __launch_bounds__(256)
+router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, int E, int k, float scale,
+                     int gate, int n_group, int topk_group, float prior, HeldTabs held, int32_t* __restrict__ ids,
+                     float* __restrict__ weights) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t t = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    select_token<REGT>(logits + t * E, bias, E, k, scale, gate, n_group, topk_group, prior, held, ids + t * k, weights + t * k);
 }
 
 // ---------------------------------------------------------------------------------------------- fp64 softmax router
@@ -371,6 +505,38 @@ route_tail_skip_kernel(int32_t* __restrict__ ids, float* __restrict__ w, HeldTab
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------- selection + plan in one launch
+// One block: its 32 warps choose the experts of the window's tokens (the per-token routines above, so ids and weights carry
+// the same bits as the separate kernels'), leave the ids in shared memory, and the block goes straight on to the
+// decode-window plan (plan.cuh) - one launch and one round trip through global memory fewer in a step that is latency-bound.
+// With items / n_items the pass list of the packed expert kernels is written as well.
+template <int REGT>
+__global__ void __launch_bounds__(1024)
+route_plan_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int k, float scale, int gate, int n_group,
+                  int topk_group, float prior, HeldTabs held, const unsigned long long* __restrict__ blobs, unsigned long long shared_blob,
+                  int32_t* ids, float* weights, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
+                  int32_t* __restrict__ n_groups, int32_t* __restrict__ dst, int32_t* __restrict__ tok, PassRec* __restrict__ items,
+                  int* __restrict__ n_items) {
+    extern __shared__ unsigned long long smb[];
+    const PlanSmem ps = plan_smem(smb, E);
+    plan_load_blobs(ps, blobs, E);       // constant addresses: before the wait for the kernel that wrote the logits
+    pdl_wait();
+    pdl_launch_dependents();
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int t = warp; t < T; t += 32) {
+        int32_t* it = ids + (size_t) t * k;
+        float* wt = weights + (size_t) t * k;
+        if (gate == BSX_GATE_SOFTMAX) softmax_topk_token<REGT>(logits + (size_t) t * E, it, wt, E, k);
+        else select_token<REGT>(logits + (size_t) t * E, bias, E, k, scale, gate, n_group, topk_group, prior, held, it, wt);
+        __syncwarp();                    // lane 0's ids are visible to the warp
+        if (lane < k) plan_note_pair(ps, t * k + lane, it[lane], E);
+    }
+    __syncthreads();
+    plan_finish(ps, T * k, k, E, shared_blob, shared_blob != 0ull ? T : 0, ptr, start, n_groups, dst, tok, items, n_items);
+}
+
 bool make_held(const int32_t* const* tabs, int n, HeldTabs& h) {
     h.n = 0;
     for (int i = 0; i < BSX_MAX_HELD_TABS; ++i) h.t[i] = nullptr;
@@ -393,6 +559,20 @@ static int32_t logits_launch(const void* x, int32_t x_kind, const float* gate, i
     if (!aligned(x, 16) || !aligned(gate, 16) || !aligned(logits, 4)) return BSX_E_POINTER;
     const bool bf16 = x_kind == BSX_X_BF16;
     const int nv = (H / 4 + kLogitThreads - 1) / kLogitThreads;
+    // decode windows of 16+ tokens whose rows fit shared memory: the staged kernel, one wave of blocks
+    const size_t row_bytes = (size_t) H * (bf16 ? 2 : 4);
+    if (T >= 16 && T <= 1024 && nv <= 4 && 8 * row_bytes <= kStagedSmemMax) {
+        int tpb = (int) (kStagedSmemMax / row_bytes) & ~7;
+        tpb = tpb > 32 ? 32 : tpb;
+        if (tpb > ((T + 7) & ~7)) tpb = (T + 7) & ~7;
+        const int tiles = (T + tpb - 1) / tpb;
+        int Gs = nv <= 2 ? 8 : 4;
+        while (Gs > 4 && (E / Gs) * tiles < 96) Gs >>= 1;
+        if (E % Gs == 0) {
+            const int32_t rc = bf16 ? staged_dispatch<true>(nv, Gs, x, gate, T, E, H, tpb, logits, st) : staged_dispatch<false>(nv, Gs, x, gate, T, E, H, tpb, logits, st);
+            if (rc != -1) return rc;
+        }
+    }
     // the most gate rows a block whose registers fit and whose grid still covers the SMs twice
     int G = nv <= 2 ? 8 : nv <= 4 ? 4 : 2;
     const int tiles = (T + kTokTile - 1) / kTokTile;
@@ -446,7 +626,7 @@ extern "C" int32_t bsx_router_select(const float* logits, const float* bias, int
         HeldTabs held;
         if (!make_held(held_tabs, n_held, held)) return BSX_E_POINTER;
         const unsigned blocks = (unsigned) ((T + 7) / 8);
-#define BSX_SEL(R) router_select_kernel<R><<<blocks, 256, 0, st>>>(logits, bias, T, E, k, weight_scale, gate_kind, n_group, topk_group, prior, held, ids, weights)
+#define BSX_SEL(R) launch_k(router_select_kernel<R>, dim3(blocks), dim3(256), 0, st, logits, bias, (int64_t) T, E, k, weight_scale, gate_kind, n_group, topk_group, prior, held, ids, weights)
         switch (E >> 5) {
             case 2: BSX_SEL(2); break;
             case 4: BSX_SEL(4); break;
@@ -498,4 +678,48 @@ extern "C" int32_t bsx_route_tail_skip(int32_t* ids, float* weights, const int32
     if (!make_held(held_tabs, n_held, held)) return BSX_E_POINTER;
     route_tail_skip_kernel<<<1, BSX_TAIL_SKIP_MAX, 0, (cudaStream_t) stream>>>(ids, weights, held, n_entries, k, rank, E, counts);
     return launch_status();
+}
+
+namespace bsx {
+// selection + plan (+ the packed kernels' pass list when items is given); BSX_E_TYPE: a gate kind the fused kernel does not cover
+int32_t route_plan_launch(const float* logits, const float* bias, int32_t T, int32_t E, int32_t k, int32_t gate_kind, float weight_scale,
+                          int32_t n_group, int32_t topk_group, const unsigned long long* blob_table, unsigned long long shared_blob, int32_t* ids,
+                          float* weights, unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok, PassRec* items,
+                          int* n_items, cudaStream_t st) {
+    if (gate_kind != BSX_GATE_SOFTMAX && gate_kind != BSX_GATE_SIGMOID && gate_kind != BSX_GATE_SQRT_SOFTPLUS) return BSX_E_TYPE;
+    if (E < 32 || E % 32 || E > 1024 || k < 1 || k > 32 || k > E || T < 0) return BSX_E_GEOMETRY;
+    if ((int64_t) T * k > BSX_PLAN_MAX_PAIRS) return BSX_E_LIMIT;
+    if (T == 0) return BSX_OK;
+    if (!logits || !ids || !weights || !blob_table || !ptr || !start || !n_groups || !dst || !tok) return BSX_E_POINTER;
+    HeldTabs held;
+    make_held(nullptr, 0, held);
+    if (gate_kind != BSX_GATE_SOFTMAX) {
+        if (k > 16) return BSX_E_GEOMETRY;
+        if (n_group < 1) n_group = 1;
+        if (n_group > 32 || E % n_group) return BSX_E_GEOMETRY;
+        if (topk_group < 1 || topk_group > n_group) topk_group = n_group;
+        if ((int64_t) topk_group * (E / n_group) < k) return BSX_E_GEOMETRY;
+    }
+    const size_t smem = plan_smem_bytes(E, T * k);
+#define BSX_RP(R) launch_k(route_plan_kernel<R>, dim3(1), dim3(1024), smem, st, logits, bias, (int) T, (int) E, (int) k, weight_scale, (int) gate_kind, (int) n_group, \
+                           (int) topk_group, 0.f, held, blob_table, shared_blob, ids, weights, ptr, start, n_groups, dst, tok, items, n_items)
+    switch (E >> 5) {
+        case 2: BSX_RP(2); break;
+        case 4: BSX_RP(4); break;
+        case 8: BSX_RP(8); break;
+        case 16: BSX_RP(16); break;
+        default: BSX_RP(0); break;
+    }
+#undef BSX_RP
+    return launch_status();
+}
+}  // namespace bsx
+
+extern "C" int32_t bsx_route_plan(const float* logits, const float* bias, int32_t T, int32_t E, int32_t k, int32_t gate_kind, float weight_scale,
+                                  int32_t n_group, int32_t topk_group, const unsigned long long* blob_table, unsigned long long shared_blob,
+                                  int32_t* ids, float* weights, unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok,
+                                  void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    return route_plan_launch(logits, bias, T, E, k, gate_kind, weight_scale, n_group, topk_group, blob_table, shared_blob, ids, weights, ptr, start,
+                             n_groups, dst, tok, nullptr, nullptr, (cudaStream_t) stream);
 }

@@ -2,6 +2,7 @@
 // zero), as the Basalt decode path builds its own (src/models/qwen4exp/kernels/native_router.cu:44-99 with the flags of
 // CMakeLists.txt:572-590), so that BSX_GATE_SOFTMAX_FAST gives that kernel's bits.  Only this file gets the flag.
 #define BSX_SOFTMAX_KERNEL softmax_topk_fast_kernel
+#define BSX_SOFTMAX_TOKEN softmax_topk_fast_token
 #define BSX_SOFTMAX_LAUNCH softmax_topk_fast_launch
 #define BSX_SOFTMAX_RECIPROCAL 1
 #include "router_softmax.cuh"

@@ -2,7 +2,7 @@
 // (IEEE expf and division; the Basalt prompt path's route_kernel, src/models/qwen4exp/prefill/kernels.cu:351-390) and
 // router_fast.cu (built with --use_fast_math, weight = p * (1 / sum); the decode path's route,
 // src/models/qwen4exp/kernels/native_router.cu:44-99).  The including file defines BSX_SOFTMAX_KERNEL (the kernel's name)
-// and BSX_SOFTMAX_RECIPROCAL (0: divide, 1: multiply by the reciprocal).
+// BSX_SOFTMAX_TOKEN (the per-token device routine's name) and BSX_SOFTMAX_RECIPROCAL (0: divide, 1: multiply by the reciprocal).
 //
 // Arithmetic order, which fixes every bit of the result: lane l holds experts l, l+32, ...; max over all experts; per lane
 // v = expf(v - max) summed in index order, lanes summed by xor butterfly; v *= 1/sum; NaN -> -FLT_MAX; k argmax passes
@@ -12,18 +12,16 @@
 #include <cfloat>
 
 #include "common.cuh"
+#include "pdl.cuh"
 
 namespace bsx {
 
+// one token by one warp: lg = the token's E logits; ids / wout = its k outputs
 template <int REGT>
-__global__ void __launch_bounds__(256) BSX_SOFTMAX_KERNEL(const float* __restrict__ logits, int32_t* __restrict__ ids,
-                                                         float* __restrict__ wout, int64_t T, int E, int k) {
+__device__ __forceinline__ void BSX_SOFTMAX_TOKEN(const float* __restrict__ lg, int32_t* __restrict__ ids, float* __restrict__ wout, int E, int k) {
     constexpr int MAXR = REGT > 0 ? REGT : 32;
-    const int64_t t = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (t >= T) return;
     const int lane = threadIdx.x & 31;
     const int reg = REGT > 0 ? REGT : (E >> 5);
-    const float* lg = logits + t * E;
     float v[MAXR];
 #pragma unroll
     for (int i = 0; i < MAXR; ++i) v[i] = i < reg ? lg[lane + i * 32] : -INFINITY;
@@ -68,27 +66,37 @@ __global__ void __launch_bounds__(256) BSX_SOFTMAX_KERNEL(const float* __restric
             rescan();
         }
         best = __shfl_sync(kFull, best, ex & 31);
-        if (lane == 0) ids[t * k + rank] = ex;
+        if (lane == 0) ids[rank] = ex;
         if (rank == lane) selected = best;
     }
     selected_sum = fmaxf(warp_sum_xor(selected_sum), 6.103515625e-5f);
 #if BSX_SOFTMAX_RECIPROCAL
     const float inv = 1.0f / selected_sum;
-    if (lane < k) wout[t * k + lane] = selected * inv;
+    if (lane < k) wout[lane] = selected * inv;
 #else
-    if (lane < k) wout[t * k + lane] = selected / selected_sum;
+    if (lane < k) wout[lane] = selected / selected_sum;
 #endif
+}
+
+template <int REGT>
+__global__ void __launch_bounds__(256) BSX_SOFTMAX_KERNEL(const float* __restrict__ logits, int32_t* __restrict__ ids,
+                                                         float* __restrict__ wout, int64_t T, int E, int k) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int64_t t = (int64_t) blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    BSX_SOFTMAX_TOKEN<REGT>(logits + t * E, ids + t * k, wout + t * k, E, k);
 }
 
 static inline int32_t BSX_SOFTMAX_LAUNCH(const float* logits, int64_t T, int E, int k, int32_t* ids, float* w, cudaStream_t st) {
     const unsigned blocks = (unsigned) ((T + 7) / 8);
     switch (E >> 5) {
-        case 2: BSX_SOFTMAX_KERNEL<2><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
-        case 4: BSX_SOFTMAX_KERNEL<4><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
-        case 8: BSX_SOFTMAX_KERNEL<8><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
-        case 12: BSX_SOFTMAX_KERNEL<12><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
-        case 16: BSX_SOFTMAX_KERNEL<16><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
-        default: BSX_SOFTMAX_KERNEL<0><<<blocks, 256, 0, st>>>(logits, ids, w, T, E, k); break;
+        case 2: launch_k(BSX_SOFTMAX_KERNEL<2>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
+        case 4: launch_k(BSX_SOFTMAX_KERNEL<4>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
+        case 8: launch_k(BSX_SOFTMAX_KERNEL<8>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
+        case 12: launch_k(BSX_SOFTMAX_KERNEL<12>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
+        case 16: launch_k(BSX_SOFTMAX_KERNEL<16>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
+        default: launch_k(BSX_SOFTMAX_KERNEL<0>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
     }
     return launch_status();
 }

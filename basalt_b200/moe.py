@@ -276,14 +276,32 @@ def gated_mlp(L: ExpertLayout, blob, x, cap_tok: Optional[int] = None, out=None,
     return out
 
 
-def moe_combine(rows, slot, weights, shared=None, shared_gate=None, y=None, stream=None):
-    """native_moe_combine_multi (native_moe.hpp:10-15) / prompt-path moe_combine (prefill/kernels.cu:705-709)."""
+def moe_combine(rows, slot, weights, shared=None, shared_gate=None, y=None, stream=None, residual=None):
+    """native_moe_combine_multi (native_moe.hpp:10-15) / prompt-path moe_combine (prefill/kernels.cu:705-709); residual: the
+    residual stream's rows, added last (the step after the layer, fused into the same pass)."""
     T, k = weights.shape
     H = rows.shape[-1]
     y = torch.empty((T, H), dtype=torch.float32, device=rows.device) if y is None else y
-    check("bsx_combine", capi.lib().bsx_combine(_p(rows), _p(slot), _p(weights), _p(shared), _p(shared_gate), T, k, H, _p(y),
-                                                 _stream(stream)))
+    check("bsx_combine", capi.lib().bsx_combine_residual(_p(rows), _p(slot), _p(weights), _p(shared), _p(shared_gate), _p(residual), T, k, H, _p(y),
+                                                          _stream(stream)))
     return y
+
+
+def route_plan(logits, bias, a: RouterArgs, blob_table, shared_blob: int = 0, stream=None):
+    """bsx_route_plan: router_select and moe_plan[_shared] as one launch; returns (ids, weights, ptr, start, n_groups, dst, tok)."""
+    T, E = logits.shape
+    dev, n = logits.device, T * a.k
+    rows = n + (T if shared_blob else 0)
+    ids = torch.empty((T, a.k), dtype=torch.int32, device=dev)
+    w = torch.empty((T, a.k), dtype=torch.float32, device=dev)
+    ptr = torch.zeros(n + 3, dtype=torch.int64, device=dev)
+    start = torch.zeros(n + 3, dtype=torch.int32, device=dev)
+    n_groups = torch.zeros(1, dtype=torch.int32, device=dev)
+    dst = torch.zeros(rows, dtype=torch.int32, device=dev)
+    tok = torch.zeros(rows, dtype=torch.int32, device=dev)
+    check("bsx_route_plan", capi.lib().bsx_route_plan(_p(logits), _p(bias), T, E, a.k, a.gate, a.weight_scale, a.n_group, a.topk_group, _p(blob_table),
+                                                       shared_blob, _p(ids), _p(w), _p(ptr), _p(start), _p(n_groups), _p(dst), _p(tok), _stream(stream)))
+    return ids, w, ptr, start, n_groups, dst, tok
 
 
 class KernelWaitTimeout(RuntimeError):
@@ -461,6 +479,70 @@ class MoELayer:
                 shared = self.s_out
         check("bsx_combine", lib.bsx_combine(_p(self.rows), None, _p(self.w), _p(shared), None, T, a.k, self.L.n_embd, _p(self.y), st))
         return self.y[:T]
+
+
+class NativeMoELayer:
+    """The same resident layer run by ONE C ABI call per step (bsx_moe_layer): the input norm, router logits, selection + plan,
+    grouped experts with the shared expert, combine and the residual add are issued inside the library, every kernel after the
+    first as a programmatic dependent launch.  What a C++ engine would call from its layer loop (the reference's sequence at
+    src/models/inkling2/session.cpp:680-716); this class only owns the buffers.  Routing results (logits, ids, w) are views into
+    the call's workspace."""
+
+    def __init__(self, gate_w: torch.Tensor, bias: Optional[torch.Tensor], blobs: torch.Tensor, layout: ExpertLayout, args: RouterArgs,
+                 shared_blob: Optional[torch.Tensor] = None, shared_layout: Optional[ExpertLayout] = None, max_tokens: int = 64,
+                 packed: bool = False, norm_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6, pdl: bool = True):
+        assert blobs.dtype == torch.uint8 and blobs.dim() == 2 and blobs.is_cuda
+        dev = blobs.device
+        E, stride = blobs.shape
+        self.gate_w, self.bias, self.blobs, self.L, self.args, self.shared_blob, self.norm_w = gate_w, bias, blobs, layout, args, shared_blob, norm_w
+        self.packed, self.max_tokens = packed, max_tokens
+        self.blob_table = (blobs.data_ptr() + torch.arange(E, dtype=torch.int64) * stride).to(dev)
+        d = capi.MoELayerDesc()
+        d.layout = layout
+        if shared_layout is not None:
+            d.shared_layout = shared_layout
+        d.n_expert, d.top_k, d.gate_kind, d.n_group, d.topk_group = E, args.k, args.gate, args.n_group, args.topk_group
+        d.packed, d.flags, d.weight_scale, d.norm_eps = int(packed), 0 if pdl else capi.LAYER_NO_PDL, args.weight_scale, float(norm_eps)
+        d.gate, d.bias, d.blob_table = gate_w.data_ptr(), (bias.data_ptr() if bias is not None else None), self.blob_table.data_ptr()
+        d.shared_blob = shared_blob.data_ptr() if shared_blob is not None else 0
+        d.norm_w = norm_w.data_ptr() if norm_w is not None else None
+        self.desc = d
+        nbytes = capi.lib().bsx_moe_layer_workspace_bytes(C.byref(d), max_tokens)
+        if not nbytes:
+            raise ValueError("bsx_moe_layer does not take this layer (experts, top-k, window size or block formats)")
+        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.y = torch.empty((max_tokens, layout.n_embd), dtype=torch.float32, device=dev)
+        v = capi.MoELayerViews()
+        check("bsx_moe_layer_views", capi.lib().bsx_moe_layer_views(C.byref(d), max_tokens, self.workspace.data_ptr(), C.byref(v)))
+        base = self.workspace.data_ptr()
+
+        def view(ptr, shape, dtype):
+            n = int(torch.tensor(shape).prod().item()) * torch.empty((), dtype=dtype).element_size()
+            return self.workspace[ptr - base:ptr - base + n].view(dtype).view(shape)
+        self.logits = view(v.logits, (max_tokens, E), torch.float32)
+        self.ids = view(v.ids, (max_tokens, args.k), torch.int32)
+        self.w = view(v.weights, (max_tokens, args.k), torch.float32)
+        self.n_groups = view(v.n_groups, (1,), torch.int32)
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        T = x.shape[0]
+        check("bsx_moe_layer", capi.lib().bsx_moe_layer(C.byref(self.desc), _p(x), _x_kind(x), T, self.max_tokens, _p(residual), self.workspace.data_ptr(),
+                                                         _p(self.y), _p(self.status), _stream(stream)))
+        return self.y[:T]
+
+    def check_status(self) -> None:
+        """See MoELayer.check_status."""
+        read_status(self.status, "NativeMoELayer")
+
+    def capture(self, x_example: torch.Tensor):
+        return _capture(self, x_example)
+
+    def forward_graphed(self, x: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if x is not None:
+            self.x_static.copy_(x, non_blocking=True)
+        self.graph.replay()
+        return self.y
 
 
 def _capture(layer, x_example: torch.Tensor):

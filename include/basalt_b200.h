@@ -281,6 +281,58 @@ BSX_API int32_t bsx_experts_prefill_packed(const bsx_expert_layout* layout, cons
 BSX_API int32_t bsx_combine(const float* rows, const int32_t* slot, const float* weights, const float* shared, const float* shared_gate,
                     int32_t T, int32_t k, int32_t H, float* y, void* stream);
 
+/* ---- a13 + the step after the layer: bsx_combine with the residual stream's row added last, y[t] = (combine) + residual[t] as one
+ * more rounded fp32 add - the weighted sum and the residual write in one pass over the rows instead of a T x H round trip
+ * through HBM (Basalt fuses the same pair in its per-model finish kernels: moe_finish, src/models/inkling2/kernels/glue.cu:507-546
+ * called at src/models/inkling2/session.cpp:706-716).  residual [T][H] fp32, may be null (= bsx_combine); y may alias it. */
+BSX_API int32_t bsx_combine_residual(const float* rows, const int32_t* slot, const float* weights, const float* shared, const float* shared_gate,
+                                     const float* residual, int32_t T, int32_t k, int32_t H, float* y, void* stream);
+
+/* ---- a2-a4 + a6 in one launch: bsx_router_select followed by bsx_moe_plan_shared (shared_blob = 0: bsx_moe_plan), for decode
+ * windows (T * k <= 1024).  One block chooses every token's experts and goes straight on to the plan, the ids never leaving
+ * shared memory in between; ids, weights, groups and entries carry the bits of the two separate calls.  Gate kinds SOFTMAX,
+ * SIGMOID and SQRT_SOFTPLUS (with groups); BSX_E_TYPE for the others (use the separate calls); no held tables / prior. */
+BSX_API int32_t bsx_route_plan(const float* logits, const float* bias, int32_t T, int32_t E, int32_t k, int32_t gate_kind, float weight_scale,
+                               int32_t n_group, int32_t topk_group, const unsigned long long* blob_table, unsigned long long shared_blob,
+                               int32_t* ids, float* weights, unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok,
+                               void* stream);
+
+/* ---- a1-a13 in one call: the whole decode-window step of a resident layer - (input RMS norm,) router logits, selection,
+ * plan, grouped experts with the shared expert, weighted combine, (+ residual row).  It is the sequence Basalt's layer loop
+ * issues call by call (src/models/inkling2/session.cpp:680-716; src/models/deepseek41/ops_kernels.cpp:797,931,964), for a C or
+ * C++ caller that wants the step without a host layer of its own.  Every kernel after the first is a programmatic dependent
+ * launch (as Basalt's decode chain: include/basalt/kernels/pdl.hpp:20-32), selection + plan (+ the packed kernels' pass list)
+ * are one kernel.  Nothing is allocated or read back; the call can be captured into a CUDA graph.
+ * desc: layout = the routed experts' (and, with `packed`, the shared expert's); shared_layout = the shared expert's when its
+ * ggml blob has another layout (n_embd = 0: same as layout); packed = blobs are bsx_expert_pack planes (all-NVFP4).
+ * x [n_tokens][n_embd] fp32 or bf16; y [n_tokens][n_embd] fp32; residual [n_tokens][n_embd] fp32 or null; n_tokens <= max_tokens,
+ * max_tokens * top_k <= 1024.  workspace: bsx_moe_layer_workspace_bytes(desc, max_tokens), 256-byte aligned, the same max_tokens
+ * on every call.  status: a device int32 the caller zeroes (bit 0: a bounded wait inside a kernel ran out); required with packed.
+ * bsx_moe_layer_views: where the step leaves its routing inside the workspace (logits, ids, weights, groups), for a caller that
+ * wants to look at them. */
+enum { BSX_LAYER_NO_PDL = 1 };   /* flags: plain launches (for comparison) */
+typedef struct bsx_moe_layer_desc {
+    bsx_expert_layout layout, shared_layout;
+    int32_t n_expert, top_k, gate_kind, n_group, topk_group, packed, flags;
+    float weight_scale, norm_eps;
+    const float* gate;                     /* [n_expert][n_embd] fp32 */
+    const float* bias;                     /* [n_expert] fp32 or null */
+    const unsigned long long* blob_table;  /* [n_expert] device addresses of the experts' blobs; 0 = not held here */
+    unsigned long long shared_blob;        /* 0 = no shared expert */
+    const float* norm_w;                   /* [n_embd] fp32: the layer's input RMS norm weights, or null (rows arrive normed) */
+} bsx_moe_layer_desc;
+typedef struct bsx_moe_layer_views_t {
+    float* logits;
+    int32_t* ids;
+    float* weights;
+    int32_t *n_groups, *grp_start, *ent_dst, *ent_tok;
+    float* rows;
+} bsx_moe_layer_views_t;
+BSX_API size_t bsx_moe_layer_workspace_bytes(const bsx_moe_layer_desc* desc, int32_t max_tokens);
+BSX_API int32_t bsx_moe_layer_views(const bsx_moe_layer_desc* desc, int32_t max_tokens, void* workspace, bsx_moe_layer_views_t* views);
+BSX_API int32_t bsx_moe_layer(const bsx_moe_layer_desc* desc, const void* x, int32_t x_kind, int32_t n_tokens, int32_t max_tokens,
+                              const float* residual, void* workspace, float* y, int32_t* status, void* stream);
+
 /* ---- expert parallelism (no counterpart in the reference, which moves rows between cards through host memory:
  * include/basalt/models/qwen4exp/kernels/dec_moe.hpp:1-11).  bsx_plan_groups turns a dispatch (cnt, off, src over ALL experts)
  * into the groups of the experts this device holds (blob_table[e] != 0): ptr/start/n_groups as bsx_moe_plan makes them,

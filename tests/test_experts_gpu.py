@@ -45,7 +45,9 @@ def run_grouped(L, blobs_dev, group_experts, group_tokens, x_dev, n_out_rows, ou
 CASES = [("nvfp4", 40, 40, 2048, 512), ("q6k", 14, 14, 2048, 512), ("iq1m", 29, 29, 2048, 512), ("nvfp4", 40, 40, 2560, 640),
          ("iq1m_q6k", 29, 14, 1024, 256), ("nvfp4_big", 40, 40, 7168, 2048), ("q8_0", 8, 8, 1024, 256), ("q4k", 12, 12, 1024, 512),
          ("q5k", 13, 13, 1024, 256), ("q4k_q6k", 12, 14, 2048, 512), ("q5_0", 6, 6, 1024, 256), ("q5_1", 7, 7, 1024, 256),
-         ("iq4nl", 20, 20, 1024, 256), ("iq4xs", 23, 23, 1024, 512), ("iq4xs_q5_0", 23, 6, 1024, 256)]
+         ("iq4nl", 20, 20, 1024, 256), ("iq4xs", 23, 23, 1024, 512), ("iq4xs_q5_0", 23, 6, 1024, 256),
+         # the integer tensor-core kernels at the large layer's shape, and a mixed pair they cover
+         ("iq1m_big", 29, 29, 7168, 2048), ("q6k_big", 14, 14, 7168, 2048), ("iq1m_q6k_1k", 29, 14, 2048, 1024)]
 
 
 @pytest.mark.parametrize("impl", ["fast", "simple"])
