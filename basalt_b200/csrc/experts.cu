@@ -19,7 +19,9 @@ const uint16_t h_iq1_grid[2048] = {
 #include "iq1_grid_u16.inc"
 };
 
-const uint16_t* device_grid() {
+}  // namespace
+
+const uint16_t* iq1_device_grid() {
     static std::atomic<const uint16_t*> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
@@ -32,6 +34,8 @@ const uint16_t* device_grid() {
     }
     return g;
 }
+
+namespace {
 
 // src/kernels/cuda/iq_kernels.cu:2471-2503 with include/basalt/kernels/q8_1_finite.hpp:17-31: a warp per 32 values
 __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const float* __restrict__ x, uint8_t* __restrict__ y, int64_t n) {
@@ -274,7 +278,7 @@ static int32_t experts_grouped_impl(int32_t n_x_rows, const bsx_expert_layout* l
     a.out = out;
     a.out_kind = out_kind;
     a.n_x_rows = n_x_rows > 0 ? n_x_rows : 0;
-    a.grid = device_grid();
+    a.grid = iq1_device_grid();
     if (!a.grid) return (int32_t) cudaErrorInvalidSymbol;
     const cudaStream_t st = (cudaStream_t) stream;
     // BSX_EXPERT_IMPL=simple forces the plain kernels (tests compare the two paths)

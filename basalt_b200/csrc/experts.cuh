@@ -76,6 +76,9 @@ __device__ __forceinline__ void load16(const void* x, int kind, int64_t row, int
     }
 }
 
+// the IQ1 codebook (2048 x uint16, 2 bits a coordinate) in this device's global memory; null on a CUDA error
+const uint16_t* iq1_device_grid();
+
 // 0 all launches, 1 gate/up only, 2 down only (bsx_experts_set_phase)
 int experts_phase();
 

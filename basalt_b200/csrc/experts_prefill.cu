@@ -42,6 +42,8 @@ constexpr int kThreadsP = 32 * (1 + kLoaderWarps + kDecoderWarps + kEpilogueWarp
 constexpr float kHScale = 0.25f;   // the SwiGLU output is stored as fp16(h / 4): fp16 then holds |h| up to 2.6e5
 
 enum { PMODE_GU = 0, PMODE_DOWN = 1 };
+enum { WT_NVFP4 = 0, WT_Q6K = 1, WT_IQ1M = 2 };      // how the decoder warps read a weight row
+constexpr float kWScaleKQ = 16.f;  // K / I-quant weights are stored as fp16(16 w): typical weights (~1e-2) sit well inside fp16's normal range
 enum { kStatusTimeout = 1 };
 
 constexpr uint32_t kInstrDesc = instr_desc_f16(kTileM, kTileN);
@@ -73,6 +75,7 @@ struct PrefillArgs {
     const int32_t* n_tiles;
     const __half* xh;                        // [T][H] fp16, permuted, row-scaled
     const float* xinv;                       // [T]
+    const uint16_t* grid;                    // the IQ1 codebook on this device
     __half* h;                               // [rows][I] fp16 (permuted, times kHScale)
     float* dm;                               // [rows][H] fp32
     int32_t* status;                         // sticky error word (0 = ok)
@@ -102,7 +105,7 @@ __global__ void __launch_bounds__(256) prefill_prep_x_kernel(const void* __restr
     for (int64_t c = lane; c < H; c += 32) xh[t * H + (c & ~(int64_t) 15) + perm16((int) (c & 15))] = __float2half_rn(ld(c) * s);
 }
 
-template <int MODE, bool ALIGNED>
+template <int MODE, bool ALIGNED, int WT>
 __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte aligned operand stages: A then B per stage
@@ -115,6 +118,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
     uint64_t* acc_empty = acc_full + 2;           // [2] the 128 epilogue threads arrive
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     uint32_t* lut = tmem_slot + 2;                // [256] fp16 scale pairs
+    uint16_t* s_grid = reinterpret_cast<uint16_t*>(lut + 256);   // [2048] the IQ1 codebook (IQ1_M rows only)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t K = MODE == PMODE_GU ? a.L.n_embd : a.L.n_ff;
@@ -125,6 +129,8 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
     const int n_items = *a.n_tiles * n_n;
 
     for (int i = threadIdx.x; i < 256; i += kThreadsP) lut[i] = scale_pair_bits(i);
+    if (WT == WT_IQ1M)
+        for (int i = threadIdx.x; i < 2048; i += kThreadsP) s_grid[i] = a.grid[i];
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStagesP; ++s) {
             mbar_init(&full[s], kGroupThreads + 32 * kLoaderWarps);
@@ -297,41 +303,92 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
                 for (int i = 0; i < 18; ++i) w[i] = i < nw ? reinterpret_cast<const uint32_t*>(src)[i] : 0u;
             }
         };
-        // the stream of own pairs runs across items: the first pair of the next item is requested while the last pair of this
-        // one is decoded, so a tile switch does not expose a load
-        uint32_t wc[18], wn[18];
-        uint32_t kc = 0;
-        int item = blockIdx.x;
-        Item it;
-        while (item < n_items && !get_item(item, it)) item += gridDim.x;
-        if (item < n_items && grp < npair) load_pair(weight_row(it), grp, wn);
-        while (item < n_items && ok) {
-            const uint8_t* wrow = weight_row(it);
-            int nxt = item + gridDim.x;
-            Item itn;
-            while (nxt < n_items && !get_item(nxt, itn)) nxt += gridDim.x;
-            for (int q = grp; q < npair && ok; q += 2) {
+        if constexpr (WT == WT_NVFP4) {
+            // the stream of own pairs runs across items: the first pair of the next item is requested while the last pair of this
+            // one is decoded, so a tile switch does not expose a load
+            uint32_t wc[18], wn[18];
+            uint32_t kc = 0;
+            int item = blockIdx.x;
+            Item it;
+            while (item < n_items && !get_item(item, it)) item += gridDim.x;
+            if (item < n_items && grp < npair) load_pair(weight_row(it), grp, wn);
+            while (item < n_items && ok) {
+                const uint8_t* wrow = weight_row(it);
+                int nxt = item + gridDim.x;
+                Item itn;
+                while (nxt < n_items && !get_item(nxt, itn)) nxt += gridDim.x;
+                for (int q = grp; q < npair && ok; q += 2) {
 #pragma unroll
-                for (int i = 0; i < 18; ++i) wc[i] = wn[i];
-                if (q + 2 < npair) load_pair(wrow, q + 2, wn);
-                else if (nxt < n_items) load_pair(weight_row(itn), grp, wn);
+                    for (int i = 0; i < 18; ++i) wc[i] = wn[i];
+                    if (q + 2 < npair) load_pair(wrow, q + 2, wn);
+                    else if (nxt < n_items) load_pair(weight_row(itn), grp, wn);
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const int kb = 2 * q + j;
-                    if (kb < nkb && ok) {
-                        const uint32_t kk = kc + (uint32_t) kb, s = kk % kStagesP;
-                        ok = mbar_wait(&empty[s], ((kk / kStagesP) & 1u) ^ 1u);
-                        if (ok) {
-                            store_b(s, &wc[9 * j]);
-                            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
-                            mbar_arrive(&full[s]);
+                    for (int j = 0; j < 2; ++j) {
+                        const int kb = 2 * q + j;
+                        if (kb < nkb && ok) {
+                            const uint32_t kk = kc + (uint32_t) kb, s = kk % kStagesP;
+                            ok = mbar_wait(&empty[s], ((kk / kStagesP) & 1u) ^ 1u);
+                            if (ok) {
+                                store_b(s, &wc[9 * j]);
+                                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+                                mbar_arrive(&full[s]);
+                            }
                         }
                     }
                 }
+                kc += (uint32_t) nkb;
+                item = nxt;
+                it = itn;
             }
-            kc += (uint32_t) nkb;
-            item = nxt;
-            it = itn;
+        } else {
+            // K- and I-quant rows (Q6_K: 210 bytes per 256 values, IQ1_M: 56): the thread decodes its row's 64 values of a k-block
+            // exactly (formats.cuh), stores them as fp16(16 w) - the rounding, 2^-11 relative, is the only one - in the permuted
+            // k order, and hands the stage over.  The decode runs before the wait for the stage, so it overlaps the tensor core.
+            constexpr int kBB = WT == WT_Q6K ? 210 : 56;
+            uint32_t kc = 0;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                Item it;
+                if (!get_item(item, it)) continue;
+                const uint8_t* wrow = weight_row(it);
+                for (int q = grp; q < npair && ok; q += 2) {
+#pragma unroll 1
+                    for (int j = 0; j < 2; ++j) {
+                        const int kb = 2 * q + j;
+                        if (kb >= nkb || !ok) continue;
+                        float v[64];
+                        const uint8_t* blk = wrow + (size_t) (kb >> 2) * kBB;
+                        const int u0 = 2 * (kb & 3);
+                        if (WT == WT_Q6K) {
+                            decode_q6k_32(blk, u0, v);
+                            decode_q6k_32(blk, u0 + 1, v + 32);
+                        } else {
+                            decode_iq1m_32(blk, u0, s_grid, v);
+                            decode_iq1m_32(blk, u0 + 1, s_grid, v + 32);
+                        }
+                        const uint32_t kk = kc + (uint32_t) kb, s = kk % kStagesP;
+                        ok = mbar_wait(&empty[s], ((kk / kStagesP) & 1u) ^ 1u);
+                        if (!ok) break;
+                        uint4* brow = reinterpret_cast<uint4*>(smem + s * kStage + row_off);
+#pragma unroll
+                        for (int sub = 0; sub < 4; ++sub) {
+                            const float* w = v + 16 * sub;
+                            uint32_t p0[4], p1[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const __half2 a2 = __floats2half2_rn(w[i] * kWScaleKQ, w[i + 8] * kWScaleKQ);
+                                const __half2 b2 = __floats2half2_rn(w[4 + i] * kWScaleKQ, w[12 + i] * kWScaleKQ);
+                                p0[i] = *reinterpret_cast<const uint32_t*>(&a2);
+                                p1[i] = *reinterpret_cast<const uint32_t*>(&b2);
+                            }
+                            brow[(2 * sub) ^ swz] = make_uint4(p0[0], p0[1], p0[2], p0[3]);
+                            brow[(2 * sub + 1) ^ swz] = make_uint4(p1[0], p1[1], p1[2], p1[3]);
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                        mbar_arrive(&full[s]);
+                    }
+                }
+                kc += (uint32_t) nkb;
+            }
         }
         if (!ok) atomicOr(a.status, kStatusTimeout);
     } else {
@@ -348,11 +405,15 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const bool row_live = p < it.rows;
+            // NVFP4 blobs end in {s_gate, s_up, s_down, 0}; the block scales were used as scale / 2^8.  K / I-quant rows have no
+            // tail and were stored as 16 w.
+            const bool nv_tail = a.L.gu_type == kTypeNVFP4;
             const float* tail = reinterpret_cast<const float*>(it.blob + a.L.bytes - 16);
+            constexpr float kUnscale = WT == WT_NVFP4 ? 256.f : 1.f / kWScaleKQ;
             const uint32_t tbase = tmem + lane_base + acc * kTileN;
             if (MODE == PMODE_GU) {
-                const float f = row_live ? a.xinv[a.src[it.row0 + p]] * 256.f : 0.f;
-                const float sg = tail[0] * f, su = tail[1] * f;
+                const float f = row_live ? a.xinv[a.src[it.row0 + p]] * kUnscale : 0.f;
+                const float sg = (nv_tail ? tail[0] : 1.f) * f, su = (nv_tail ? tail[1] : 1.f) * f;
                 __half* hrow = a.h + (size_t) (it.row0 + p) * a.L.n_ff + it.n0;
 #pragma unroll 1
                 for (int c0 = 0; c0 < kTileN / 2; c0 += 16) {
@@ -371,7 +432,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
                     }
                 }
             } else {
-                const float f = tail[2] * (256.f / kHScale);
+                const float f = (nv_tail ? tail[2] : 1.f) * (kUnscale / kHScale);
                 float* orow = a.dm + (size_t) (it.row0 + p) * a.L.n_embd + it.n0;
 #pragma unroll 1
                 for (int c0 = 0; c0 < kTileN; c0 += 32) {
@@ -402,7 +463,24 @@ __global__ void __launch_bounds__(kThreadsP, 1) prefill_gemm_kernel(PrefillArgs 
 }
 
 size_t align256p(size_t v) { return (v + 255) & ~(size_t) 255; }
-constexpr size_t kSmemP = 1024 + kStagesP * (kTileM * kBlockK * 2 + kTileN * kBlockK * 2) + 256 + 1024 + 64;   // 199,040 bytes: one CTA per SM
+constexpr size_t kSmemP = 1024 + kStagesP * (kTileM * kBlockK * 2 + kTileN * kBlockK * 2) + 256 + 1024 + 4096 + 64;   // 203,136 bytes: one CTA per SM
+
+int wt_of(int type) { return type == kTypeNVFP4 ? WT_NVFP4 : type == kTypeQ6K ? WT_Q6K : type == kTypeIQ1M ? WT_IQ1M : -1; }
+
+template <int MODE, bool ALIGNED, int WT>
+cudaError_t configure_one() { return cudaFuncSetAttribute(prefill_gemm_kernel<MODE, ALIGNED, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP); }
+
+template <int MODE>
+void launch_mode(int wt, bool aligned16, unsigned grid, const PrefillArgs& a, cudaStream_t st) {
+    if (wt == WT_NVFP4) {
+        if (aligned16) prefill_gemm_kernel<MODE, true, WT_NVFP4><<<grid, kThreadsP, kSmemP, st>>>(a);
+        else prefill_gemm_kernel<MODE, false, WT_NVFP4><<<grid, kThreadsP, kSmemP, st>>>(a);
+    } else if (wt == WT_Q6K) {
+        prefill_gemm_kernel<MODE, false, WT_Q6K><<<grid, kThreadsP, kSmemP, st>>>(a);
+    } else {
+        prefill_gemm_kernel<MODE, false, WT_IQ1M><<<grid, kThreadsP, kSmemP, st>>>(a);
+    }
+}
 
 }  // namespace
 }  // namespace bsx
@@ -421,8 +499,11 @@ extern "C" int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const un
     if (!layout || !blob_table || !off || !src || !tiles || !n_tiles || !aligned(x, 16) || !aligned(scratch, 256) || !aligned(dm, 16) || !status)
         return BSX_E_POINTER;
     const bsx_expert_layout& L = *layout;
-    if (L.gu_type != kTypeNVFP4 || L.up_type != kTypeNVFP4 || L.d_type != kTypeNVFP4) return BSX_E_TYPE;
+    const int wt_gu = wt_of(L.gu_type), wt_d = wt_of(L.d_type);
+    if (wt_gu < 0 || wt_d < 0 || L.up_type != L.gu_type) return BSX_E_TYPE;       // NVFP4, Q6_K or IQ1_M; gate and up of one format
+    if ((L.gu_type == kTypeNVFP4) != (L.d_type == kTypeNVFP4) && L.gu_type == kTypeNVFP4) return BSX_E_TYPE;   // an NVFP4 tail needs NVFP4 gate / up
     if (L.n_embd % 64 || L.n_ff % 64 || (x_kind != BSX_X_F32 && x_kind != BSX_X_BF16)) return BSX_E_GEOMETRY;
+    if ((wt_gu != WT_NVFP4 && L.n_embd % 256) || (wt_d != WT_NVFP4 && L.n_ff % 256)) return BSX_E_GEOMETRY;   // whole 256-value blocks
     if (cap_tiles < 0 || cap_tiles > 65535 || cap_rows < 0 || n_tokens < 0) return BSX_E_GEOMETRY;
     if (cap_tiles == 0 || n_tokens == 0) return BSX_OK;
     const cudaStream_t st = (cudaStream_t) stream;
@@ -440,6 +521,8 @@ extern "C" int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const un
     p += align256p((size_t) n_tokens * 4);
     a.xh = xh;
     a.xinv = xinv;
+    a.grid = iq1_device_grid();
+    if (!a.grid) return (int32_t) cudaErrorInvalidSymbol;
     a.h = reinterpret_cast<__half*>(p);
     a.dm = dm;
     a.status = status;
@@ -447,19 +530,21 @@ extern "C" int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const un
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
     if (!configured[dev].load(std::memory_order_acquire)) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_GU, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_GU, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_DOWN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_gemm_kernel<PMODE_DOWN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemP);
+        cudaError_t e = configure_one<PMODE_GU, true, WT_NVFP4>();
+        if (e == cudaSuccess) e = configure_one<PMODE_GU, false, WT_NVFP4>();
+        if (e == cudaSuccess) e = configure_one<PMODE_DOWN, true, WT_NVFP4>();
+        if (e == cudaSuccess) e = configure_one<PMODE_DOWN, false, WT_NVFP4>();
+        if (e == cudaSuccess) e = configure_one<PMODE_GU, false, WT_Q6K>();
+        if (e == cudaSuccess) e = configure_one<PMODE_DOWN, false, WT_Q6K>();
+        if (e == cudaSuccess) e = configure_one<PMODE_GU, false, WT_IQ1M>();
+        if (e == cudaSuccess) e = configure_one<PMODE_DOWN, false, WT_IQ1M>();
         if (e != cudaSuccess) return (int32_t) e;
         configured[dev].store(true, std::memory_order_release);
     }
     prefill_prep_x_kernel<<<(unsigned) ((n_tokens + 7) / 8), 256, 0, st>>>(x, x_kind, n_tokens, L.n_embd, xh, xinv);
     // persistent CTAs, one per SM; rows that are whole 144-byte chunks (K % 256 == 0) take the variant with 16-byte weight loads
     const unsigned grid = (unsigned) sm_count();
-    if (L.n_embd % 256 == 0) prefill_gemm_kernel<PMODE_GU, true><<<grid, kThreadsP, kSmemP, st>>>(a);
-    else prefill_gemm_kernel<PMODE_GU, false><<<grid, kThreadsP, kSmemP, st>>>(a);
-    if (L.n_ff % 256 == 0) prefill_gemm_kernel<PMODE_DOWN, true><<<grid, kThreadsP, kSmemP, st>>>(a);
-    else prefill_gemm_kernel<PMODE_DOWN, false><<<grid, kThreadsP, kSmemP, st>>>(a);
+    launch_mode<PMODE_GU>(wt_gu, L.n_embd % 256 == 0, grid, a, st);
+    launch_mode<PMODE_DOWN>(wt_d, L.n_ff % 256 == 0, grid, a, st);
     return launch_status();
 }

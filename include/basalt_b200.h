@@ -242,8 +242,10 @@ BSX_API int32_t bsx_experts_grouped_packed(const bsx_expert_layout* layout, cons
  * alone.  Mirrors native_expert_set_mode's phase (iq_kernels.hpp:113-115).  Process-wide; set it back to 0. */
 BSX_API void bsx_experts_set_phase(int32_t phase);
 
-/* ---- a11: prompt-sized grouped experts on the tcgen05 tensor cores (NVFP4 blobs).  Replaces fp4::run_group / run_experts
- * (include/basalt/prefill/moe_fp4.hpp:43-113, src/prefill/moe_fp4.cu:604-687): for the expert-sorted rows of a bsx_dispatch
+/* ---- a11 / a12: prompt-sized grouped experts on the tcgen05 tensor cores, ggml blobs in place: NVFP4 (replaces fp4::run_group /
+ * run_experts, include/basalt/prefill/moe_fp4.hpp:43-113, src/prefill/moe_fp4.cu:604-687) and the K- / I-quant formats Q6_K and
+ * IQ1_M (replaces the int8 MMQ path mmq::quantize -> Context::run -> swiglu -> Context::run, include/basalt/prefill/moe_mmq.hpp:37-125,
+ * src/prefill/moe_mmq.cu:246-356; gate and up of one format, n_embd and n_ff multiples of 256): for the expert-sorted rows of a bsx_dispatch
  * (off, src, and its tile list with tile_rows = 128), gate/up through the rows' tokens, SwiGLU, down; dm[row] (fp32,
  * unweighted, row = dispatch slot) is what bsx_combine reads.  blob_table[e] = device address of expert e's blob.
  * x: fp32 or bf16 [n_tokens][n_embd].  Weights are decoded exactly to fp16 and multiplied by fp16 activations with fp32
@@ -260,6 +262,23 @@ BSX_API int32_t bsx_experts_prefill(const bsx_expert_layout* layout, const unsig
  * expert row bounds on the device -> tiles {expert, first row} per tile_rows rows of an expert, in expert order, and their
  * count.  tiles must hold off[E] / tile_rows + E entries.  E <= 1024. */
 BSX_API int32_t bsx_tiles_from_bounds(const int32_t* off, int32_t E, int32_t tile_rows, int32_t* tiles, int32_t* n_tiles, void* stream);
+
+/* ---- a11 / a12 as the engine's prompt path drives them: a group of up to 16 consecutive experts of a layer, each given by its
+ * blob's address on the HOST side (blobs[i], i < n), over rows the caller grouped by expert.  Replaces fp4::run_group /
+ * run_experts and the Group they take (include/basalt/prefill/moe_fp4.hpp:82-113; call site
+ * src/models/qwen4exp/prefill/expert_fp4.cpp:10-30).  bounds: n + 1 ABSOLUTE row bounds on the device (expert i's rows are
+ * [bounds[i], bounds[i+1]) of dm and of row_token); row_token[row] = the row's token; cap_rows >= the layer's row count (the
+ * largest bound any group of the layer has); x, dm, status as for bsx_experts_prefill.  The blob addresses travel as kernel
+ * arguments: no copy, no synchronisation, capturable.  scratch: bsx_experts_prefill_group_scratch_bytes, 256-byte aligned.
+ * bsx_unit_offsets: out[0] = 0, out[j+1] = sum over i <= j of ceil(rows_i / unit_rows) for n <= 1024 segments of `bounds` -
+ * fp4::plan (unit 64) and plan_blocks (units 64 and 128), moe_fp4.hpp:23-41.  bsx_rebase_bounds: out[i] = bounds[i] - bounds[0],
+ * i <= n (fp4::rebase). */
+BSX_API size_t bsx_experts_prefill_group_scratch_bytes(const bsx_expert_layout* layout, int64_t n_tokens, int64_t cap_rows);
+BSX_API int32_t bsx_experts_prefill_group(const bsx_expert_layout* layout, const void* const* blobs, int32_t n, const int32_t* bounds,
+                                          const int32_t* row_token, int64_t cap_rows, const void* x, int32_t x_kind, int64_t n_tokens,
+                                          void* scratch, float* dm, int32_t* status, void* stream);
+BSX_API int32_t bsx_unit_offsets(const int32_t* bounds, int32_t n, int32_t unit_rows, int32_t* out, void* stream);
+BSX_API int32_t bsx_rebase_bounds(const int32_t* bounds, int32_t n, int32_t* out, void* stream);
 
 /* ---- a11 on the block-scaled FP4 tensor cores: bsx_experts_prefill over blobs packed by bsx_expert_pack (blob_table[e] = a
  * packed blob, 0 = held elsewhere).  Activations enter as four FP4 terms per row (x rows and the SwiGLU rows alike), so the

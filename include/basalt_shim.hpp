@@ -312,3 +312,212 @@ inline bool expert_layout_load_text(const std::string& text, int64_t n_layers, i
     return true;
 }
 }  // namespace basalt::kernels::cpu
+
+// ---- the decode window's plan (src/models/inkling2/kernels/ops.hpp: moe_plan) and the whole step as one call
+namespace basalt::kernels {
+inline void moe_plan(const int32_t* ids, int n_tokens, int k, int n_expert, const unsigned long long* blob_table, unsigned long long* ptr,
+                     int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok, void* stream) {
+    shim_detail::raise("moe_plan", bsx_moe_plan(ids, n_tokens, k, n_expert, blob_table, ptr, start, n_groups, dst, tok, stream));
+}
+}  // namespace basalt::kernels
+
+// ---- include/basalt/prefill/moe_fp4.hpp: the prompt path's NVFP4 experts, a group of up to 16 experts at a time.
+// Same names, argument order and meaning as the reference's, with these differences a caller can observe:
+//   - The reference rounds activations to FP4 planes (one or two terms) that run() and run_group() then read.  This library
+//     multiplies exactly decoded weights by fp16 activations instead (results ~2e-4 from the dequantised fp32 reference, not
+//     ~1e-1 .. 1e-2), so quantize_tokens() does no arithmetic: it notes which rows the planes `a4` stand for, and run_group()
+//     reads those rows (they must still be there when it runs, as they are in the reference's call sites: the layer's input
+//     is not rewritten before its experts have run).  The planes and scale arrays are left untouched.
+//   - The kernels need scratch of their own that the reference's buffers cannot hold (fp16 images of the layer's rows):
+//     Group carries two more fields at its end, `scratch` / `scratch_bytes` (size: group_scratch_bytes) and `status` (a device
+//     int32 the caller zeroes; bit 0 = a bounded wait inside a kernel ran out).  run_group() throws std::invalid_argument
+//     when they are missing.
+//   - run_experts() runs any layer geometry the layout describes (the reference's is built for 2560 x 640); set
+//     Group::layout (basalt::kernels::NativeExpertLayout) - down_off / tail_off are then read from it.
+//   - The plane-level calls quantize() and run(Product) have no counterpart here (there are no planes to multiply); they
+//     throw std::logic_error.  plan(), plan_blocks(), rebase(), cut_pieces(), run_length() and the size helpers are the
+//     reference's.
+#include <algorithm>
+#include <mutex>
+#include <unordered_map>
+
+namespace basalt::prefill::fp4 {
+
+constexpr int kTileTokens = 64;
+constexpr int kMaxExperts = 16;   // experts per launch
+
+namespace shim_detail {
+using basalt::kernels::shim_detail::raise;
+struct Rows {
+    const void* x;
+    int64_t tokens, cols;
+};
+inline std::mutex& mu() {
+    static std::mutex m;
+    return m;
+}
+inline std::unordered_map<const void*, Rows>& noted() {
+    static std::unordered_map<const void*, Rows> m;
+    return m;
+}
+}  // namespace shim_detail
+
+// the reference's sizes (src/prefill/moe_fp4.cu:527-532,566): a caller that sizes its buffers by them keeps working
+inline size_t a4_bytes(int64_t rows, int64_t cols, int experts) {
+    return (size_t) ((rows + kTileTokens - 1) / kTileTokens + experts) * (size_t) (cols / 128) * 4608u;
+}
+inline size_t scale_count(int64_t rows, int experts) { return (size_t) ((rows + kTileTokens - 1) / kTileTokens + experts) * kTileTokens; }
+inline size_t token_bytes(int64_t tokens, int64_t cols) { return (size_t) tokens * (size_t) (cols / 2 + cols / 16); }
+inline int64_t max_blocks(int64_t rows, int n) { return (rows + 2 * kTileTokens - 1) / (2 * kTileTokens) + n; }
+
+inline void plan(const int32_t* bounds, int n, int32_t* tile_off, void* stream) {
+    shim_detail::raise("fp4::plan", bsx_unit_offsets(bounds, n, kTileTokens, tile_off, stream));
+}
+inline void rebase(const int32_t* bounds, int n, int32_t* out, void* stream) { shim_detail::raise("fp4::rebase", bsx_rebase_bounds(bounds, n, out, stream)); }
+inline void plan_blocks(const int32_t* bounds, int n, int32_t* tile_off, int32_t* blk_off, void* stream) {
+    shim_detail::raise("fp4::plan_blocks", bsx_unit_offsets(bounds, n, kTileTokens, tile_off, stream));
+    shim_detail::raise("fp4::plan_blocks", bsx_unit_offsets(bounds, n, 2 * kTileTokens, blk_off, stream));
+}
+
+/// Notes that the planes `a4` stand for rows x[0 .. tokens) of `cols` floats (ld == cols); see the header comment.
+inline void quantize_tokens(const float* x, int64_t tokens, int64_t cols, int64_t ld, void* a4, float* gs, void* stream, bool two = false) {
+    (void) gs; (void) stream; (void) two;
+    if (tokens <= 0) return;
+    if (ld != cols || a4 == nullptr) throw std::invalid_argument("fp4::quantize_tokens: rows must be dense and the planes given");
+    std::lock_guard<std::mutex> lock(shim_detail::mu());
+    shim_detail::noted()[a4] = shim_detail::Rows{x, tokens, cols};
+}
+inline void quantize(const float*, const int32_t*, const int32_t*, const int32_t*, int, void*, float*, int64_t, int64_t, int64_t, void*, bool = false) {
+    throw std::logic_error("fp4::quantize: this library keeps no FP4 planes of the SwiGLU rows; run the experts through fp4::run_group");
+}
+
+struct Product {
+    const uint8_t* blob[kMaxExperts] = {};
+    size_t w_off = 0;
+    int64_t w_rows = 0, w_cols = 0;
+    int n = 0;
+    const void* a4 = nullptr;
+    const float* gs = nullptr;
+    const int32_t* bounds = nullptr;
+    const int32_t* tile_off = nullptr;
+    float* dst = nullptr;
+    int64_t ld_dst = 0, max_rows = 0;
+    bool swiglu = false;
+    const int32_t* ids = nullptr;
+    int64_t tokens = 0;
+    size_t tail_off = 0;
+    const uint8_t* base = nullptr;
+    size_t stride = 0;
+    const int32_t* blk_off = nullptr;
+    int64_t blocks = 0;
+    const int32_t* dst_ids = nullptr;
+    float gate_softcap = 0.0f, up_softcap = 0.0f;
+    bool two = false;
+};
+inline void run(const Product&, void*) {
+    throw std::logic_error("fp4::run: single products over FP4 planes are not provided; fp4::run_group runs gate/up, SwiGLU and down");
+}
+
+struct Group {
+    int n = 0;
+    const uint8_t* blob[kMaxExperts] = {};
+    const int32_t* bounds_host = nullptr;   ///< n + 1 absolute row bounds, on the host
+    const int32_t* bounds_dev = nullptr;    ///< the same bounds on the device
+    const int32_t* ids = nullptr;           ///< the layer's token of each absolute row
+    const void* a4x = nullptr;              ///< the planes quantize_tokens() was given for the layer's rows
+    const float* gsx = nullptr;
+    int64_t tokens = 0;
+    size_t down_off = 0, tail_off = 0;
+    float *h = nullptr, *dm = nullptr;      ///< dm: the layer's output rows [absolute row][n_embd]; h is not used
+    void* a4h = nullptr;
+    float* gsh = nullptr;
+    int32_t *toh = nullptr, *rel = nullptr;
+    // ---- added by this library (see the header comment)
+    basalt::kernels::NativeExpertLayout layout;   ///< the experts' blob geometry
+    void* scratch = nullptr;                      ///< group_scratch_bytes(layout, tokens, the layer's row count), 256-byte aligned
+    size_t scratch_bytes = 0;
+    int32_t* status = nullptr;
+};
+inline size_t group_scratch_bytes(const basalt::kernels::NativeExpertLayout& L, int64_t tokens, int64_t layer_rows) {
+    const bsx_expert_layout c = basalt::kernels::shim_detail::to_c(L);
+    return bsx_experts_prefill_group_scratch_bytes(&c, tokens, layer_rows);
+}
+
+/// How many experts from i0 form the next run: consecutive ones while their rows together stay within row_cap, and at least one.
+inline int run_length(const Group& g, int i0, int64_t row_cap) {
+    const int32_t* b = g.bounds_host;
+    int last = i0 + 1;                             // one past the run's last expert
+    while (last < g.n && (int64_t) b[last + 1] - b[i0] <= row_cap) ++last;
+    return last - i0;
+}
+
+/// Consecutive experts [i0, i0 + n) of the group: gate/up over the rows' tokens, SwiGLU, down -> dm[absolute row].
+inline void run_experts(const Group& g, int i0, int n, void* stream) {
+    if (n < 1 || i0 < 0 || i0 + n > g.n || n > kMaxExperts) throw std::invalid_argument("fp4::run_experts: experts outside the group");
+    shim_detail::Rows rows{};
+    {
+        std::lock_guard<std::mutex> lock(shim_detail::mu());
+        const auto it = shim_detail::noted().find(g.a4x);
+        if (it == shim_detail::noted().end()) throw std::invalid_argument("fp4::run_experts: quantize_tokens() was not called for these planes");
+        rows = it->second;
+    }
+    if (!g.scratch || !g.status) throw std::invalid_argument("fp4::run_experts: Group::scratch and Group::status must be set (fp4::group_scratch_bytes)");
+    const bsx_expert_layout c = basalt::kernels::shim_detail::to_c(g.layout);
+    if (c.n_embd != rows.cols) throw std::invalid_argument("fp4::run_experts: the noted rows are not n_embd wide");
+    const int64_t layer_rows = g.bounds_host[g.n];
+    if (bsx_experts_prefill_group_scratch_bytes(&c, rows.tokens, layer_rows) > g.scratch_bytes) throw std::invalid_argument("fp4::run_experts: scratch too small");
+    const void* blobs[kMaxExperts];
+    for (int i = 0; i < n; ++i) blobs[i] = g.blob[i0 + i];
+    shim_detail::raise("fp4::run_experts", bsx_experts_prefill_group(&c, blobs, n, g.bounds_dev + i0, g.ids, layer_rows, rows.x, BSX_X_F32, rows.tokens,
+                                                                     g.scratch, g.dm, g.status, stream));
+}
+
+inline int run_group(const Group& g, int64_t row_cap, void* stream) {
+    int runs = 0;
+    for (int i0 = 0; i0 < g.n;) {
+        const int n = run_length(g, i0, row_cap);
+        run_experts(g, i0, n, stream);
+        i0 += n;
+        ++runs;
+    }
+    return runs;
+}
+
+struct Pieces {
+    std::vector<int32_t> expert;   ///< per piece: its expert's index j
+    std::vector<int32_t> bounds;   ///< per piece its first row, then the last piece's end
+    std::vector<int32_t> group;    ///< per group its first piece, then the piece count
+};
+/// Splits the rows of n consecutive experts (host row bounds) for buffers of `cap` rows, with the result the reference's
+/// cut_pieces gives (include/basalt/prefill/moe_fp4.hpp:115-123): an expert is laid out as pieces of `whole` rows from its first
+/// row on, `whole` being the largest multiple of the tile size within cap (at least one tile), so that every piece starts on
+/// one of the expert's own tile boundaries; an expert without rows has no piece.  Pieces are then gathered greedily, in order,
+/// into groups of at most kMaxExperts pieces and at most `cap` rows.
+inline void cut_pieces(const int32_t* bounds, int n, int64_t cap, Pieces& out) {
+    out.expert.clear();
+    out.bounds.clear();
+    out.group.clear();
+    int64_t whole = cap - cap % kTileTokens;
+    if (whole < kTileTokens) whole = kTileTokens;
+    for (int j = 0; j < n; ++j) {
+        const int64_t first = bounds[j], rows = bounds[j + 1] - first;
+        const int64_t pieces = rows > 0 ? (rows + whole - 1) / whole : 0;
+        for (int64_t i = 0; i < pieces; ++i) {
+            out.expert.push_back(j);
+            out.bounds.push_back((int32_t) (first + i * whole));
+        }
+    }
+    out.bounds.push_back(n > 0 ? bounds[n] : 0);
+    const int total = (int) out.expert.size();
+    int head = 0;                                  // first piece of the group being filled
+    for (int i = 0; i < total; ++i) {
+        const bool full = i - head == kMaxExperts || (int64_t) out.bounds[(size_t) i + 1] - out.bounds[(size_t) head] > cap;
+        if (i == 0 || full) {
+            out.group.push_back(i);
+            head = i;
+        }
+    }
+    out.group.push_back(total);
+}
+
+}  // namespace basalt::prefill::fp4

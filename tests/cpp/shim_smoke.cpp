@@ -40,6 +40,26 @@ int main() {
     threw = false;
     try { basalt::kernels::wgemm::norm_pack((const float*) nullptr, nullptr, 1e-6f, 2048, 4, nullptr, nullptr, nullptr); } catch (const std::invalid_argument&) { threw = true; }
     if (!threw) { std::puts("norm_pack without a stream must throw"); ++failures; }
+    {
+        // the prompt path's host-side helpers (include/basalt/prefill/moe_fp4.hpp): sizes, runs and pieces
+        namespace fp4 = basalt::prefill::fp4;
+        if (fp4::token_bytes(10, 2560) != 10u * (1280 + 160) || fp4::scale_count(100, 16) != (2 + 16) * 64u || fp4::max_blocks(300, 4) != 3 + 4) { std::puts("fp4 sizes"); ++failures; }
+        const int32_t bounds[6] = {0, 100, 100, 500, 520, 700};      // five experts: 100, 0, 400, 20, 180 rows
+        fp4::Group g;
+        g.n = 5;
+        g.bounds_host = bounds;
+        if (fp4::run_length(g, 0, 256) != 2 || fp4::run_length(g, 2, 256) != 1 || fp4::run_length(g, 3, 256) != 2 || fp4::run_length(g, 0, 1000) != 5) { std::puts("run_length"); ++failures; }
+        fp4::Pieces pc;
+        fp4::cut_pieces(bounds, 5, 200, pc);       // whole = 192: expert 2 is cut into 192 + 192 + 16
+        const std::vector<int32_t> want_e = {0, 2, 2, 2, 3, 4}, want_b = {0, 100, 292, 484, 500, 520, 700}, want_g = {0, 1, 2, 3, 5, 6};
+        if (pc.expert != want_e || pc.bounds != want_b || pc.group != want_g) { std::puts("cut_pieces"); ++failures; }
+        threw = false;
+        try { fp4::run_group(g, 256, nullptr); } catch (const std::invalid_argument&) { threw = true; }
+        if (!threw) { std::puts("run_group without noted rows must throw"); ++failures; }
+        threw = false;
+        try { fp4::run(fp4::Product{}, nullptr); } catch (const std::logic_error&) { threw = true; }
+        if (!threw) { std::puts("run(Product) must say it is not provided"); ++failures; }
+    }
     std::printf("shim %s\n", failures ? "FAILED" : "ok");
     return failures;
 }

@@ -62,6 +62,29 @@ def test_prefill_vs_dequantised_reference(lib, cuda, E, H, I, T, k, xdt):
     assert worst < TOL, worst
 
 
+@pytest.mark.parametrize("name,gt,dt,E,H,I,T,k", [("q6k", 14, 14, 8, 2048, 512, 1100, 2), ("iq1m", 29, 29, 8, 2048, 512, 1100, 2),
+                                                   ("iq1m_q6k_down", 29, 14, 4, 1024, 512, 300, 2), ("iq1m_big", 29, 29, 3, 7168, 2048, 260, 1)])
+def test_prefill_k_and_i_quant_blobs_vs_dequantised_reference(lib, cuda, name, gt, dt, E, H, I, T, k):
+    """Prompt-sized experts over K- and I-quant blobs in place (the reference runs these through its int8 MMQ path,
+    include/basalt/prefill/moe_mmq.hpp:37-125): the decoder warps of the tcgen05 kernel read Q6_K / IQ1_M rows."""
+    rng = np.random.default_rng(E + H + T + gt)
+    Lo, blobs = make_expert_blobs(rng, E, gt, dt, H, I)
+    L = moe.native_expert_layout(gt, dt, H, I)
+    ids = zipf_ids(rng, T, k, E)
+    xd = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).cuda().bfloat16()
+    x = xd.float().cpu().numpy()
+    dm, cnt, off, src, slot = run_prefill(L, dev(stack_blobs(blobs)), ids, k, E, xd)
+    worst = 0.0
+    for e in range(E):
+        if cnt[e]:
+            want = O.expert_forward(Lo, blobs[e], x[src[off[e]:off[e + 1]]])
+            got = dm[off[e]:off[e + 1]]
+            assert np.isfinite(got).all()
+            worst = max(worst, rel_l2(got, want))
+    print("worst relative L2 over experts:", worst)
+    assert worst < TOL, worst
+
+
 def test_prefill_skips_experts_held_elsewhere_and_matches_decode_kernels(lib, cuda):
     rng = np.random.default_rng(77)
     E, H, I, T, k = 8, 2048, 512, 64, 4
