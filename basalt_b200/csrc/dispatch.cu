@@ -156,7 +156,8 @@ dispatch_place_kernel(const int32_t* __restrict__ ids, int64_t n, int k, int E, 
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsigned long long* __restrict__ blobs,
                 unsigned long long shared_blob, int n_tok, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
-                int32_t* __restrict__ n_groups, int32_t* __restrict__ dst, int32_t* __restrict__ tok) {
+                int32_t* __restrict__ n_groups, int32_t* __restrict__ dst, int32_t* __restrict__ tok, PassRec* __restrict__ items,
+                int* __restrict__ n_items) {
     extern __shared__ unsigned long long smb[];
     const PlanSmem ps = plan_smem(smb, E);
     plan_load_blobs(ps, blobs, E);       // constant addresses: before the wait for the kernel that wrote the ids
@@ -165,7 +166,7 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsi
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) plan_note_pair(ps, i, ids[i], E);
     __syncthreads();
-    plan_finish(ps, n, k, E, shared_blob, n_tok, ptr, start, n_groups, dst, tok, nullptr, nullptr);
+    plan_finish(ps, n, k, E, shared_blob, n_tok, ptr, start, n_groups, dst, tok, items, n_items);
 }
 
 // Groups for the experts this device holds, from a dispatch: the experts with rows and a non-zero blob address become
@@ -301,7 +302,7 @@ extern "C" int32_t bsx_dispatch(const int32_t* ids, int64_t n_pairs, int32_t k, 
 
 static int32_t plan_launch(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table,
                            unsigned long long shared_blob, unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst,
-                           int32_t* tok, void* stream) {
+                           int32_t* tok, void* stream, PassRec* items = nullptr, int* n_items = nullptr) {
     if (!stream) return BSX_E_STREAM;
     const int64_t n = (int64_t) T * k;
     if (n <= 0) return BSX_OK;   // the reference returns without touching its outputs (ops.cu:491)
@@ -309,9 +310,18 @@ static int32_t plan_launch(const int32_t* ids, int32_t T, int32_t k, int32_t E, 
     if (E < 1 || E > BSX_PLAN_MAX_EXPERTS) return BSX_E_GEOMETRY;   // E * 16 + n * 4 bytes of shared memory must stay below 48 KB
     if (!ids || !blob_table || !ptr || !start || !n_groups || !dst || !tok) return BSX_E_POINTER;
     const size_t smem = (size_t) E * (sizeof(unsigned long long) + 2 * sizeof(int32_t)) + (size_t) n * sizeof(int32_t);
-    launch_k(moe_plan_kernel, dim3(1), dim3(1024), smem, (cudaStream_t) stream, ids, (int) n, k, E, blob_table, shared_blob, (int) T, ptr, start, n_groups, dst, tok);
+    launch_k(moe_plan_kernel, dim3(1), dim3(1024), smem, (cudaStream_t) stream, ids, (int) n, k, E, blob_table, shared_blob, (int) T, ptr, start, n_groups, dst, tok, items, n_items);
     return launch_status();
 }
+
+namespace bsx {
+// the decode-window plan that also writes the packed expert kernels' pass list (plan.cuh)
+int32_t moe_plan_with_passes(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table, unsigned long long shared_blob,
+                             unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok, PassRec* items, int* n_items,
+                             cudaStream_t st) {
+    return plan_launch(ids, T, k, E, blob_table, shared_blob, ptr, start, n_groups, dst, tok, (void*) st, items, n_items);
+}
+}  // namespace bsx
 
 // the tile list of a dispatch from its row bounds alone: one block, a scan over the experts' tile counts
 __global__ void __launch_bounds__(1024)

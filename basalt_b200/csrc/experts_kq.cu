@@ -75,7 +75,8 @@ __device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1
 // One warp per image row: the row as two int8 terms under one scale, x s ~ q1 + q2 / 254, s = 127 / max|x|; inv[row] = 1 / s.
 // Layout: img[row][term][K] int8 in column order.  CORR (IQ1_M): per 256 columns the 32 negated group-of-8 sums of each term as
 // 16 hi + lo, corr[row][term][K / 256][hi 32 bytes | lo 32 bytes], a group at the byte its coefficient has in the A fragment:
-// group 4 u + t (u = 32-column unit, t = group inside it) -> byte 4 t + u (u < 4) or 16 + 4 t + (u - 4).
+// group 4 u + t (u = 32-column unit, t = group inside it) -> byte 4 t + p (u < 4) or 16 + 4 t + p with p = 0, 2, 1, 3 for
+// u % 4 = 0, 1, 2, 3 (the order in which the product kernel can assemble the coefficients cheaply).
 // FROM_H = false: rows of x (row i of x when the caller gave the number of x rows, else the row of entry i); true: row e of
 // the SwiGLU output.  The last block lists the passes (up to 4 consecutive entries of a group) and zeroes the work counter.
 template <bool FROM_H, bool CORR>
@@ -169,7 +170,8 @@ kq_image_kernel(ExpertArgs a, int8_t* __restrict__ img, int8_t* __restrict__ cor
             for (int h = 0; h < 2; ++h) {
                 const int gi = ((sb & 15) << 1) + h;               // group inside the 256-column block
                 const int u = gi >> 2, t = gi & 3;
-                const int slot = u < 4 ? 4 * t + u : 16 + 4 * t + (u - 4);
+                const int pos = ((u & 1) << 1) | ((u >> 1) & 1);      // units (0, 1, 2, 3) of a half sit in bytes (0, 2, 1, 3)
+                const int slot = (u < 4 ? 0 : 16) + 4 * t + pos;
 #pragma unroll
                 for (int term = 0; term < 2; ++term) {
                     const int neg = -(term ? sum2[h] : sum1[h]);
@@ -188,7 +190,7 @@ kq_image_kernel(ExpertArgs a, int8_t* __restrict__ img, int8_t* __restrict__ cor
 // activation columns; adds d / 8-scaled... the caller scales: tot[i] += I[i] * d[row] where I is the exact integer
 // 8 m c q - coefficient sums described at the top.  bcol: this lane's column, at the block's first byte plus 8 t;
 // ccol: the column's 64 correction bytes of this block.
-__device__ __forceinline__ void iq1m_block(const uint8_t* ra, const uint8_t* rb, const uint32_t* __restrict__ grid32, const uint8_t* bcol,
+__device__ __forceinline__ void iq1m_block(const uint8_t* ra, const uint8_t* rb, const uint2* __restrict__ tab, const uint8_t* bcol,
                                            const uint8_t* ccol, int t, float (&tot)[4]) {
     uint32_t wa[14], wb[14];
 #pragma unroll
@@ -197,28 +199,42 @@ __device__ __forceinline__ void iq1m_block(const uint8_t* ra, const uint8_t* rb,
         wa[2 * i] = va.x; wa[2 * i + 1] = va.y;
         wb[2 * i] = vb.x; wb[2 * i + 1] = vb.y;
     }
-    // words 0-7: qs (unit u = bytes 4u..4u+3), 8-11: qh (unit u = bytes 2u, 2u+1), 12-13: four scale words
+    // words 0-7: qs (unit u = bytes 4u..4u+3), 8-11: qh (unit u = bytes 2u, 2u+1; group t = nibble t), 12-13: four scale words
     int acc[4] = {0, 0, 0, 0};
-    uint32_t ca[4] = {0u, 0u, 0u, 0u};     // correction operand in fragment order: row g low, row g+8 low, row g high, row g+8 high
-    const int sq = 8 * t, sh4 = 4 * t, s3 = 3 * (t >> 1);
+    const uint32_t sel = 0x4440u | (uint32_t) t;     // byte t of a word, zero-extended
+    const int s4 = 4 * t, s3 = 3 * (t >> 1);
+    uint32_t msum[4] = {0u, 0u, 0u, 0u};              // the groups' scales m as bytes, in the correction operand's order (below)
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         uint32_t a[4];
+        constexpr int kPos[4] = {0, 2, 1, 3};        // unit u of a half sits in byte kPos[u & 3] of that half's correction word
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const uint32_t* w = r ? wb : wa;
-            const uint32_t qsb = (w[u] >> sq) & 0xFFu;
-            const uint32_t nib = (w[8 + (u >> 1)] >> (16 * (u & 1) + sh4)) & 0xFu;
-            const uint32_t scw = w[12 + (u >> 2)] >> (16 * ((u >> 1) & 1));          // scale word u / 2
-            const uint32_t m = 2u * ((scw >> (6 * (u & 1) + s3)) & 7u) + 1u;
-            const uint32_t e = grid32[qsb | ((nib & 7u) << 8)];
-            a[r] = (e & 0x0F0F0F0Fu) * m;
-            a[2 + r] = ((e >> 4) & 0x0F0F0F0Fu) * m;
-            const uint32_t coef = m * ((nib & 8u) ? 9u : 7u);
-            ca[(u < 4 ? 0 : 2) + r] |= coef << (8 * (u & 3));
+            const uint32_t qsb = __byte_perm(w[u], 0u, sel);
+            const uint32_t nib = (w[8 + (u >> 1)] >> (16 * (u & 1) + s4)) & 0xFu;
+            const uint2 e = tab[nib * 256u + qsb];                                         // 12-bit index: the delta bit rides along
+            const uint32_t sw = w[12 + (u >> 2)] >> s3;                                    // the thread's scale field of unit u now sits at a fixed bit
+            const int fb = 16 * ((u >> 1) & 1) + 6 * (u & 1);
+            const uint32_t m = fb > 0 ? (((sw >> (fb - 1)) & 14u) | 1u) : (((sw << 1) & 14u) | 1u);   // 2 s + 1
+            a[r] = e.x * m;
+            a[2 + r] = e.y * m;
+            msum[(u < 4 ? 0 : 2) + r] += m << (8 * kPos[u & 3]);
         }
         const uint2 b = *reinterpret_cast<const uint2*>(bcol + 32 * u);
         mma_u8s8_k32(acc, a[0], a[1], a[2], a[3], b.x, b.y);
+    }
+    // the correction operand: byte = m (8 - 8 delta) = 7 m + 2 m [delta = -1/8], four groups at a time.  The delta bits of units
+    // (0, 1) are bits 4t+3 and 4t+19 of qh word 0, of units (2, 3) the same bits of qh word 1: shifted and merged they land in bytes
+    // 0, 2 and 1, 3 - the order kPos gives the scales.
+    uint32_t ca[4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint32_t* w = r ? wb : wa;
+        const uint32_t dlo = ((w[8] >> (s4 + 3)) & 0x00010001u) | (((w[9] >> (s4 + 3)) & 0x00010001u) << 8);
+        const uint32_t dhi = ((w[10] >> (s4 + 3)) & 0x00010001u) | (((w[11] >> (s4 + 3)) & 0x00010001u) << 8);
+        ca[r] = 7u * msum[r] + 2u * (msum[r] & (dlo * 0xFFu));
+        ca[2 + r] = 7u * msum[2 + r] + 2u * (msum[2 + r] & (dhi * 0xFFu));
     }
     int chi[4] = {0, 0, 0, 0}, clo[4] = {0, 0, 0, 0};
     {
@@ -295,8 +311,8 @@ kq_mma_kernel(ExpertArgs a, const int8_t* __restrict__ img, const int8_t* __rest
     const int xstride = nblk * 64 + 16;                                        // ... and between their correction columns
     uint8_t* xs = smem;                                                        // [8][cstride]
     uint8_t* cs = xs + (size_t) kColsQ * cstride;                              // [8][xstride] (IQ1_M)
-    uint32_t* grid32 = reinterpret_cast<uint32_t*>(cs + (Q::kCorr ? (size_t) kColsQ * xstride : 0));   // [2048] (IQ1_M)
-    uint8_t* wbase = reinterpret_cast<uint8_t*>(grid32) + (Q::kCorr ? 8192 : 0);
+    uint2* tab = reinterpret_cast<uint2*>(cs + (Q::kCorr ? (size_t) kColsQ * xstride : 0));   // [4096] (IQ1_M)
+    uint8_t* wbase = reinterpret_cast<uint8_t*>(tab) + (Q::kCorr ? 32768 : 0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     uint8_t* wring = wbase + (size_t) warp * kStages * kStageBytes;
@@ -306,14 +322,18 @@ kq_mma_kernel(ExpertArgs a, const int8_t* __restrict__ img, const int8_t* __rest
     __shared__ int s_work;
 
     if (Q::kCorr) {
-        // the codebook as one word per point: coordinate i's code c = g + 1 in the low nibble of byte i (i < 4) or the high nibble
-        // of byte i - 4, so that `word & 0x0F0F0F0F` and `(word >> 4) & 0x0F0F0F0F` are the two halves of an 8-weight group
-        for (int i = threadIdx.x; i < 2048; i += kThreads) {
-            const uint32_t p = a.grid[i];
-            uint32_t e = 0u;
+        // the codebook as 8 bytes per point, coordinate i's code c = g + 1 in byte i: the two words are the two MMA operand
+        // registers of an 8-weight group.  Indexed by the block's 12-bit (qh nibble, qs byte) pair, whose top bit (the group's
+        // delta sign) does not change the point: 4096 entries, each point twice.
+        for (int i = threadIdx.x; i < 4096; i += kThreads) {
+            const uint32_t p = a.grid[i & 2047];
+            uint32_t lo = 0u, hi = 0u;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) e |= ((p >> (2 * c)) & 3u) << (8 * (c & 3) + 4 * (c >> 2));
-            grid32[i] = e;
+            for (int c = 0; c < 4; ++c) {
+                lo |= ((p >> (2 * c)) & 3u) << (8 * c);
+                hi |= ((p >> (2 * c + 8)) & 3u) << (8 * c);
+            }
+            tab[i] = make_uint2(lo, hi);
         }
     }
     pdl_wait();
@@ -426,7 +446,7 @@ kq_mma_kernel(ExpertArgs a, const int8_t* __restrict__ img, const int8_t* __rest
                 const int blk = chunk * kChunkBlocks + b;
                 const uint8_t* ra = st + g * kChunkBytes + b * Q::kBlock;
                 const uint8_t* rbp = st + (g + 8) * kChunkBytes + b * Q::kBlock;
-                if constexpr (Q::kCorr) iq1m_block(ra, rbp, grid32, bcol + 256 * blk, ccol + 64 * blk, t, tot);
+                if constexpr (Q::kCorr) iq1m_block(ra, rbp, tab, bcol + 256 * blk, ccol + 64 * blk, t, tot);
                 else q6k_block(ra, rbp, bcol + 256 * blk, t, tot);
             }
             __syncwarp();   // every lane is done with this stage before a later issue overwrites it
@@ -455,7 +475,7 @@ size_t al256q(size_t v) { return (v + 255) & ~(size_t) 255; }
 template <int TYPE>
 size_t kq_smem(int64_t K) {
     using Q = QT<TYPE>;
-    return (size_t) kColsQ * (K + Q::kPad) + (Q::kCorr ? (size_t) kColsQ * ((K >> 8) * 64 + 16) + 8192 : 0) +
+    return (size_t) kColsQ * (K + Q::kPad) + (Q::kCorr ? (size_t) kColsQ * ((K >> 8) * 64 + 16) + 32768 : 0) +
            (size_t) Q::kWarps * Q::kStages * kRowsQ * kChunkBlocks * Q::kBlock + 128;
 }
 

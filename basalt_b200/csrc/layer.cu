@@ -71,7 +71,9 @@ Carve carve(const bsx_moe_layer_desc& d, int32_t T, void* ws) {
     c.scratch = take(d.packed ? bsx_experts_packed_scratch_bytes(&d.layout, c.cap_rows) : bsx_expert_scratch_bytes(&d.layout, c.cap_rows));
     if (c.own_shared) {
         c.s_out = reinterpret_cast<float*>(take((size_t) T * H * 4));
-        c.s_scratch = take(bsx_expert_scratch_bytes(&d.shared_layout, T));
+        // the decode kernels' scratch, or (windows of 16+ tokens) the prompt kernels': the larger of the two
+        const size_t dec = bsx_expert_scratch_bytes(&d.shared_layout, T), pre = bsx_experts_prefill_group_scratch_bytes(&d.shared_layout, T, T);
+        c.s_scratch = take(dec > pre ? dec : pre);
         c.s_ptr = reinterpret_cast<unsigned long long*>(take(16));
         c.s_start = reinterpret_cast<int32_t*>(take(16));
         c.s_one = reinterpret_cast<int32_t*>(take(16));
@@ -203,7 +205,16 @@ extern "C" int32_t bsx_moe_layer(const bsx_moe_layer_desc* d, const void* x, int
         launch_k(own_shared_plan_kernel, dim3(1), dim3(128), 0, st, d->shared_blob, (int) T, c.s_ptr, c.s_start, c.s_one, c.s_iota);
         rc = launch_status();
         if (rc != BSX_OK) return rc;
-        rc = bsx_experts_grouped(&d->shared_layout, c.s_ptr, c.s_start, c.s_one, c.s_iota, c.s_iota, 1, T, xe, xe_kind, c.s_scratch, c.s_out, BSX_OUT_F32, stream);
+        // A shared expert sees every token.  From 16 tokens on its rows go through the prompt-sized kernel (one pass over the blob
+        // for the whole window; the decode kernels take 4 or 8 entries a pass and would stream it several times), when that
+        // kernel reads the blob's formats and the caller gave a status word.
+        rc = BSX_E_TYPE;
+        if (T >= 16 && status != nullptr && bsx_experts_prefill_group_scratch_bytes(&d->shared_layout, T, T) != 0) {
+            const void* blob1[1] = {reinterpret_cast<const void*>((uintptr_t) d->shared_blob)};
+            rc = bsx_experts_prefill_group(&d->shared_layout, blob1, 1, c.s_start, c.s_iota, T, xe, xe_kind, T, c.s_scratch, c.s_out, status, stream);
+        }
+        if (rc == BSX_E_TYPE || rc == BSX_E_GEOMETRY)
+            rc = bsx_experts_grouped(&d->shared_layout, c.s_ptr, c.s_start, c.s_one, c.s_iota, c.s_iota, 1, T, xe, xe_kind, c.s_scratch, c.s_out, BSX_OUT_F32, stream);
         if (rc != BSX_OK) return rc;
         shared = c.s_out;
     }

@@ -13,6 +13,7 @@
 
 #include <atomic>
 #include <climits>
+#include <cstdlib>
 
 #include "plan.cuh"
 
@@ -168,7 +169,7 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
 // as one fmaf chain, xor butterfly over the warp, the 8 warp sums in order.  The per-tile reduction buffer is doubled so a
 // tile needs one block barrier.
 template <int NV, int G, bool BF16>
-__global__ void __launch_bounds__(kLogitThreads, 1)
+__global__ void __launch_bounds__(kLogitThreads, 2)
 router_logits_staged_kernel(const void* __restrict__ x, const float* __restrict__ gate, int n_embd, int n_expert, int n_tokens,
                             int tok_per_block, float* __restrict__ logits) {
     extern __shared__ __align__(16) uint8_t xsm[];
@@ -242,7 +243,7 @@ router_logits_staged_kernel(const void* __restrict__ x, const float* __restrict_
     }
 }
 
-constexpr size_t kStagedSmemMax = 160 * 1024;
+constexpr size_t kStagedSmemMax = 96 * 1024;
 
 template <int NV, int G, bool BF16>
 int32_t launch_logits_staged(const void* x, const float* gate, int T, int E, int H, int tpb, float* logits, cudaStream_t st) {
@@ -561,9 +562,10 @@ static int32_t logits_launch(const void* x, int32_t x_kind, const float* gate, i
     const int nv = (H / 4 + kLogitThreads - 1) / kLogitThreads;
     // decode windows of 16+ tokens whose rows fit shared memory: the staged kernel, one wave of blocks
     const size_t row_bytes = (size_t) H * (bf16 ? 2 : 4);
-    if (T >= 16 && T <= 1024 && nv <= 4 && 8 * row_bytes <= kStagedSmemMax) {
+    static const bool plain_only = [] { const char* e = getenv("BSX_LOGITS_PLAIN"); return e && e[0] == '1'; }();   // measurement switch
+    if (!plain_only && T >= 16 && T <= 1024 && nv <= 4 && 8 * row_bytes <= kStagedSmemMax) {
         int tpb = (int) (kStagedSmemMax / row_bytes) & ~7;
-        tpb = tpb > 32 ? 32 : tpb;
+        tpb = tpb > 16 ? 16 : tpb;      // 16 tokens (64 KB of bf16 rows at hidden 2048): two or three blocks share an SM
         if (tpb > ((T + 7) & ~7)) tpb = (T + 7) & ~7;
         const int tiles = (T + tpb - 1) / tpb;
         int Gs = nv <= 2 ? 8 : 4;
@@ -681,6 +683,10 @@ extern "C" int32_t bsx_route_tail_skip(int32_t* ids, float* weights, const int32
 }
 
 namespace bsx {
+int32_t moe_plan_with_passes(const int32_t* ids, int32_t T, int32_t k, int32_t E, const unsigned long long* blob_table, unsigned long long shared_blob,
+                             unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok, PassRec* items, int* n_items,
+                             cudaStream_t st);
+
 // selection + plan (+ the packed kernels' pass list when items is given); BSX_E_TYPE: a gate kind the fused kernel does not cover
 int32_t route_plan_launch(const float* logits, const float* bias, int32_t T, int32_t E, int32_t k, int32_t gate_kind, float weight_scale,
                           int32_t n_group, int32_t topk_group, const unsigned long long* blob_table, unsigned long long shared_blob, int32_t* ids,
@@ -699,6 +705,13 @@ int32_t route_plan_launch(const float* logits, const float* bias, int32_t T, int
         if (n_group > 32 || E % n_group) return BSX_E_GEOMETRY;
         if (topk_group < 1 || topk_group > n_group) topk_group = n_group;
         if ((int64_t) topk_group * (E / n_group) < k) return BSX_E_GEOMETRY;
+    }
+    if (T > 32) {
+        // One warp's selection is a chain of ~10 us whatever the window; the fused block has 32 warps, so beyond 32 tokens its
+        // warps would take tokens in turn.  Wider windows keep the selection spread over blocks and fuse only plan + pass list.
+        const int32_t rc = bsx_router_select(logits, bias, T, E, k, gate_kind, weight_scale, n_group, topk_group, 0.f, nullptr, 0, ids, weights, (void*) st);
+        if (rc != BSX_OK) return rc;
+        return moe_plan_with_passes(ids, T, k, E, blob_table, shared_blob, ptr, start, n_groups, dst, tok, items, n_items, st);
     }
     const size_t smem = plan_smem_bytes(E, T * k);
 #define BSX_RP(R) launch_k(route_plan_kernel<R>, dim3(1), dim3(1024), smem, st, logits, bias, (int) T, (int) E, (int) k, weight_scale, (int) gate_kind, (int) n_group, \

@@ -31,9 +31,15 @@ def build(force: bool = False) -> None:
     src = HERE / "moe_oracle.c"
     if force or not so.exists() or so.stat().st_mtime < src.stat().st_mtime or not (HERE / "libstdrandn.so").exists():
         subprocess.check_call(["make", "-C", str(HERE), "oracle"], stdout=subprocess.DEVNULL)
-    ref = Path(os.environ.get("BASALT_REFERENCE", "/root/reference"))
+    ref = reference_checkout()
     if ref.is_dir() and (force or not (HERE / "_ref" / "libref_cpu.so").exists() or not (HERE / "_ref" / "libref_gpu.so").exists()):
         subprocess.check_call(["make", "-C", str(HERE), "-j8", "ref", f"REF={ref}"], stdout=subprocess.DEVNULL)
+
+
+def reference_checkout() -> Path:
+    """Where the reference engine's sources lie: $BASALT_REFERENCE, else a directory named `reference` beside this repository."""
+    env = os.environ.get("BASALT_REFERENCE")
+    return Path(env) if env else HERE.parent.parent / "reference"
 
 
 _lib = None
@@ -398,6 +404,9 @@ def ref_cpu():
         L.ref_pool_workers.argtypes = [C.c_void_p]
         L.ref_pool_layer.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_float, C.c_void_p, C.c_int,
                                      _i32p, _i32p, _f32p, C.c_int, _f32p]
+        if hasattr(L, "ref_avx2_layer"):
+            L.ref_avx2_layer.argtypes = [C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_int, _i32p, _i32p, _f32p, C.c_int, _f32p]
+            L.ref_cpu_info.argtypes = [C.c_char_p, C.c_int]
         if hasattr(L, "ref_layout_load_text"):
             L.ref_layout_load_text.argtypes = [C.c_char_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float,
                                                C.c_void_p, C.c_void_p, C.c_char_p, C.c_int]

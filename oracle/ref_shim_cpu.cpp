@@ -8,10 +8,17 @@
 //   cpu::native_fmt / native_quant_act / native_quant_h  include/basalt/kernels/cpu/native_expert.hpp:44-58
 //   cpu::ExpertPool::run_split_multi_native              include/basalt/kernels/cpu/pool.hpp:96-97
 //   cpu::expert_layout_load_text / expert_layout         include/basalt/kernels/cpu/expert_layout.hpp:53-65
+//   cpu::cpu_name / cpu_avx512_ok / cpu_avx2_ok           include/basalt/kernels/cpu/expert_layout.hpp:37-52
+//   cpu::nvfp4_256_gu_rows / nvfp4_256_down_rows          include/basalt/kernels/cpu/nvfp4_avx2.hpp:10-18 (the AVX2 kernels, called
+//                                                         directly so that the AVX2 path can be timed on a CPU that also has AVX-512)
 #include "basalt/ggml/ggml.h"
 #include "basalt/kernels/cpu/expert_layout.hpp"
 #include "basalt/kernels/cpu/native_expert.hpp"
+#include "basalt/kernels/cpu/nvfp4_avx2.hpp"
 #include "basalt/kernels/cpu/pool.hpp"
+
+#include <barrier>
+#include <thread>
 
 #include <cstdint>
 #include <cstring>
@@ -121,6 +128,70 @@ int ref_layout_load_text(const char* text, int64_t len, int64_t n_layers, int64_
         r[5] = (int64_t) f.up_off;
     }
     return 1;
+}
+
+// The host CPU as the reference names it, and the widest instruction set its kernels pick here: 3 = AVX-512, 2 = AVX2, 0 = neither.
+int ref_cpu_info(char* name, int name_len) {
+    const std::string n = cpu::cpu_name();
+    if (name && name_len > 0) { std::strncpy(name, n.c_str(), (size_t) name_len - 1); name[name_len - 1] = 0; }
+    return cpu::cpu_avx512_ok() ? 3 : cpu::cpu_avx2_ok() ? 2 : 0;
+}
+
+// The same layer step as ref_pool_layer for all-NVFP4 blobs with the reference's AVX2 kernels forced (nvfp4_256_*), whatever
+// else the CPU has: `n_threads` threads, each taking the same slice of rows of every job (the pool's row split), gate/up
+// rows first, then - after every thread has finished them - the down rows.  Returns 0, -1 on a geometry the kernels refuse.
+int ref_avx2_layer(int n_threads, int64_t n_embd, int64_t n_ff, const uint8_t* const* blobs, int n_expert, const int32_t* off,
+                   const int32_t* src, const float* x, int T, float* rows_out) {
+    cpu::NativeFmt f;
+    std::string e;
+    if (!cpu::native_fmt(40, 40, n_embd, n_ff, f, e, 0.f)) return -1;
+    if (!cpu::cpu_avx2_ok() || !cpu::nvfp4_256_fits((int) n_embd, (int) n_ff)) return -1;
+    std::vector<uint8_t> act((size_t) T * f.act_bytes);
+    for (int t = 0; t < T; ++t) cpu::native_quant_act(f, x + (size_t) t * n_embd, act.data() + (size_t) t * f.act_bytes);
+    struct Job { const uint8_t* blob; int r0, nt; };
+    std::vector<Job> jobs;
+    for (int ex = 0; ex < n_expert; ++ex)
+        for (int r0 = off[ex]; r0 < off[ex + 1]; r0 += cpu::MAXT) jobs.push_back(Job{blobs[ex], r0, off[ex + 1] - r0 < cpu::MAXT ? off[ex + 1] - r0 : cpu::MAXT});
+    const int n_rows = off[n_expert];
+    std::vector<float> h((size_t) n_rows * n_ff);
+    std::vector<uint8_t> hq((size_t) n_rows * f.h_bytes);
+    if (n_threads < 1) n_threads = 1;
+    std::barrier sync(n_threads);
+    auto work = [&](int tid) {
+        const int g0 = (int) (n_ff * tid / n_threads), g1 = (int) (n_ff * (tid + 1) / n_threads);
+        for (const Job& j : jobs) {
+            const void* a[cpu::MAXT];
+            float* ff[cpu::MAXT];
+            for (int i = 0; i < j.nt; ++i) {
+                a[i] = act.data() + (size_t) src[j.r0 + i] * f.act_bytes;
+                ff[i] = h.data() + (size_t) (j.r0 + i) * n_ff;
+            }
+            float sg, su;
+            std::memcpy(&sg, j.blob + f.bytes - 16, 4);
+            std::memcpy(&su, j.blob + f.bytes - 12, 4);
+            if (g1 > g0) cpu::nvfp4_256_gu_rows(j.blob, f.gu_row, f.up_off, (int) n_embd, sg, su, 0.f, a, j.nt, ff, g0, g1);
+        }
+        sync.arrive_and_wait();
+        for (int r = tid; r < n_rows; r += n_threads) cpu::native_quant_h(f, h.data() + (size_t) r * n_ff, hq.data() + (size_t) r * f.h_bytes);
+        sync.arrive_and_wait();
+        const int d0 = (int) (n_embd * tid / n_threads), d1 = (int) (n_embd * (tid + 1) / n_threads);
+        for (const Job& j : jobs) {
+            const void* a[cpu::MAXT];
+            float* out[cpu::MAXT];
+            for (int i = 0; i < j.nt; ++i) {
+                a[i] = hq.data() + (size_t) (j.r0 + i) * f.h_bytes;
+                out[i] = rows_out + (size_t) (j.r0 + i) * n_embd;
+            }
+            float sd;
+            std::memcpy(&sd, j.blob + f.bytes - 8, 4);
+            if (d1 > d0) cpu::nvfp4_256_down_rows(j.blob + f.down_off, f.d_row, (int) n_ff, sd, a, j.nt, out, d0, d1);
+        }
+    };
+    std::vector<std::thread> pool;
+    for (int t = 1; t < n_threads; ++t) pool.emplace_back(work, t);
+    work(0);
+    for (std::thread& t : pool) t.join();
+    return 0;
 }
 
 }  // extern "C"

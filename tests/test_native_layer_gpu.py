@@ -162,3 +162,17 @@ def test_one_call_layer_with_input_norm_vs_oracle(lib, cuda):
             rows[off[e]:off[e + 1]] = O.expert_forward(Lo, blobs[e], xn[src[off[e]:off[e + 1]]])
     want = O.combine(rows, slot, w, O.expert_forward(Lo, blobs[E], xn))
     assert rel_l2(y, want) < 2e-3, rel_l2(y, want)
+
+
+def test_one_call_layer_wide_window_with_a_shared_expert_of_its_own_format(lib, cuda):
+    """24 tokens, IQ1_M routed experts, a Q6_K shared expert: from 16 tokens on the shared expert's rows go through the
+    prompt-sized kernel (one pass over its blob); the result sits on the oracle and on the call-by-call layer within the bar."""
+    rng = np.random.default_rng(8)
+    E, H, I, k, T = 32, 1024, 512, 4, 24
+    ref, nat = _layers(rng, E, H, I, k, capi.GATE_SIGMOID, 29, 29, True, False, T, True, 14)
+    x = torch.from_numpy(rng.standard_normal((T, H)).astype(np.float32)).cuda().bfloat16()
+    y0 = ref.forward(x).clone()
+    y1 = nat.forward(x).clone()
+    nat.check_status()
+    assert torch.equal(nat.ids[:T], ref.ids[:T])
+    assert rel_l2(y1.cpu().numpy(), y0.cpu().numpy()) < 1e-3
