@@ -169,6 +169,30 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsi
     plan_finish(ps, n, k, E, shared_blob, n_tok, ptr, start, n_groups, dst, tok, items, n_items);
 }
 
+// ---------------------------------------------------------------------------------------------- expert-parallel plan, one launch
+// Every rank holds every token's routing (all-gathered); this block turns the pairs that name experts held HERE (a non-zero
+// blob address) into groups and entries - ent_dst = the pair's index (its row in the rows buffer), ent_tok = its token's
+// index among all gathered tokens - plus one group for the shared expert over this rank's own tokens.  Replaces a full
+// dispatch of all pairs (three launches) and the group extraction after it.  ids may come in blocks of `blk` pairs, one per
+// source rank, `blk_stride` values apart (the layout an all-gather of [ids | weights] buffers leaves); blk = 0: dense.
+__global__ void __launch_bounds__(1024)
+ep_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int blk, int blk_stride, int E, const unsigned long long* __restrict__ blobs,
+               unsigned long long shared_blob, int tok_lo, int tok_n, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
+               int32_t* __restrict__ n_groups, int32_t* __restrict__ dst, int32_t* __restrict__ tok) {
+    extern __shared__ unsigned long long smb[];
+    const PlanSmem ps = plan_smem(smb, E);
+    plan_load_blobs(ps, blobs, E);
+    pdl_wait();
+    pdl_launch_dependents();
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int at = blk > 0 ? (i / blk) * blk_stride + (i % blk) : i;
+        plan_note_pair(ps, i, ids[at], E);
+    }
+    __syncthreads();
+    plan_finish<false>(ps, n, k, E, shared_blob, tok_n, ptr, start, n_groups, dst, tok, nullptr, nullptr, tok_lo);
+}
+
 // Groups for the experts this device holds, from a dispatch: the experts with rows and a non-zero blob address become
 // groups in ascending order; their dispatch rows, in order, become the entries (ent_dst = the dispatch row, so outputs land
 // where the combine's slot[] points; ent_tok = the row's token).  Rows of experts held elsewhere get no entry.
@@ -345,6 +369,19 @@ extern "C" int32_t bsx_tiles_from_bounds(const int32_t* off, int32_t E, int32_t 
     if (E < 1 || E > kMaxExpert || tile_rows < 1) return BSX_E_GEOMETRY;
     if (!off || !tiles || !n_tiles) return BSX_E_POINTER;
     tiles_from_bounds_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(off, E, tile_rows, tiles, n_tiles);
+    return launch_status();
+}
+
+extern "C" int32_t bsx_ep_plan(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t pairs_per_block, int32_t block_stride, int32_t E,
+                               const unsigned long long* blob_table, unsigned long long shared_blob, int32_t tok_lo, int32_t tok_n,
+                               unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* ent_dst, int32_t* ent_tok, void* stream) {
+    if (!stream) return BSX_E_STREAM;
+    if (E < 1 || E > BSX_PLAN_MAX_EXPERTS || k < 1 || n_pairs < 0 || tok_lo < 0 || tok_n < 0 || pairs_per_block < 0) return BSX_E_GEOMETRY;
+    const size_t smem = plan_smem_bytes(E, (int) n_pairs);
+    if (n_pairs > BSX_EP_PLAN_MAX_PAIRS || smem > 48 * 1024) return BSX_E_LIMIT;
+    if (!ids || !blob_table || !ptr || !start || !n_groups || !ent_dst || !ent_tok) return BSX_E_POINTER;
+    launch_k(ep_plan_kernel, dim3(1), dim3(1024), smem, (cudaStream_t) stream, ids, (int) n_pairs, (int) k, (int) pairs_per_block, (int) block_stride, (int) E,
+             blob_table, shared_blob, (int) tok_lo, (int) tok_n, ptr, start, n_groups, ent_dst, ent_tok);
     return launch_status();
 }
 

@@ -74,10 +74,15 @@ __device__ inline void plan_note_pair(const PlanSmem& s, int i, int e, int E) {
     if (e >= 0) atomicAdd(&s.count[e], 1);
 }
 // every thread of the block.  items / n_items (optional): the pass list of the packed expert kernels, made here so that no
-// kernel of its own has to.
+// kernel of its own has to.  tok_base: the first token of the shared expert's group (its entries read tokens tok_base ..
+// tok_base + n_tok - 1).  STABLE = false: an expert's entries take their places from a shared-memory cursor instead of by counting
+// earlier pairs - for callers to whom the order of the entries inside a group does not matter (every entry writes its own row),
+// where the counting loop, quadratic in the pairs, would dominate (thousands of pairs).
+template <bool STABLE = true>
 __device__ inline void plan_finish(const PlanSmem& s, int n, int k, int E, unsigned long long shared_blob, int n_tok,
                                    unsigned long long* __restrict__ ptr, int32_t* __restrict__ start, int32_t* __restrict__ n_groups,
-                                   int32_t* __restrict__ dst, int32_t* __restrict__ tok, PassRec* __restrict__ items, int* __restrict__ n_items) {
+                                   int32_t* __restrict__ dst, int32_t* __restrict__ tok, PassRec* __restrict__ items, int* __restrict__ n_items,
+                                   int tok_base = 0) {
     __shared__ int sh[32];
     int at = 0, g = 0, np_total = 0;   // running totals over the expert chunks of blockDim.x
     for (int e0 = 0; e0 < E; e0 += blockDim.x) {
@@ -115,7 +120,7 @@ __device__ inline void plan_finish(const PlanSmem& s, int n, int k, int E, unsig
         }
         for (int t = threadIdx.x; t < n_tok; t += blockDim.x) {
             dst[at + t] = n + t;
-            tok[at + t] = t;
+            tok[at + t] = tok_base + t;
         }
         if (items) {
             const int np = (n_tok + kPassEntries - 1) / kPassEntries;
@@ -141,11 +146,16 @@ __device__ inline void plan_finish(const PlanSmem& s, int n, int k, int E, unsig
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int e = s.sid[i];
         if (e < 0) continue;
-        int before = 0;
-        int j = 0;
-        for (; j + 4 <= i; j += 4) before += (s.sid[j] == e) + (s.sid[j + 1] == e) + (s.sid[j + 2] == e) + (s.sid[j + 3] == e);
-        for (; j < i; ++j) before += s.sid[j] == e;
-        const int p = s.first[e] + before;
+        int p;
+        if (STABLE) {
+            int before = 0;
+            int j = 0;
+            for (; j + 4 <= i; j += 4) before += (s.sid[j] == e) + (s.sid[j + 1] == e) + (s.sid[j + 2] == e) + (s.sid[j + 3] == e);
+            for (; j < i; ++j) before += s.sid[j] == e;
+            p = s.first[e] + before;
+        } else {
+            p = atomicAdd(&s.first[e], 1);
+        }
         dst[p] = i;
         tok[p] = i / k;
     }

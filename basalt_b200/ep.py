@@ -162,12 +162,21 @@ class EPMoELayerA2A:
 
 
 class EPMoELayer:
-    """The expert-parallel layer on one rank, collective form: all-gather (activations, routing) -> local experts ->
-    partial combine -> reduce-scatter.  Every size is fixed by (world, max_tokens), nothing is read back to the host, and
-    every rank must pass the same number of tokens per step.  packed: blobs and the shared blob are in the plane layout
-    of moe.pack_experts and run on the block-scaled FP4 tensor cores.  The shared expert (replicated) runs on the rank's
-    own tokens as one more group of the same grouped call.  capture() records the step, collectives included, into a
-    CUDA graph."""
+    """The expert-parallel layer on one rank for decode-sized steps, collective form.  Every size is fixed by (world,
+    max_tokens), nothing is read back to the host, every rank passes the same number of tokens per step, and capture()
+    records the step - collectives included - into a CUDA graph.
+
+    Step: the rank's activations are all-gathered on a side stream WHILE the router runs on them (the exchange needs no
+    routing); the routing ([ids | weights], one small buffer) is all-gathered after the selection; one kernel (bsx_ep_plan) turns
+    all gathered pairs into the groups of the experts held here plus the shared expert's group over the rank's own tokens; the
+    grouped experts run; one kernel (bsx_combine_partial_ep) sums each token's local pairs and, on the token's owner, adds the
+    shared row; a reduce-scatter adds the ranks' partial rows and leaves every rank its own tokens' finished rows.  The
+    cross-rank sum is NCCL's, so results match the single-GPU layer to fp32 rounding, not bit for bit.
+    packed: blobs and the shared blob are in the plane layout of moe.pack_experts (block-scaled FP4 tensor cores)."""
+
+    DATA_PLANE = ("NCCL all-gather of the bf16 rows (beside the router) and of the routing, local grouped experts, "
+                  "reduce-scatter of fp32 partial rows")
+    LAUNCHES = 8      # logits, selection, plan, x images + pass list, gate/up, h images, down, partial combine (+ 3 NCCL kernels)
 
     def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, shared_blob=None, max_tokens: int = 64, group=None,
                  packed: bool = False):
@@ -191,20 +200,14 @@ class EPMoELayer:
         W, T, k, H = self.world, max_tokens, args.k, layout.n_embd
         self.max_tokens = T
         n = W * T * k
+        assert n <= 8192, "bsx_ep_plan takes at most 8192 gathered pairs"
         rows = n + (T if shared_blob is not None else 0)
         f32, i32 = torch.float32, torch.int32
         self.logits = torch.empty((T, n_expert_total), dtype=f32, device=dev)
-        self.ids = torch.empty((T, k), dtype=i32, device=dev)
-        self.w = torch.empty((T, k), dtype=f32, device=dev)
-        self.route = torch.empty((T, 2 * k), dtype=i32, device=dev)          # [ids | weight bits] of the rank's own tokens
-        self.route_all = torch.empty((W * T, 2 * k), dtype=i32, device=dev)
-        self.ids_all = torch.empty((W * T, k), dtype=i32, device=dev)
-        self.w_all = torch.empty((W * T, k), dtype=f32, device=dev)
-        self.cnt = torch.empty(n_expert_total, dtype=i32, device=dev)
-        self.off = torch.empty(n_expert_total + 1, dtype=i32, device=dev)
-        self.slot = torch.empty(n, dtype=i32, device=dev)
-        self.src = torch.empty(n, dtype=i32, device=dev)
-        self.dscratch = torch.empty(capi.lib().bsx_dispatch_scratch_bytes(n, n_expert_total), dtype=torch.uint8, device=dev)
+        self.route = torch.empty(2 * T * k, dtype=i32, device=dev)           # [ids T x k | weight bits T x k] of the rank's own tokens
+        self.ids = self.route[:T * k].view(T, k)
+        self.w = self.route[T * k:].view(f32).view(T, k)
+        self.route_all = torch.empty(W * 2 * T * k, dtype=i32, device=dev)   # the ranks' buffers, one after the other
         self.ptr = torch.zeros(n_expert_total + 3, dtype=torch.int64, device=dev)
         self.start = torch.zeros(n_expert_total + 3, dtype=i32, device=dev)
         self.n_groups = torch.zeros(1, dtype=i32, device=dev)
@@ -218,15 +221,20 @@ class EPMoELayer:
         self.status = torch.zeros(1, dtype=i32, device=dev)
         self.y_part = torch.empty((W * T, H), dtype=f32, device=dev)
         self.y = torch.empty((T, H), dtype=f32, device=dev)
-        self.y_sum = torch.empty((T, H), dtype=f32, device=dev)
-        self.ones = torch.ones((T, 1), dtype=f32, device=dev)
         self.x_all = None
-        self.time_experts, self.last_expert_ms, self.last_groups = False, 0.0, 0
+        self.side = torch.cuda.Stream(device=dev)
+        self.events = None       # set to a list to collect (name, event) marks between the stages
         self.graph = None
 
     def check_status(self):
         """Raises moe.KernelWaitTimeout if a kernel of a step since the last check gave up on a bounded wait; clears the word."""
         self.moe.read_status(self.status, "EPMoELayer")
+
+    def _mark(self, name):
+        if self.events is not None:
+            ev = self.torch.cuda.Event(enable_timing=True)
+            ev.record(self.torch.cuda.current_stream())
+            self.events.append((name, ev))
 
     def capture(self, x_example):
         """Records forward() into a CUDA graph (NCCL collectives included).  Every rank must capture, and replay, in step."""
@@ -260,29 +268,28 @@ class EPMoELayer:
         cur = torch.cuda.current_stream()
         st = moe._stream(cur)
         p = moe._p
-        # 1. route the rank's own tokens; ids and weights travel as one int32 row per token
-        moe.router_x(x, self.gate_w, self.bias, a, self.logits, self.ids, self.w)
-        self.route[:, :k].copy_(self.ids)
-        self.route[:, k:].view(torch.float32).copy_(self.w)
-        # 2. everyone gets every token's activations and routing
+        self._mark("start")
+        # 1. everyone gets every token's activations - on the side stream, beside the router
         if self.x_all is None or self.x_all.dtype != x.dtype:
             self.x_all = torch.empty((W * T, H), dtype=x.dtype, device=self.dev)
-        dist.all_gather_into_tensor(self.x_all, x, group=self.group)
+        self.side.wait_stream(cur)
+        with torch.cuda.stream(self.side):
+            dist.all_gather_into_tensor(self.x_all, x, group=self.group)
+        # 2. route the rank's own tokens; ids and weights land in one buffer, which is then gathered
+        moe.router_x(x, self.gate_w, self.bias, a, self.logits, self.ids, self.w)
+        self._mark("router")
         dist.all_gather_into_tensor(self.route_all, self.route, group=self.group)
-        self.ids_all.copy_(self.route_all[:, :k])
-        self.w_all.copy_(self.route_all[:, k:].view(torch.float32))
-        # 3. dispatch all pairs; groups only for the experts held here (+ the shared expert over the rank's own tokens)
+        self._mark("all_gather_route")
+        # 3. all gathered pairs -> the groups of the experts held here (+ the shared expert over the rank's own tokens)
         n = W * T * k
-        capi.check("bsx_dispatch", lib.bsx_dispatch(p(self.ids_all), n, k, self.E, p(self.cnt), p(self.off), p(self.slot), p(self.src), 0, None, None,
-                                                     p(self.dscratch), st))
         shared = self.shared_blob is not None
-        capi.check("bsx_plan_groups_shared", lib.bsx_plan_groups_shared(p(self.cnt), p(self.off), p(self.src), self.E, p(self.blob_table),
-                                                                         self.shared_blob.data_ptr() if shared else 0, self.rank * T, T if shared else 0,
-                                                                         p(self.ptr), p(self.start), p(self.n_groups), p(self.ent_dst), p(self.ent_tok), st))
-        # 4. the local experts over the rows routed to them (outputs land on their dispatch rows; shared rows after them)
-        if self.time_experts:
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0.record(cur)
+        capi.check("bsx_ep_plan", lib.bsx_ep_plan(p(self.route_all), n, k, T * k, 2 * T * k, self.E, p(self.blob_table),
+                                                   self.shared_blob.data_ptr() if shared else 0, self.rank * T, T if shared else 0, p(self.ptr), p(self.start),
+                                                   p(self.n_groups), p(self.ent_dst), p(self.ent_tok), st))
+        self._mark("plan")
+        cur.wait_stream(self.side)           # the gathered activations are needed from here on
+        self._mark("all_gather_x_wait")
+        # 4. the local experts over the rows routed to them (a pair's output lands on row = its index; shared rows after them)
         cap_groups, cap_rows = self.hi - self.lo + (1 if shared else 0), n + (T if shared else 0)
         if self.packed:
             moe.native_expert_grouped_packed(L, self.ptr, self.start, self.n_groups, self.ent_dst, self.ent_tok, cap_groups, cap_rows, self.x_all,
@@ -290,19 +297,14 @@ class EPMoELayer:
         else:
             moe.native_expert_grouped(L, self.ptr, self.start, self.n_groups, self.ent_dst, self.ent_tok, cap_groups, cap_rows, self.x_all, self.scratch,
                                       self.rows, n_x_rows=W * T)
-        if self.time_experts:
-            t1.record(cur)
-            t1.synchronize()
-            self.last_expert_ms, self.last_groups = t0.elapsed_time(t1), int(self.n_groups.item())
-        # 5. each token's local pairs summed here, the ranks' partial sums reduced onto the token's owner
-        capi.check("bsx_combine_partial", lib.bsx_combine_partial(p(self.rows), p(self.slot), p(self.w_all), p(self.ids_all), self.lo, self.hi, W * T, k, H,
-                                                                   p(self.y_part), st))
-        if not shared:
-            dist.reduce_scatter_tensor(self.y, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
-            return self.y
-        dist.reduce_scatter_tensor(self.y_sum, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
-        # y = 1 * sum + shared, through the combine kernel (one "row" per token)
-        capi.check("bsx_combine", lib.bsx_combine(p(self.y_sum), None, p(self.ones), p(self.rows[n:n + T]), None, T, 1, H, p(self.y), st))
+        self._mark("experts")
+        # 5. each token's local pairs summed here (its owner adds the shared row), the ranks' partial rows reduced onto the owner
+        capi.check("bsx_combine_partial_ep", lib.bsx_combine_partial_ep(p(self.rows), self.route_all.data_ptr() + 4 * T * k, p(self.route_all), T, 2 * T * k,
+                                                                         self.lo, self.hi, W * T, k, H, p(self.rows[n:]) if shared else None,
+                                                                         self.rank * T, T if shared else 0, p(self.y_part), st))
+        self._mark("combine_partial")
+        dist.reduce_scatter_tensor(self.y, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
+        self._mark("reduce_scatter")
         return self.y
 
 

@@ -176,3 +176,66 @@ def test_one_call_layer_wide_window_with_a_shared_expert_of_its_own_format(lib, 
     nat.check_status()
     assert torch.equal(nat.ids[:T], ref.ids[:T])
     assert rel_l2(y1.cpu().numpy(), y0.cpu().numpy()) < 1e-3
+
+
+@pytest.mark.parametrize("packed", [False, True])
+def test_expert_parallel_step_emulated_on_one_gpu(lib, cuda, packed):
+    """The expert-parallel decode step's device side (bsx_ep_plan -> grouped experts -> bsx_combine_partial_ep) with the ranks
+    emulated one after the other on one GPU: W = 4 ranks' gathered rows and routing in the layout the all-gathers leave, each
+    rank holding a quarter of the experts; the sum of the ranks' partial rows (what the reduce-scatter forms) must equal the
+    single-GPU layer's rows to fp32 rounding."""
+    rng = np.random.default_rng(31)
+    E, H, I, k, T, W = 64, 2048, 512, 10, 8, 4
+    Lo, blobs = make_expert_blobs(rng, E + 1, 40, 40, H, I)
+    L = moe.native_expert_layout(40, 40, H, I)
+    bd = dev(stack_blobs(blobs))
+    if packed:
+        bd = moe.pack_experts(L, bd)
+    gate_w = dev((rng.standard_normal((E, H)) * 0.02).astype(np.float32))
+    args = moe.RouterArgs(n_expert=E, n_embd=H, k=k, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
+    x_all = torch.from_numpy(rng.standard_normal((W * T, H)).astype(np.float32)).cuda().bfloat16()
+    single = moe.MoELayer(gate_w, None, bd[:E], L, args, shared_blob=bd[E], max_tokens=W * T, packed=packed)
+    want = single.forward(x_all).clone()
+    ids_all, w_all = single.ids[:W * T].clone(), single.w[:W * T].clone()
+    # the all-gather's layout: per rank [ids T x k | weight bits T x k]
+    route_all = torch.empty(W * 2 * T * k, dtype=torch.int32, device="cuda")
+    for r in range(W):
+        route_all[r * 2 * T * k:r * 2 * T * k + T * k] = ids_all[r * T:(r + 1) * T].reshape(-1)
+        route_all[r * 2 * T * k + T * k:(r + 1) * 2 * T * k] = w_all[r * T:(r + 1) * T].reshape(-1).view(torch.int32)
+    n = W * T * k
+    st = torch.cuda.current_stream().cuda_stream or 1
+    stride = bd.shape[1]
+    total = torch.zeros((W * T, H), dtype=torch.float32, device="cuda")
+    for r in range(W):
+        lo, hi = r * E // W, (r + 1) * E // W
+        table = np.zeros(E, np.int64)
+        table[lo:hi] = bd.data_ptr() + np.arange(lo, hi, dtype=np.int64) * stride
+        tab = dev(table)
+        ptr = torch.zeros(E + 3, dtype=torch.int64, device="cuda"); start = torch.zeros(E + 3, dtype=torch.int32, device="cuda")
+        ng = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ed = torch.zeros(n + T, dtype=torch.int32, device="cuda"); et = torch.zeros(n + T, dtype=torch.int32, device="cuda")
+        moe.check("bsx_ep_plan", lib.bsx_ep_plan(route_all.data_ptr(), n, k, T * k, 2 * T * k, E, tab.data_ptr(), bd[E].data_ptr(), r * T, T, ptr.data_ptr(),
+                                                  start.data_ptr(), ng.data_ptr(), ed.data_ptr(), et.data_ptr(), st))
+        rows = torch.full((n + T, H), float("nan"), dtype=torch.float32, device="cuda")
+        if packed:
+            scratch = torch.empty(lib.bsx_experts_packed_scratch_bytes(C.byref(L), n + T), dtype=torch.uint8, device="cuda")
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            moe.native_expert_grouped_packed(L, ptr, start, ng, ed, et, hi - lo + 1, n + T, x_all, scratch, rows, status, n_x_rows=W * T)
+            assert int(status.item()) == 0
+        else:
+            scratch = torch.empty(moe.native_expert_scratch_bytes(L, n + T), dtype=torch.uint8, device="cuda")
+            moe.native_expert_grouped(L, ptr, start, ng, ed, et, hi - lo + 1, n + T, x_all, scratch, rows, n_x_rows=W * T)
+        y_part = torch.empty((W * T, H), dtype=torch.float32, device="cuda")
+        moe.check("bsx_combine_partial_ep", lib.bsx_combine_partial_ep(rows.data_ptr(), route_all.data_ptr() + 4 * T * k, route_all.data_ptr(), T, 2 * T * k, lo, hi,
+                                                                        W * T, k, H, rows[n:].data_ptr(), r * T, T, y_part.data_ptr(), st))
+        torch.cuda.synchronize()
+        g = int(ng.item())
+        # the groups are this rank's experts with pairs, ascending, plus the shared group; every local pair has exactly one entry
+        local = ((ids_all >= lo) & (ids_all < hi)).reshape(-1)
+        rows_used = int(start[g].item())
+        assert rows_used == int(local.sum().item()) + T
+        assert sorted(ed[:rows_used - T].tolist()) == torch.nonzero(local).reshape(-1).tolist()
+        assert torch.equal(et[:rows_used - T], ed[:rows_used - T] // k)
+        assert torch.isfinite(y_part).all()
+        total += y_part
+    assert rel_l2(total.cpu().numpy(), want.cpu().numpy()) < 2e-6
