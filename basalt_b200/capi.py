@@ -56,8 +56,8 @@ _SIGNATURES = {
     "bsx_experts_prefill_group": (C.c_int32, [C.POINTER(ExpertLayout), P, C.c_int32, P, P, C.c_int64, P, C.c_int32, C.c_int64, P, P, P, P]),
     "bsx_unit_offsets": (C.c_int32, [P, C.c_int32, C.c_int32, P, P]),
     "bsx_rebase_bounds": (C.c_int32, [P, C.c_int32, P, P]),
-    "bsx_ep_plan": (C.c_int32, [P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, C.c_uint64, C.c_int32, C.c_int32, P, P, P, P, P, P]),
-    "bsx_combine_partial_ep": (C.c_int32, [P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, C.c_int32, C.c_int32, P, P]),
+    "bsx_ep_plan": (C.c_int32, [P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, C.c_uint64, C.c_int32, C.c_int32, P, P, P, P, P, P, P]),
+    "bsx_combine_partial_ep": (C.c_int32, [P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, C.c_int32, C.c_int32, P, P, P]),
     "bsx_combine_residual": (C.c_int32, [P, P, P, P, P, P, C.c_int32, C.c_int32, C.c_int32, P, P]),
     "bsx_route_plan": (C.c_int32, [P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_int32, C.c_int32, P, C.c_uint64, P, P, P, P, P, P, P, P]),
     "bsx_moe_layer_workspace_bytes": (C.c_size_t, [C.POINTER(MoELayerDesc), C.c_int32]),

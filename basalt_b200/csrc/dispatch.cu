@@ -175,10 +175,13 @@ moe_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int E, const unsi
 // index among all gathered tokens - plus one group for the shared expert over this rank's own tokens.  Replaces a full
 // dispatch of all pairs (three launches) and the group extraction after it.  ids may come in blocks of `blk` pairs, one per
 // source rank, `blk_stride` values apart (the layout an all-gather of [ids | weights] buffers leaves); blk = 0: dense.
+// replicated (optional, [E] bytes): experts every rank holds a copy of (hot experts); a pair naming one is computed by the
+// rank that owns the pair's TOKEN (pairs own_lo .. own_lo + own_n - 1), so each pair still has exactly one rank.
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int blk, int blk_stride, int E, const unsigned long long* __restrict__ blobs,
                unsigned long long shared_blob, int tok_lo, int tok_n, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
-               int32_t* __restrict__ n_groups, int32_t* __restrict__ dst, int32_t* __restrict__ tok) {
+               int32_t* __restrict__ n_groups, int32_t* __restrict__ dst, int32_t* __restrict__ tok, const uint8_t* __restrict__ replicated,
+               int own_lo, int own_n) {
     extern __shared__ unsigned long long smb[];
     const PlanSmem ps = plan_smem(smb, E);
     plan_load_blobs(ps, blobs, E);
@@ -187,7 +190,9 @@ ep_plan_kernel(const int32_t* __restrict__ ids, int n, int k, int blk, int blk_s
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int at = blk > 0 ? (i / blk) * blk_stride + (i % blk) : i;
-        plan_note_pair(ps, i, ids[at], E);
+        int e = ids[at];
+        if (replicated && (unsigned) e < (unsigned) E && replicated[e] && (i < own_lo || i >= own_lo + own_n)) e = -1;   // its token's owner runs it
+        plan_note_pair(ps, i, e, E);
     }
     __syncthreads();
     plan_finish<false>(ps, n, k, E, shared_blob, tok_n, ptr, start, n_groups, dst, tok, nullptr, nullptr, tok_lo);
@@ -374,14 +379,15 @@ extern "C" int32_t bsx_tiles_from_bounds(const int32_t* off, int32_t E, int32_t 
 
 extern "C" int32_t bsx_ep_plan(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t pairs_per_block, int32_t block_stride, int32_t E,
                                const unsigned long long* blob_table, unsigned long long shared_blob, int32_t tok_lo, int32_t tok_n,
-                               unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* ent_dst, int32_t* ent_tok, void* stream) {
+                               const uint8_t* replicated, unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* ent_dst,
+                               int32_t* ent_tok, void* stream) {
     if (!stream) return BSX_E_STREAM;
     if (E < 1 || E > BSX_PLAN_MAX_EXPERTS || k < 1 || n_pairs < 0 || tok_lo < 0 || tok_n < 0 || pairs_per_block < 0) return BSX_E_GEOMETRY;
     const size_t smem = plan_smem_bytes(E, (int) n_pairs);
     if (n_pairs > BSX_EP_PLAN_MAX_PAIRS || smem > 48 * 1024) return BSX_E_LIMIT;
     if (!ids || !blob_table || !ptr || !start || !n_groups || !ent_dst || !ent_tok) return BSX_E_POINTER;
     launch_k(ep_plan_kernel, dim3(1), dim3(1024), smem, (cudaStream_t) stream, ids, (int) n_pairs, (int) k, (int) pairs_per_block, (int) block_stride, (int) E,
-             blob_table, shared_blob, (int) tok_lo, (int) tok_n, ptr, start, n_groups, ent_dst, ent_tok);
+             blob_table, shared_blob, (int) tok_lo, (int) tok_n, ptr, start, n_groups, ent_dst, ent_tok, replicated, (int) (tok_lo * k), (int) (tok_n * k));
     return launch_status();
 }
 

@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const float* __restr
 __global__ void __launch_bounds__(128)
 combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ slot, const float* __restrict__ w,
                const float* __restrict__ shared, const float* __restrict__ sg, const float* __restrict__ resid, int k, int H, int pair0,
-               const int32_t* __restrict__ ids, int e_lo, int e_hi, float* __restrict__ y, int blk_tok, int blk_stride, int sh_lo, int sh_n) {
+               const int32_t* __restrict__ ids, int e_lo, int e_hi, float* __restrict__ y, int blk_tok, int blk_stride, int sh_lo, int sh_n,
+               const uint8_t* __restrict__ replicated) {
     __shared__ int s_row[64];
     __shared__ float s_w[64];
     pdl_wait();
@@ -80,7 +81,9 @@ combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ slot,
         const size_t at = blk_tok > 0 ? (size_t) (t / blk_tok) * blk_stride + (size_t) (t % blk_tok) * k + threadIdx.x : (size_t) t * k + threadIdx.x;
         if (ids) {   // expert-parallel partial sum: only the pairs whose expert lies in [e_lo, e_hi)
             const int e = ids[at];
-            if (e < e_lo || e >= e_hi) r = -1;
+            // a replicated (hot) expert's pair belongs to the rank that owns the token (tokens sh_lo .. sh_lo + sh_n - 1 here)
+            const bool rep = replicated != nullptr && e >= 0 && replicated[e] != 0;
+            if (rep ? !(t >= sh_lo && t < sh_lo + sh_n) : (e < e_lo || e >= e_hi)) r = -1;
         }
         s_row[threadIdx.x] = r;
         s_w[threadIdx.x] = w[at];
@@ -348,7 +351,7 @@ extern "C" int32_t bsx_gated_mlp(const bsx_expert_layout* layout, const void* bl
 
 static int32_t combine_impl(const float* rows, const int32_t* slot, const float* weights, const float* shared, const float* shared_gate,
                             const float* resid, int32_t T, int32_t k, int32_t H, const int32_t* ids, int32_t e_lo, int32_t e_hi, float* y, void* stream,
-                            int32_t blk_tok = 0, int32_t blk_stride = 0, int32_t sh_lo = 0, int32_t sh_n = 0) {
+                            int32_t blk_tok = 0, int32_t blk_stride = 0, int32_t sh_lo = 0, int32_t sh_n = 0, const uint8_t* replicated = nullptr) {
     if (!stream) return BSX_E_STREAM;
     if (T < 0 || k < 1 || k > 64 || H < 4 || H % 4) return BSX_E_GEOMETRY;
     if (T == 0) return BSX_OK;
@@ -359,7 +362,7 @@ static int32_t combine_impl(const float* rows, const int32_t* slot, const float*
         launch_k(combine_kernel, grid, dim3(128), 0, (cudaStream_t) stream, rows, slot ? slot + (size_t) t0 * k : nullptr, weights + (size_t) t0 * k,
                  shared ? shared + (size_t) t0 * H : nullptr, shared_gate ? shared_gate + t0 : nullptr, resid ? resid + (size_t) t0 * H : nullptr,
                  (int) k, (int) H, (int) (t0 * k), ids ? ids + (size_t) t0 * k : nullptr, (int) e_lo, (int) e_hi, y + (size_t) t0 * H, (int) blk_tok,
-                 (int) blk_stride, (int) sh_lo, (int) sh_n);
+                 (int) blk_stride, (int) sh_lo, (int) sh_n, replicated);
         if (blk_tok > 0 || sh_n > 0) break;   // the blocked / own-token forms take one launch (T <= 65535)
     }
     return launch_status();
@@ -377,11 +380,11 @@ extern "C" int32_t bsx_combine_residual(const float* rows, const int32_t* slot, 
 
 extern "C" int32_t bsx_combine_partial_ep(const float* rows, const float* weights, const int32_t* ids, int32_t tokens_per_block, int32_t block_stride,
                                           int32_t e_lo, int32_t e_hi, int32_t T, int32_t k, int32_t H, const float* shared, int32_t tok_lo, int32_t tok_n,
-                                          float* y, void* stream) {
+                                          const uint8_t* replicated, float* y, void* stream) {
     if (!ids) return BSX_E_POINTER;
-    if (T > 65535 || tokens_per_block < 0 || tok_lo < 0 || tok_n < 0) return BSX_E_GEOMETRY;
-    return combine_impl(rows, nullptr, weights, tok_n > 0 ? shared : nullptr, nullptr, nullptr, T, k, H, ids, e_lo, e_hi, y, stream, tokens_per_block, block_stride,
-                        tok_lo, tok_n);
+    if (T > 65535 || tokens_per_block < 0 || tok_lo < 0 || tok_n < 0 || (replicated && tok_n <= 0)) return BSX_E_GEOMETRY;
+    return combine_impl(rows, nullptr, weights, tok_n > 0 ? shared : nullptr, nullptr, nullptr, T, k, H, ids, e_lo, e_hi, y, stream, tokens_per_block,
+                        block_stride, tok_lo, tok_n, replicated);
 }
 
 extern "C" int32_t bsx_combine_partial(const float* rows, const int32_t* slot, const float* weights, const int32_t* ids, int32_t e_lo,

@@ -205,11 +205,11 @@ extern "C" int32_t bsx_moe_layer(const bsx_moe_layer_desc* d, const void* x, int
         launch_k(own_shared_plan_kernel, dim3(1), dim3(128), 0, st, d->shared_blob, (int) T, c.s_ptr, c.s_start, c.s_one, c.s_iota);
         rc = launch_status();
         if (rc != BSX_OK) return rc;
-        // A shared expert sees every token.  From 16 tokens on its rows go through the prompt-sized kernel (one pass over the blob
-        // for the whole window; the decode kernels take 4 or 8 entries a pass and would stream it several times), when that
-        // kernel reads the blob's formats and the caller gave a status word.
+        // A shared expert sees every token.  From 16 tokens on, an NVFP4 one goes through the prompt-sized kernel (one pass over the
+        // blob for the whole window; the decode kernels take 4 or 8 entries a pass and would stream it several times).  K- and
+        // I-quant blobs stay on the decode kernels: the prompt kernel's decoders read those formats byte by byte and are slower.
         rc = BSX_E_TYPE;
-        if (T >= 16 && status != nullptr && bsx_experts_prefill_group_scratch_bytes(&d->shared_layout, T, T) != 0) {
+        if (T >= 16 && status != nullptr && d->shared_layout.gu_type == kTypeNVFP4 && bsx_experts_prefill_group_scratch_bytes(&d->shared_layout, T, T) != 0) {
             const void* blob1[1] = {reinterpret_cast<const void*>((uintptr_t) d->shared_blob)};
             rc = bsx_experts_prefill_group(&d->shared_layout, blob1, 1, c.s_start, c.s_iota, T, xe, xe_kind, T, c.s_scratch, c.s_out, status, stream);
         }

@@ -376,11 +376,13 @@ __device__ __forceinline__ void select_token(const float* __restrict__ lg, const
     }
     float my_sel = 0.f, sum = 0.f;
     for (int r = 0; r < k; ++r) {
-        float best = -INFINITY;
+        // every index into s[] / b[] is a compile-time constant (a runtime index would move the arrays to local memory): the scan
+        // carries the candidate's unbiased score along, and taken experts are remembered in the `dead` mask
+        float best = -INFINITY, best_s = 0.f;
         int ex = INT_MAX;
 #pragma unroll
         for (int i = 0; i < MAXR; ++i)
-            if (!((dead >> i) & 1u) && (ex == INT_MAX || b[i] > best)) { best = b[i]; ex = lane + i * 32; }
+            if (!((dead >> i) & 1u) && (ex == INT_MAX || b[i] > best)) { best = b[i]; best_s = s[i]; ex = lane + i * 32; }
 #pragma unroll
         for (int m = 16; m; m >>= 1) {
             const float ob = __shfl_xor_sync(kFull, best, m);
@@ -388,10 +390,9 @@ __device__ __forceinline__ void select_token(const float* __restrict__ lg, const
             if (oi != INT_MAX && (ex == INT_MAX || ob > best || (ob == best && oi < ex))) { best = ob; ex = oi; }
         }
         float sv = 0.f;
-        if (ex != INT_MAX && (ex & 31) == lane) {
-#pragma unroll
-            for (int i = 0; i < MAXR; ++i)
-                if (i == (ex >> 5)) { sv = s[i]; dead |= 1u << i; }
+        if (ex != INT_MAX && (ex & 31) == lane) {     // this lane's candidate won: ex is still its own (lane + 32 i)
+            sv = best_s;
+            dead |= 1u << (ex >> 5);
         }
         sv = __shfl_sync(kFull, sv, ex == INT_MAX ? 0 : (ex & 31));
         sum += sv;

@@ -42,16 +42,23 @@ __device__ __forceinline__ void BSX_SOFTMAX_TOKEN(const float* __restrict__ lg, 
     // unsigned integers, so the warp-wide maximum and the lowest index holding it are one redux instruction each; a lane
     // keeps the maximum of its own values and only the winning lane rescans.  (+0 and -0 would order differently from the
     // float compare, but a probability here is +0 at the lowest, and the markers -FLT_MAX and -inf are distinct values.)
+    // The values stay in registers: every index into v[] below is a compile-time constant.  (Reading "the winner's value" as
+    // v[ex >> 5] makes the compiler put the array in local memory, and the selection becomes a chain of L1 round trips -
+    // measured ~6 us a token.)  A chosen value is recovered from its key, and chosen positions are remembered in a bit mask.
     float selected = 0.0f, selected_sum = 0.0f;
     auto key = [](float f) { const uint32_t b = __float_as_uint(f); return (b & 0x80000000u) ? ~b : (b | 0x80000000u); };
-    uint32_t lmax = 0u;
+    auto unkey = [](uint32_t q) { return __uint_as_float((q & 0x80000000u) ? (q & 0x7FFFFFFFu) : ~q); };
+    uint32_t kv[MAXR];
+#pragma unroll
+    for (int i = 0; i < MAXR; ++i) kv[i] = i < reg ? key(v[i]) : 0u;
+    uint32_t lmax = 0u, taken = 0u;
     int lidx = 0;
     auto rescan = [&]() {
-        lmax = key(v[0]);
+        lmax = 0u;       // below every key (the key of -inf is 0x007FFFFF)
         lidx = 0;
 #pragma unroll
-        for (int i = 1; i < MAXR; ++i)
-            if (i < reg && key(v[i]) > lmax) { lmax = key(v[i]); lidx = i; }
+        for (int i = 0; i < MAXR; ++i)
+            if (i < reg && !((taken >> i) & 1u) && kv[i] > lmax) { lmax = kv[i]; lidx = i; }
     };
     rescan();
     for (int rank = 0; rank < k; ++rank) {
@@ -59,9 +66,8 @@ __device__ __forceinline__ void BSX_SOFTMAX_TOKEN(const float* __restrict__ lg, 
         const int ex = (int) __reduce_min_sync(kFull, lmax == gmax ? (unsigned) (lane + lidx * 32) : 0xFFFFFFFFu);
         float best = 0.f;
         if ((ex & 31) == lane) {
-#pragma unroll
-            for (int i = 0; i < MAXR; ++i)
-                if (i == (ex >> 5)) { best = v[i]; v[i] = -INFINITY; }
+            best = unkey(lmax);
+            taken |= 1u << lidx;
             selected_sum += best;
             rescan();
         }

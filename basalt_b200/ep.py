@@ -36,6 +36,30 @@ def ep_partition(n_expert: int, world: int) -> np.ndarray:
     return np.arange(world + 1, dtype=np.int64) * (n_expert // world)
 
 
+def choose_replicas(load: np.ndarray, world: int, n_replicas: int) -> np.ndarray:
+    """Which experts to hold on every rank: the n_replicas most loaded ones (load[e] = pairs per step, e.g. a running count of
+    the router's choices), ties to the lower id - the experts whose rows would otherwise all land on their one owner.  Returns
+    their ids, ascending.  Basalt decides residency from the same kind of counts (include/basalt/core/tier_policy.hpp)."""
+    load = np.asarray(load, np.float64)
+    n = int(min(max(n_replicas, 0), load.size))
+    order = np.lexsort((np.arange(load.size), -load))[:n]
+    return np.sort(order).astype(np.int64)
+
+
+def ep_rank_rows(ids_all: np.ndarray, tokens_per_rank: int, n_expert: int, world: int, replicated=()) -> np.ndarray:
+    """rows each rank computes for gathered routing ids_all [world * tokens_per_rank][k]: an expert's pairs go to its owner, a
+    replicated expert's pairs to the rank that owns the token.  The balance check of a replica choice."""
+    first = ep_partition(n_expert, world)
+    rep = np.zeros(n_expert, bool)
+    rep[list(replicated)] = True
+    ids = np.asarray(ids_all)
+    tok_rank = np.repeat(np.arange(world), tokens_per_rank)[:, None] * np.ones_like(ids)
+    owner = np.searchsorted(first, ids, side="right") - 1
+    where = np.where(rep[np.clip(ids, 0, n_expert - 1)], tok_rank, owner)
+    valid = (ids >= 0) & (ids < n_expert)
+    return np.bincount(where[valid].reshape(-1), minlength=world)
+
+
 def ep_splits(cnt_all: np.ndarray, rank: int) -> Tuple[np.ndarray, np.ndarray]:
     """cnt_all [N][E] = every rank's per-expert pair counts.  Returns (send_splits, recv_splits): rows this rank sends to /
     receives from each rank."""
@@ -179,7 +203,10 @@ class EPMoELayer:
     LAUNCHES = 8      # logits, selection, plan, x images + pass list, gate/up, h images, down, partial combine (+ 3 NCCL kernels)
 
     def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, shared_blob=None, max_tokens: int = 64, group=None,
-                 packed: bool = False):
+                 packed: bool = False, replicas=None):
+        """replicas: {expert id: blob tensor} of hot experts this rank (and every other rank: the same ids everywhere) holds a
+        copy of besides its own block (choose_replicas picks them from load counts).  A pair naming one runs on the rank that
+        owns its token."""
         import torch
         import torch.distributed as dist
         from . import capi, moe
@@ -196,6 +223,13 @@ class EPMoELayer:
         assert El == self.hi - self.lo
         table = np.zeros(n_expert_total, np.int64)                 # 0 = an expert another rank holds
         table[self.lo:self.hi] = blobs.data_ptr() + np.arange(El, dtype=np.int64) * stride
+        self.replicas, self.replicated = replicas or {}, None
+        if self.replicas:
+            mask = np.zeros(n_expert_total, np.uint8)
+            for e, blob in self.replicas.items():
+                table[e] = blob.data_ptr()
+                mask[e] = 1
+            self.replicated = torch.from_numpy(mask).to(dev)
         self.blob_table = torch.from_numpy(table).to(dev)
         W, T, k, H = self.world, max_tokens, args.k, layout.n_embd
         self.max_tokens = T
@@ -284,13 +318,13 @@ class EPMoELayer:
         n = W * T * k
         shared = self.shared_blob is not None
         capi.check("bsx_ep_plan", lib.bsx_ep_plan(p(self.route_all), n, k, T * k, 2 * T * k, self.E, p(self.blob_table),
-                                                   self.shared_blob.data_ptr() if shared else 0, self.rank * T, T if shared else 0, p(self.ptr), p(self.start),
-                                                   p(self.n_groups), p(self.ent_dst), p(self.ent_tok), st))
+                                                   self.shared_blob.data_ptr() if shared else 0, self.rank * T, T if (shared or self.replicas) else 0,
+                                                   p(self.replicated), p(self.ptr), p(self.start), p(self.n_groups), p(self.ent_dst), p(self.ent_tok), st))
         self._mark("plan")
         cur.wait_stream(self.side)           # the gathered activations are needed from here on
         self._mark("all_gather_x_wait")
         # 4. the local experts over the rows routed to them (a pair's output lands on row = its index; shared rows after them)
-        cap_groups, cap_rows = self.hi - self.lo + (1 if shared else 0), n + (T if shared else 0)
+        cap_groups, cap_rows = self.hi - self.lo + len(self.replicas) + (1 if shared else 0), n + (T if shared else 0)
         if self.packed:
             moe.native_expert_grouped_packed(L, self.ptr, self.start, self.n_groups, self.ent_dst, self.ent_tok, cap_groups, cap_rows, self.x_all,
                                              self.scratch, self.rows, self.status, n_x_rows=W * T)
@@ -301,7 +335,7 @@ class EPMoELayer:
         # 5. each token's local pairs summed here (its owner adds the shared row), the ranks' partial rows reduced onto the owner
         capi.check("bsx_combine_partial_ep", lib.bsx_combine_partial_ep(p(self.rows), self.route_all.data_ptr() + 4 * T * k, p(self.route_all), T, 2 * T * k,
                                                                          self.lo, self.hi, W * T, k, H, p(self.rows[n:]) if shared else None,
-                                                                         self.rank * T, T if shared else 0, p(self.y_part), st))
+                                                                         self.rank * T, T if (shared or self.replicas) else 0, p(self.replicated), p(self.y_part), st))
         self._mark("combine_partial")
         dist.reduce_scatter_tensor(self.y, self.y_part, op=dist.ReduceOp.SUM, group=self.group)
         self._mark("reduce_scatter")

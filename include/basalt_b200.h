@@ -374,14 +374,20 @@ BSX_API int32_t bsx_combine_partial(const float* rows, const int32_t* slot, cons
  * shared_blob, one group over tokens tok_lo .. tok_lo + tok_n - 1 whose rows follow the pairs' rows (row n_pairs + i).  The
  * order of the entries inside a group is not fixed (every entry writes its own row, so results do not depend on it).
  * n_pairs <= BSX_EP_PLAN_MAX_PAIRS.  bsx_combine_partial_ep: bsx_combine_partial over that layout (row = pair index) with the
- * shared rows of tokens tok_lo .. added on their owner, so that the reduce-scatter that follows yields finished rows. */
+ * shared rows of tokens tok_lo .. added on their owner, so that the reduce-scatter that follows yields finished rows.
+ * replicated (optional, [E] bytes on the device, the same table on every rank): hot experts of which EVERY rank holds a copy
+ * (blob_table[e] != 0 everywhere) - the B200 form of Basalt's expert residency tiers (include/basalt/core/expert_tier.hpp:1-10:
+ * experts never leave HBM here, the popular ones are simply held more than once).  A pair naming a replicated expert is run
+ * by the rank that owns its token (tokens tok_lo .. tok_lo + tok_n - 1), so popular experts stop loading one rank with
+ * everybody's rows; every pair still has exactly one rank in the plan and in the partial sums. */
 #define BSX_EP_PLAN_MAX_PAIRS 8192
 BSX_API int32_t bsx_ep_plan(const int32_t* ids, int64_t n_pairs, int32_t k, int32_t pairs_per_block, int32_t block_stride, int32_t E,
                             const unsigned long long* blob_table, unsigned long long shared_blob, int32_t tok_lo, int32_t tok_n,
-                            unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* ent_dst, int32_t* ent_tok, void* stream);
+                            const uint8_t* replicated, unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* ent_dst,
+                            int32_t* ent_tok, void* stream);
 BSX_API int32_t bsx_combine_partial_ep(const float* rows, const float* weights, const int32_t* ids, int32_t tokens_per_block, int32_t block_stride,
                                        int32_t e_lo, int32_t e_hi, int32_t T, int32_t k, int32_t H, const float* shared, int32_t tok_lo, int32_t tok_n,
-                                       float* y, void* stream);
+                                       const uint8_t* replicated, float* y, void* stream);
 
 /* ---- the step before the layer: the RMS norm of the layer's input rows (weights w, any offset folded), as fp32 rows xn (what
  * the router reads) and / or bf16 rows act; either may be null, not both.  Replaces wgemm::norm_pack

@@ -99,3 +99,22 @@ def test_ep_plan_properties():
             assert (np.diff(seg) > 0).all()                                    # source-rank order, then pair order
     for r in range(world):
         assert np.array_equal(ep.ep_splits(cnt_all, r)[1], tot_send[:, r])     # what r receives is what the others send it
+
+
+def test_replica_choice_balances_a_skewed_load():
+    """Hot-expert replication: with Zipf-like routing the owner of the popular experts gets most rows; holding the few most
+    loaded experts on every rank moves their pairs to the tokens' own ranks and evens the rows out."""
+    from basalt_b200 import ep
+    rng = np.random.default_rng(0)
+    E, W, T, k = 64, 4, 128, 4
+    p = 1.0 / np.arange(1, E + 1) ** 1.1
+    ids = np.stack([rng.choice(E, k, replace=False, p=p / p.sum()) for _ in range(W * T)]).astype(np.int32)
+    load = np.bincount(ids.reshape(-1), minlength=E)
+    plain = ep.ep_rank_rows(ids, T, E, W)
+    assert plain.sum() == ids.size and plain[0] > 1.8 * plain.mean()          # rank 0 owns the popular experts
+    reps = ep.choose_replicas(load, W, 6)
+    assert reps.tolist() == sorted(np.argsort(-load, kind="stable")[:6].tolist())
+    bal = ep.ep_rank_rows(ids, T, E, W, reps)
+    assert bal.sum() == ids.size
+    assert bal.max() / bal.mean() < 0.75 * plain.max() / plain.mean()
+    assert ep.choose_replicas(load, W, 0).size == 0

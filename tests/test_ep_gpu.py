@@ -60,6 +60,12 @@ def _rank_body(rank, world, port, q):
     yc = coll.forward(xf).clone()
     yc2 = coll.forward(xf).clone()
     wantc = single.forward(xf).clone()
+    # hot experts held on every rank (one from each rank's block): a replicated expert's pairs run where their token lives
+    reps = {e: bd[e] for e in (3, E // 2 + 5)}
+    rep = ep.EPMoELayer(gw, None, own, L, args, E, shared_blob=bd[E], max_tokens=T, replicas=reps)
+    yr = rep.forward(xf).clone()
+    relr = float((yr - wantc).norm() / wantc.norm())
+    assert relr < 1e-5, f"collective form with replicated experts differs from the single-GPU layer (relative L2 {relr})"
     # the collective form over packed blobs (block-scaled FP4 tensor cores), launched kernel by kernel and as a CUDA graph
     mine = moe.pack_experts(L, torch.cat([own, bd[E:E + 1]]))
     pk = ep.EPMoELayer(gw, None, mine[:El], L, args, E, shared_blob=mine[El], max_tokens=T, packed=True)

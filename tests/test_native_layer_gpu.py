@@ -165,8 +165,8 @@ def test_one_call_layer_with_input_norm_vs_oracle(lib, cuda):
 
 
 def test_one_call_layer_wide_window_with_a_shared_expert_of_its_own_format(lib, cuda):
-    """24 tokens, IQ1_M routed experts, a Q6_K shared expert: from 16 tokens on the shared expert's rows go through the
-    prompt-sized kernel (one pass over its blob); the result sits on the oracle and on the call-by-call layer within the bar."""
+    """24 tokens, IQ1_M routed experts, a Q6_K shared expert with a layout of its own, through the one-call step: the rows sit
+    on the call-by-call layer's (same kernels)."""
     rng = np.random.default_rng(8)
     E, H, I, k, T = 32, 1024, 512, 4, 24
     ref, nat = _layers(rng, E, H, I, k, capi.GATE_SIGMOID, 29, 29, True, False, T, True, 14)
