@@ -12,11 +12,14 @@
 namespace bsx {
 namespace {
 
-__device__ const uint16_t g_iq1_grid[2048] = {
+// every codebook in one table: the IQ1 points, then the IQ2 and IQ3 points (offsets kGrid* of formats.cuh)
+__device__ const uint16_t g_iq1_grid[kGridWords] = {
 #include "iq1_grid_u16.inc"
+#include "iq_grids_u16.inc"
 };
-const uint16_t h_iq1_grid[2048] = {
+const uint16_t h_iq1_grid[kGridWords] = {
 #include "iq1_grid_u16.inc"
+#include "iq_grids_u16.inc"
 };
 
 }  // namespace
@@ -180,25 +183,7 @@ extern "C" const char* bsx_version(void) { return "basalt_b200 0.1 (sm_100a)"; }
 extern "C" int32_t bsx_host_decode_row(int32_t type, const void* row, float* y, int64_t n) {
     if (!row_bytes(type, n) || !row || !y) return BSX_E_TYPE;
     const uint8_t* b = static_cast<const uint8_t*>(row);
-    if (type == kTypeNVFP4) {
-        for (int64_t i = 0; i < n / 64; ++i) decode_block_nvfp4(b + i * 36, y + i * 64);
-    } else if (type == kTypeQ6K) {
-        for (int64_t u = 0; u < n / 32; ++u) decode_q6k_32(b + (u >> 3) * 210, (int) (u & 7), y + u * 32);
-    } else if (type == kTypeQ8_0) {
-        for (int64_t u = 0; u < n / 32; ++u) decode_q8_0_32(b + u * 34, y + u * 32);
-    } else if (type == kTypeQ4K) {
-        for (int64_t u = 0; u < n / 32; ++u) decode_q4k_32(b + (u >> 3) * 144, (int) (u & 7), y + u * 32);
-    } else if (type == kTypeQ5K) {
-        for (int64_t u = 0; u < n / 32; ++u) decode_q5k_32(b + (u >> 3) * 176, (int) (u & 7), y + u * 32);
-    } else if (type == kTypeQ5_0 || type == kTypeQ5_1) {
-        for (int64_t u = 0; u < n / 32; ++u) decode_q5_01_32(b + u * (type == kTypeQ5_1 ? 24 : 22), type == kTypeQ5_1, y + u * 32);
-    } else if (type == kTypeIQ4NL) {
-        for (int64_t u = 0; u < n / 32; ++u) decode_iq4nl_32(b + u * 18, y + u * 32);
-    } else if (type == kTypeIQ4XS) {
-        for (int64_t u = 0; u < n / 32; ++u) decode_iq4xs_32(b + (u >> 3) * 136, (int) (u & 7), y + u * 32);
-    } else {
-        for (int64_t u = 0; u < n / 32; ++u) decode_iq1m_32(b + (u >> 3) * 56, (int) (u & 7), h_iq1_grid, y + u * 32);
-    }
+    for (int64_t u = 0; u < n / 32; ++u) decode_any_32(type, b, (int) u, h_iq1_grid, y + u * 32);
     return BSX_OK;
 }
 

@@ -50,9 +50,24 @@ __device__ __forceinline__ void decode32(int type, const uint8_t* row, int unit,
         decode_iq4nl_32(row + (size_t) unit * 18, y);
     } else if (type == kTypeIQ4XS) {
         decode_iq4xs_32(row + (size_t) (unit >> 3) * 136, unit & 7, y);
-    } else {
+    } else if (type == kTypeIQ1M) {
         decode_iq1m_32(row + (size_t) (unit >> 3) * 56, unit & 7, grid, y);
+    } else {
+        decode_any_32(type, row, unit, grid, y);
     }
+}
+
+// the codebook words the formats `t0` and `t1` read, from the device table to the block's copy (same offsets)
+__device__ __forceinline__ void stage_grid(uint16_t* s_grid, const uint16_t* grid, int t0, int t1) {
+    if (!type_needs_grid(t0) && !type_needs_grid(t1)) return;   // uniform over the block
+    int lo, n;
+    grid_range(t0, lo, n);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s_grid[lo + i] = grid[lo + i];
+    if (t1 != t0) {
+        grid_range(t1, lo, n);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) s_grid[lo + i] = grid[lo + i];
+    }
+    __syncthreads();
 }
 
 // 32 consecutive activations [32 unit, 32 unit + 32) of row `tok`
@@ -97,12 +112,8 @@ __device__ __forceinline__ float dot32(const float* w, const float* v, float acc
 // gate and up row r of every group against the group's entries -> h[entry][r]
 __global__ void __launch_bounds__(256)
 gu_simple_kernel(ExpertArgs a) {
-    __shared__ uint16_t s_grid[2048];
-    const bool need_grid = a.L.gu_type == kTypeIQ1M || a.L.up_type == kTypeIQ1M;
-    if (need_grid) {
-        for (int i = threadIdx.x; i < 2048; i += blockDim.x) s_grid[i] = a.grid[i];
-        __syncthreads();
-    }
+    __shared__ uint16_t s_grid[kGridWords];
+    stage_grid(s_grid, a.grid, a.L.gu_type, a.L.up_type);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * 8 + warp;
     if (r >= a.L.n_ff) return;
@@ -149,11 +160,8 @@ gu_simple_kernel(ExpertArgs a) {
 // down row r of every group against h[entry] -> out[dst[entry]][r]
 __global__ void __launch_bounds__(256)
 down_simple_kernel(ExpertArgs a) {
-    __shared__ uint16_t s_grid[2048];
-    if (a.L.d_type == kTypeIQ1M) {
-        for (int i = threadIdx.x; i < 2048; i += blockDim.x) s_grid[i] = a.grid[i];
-        __syncthreads();
-    }
+    __shared__ uint16_t s_grid[kGridWords];
+    stage_grid(s_grid, a.grid, a.L.d_type, a.L.d_type);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * 8 + warp;
     if (r >= a.L.n_embd) return;

@@ -50,8 +50,9 @@ enum {
 };
 
 /* ggml type ids of the block formats (include/basalt/ggml/ggml.h) */
-enum { BSX_TYPE_Q5_0 = 6, BSX_TYPE_Q5_1 = 7, BSX_TYPE_Q8_0 = 8, BSX_TYPE_Q4_K = 12, BSX_TYPE_Q5_K = 13, BSX_TYPE_Q6_K = 14, BSX_TYPE_IQ4_NL = 20,
-       BSX_TYPE_IQ4_XS = 23, BSX_TYPE_IQ1_M = 29, BSX_TYPE_NVFP4 = 40 };
+enum { BSX_TYPE_Q5_0 = 6, BSX_TYPE_Q5_1 = 7, BSX_TYPE_Q8_0 = 8, BSX_TYPE_Q2_K = 10, BSX_TYPE_Q3_K = 11, BSX_TYPE_Q4_K = 12, BSX_TYPE_Q5_K = 13,
+       BSX_TYPE_Q6_K = 14, BSX_TYPE_IQ2_XXS = 16, BSX_TYPE_IQ2_XS = 17, BSX_TYPE_IQ3_XXS = 18, BSX_TYPE_IQ1_S = 19, BSX_TYPE_IQ4_NL = 20,
+       BSX_TYPE_IQ3_S = 21, BSX_TYPE_IQ2_S = 22, BSX_TYPE_IQ4_XS = 23, BSX_TYPE_IQ1_M = 29, BSX_TYPE_NVFP4 = 40, BSX_TYPE_Q2_0 = 42 };
 
 /* activation / output element kinds */
 enum { BSX_X_F32 = 0, BSX_X_BF16 = 1, BSX_X_Q8_1 = 2 };

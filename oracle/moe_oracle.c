@@ -63,7 +63,8 @@ EXPORT float orc_h2f(uint16_t h) { return h2f(h); }
 EXPORT uint16_t orc_f2h(float f) { return f2h(f); }
 
 /* ------------------------------------------------------------------------------------------------ block formats */
-enum { T_Q5_0 = 6, T_Q5_1 = 7, T_IQ4_NL = 20, T_IQ4_XS = 23, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ1_M = 29, T_NVFP4 = 40 };
+enum { T_Q5_0 = 6, T_Q5_1 = 7, T_IQ4_NL = 20, T_IQ4_XS = 23, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ1_M = 29, T_NVFP4 = 40,
+       T_Q2_K = 10, T_Q3_K = 11, T_IQ2_XXS = 16, T_IQ2_XS = 17, T_IQ3_XXS = 18, T_IQ1_S = 19, T_IQ3_S = 21, T_IQ2_S = 22, T_Q2_0 = 42 };
 
 /* include/basalt/ggml/ggml_common.h:1029-1031 - E2M1 values, doubled */
 static const int8_t kFp4x2[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
@@ -82,6 +83,12 @@ EXPORT float orc_ue4m3_half(uint8_t b) { return ue4m3_half(b); }
 static const uint16_t kIq1Grid[2048] = {
 #include "../basalt_b200/csrc/iq1_grid_u16.inc"
 };
+/* the IQ2 and IQ3 codebooks, packed: iq2xxs 256, iq2xs 512, iq2s 1024 points (8 coordinates x 2 bits -> 8, 25, 43), iq3xxs 256 points
+ * (4 x 3 bits -> 4, 12, ..., 52, 62), iq3s 512 points (4 x 3 bits -> 1, 3, ..., 15); include/basalt/ggml/ggml_common.h:444-1020 */
+static const uint16_t kIqGrids[2560] = {
+#include "../basalt_b200/csrc/iq_grids_u16.inc"
+};
+enum { G_IQ2XXS = 0, G_IQ2XS = 256, G_IQ2S = 768, G_IQ3XXS = 1792, G_IQ3S = 2048 };
 
 EXPORT int64_t orc_row_bytes(int type, int64_t n) {
     switch (type) {
@@ -95,6 +102,15 @@ EXPORT int64_t orc_row_bytes(int type, int64_t n) {
         case T_Q8_0: return n % 32 ? 0 : n / 32 * 34;      /* block_q8_0: fp16 d, int8 qs[32] */
         case T_Q4_K: return n % 256 ? 0 : n / 256 * 144;   /* block_q4_K: d, dmin, scales[12], qs[128] */
         case T_Q5_K: return n % 256 ? 0 : n / 256 * 176;   /* block_q5_K: d, dmin, scales[12], qh[32], qs[128] */
+        case T_Q2_0: return n % 64 ? 0 : n / 64 * 18;      /* block_q2_0: d, qs[16] (ggml_common.h:140-145) */
+        case T_Q2_K: return n % 256 ? 0 : n / 256 * 84;    /* block_q2_K: scales[16], qs[64], d, dmin */
+        case T_Q3_K: return n % 256 ? 0 : n / 256 * 110;   /* block_q3_K: hmask[32], qs[64], scales[12], d */
+        case T_IQ2_XXS: return n % 256 ? 0 : n / 256 * 66; /* block_iq2_xxs: d, qs[32] uint16 */
+        case T_IQ2_XS: return n % 256 ? 0 : n / 256 * 74;  /* block_iq2_xs: d, qs[32] uint16, scales[8] */
+        case T_IQ2_S: return n % 256 ? 0 : n / 256 * 82;   /* block_iq2_s: d, qs[64], qh[8], scales[8] */
+        case T_IQ3_XXS: return n % 256 ? 0 : n / 256 * 98; /* block_iq3_xxs: d, qs[96] */
+        case T_IQ3_S: return n % 256 ? 0 : n / 256 * 110;  /* block_iq3_s: d, qs[64], qh[8], signs[32], scales[4] */
+        case T_IQ1_S: return n % 256 ? 0 : n / 256 * 50;   /* block_iq1_s: d, qs[32], qh[16] uint16 */
         default: return 0;
     }
 }
@@ -272,6 +288,189 @@ static void dequant_iq4(const uint8_t* b, float* y, int64_t n, int xs) {
     }
 }
 
+/* ---- the low-bit formats.  Each follows the reference's dequantize_row_* of src/kernels/cpu/ggml/ggml_quants.c, walking a
+ * block in the order the values are stored. */
+
+static float h16_at(const uint8_t* p) {
+    uint16_t h;
+    memcpy(&h, p, 2);
+    return h2f(h);
+}
+
+/* ggml_quants.c:209-227 - Q2_0: four 2-bit codes a byte, value = (code - 1) d */
+static void dequant_q2_0(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / 64; ++i, b += 18) {
+        const float d = h16_at(b);
+        for (int j = 0; j < 16; ++j)
+            for (int l = 0; l < 4; ++l) *y++ = (float) ((int) ((b[2 + j] >> (2 * l)) & 3) - 1) * d;
+    }
+}
+
+/* ggml_quants.c:593-625 - Q2_K: per 16 values a byte (scale | min << 4); value = d scale code - dmin min, product and
+ * difference rounded separately.  128 values share 32 code bytes, bit pair p of a byte belonging to values 32 p + l. */
+static void dequant_q2k(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / 256; ++i, b += 84) {
+        const float d = h16_at(b + 80), dmin = h16_at(b + 82);
+        const uint8_t* sc = b;
+        for (int half = 0; half < 2; ++half) {
+            const uint8_t* q = b + 16 + 32 * half;
+            for (int p = 0; p < 4; ++p)
+                for (int h = 0; h < 2; ++h, ++sc) {
+                    const float dl = d * (float) (*sc & 0xF), ml = dmin * (float) (*sc >> 4);
+                    for (int l = 0; l < 16; ++l) {
+                        volatile float t = dl * (float) ((q[16 * h + l] >> (2 * p)) & 3);
+                        *y++ = t - ml;
+                    }
+                }
+        }
+    }
+}
+
+/* ggml_quants.c:712-760 - Q3_K: sixteen 6-bit scales in 12 bytes (low nibbles of bytes 0..7, high nibbles of bytes 0..7, then
+ * the two top bits of scale j in byte 8 + j % 4 at bit 2 (j / 4)); value = d (scale - 32) (code - (hmask bit ? 0 : 4)). */
+static void dequant_q3k(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / 256; ++i, b += 110) {
+        const float d = h16_at(b + 108);
+        const uint8_t *hm = b, *s12 = b + 96;
+        int scales[16];
+        for (int j = 0; j < 16; ++j) {
+            const int lo = j < 8 ? (s12[j] & 0xF) : (s12[j - 8] >> 4);
+            const int hi = (s12[8 + j % 4] >> (2 * (j / 4))) & 3;
+            scales[j] = (lo | (hi << 4)) - 32;
+        }
+        int is = 0, bit = 0;
+        for (int half = 0; half < 2; ++half) {
+            const uint8_t* q = b + 32 + 32 * half;
+            for (int p = 0; p < 4; ++p, ++bit)
+                for (int h = 0; h < 2; ++h, ++is) {
+                    const float dl = d * (float) scales[is];
+                    for (int l = 0; l < 16; ++l) {
+                        const int code = (int) ((q[16 * h + l] >> (2 * p)) & 3) - ((hm[16 * h + l] >> bit) & 1 ? 0 : 4);
+                        *y++ = dl * (float) code;
+                    }
+                }
+        }
+    }
+}
+
+/* include/basalt/ggml/ggml_common.h (ksigns_iq2xs): seven stored sign bits, the eighth keeps the count of minus signs even */
+static unsigned signs_from7(unsigned i) { return i | ((unsigned) (__builtin_popcount(i) & 1) << 7); }
+
+static const float kIq2Mag[4] = {8.f, 25.f, 43.f, 43.f};
+static void iq2_emit(uint16_t point, unsigned signs, float db, float** y) {
+    for (int j = 0; j < 8; ++j) {
+        const float v = db * kIq2Mag[(point >> (2 * j)) & 3];
+        *(*y)++ = (signs >> j) & 1 ? -v : v;
+    }
+}
+static float iq3_mag(int s_table, unsigned c) { return s_table ? (float) (2 * c + 1) : (c == 7 ? 62.f : (float) (4 + 8 * c)); }
+static void iq3_emit(uint16_t point, unsigned signs4, float db, int s_table, float** y) {
+    for (int j = 0; j < 4; ++j) {
+        const float v = db * iq3_mag(s_table, (point >> (3 * j)) & 7);
+        *(*y)++ = (signs4 >> j) & 1 ? -v : v;
+    }
+}
+
+/* ggml_quants.c:1081-1107 - IQ2_XXS: per 32 values four point bytes and a word: 4 x 7 sign bits, scale in the top nibble;
+ * db = d (0.5 + scale) / 4 */
+static void dequant_iq2xxs(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / 256; ++i, b += 66) {
+        const float d = h16_at(b);
+        for (int ib = 0; ib < 8; ++ib) {
+            const uint8_t* q = b + 2 + 8 * ib;
+            uint32_t w;
+            memcpy(&w, q + 4, 4);
+            const float db = d * (0.5f + (float) (w >> 28)) * 0.25f;
+            for (int l = 0; l < 4; ++l) iq2_emit(kIqGrids[G_IQ2XXS + q[l]], signs_from7((w >> (7 * l)) & 127), db, &y);
+        }
+    }
+}
+
+/* ggml_quants.c:1109-1134 - IQ2_XS: a uint16 per 8 values (9-bit point, 7 sign bits), a 4-bit scale per 16 values */
+static void dequant_iq2xs(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / 256; ++i, b += 74) {
+        const float d = h16_at(b);
+        for (int ib = 0; ib < 8; ++ib) {
+            const uint8_t sc = b[66 + ib];
+            for (int l = 0; l < 4; ++l) {
+                uint16_t q;
+                memcpy(&q, b + 2 + 2 * (4 * ib + l), 2);
+                const float db = d * (0.5f + (float) (l < 2 ? (sc & 0xF) : (sc >> 4))) * 0.25f;
+                iq2_emit(kIqGrids[G_IQ2XS + (q & 511)], signs_from7(q >> 9), db, &y);
+            }
+        }
+    }
+}
+
+/* ggml_quants.c:1136-1166 - IQ2_S: point = low byte | two bits of qh, the sign byte stored whole (after the 32 point bytes) */
+static void dequant_iq2s(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / 256; ++i, b += 82) {
+        const float d = h16_at(b);
+        const uint8_t *qs = b + 2, *sg = b + 34, *qh = b + 66, *scl = b + 74;
+        for (int ib = 0; ib < 8; ++ib) {
+            for (int l = 0; l < 4; ++l) {
+                const float db = d * (0.5f + (float) (l < 2 ? (scl[ib] & 0xF) : (scl[ib] >> 4))) * 0.25f;
+                const unsigned idx = qs[4 * ib + l] | ((unsigned) ((qh[ib] >> (2 * l)) & 3) << 8);
+                iq2_emit(kIqGrids[G_IQ2S + idx], sg[4 * ib + l], db, &y);
+            }
+        }
+    }
+}
+
+/* ggml_quants.c:1168-1198 - IQ3_XXS: a point byte per 4 values; per 32 values a word of 4 x 7 sign bits and the scale;
+ * db = d (0.5 + scale) / 2 */
+static void dequant_iq3xxs(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / 256; ++i, b += 98) {
+        const float d = h16_at(b);
+        for (int ib = 0; ib < 8; ++ib) {
+            uint32_t w;
+            memcpy(&w, b + 66 + 4 * ib, 4);
+            const float db = d * (0.5f + (float) (w >> 28)) * 0.5f;
+            for (int l = 0; l < 4; ++l) {
+                const unsigned signs = signs_from7((w >> (7 * l)) & 127);
+                iq3_emit(kIqGrids[G_IQ3XXS + b[2 + 8 * ib + 2 * l]], signs & 15, db, 0, &y);
+                iq3_emit(kIqGrids[G_IQ3XXS + b[2 + 8 * ib + 2 * l + 1]], signs >> 4, db, 0, &y);
+            }
+        }
+    }
+}
+
+/* ggml_quants.c:1200-1239 - IQ3_S: point = byte | ninth bit from qh (bit k of qh[ib] for the k-th point of the 32 values),
+ * sign bytes stored whole, db = d (1 + 2 scale) with a 4-bit scale per 32 values */
+static void dequant_iq3s(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / 256; ++i, b += 110) {
+        const float d = h16_at(b);
+        const uint8_t *qs = b + 2, *qh = b + 66, *sg = b + 74, *scl = b + 106;
+        for (int ib = 0; ib < 8; ++ib) {
+            const int nib = (scl[ib / 2] >> (4 * (ib % 2))) & 0xF;
+            const float db = d * (float) (1 + 2 * nib);
+            for (int k = 0; k < 8; ++k) {
+                const unsigned idx = qs[8 * ib + k] | ((unsigned) ((qh[ib] >> k) & 1) << 8);
+                const unsigned s = sg[4 * ib + k / 2];
+                iq3_emit(kIqGrids[G_IQ3S + idx], (k & 1) ? (s >> 4) : (s & 15), db, 1, &y);
+            }
+        }
+    }
+}
+
+/* ggml_quants.c:1241-1264 - IQ1_S: per 32 values a uint16: 4 x 3 high point bits, a 3-bit scale, the sign of delta;
+ * value = d (2 scale + 1) (g + delta), g in {-1, 0, 1}, delta = +-1/8 */
+static void dequant_iq1s(const uint8_t* b, float* y, int64_t n) {
+    for (int64_t i = 0; i < n / 256; ++i, b += 50) {
+        const float d = h16_at(b);
+        for (int ib = 0; ib < 8; ++ib) {
+            uint16_t qh;
+            memcpy(&qh, b + 34 + 2 * ib, 2);
+            const float dl = d * (float) (2 * ((qh >> 12) & 7) + 1);
+            const float delta = (qh & 0x8000) ? -0.125f : 0.125f;
+            for (int l = 0; l < 4; ++l) {
+                const uint16_t g = kIq1Grid[b[2 + 4 * ib + l] | (((qh >> (3 * l)) & 7) << 8)];
+                for (int j = 0; j < 8; ++j) *y++ = dl * ((float) ((int) ((g >> (2 * j)) & 3) - 1) + delta);
+            }
+        }
+    }
+}
+
 EXPORT int orc_dequant_row(int type, const void* src, float* y, int64_t n) {
     if (orc_row_bytes(type, n) == 0) return -1;
     if (type == T_NVFP4) dequant_nvfp4(src, y, n);
@@ -283,6 +482,15 @@ EXPORT int orc_dequant_row(int type, const void* src, float* y, int64_t n) {
     else if (type == T_Q5_1) dequant_q5_01(src, y, n, 1);
     else if (type == T_IQ4_NL) dequant_iq4(src, y, n, 0);
     else if (type == T_IQ4_XS) dequant_iq4(src, y, n, 1);
+    else if (type == T_Q2_0) dequant_q2_0(src, y, n);
+    else if (type == T_Q2_K) dequant_q2k(src, y, n);
+    else if (type == T_Q3_K) dequant_q3k(src, y, n);
+    else if (type == T_IQ2_XXS) dequant_iq2xxs(src, y, n);
+    else if (type == T_IQ2_XS) dequant_iq2xs(src, y, n);
+    else if (type == T_IQ2_S) dequant_iq2s(src, y, n);
+    else if (type == T_IQ3_XXS) dequant_iq3xxs(src, y, n);
+    else if (type == T_IQ3_S) dequant_iq3s(src, y, n);
+    else if (type == T_IQ1_S) dequant_iq1s(src, y, n);
     else dequant_iq1m(src, y, n);
     return 0;
 }

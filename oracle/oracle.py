@@ -16,7 +16,9 @@ HERE = Path(__file__).resolve().parent
 T_Q6_K, T_IQ1_M, T_NVFP4 = 14, 29, 40
 T_Q8_0, T_Q4_K, T_Q5_K = 8, 12, 13
 T_Q5_0, T_Q5_1, T_IQ4_NL, T_IQ4_XS = 6, 7, 20, 23
-UNQUANTISED = (T_IQ1_M, T_Q8_0, T_Q4_K, T_Q5_K, T_Q5_0, T_Q5_1, T_IQ4_NL, T_IQ4_XS)   # formats the oracle has no quantiser for
+T_Q2_K, T_Q3_K, T_IQ2_XXS, T_IQ2_XS, T_IQ3_XXS, T_IQ1_S, T_IQ3_S, T_IQ2_S, T_Q2_0 = 10, 11, 16, 17, 18, 19, 21, 22, 42
+LOW_BIT = (T_Q2_K, T_Q3_K, T_IQ2_XXS, T_IQ2_XS, T_IQ3_XXS, T_IQ1_S, T_IQ3_S, T_IQ2_S, T_Q2_0)
+UNQUANTISED = (T_IQ1_M, T_Q8_0, T_Q4_K, T_Q5_K, T_Q5_0, T_Q5_1, T_IQ4_NL, T_IQ4_XS) + LOW_BIT   # formats the oracle has no quantiser for
 GATE_SQRT_SOFTPLUS, GATE_SIGMOID, GATE_SOFTMAX = 0, 1, 2
 
 _f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
@@ -189,6 +191,17 @@ def random_rows(t: int, rng: np.random.Generator, rows: int, cols: int) -> np.nd
     values are of order 0.02, like the quantised N(0, 0.02^2) weights of the other formats)."""
     if t == T_IQ1_M:
         return random_iq1m_rows(rng, rows, cols)
+    if t in LOW_BIT:
+        # (block bytes, values, {offset of an fp16 scale: its exponent bits}); the scales put values near 0.02 as above
+        bs, nv, scales = {T_Q2_0: (18, 64, {0: 0x2400}), T_Q2_K: (84, 256, {80: 0x1000, 82: 0x1800}), T_Q3_K: (110, 256, {108: 0x0C00}),
+                          T_IQ2_XXS: (66, 256, {0: 0x0800}), T_IQ2_XS: (74, 256, {0: 0x0800}), T_IQ2_S: (82, 256, {0: 0x0800}),
+                          T_IQ3_XXS: (98, 256, {0: 0x0400}), T_IQ3_S: (110, 256, {0: 0x0400}), T_IQ1_S: (50, 256, {0: 0x1800})}[t]
+        nb = rows * cols // nv
+        raw = rng.integers(0, 256, size=(nb, bs), dtype=np.uint8)
+        for at, base in scales.items():
+            h = (base + rng.integers(0, 0x400, size=nb)).astype(np.uint16)
+            raw[:, at:at + 2] = h.view(np.uint8).reshape(nb, 2)
+        return raw.reshape(-1)
     bs, nv, scale_at = {T_Q8_0: (34, 32, (0,)), T_Q4_K: (144, 256, (0, 2)), T_Q5_K: (176, 256, (0, 2)), T_Q5_0: (22, 32, (0,)),
                         T_Q5_1: (24, 32, (0, 2)), T_IQ4_NL: (18, 32, (0,)), T_IQ4_XS: (136, 256, (0,))}[t]
     nb = rows * cols // nv

@@ -2,7 +2,8 @@
 reference checkout by oracle/Makefile).  Run in a container that has the reference; the .npz travels with the repository
 so the CPU tests can pin the oracle where the reference is absent.
 
-Contents: raw blocks of each format (NVFP4, Q6_K, IQ1_M, Q8_0, Q4_K, Q5_K, Q5_0, Q5_1, IQ4_NL, IQ4_XS) with the reference's to_float output; seeded fp32 rows with the reference quantiser's
+Contents: raw blocks of each format (NVFP4, Q6_K, IQ1_M, Q8_0, Q4_K, Q5_K, Q5_0, Q5_1, IQ4_NL, IQ4_XS, Q2_0, Q2_K, Q3_K, IQ2_XXS, IQ2_XS,
+IQ2_S, IQ3_XXS, IQ3_S, IQ1_S) with the reference's to_float output; seeded fp32 rows with the reference quantiser's
 bytes (NVFP4, Q6_K); the reference's blob geometry for the benchmark shapes; and the reference CPU expert pool's output
 rows for a small Q6_K and a small NVFP4 layer (inputs are regenerated from the seeds stored alongside).
 """
@@ -70,6 +71,14 @@ def main():
     for name, t, nv, nblk in (("q8_0", 8, 32, 16), ("q4k", 12, 256, 3), ("q5k", 13, 256, 3), ("q5_0", 6, 32, 16), ("q5_1", 7, 32, 16),
                               ("iq4nl", 20, 32, 16), ("iq4xs", 23, 256, 3)):
         raw = O.random_rows(t, rng2, 1, nblk * nv)
+        y = np.empty(nblk * nv, np.float32)
+        assert R.ref_dequantize(t, raw.ctypes.data, y, y.size) == 0
+        out[f"dec_{name}_raw"], out[f"dec_{name}_f32"] = raw, y
+    # the low-bit formats (again their own generator)
+    rng3 = np.random.default_rng(2026)
+    for name, t, nv, nblk in (("q2_0", 42, 64, 8), ("q2k", 10, 256, 3), ("q3k", 11, 256, 3), ("iq2xxs", 16, 256, 3), ("iq2xs", 17, 256, 3),
+                              ("iq2s", 22, 256, 3), ("iq3xxs", 18, 256, 3), ("iq3s", 21, 256, 3), ("iq1s", 19, 256, 3)):
+        raw = O.random_rows(t, rng3, 1, nblk * nv)
         y = np.empty(nblk * nv, np.float32)
         assert R.ref_dequantize(t, raw.ctypes.data, y, y.size) == 0
         out[f"dec_{name}_raw"], out[f"dec_{name}_f32"] = raw, y

@@ -23,7 +23,7 @@ def test_every_declared_symbol_is_exported(lib):
     assert declared == set(capi.exported_symbols()), declared ^ set(capi.exported_symbols())
 
 
-@pytest.mark.parametrize("name,t", [("nvfp4", 40), ("q6k", 14), ("iq1m", 29), ("q8_0", 8), ("q4k", 12), ("q5k", 13), ("q5_0", 6), ("q5_1", 7), ("iq4nl", 20), ("iq4xs", 23)])
+@pytest.mark.parametrize("name,t", [("nvfp4", 40), ("q6k", 14), ("iq1m", 29), ("q8_0", 8), ("q4k", 12), ("q5k", 13), ("q5_0", 6), ("q5_1", 7), ("iq4nl", 20), ("iq4xs", 23), ("q2_0", 42), ("q2k", 10), ("q3k", 11), ("iq2xxs", 16), ("iq2xs", 17), ("iq2s", 22), ("iq3xxs", 18), ("iq3s", 21), ("iq1s", 19)])
 def test_host_decoders_match_reference_golden(lib, name, t):
     raw, want = np.ascontiguousarray(G[f"dec_{name}_raw"]), G[f"dec_{name}_f32"]
     got = np.empty(want.size, np.float32)

@@ -47,7 +47,11 @@ CASES = [("nvfp4", 40, 40, 2048, 512), ("q6k", 14, 14, 2048, 512), ("iq1m", 29, 
          ("q5k", 13, 13, 1024, 256), ("q4k_q6k", 12, 14, 2048, 512), ("q5_0", 6, 6, 1024, 256), ("q5_1", 7, 7, 1024, 256),
          ("iq4nl", 20, 20, 1024, 256), ("iq4xs", 23, 23, 1024, 512), ("iq4xs_q5_0", 23, 6, 1024, 256),
          # the integer tensor-core kernels at the large layer's shape, and a mixed pair they cover
-         ("iq1m_big", 29, 29, 7168, 2048), ("q6k_big", 14, 14, 7168, 2048), ("iq1m_q6k_1k", 29, 14, 2048, 1024)]
+         ("iq1m_big", 29, 29, 7168, 2048), ("q6k_big", 14, 14, 7168, 2048), ("iq1m_q6k_1k", 29, 14, 2048, 1024),
+         # the low-bit formats, alone and in the gate-up / down pairs a mixed-precision file uses
+         ("q2_0", 42, 42, 1024, 256), ("q2k", 10, 10, 1024, 256), ("q3k", 11, 11, 1024, 256), ("iq2xxs", 16, 16, 1024, 256),
+         ("iq2xs", 17, 17, 1024, 512), ("iq2s", 22, 22, 1024, 256), ("iq3xxs", 18, 18, 1024, 256), ("iq3s", 21, 21, 1024, 256),
+         ("iq1s", 19, 19, 1024, 256), ("iq2xxs_q3k", 16, 11, 1024, 256), ("iq1s_iq3s", 19, 21, 1024, 512), ("iq2s_q2k", 22, 10, 2048, 256)]
 
 
 @pytest.mark.parametrize("impl", ["fast", "simple"])

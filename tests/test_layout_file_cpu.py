@@ -148,12 +148,11 @@ def test_refusals():
         load(layout(6, b, types="40 14"))                                          # NVFP4's scale tail covers all three matrices
     with pytest.raises(ValueError, match="no dot product"):
         load(layout(5, b, types="9 14"))                                           # Q8_1 is an activation format, not a weight's
-    # a format without kernels here still parses (the table is about bytes); the row says it cannot run yet
+    # every format the table knows has kernels: the low-bit ones too
     q23 = 2 * I * (H // 256 * 84) + H * (I // 256 * 110)                           # Q2_K gate/up, Q3_K down
     t = load(layout(5, q23, types="10 11"))
-    assert not t.rows[0].kernels and load(layout(5, b)).rows[0].kernels
-    with pytest.raises(Exception, match="unsupported block format"):
-        t.layout(0)
+    assert t.rows[0].kernels and load(layout(5, b)).rows[0].kernels
+    assert t.layout(0).bytes == q23
 
 
 def test_v7_up_type_column():

@@ -13,7 +13,8 @@ from tests.helpers import make_expert_blobs, rel_l2
 G = np.load(Path(__file__).parent / "golden" / "ref_vectors.npz")
 
 
-@pytest.mark.parametrize("name,t,nv", [("nvfp4", 40, 64), ("q6k", 14, 256), ("iq1m", 29, 256), ("q8_0", 8, 32), ("q4k", 12, 256), ("q5k", 13, 256), ("q5_0", 6, 32), ("q5_1", 7, 32), ("iq4nl", 20, 32), ("iq4xs", 23, 256)])
+@pytest.mark.parametrize("name,t,nv", [("nvfp4", 40, 64), ("q6k", 14, 256), ("iq1m", 29, 256), ("q8_0", 8, 32), ("q4k", 12, 256), ("q5k", 13, 256), ("q5_0", 6, 32), ("q5_1", 7, 32), ("iq4nl", 20, 32), ("iq4xs", 23, 256), ("q2_0", 42, 64), ("q2k", 10, 256), ("q3k", 11, 256), ("iq2xxs", 16, 256), ("iq2xs", 17, 256),
+                                    ("iq2s", 22, 256), ("iq3xxs", 18, 256), ("iq3s", 21, 256), ("iq1s", 19, 256)])
 def test_decoders_match_reference_golden(name, t, nv):
     raw, want = G[f"dec_{name}_raw"], G[f"dec_{name}_f32"]
     got = O.dequantize(t, raw, 1, want.size).reshape(-1)
