@@ -16,10 +16,11 @@ GATE_SQRT_SOFTPLUS, GATE_SIGMOID, GATE_SOFTMAX, GATE_SOFTMAX_FAST, GATE_SOFTMAX_
 TYPE_Q6_K, TYPE_IQ1_M, TYPE_NVFP4 = 14, 29, 40
 X_F32, X_BF16, X_Q8_1 = 0, 1, 2
 OUT_F32, OUT_BF16 = 0, 1
+EXPERT_STAGE_ALL, EXPERT_STAGE_GU, EXPERT_STAGE_DOWN, EXPERT_PLAIN = 0, 1, 2, 4   # bsx_expert_layout.options
 
 
 class ExpertLayout(C.Structure):
-    _fields_ = [("gu_type", C.c_int32), ("d_type", C.c_int32), ("up_type", C.c_int32), ("reserved", C.c_int32),
+    _fields_ = [("gu_type", C.c_int32), ("d_type", C.c_int32), ("up_type", C.c_int32), ("options", C.c_int32),
                 ("n_embd", C.c_int64), ("n_ff", C.c_int64),
                 ("gu_row", C.c_uint64), ("d_row", C.c_uint64), ("up_row", C.c_uint64),
                 ("up_off", C.c_uint64), ("down_off", C.c_uint64), ("bytes", C.c_uint64),
@@ -80,7 +81,6 @@ _SIGNATURES = {
     "bsx_router_logits_x": (C.c_int32, [P, C.c_int32, P, C.c_int32, C.c_int32, C.c_int32, P, P]),
     "bsx_router_x": (C.c_int32, [P, C.c_int32, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_int32,
                                  C.c_int32, C.c_float, P, C.c_int32, P, P, P, P]),
-    "bsx_experts_set_phase": (None, [C.c_int32]),
     "bsx_route_tail_skip": (C.c_int32, [P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, P]),
     "bsx_dispatch_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "bsx_dispatch": (C.c_int32, [P, C.c_int64, C.c_int32, C.c_int32, P, P, P, P, C.c_int32, P, P, P, P]),

@@ -168,14 +168,7 @@ size_t row_bytes(int type, int64_t n) {
 }  // namespace
 }  // namespace bsx
 
-namespace bsx {
-static int g_phase = 0;
-int experts_phase() { return g_phase; }
-}  // namespace bsx
-
 using namespace bsx;
-
-extern "C" void bsx_experts_set_phase(int32_t phase) { g_phase = phase == 1 || phase == 2 ? phase : 0; }
 
 extern "C" size_t bsx_row_bytes(int32_t type, int64_t n) { return row_bytes(type, n); }
 extern "C" const char* bsx_version(void) { return "basalt_b200 0.1 (sm_100a)"; }
@@ -271,9 +264,7 @@ static int32_t experts_grouped_impl(int32_t n_x_rows, const bsx_expert_layout* l
     a.grid = iq1_device_grid();
     if (!a.grid) return (int32_t) cudaErrorInvalidSymbol;
     const cudaStream_t st = (cudaStream_t) stream;
-    // BSX_EXPERT_IMPL=simple forces the plain kernels (tests compare the two paths)
-    static const bool force_simple = [] { const char* e = getenv("BSX_EXPERT_IMPL"); return e && !strcmp(e, "simple"); }();
-    if (!force_simple) {
+    if (!(a.L.options & BSX_EXPERT_PLAIN)) {
         int32_t rc = experts_grouped_mma(a, st);      // NVFP4 blobs: fp16 images, mma.sync
         if (rc != BSX_E_TYPE) return rc;
         rc = experts_grouped_kq(a, st);               // Q6_K / IQ1_M blobs: int8 images, integer mma.sync

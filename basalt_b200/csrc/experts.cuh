@@ -79,8 +79,8 @@ __device__ __forceinline__ void load16(const void* x, int kind, int64_t row, int
 // the IQ1 codebook (2048 x uint16, 2 bits a coordinate) in this device's global memory; null on a CUDA error
 const uint16_t* iq1_device_grid();
 
-// 0 all launches, 1 gate/up only, 2 down only (bsx_experts_set_phase)
-int experts_phase();
+// 0 all launches, 1 gate/up only, 2 down only (the stage bits of bsx_expert_layout.options)
+inline int experts_phase(const bsx_expert_layout& L) { return L.options & BSX_EXPERT_STAGE_MASK; }
 
 int32_t experts_grouped_simple(const ExpertArgs& a, cudaStream_t st);
 // returns BSX_E_TYPE when the fast path does not cover the layout (the caller then runs the plain kernels)

@@ -545,7 +545,7 @@ int32_t experts_grouped_kq(const ExpertArgs& a, cudaStream_t st) {
     p += al256q((size_t) cap * 4);
     int* n_items = reinterpret_cast<int*>(p);
     int2* items = reinterpret_cast<int2*>(n_items + 4);
-    const int phase = experts_phase();
+    const int phase = experts_phase(a.L);
     const int64_t x_rows = a.n_x_rows > 0 ? a.n_x_rows : cap;
     const unsigned nbx = (unsigned) ((x_rows + 7) / 8 + 1), nbh = (unsigned) ((cap + 7) / 8 + 1);
     int32_t rc = BSX_OK;

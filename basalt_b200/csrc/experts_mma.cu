@@ -459,7 +459,7 @@ int32_t experts_grouped_mma(const ExpertArgs& a, cudaStream_t st) {
     float* hinv = xinv + align256((size_t) a.cap_entries * 4) / 4;
     int* n_items = reinterpret_cast<int*>(hinv + align256((size_t) a.cap_entries * 4) / 4);
     int2* items = reinterpret_cast<int2*>(n_items + 4);
-    const int phase = experts_phase();
+    const int phase = experts_phase(a.L);
     // a warp per image row, 8 a block, plus the block that lists the passes
     const int64_t x_rows = a.n_x_rows > 0 ? a.n_x_rows : a.cap_entries;
     const unsigned nbx = (unsigned) ((x_rows + 7) / 8 + 1), nbh = (unsigned) ((a.cap_entries + 7) / 8 + 1);

@@ -554,7 +554,7 @@ int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_
     float *xinv = sc.xinv, *hinv = sc.hinv;
     int* n_items = sc.n_items;
     PassRec* items = sc.items;
-    const int phase = experts_phase();
+    const int phase = experts_phase(a.L);
     const int64_t x_rows = a.n_x_rows > 0 ? a.n_x_rows : cap;
     StreamArgs sa;
     sa.e = a;

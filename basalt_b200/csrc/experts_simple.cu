@@ -196,7 +196,7 @@ down_simple_kernel(ExpertArgs a) {
 
 int32_t experts_grouped_simple(const ExpertArgs& a, cudaStream_t st) {
     const unsigned gy = (unsigned) (a.cap_groups < 1 ? 1 : a.cap_groups > 512 ? 512 : a.cap_groups);
-    const int phase = experts_phase();
+    const int phase = experts_phase(a.L);
     if (phase != 2) gu_simple_kernel<<<dim3((unsigned) ((a.L.n_ff + 7) / 8), gy), 256, 0, st>>>(a);
     if (phase != 1) down_simple_kernel<<<dim3((unsigned) ((a.L.n_embd + 7) / 8), gy), 256, 0, st>>>(a);
     return launch_status();

@@ -439,18 +439,18 @@ def instrumented_pass(layers, xs, stream, steps, L, T):
         capi.check("plan", lib.bsx_moe_plan_shared(_p(ly.ids), T, a.k, a.n_expert, _p(ly.blob_table), ly.shared_blob.data_ptr(), _p(ly.ptr), _p(ly.start),
                                                    _p(ly.n_groups), _p(ly.dst), _p(ly.tok), st))
         ev[2].record(stream)
-        for phase in (1, 2):
-            lib.bsx_experts_set_phase(phase)
+        for phase in (capi.EXPERT_STAGE_GU, capi.EXPERT_STAGE_DOWN):
+            Lp = capi.ExpertLayout.from_buffer_copy(ly.L)     # the same layout, one stage of the two
+            Lp.options = phase
             if ly.packed:
-                capi.check("experts", lib.bsx_experts_grouped_packed(C.byref(ly.L), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
+                capi.check("experts", lib.bsx_experts_grouped_packed(C.byref(Lp), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
                                                                       min(n, a.n_expert) + 1, n + T, _p(x), _x_kind(x), T, _p(ly.scratch), _p(ly.rows),
                                                                       capi.OUT_F32, _p(ly.status), st))
             else:
-                capi.check("experts", lib.bsx_experts_grouped_rows(C.byref(ly.L), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
+                capi.check("experts", lib.bsx_experts_grouped_rows(C.byref(Lp), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
                                                                     min(n, a.n_expert) + 1, n + T, _p(x), _x_kind(x), T, _p(ly.scratch), _p(ly.rows),
                                                                     capi.OUT_F32, st))
             ev[2 + phase].record(stream)
-        lib.bsx_experts_set_phase(0)
         capi.check("combine", lib.bsx_combine(_p(ly.rows), None, _p(ly.w), _p(ly.rows[n:n + T]), None, T, a.k, L.n_embd, _p(ly.y), st))
         ev[5].record(stream)
         stream.synchronize()

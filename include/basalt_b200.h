@@ -168,7 +168,7 @@ BSX_API int32_t bsx_moe_plan_shared(const int32_t* ids, int32_t T, int32_t k, in
  * blob = [gate rows | up rows | down rows | NVFP4 only: fp32 {s_gate, s_up, s_down, 0}], raw ggml blocks. */
 typedef struct bsx_expert_layout {
     int32_t gu_type, d_type, up_type;
-    int32_t reserved;
+    int32_t options;                   /* BSX_EXPERT_* bits below; 0 from bsx_expert_layout_init */
     int64_t n_embd, n_ff;
     uint64_t gu_row, d_row, up_row;    /* bytes per gate, down and up row */
     uint64_t up_off, down_off, bytes;  /* offsets inside the blob; its size */
@@ -176,6 +176,17 @@ typedef struct bsx_expert_layout {
     float gate_softcap, up_softcap;    /* > 0 (both): h = cg tanh(g/cg) sigmoid(g) cu tanh(u/cu) */
     float reserved_f;
 } bsx_expert_layout;
+
+/* bsx_expert_layout.options, read by every bsx_experts_grouped* call that gets the layout (per call: nothing process-wide).
+ * The stage bits mirror native_expert_set_mode's phase (include/basalt/kernels/iq_kernels.hpp:113-115), which the reference's
+ * bench uses to time each half alone. */
+enum {
+    BSX_EXPERT_STAGE_ALL = 0,    /* gate/up + SwiGLU, then down */
+    BSX_EXPERT_STAGE_GU = 1,     /* gate/up + SwiGLU only (h stays in the scratch) */
+    BSX_EXPERT_STAGE_DOWN = 2,   /* down only, over the h a GU call left */
+    BSX_EXPERT_STAGE_MASK = 3,
+    BSX_EXPERT_PLAIN = 4         /* the warp-per-row kernels whatever the format (the second opinion of the parity tests) */
+};
 
 BSX_API int32_t bsx_expert_layout_init(int32_t gu_type, int32_t d_type, int32_t up_type, int64_t n_embd, int64_t n_ff,
                                float swiglu_limit, float gate_softcap, float up_softcap, bsx_expert_layout* layout);
@@ -238,10 +249,6 @@ BSX_API int32_t bsx_experts_grouped_packed(const bsx_expert_layout* layout, cons
                                            const int32_t* n_groups, const int32_t* ent_dst, const int32_t* ent_tok, int64_t cap_groups,
                                            int64_t cap_entries, const void* x, int32_t x_kind, int32_t n_x_rows, void* scratch, void* out,
                                            int32_t out_kind, int32_t* status, void* stream);
-
-/* The bench only: which launches bsx_experts_grouped makes (0 all, 1 gate/up + SwiGLU, 2 down), so each stage can be timed
- * alone.  Mirrors native_expert_set_mode's phase (iq_kernels.hpp:113-115).  Process-wide; set it back to 0. */
-BSX_API void bsx_experts_set_phase(int32_t phase);
 
 /* ---- a11 / a12: prompt-sized grouped experts on the tcgen05 tensor cores, ggml blobs in place: NVFP4 (replaces fp4::run_group /
  * run_experts, include/basalt/prefill/moe_fp4.hpp:43-113, src/prefill/moe_fp4.cu:604-687) and the K- / I-quant formats Q6_K and

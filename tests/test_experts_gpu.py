@@ -57,8 +57,6 @@ CASES = [("nvfp4", 40, 40, 2048, 512), ("q6k", 14, 14, 2048, 512), ("iq1m", 29, 
 @pytest.mark.parametrize("impl", ["fast", "simple"])
 @pytest.mark.parametrize("name,gt,dt,H,I", CASES)
 def test_grouped_experts_vs_dequantised_reference(lib, cuda, name, gt, dt, H, I, impl, monkeypatch):
-    if impl == "simple":
-        pytest.importorskip("subprocess")
     rng = np.random.default_rng(H + I + gt)
     E = 3 if H > 4096 else 5
     Lo, blobs = make_expert_blobs(rng, E, gt, dt, H, I)
@@ -86,17 +84,10 @@ def test_grouped_experts_vs_dequantised_reference(lib, cuda, name, gt, dt, H, I,
 
 
 def _run_simple(L, bd, ge, gt_, xd, n):
-    """the plain kernels are selected by BSX_EXPERT_IMPL=simple, read once per process: run them in a child process"""
-    import pickle, subprocess, sys, tempfile
-    with tempfile.TemporaryDirectory() as d:
-        with open(d + "/in.pkl", "wb") as f:
-            pickle.dump(dict(L=bytes(L), blobs=bd.cpu().numpy(), ge=ge, gt=gt_, x=xd.cpu().numpy(), n=n), f)
-        code = ("import pickle,sys,torch,numpy as np;sys.path.insert(0,%r);from tests.test_experts_gpu import run_grouped,dev;"
-                "from basalt_b200 import capi;d=pickle.load(open(%r,'rb'));L=capi.ExpertLayout.from_buffer_copy(d['L']);"
-                "o=run_grouped(L,dev(d['blobs']),d['ge'],d['gt'],dev(d['x']),d['n']).cpu().numpy();np.save(%r,o)") % (
-                    os.path.dirname(os.path.dirname(os.path.abspath(__file__))), d + "/in.pkl", d + "/out.npy")
-        subprocess.check_call([sys.executable, "-c", code], env=dict(os.environ, BSX_EXPERT_IMPL="simple"))
-        return np.load(d + "/out.npy")
+    """the warp-per-row kernels: the same call with BSX_EXPERT_PLAIN in the layout's options"""
+    Lp = capi.ExpertLayout.from_buffer_copy(L)
+    Lp.options |= capi.EXPERT_PLAIN
+    return run_grouped(Lp, bd, ge, gt_, xd, n).cpu().numpy()
 
 
 @pytest.mark.parametrize("kind", ["bf16", "q8_1", "bf16_out"])

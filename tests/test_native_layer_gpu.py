@@ -214,7 +214,7 @@ def test_expert_parallel_step_emulated_on_one_gpu(lib, cuda, packed):
         ptr = torch.zeros(E + 3, dtype=torch.int64, device="cuda"); start = torch.zeros(E + 3, dtype=torch.int32, device="cuda")
         ng = torch.zeros(1, dtype=torch.int32, device="cuda")
         ed = torch.zeros(n + T, dtype=torch.int32, device="cuda"); et = torch.zeros(n + T, dtype=torch.int32, device="cuda")
-        moe.check("bsx_ep_plan", lib.bsx_ep_plan(route_all.data_ptr(), n, k, T * k, 2 * T * k, E, tab.data_ptr(), bd[E].data_ptr(), r * T, T, ptr.data_ptr(),
+        moe.check("bsx_ep_plan", lib.bsx_ep_plan(route_all.data_ptr(), n, k, T * k, 2 * T * k, E, tab.data_ptr(), bd[E].data_ptr(), r * T, T, None, ptr.data_ptr(),
                                                   start.data_ptr(), ng.data_ptr(), ed.data_ptr(), et.data_ptr(), st))
         rows = torch.full((n + T, H), float("nan"), dtype=torch.float32, device="cuda")
         if packed:
@@ -227,7 +227,7 @@ def test_expert_parallel_step_emulated_on_one_gpu(lib, cuda, packed):
             moe.native_expert_grouped(L, ptr, start, ng, ed, et, hi - lo + 1, n + T, x_all, scratch, rows, n_x_rows=W * T)
         y_part = torch.empty((W * T, H), dtype=torch.float32, device="cuda")
         moe.check("bsx_combine_partial_ep", lib.bsx_combine_partial_ep(rows.data_ptr(), route_all.data_ptr() + 4 * T * k, route_all.data_ptr(), T, 2 * T * k, lo, hi,
-                                                                        W * T, k, H, rows[n:].data_ptr(), r * T, T, y_part.data_ptr(), st))
+                                                                        W * T, k, H, rows[n:].data_ptr(), r * T, T, None, y_part.data_ptr(), st))
         torch.cuda.synchronize()
         g = int(ng.item())
         # the groups are this rank's experts with pairs, ascending, plus the shared group; every local pair has exactly one entry
