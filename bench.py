@@ -835,6 +835,18 @@ def run_expert_parallel(args, rank, world, dev):
     vals = times.tolist()
     ms_total, ms_e2e = vals[0], vals[1]
     stage_max = dict(zip(sorted(stage_ms), vals[2:]))
+    wl = None
+    if not args.no_workloads and T == 64:
+        # the DeepSeek-style layer, 8192 prompt tokens in total split over the ranks (strong scaling across N): every rank joins
+        del layers, mine, ly
+        torch.cuda.empty_cache()
+        wp = argparse.Namespace(**vars(args))
+        wp.experts = "packed"
+        n_tok = 8192 // world
+        pl = run_prefill(wp, dev, rank, world, shape="c3", tokens=n_tok, steps=5, warmup=3)
+        if pl is not None:
+            pl["config"]["workload"] = f"{SHAPES['c3']['name']} prefill, 8192 tokens/step in total ({n_tok} per GPU x {world} GPUs: total work fixed as N grows)"
+            wl = [short(pl)]
     if rank != 0:
         return
     ms_step = ms_total / args.steps
@@ -861,6 +873,13 @@ def run_expert_parallel(args, rank, world, dev):
         "stage_ms": stage_max, "stage_ms_note": "max over ranks, steps launched call by call with events between the stages (the timed steps replay one graph)",
         "clocks": clocks.summary(),
     }
+    if stage_max:
+        outside = {k: v for k, v in stage_max.items() if k != "experts"}
+        top = max(outside, key=outside.get) if outside else None
+        line["limiter"] = (f"local experts {stage_max.get('experts', 0.0) * 1e3:.0f} us of {sum(stage_max.values()) * 1e3:.0f} us of stages; largest stage outside them: "
+                           f"{top} {outside[top] * 1e3:.0f} us" if top else "local experts")
+    if wl:
+        line["workloads"] = wl
     print(json.dumps(line))
 
 
