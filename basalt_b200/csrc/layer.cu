@@ -162,8 +162,10 @@ extern "C" int32_t bsx_moe_layer(const bsx_moe_layer_desc* d, const void* x, int
     } else if (d->packed) {
         rc = experts_packed_x_images(L, x, x_kind, T, c.cap_rows, c.scratch, st);
         if (rc != BSX_OK) return rc;
+        pdl_state().late_wait = true;   // the logits read x, not the images: the two kernels run side by side
     }
     rc = bsx_router_logits_x(xe, xe_kind, d->gate, T, E, H, c.logits, stream);
+    pdl_state().late_wait = false;
     if (rc != BSX_OK) return rc;
     PassRec* items = nullptr;
     int* n_items = nullptr;

@@ -15,6 +15,10 @@ namespace bsx {
 struct PdlState {
     bool on = false;
     int plain = 0;   // launches still to go the plain way (the first kernel of a step follows work of another kind)
+    // The next launch reads nothing the kernel before it writes (its inputs were complete before that kernel started): it may run
+    // beside its predecessor and wait for it only before it exits, which keeps "my completion implies my predecessors'" true for
+    // the kernels after it.  Read and cleared by the launch code of the kernels that support it.
+    bool late_wait = false;
 };
 inline PdlState& pdl_state() {
     thread_local PdlState s;

@@ -85,7 +85,7 @@ __device__ __forceinline__ int merged_butterfly(float (&acc)[G], int lane) {
 template <int NV, int G, bool BF16>
 __global__ void __launch_bounds__(kLogitThreads, (NV <= 4 ? 2 : 1))
 router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate, int n_embd, int n_expert, int n_tokens,
-                     int tok_per_block, float* __restrict__ logits) {
+                     int tok_per_block, float* __restrict__ logits, int late_wait) {
     __shared__ float red[G][kTokTile][kLogitThreads / 32];
     const int n4 = n_embd >> 2;
     const int r0 = blockIdx.x * G;
@@ -99,7 +99,9 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
             const int i = threadIdx.x + c * kLogitThreads;
             w[g][c] = i < n4 ? reinterpret_cast<const float4*>(gate + (size_t) (r0 + g) * n_embd)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-    pdl_wait();
+    // late_wait: x was complete before the kernel ahead of this one started (that kernel makes the expert kernels' images of x),
+    // so this grid runs beside it and only orders itself after it before exiting
+    if (!late_wait) pdl_wait();
     pdl_launch_dependents();
     const int t_begin = blockIdx.y * tok_per_block;
     const int t_end = min(n_tokens, t_begin + tok_per_block);
@@ -159,6 +161,7 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
         }
         __syncthreads();
     }
+    if (late_wait) pdl_wait();
 }
 
 
@@ -171,7 +174,7 @@ router_logits_kernel(const void* __restrict__ x, const float* __restrict__ gate,
 template <int NV, int G, bool BF16>
 __global__ void __launch_bounds__(kLogitThreads, 2)
 router_logits_staged_kernel(const void* __restrict__ x, const float* __restrict__ gate, int n_embd, int n_expert, int n_tokens,
-                            int tok_per_block, float* __restrict__ logits) {
+                            int tok_per_block, float* __restrict__ logits, int late_wait) {
     extern __shared__ __align__(16) uint8_t xsm[];
     __shared__ float red[2][G][kTokTile][kLogitThreads / 32];
     const int n4 = n_embd >> 2;
@@ -185,7 +188,9 @@ router_logits_staged_kernel(const void* __restrict__ x, const float* __restrict_
             const int i = threadIdx.x + c * kLogitThreads;
             w[g][c] = i < n4 ? reinterpret_cast<const float4*>(gate + (size_t) (r0 + g) * n_embd)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-    pdl_wait();
+    // late_wait: x was complete before the kernel ahead of this one started (that kernel makes the expert kernels' images of x),
+    // so this grid runs beside it and only orders itself after it before exiting
+    if (!late_wait) pdl_wait();
     pdl_launch_dependents();
     const int t_begin = blockIdx.y * tok_per_block;
     const int nt_all = min(n_tokens, t_begin + tok_per_block) - t_begin;
@@ -241,9 +246,18 @@ router_logits_staged_kernel(const void* __restrict__ x, const float* __restrict_
             }
         }
     }
+    if (late_wait) pdl_wait();
 }
 
 constexpr size_t kStagedSmemMax = 96 * 1024;
+
+// 1 when this launch may run beside the kernel ahead of it (pdl.cuh); only inside a scope whose launches are programmatic
+inline int take_late_wait() {
+    PdlState& ps = pdl_state();
+    const bool late = ps.late_wait && ps.on && ps.plain == 0;
+    ps.late_wait = false;
+    return late ? 1 : 0;
+}
 
 template <int NV, int G, bool BF16>
 int32_t launch_logits_staged(const void* x, const float* gate, int T, int E, int H, int tpb, float* logits, cudaStream_t st) {
@@ -257,7 +271,7 @@ int32_t launch_logits_staged(const void* x, const float* gate, int T, int E, int
     }
     const size_t smem = (size_t) tpb * H * (BF16 ? 2 : 4);
     const dim3 grid((unsigned) (E / G), (unsigned) ((T + tpb - 1) / tpb));
-    launch_k(router_logits_staged_kernel<NV, G, BF16>, grid, dim3(kLogitThreads), smem, st, x, gate, H, E, T, tpb, logits);
+    launch_k(router_logits_staged_kernel<NV, G, BF16>, grid, dim3(kLogitThreads), smem, st, x, gate, H, E, T, tpb, logits, take_late_wait());
     return launch_status();
 }
 
@@ -278,8 +292,9 @@ template <int NV, int G>
 void launch_logits(const void* x, bool bf16, const float* gate, int T, int E, int H, float* logits, cudaStream_t st) {
     const int tpb = T <= 256 ? kTokTile : 8 * kTokTile;
     const dim3 grid((unsigned) (E / G), (unsigned) ((T + tpb - 1) / tpb));
-    if (bf16) launch_k(router_logits_kernel<NV, G, true>, grid, dim3(kLogitThreads), 0, st, x, gate, H, E, T, tpb, logits);
-    else launch_k(router_logits_kernel<NV, G, false>, grid, dim3(kLogitThreads), 0, st, x, gate, H, E, T, tpb, logits);
+    const int late = take_late_wait();
+    if (bf16) launch_k(router_logits_kernel<NV, G, true>, grid, dim3(kLogitThreads), 0, st, x, gate, H, E, T, tpb, logits, late);
+    else launch_k(router_logits_kernel<NV, G, false>, grid, dim3(kLogitThreads), 0, st, x, gate, H, E, T, tpb, logits, late);
 }
 
 template <int G>
@@ -563,8 +578,7 @@ static int32_t logits_launch(const void* x, int32_t x_kind, const float* gate, i
     const int nv = (H / 4 + kLogitThreads - 1) / kLogitThreads;
     // decode windows of 16+ tokens whose rows fit shared memory: the staged kernel, one wave of blocks
     const size_t row_bytes = (size_t) H * (bf16 ? 2 : 4);
-    static const bool plain_only = [] { const char* e = getenv("BSX_LOGITS_PLAIN"); return e && e[0] == '1'; }();   // measurement switch
-    if (!plain_only && T >= 16 && T <= 1024 && nv <= 4 && 8 * row_bytes <= kStagedSmemMax) {
+    if (T >= 16 && T <= 1024 && nv <= 4 && 8 * row_bytes <= kStagedSmemMax) {
         int tpb = (int) (kStagedSmemMax / row_bytes) & ~7;
         tpb = tpb > 16 ? 16 : tpb;      // 16 tokens (64 KB of bf16 rows at hidden 2048): two or three blocks share an SM
         if (tpb > ((T + 7) & ~7)) tpb = (T + 7) & ~7;
@@ -688,6 +702,8 @@ int32_t moe_plan_with_passes(const int32_t* ids, int32_t T, int32_t k, int32_t E
                              unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok, PassRec* items, int* n_items,
                              cudaStream_t st);
 
+constexpr int kRoutePlanMaxTokens = 64;
+
 // selection + plan (+ the packed kernels' pass list when items is given); BSX_E_TYPE: a gate kind the fused kernel does not cover
 int32_t route_plan_launch(const float* logits, const float* bias, int32_t T, int32_t E, int32_t k, int32_t gate_kind, float weight_scale,
                           int32_t n_group, int32_t topk_group, const unsigned long long* blob_table, unsigned long long shared_blob, int32_t* ids,
@@ -707,9 +723,10 @@ int32_t route_plan_launch(const float* logits, const float* bias, int32_t T, int
         if (topk_group < 1 || topk_group > n_group) topk_group = n_group;
         if ((int64_t) topk_group * (E / n_group) < k) return BSX_E_GEOMETRY;
     }
-    if (T > 32) {
-        // One warp's selection is a chain of ~10 us whatever the window; the fused block has 32 warps, so beyond 32 tokens its
-        // warps would take tokens in turn.  Wider windows keep the selection spread over blocks and fuse only plan + pass list.
+    if (T > kRoutePlanMaxTokens) {
+        // The fused block has 32 warps and a warp's selection is one dependent chain, so its warps take the window's tokens in turn:
+        // up to two rounds that is still cheaper than a launch.  Wider windows keep the selection spread over blocks and fuse only
+        // plan + pass list.
         const int32_t rc = bsx_router_select(logits, bias, T, E, k, gate_kind, weight_scale, n_group, topk_group, 0.f, nullptr, 0, ids, weights, (void*) st);
         if (rc != BSX_OK) return rc;
         return moe_plan_with_passes(ids, T, k, E, blob_table, shared_blob, ptr, start, n_groups, dst, tok, items, n_items, st);

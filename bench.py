@@ -835,10 +835,12 @@ def run_expert_parallel(args, rank, world, dev):
     vals = times.tolist()
     ms_total, ms_e2e = vals[0], vals[1]
     stage_max = dict(zip(sorted(stage_ms), vals[2:]))
+    data_plane, launches_per_step = layers[0].DATA_PLANE, layers[0].LAUNCHES
     wl = None
     if not args.no_workloads and T == 64:
         # the DeepSeek-style layer, 8192 prompt tokens in total split over the ranks (strong scaling across N): every rank joins
-        del layers, mine, ly
+        layers.clear()
+        del mine, ly
         torch.cuda.empty_cache()
         wp = argparse.Namespace(**vars(args))
         wp.experts = "packed"
@@ -860,13 +862,13 @@ def run_expert_parallel(args, rank, world, dev):
         "dtype": ("NVFP4 weights x 4-term FP4 activations on tcgen05 kind::mxf4nvf4 (block-scaled), fp32 accumulation" if use_packed
                   else "fp16 x NVFP4 tensor-core products (mma.sync), fp32 accumulation"), "data": "synthetic",
         "config": dict(decode_config(sh, T), tokens_per_step=T * world, tokens_per_gpu=T,
-                       parallelism=f"ep{world}: {E // world} routed experts per GPU, router and shared expert replicated; " + layers[0].DATA_PLANE,
+                       parallelism=f"ep{world}: {E // world} routed experts per GPU, router and shared expert replicated; " + data_plane,
                        l2_policy=f"each rank cycles through {args.copies} copies of its expert shard",
                        expert_kernels="packed planes + tcgen05 block-scaled FP4" if use_packed else "ggml blobs in place + fp16 images + mma.sync",
                        launch="one CUDA graph per step, collectives included" if use_graph else "one host launch per kernel"),
         "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2 * world,
                 "d2h_bytes_per_step": T * H * 4 * world},
-        "gpu_launches": layers[0].LAUNCHES * args.steps,
+        "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "kernel": "rank 0's local grouped experts (image prep, gate/up, down)", "achieved": achieved, "peak": pk["hbm"],
                      "unit": "GB/s", "frac": achieved / pk["hbm"], "peak_source": pk["source"], "traffic": None, "algorithmic_bytes_per_launch": k_bytes,
                      "kernel_ms": k_ms},
