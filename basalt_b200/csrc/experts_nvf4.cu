@@ -43,25 +43,35 @@
 namespace bsx {
 namespace {
 
-constexpr int kEntF = kPassEntries;        // entries per pass (8)
-constexpr int kColsF = kTermsF * kEntF;    // 32 = MMA N
-constexpr int kStagesF = 5;
 constexpr int kATile = 128 * 128;          // one operand tile of a stage: 128 rows x 128 bytes (256 columns of codes)
-constexpr int kBTile = kColsF * 128;
 constexpr int kSFTile = 4 * 512;           // 4 K-steps x (32 lanes x 4 words)
-// a stage: [tile 0 codes | tile 0 scales | tile 1 codes | tile 1 scales | activation codes | activation scales]
-constexpr int kOffSFA0 = kATile, kOffA1 = kATile + kSFTile, kOffSFA1 = kOffA1 + kATile, kOffB = kOffSFA1 + kSFTile, kOffSFB = kOffB + kBTile;
-constexpr int kStageF = kOffSFB + kSFTile;             // 43,008 bytes
-constexpr int kThreadsF = 32 * 7;                      // MMA warp, weight loader warp, activation loader warp, four epilogue warps
-constexpr size_t kSmemF = 1024 + (size_t) kStagesF * kStageF + 256;
-// tensor-memory columns: two accumulator sets of (D0, D1) x 32 columns, then per stage 16 columns each for SFA0, SFA1, SFB
-constexpr uint32_t kTmemSF = 128, kTmemCols = 512;
-// kind::mxf4nvf4, scale_vec::4X: E2M1 x E2M1, UE4M3 scales (bit 23 = 0), both K-major, N = 32, M = 128
-constexpr uint32_t kIdescF = (1u << 7) | (1u << 10) | ((uint32_t) (kColsF >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
+constexpr int kThreadsF = 32 * 7;          // MMA warp, weight loader warp, activation loader warp, four epilogue warps
+constexpr uint32_t kTmemCols = 512;
+constexpr int kOffSFA0 = kATile, kOffA1 = kATile + kSFTile, kOffSFA1 = kOffA1 + kATile, kOffB = kOffSFA1 + kSFTile;
+constexpr int kEntNarrow = kPassEntries, kEntWide = 2 * kPassEntries;
+
+// The kernel in two widths.  ENT = entries per pass: 8 (the MMA's N = 32 columns; what a decode window on one GPU needs, where an
+// expert sees a handful of tokens) or 16 (N = 64; for expert-parallel steps, where the gathered tokens of all ranks give every local
+// expert tens of entries and each pass streams the expert's blocks again - from L2 after the first, but at half the passes).
+template <int ENT>
+struct FG {
+    static constexpr int kCols = kTermsF * ENT;         // MMA N
+    static constexpr int kBTile = kCols * 128;
+    // a stage: [tile 0 codes | tile 0 scales | tile 1 codes | tile 1 scales | activation codes | activation scales]
+    static constexpr int kOffSFB = kOffB + kBTile;
+    static constexpr int kStage = kOffSFB + kSFTile;    // 43,008 or 47,104 bytes: multiples of 1024
+    static constexpr int kStages = ENT == kEntNarrow ? 5 : 4;
+    static constexpr size_t kSmem = 1024 + (size_t) kStages * kStage + 256;
+    // tensor-memory columns: two accumulator sets of (D0, D1) x kCols columns, then per stage 16 columns each for SFA0, SFA1, SFB
+    static constexpr uint32_t kAccCols = 2 * kCols, kTmemSF = 2 * kAccCols;
+    // kind::mxf4nvf4, scale_vec::4X: E2M1 x E2M1, UE4M3 scales (bit 23 = 0), both K-major, N = kCols, M = 128
+    static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t) (kCols >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
+    static_assert(kStage % 1024 == 0 && kSmem <= 227 * 1024 && kTmemSF + kStages * 48 <= kTmemCols, "stage geometry");
+};
 
 enum { FMODE_GU = 0, FMODE_DOWN = 1 };
 
-// a pass (PassRec, plan.cuh): up to kEntF consecutive entries [eb, eb + ntok) of one group, with the group's blob - everything a
+// a pass (PassRec, plan.cuh): up to ENT consecutive entries [eb, eb + ntok) of one group, with the group's blob - everything a
 // stream kernel needs about it in one 16-byte load
 
 size_t al256f(size_t v) { return (v + 255) & ~(size_t) 255; }
@@ -110,10 +120,10 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint8_t* __restrict__ i
 // residual -= code value x s.  Layout: codes [row][term][K / 2] bytes with ggml's nibble order (byte b of a sub-block =
 // values b and b + 8), scales [row][term][K / 16] bytes, inv[row].  FROM_H = false: rows of x (kind x_kind) - row i of x
 // when the caller gave the number of x rows, else the row of entry i; true: row e of the SwiGLU output h.  The last block
-// lists the passes (up to kEntF consecutive entries of one group).
+// lists the passes (up to pass_entries consecutive entries of one group).
 template <bool FROM_H, int TPR>
 __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __restrict__ codes, uint8_t* __restrict__ sfs, float* __restrict__ inv,
-                                                        PassRec* __restrict__ items, int* __restrict__ n_items) {
+                                                        PassRec* __restrict__ items, int* __restrict__ n_items, int pass_entries) {
     pdl_wait();
     pdl_launch_dependents();
     const int ng = min(*a.n_groups, (int) a.cap_groups);
@@ -129,7 +139,7 @@ __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __
             const int g = g0 + threadIdx.x;
             const int s0 = g < ng ? a.grp_start[g] : 0;
             const int cnt = g < ng ? max(0, min(a.grp_start[g + 1], (int) a.cap_entries) - s0) : 0;
-            const int np = (cnt + kEntF - 1) / kEntF;
+            const int np = (cnt + pass_entries - 1) / pass_entries;
             int x = np;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -143,8 +153,8 @@ __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __
             for (int p = 0; p < np; ++p) {
                 PassRec r;
                 r.blob = a.grp_ptr[g];
-                r.eb = s0 + p * kEntF;
-                r.ntok = min(kEntF, cnt - p * kEntF);
+                r.eb = s0 + p * pass_entries;
+                r.ntok = min(pass_entries, cnt - p * pass_entries);
                 items[before + x - np + p] = r;
             }
             __syncthreads();
@@ -190,11 +200,12 @@ __global__ void __launch_bounds__(kNormThreads) norm_images_kernel(const void* _
 }
 
 template <bool FROM_H>
-void launch_prep(const ExpertArgs& a, int64_t rows, int64_t K, uint8_t* codes, uint8_t* sfs, float* inv, PassRec* items, int* n_items, cudaStream_t st) {
+void launch_prep(const ExpertArgs& a, int64_t rows, int64_t K, uint8_t* codes, uint8_t* sfs, float* inv, PassRec* items, int* n_items, int pass_entries,
+                 cudaStream_t st) {
     const int64_t n_sb = K / 16;
-    if (n_sb <= 32) launch_k(prep_fp4_kernel<FROM_H, 32>, dim3((unsigned) ((rows + 7) / 8 + 1)), dim3(256), 0, st, a, codes, sfs, inv, items, n_items);
-    else if (n_sb <= 128) launch_k(prep_fp4_kernel<FROM_H, 128>, dim3((unsigned) ((rows + 1) / 2 + 1)), dim3(256), 0, st, a, codes, sfs, inv, items, n_items);
-    else launch_k(prep_fp4_kernel<FROM_H, 256>, dim3((unsigned) (rows + 1)), dim3(256), 0, st, a, codes, sfs, inv, items, n_items);
+    if (n_sb <= 32) launch_k(prep_fp4_kernel<FROM_H, 32>, dim3((unsigned) ((rows + 7) / 8 + 1)), dim3(256), 0, st, a, codes, sfs, inv, items, n_items, pass_entries);
+    else if (n_sb <= 128) launch_k(prep_fp4_kernel<FROM_H, 128>, dim3((unsigned) ((rows + 1) / 2 + 1)), dim3(256), 0, st, a, codes, sfs, inv, items, n_items, pass_entries);
+    else launch_k(prep_fp4_kernel<FROM_H, 256>, dim3((unsigned) (rows + 1)), dim3(256), 0, st, a, codes, sfs, inv, items, n_items, pass_entries);
 }
 
 // ---------------------------------------------------------------- the stream kernel
@@ -212,8 +223,11 @@ __device__ __forceinline__ uint64_t sf_desc(uint32_t addr) {   // 32 rows x 16 b
     return (uint64_t) ((addr & 0x3FFFFu) >> 4) | ((uint64_t) (128 >> 4) << 16) | ((uint64_t) (128 >> 4) << 32) | ((uint64_t) 1 << 46);
 }
 
-template <int MODE>
+template <int MODE, int ENT>
 __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa) {
+    using G = FG<ENT>;
+    constexpr int kStagesF = G::kStages, kStageF = G::kStage, kOffSFB = G::kOffSFB;
+    constexpr uint32_t kTmemSF = G::kTmemSF, kIdescF = G::kIdesc;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStagesF * kStageF);
@@ -283,7 +297,7 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
                     ok = mbar_wait(&acc_empty[acc], ((ti >> 1) & 1u) ^ 1u);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const uint32_t d0 = tmem + acc * 64, d1 = d0 + 32;
+                    const uint32_t d0 = tmem + acc * G::kAccCols, d1 = d0 + G::kCols;
                     for (int c = 0; c < n_chunk; ++c, ++kc) {
                         const uint32_t s = kc % kStagesF;
                         ok = mbar_wait(&full[s], (kc / kStagesF) & 1u);
@@ -372,18 +386,22 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
             if (unit + (int) gridDim.x < n_units) nxt = sa.items[(unit + gridDim.x) / n_upp];
             int rb0, rb1;
             unit_blocks(unit, rb0, rb1);
-            const uint8_t* crow[kEntF];
+            const uint8_t* crow[ENT];
 #pragma unroll
-            for (int j = 0; j < kEntF; ++j) {
+            for (int j = 0; j < ENT; ++j) {
                 const int e = u.eb + (j < u.ntok ? j : 0);
                 const int ir = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
                 crow[j] = sa.codes + ((size_t) ir * kTermsF + r4) * (size_t) (K >> 1) + c8 * 16;
             }
-            const uint8_t* srow;
-            {
-                const int e = u.eb + ((lane >> 2) < u.ntok ? (lane >> 2) : 0);
+            // scales: column n = 4 entry + term is row n of the B operand; its word of a K-step sits at lane n % 32, word n / 32 of
+            // the step's 512-byte block.  A lane serves columns lane, lane + 32, ...
+            const uint8_t* srow[ENT / 8];
+#pragma unroll
+            for (int h = 0; h < ENT / 8; ++h) {
+                const int j = 8 * h + (lane >> 2);
+                const int e = u.eb + (j < u.ntok ? j : 0);
                 const int ir = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
-                srow = sa.sfs + ((size_t) ir * kTermsF + (lane & 3)) * (size_t) (K >> 4);
+                srow[h] = sa.sfs + ((size_t) ir * kTermsF + (lane & 3)) * (size_t) (K >> 4);
             }
             for (int rb = rb0; rb < rb1 && ok; ++rb) {
                 for (int c = 0; c < n_chunk; ++c) {
@@ -392,13 +410,16 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
                     if (!ok) break;
                     const uint32_t st = smem_u32(smem + s * kStageF);
 #pragma unroll
-                    for (int i = 0; i < kEntF; ++i)
+                    for (int i = 0; i < ENT; ++i)
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(st + (uint32_t) ((i >> 1) * 1024) + dsto[i & 1]), "l"(crow[i] + (size_t) c * 128)
                                      : "memory");
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(st + (uint32_t) kOffSFB + k * 512 + lane * 16), "l"(srow + (size_t) c * 16 + 4 * k)
-                                     : "memory");
+                    for (int h = 0; h < ENT / 8; ++h)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(st + (uint32_t) kOffSFB + k * 512 + lane * 16 + h * 4),
+                                         "l"(srow[h] + (size_t) c * 16 + 4 * k)
+                                         : "memory");
                     asm volatile("cp.async.commit_group;\n" ::: "memory");
                     ++issued;
                     if (issued - arrived > 2) {
@@ -432,10 +453,10 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
             unit_blocks(unit, rb0, rb1);
             const float* tail = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(u.blob) + geo.tail);
             const float sg = tail[0], su = tail[1], sd = tail[2];
-            float f[kEntF];
-            int64_t orow[kEntF];
+            float f[ENT];
+            int64_t orow[ENT];
 #pragma unroll
-            for (int j = 0; j < kEntF; ++j) {
+            for (int j = 0; j < ENT; ++j) {
                 const int e = u.eb + (j < u.ntok ? j : 0);
                 const int ir = (MODE == FMODE_GU && a.n_x_rows > 0) ? a.ent_tok[e] : e;
                 f[j] = sa.inv[ir];
@@ -447,23 +468,30 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
                 ok = __all_sync(kFull, mbar_wait(&acc_full[acc], (ti >> 1) & 1u));
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                uint32_t d0[32], d1[32];
-                tmem_ld32(tmem + lane_base + acc * 64, d0);
-                tmem_ld32(tmem + lane_base + acc * 64 + 32, d1);
-                // the accumulators are in registers: the MMA warp may start the next row block on this set
-                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-                mbar_arrive(&acc_empty[acc]);
-                ++ti;
+                // 8 entries (32 accumulator columns of each tile) at a time
 #pragma unroll
-                for (int j = 0; j < kEntF; ++j) {
-                    if (j < u.ntok) {
-                        const float v0 = ((__uint_as_float(d0[4 * j]) + __uint_as_float(d0[4 * j + 1])) + __uint_as_float(d0[4 * j + 2])) + __uint_as_float(d0[4 * j + 3]);
-                        const float v1 = ((__uint_as_float(d1[4 * j]) + __uint_as_float(d1[4 * j + 1])) + __uint_as_float(d1[4 * j + 2])) + __uint_as_float(d1[4 * j + 3]);
-                        if (MODE == FMODE_GU) {
-                            a.h[orow[j] + r0 + rl] = swiglu(v0 * f[j] * sg, v1 * f[j] * su, a.L);
-                        } else {
-                            store_out(a.out, a.out_kind, orow[j] + r0 + rl, v0 * f[j] * sd);
-                            store_out(a.out, a.out_kind, orow[j] + r0 + 128 + rl, v1 * f[j] * sd);
+                for (int hb = 0; hb < ENT / 8; ++hb) {
+                    uint32_t d0[32], d1[32];
+                    tmem_ld32(tmem + lane_base + acc * G::kAccCols + 32 * hb, d0);
+                    tmem_ld32(tmem + lane_base + acc * G::kAccCols + G::kCols + 32 * hb, d1);
+                    if (hb == ENT / 8 - 1) {
+                        // the accumulators are in registers: the MMA warp may start the next row block on this set
+                        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+                        mbar_arrive(&acc_empty[acc]);
+                        ++ti;
+                    }
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) {
+                        const int j = 8 * hb + jj;
+                        if (j < u.ntok) {
+                            const float v0 = ((__uint_as_float(d0[4 * jj]) + __uint_as_float(d0[4 * jj + 1])) + __uint_as_float(d0[4 * jj + 2])) + __uint_as_float(d0[4 * jj + 3]);
+                            const float v1 = ((__uint_as_float(d1[4 * jj]) + __uint_as_float(d1[4 * jj + 1])) + __uint_as_float(d1[4 * jj + 2])) + __uint_as_float(d1[4 * jj + 3]);
+                            if (MODE == FMODE_GU) {
+                                a.h[orow[j] + r0 + rl] = swiglu(v0 * f[j] * sg, v1 * f[j] * su, a.L);
+                            } else {
+                                store_out(a.out, a.out_kind, orow[j] + r0 + rl, v0 * f[j] * sd);
+                                store_out(a.out, a.out_kind, orow[j] + r0 + 128 + rl, v1 * f[j] * sd);
+                            }
                         }
                     }
                 }
@@ -480,17 +508,17 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
     }
 }
 
-template <int MODE>
+template <int MODE, int ENT>
 int32_t launch_stream(const StreamArgs& sa, cudaStream_t st) {
     static std::atomic<bool> configured[64];   // per device; threads of different devices call concurrently
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int32_t) cudaErrorInvalidDevice;
     if (!configured[dev].load(std::memory_order_acquire)) {
-        const cudaError_t e = cudaFuncSetAttribute(nvf4_stream_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) kSmemF);
+        const cudaError_t e = cudaFuncSetAttribute(nvf4_stream_kernel<MODE, ENT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) FG<ENT>::kSmem);
         if (e != cudaSuccess) return (int32_t) e;
         configured[dev].store(true, std::memory_order_release);
     }
-    launch_k(nvf4_stream_kernel<MODE>, dim3((unsigned) sm_count()), dim3(kThreadsF), kSmemF, st, sa);
+    launch_k(nvf4_stream_kernel<MODE, ENT>, dim3((unsigned) sm_count()), dim3(kThreadsF), FG<ENT>::kSmem, st, sa);
     return launch_status();
 }
 
@@ -562,20 +590,25 @@ int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_
     sa.n_items = n_items;
     sa.status = status;
     int32_t rc = BSX_OK;
+    // Passes of 16 entries where the groups are deep: the capacities say how many entries a group gets on average (an expert-parallel
+    // rank sees every rank's tokens on its share of the experts).  A pass list that came with the plan has passes of 8.
+    const bool wide = !pass_list_ready && a.cap_groups > 0 && cap >= 12 * a.cap_groups;
+    const int pass_entries = wide ? kEntWide : kEntNarrow;
     if (phase != 2) {
-        if (x_images_ready && !pass_list_ready) launch_k(prep_fp4_kernel<false, 32>, dim3(1), dim3(256), 0, st, a, xcodes, xsf, xinv, items, n_items);   // the pass list alone
-        else if (!x_images_ready) launch_prep<false>(a, x_rows, H, xcodes, xsf, xinv, items, n_items, st);
+        if (x_images_ready && !pass_list_ready)
+            launch_k(prep_fp4_kernel<false, 32>, dim3(1), dim3(256), 0, st, a, xcodes, xsf, xinv, items, n_items, pass_entries);   // the pass list alone
+        else if (!x_images_ready) launch_prep<false>(a, x_rows, H, xcodes, xsf, xinv, items, n_items, pass_entries, st);
         sa.codes = xcodes;
         sa.sfs = xsf;
         sa.inv = xinv;
-        rc = launch_stream<FMODE_GU>(sa, st);
+        rc = wide ? launch_stream<FMODE_GU, kEntWide>(sa, st) : launch_stream<FMODE_GU, kEntNarrow>(sa, st);
     }
     if (rc != BSX_OK || phase == 1) return rc;
-    launch_prep<true>(a, cap, I, hcodes, hsf, hinv, items, n_items, st);
+    launch_prep<true>(a, cap, I, hcodes, hsf, hinv, items, n_items, pass_entries, st);
     sa.codes = hcodes;
     sa.sfs = hsf;
     sa.inv = hinv;
-    return launch_stream<FMODE_DOWN>(sa, st);
+    return wide ? launch_stream<FMODE_DOWN, kEntWide>(sa, st) : launch_stream<FMODE_DOWN, kEntNarrow>(sa, st);
 }
 
 }  // namespace bsx

@@ -642,8 +642,9 @@ extern "C" int32_t bsx_router_select(const float* logits, const float* bias, int
         if ((int64_t) topk_group * (E / n_group) < k) return BSX_E_GEOMETRY;
         HeldTabs held;
         if (!make_held(held_tabs, n_held, held)) return BSX_E_POINTER;
-        const unsigned blocks = (unsigned) ((T + 7) / 8);
-#define BSX_SEL(R) launch_k(router_select_kernel<R>, dim3(blocks), dim3(256), 0, st, logits, bias, (int64_t) T, E, k, weight_scale, gate_kind, n_group, topk_group, prior, held, ids, weights)
+        // decode windows: two tokens a block, so the window's selections spread over the SMs instead of queueing on a few
+        const unsigned wpb = T <= 256 ? 2u : 8u, blocks = (unsigned) ((T + wpb - 1) / wpb);
+#define BSX_SEL(R) launch_k(router_select_kernel<R>, dim3(blocks), dim3(32 * wpb), 0, st, logits, bias, (int64_t) T, E, k, weight_scale, gate_kind, n_group, topk_group, prior, held, ids, weights)
         switch (E >> 5) {
             case 2: BSX_SEL(2); break;
             case 4: BSX_SEL(4); break;
@@ -702,7 +703,7 @@ int32_t moe_plan_with_passes(const int32_t* ids, int32_t T, int32_t k, int32_t E
                              unsigned long long* ptr, int32_t* start, int32_t* n_groups, int32_t* dst, int32_t* tok, PassRec* items, int* n_items,
                              cudaStream_t st);
 
-constexpr int kRoutePlanMaxTokens = 64;
+constexpr int kRoutePlanMaxTokens = 16;
 
 // selection + plan (+ the packed kernels' pass list when items is given); BSX_E_TYPE: a gate kind the fused kernel does not cover
 int32_t route_plan_launch(const float* logits, const float* bias, int32_t T, int32_t E, int32_t k, int32_t gate_kind, float weight_scale,
@@ -724,9 +725,9 @@ int32_t route_plan_launch(const float* logits, const float* bias, int32_t T, int
         if ((int64_t) topk_group * (E / n_group) < k) return BSX_E_GEOMETRY;
     }
     if (T > kRoutePlanMaxTokens) {
-        // The fused block has 32 warps and a warp's selection is one dependent chain, so its warps take the window's tokens in turn:
-        // up to two rounds that is still cheaper than a launch.  Wider windows keep the selection spread over blocks and fuse only
-        // plan + pass list.
+        // The fused kernel is one block on one SM, and a token's selection is ~2500 warp instructions: with 32 warps at it the SM's
+        // four schedulers are the limit (measured: 64 tokens in the one block 31 us, against 16.5 us for selection spread over
+        // blocks followed by the plan kernel).  Wider windows keep the selection spread over blocks and fuse only plan + pass list.
         const int32_t rc = bsx_router_select(logits, bias, T, E, k, gate_kind, weight_scale, n_group, topk_group, 0.f, nullptr, 0, ids, weights, (void*) st);
         if (rc != BSX_OK) return rc;
         return moe_plan_with_passes(ids, T, k, E, blob_table, shared_blob, ptr, start, n_groups, dst, tok, items, n_items, st);

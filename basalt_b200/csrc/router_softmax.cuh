@@ -95,14 +95,15 @@ __global__ void __launch_bounds__(256) BSX_SOFTMAX_KERNEL(const float* __restric
 }
 
 static inline int32_t BSX_SOFTMAX_LAUNCH(const float* logits, int64_t T, int E, int k, int32_t* ids, float* w, cudaStream_t st) {
-    const unsigned blocks = (unsigned) ((T + 7) / 8);
+    // decode windows: two tokens a block, so the window's selections spread over the SMs instead of queueing on a few
+    const unsigned wpb = T <= 256 ? 2u : 8u, blocks = (unsigned) ((T + wpb - 1) / wpb);
     switch (E >> 5) {
-        case 2: launch_k(BSX_SOFTMAX_KERNEL<2>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
-        case 4: launch_k(BSX_SOFTMAX_KERNEL<4>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
-        case 8: launch_k(BSX_SOFTMAX_KERNEL<8>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
-        case 12: launch_k(BSX_SOFTMAX_KERNEL<12>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
-        case 16: launch_k(BSX_SOFTMAX_KERNEL<16>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
-        default: launch_k(BSX_SOFTMAX_KERNEL<0>, dim3(blocks), dim3(256), 0, st, logits, ids, w, T, E, k); break;
+        case 2: launch_k(BSX_SOFTMAX_KERNEL<2>, dim3(blocks), dim3(32 * wpb), 0, st, logits, ids, w, T, E, k); break;
+        case 4: launch_k(BSX_SOFTMAX_KERNEL<4>, dim3(blocks), dim3(32 * wpb), 0, st, logits, ids, w, T, E, k); break;
+        case 8: launch_k(BSX_SOFTMAX_KERNEL<8>, dim3(blocks), dim3(32 * wpb), 0, st, logits, ids, w, T, E, k); break;
+        case 12: launch_k(BSX_SOFTMAX_KERNEL<12>, dim3(blocks), dim3(32 * wpb), 0, st, logits, ids, w, T, E, k); break;
+        case 16: launch_k(BSX_SOFTMAX_KERNEL<16>, dim3(blocks), dim3(32 * wpb), 0, st, logits, ids, w, T, E, k); break;
+        default: launch_k(BSX_SOFTMAX_KERNEL<0>, dim3(blocks), dim3(32 * wpb), 0, st, logits, ids, w, T, E, k); break;
     }
     return launch_status();
 }

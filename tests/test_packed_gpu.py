@@ -114,6 +114,36 @@ def test_packed_activation_output_and_swiglu_kinds(lib, cuda, kind):
         at += len(toks)
 
 
+@pytest.mark.parametrize("H,I,sizes", [(2048, 512, [37, 16, 1, 52]), (1024, 1024, [33, 47])])
+def test_packed_deep_groups_take_the_wide_passes(lib, cuda, H, I, sizes):
+    """Groups of tens of entries (what an expert-parallel rank sees): with 12+ entries a group on average the call takes passes of
+    16 entries (MMA N = 64).  Every row against the dequantised reference, and against the same rows computed with shallow groups
+    (passes of 8): the two widths sum the same products, so they agree to fp32 rounding."""
+    rng = np.random.default_rng(H + I + len(sizes))
+    E, T = len(sizes), 40
+    Lo, blobs = make_expert_blobs(rng, E, 40, 40, H, I)
+    L = moe.native_expert_layout(40, 40, H, I)
+    packed = moe.pack_experts(L, dev(stack_blobs(blobs)))
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda().bfloat16()
+    x_eff = xd.float().cpu().numpy()
+    group_tokens = [rng.integers(0, T, n).tolist() for n in sizes]
+    assert sum(sizes) >= 12 * E
+    out = run_packed(L, packed, list(range(E)), group_tokens, xd, n_x_rows=T)
+    at = 0
+    for e, toks in enumerate(group_tokens):
+        want = O.expert_forward(Lo, blobs[e], x_eff[toks])
+        for r in range(len(toks)):
+            assert rel_l2(out[at + r], want[r]) < TOL, (e, r, rel_l2(out[at + r], want[r]))
+        # the same entries as groups of at most 5 (capacity below 12 a group: passes of 8)
+        for lo in range(0, len(toks), 5):
+            part = toks[lo:lo + 5]
+            narrow = run_packed(L, packed, [e] * 2, [part, []], xd, n_x_rows=T)
+            assert rel_l2(narrow[:len(part)], out[at + lo:at + lo + len(part)]) < 1e-6
+        at += len(toks)
+    del packed
+
+
 def test_packed_call_with_no_groups_returns_cleanly(lib, cuda):
     """A plan without groups (every expert held elsewhere): the kernels start, find no work and return; nothing is written."""
     rng = np.random.default_rng(97)
