@@ -124,8 +124,13 @@ __global__ void __launch_bounds__(256) pack_kernel(const uint8_t* __restrict__ i
 template <bool FROM_H, int TPR>
 __global__ void __launch_bounds__(256) prep_fp4_kernel(ExpertArgs a, uint8_t* __restrict__ codes, uint8_t* __restrict__ sfs, float* __restrict__ inv,
                                                         PassRec* __restrict__ items, int* __restrict__ n_items, int pass_entries) {
+    // pass_entries = 0: the pass list exists already (and a kernel launched after this one may be reading it): leave it alone
+    if (pass_entries == 0 && blockIdx.x == gridDim.x - 1) return;
+    // The kernel after the h images is the down stage, whose weight loader may run ahead (it reads constants): letting it be
+    // scheduled before this kernel's own wait means its blocks start on each SM as the gate/up stage's block there exits.
+    if (FROM_H) pdl_launch_dependents();
     pdl_wait();
-    pdl_launch_dependents();
+    if (!FROM_H) pdl_launch_dependents();
     const int ng = min(*a.n_groups, (int) a.cap_groups);
     const int total = min(a.grp_start[ng], (int) a.cap_entries);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -217,6 +222,7 @@ struct StreamArgs {
     const PassRec* items;
     const int* n_items;
     int32_t* status;
+    int early_weights;        // the pass list was complete before the kernel ahead of this one started: the weight loader need not wait
 };
 
 __device__ __forceinline__ uint64_t sf_desc(uint32_t addr) {   // 32 rows x 16 bytes, 8-row groups 128 bytes apart, no swizzle
@@ -271,8 +277,10 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
     // barriers and tensor memory are set up; from here on the kernel reads what the kernels before it wrote (the pass list,
-    // the activation images), so a programmatic launch waits here for them to finish
-    pdl_wait();
+    // the activation images), so a programmatic launch waits here for them to finish.  Except the weight loader of the down
+    // stage: the pass list it follows was written before the gate/up stage ran and the blobs are constants, so it fills the
+    // stages while the SwiGLU rows' images are still being made - the stream is in flight when the first image arrives.
+    if (!(sa.early_weights && warp == 1)) pdl_wait();
     pdl_launch_dependents();
     const int n_units = sa.n_items[0] * n_upp;
 
@@ -589,6 +597,7 @@ int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_
     sa.items = items;
     sa.n_items = n_items;
     sa.status = status;
+    sa.early_weights = 0;
     int32_t rc = BSX_OK;
     // Passes of 16 entries where the groups are deep: the capacities say how many entries a group gets on average (an expert-parallel
     // rank sees every rank's tokens on its share of the experts).  A pass list that came with the plan has passes of 8.
@@ -604,10 +613,11 @@ int32_t experts_grouped_packed(const ExpertArgs& a, int32_t* status, cudaStream_
         rc = wide ? launch_stream<FMODE_GU, kEntWide>(sa, st) : launch_stream<FMODE_GU, kEntNarrow>(sa, st);
     }
     if (rc != BSX_OK || phase == 1) return rc;
-    launch_prep<true>(a, cap, I, hcodes, hsf, hinv, items, n_items, pass_entries, st);
+    launch_prep<true>(a, cap, I, hcodes, hsf, hinv, items, n_items, 0, st);   // the pass list is the gate/up stage's
     sa.codes = hcodes;
     sa.sfs = hsf;
     sa.inv = hinv;
+    sa.early_weights = 1;
     return wide ? launch_stream<FMODE_DOWN, kEntWide>(sa, st) : launch_stream<FMODE_DOWN, kEntNarrow>(sa, st);
 }
 
