@@ -544,6 +544,9 @@ def run_decode_codebook(args, dev, sh, steps=None, warmup=None, copies=None):
     L = moe.native_expert_layout(rt, rt, H, I)
     Ls = moe.native_expert_layout(st_, st_, H, I)
     assert L.bytes == rb and Ls.bytes == sb
+    if getattr(args, "plain_experts", False):      # the warp-per-row kernels instead (what every format without a tensor-core kernel runs)
+        L.options |= capi.EXPERT_PLAIN
+        Ls.options |= capi.EXPERT_PLAIN
     rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=sh["scale"], gate=capi.GATE_SIGMOID, n_group=sh["n_group"],
                            topk_group=sh["topk_group"])
     layers = [moe.NativeMoELayer(gate, bias, blobs if c == 0 else blobs.clone(), L, rargs, shared_blob=(shared if c == 0 else shared.clone())[0],
@@ -586,7 +589,8 @@ def run_decode_codebook(args, dev, sh, steps=None, warmup=None, copies=None):
         "config": dict(workload=f"{sh['name']} decode, {T} tokens/step", hidden=H, n_expert=E, n_shared=1, intermediate=I, top_k=K_TOP, router=sh["router"],
                        expert_format="IQ1_M routed (56 B / 256 values), Q6_K shared (210 B / 256 values)", activations="bf16", tokens_per_step=T,
                        l2_policy=f"weights cycle through {copies} layer copies; a step touches {bytes_step / 1e9:.2f} GB: larger than L2", parallelism="single GPU",
-                       expert_kernels="ggml blobs in place, integer tensor-core kernels (experts_kq.cu)"),
+                       expert_kernels=("ggml blobs in place, warp-per-row fp32 kernels (experts_simple.cu)" if getattr(args, "plain_experts", False)
+                                       else "ggml blobs in place, integer tensor-core kernels (experts_kq.cu)")),
         "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 4},
         "gpu_launches": 11 * steps,   # logits, selection + plan, 2 x (images, product) routed, shared plan, 2 x (images, product) shared... combine
         "roofline": {"bound": "hbm", "kernel": "whole step (kq_mma_kernel<IQ1_M> gate/up and down dominate)", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s",
@@ -911,6 +915,7 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: 64 tokens a step (the default line); prefill: --tokens rows a step, Zipf(1.1) expert popularity, tcgen05 grouped experts")
     ap.add_argument("--tokens", type=int, default=4096, help="rows per step of the prefill workload, per GPU (4096 or 16384 in the reference's configs)")
+    ap.add_argument("--plain-experts", action="store_true", help="with --shape c4: the warp-per-row kernels instead of the integer tensor-core ones")
     ap.add_argument("--shape", default="c1", choices=sorted(SHAPES), help="layer: c1 (H 2048, 512 experts), c3 (H 7168, 256 experts), c4 (c3 with IQ1_M / Q6_K blobs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
