@@ -264,16 +264,16 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
             }
             return it;
         };
-        auto load_idx = [&](const TileRec& r, int (&idx)[12]) {   // image rows of this lane's 8 code rows and its 4 scale rows
+        auto load_idx = [&](const TileRec& r, int (&idx)[9]) {   // image rows of this lane's 8 code rows and its scale row
 #pragma unroll
-            for (int i = 0; i < 12; ++i) {
-                const int rw = i < 8 ? r16 + 16 * i : (tl & 31) + 32 * (i - 8);
+            for (int i = 0; i < 9; ++i) {
+                const int rw = i < 8 ? r16 + 16 * i : tl;
                 const int rr = rw < r.rows ? rw : 0;
                 idx[i] = MODE == QMODE_GU ? a.src[r.row0 + rr] : r.row0 + rr;
             }
         };
         TileRec rec0, rec1, rec2;
-        int idx0[12], idx1[12];
+        int idx0[9], idx1[9];
         int item = next_valid(blockIdx.x, rec0);
         int item1 = item < n_items ? next_valid(item + gridDim.x, rec1) : n_items;
         if (item < n_items) load_idx(rec0, idx0);
@@ -295,13 +295,8 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
                 crow[i] = a.codes + (size_t) idx0[i] * kTermsF * (size_t) (K >> 1) + c8 * 16;
                 cdst[i] = (uint32_t) ((r >> 3) * 1024 + (r & 7) * 128 + ((c8 ^ (r & 7)) << 4));
             }
-            // Scale words.  Slot (m % 32, m / 32) of a K-step's 512-byte block holds tile row m's word, so the four rows lane, lane + 32,
-            // lane + 64, lane + 96 share one 16-byte slot: a thread fetches those four rows' words of ONE K-step (its warp's number)
-            // and places them with a single 16-byte store - consecutive lanes, consecutive slots, no bank conflict.
-            const uint8_t* srow[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) srow[j] = a.sfs + (size_t) idx0[8 + j] * kTermsF * (size_t) (K >> 4) + (size_t) (tl >> 5) * 4;
-            const uint32_t sdst = (uint32_t) (G::kOffSFA + (tl >> 5) * 512 + (tl & 31) * 16);
+            const uint8_t* srow = a.sfs + (size_t) idx0[8] * kTermsF * (size_t) (K >> 4);
+            const uint32_t sdst = (uint32_t) (G::kOffSFA + (tl & 31) * 16 + (tl >> 5) * 4);
             for (int c = 0; c < n_chunk; ++c) {
                 // hand over what is already on its way before blocking on the next slot (it frees only when the tensor core has
                 // consumed the stage before this one)
@@ -322,16 +317,18 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
                                      "l"(crow[i] + (size_t) t * (size_t) (K >> 1) + (size_t) c * 128)
                                      : "memory");
                 }
-                uint32_t sv[kTermsF][4];
+                // this row's scale words: 16 bytes a term (the chunk's four K-steps) through registers, then one word into slot
+                // (m % 32, m / 32) of each step's block (four rows share a 16-byte slot, so no 16-byte copy can place them)
+                uint4 sv[kTermsF];
 #pragma unroll
-                for (int t = 0; t < kTermsF; ++t)
+                for (int t = 0; t < kTermsF; ++t) sv[t] = *reinterpret_cast<const uint4*>(srow + (size_t) t * (size_t) (K >> 4) + (size_t) c * 16);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) sv[t][j] = *reinterpret_cast<const uint32_t*>(srow[j] + (size_t) t * (size_t) (K >> 4) + (size_t) c * 16);
+                for (int t = 0; t < kTermsF; ++t) {
+                    const uint32_t w[4] = {sv[t].x, sv[t].y, sv[t].z, sv[t].w};
 #pragma unroll
-                for (int t = 0; t < kTermsF; ++t)
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(st + sdst + (uint32_t) (t * kSFQ)), "r"(sv[t][0]), "r"(sv[t][1]), "r"(sv[t][2]),
-                                 "r"(sv[t][3])
-                                 : "memory");
+                    for (int k = 0; k < 4; ++k)
+                        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(st + sdst + (uint32_t) (t * kSFQ + k * 512)), "r"(w[k]) : "memory");
+                }
                 asm volatile("cp.async.commit_group;\n" ::: "memory");
                 ++issued;
             }
@@ -341,7 +338,7 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
             rec0 = rec1;
             rec1 = rec2;
 #pragma unroll
-            for (int i = 0; i < 12; ++i) idx0[i] = idx1[i];
+            for (int i = 0; i < 9; ++i) idx0[i] = idx1[i];
             if (item1 < n_items) load_idx(rec1, idx1);
         }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -551,7 +548,7 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_down_resident_kernel(Pre
         // ---- the tile's rows (images of dispatch rows row0 ..): codes by 16-byte cp.async, scale words through registers
         const int tl = threadIdx.x - 64;
         const int c8 = tl & 7, r16 = tl >> 3;
-        const uint32_t sdst = sbase + (uint32_t) (G::kOffSFA + (tl >> 5) * 512 + (tl & 31) * 16);
+        const uint32_t sdst = sbase + (uint32_t) (G::kOffSFA + (tl & 31) * 16 + (tl >> 5) * 4);
         uint32_t ti = 0;
         TileRec rec, nrec;
         int tile = blockIdx.x;
@@ -583,24 +580,17 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_down_resident_kernel(Pre
             }
             asm volatile("cp.async.commit_group;\n" ::: "memory");
             {
-                // the four rows lane, lane + 32, lane + 64, lane + 96 share a 16-byte slot of a K-step's block: this thread places
-                // their words of K-step (its warp's number) with one 16-byte store
-                const uint8_t* srow[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int m = (tl & 31) + 32 * j;
-                    srow[j] = a.sfs + (size_t) (rec.row0 + (m < rec.rows ? m : 0)) * kTermsF * (size_t) (K >> 4) + (size_t) (tl >> 5) * 4;
-                }
+                const int64_t ir = rec.row0 + (tl < rec.rows ? tl : 0);
+                const uint8_t* srow = a.sfs + (size_t) ir * kTermsF * (size_t) (K >> 4);
 #pragma unroll
                 for (int c = 0; c < KC; ++c)
 #pragma unroll
                     for (int t = 0; t < kTermsF; ++t) {
-                        uint32_t w[4];
+                        const uint4 sv = *reinterpret_cast<const uint4*>(srow + (size_t) t * (size_t) (K >> 4) + (size_t) c * 16);
+                        const uint32_t w[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) w[j] = *reinterpret_cast<const uint32_t*>(srow[j] + (size_t) t * (size_t) (K >> 4) + (size_t) c * 16);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(sdst + (uint32_t) (((c * kTermsF + t) * 4) * 512)), "r"(w[0]), "r"(w[1]),
-                                     "r"(w[2]), "r"(w[3])
-                                     : "memory");
+                        for (int k = 0; k < 4; ++k)
+                            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(sdst + (uint32_t) (((c * kTermsF + t) * 4 + k) * 512)), "r"(w[k]) : "memory");
                     }
             }
             asm volatile("cp.async.wait_group 0;\n" ::: "memory");
