@@ -16,7 +16,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "libbasalt_b200.so"
 OBJ = PKG / "lib" / "obj"
 
-SOURCES = ["router.cu", "router_fast.cu", "dispatch.cu", "experts.cu", "experts_simple.cu", "experts_mma.cu", "experts_kq.cu", "experts_prefill.cu", "router_prefill.cu", "experts_nvf4.cu", "experts_prefill_nvf4.cu", "layout_file.cu", "norm_pack.cu", "layer.cu", "prefill_group.cu"]
+SOURCES = ["router.cu", "router_fast.cu", "dispatch.cu", "experts.cu", "experts_simple.cu", "experts_mma.cu", "experts_kq.cu", "experts_prefill.cu", "router_prefill.cu", "experts_nvf4.cu", "experts_prefill_nvf4.cu", "layout_file.cu", "norm_pack.cu", "layer.cu", "prefill_group.cu", "ep_layer.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 EXTRA = {"router_fast.cu": ["--use_fast_math"]}
@@ -51,7 +51,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         list(ex.map(run, jobs))
     objs = [OBJ / (s + ".o") for s in SOURCES]
     if force or jobs or _stale(LIB, objs):
-        run([nvcc, "-shared", "-o", str(LIB)] + [str(o) for o in objs] + ["-lcudart"])
+        run([nvcc, "-shared", "-o", str(LIB)] + [str(o) for o in objs] + ["-lcudart", "-ldl"])
     return LIB
 
 

@@ -11,7 +11,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / "lib" / "libbasalt_b200.so"
 
-OK, E_GEOMETRY, E_STREAM, E_TYPE, E_POINTER, E_LIMIT = 0, -1, -2, -3, -4, -5
+OK, E_GEOMETRY, E_STREAM, E_TYPE, E_POINTER, E_LIMIT, E_UNAVAILABLE = 0, -1, -2, -3, -4, -5, -6
 GATE_SQRT_SOFTPLUS, GATE_SIGMOID, GATE_SOFTMAX, GATE_SOFTMAX_FAST, GATE_SOFTMAX_F64 = 0, 1, 2, 3, 4
 TYPE_Q6_K, TYPE_IQ1_M, TYPE_NVFP4 = 14, 29, 40
 X_F32, X_BF16, X_Q8_1 = 0, 1, 2
@@ -44,6 +44,14 @@ class MoELayerDesc(C.Structure):
                 ("gate", C.c_void_p), ("bias", C.c_void_p), ("blob_table", C.c_void_p), ("shared_blob", C.c_uint64), ("norm_w", C.c_void_p)]
 
 
+class EPLayerDesc(C.Structure):
+    _fields_ = [("layout", ExpertLayout),
+                ("n_expert", C.c_int32), ("top_k", C.c_int32), ("gate_kind", C.c_int32), ("n_group", C.c_int32), ("topk_group", C.c_int32),
+                ("packed", C.c_int32), ("e_lo", C.c_int32), ("n_local", C.c_int32), ("n_replicas", C.c_int32), ("reserved", C.c_int32),
+                ("weight_scale", C.c_float), ("reserved_f", C.c_float),
+                ("gate", C.c_void_p), ("bias", C.c_void_p), ("blob_table", C.c_void_p), ("shared_blob", C.c_uint64), ("replicated", C.c_void_p)]
+
+
 class MoELayerViews(C.Structure):
     _fields_ = [("logits", C.c_void_p), ("ids", C.c_void_p), ("weights", C.c_void_p), ("n_groups", C.c_void_p), ("grp_start", C.c_void_p),
                 ("ent_dst", C.c_void_p), ("ent_tok", C.c_void_p), ("rows", C.c_void_p)]
@@ -57,6 +65,10 @@ _SIGNATURES = {
     "bsx_experts_prefill_group": (C.c_int32, [C.POINTER(ExpertLayout), P, C.c_int32, P, P, C.c_int64, P, C.c_int32, C.c_int64, P, P, P, P]),
     "bsx_unit_offsets": (C.c_int32, [P, C.c_int32, C.c_int32, P, P]),
     "bsx_rebase_bounds": (C.c_int32, [P, C.c_int32, P, P]),
+    "bsx_ep_available": (C.c_int32, []),
+    "bsx_ep_layer_workspace_bytes": (C.c_size_t, [P, C.c_int32, C.c_int32]),
+    "bsx_ep_layer_views": (C.c_int32, [P, C.c_int32, C.c_int32, P, P]),
+    "bsx_ep_layer": (C.c_int32, [P, P, P, C.c_int32, C.c_int32, P, P, P, P, P, P, P]),
     "bsx_ep_plan": (C.c_int32, [P, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, C.c_uint64, C.c_int32, C.c_int32, P, P, P, P, P, P, P]),
     "bsx_combine_partial_ep": (C.c_int32, [P, P, P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, P, C.c_int32, C.c_int32, P, P, P]),
     "bsx_combine_residual": (C.c_int32, [P, P, P, P, P, P, C.c_int32, C.c_int32, C.c_int32, P, P]),
@@ -140,7 +152,7 @@ def exported_symbols():
 class BsxError(RuntimeError):
     def __init__(self, fn: str, code: int):
         names = {-1: "unsupported geometry", -2: "null stream", -3: "unsupported block format", -4: "bad pointer",
-                 -5: "size beyond a fixed limit"}
+                 -5: "size beyond a fixed limit", -6: "no NCCL library in the process, or NCCL refused the call"}
         super().__init__(f"{fn}: " + (names.get(code, f"CUDA error {code}") if code < 0 else f"CUDA error {code}"))
         self.code = code
 

@@ -342,6 +342,135 @@ class EPMoELayer:
         return self.y
 
 
+class NcclComm:
+    """An NCCL communicator of this process's own, made through NCCL's C API with ctypes (ncclGetUniqueId on rank 0, the id
+    broadcast over the existing torch.distributed group, ncclCommInitRank everywhere): what a C++ host would hand to
+    bsx_ep_layer.  torch keeps its own communicators private, so the layer behind the C ABI gets this one.  The library is the
+    libnccl the process has already loaded (torch's), found by its soname - the same one bsx_ep_layer resolves."""
+
+    def __init__(self, group=None):
+        import torch
+        import torch.distributed as dist
+        self.lib = C.CDLL("libnccl.so.2", mode=C.RTLD_GLOBAL)
+        self.lib.ncclGetUniqueId.argtypes = [C.c_void_p]
+        self.lib.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_char * 128, C.c_int]
+        self.lib.ncclCommDestroy.argtypes = [C.c_void_p]
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        uid = (C.c_char * 128)()
+        if rank == 0:
+            rc = self.lib.ncclGetUniqueId(C.byref(uid))
+            assert rc == 0, f"ncclGetUniqueId: {rc}"
+        # the id travels as a byte tensor on the group's own backend (a CUDA tensor for nccl, a CPU tensor for gloo)
+        on_gpu = dist.get_backend(group) == "nccl"
+        t = torch.frombuffer(bytearray(bytes(uid)), dtype=torch.uint8).clone()
+        t = t.cuda() if on_gpu else t
+        dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        raw = bytes(t.cpu().numpy().tobytes())
+        uid = (C.c_char * 128).from_buffer_copy(raw)
+        self.handle = C.c_void_p()
+        rc = self.lib.ncclCommInitRank(C.byref(self.handle), world, uid, rank)
+        assert rc == 0, f"ncclCommInitRank: {rc}"
+        self.rank, self.world = rank, world
+
+    def destroy(self):
+        if self.handle:
+            self.lib.ncclCommDestroy(self.handle)
+            self.handle = C.c_void_p()
+
+
+class EPMoELayerNative:
+    """EPMoELayer's step as ONE call behind the C ABI (bsx_ep_layer): the collectives are issued by the library on an NCCL
+    communicator the caller owns, so a C or C++ host gets the expert-parallel layer without this module.  Same arguments,
+    same buffers' meaning, same result as EPMoELayer (bit for bit: the same kernels and the same collectives in the same order)."""
+
+    DATA_PLANE = EPMoELayer.DATA_PLANE + "; the whole step is one C ABI call (bsx_ep_layer) on the caller's ncclComm_t"
+    LAUNCHES = EPMoELayer.LAUNCHES
+
+    def __init__(self, gate_w, bias, blobs, layout, args, n_expert_total: int, comm: NcclComm, shared_blob=None, max_tokens: int = 64,
+                 packed: bool = False, replicas=None):
+        import torch
+        from . import capi, moe
+        self.torch, self.moe, self.capi, self.comm = torch, moe, capi, comm
+        assert capi.lib().bsx_ep_available() == 1, "no NCCL library in the process"
+        self.rank, self.world = comm.rank, comm.world
+        first = ep_partition(n_expert_total, self.world)
+        self.lo, self.hi = int(first[self.rank]), int(first[self.rank + 1])
+        self.gate_w, self.bias, self.blobs, self.shared_blob = gate_w, bias, blobs, shared_blob
+        dev = blobs.device
+        self.dev, self.L, self.args, self.E, self.max_tokens = dev, layout, args, n_expert_total, max_tokens
+        El, stride = blobs.shape
+        assert El == self.hi - self.lo
+        table = np.zeros(n_expert_total, np.int64)
+        table[self.lo:self.hi] = blobs.data_ptr() + np.arange(El, dtype=np.int64) * stride
+        self.replicas, self.replicated = replicas or {}, None
+        if self.replicas:
+            mask = np.zeros(n_expert_total, np.uint8)
+            for e, blob in self.replicas.items():
+                table[e] = blob.data_ptr()
+                mask[e] = 1
+            self.replicated = torch.from_numpy(mask).to(dev)
+        self.blob_table = torch.from_numpy(table).to(dev)
+        d = capi.EPLayerDesc()
+        d.layout = layout
+        d.n_expert, d.top_k, d.gate_kind = n_expert_total, args.k, args.gate
+        d.n_group, d.topk_group, d.packed = args.n_group, args.topk_group, 1 if packed else 0
+        d.e_lo, d.n_local, d.n_replicas = self.lo, El, len(self.replicas)
+        d.weight_scale = args.weight_scale
+        d.gate, d.bias = gate_w.data_ptr(), (bias.data_ptr() if bias is not None else None)
+        d.blob_table = self.blob_table.data_ptr()
+        d.shared_blob = shared_blob.data_ptr() if shared_blob is not None else 0
+        d.replicated = self.replicated.data_ptr() if self.replicated is not None else None
+        self.desc = d
+        lib = capi.lib()
+        nbytes = lib.bsx_ep_layer_workspace_bytes(C.byref(d), max_tokens, self.world)
+        assert nbytes > 0, "bsx_ep_layer_workspace_bytes refused the layer"
+        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.y = torch.empty((max_tokens, layout.n_embd), dtype=torch.float32, device=dev)
+        self.side = torch.cuda.Stream(device=dev)
+        self.ev_fork, self.ev_join = torch.cuda.Event(), torch.cuda.Event()
+        # the events must exist as CUDA objects before their handles are passed on
+        self.ev_fork.record(torch.cuda.current_stream())
+        self.ev_join.record(torch.cuda.current_stream())
+        self.graph = None
+
+    def check_status(self):
+        """Raises moe.KernelWaitTimeout if a kernel of a step since the last check gave up on a bounded wait; clears the word."""
+        self.moe.read_status(self.status, "EPMoELayerNative")
+
+    def forward(self, x):
+        torch, capi, moe = self.torch, self.capi, self.moe
+        assert x.shape[0] == self.max_tokens, "the collective form exchanges fixed-size buffers: pass max_tokens rows"
+        cur = torch.cuda.current_stream()
+        kind = capi.X_BF16 if x.dtype == torch.bfloat16 else capi.X_F32
+        capi.check("bsx_ep_layer", capi.lib().bsx_ep_layer(C.byref(self.desc), self.comm.handle, x.data_ptr(), kind, x.shape[0], self.workspace.data_ptr(),
+                                                           self.y.data_ptr(), self.status.data_ptr(), moe._stream(cur), self.side.cuda_stream,
+                                                           self.ev_fork.cuda_event, self.ev_join.cuda_event))
+        return self.y
+
+    def capture(self, x_example):
+        """Records forward() into a CUDA graph (NCCL's kernels included).  Every rank must capture, and replay, in step."""
+        torch = self.torch
+        self.x_static = torch.zeros((self.max_tokens, self.L.n_embd), dtype=x_example.dtype, device=self.dev)
+        warm = torch.cuda.Stream(device=self.dev)
+        warm.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(warm):
+            for _ in range(3):
+                self.forward(self.x_static)
+        torch.cuda.current_stream().wait_stream(warm)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            self.forward(self.x_static)
+        return self
+
+    def forward_graphed(self, x=None):
+        if x is not None:
+            self.x_static.copy_(x, non_blocking=True)
+        self.graph.replay()
+        return self.y
+
+
 class EPPrefillMoELayer:
     """The expert-parallel layer for prompt-sized batches, collective form: every rank routes its own T tokens (tensor-core
     gate product + selection), all-gathers activations and routing, dispatches all pairs, runs bsx_experts_prefill over the

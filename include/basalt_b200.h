@@ -37,7 +37,8 @@ enum {
     BSX_E_STREAM = -2,     /* null stream where the reference forbids it */
     BSX_E_TYPE = -3,       /* block format not supported */
     BSX_E_POINTER = -4,    /* null or misaligned pointer */
-    BSX_E_LIMIT = -5       /* a size beyond a documented fixed maximum */
+    BSX_E_LIMIT = -5,      /* a size beyond a documented fixed maximum */
+    BSX_E_UNAVAILABLE = -6 /* the expert-parallel entries only: no NCCL library in the process, or NCCL refused the call */
 };
 
 /* gate functions of bsx_router_select */
@@ -396,6 +397,35 @@ BSX_API int32_t bsx_ep_plan(const int32_t* ids, int64_t n_pairs, int32_t k, int3
 BSX_API int32_t bsx_combine_partial_ep(const float* rows, const float* weights, const int32_t* ids, int32_t tokens_per_block, int32_t block_stride,
                                        int32_t e_lo, int32_t e_hi, int32_t T, int32_t k, int32_t H, const float* shared, int32_t tok_lo, int32_t tok_n,
                                        const uint8_t* replicated, float* y, void* stream);
+
+/* The whole decode-window step of an expert-parallel layer in one call, on the caller's NCCL communicator (one process per GPU;
+ * no counterpart in the reference, see above).  Rank r of the communicator holds the layer's experts e_lo .. e_lo + n_local - 1
+ * (blob_table[e] != 0 for those, for the replicated ones and for nothing else), the router weights and the shared expert; every
+ * rank calls with the same n_tokens rows of its own.  Sequence: all-gather of the rows (on side_stream when given, beside the
+ * router; ev_fork / ev_join are two events of the caller's that order the two streams), router, all-gather of [ids | weights],
+ * bsx_ep_plan, grouped experts, bsx_combine_partial_ep, reduce-scatter.  y [n_tokens][n_embd] fp32: this rank's tokens, equal to
+ * bsx_moe_layer on one GPU holding every expert up to the order of the fp32 sum over the ranks.
+ * comm: an ncclComm_t.  NCCL is looked up at run time in the process (libnccl.so.2), never linked: bsx_ep_available() says
+ * whether it was found; without it the call returns BSX_E_UNAVAILABLE.  n_tokens is the same on every rank and on every call
+ * with one workspace (fixed-size collectives), world * n_tokens * top_k <= BSX_EP_PLAN_MAX_PAIRS.  Nothing is allocated or read
+ * back; the call can be captured into a CUDA graph (NCCL's kernels included).  No kernel waits on another rank: a rank that
+ * does not call shows up as NCCL's timeout on the host. */
+typedef struct bsx_ep_layer_desc {
+    bsx_expert_layout layout;
+    int32_t n_expert, top_k, gate_kind, n_group, topk_group, packed;
+    int32_t e_lo, n_local, n_replicas, reserved;
+    float weight_scale, reserved_f;
+    const float* gate;                     /* [n_expert][n_embd] fp32 */
+    const float* bias;                     /* [n_expert] fp32 or null */
+    const unsigned long long* blob_table;  /* [n_expert] device addresses; 0 = held by another rank */
+    unsigned long long shared_blob;        /* 0 = no shared expert */
+    const uint8_t* replicated;             /* [n_expert] device bytes, 1 = every rank holds a copy; or null */
+} bsx_ep_layer_desc;
+BSX_API int32_t bsx_ep_available(void);
+BSX_API size_t bsx_ep_layer_workspace_bytes(const bsx_ep_layer_desc* desc, int32_t n_tokens, int32_t world);
+BSX_API int32_t bsx_ep_layer_views(const bsx_ep_layer_desc* desc, int32_t n_tokens, int32_t world, void* workspace, bsx_moe_layer_views_t* views);
+BSX_API int32_t bsx_ep_layer(const bsx_ep_layer_desc* desc, void* comm, const void* x, int32_t x_kind, int32_t n_tokens, void* workspace, float* y,
+                             int32_t* status, void* stream, void* side_stream, void* ev_fork, void* ev_join);
 
 /* ---- the step before the layer: the RMS norm of the layer's input rows (weights w, any offset folded), as fp32 rows xn (what
  * the router reads) and / or bf16 rows act; either may be null, not both.  Replaces wgemm::norm_pack

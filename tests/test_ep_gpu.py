@@ -72,6 +72,25 @@ def _rank_body(rank, world, port, q):
     ypk = pk.forward(xf).clone()
     pk.capture(xf)
     ypg = pk.forward_graphed(xf).clone()
+    # the same step as one C ABI call on a communicator of the caller's own (bsx_ep_layer): the bits of the Python-driven form,
+    # in place and over packed blobs, launched and replayed as a graph; with replicated experts too
+    comm = ep.NcclComm()
+    nat = ep.EPMoELayerNative(gw, None, own, L, args, E, comm, shared_blob=bd[E], max_tokens=T)
+    yn = nat.forward(xf).clone()
+    assert torch.equal(yn.view(torch.int32), yc.view(torch.int32)), "bsx_ep_layer differs from the Python-driven collective form"
+    natp = ep.EPMoELayerNative(gw, None, mine[:El], L, args, E, comm, shared_blob=mine[El], max_tokens=T, packed=True)
+    ynp = natp.forward(xf).clone()
+    assert torch.equal(ynp.view(torch.int32), ypk.view(torch.int32)), "bsx_ep_layer (packed) differs from the Python-driven collective form"
+    natp.capture(xf)
+    yng = natp.forward_graphed(xf).clone()
+    assert torch.equal(yng.view(torch.int32), ypk.view(torch.int32)), "bsx_ep_layer graph replay differs from the launched step"
+    natp.check_status()
+    natr = ep.EPMoELayerNative(gw, None, own, L, args, E, comm, shared_blob=bd[E], max_tokens=T, replicas=reps)
+    ynr = natr.forward(xf).clone()
+    assert torch.equal(ynr.view(torch.int32), yr.view(torch.int32)), "bsx_ep_layer with replicated experts differs from the Python-driven form"
+    torch.cuda.synchronize()
+    natp.graph.reset()
+    del natp
     # the prompt-sized form (tensor-core experts): against the single-GPU prompt layer, and that layer against the decode one
     pre = ep.EPPrefillMoELayer(gw, None, own, L, args, E, shared_blob=bd[E], max_tokens=T)
     yp = pre.forward(xf).clone()
@@ -97,6 +116,7 @@ def _rank_body(rank, world, port, q):
     del pk
     dist.barrier()
     torch.cuda.synchronize()
+    comm.destroy()
     dist.destroy_process_group()
 
 
