@@ -298,9 +298,13 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
             const uint8_t* srow = a.sfs + (size_t) idx0[8] * kTermsF * (size_t) (K >> 4);
             const uint32_t sdst = (uint32_t) (G::kOffSFA + (tl & 31) * 16 + (tl >> 5) * 4);
             for (int c = 0; c < n_chunk; ++c) {
-                // The slot of stage `issued` frees when the tensor core has consumed stage issued - kStagesQ, which it can only start
-                // once that stage was handed over: the hand-over below keeps at most one stage of this thread's copies in flight, so
-                // that stage always has been.
+                // hand over what is already on its way before blocking on the next slot (it frees only when the tensor core has
+                // consumed the stage before this one)
+                if (issued > arrived) {
+                    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    for (; arrived < issued; ++arrived) mbar_arrive(&full[arrived % kStagesQ]);
+                }
                 const uint32_t s = issued % kStagesQ;
                 ok = mbar_wait(&empty[s], ((issued / kStagesQ) & 1u) ^ 1u);
                 if (!ok) break;
@@ -327,15 +331,6 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
                 }
                 asm volatile("cp.async.commit_group;\n" ::: "memory");
                 ++issued;
-                // Hand over the stage before the one just requested, which has had a whole issue round to land, and leave the new
-                // one in flight: two stages of gathered rows are on their way at any time (waiting for every copy before
-                // requesting the next stage would put the full load latency into every stage).
-                if (issued - arrived > 1) {
-                    asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                    mbar_arrive(&full[arrived % kStagesQ]);
-                    ++arrived;
-                }
             }
             // advance the pipeline: the next item's indices were requested one item ago; request those of the item after it
             item = item1;

@@ -342,6 +342,11 @@ class EPMoELayer:
         return self.y
 
 
+class _NcclUniqueId(C.Structure):
+    """ncclUniqueId: 128 opaque bytes, passed to ncclCommInitRank BY VALUE (a ctypes array would decay to a pointer)"""
+    _fields_ = [("internal", C.c_byte * 128)]
+
+
 class NcclComm:
     """An NCCL communicator of this process's own, made through NCCL's C API with ctypes (ncclGetUniqueId on rank 0, the id
     broadcast over the existing torch.distributed group, ncclCommInitRank everywhere): what a C++ host would hand to
@@ -352,11 +357,11 @@ class NcclComm:
         import torch
         import torch.distributed as dist
         self.lib = C.CDLL("libnccl.so.2", mode=C.RTLD_GLOBAL)
-        self.lib.ncclGetUniqueId.argtypes = [C.c_void_p]
-        self.lib.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_char * 128, C.c_int]
+        self.lib.ncclGetUniqueId.argtypes = [C.POINTER(_NcclUniqueId)]
+        self.lib.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, _NcclUniqueId, C.c_int]
         self.lib.ncclCommDestroy.argtypes = [C.c_void_p]
         rank, world = dist.get_rank(group), dist.get_world_size(group)
-        uid = (C.c_char * 128)()
+        uid = _NcclUniqueId()
         if rank == 0:
             rc = self.lib.ncclGetUniqueId(C.byref(uid))
             assert rc == 0, f"ncclGetUniqueId: {rc}"
@@ -365,8 +370,7 @@ class NcclComm:
         t = torch.frombuffer(bytearray(bytes(uid)), dtype=torch.uint8).clone()
         t = t.cuda() if on_gpu else t
         dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
-        raw = bytes(t.cpu().numpy().tobytes())
-        uid = (C.c_char * 128).from_buffer_copy(raw)
+        uid = _NcclUniqueId.from_buffer_copy(bytes(t.cpu().numpy().tobytes()))
         self.handle = C.c_void_p()
         rc = self.lib.ncclCommInitRank(C.byref(self.handle), world, uid, rank)
         assert rc == 0, f"ncclCommInitRank: {rc}"
