@@ -498,8 +498,9 @@ def decode_line(args, w, T, r, world=1):
                             "unit": "GB/s", "frac": achieved / pk["hbm"], "peak_source": pk["source"],
                             # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch of this workload at 64 tokens (seeded, so the same
                             # experts every run), from the ncu capture summarised in profiles/nvf4_stream_kernel_c1_t64.md; not measured by this run
-                            "traffic": ((450646784 if use_packed else 451744256) if (T == 64 and w.key == "c1") else None),
-                            "traffic_source": "ncu capture of nvf4_stream_kernel (profiles/nvf4_stream_kernel_c1_t64.md); the kernel's streaming loop is unchanged since",
+                            "traffic": ((450112000 if use_packed else 451744256) if (T == 64 and w.key == "c1") else None),
+                            "traffic_source": ("dram__bytes_read.sum + dram__bytes_write.sum of one launch, ncu capture of source revision b1578ff "
+                                               "(profiles/nvf4_stream_kernel_c1_t64.md); per launch on the same workload, not measured by this run"),
                             "algorithmic_bytes_per_launch": r["gu_bytes"], "kernel_ms": gu_ms, "frac_of_nominal_8TBs": achieved / 8000.0}
         line["stage_ms"] = r["stage_ms"]
     else:
@@ -765,10 +766,14 @@ def run_expert_parallel(args, rank, world, dev):
     mine = torch.cat([mine, shared])
     if use_packed:
         mine = moe.pack_experts(L, mine)
+    # the timed layers: the whole step as one C ABI call (bsx_ep_layer) on a communicator of this process's own
+    comm = ep.NcclComm()
     layers = []
     for c in range(args.copies):
         b = mine.clone()
-        layers.append(ep.EPMoELayer(gate.clone(), None, b[:El], L, rargs, E, shared_blob=b[El], max_tokens=T, packed=use_packed))
+        layers.append(ep.EPMoELayerNative(gate.clone(), None, b[:El], L, rargs, E, comm, shared_blob=b[El], max_tokens=T, packed=use_packed))
+    # the same step driven call by call from Python, for the per-stage times only (events between the stages)
+    probe = ep.EPMoELayer(gate, None, mine[:El], L, rargs, E, shared_blob=mine[El], max_tokens=T, packed=use_packed)
     n_batches = 8
     g = torch.Generator(device=dev).manual_seed(1 + rank)
     xs = [torch.randn((T, H), generator=g, device=dev).bfloat16() for _ in range(n_batches)]
@@ -817,7 +822,7 @@ def run_expert_parallel(args, rank, world, dev):
         barrier()
         ms_e2e = e0.elapsed_time(e1)
         # per-stage device times of the step (events between the stages, launched call by call) and the local expert stage's bytes
-        ly = layers[0]
+        ly = probe
         stage_acc, exp_bytes = {}, []
         n_inst = min(args.steps, 30)
         for i in range(n_inst):
@@ -831,8 +836,14 @@ def run_expert_parallel(args, rank, world, dev):
             dist.barrier()
         ly.events = None
         stage_ms = {k: v / n_inst for k, v in stage_acc.items()}
-        for ly in layers:
+        for ly in layers + [probe]:
             ly.check_status()
+        # the one-call step and the call-by-call step are the same kernels and collectives: their rows must agree
+        y_nat = layers[0].forward(xs[0]).clone()
+        y_py = probe.forward(xs[0]).clone()
+        torch.cuda.synchronize()
+        rel_check = float((y_nat - y_py).norm() / y_py.norm())
+        assert rel_check < 1e-5, f"bsx_ep_layer differs from the call-by-call step (relative L2 {rel_check})"
         barrier()
     times = torch.tensor([ms_total, ms_e2e] + [stage_ms[k] for k in sorted(stage_ms)], dtype=torch.float64, device=dev)
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -843,8 +854,11 @@ def run_expert_parallel(args, rank, world, dev):
     wl = None
     if not args.no_workloads and T == 64:
         # the DeepSeek-style layer, 8192 prompt tokens in total split over the ranks (strong scaling across N): every rank joins
+        for l_ in layers:
+            if l_.graph is not None:
+                l_.graph.reset()
         layers.clear()
-        del mine, ly
+        del mine, ly, probe
         torch.cuda.empty_cache()
         wp = argparse.Namespace(**vars(args))
         wp.experts = "packed"
@@ -879,6 +893,7 @@ def run_expert_parallel(args, rank, world, dev):
         "stage_ms": stage_max, "stage_ms_note": "max over ranks, steps launched call by call with events between the stages (the timed steps replay one graph)",
         "clocks": clocks.summary(),
     }
+    line["check"] = {"one_call_step_vs_call_by_call_rel_l2": rel_check, "status_words": "clear"}
     if stage_max:
         outside = {k: v for k, v in stage_max.items() if k != "experts"}
         top = max(outside, key=outside.get) if outside else None
