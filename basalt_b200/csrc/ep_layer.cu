@@ -179,8 +179,11 @@ extern "C" int32_t bsx_ep_layer(const bsx_ep_layer_desc* d, void* comm, const vo
     // 2. the rank's own routing: ids, then weight bits, in one buffer
     int32_t* ids = c.route;
     float* w = reinterpret_cast<float*>(c.route + (size_t) T * k);
-    rc = bsx_router_x(x, x_kind, d->gate, d->bias, T, E, H, k, d->gate_kind, d->weight_scale, d->n_group, d->topk_group, 0.f, nullptr, 0, c.logits, ids, w,
-                      stream);
+    {
+        PdlScope pdl(true, 1);   // logits follow the caller's work; the selection is a programmatic dependent launch
+        rc = bsx_router_x(x, x_kind, d->gate, d->bias, T, E, H, k, d->gate_kind, d->weight_scale, d->n_group, d->topk_group, 0.f, nullptr, 0, c.logits, ids, w,
+                          stream);
+    }
     if (rc != BSX_OK) return rc;
     // 3. everyone's routing
     if (nc.all_gather(c.route, c.route_all, (size_t) 2 * T * k, kNcclInt32, comm, st) != 0) return BSX_E_UNAVAILABLE;
@@ -190,7 +193,10 @@ extern "C" int32_t bsx_ep_layer(const bsx_ep_layer_desc* d, void* comm, const vo
                      c.ent_dst, c.ent_tok, stream);
     if (rc != BSX_OK) return rc;
     if (side != st && cudaStreamWaitEvent(st, (cudaEvent_t) ev_join, 0) != cudaSuccess) return launch_status();
-    // 5. the local experts over the gathered rows (a pair's output lands on row = its index; shared rows after them)
+    // 5. the local experts over the gathered rows (a pair's output lands on row = its index; shared rows after them).  The first
+    // kernel of the chain follows a collective and an event of another stream, so it is a plain launch; the ones behind it
+    // (gate/up, SwiGLU images, down, partial combine) are programmatic dependent launches of each other.
+    PdlScope pdl(true, 1);
     const int64_t cap_groups = (int64_t) d->n_local + d->n_replicas + (shared ? 1 : 0);
     if (d->packed) {
         rc = bsx_experts_grouped_packed(&L, c.ptr, c.start, c.n_groups, c.ent_dst, c.ent_tok, cap_groups, c.cap_rows, c.x_all, x_kind, W * T, c.scratch, c.rows,
