@@ -251,8 +251,7 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
     const int n_rb = (int) ((R + kRowsPerBlock - 1) / kRowsPerBlock);
     // a unit = one pass x n_sub consecutive row blocks, sized to at least 4 stages so that the per-unit bookkeeping (the
     // pass record, the entries' rows and scales) is amortised and its loads hide behind the stream
-    const int n_sub = max(1, min(n_rb, (4 + n_chunk - 1) / n_chunk));
-    const int n_upp = (n_rb + n_sub - 1) / n_sub;                        // units per pass
+    const int n_sub_full = max(1, min(n_rb, (4 + n_chunk - 1) / n_chunk));
     const PackedGeom geo = packed_geom(a.L.n_embd, a.L.n_ff);
 
     if (threadIdx.x == 0) {
@@ -282,7 +281,12 @@ __global__ void __launch_bounds__(kThreadsF, 1) nvf4_stream_kernel(StreamArgs sa
     // stages while the SwiGLU rows' images are still being made - the stream is in flight when the first image arrives.
     if (!(sa.early_weights && warp == 1)) pdl_wait();
     pdl_launch_dependents();
-    const int n_units = sa.n_items[0] * n_upp;
+    // ... unless the window is so small that such units would not go round the SMs three times: then one row block a unit, so that
+    // the last, partial round of the static schedule costs half as much (a window of 8 tokens has ~80 passes)
+    const int n_pass = sa.n_items[0];
+    const int n_sub = (n_sub_full > 1 && n_pass * ((n_rb + n_sub_full - 1) / n_sub_full) < 3 * (int) gridDim.x) ? 1 : n_sub_full;
+    const int n_upp = (n_rb + n_sub - 1) / n_sub;                        // units per pass
+    const int n_units = n_pass * n_upp;
 
     // unit -> its pass record and its row blocks [rb0, rb1).  Tile 0 / tile 1 of a row block: the 128 gate rows r0.. and the
     // 128 up rows r0.. (gate/up), or down rows r0.. and r0 + 128.. (down).

@@ -161,4 +161,91 @@ __device__ inline void plan_finish(const PlanSmem& s, int n, int k, int E, unsig
     }
 }
 
+// The same plan for a window of a few tokens, from the pairs alone: every thread owns one pair and counts, over the n pairs in
+// shared memory, what the scans over the E experts would have told it - how many entries precede its group, its place inside the
+// group (pairs keep their order), whether it is its expert's first pair (the group's leader) and, for leaders, how many groups
+// and passes come before theirs.  No table of E entries is read or cleared and the block meets at four barriers; the work is
+// n^2 shared-memory reads, which for n <= 512 is less than one scan over the experts.  Groups, entries and passes come out in
+// exactly the order of plan_finish (ascending expert, pairs in order).  sid[i]: pair i's expert, or -1 (out of range / not held
+// here); blob[i]: that expert's blob address; lead: n ints of scratch.  Every thread of the block calls; blockDim.x >= n.
+__device__ inline void plan_small(const int32_t* sid, const unsigned long long* blob, int32_t* lead, int n, int k, unsigned long long shared_blob,
+                                  int n_tok, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start, int32_t* __restrict__ n_groups,
+                                  int32_t* __restrict__ dst, int32_t* __restrict__ tok, PassRec* __restrict__ items, int* __restrict__ n_items,
+                                  int tok_base = 0) {
+    __shared__ int s_passes;
+    const int i = threadIdx.x;
+    const int e = i < n ? sid[i] : -1;
+    int less = 0, before = 0, cnt = 0;
+    if (e >= 0) {
+        for (int j = 0; j < n; ++j) {
+            const int sj = sid[j];
+            less += (sj >= 0) & (sj < e);
+            before += (sj == e) & (j < i);
+            cnt += sj == e;
+        }
+        dst[less + before] = i;
+        tok[less + before] = i / k;
+    }
+    const bool leader = e >= 0 && before == 0;
+    if (i < n) lead[i] = leader ? cnt : 0;
+    if (i == 0) s_passes = 0;
+    const int n_valid = __syncthreads_count(e >= 0);       // also publishes lead[] and s_passes
+    const int n_lead = __syncthreads_count(leader);
+    if (leader) {
+        int g = 0, po = 0;
+        for (int j = 0; j < n; ++j) {
+            const int c = lead[j];
+            if (c > 0 && sid[j] < e) {
+                ++g;
+                po += (c + kPassEntries - 1) / kPassEntries;
+            }
+        }
+        ptr[g] = blob[i];
+        start[g] = less;
+        const int np = (cnt + kPassEntries - 1) / kPassEntries;
+        if (items) {
+            for (int p = 0; p < np; ++p) {
+                PassRec r;
+                r.blob = blob[i];
+                r.eb = less + p * kPassEntries;
+                r.ntok = min(kPassEntries, cnt - p * kPassEntries);
+                items[po + p] = r;
+            }
+        }
+        atomicAdd(&s_passes, np);
+    }
+    __syncthreads();
+    int at = n_valid, g = n_lead, np_total = s_passes;
+    if (shared_blob != 0ull && n_tok > 0) {
+        // the shared expert: one more group holding every token, its rows after the routed pairs' rows
+        if (i == 0) {
+            ptr[g] = shared_blob;
+            start[g] = at;
+        }
+        for (int t = i; t < n_tok; t += blockDim.x) {
+            dst[at + t] = n + t;
+            tok[at + t] = tok_base + t;
+        }
+        const int np = (n_tok + kPassEntries - 1) / kPassEntries;
+        if (items) {
+            for (int p = i; p < np; p += blockDim.x) {
+                PassRec r;
+                r.blob = shared_blob;
+                r.eb = at + p * kPassEntries;
+                r.ntok = min(kPassEntries, n_tok - p * kPassEntries);
+                items[np_total + p] = r;
+            }
+        }
+        np_total += np;
+        at += n_tok;
+        ++g;
+    }
+    if (i == 0) {
+        start[g] = at;
+        start[g + 1] = at;
+        *n_groups = g;
+        if (n_items) n_items[0] = np_total;
+    }
+}
+
 }  // namespace bsx

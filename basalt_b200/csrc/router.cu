@@ -524,34 +524,43 @@ route_tail_skip_kernel(int32_t* __restrict__ ids, float* __restrict__ w, HeldTab
 
 
 // ---------------------------------------------------------------------------------------------- selection + plan in one launch
-// One block: its 32 warps choose the experts of the window's tokens (the per-token routines above, so ids and weights carry
-// the same bits as the separate kernels'), leave the ids in shared memory, and the block goes straight on to the
-// decode-window plan (plan.cuh) - one launch and one round trip through global memory fewer in a step that is latency-bound.
+// One block for a window of up to 16 tokens: a warp per token chooses its experts (the per-token routines above, so ids and
+// weights carry the same bits as the separate kernels'), leaves the ids in shared memory with their blobs' addresses, and the
+// block goes straight on to the window's plan from those pairs alone (plan_small, plan.cuh) - one launch and one round trip
+// through global memory fewer in a step that is latency-bound, and nothing in it grows with the number of experts.
 // With items / n_items the pass list of the packed expert kernels is written as well.
+constexpr int kRoutePlanThreads = 512;     // 16 warps: the window's tokens; and one thread per pair of the plan (T k <= 512)
+
 template <int REGT>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(kRoutePlanThreads)
 route_plan_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int k, float scale, int gate, int n_group,
                   int topk_group, float prior, HeldTabs held, const unsigned long long* __restrict__ blobs, unsigned long long shared_blob,
                   int32_t* ids, float* weights, unsigned long long* __restrict__ ptr, int32_t* __restrict__ start,
                   int32_t* __restrict__ n_groups, int32_t* __restrict__ dst, int32_t* __restrict__ tok, PassRec* __restrict__ items,
                   int* __restrict__ n_items) {
-    extern __shared__ unsigned long long smb[];
-    const PlanSmem ps = plan_smem(smb, E);
-    plan_load_blobs(ps, blobs, E);       // constant addresses: before the wait for the kernel that wrote the logits
+    __shared__ int32_t s_sid[kRoutePlanThreads], s_lead[kRoutePlanThreads];
+    __shared__ unsigned long long s_blob[kRoutePlanThreads];
     pdl_wait();
     pdl_launch_dependents();
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int t = warp; t < T; t += 32) {
+    if (warp < T) {
+        const int t = warp;
         int32_t* it = ids + (size_t) t * k;
         float* wt = weights + (size_t) t * k;
         if (gate == BSX_GATE_SOFTMAX) softmax_topk_token<REGT>(logits + (size_t) t * E, it, wt, E, k);
         else select_token<REGT>(logits + (size_t) t * E, bias, E, k, scale, gate, n_group, topk_group, prior, held, it, wt);
         __syncwarp();                    // lane 0's ids are visible to the warp
-        if (lane < k) plan_note_pair(ps, t * k + lane, it[lane], E);
+        if (lane < k) {
+            int e = it[lane];
+            unsigned long long b = 0ull;
+            if ((unsigned) e < (unsigned) E) b = blobs[e];
+            if (!b) e = -1;              // out of range, or an expert this device does not hold: no entry
+            s_sid[t * k + lane] = e;
+            s_blob[t * k + lane] = b;
+        }
     }
     __syncthreads();
-    plan_finish(ps, T * k, k, E, shared_blob, shared_blob != 0ull ? T : 0, ptr, start, n_groups, dst, tok, items, n_items);
+    plan_small(s_sid, s_blob, s_lead, T * k, k, shared_blob, shared_blob != 0ull ? T : 0, ptr, start, n_groups, dst, tok, items, n_items);
 }
 
 bool make_held(const int32_t* const* tabs, int n, HeldTabs& h) {
@@ -732,8 +741,8 @@ int32_t route_plan_launch(const float* logits, const float* bias, int32_t T, int
         if (rc != BSX_OK) return rc;
         return moe_plan_with_passes(ids, T, k, E, blob_table, shared_blob, ptr, start, n_groups, dst, tok, items, n_items, st);
     }
-    const size_t smem = plan_smem_bytes(E, T * k);
-#define BSX_RP(R) launch_k(route_plan_kernel<R>, dim3(1), dim3(1024), smem, st, logits, bias, (int) T, (int) E, (int) k, weight_scale, (int) gate_kind, (int) n_group, \
+    static_assert(kRoutePlanMaxTokens * 32 <= kRoutePlanThreads, "a warp per token, a thread per pair");
+#define BSX_RP(R) launch_k(route_plan_kernel<R>, dim3(1), dim3(kRoutePlanThreads), 0, st, logits, bias, (int) T, (int) E, (int) k, weight_scale, (int) gate_kind, (int) n_group, \
                            (int) topk_group, 0.f, held, blob_table, shared_blob, ids, weights, ptr, start, n_groups, dst, tok, items, n_items)
     switch (E >> 5) {
         case 2: BSX_RP(2); break;
