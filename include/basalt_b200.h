@@ -316,9 +316,10 @@ BSX_API int32_t bsx_combine(const float* rows, const int32_t* slot, const float*
 BSX_API int32_t bsx_combine_residual(const float* rows, const int32_t* slot, const float* weights, const float* shared, const float* shared_gate,
                                      const float* residual, int32_t T, int32_t k, int32_t H, float* y, void* stream);
 
-/* ---- a2-a4 + a6 in one launch: bsx_router_select followed by bsx_moe_plan_shared (shared_blob = 0: bsx_moe_plan), for decode
- * windows (T * k <= 1024).  One block chooses every token's experts and goes straight on to the plan, the ids never leaving
- * shared memory in between; ids, weights, groups and entries carry the bits of the two separate calls.  Gate kinds SOFTMAX,
+/* ---- a2-a4 + a6 together: bsx_router_select followed by bsx_moe_plan_shared (shared_blob = 0: bsx_moe_plan), for decode
+ * windows (T * k <= 1024).  Up to 16 tokens it is one launch: one block chooses every token's experts and goes straight on to
+ * the plan, the ids never leaving shared memory in between; wider windows keep the selection spread over the SMs and take two
+ * launches.  Either way ids, weights, groups and entries carry the bits of the two separate calls.  Gate kinds SOFTMAX,
  * SIGMOID and SQRT_SOFTPLUS (with groups); BSX_E_TYPE for the others (use the separate calls); no held tables / prior. */
 BSX_API int32_t bsx_route_plan(const float* logits, const float* bias, int32_t T, int32_t E, int32_t k, int32_t gate_kind, float weight_scale,
                                int32_t n_group, int32_t topk_group, const unsigned long long* blob_table, unsigned long long shared_blob,
@@ -330,7 +331,7 @@ BSX_API int32_t bsx_route_plan(const float* logits, const float* bias, int32_t T
  * issues call by call (src/models/inkling2/session.cpp:680-716; src/models/deepseek41/ops_kernels.cpp:797,931,964), for a C or
  * C++ caller that wants the step without a host layer of its own.  Every kernel after the first is a programmatic dependent
  * launch (as Basalt's decode chain: include/basalt/kernels/pdl.hpp:20-32), selection + plan (+ the packed kernels' pass list)
- * are one kernel.  Nothing is allocated or read back; the call can be captured into a CUDA graph.
+ * are one kernel for windows of up to 16 tokens.  Nothing is allocated or read back; the call can be captured into a CUDA graph.
  * desc: layout = the routed experts' (and, with `packed`, the shared expert's); shared_layout = the shared expert's when its
  * ggml blob has another layout (n_embd = 0: same as layout); packed = blobs are bsx_expert_pack planes (all-NVFP4).
  * x [n_tokens][n_embd] fp32 or bf16; y [n_tokens][n_embd] fp32; residual [n_tokens][n_embd] fp32 or null; n_tokens <= max_tokens,
