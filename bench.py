@@ -603,6 +603,78 @@ def run_decode_codebook(args, dev, sh, steps=None, warmup=None, copies=None):
     return line
 
 
+def run_prefill_codebook(args, dev, sh, tokens=4096, steps=3, warmup=3):
+    """The prompt-sized step over K/IQ-format experts read in place (the path the reference runs as its int8 MMQ product): the
+    DeepSeek-style layer's IQ1_M routed experts, `tokens` rows a step, through router GEMM -> selection -> dispatch with the tile
+    list -> bsx_experts_prefill (decoder warps feeding tcgen05 kind::f16) -> combine.  No shared expert in this entry: the routed
+    product is what it measures.  Tensor roofline against the measured bf16 peak (the weights are decoded to fp16 operands)."""
+    from basalt_b200 import capi, moe
+    H, E, I, K_TOP = sh["H"], sh["E"], sh["I"], sh["k"]
+    rt = sh["routed_type"]
+    gate = (torch.randn((E, H), generator=torch.Generator(device=dev).manual_seed(0), device=dev) * 0.02).float()
+    bias = (torch.randn(E, generator=torch.Generator(device=dev).manual_seed(7), device=dev) * 0.01).float()
+    blobs, rb = random_codebook_blobs(dev, rt, E, H, I, 11)
+    L = moe.native_expert_layout(rt, rt, H, I)
+    assert L.bytes == rb
+    rargs = moe.RouterArgs(n_expert=E, n_embd=H, k=K_TOP, weight_scale=sh["scale"], gate=capi.GATE_SIGMOID, n_group=sh["n_group"],
+                           topk_group=sh["topk_group"])
+    layer = moe.PrefillMoELayer(gate, bias, blobs, L, rargs, shared_blob=None, max_tokens=tokens, packed=False)
+    g = torch.Generator(device=dev).manual_seed(1)
+    xs = [torch.randn((tokens, H), generator=g, device=dev).bfloat16() for _ in range(2)]
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        for i in range(warmup):
+            layer.forward(xs[i % 2], None, stream)
+        torch.cuda.synchronize()
+        layer.check_status()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(dev.index or 0) as clocks:
+            ev0.record(stream)
+            for i in range(steps):
+                layer.forward(xs[i % 2], None, stream)
+            ev1.record(stream)
+            torch.cuda.synchronize()
+        ms_step = ev0.elapsed_time(ev1) / steps
+        x_host = [x.cpu().pin_memory() for x in xs]
+        xin = torch.empty((tokens, H), dtype=torch.bfloat16, device=dev)
+        y_host = torch.empty((tokens, H), dtype=torch.float32).pin_memory()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            xin.copy_(x_host[i % 2], non_blocking=True)
+            y_host.copy_(layer.forward(xin, None, stream), non_blocking=True)
+            stream.synchronize()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms_e2e = e0.elapsed_time(e1) / steps
+        layer.events = []
+        layer.forward(xs[0], None, stream)
+        stream.synchronize()
+        stage_ms = {nme: a.elapsed_time(b) for (_, a), (nme, b) in zip(layer.events[:-1], layer.events[1:])}
+        layer.events = None
+        layer.check_status()
+    pk = peaks()
+    flops = 6.0 * H * I * tokens * K_TOP
+    achieved = flops / (stage_ms["experts"] * 1e-3) / 1e12
+    line = {
+        "metric": "MoE-layer tokens/s (prefill)", "value": tokens / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16 x (IQ1_M decoded to fp16, scaled by 16) on tcgen05 kind::f16, fp32 accumulation in tensor memory", "data": "synthetic (random valid blocks)",
+        "config": dict(workload=f"{sh['name']} prefill, IQ1_M routed experts in place, {tokens} tokens/step (no shared expert)", hidden=H, n_expert=E, n_shared=0,
+                       intermediate=I, top_k=K_TOP, router=sh["router"], expert_format="IQ1_M (56 B / 256 values)", activations="bf16", tokens_per_step=tokens,
+                       l2_policy="every step reads every touched expert blob", parallelism="single GPU"),
+        "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": tokens * H * 2, "d2h_bytes_per_step": tokens * H * 4},
+        "gpu_launches": 10 * steps,
+        "roofline": {"bound": "tensor", "kernel": "prefill_gemm_kernel<IQ1_M> gate/up + down", "achieved": achieved, "peak": pk["bf16"], "unit": "TFLOP/s",
+                     "frac": achieved / pk["bf16"], "peak_source": pk["source"], "traffic": None, "algorithmic_flops_per_launch": flops,
+                     "kernel_ms": stage_ms["experts"]},
+        "stage_ms": stage_ms, "clocks": clocks.summary(),
+    }
+    del layer, blobs
+    torch.cuda.empty_cache()
+    return line
+
+
 # --------------------------------------------------------------------------------------------------------- prompt-sized steps
 def zipf_logits(n_tokens, n_expert, gen, dev, s=1.1):
     """[T][E] fp32 scores whose top-k sets follow Zipf(s) popularity: log p_e + Gumbel noise, the popularity ranks dealt to
@@ -959,6 +1031,9 @@ def main():
     if world > 1:
         dist.barrier()
     capi.lib()
+    if args.workload == "prefill" and "routed_type" in SHAPES[args.shape]:
+        print(json.dumps(run_prefill_codebook(args, dev, SHAPES[args.shape], tokens=args.tokens, steps=max(args.steps // 20, 3), warmup=3)))
+        return
     if args.workload == "prefill":
         line = run_prefill(args, dev, rank, world)
         if line is not None:
@@ -1010,6 +1085,7 @@ def main():
         torch.cuda.empty_cache()
         sub.decode_tokens = 64
         wl.append(short(run_decode_codebook(sub, dev, SHAPES["c4"], steps=10, warmup=3, copies=1)))
+        wl.append(short(run_prefill_codebook(sub, dev, SHAPES["c4"], tokens=4096, steps=3, warmup=3)))
         line["workloads"] = wl
     print(json.dumps(line))
 
