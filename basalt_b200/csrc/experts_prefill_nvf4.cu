@@ -113,16 +113,9 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
     using G = Geo<MODE>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
-    // Barriers.  A stage's weights (one or two packed blocks, bulk copies) and its gathered activation rows are handed over
-    // separately, and the activation rows in two halves of two K-steps each: the rows come from all over L2 / HBM and their
-    // latency is what the tensor core waits for, so the first half of a stage's buffer is refilled as soon as its two K-steps have
-    // been multiplied - up to three half-stages of rows are then on their way while the fourth is consumed, where whole-stage
-    // hand-overs keep one stage in flight.
-    uint64_t* fullw = reinterpret_cast<uint64_t*>(smem + kStagesQ * G::kStage);   // [stage]: the weight blocks have landed
-    uint64_t* emptyw = fullw + kStagesQ;                                           // [stage]: the stage's last MMA has read them
-    uint64_t* fulla = emptyw + kStagesQ;                                           // [2 stage + half]: the half's rows and scale words are in place
-    uint64_t* emptya = fulla + 2 * kStagesQ;                                       // [2 stage + half]: the half's MMAs are done
-    uint64_t* acc_full = emptya + 2 * kStagesQ;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStagesQ * G::kStage);
+    uint64_t* empty = full + kStagesQ;
+    uint64_t* acc_full = empty + kStagesQ;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
@@ -136,12 +129,8 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStagesQ; ++s) {
-            mbar_init(&fullw[s], 1);         // the weight loader's expect_tx arrival
-            mbar_init(&emptyw[s], 1);
-        }
-        for (int q = 0; q < 2 * kStagesQ; ++q) {
-            mbar_init(&fulla[q], 128);       // the 128 activation-loader lanes
-            mbar_init(&emptya[q], 1);
+            mbar_init(&full[s], 1 + 128);    // the weight loader's expect_tx arrival + the 128 activation-loader lanes
+            mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&acc_full[s], 1);
@@ -187,18 +176,14 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const uint32_t d = tmem + acc * G::kN;
                 for (int c = 0; c < n_chunk; ++c, ++kc) {
-                    const uint32_t s = kc % kStagesQ, ph = (kc / kStagesQ) & 1u;
-                    ok = mbar_wait(&fullw[s], ph);
+                    const uint32_t s = kc % kStagesQ;
+                    ok = mbar_wait(&full[s], (kc / kStagesQ) & 1u);
                     if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     const uint32_t st = smem_u32(smem + s * G::kStage);
                     const uint32_t tsfa = tmem + G::kTmemSF + s * G::kSFStage, tsfb = tsfa + G::kSFACols;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        if ((k & 1) == 0) {      // the half-stage that holds K-steps k, k + 1
-                            ok = mbar_wait(&fulla[2 * s + (k >> 1)], ph);
-                            if (!ok) break;
-                            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                        }
 #pragma unroll
                         for (int b = 0; b < G::kBlocks; ++b)
                             asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tsfb + (uint32_t) (4 * G::kBlocks * k + 4 * b)),
@@ -217,10 +202,8 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
                                          "r"(tsfb + (uint32_t) (4 * G::kBlocks * k)), "r"(accum)
                                          : "memory");
                         }
-                        if (k & 1) umma_commit(&emptya[2 * s + (k >> 1)]);   // this half's rows may be overwritten once these MMAs are done
                     }
-                    if (!ok) break;
-                    umma_commit(&emptyw[s]);
+                    umma_commit(&empty[s]);
                 }
                 if (!ok) break;
                 umma_commit(&acc_full[acc]);
@@ -245,9 +228,9 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
                 }
                 for (int c = 0; c < n_chunk; ++c, ++issued) {
                     const uint32_t s = issued % kStagesQ;
-                    ok = mbar_wait(&emptyw[s], ((issued / kStagesQ) & 1u) ^ 1u);
+                    ok = mbar_wait(&empty[s], ((issued / kStagesQ) & 1u) ^ 1u);
                     if (!ok) break;
-                    const uint32_t st = smem_u32(smem + s * G::kStage), bar = smem_u32(&fullw[s]);
+                    const uint32_t st = smem_u32(smem + s * G::kStage), bar = smem_u32(&full[s]);
                     asm volatile("{\n.reg .b64 t;\nmbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1;\n}\n" ::"r"(bar), "r"((uint32_t) (G::kBlocks * kBlockF))
                                  : "memory");
 #pragma unroll
@@ -265,13 +248,12 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
             if (!ok) atomicOr(a.status, 1);
         }
     } else if (warp <= 5) {
-        // ---- activation loaders (128 lanes), one half-stage (two K-steps = 64 of a row's 128 code bytes, every term) at a time.
-        // Codes of half h: lane = (16-byte piece 4 h + tl % 4, row group tl / 4); rows tl / 4 + 32 i.  Scales: lane = row m; for
-        // each term and each of the half's two K-steps one word into slot (m % 32, m / 32) of that step's block.  A lane hands a
-        // half over when its copies there have landed, and keeps at most two halves of copies in flight.
+        // ---- activation loaders (128 lanes).  Codes: lane = (16-byte piece c8, row group r16); rows r16 + 16 i, every term.
+        // Scales: lane = row m; for each term and K-step one word into slot (m % 32, m / 32) of that step's block.  A lane
+        // arrives on a stage when its copies there have landed.
         const int tl = threadIdx.x - 64;
-        const int c4 = tl & 3, r32 = tl >> 2;
-        uint32_t issued = 0, arrived = 0;      // in half-stages
+        const int c8 = tl & 7, r16 = tl >> 3;
+        uint32_t issued = 0, arrived = 0;
         // Software pipeline over items so that no item starts with a chain of dependent loads: the tile record of the item after
         // next and the row indices of the next item are requested while this item streams.
         auto next_valid = [&](int from, TileRec& r) {     // first item >= from (in this CTA's stride) whose expert is held here
@@ -282,73 +264,73 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
             }
             return it;
         };
-        auto load_idx = [&](const TileRec& r, int (&idx)[5]) {   // image rows of this lane's 4 code rows and its scale row
+        auto load_idx = [&](const TileRec& r, int (&idx)[9]) {   // image rows of this lane's 8 code rows and its scale row
 #pragma unroll
-            for (int i = 0; i < 5; ++i) {
-                const int rw = i < 4 ? r32 + 32 * i : tl;
+            for (int i = 0; i < 9; ++i) {
+                const int rw = i < 8 ? r16 + 16 * i : tl;
                 const int rr = rw < r.rows ? rw : 0;
                 idx[i] = MODE == QMODE_GU ? a.src[r.row0 + rr] : r.row0 + rr;
             }
         };
         TileRec rec0, rec1, rec2;
-        int idx0[5], idx1[5];
+        int idx0[9], idx1[9];
         int item = next_valid(blockIdx.x, rec0);
         int item1 = item < n_items ? next_valid(item + gridDim.x, rec1) : n_items;
         if (item < n_items) load_idx(rec0, idx0);
         if (item1 < n_items) load_idx(rec1, idx1);
         while (item < n_items && ok) {
             const int item2 = item1 < n_items ? next_valid(item1 + gridDim.x, rec2) : n_items;
+            Item it;
+            it.blob = reinterpret_cast<const uint8_t*>(rec0.blob);
+            it.row0 = rec0.row0;
+            it.rows = rec0.rows;
+            it.n0 = (item - (item / n_n) * n_n) * 128;
             // image rows behind the tile's rows: the row's token (gate/up) or the dispatch row itself (down); rows past the
             // expert's last row read the tile's first row (their results are never stored)
-            const uint8_t* crow[4];
-            uint32_t cdst[4];
+            const uint8_t* crow[8];
+            uint32_t cdst[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int r = r32 + 32 * i;
-                crow[i] = a.codes + (size_t) idx0[i] * kTermsF * (size_t) (K >> 1);
-                cdst[i] = (uint32_t) ((r >> 3) * 1024 + (r & 7) * 128);
+            for (int i = 0; i < 8; ++i) {
+                const int r = r16 + 16 * i;
+                crow[i] = a.codes + (size_t) idx0[i] * kTermsF * (size_t) (K >> 1) + c8 * 16;
+                cdst[i] = (uint32_t) ((r >> 3) * 1024 + (r & 7) * 128 + ((c8 ^ (r & 7)) << 4));
             }
-            const uint8_t* srow = a.sfs + (size_t) idx0[4] * kTermsF * (size_t) (K >> 4);
+            const uint8_t* srow = a.sfs + (size_t) idx0[8] * kTermsF * (size_t) (K >> 4);
             const uint32_t sdst = (uint32_t) (G::kOffSFA + (tl & 31) * 16 + (tl >> 5) * 4);
-            for (int c = 0; c < n_chunk && ok; ++c) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    // The slot of half-stage `issued` frees when the tensor core is done with half-stage issued - 4, which it can only
-                    // start once that one was handed over: at most two are kept back below, so it has been.
-                    const uint32_t q = issued % (2 * kStagesQ);
-                    ok = mbar_wait(&emptya[q], ((issued / (2 * kStagesQ)) & 1u) ^ 1u);
-                    if (!ok) break;
-                    const uint32_t st = smem_u32(smem + (q >> 1) * G::kStage);
-                    const int piece = 4 * h + c4;
-#pragma unroll
-                    for (int t = 0; t < kTermsF; ++t) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int r = r32 + 32 * i;
-                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(st + (uint32_t) (t * kATileQ) + cdst[i] + (uint32_t) ((piece ^ (r & 7)) << 4)),
-                                         "l"(crow[i] + (size_t) t * (size_t) (K >> 1) + (size_t) c * 128 + piece * 16)
-                                         : "memory");
-                        }
-                    }
-                    // this row's scale words of the half's two K-steps: 8 bytes a term through registers, then one word into slot
-                    // (m % 32, m / 32) of each step's block (four rows share a 16-byte slot, so no 16-byte copy can place them)
-                    uint2 sv[kTermsF];
-#pragma unroll
-                    for (int t = 0; t < kTermsF; ++t) sv[t] = *reinterpret_cast<const uint2*>(srow + (size_t) t * (size_t) (K >> 4) + (size_t) c * 16 + 8 * h);
-#pragma unroll
-                    for (int t = 0; t < kTermsF; ++t) {
-                        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(st + sdst + (uint32_t) (t * kSFQ + (2 * h) * 512)), "r"(sv[t].x) : "memory");
-                        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(st + sdst + (uint32_t) (t * kSFQ + (2 * h + 1) * 512)), "r"(sv[t].y) : "memory");
-                    }
-                    asm volatile("cp.async.commit_group;\n" ::: "memory");
-                    ++issued;
-                    if (issued - arrived > 2) {
-                        asm volatile("cp.async.wait_group 2;\n" ::: "memory");
-                        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-                        mbar_arrive(&fulla[arrived % (2 * kStagesQ)]);
-                        ++arrived;
-                    }
+            for (int c = 0; c < n_chunk; ++c) {
+                // hand over what is already on its way before blocking on the next slot (it frees only when the tensor core has
+                // consumed the stage before this one)
+                if (issued > arrived) {
+                    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                    for (; arrived < issued; ++arrived) mbar_arrive(&full[arrived % kStagesQ]);
                 }
+                const uint32_t s = issued % kStagesQ;
+                ok = mbar_wait(&empty[s], ((issued / kStagesQ) & 1u) ^ 1u);
+                if (!ok) break;
+                const uint32_t st = smem_u32(smem + s * G::kStage);
+#pragma unroll
+                for (int t = 0; t < kTermsF; ++t) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(st + (uint32_t) (t * kATileQ) + cdst[i]),
+                                     "l"(crow[i] + (size_t) t * (size_t) (K >> 1) + (size_t) c * 128)
+                                     : "memory");
+                }
+                // this row's scale words: 16 bytes a term (the chunk's four K-steps) through registers, then one word into slot
+                // (m % 32, m / 32) of each step's block (four rows share a 16-byte slot, so no 16-byte copy can place them)
+                uint4 sv[kTermsF];
+#pragma unroll
+                for (int t = 0; t < kTermsF; ++t) sv[t] = *reinterpret_cast<const uint4*>(srow + (size_t) t * (size_t) (K >> 4) + (size_t) c * 16);
+#pragma unroll
+                for (int t = 0; t < kTermsF; ++t) {
+                    const uint32_t w[4] = {sv[t].x, sv[t].y, sv[t].z, sv[t].w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(st + sdst + (uint32_t) (t * kSFQ + k * 512)), "r"(w[k]) : "memory");
+                }
+                asm volatile("cp.async.commit_group;\n" ::: "memory");
+                ++issued;
             }
             // advance the pipeline: the next item's indices were requested one item ago; request those of the item after it
             item = item1;
@@ -356,12 +338,12 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
             rec0 = rec1;
             rec1 = rec2;
 #pragma unroll
-            for (int i = 0; i < 5; ++i) idx0[i] = idx1[i];
+            for (int i = 0; i < 9; ++i) idx0[i] = idx1[i];
             if (item1 < n_items) load_idx(rec1, idx1);
         }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        for (; arrived < issued; ++arrived) mbar_arrive(&fulla[arrived % (2 * kStagesQ)]);
+        for (; arrived < issued; ++arrived) mbar_arrive(&full[arrived % kStagesQ]);
         if (!ok) atomicOr(a.status, 1);
     } else {
         // ---- epilogue: thread p reads TMEM lane p (= tile row p).  A warp may only read lanes 32 (warp % 4) .. + 31.
