@@ -112,6 +112,8 @@ void launch_images(const void* src, int kind, int64_t rows, const int32_t* rows_
 __device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p), "r"(bytes) : "memory");
 }
+// the same for the cache line that holds p, through the load path (one line a lane: a warp asks for 32 lines with one instruction)
+__device__ __forceinline__ void l2_prefetch_line(const void* p) { asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p) : "memory"); }
 constexpr int kAheadQ = 2;      // chunks between a prefetch and the copy that wants the bytes
 
 template <int MODE>
@@ -354,14 +356,13 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
                                 const uint8_t* rowp = nxt ? a.codes + (size_t) idx1[i] * kTermsF * (size_t) (K >> 1) : crow[i] - c8 * 16;
-                                l2_prefetch(rowp + (size_t) c8 * (size_t) (K >> 1) + (size_t) cc * 128, 128u);
+                                l2_prefetch_line(rowp + (size_t) c8 * (size_t) (K >> 1) + (size_t) cc * 128);
                             }
                         }
                         if ((cc & 3) == 0) {
                             const uint8_t* sp = nxt ? a.sfs + (size_t) idx1[8] * kTermsF * (size_t) (K >> 4) : srow;
-                            const uint32_t nb = (uint32_t) min(4, n_chunk - cc) * 16u;
 #pragma unroll
-                            for (int t = 0; t < kTermsF; ++t) l2_prefetch(sp + (size_t) t * (size_t) (K >> 4) + (size_t) cc * 16, nb);
+                            for (int t = 0; t < kTermsF; ++t) l2_prefetch_line(sp + (size_t) t * (size_t) (K >> 4) + (size_t) cc * 16);
                         }
                     }
                 }
