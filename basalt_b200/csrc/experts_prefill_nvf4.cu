@@ -108,14 +108,6 @@ void launch_images(const void* src, int kind, int64_t rows, const int32_t* rows_
     else prefill_images_kernel<FROM_H, 256><<<(unsigned) rows, 256, 0, st>>>(src, kind, rows, rows_dev, K, codes, sfs, inv);
 }
 
-// asks L2 for `bytes` (a multiple of 16) at a 16-byte aligned address; a hint, nothing waits for it
-__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p), "r"(bytes) : "memory");
-}
-// the same for the cache line that holds p, through the load path (one line a lane: a warp asks for 32 lines with one instruction)
-__device__ __forceinline__ void l2_prefetch_line(const void* p) { asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p) : "memory"); }
-constexpr int kAheadQ = 2;      // chunks between a prefetch and the copy that wants the bytes
-
 template <int MODE>
 __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs a) {
     using G = Geo<MODE>;
@@ -250,8 +242,6 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
                         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(st + (uint32_t) G::kOffSFB + b * kSFQ),
                                      "l"(g + kATileQ), "r"((uint32_t) kSFQ), "r"(bar)
                                      : "memory");
-                        // the block two stages on: with two buffers its copy cannot be requested yet, but L2 can already fetch it
-                        if (c + kAheadQ < n_chunk) l2_prefetch(g + (size_t) kAheadQ * kBlockF, (uint32_t) kBlockF);
                     }
                 }
             }
@@ -307,7 +297,6 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
             }
             const uint8_t* srow = a.sfs + (size_t) idx0[8] * kTermsF * (size_t) (K >> 4);
             const uint32_t sdst = (uint32_t) (G::kOffSFA + (tl & 31) * 16 + (tl >> 5) * 4);
-            const bool have_next = item1 < n_items;
             for (int c = 0; c < n_chunk; ++c) {
                 // hand over what is already on its way before blocking on the next slot (it frees only when the tensor core has
                 // consumed the stage before this one)
@@ -342,30 +331,6 @@ __global__ void __launch_bounds__(kThreadsQ, 1) prefill_nvf4_kernel(PrefillFArgs
                 }
                 asm volatile("cp.async.commit_group;\n" ::: "memory");
                 ++issued;
-                // The rows come from all over the image and, at these sizes, mostly from HBM; with two buffers a stage's copies
-                // cannot be requested before the stage two back is consumed, so their whole latency would sit in every stage.
-                // L2 is asked for them kAheadQ chunks early instead (of this item, or the first chunks of the next): the lanes
-                // holding pieces 0-3 take one term each of their eight code rows (one 128-byte line a row and term), and every lane
-                // its own scale row, 64 bytes = four chunks at a time.
-                {
-                    const int cp = c + kAheadQ;
-                    const bool nxt = cp >= n_chunk;
-                    const int cc = nxt ? cp - n_chunk : cp;
-                    if ((!nxt || have_next) && cc < n_chunk) {
-                        if (c8 < kTermsF) {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const uint8_t* rowp = nxt ? a.codes + (size_t) idx1[i] * kTermsF * (size_t) (K >> 1) : crow[i] - c8 * 16;
-                                l2_prefetch_line(rowp + (size_t) c8 * (size_t) (K >> 1) + (size_t) cc * 128);
-                            }
-                        }
-                        if ((cc & 3) == 0) {
-                            const uint8_t* sp = nxt ? a.sfs + (size_t) idx1[8] * kTermsF * (size_t) (K >> 4) : srow;
-#pragma unroll
-                            for (int t = 0; t < kTermsF; ++t) l2_prefetch_line(sp + (size_t) t * (size_t) (K >> 4) + (size_t) cc * 16);
-                        }
-                    }
-                }
             }
             // advance the pipeline: the next item's indices were requested one item ago; request those of the item after it
             item = item1;
