@@ -17,24 +17,33 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
 }
-// Waits for the phase with the given parity, at most kWaitNs of wall time (non-blocking test_wait polls, so the bound is
-// the clock's, not a multiple of try_wait's own suspend time); false when it gave up.
+// Waits for the phase with the given parity, at most kWaitNs of wall time; false when it gave up.  A few non-blocking polls
+// first (the common case: the phase completes within a microsecond), then try_wait with a suspend-time hint: the hardware parks
+// the thread and wakes it when the phase completes - no sleep granularity between the completion and the waiter - or after the
+// hint at the latest, and the clock is read between two such waits, so the bound is the clock's and every single wait is short.
+constexpr uint32_t kWaitHintNs = 4000;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t a = smem_u32(bar);
-    unsigned long long t0 = 0;
-    for (uint32_t i = 0;; ++i) {
-        uint32_t ok;
+    uint32_t ok;
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i) {
         asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
                      : "=r"(ok)
                      : "r"(a), "r"(parity)
                      : "memory");
         if (ok) return true;
-        if (i < 32) continue;
+    }
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t0));
+    for (;;) {
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok)
+                     : "r"(a), "r"(parity), "r"(kWaitHintNs)
+                     : "memory");
+        if (ok) return true;
         unsigned long long now;
         asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(now));
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > kWaitNs) return false;
-        __nanosleep(32);
+        if (now - t0 > kWaitNs) return false;
     }
 }
 
