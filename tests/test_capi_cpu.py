@@ -77,3 +77,26 @@ def test_nvfp4_packer_matches_oracle():
     L = O.Layout(40, 40, 256, 128)
     Gm, U, D = torch.randn(128, 256, generator=g) * 0.02, torch.randn(128, 256, generator=g) * 0.02, torch.randn(256, 128, generator=g) * 0.02
     assert np.array_equal(pack.pack_nvfp4_expert(Gm, U, D).numpy(), O.make_blob(L, Gm.numpy(), U.numpy(), D.numpy()))
+
+
+def test_expert_parallel_entry_host_side(lib):
+    """bsx_ep_layer's host logic without a GPU: NCCL is found in the process (torch loads it), the workspace size follows the
+    descriptor, bad descriptors are refused, and a null stream or communicator is an argument error before anything is launched."""
+    from basalt_b200 import moe
+    assert lib.bsx_ep_available() in (0, 1)
+    d = capi.EPLayerDesc()
+    d.layout = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, 2048, 512)
+    d.n_expert, d.top_k, d.gate_kind, d.n_group, d.topk_group, d.packed = 512, 10, capi.GATE_SOFTMAX, 1, 1, 1
+    d.e_lo, d.n_local, d.n_replicas, d.weight_scale = 128, 128, 0, 1.0
+    d.shared_blob = 4096
+    w4, w8 = lib.bsx_ep_layer_workspace_bytes(C.byref(d), 64, 4), lib.bsx_ep_layer_workspace_bytes(C.byref(d), 64, 8)
+    assert 0 < w4 < w8
+    assert lib.bsx_ep_layer_workspace_bytes(C.byref(d), 64, 16) == 0          # 16 x 64 x 10 pairs: beyond the plan's limit
+    d.e_lo = 448                                                               # the block would end past the last expert
+    assert lib.bsx_ep_layer_workspace_bytes(C.byref(d), 64, 4) == 0
+    d.e_lo = 128
+    assert lib.bsx_ep_layer(C.byref(d), None, None, capi.X_BF16, 64, None, None, None, None, None, None, None) == capi.E_STREAM
+    if lib.bsx_ep_available():
+        assert lib.bsx_ep_layer(C.byref(d), None, None, capi.X_BF16, 64, None, None, None, 1, None, None, None) == capi.E_POINTER
+    else:
+        assert lib.bsx_ep_layer(C.byref(d), None, None, capi.X_BF16, 64, None, None, None, 1, None, None, None) == capi.E_UNAVAILABLE
