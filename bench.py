@@ -433,6 +433,9 @@ def instrumented_pass(layers, xs, stream, steps, L, T):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         n = T * a.k
         ev[0].record(stream)
+        if ly.packed:
+            # the x images belong to the head of the step, where the one-call entry runs them beside the logits kernel
+            capi.check("x_images", lib.bsx_experts_packed_x_images(C.byref(ly.L), _p(x), _x_kind(x), T, n + T, _p(ly.scratch), st))
         capi.check("router", lib.bsx_router_x(_p(x), _x_kind(x), _p(ly.gate_w), _p(ly.bias), T, a.n_expert, a.n_embd, a.k, a.gate, a.weight_scale, a.n_group, a.topk_group, 0.0,
                                               None, 0, _p(ly.logits), _p(ly.ids), _p(ly.w), st))
         ev[1].record(stream)
@@ -444,7 +447,7 @@ def instrumented_pass(layers, xs, stream, steps, L, T):
             Lp.options = phase
             if ly.packed:
                 capi.check("experts", lib.bsx_experts_grouped_packed(C.byref(Lp), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
-                                                                      min(n, a.n_expert) + 1, n + T, _p(x), _x_kind(x), T, _p(ly.scratch), _p(ly.rows),
+                                                                      min(n, a.n_expert) + 1, n + T, _p(x), _x_kind(x), -T, _p(ly.scratch), _p(ly.rows),
                                                                       capi.OUT_F32, _p(ly.status), st))
             else:
                 capi.check("experts", lib.bsx_experts_grouped_rows(C.byref(Lp), _p(ly.ptr), _p(ly.start), _p(ly.n_groups), _p(ly.dst), _p(ly.tok),
@@ -494,7 +497,7 @@ def decode_line(args, w, T, r, world=1):
         gu_ms = r["stage_ms"]["experts_gate_up"]
         achieved = r["gu_bytes"] / (gu_ms * 1e-3) / 1e9
         line["roofline"] = {"bound": "hbm", "kernel": ("nvf4_stream_kernel<gate/up>" if use_packed else "nvfp4_mma_kernel<gate/up>") +
-                            " (routed + shared experts; stage time includes the activation-image kernel)", "achieved": achieved, "peak": pk["hbm"],
+                            " (routed + shared experts; the stage's CUDA events also span the one-block kernel that lists the passes)", "achieved": achieved, "peak": pk["hbm"],
                             "unit": "GB/s", "frac": achieved / pk["hbm"], "peak_source": pk["source"],
                             # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch of this workload at 64 tokens (seeded, so the same
                             # experts every run), from the ncu capture summarised in profiles/nvf4_stream_kernel_c1_t64.md; not measured by this run
