@@ -150,3 +150,71 @@ def test_ep_two_gpus_matches_single_gpu(lib):
         assert same, f"rank {rank}: all-to-all form differs from the single-GPU layer (max abs {err})"
         assert relc < 1e-5, f"rank {rank}: collective form differs from the single-GPU layer (relative L2 {relc})"
         assert stablec, f"rank {rank}: collective form not bit-stable from run to run"
+
+
+def _single_rank(port, q):
+    """one rank, one GPU: the expert-parallel entry with a communicator of size 1 must give the single-GPU layer's rows"""
+    try:
+        sys.path.insert(0, str(ROOT))
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        import torch.distributed as dist
+        from basalt_b200 import capi, ep, moe
+        torch.cuda.set_device(0)
+        dev = torch.device("cuda", 0)
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+        blobs, gate = _weights()
+        bd = torch.from_numpy(blobs).to(dev)
+        gw = torch.from_numpy(gate).to(dev)
+        L = moe.native_expert_layout(capi.TYPE_NVFP4, capi.TYPE_NVFP4, H, I)
+        args = moe.RouterArgs(n_expert=E, n_embd=H, k=K, weight_scale=1.0, gate=capi.GATE_SOFTMAX)
+        x = torch.randn((T, H), generator=torch.Generator(device=dev).manual_seed(5), device=dev).bfloat16()
+        comm = ep.NcclComm()
+        packed = moe.pack_experts(L, bd)
+        out = []
+        for pk, src in ((False, bd), (True, packed)):
+            single = moe.MoELayer(gw, None, src[:E], L, args, shared_blob=src[E], max_tokens=T, packed=pk)
+            want = single.forward(x).clone()
+            nat = ep.EPMoELayerNative(gw, None, src[:E], L, args, E, comm, shared_blob=src[E], max_tokens=T, packed=pk)
+            got = nat.forward(x).clone()
+            nat.check_status()
+            nat.capture(x)
+            rep = nat.forward_graphed(x).clone()
+            torch.cuda.synchronize()
+            out.append((float((got - want).norm() / want.norm()), bool(torch.equal(got.view(torch.int32), rep.view(torch.int32))),
+                        bool(torch.equal(nat_ids(nat, capi), single.ids[:T]))))
+            nat.graph.reset()
+            del nat
+        q.put(("ok", out))
+        comm.destroy()
+        dist.destroy_process_group()
+    except BaseException:
+        import traceback
+        q.put(("error", traceback.format_exc()))
+        raise
+
+
+def nat_ids(nat, capi):
+    """the ids the one-call step left in its workspace (bsx_ep_layer_views)"""
+    import ctypes as C
+    v = capi.MoELayerViews()
+    capi.check("bsx_ep_layer_views", capi.lib().bsx_ep_layer_views(C.byref(nat.desc), nat.max_tokens, nat.world, nat.workspace.data_ptr(), C.byref(v)))
+    n = nat.max_tokens * nat.args.k
+    off = (v.ids - nat.workspace.data_ptr()) // 4
+    return nat.workspace.view(torch.int32)[off:off + n].view(nat.max_tokens, nat.args.k)
+
+
+def test_ep_entry_with_one_rank_is_the_single_gpu_layer(lib, cuda):
+    """bsx_ep_layer on a communicator of one rank (every expert local, collectives of size one): the rows of the single-GPU layer
+    to fp32 rounding, the same routing, and a graph replay with the launched step's bits.  Runs on one GPU."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_single_rank, args=(29990 - os.getpid() % 80, q))
+    p.start()
+    res = q.get(timeout=180)
+    p.join(timeout=45)
+    if p.is_alive():
+        p.terminate()
+    assert res[0] == "ok", res[1]
+    for rel, same_graph, same_ids in res[1]:
+        assert rel < 1e-5 and same_graph and same_ids, res[1]
