@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstring>
 #include <cstdlib>
 #include <vector>
 
@@ -80,6 +81,30 @@ int main(int argc, char** argv) {
     native_moe_combine_multi(d_rows, d_w, nullptr, d_y, H, k, T, st);
     CK(cudaStreamSynchronize(st));
 
+    // ---- the same window as ONE call (bsx_moe_layer): fp32 rows in, the layer's rows out, everything else in a workspace.
+    // With the blobs in place and fp32 activations the experts run the fp16-image kernels, so the rows differ from the q8_1
+    // sequence above by that rounding only; the routing is the same to the bit.
+    bsx_moe_layer_desc ld;
+    std::memset(&ld, 0, sizeof ld);
+    if (bsx_expert_layout_init(40, 40, -1, H, I, 0.f, 0.f, 0.f, &ld.layout) != 0) return 4;
+    ld.n_expert = E; ld.top_k = k; ld.gate_kind = BSX_GATE_SIGMOID; ld.n_group = 1; ld.topk_group = 1; ld.packed = 0;
+    ld.weight_scale = 2.5f;
+    ld.gate = d_gate; ld.blob_table = d_table;
+    const size_t ws_bytes = bsx_moe_layer_workspace_bytes(&ld, T);
+    if (!ws_bytes) return 4;
+    uint8_t* d_ws = dev_alloc<uint8_t>(ws_bytes);
+    float* d_y1 = dev_alloc<float>((size_t) T * H);
+    int32_t* d_st1 = dev_alloc<int32_t>(4);
+    const int rc1 = bsx_moe_layer(&ld, d_x, BSX_X_F32, T, T, nullptr, d_ws, d_y1, d_st1, st);
+    if (rc1 != 0) { std::fprintf(stderr, "bsx_moe_layer: %d\n", rc1); return 4; }
+    CK(cudaStreamSynchronize(st));
+    bsx_moe_layer_views_t lv;
+    if (bsx_moe_layer_views(&ld, T, d_ws, &lv) != 0) return 4;
+    std::vector<int32_t> ids1(n);
+    std::vector<float> y1((size_t) T * H);
+    CK(cudaMemcpy(ids1.data(), lv.ids, (size_t) n * 4, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(y1.data(), d_y1, y1.size() * 4, cudaMemcpyDeviceToHost));
+
     // ---- the prompt path on the same layer: rows grouped by expert (fused::group), then the experts in groups of 16
     namespace pf = basalt::prefill;
     uint8_t* d_gscr = dev_alloc<uint8_t>(pf::fused::group_bytes(n, E));
@@ -131,6 +156,8 @@ int main(int argc, char** argv) {
     std::fwrite(w.data(), 4, w.size(), o);
     std::fwrite(y.data(), 4, y.size(), o);
     std::fwrite(dm.data(), 4, dm.size(), o);
+    std::fwrite(ids1.data(), 4, ids1.size(), o);
+    std::fwrite(y1.data(), 4, y1.size(), o);
     std::fclose(o);
     std::puts("shim gpu ok");
     return 0;

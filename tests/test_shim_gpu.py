@@ -43,10 +43,15 @@ def test_cpp_caller_through_the_shim_on_the_gpu(lib, cuda, tmp_path):
     assert out.returncode == 0, out.stdout + out.stderr
     raw = np.fromfile(tmp_path / "out.bin", np.uint8)
     n = T * k
-    sizes = [T * E * 4, n * 4, n * 4, T * H * 4, n * H * 4]
+    sizes = [T * E * 4, n * 4, n * 4, T * H * 4, n * H * 4, n * 4, T * H * 4]
     parts = np.split(raw, np.cumsum(sizes)[:-1])
     c_logits, c_ids, c_w = parts[0].view(np.float32).reshape(T, E), parts[1].view(np.int32).reshape(T, k), parts[2].view(np.float32).reshape(T, k)
     c_y, c_dm = parts[3].view(np.float32).reshape(T, H), parts[4].view(np.float32).reshape(n, H)
+    # the one-call layer from C++ (bsx_moe_layer): the routing of the call-by-call sequence to the bit, and the bits of the same
+    # call made through ctypes; its rows sit within the q8_1 rounding (1e-2) of the call-by-call sequence's
+    c_ids1, c_y1 = parts[5].view(np.int32).reshape(T, k), parts[6].view(np.float32).reshape(T, H)
+    assert np.array_equal(c_ids1, c_ids)
+    assert rel_l2(c_y1, c_y) < 3e-2
     # the same calls through ctypes
     a = moe.RouterArgs(n_expert=E, n_embd=H, k=k, weight_scale=2.5, gate=capi.GATE_SIGMOID)
     dx, bd = dev(x), dev(sb)
@@ -63,6 +68,9 @@ def test_cpp_caller_through_the_shim_on_the_gpu(lib, cuda, tmp_path):
     assert np.array_equal(c_logits.view(np.uint32), lg.cpu().numpy().view(np.uint32))
     assert np.array_equal(c_ids, ids.cpu().numpy()) and np.array_equal(c_w.view(np.uint32), w.cpu().numpy().view(np.uint32))
     assert np.array_equal(c_y.view(np.uint32), y.cpu().numpy().view(np.uint32))
+    one = moe.NativeMoELayer(dev(gate), None, bd, L, a, max_tokens=T)
+    y_one = one.forward(dx).cpu().numpy()
+    assert np.array_equal(c_y1.view(np.uint32), y_one.view(np.uint32))
     # the prompt path's rows: the dispatch + bsx_experts_prefill through ctypes give the same bits, and the oracle agrees
     cnt, off, slot, src, tiles, n_tiles = moe.dispatch(ids.reshape(-1), k, E, tile_rows=128)
     dm, status = moe.experts_prefill(L, table, off, src, tiles, n_tiles, dx, n)
